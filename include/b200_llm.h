@@ -1,0 +1,145 @@
+/* C ABI of the B200 token-loop library (libb200llm.so).
+ *
+ * It replaces, for the language model's token loop only, what the reference's Go host
+ * reaches through its Vulkan cgo layer: the method set of `llm.Graph` that
+ * `backend/llm.go` and `backend/llm_sched.go` call. Plain pointers and sizes only; every
+ * function returns a status (0 = ok) and leaves a message for b200_last_error().
+ *
+ * Threading: calls on one handle must be serialised by the caller (the reference runs
+ * them from a single goroutine inside Device.Do, backend/device.go:23-81). The library
+ * binds its device at every entry, so calls may arrive on any OS thread.
+ *
+ * Ownership: weights are copied to the device when added (the caller may unmap its
+ * checkpoint afterwards). Returned logits / hidden pointers are pinned host buffers owned
+ * by the graph, valid until the next call on the same graph (llm/graph.go:1382,1546).
+ */
+#ifndef B200_LLM_H
+#define B200_LLM_H
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  B200_OK = 0,
+  B200_EINVAL = 1,    /* refused before anything was launched: bad shape, id, slot, state */
+  B200_ECAPACITY = 2, /* more rows / cells / slots than the graph was created for */
+  B200_ECUDA = 3,     /* a CUDA call failed; the message carries cudaGetErrorString */
+  B200_ENCCL = 4,
+  B200_ETIMEOUT = 5,
+  B200_ESTATE = 6,    /* call order violated (e.g. Keep without a speculative pass) */
+  B200_ENOMEM = 7,
+  B200_EIO = 8
+};
+
+/* Hyper-parameters, read by the host from GGUF metadata the way llm/model.go:66-96,
+ * 375-407, 441-468 reads them. */
+typedef struct {
+  int32_t n_layer, n_embd, vocab;
+  int32_t n_head, n_head_kv, head_dim, rope_dims;
+  float rope_base, eps;
+  int32_t n_expert, n_expert_used, ffn_expert, ffn_shared;
+  int32_t dn_head_dim, dn_heads_k, dn_heads_v, dn_conv;
+  int32_t has_draft; /* 1: blk.<n_layer>.* is an MTP draft layer (llm/mtp.go:36-48) */
+} b200_config;
+
+/* Mirrors llm.GraphOpts (llm/graph.go:57-126). */
+typedef struct {
+  int32_t max_tokens;  /* rows per pass; longer inputs are cut into chunks (MaxTokens) */
+  int32_t n_kv;        /* cells per slot (NKV) */
+  int32_t slots;       /* independent sequences (Slots) */
+  int32_t speculative; /* keep per-row state planes so Keep(k) can pick a prefix (Speculative) */
+  int32_t spec_rows;   /* largest verify pass, depth + 1 (SpecRows) */
+  int32_t attn_split_cells; /* cells per split of the decode attention; 0 = default */
+  int32_t use_cuda_graph;   /* 1: replay single-token passes as a captured CUDA graph (vk.Prerecorded) */
+  int32_t trace;            /* 1: keep per-layer hidden states and routing for b200_graph_trace */
+} b200_graph_opts;
+
+typedef struct b200_model b200_model;
+typedef struct b200_graph b200_graph;
+
+const char* b200_last_error(void);
+int32_t b200_device_count(void);
+
+/* ---- checkpoint (replaces the weight staging of llm.NewGraph, llm/graph.go:609-876) ---- */
+int32_t b200_model_new(const b200_config* cfg, int32_t device, b200_model** out);
+/* One GGUF tensor: ggml type id, dims in ggml order (dims[0] = row length), host bytes in the
+ * file's own block layout (gguf.Tensor.Data, gguf/gguf.go:175-244). */
+int32_t b200_model_add_tensor(b200_model* m, const char* name, uint32_t type, uint32_t n_dims, const int64_t* dims, const void* host_data);
+/* A synthetic tensor generated and quantised on the device: rule 0 = normal(p0, p1),
+ * rule 1 = -exp(uniform(p0, p1)). Used by the benchmark for checkpoints too large to ship. */
+int32_t b200_model_add_synthetic(b200_model* m, const char* name, uint32_t type, uint32_t n_dims, const int64_t* dims, uint64_t seed, int32_t rule, float p0, float p1);
+int32_t b200_model_finalize(b200_model* m);
+/* Parses a GGUF v2/v3 file (gguf/gguf.go:265-403) and adds every tensor. */
+int32_t b200_model_open_gguf(const char* path, int32_t device, b200_model** out);
+int32_t b200_model_config(const b200_model* m, b200_config* out);
+int64_t b200_model_weight_bytes(const b200_model* m);
+/* Tensor bytes back in GGUF block layout (for checking synthetic checkpoints on the host). */
+int64_t b200_model_tensor_bytes(const b200_model* m, const char* name);
+int32_t b200_model_read_tensor(const b200_model* m, const char* name, void* dst, int64_t nbytes);
+void b200_model_free(b200_model* m);
+
+/* ---- graph: llm.Graph's method set ---------------------------------------------------- */
+int32_t b200_graph_create(b200_model* m, const b200_graph_opts* opts, b200_graph** out); /* NewGraph  llm/graph.go:609 */
+void b200_graph_destroy(b200_graph* g);                                                    /* Destroy   :2534 */
+int32_t b200_graph_slots(const b200_graph* g);                                             /* Slots     :902 */
+int32_t b200_graph_nkv(const b200_graph* g);                                               /* NKV       :881 */
+int32_t b200_graph_use_slot(b200_graph* g, int32_t slot);                                  /* UseSlot   :916 */
+int32_t b200_graph_reset(b200_graph* g);                                                   /* Reset     :1079 */
+int32_t b200_graph_past(const b200_graph* g);
+/* Forward = Reset + Extend (:1695). logits: [vocab] of the last row; hidden: [n_embd] output-normed last row. */
+int32_t b200_graph_forward(b200_graph* g, const int32_t* ids, int32_t n, const float** logits, const float** hidden);
+int32_t b200_graph_extend(b200_graph* g, const int32_t* ids, int32_t n, const float** logits, const float** hidden); /* Extend :1709 */
+/* Every row's logits [n][vocab] and residual [n][n_embd]; n <= spec_rows when speculating (ExtendRows :1383). */
+int32_t b200_graph_extend_rows(b200_graph* g, const int32_t* ids, int32_t n, const float** logits, const float** residual);
+/* Last row's logits plus every row's residual (ExtendResidual :1468). */
+int32_t b200_graph_extend_residual(b200_graph* g, const int32_t* ids, int32_t n, const float** logits, const float** residual);
+/* One token for each of n distinct slots in one pass; logits [n][vocab] (DecodeRows :1527, llm/batch.go:45-63). */
+int32_t b200_graph_decode_rows(b200_graph* g, const int32_t* slots, const int32_t* ids, int32_t n, const float** logits);
+/* Sequence checkpoints (Checkpoint/Restore :1004,:1037): DeltaNet state + conv rings of the
+ * current slot; KV cells below the mark stay in place. */
+int32_t b200_graph_checkpoint(b200_graph* g, int32_t* handle_out);
+int32_t b200_graph_restore(b200_graph* g, int32_t handle);
+int32_t b200_graph_checkpoint_free(b200_graph* g, int32_t handle);
+/* Speculation (Speculate/Keep/Commit/Rewind :1122-1302). */
+int32_t b200_graph_speculate(b200_graph* g, int32_t on);
+int32_t b200_graph_keep(b200_graph* g, int32_t k);
+int32_t b200_graph_commit(b200_graph* g);
+int32_t b200_graph_rewind(b200_graph* g);
+
+/* Device-resident greedy decoding: only token ids cross the bus. Each of n slots advances
+ * `steps` tokens starting from first_ids; out_ids is [steps][n]. */
+int32_t b200_graph_generate_greedy(b200_graph* g, const int32_t* slots, const int32_t* first_ids, int32_t n, int32_t steps, int32_t* out_ids);
+/* Milliseconds of device time of the last generate_greedy call (CUDA events on its stream). */
+float b200_graph_last_device_ms(const b200_graph* g);
+/* Kernel launches issued by the last pass (or per step of the last generate_greedy). */
+int32_t b200_graph_last_launches(const b200_graph* g);
+
+/* Trace of the last pass (opts.trace = 1): what = 0 residual after the token mixer
+ * [n_layer][rows][n_embd], 1 residual after the MoE block, 2 routed experts
+ * [n_layer][rows][used] (int32), 3 routing weights [n_layer][rows][used+1], 4 top-k margin
+ * [n_layer][rows]. Returns bytes written or a negative status. */
+int64_t b200_graph_trace(b200_graph* g, int32_t what, void* dst, int64_t nbytes);
+
+/* ---- MTP draft head (llm.MTPHead, llm/mtp.go:441-760) ---------------------------------- */
+/* One draft step per row: seeds from residual rows hs [n][n_embd] and token ids (the tokens
+ * one position ahead), runs the draft layer on the current slot's draft cache, returns the
+ * draft's residual [n][n_embd] and logits over the first `vocab_k` ids [n][vocab_k]. */
+int32_t b200_draft_rows(b200_graph* g, const float* hs, const int32_t* ids, int32_t n, int32_t vocab_k, const float** residual, const float** logits);
+int32_t b200_draft_past(const b200_graph* g);
+int32_t b200_draft_rewind(b200_graph* g, int32_t past);
+
+/* ---- unit entry points used by the parity tests ------------------------------------------ */
+/* n elements of `type` in GGUF block layout -> f32 through the device layout and the device
+ * dequantiser (bit-exact with gguf/dequant.go:54-100). */
+int32_t b200_dequantize(uint32_t type, const void* host_data, int64_t n, float* host_out);
+/* y[m][rows] = W[rows][k] . fp16(x[m][k]) through the fused K-quant projection kernel. */
+int32_t b200_qgemv(uint32_t type, const void* host_w, int64_t rows, int64_t k, const float* host_x, int32_t m, float* host_y);
+/* The repo's quantiser on the device (llm/quantk.go:87-179): rows x k f32 -> GGUF blocks. */
+int32_t b200_quantize(uint32_t type, const float* host_src, int64_t rows, int64_t k, void* host_dst);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,219 @@
+// extern "C" surface of libb200llm.so (include/b200_llm.h).
+#include <cstring>
+#include <new>
+
+#include "graph.h"
+
+using namespace b200;
+
+struct b200_model { Model m; };
+struct b200_graph { Graph g; };
+
+extern "C" {
+
+const char* b200_last_error(void) { return last_error(); }
+
+int32_t b200_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) return 0;
+  return n;
+}
+
+int32_t b200_model_new(const b200_config* cfg, int32_t device, b200_model** out) {
+  if (!cfg || !out) { set_error("model_new: null argument"); return EINVAL_; }
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) { set_error("no CUDA device: this library has no CPU path"); return ECUDA; }
+  if (device < 0 || device >= n) { set_error("model_new: no such device"); return EINVAL_; }
+  auto* m = new (std::nothrow) b200_model();
+  if (!m) return ENOMEM_;
+  m->m.c = *cfg; m->m.device = device;
+  *out = m;
+  return OK;
+}
+int32_t b200_model_add_tensor(b200_model* m, const char* name, uint32_t type, uint32_t n_dims, const int64_t* dims, const void* host) {
+  if (!m || !name || !dims || !host) { set_error("add_tensor: null argument"); return EINVAL_; }
+  return m->m.add_host(name, type, n_dims, dims, host);
+}
+int32_t b200_model_add_synthetic(b200_model* m, const char* name, uint32_t type, uint32_t n_dims, const int64_t* dims, uint64_t seed, int32_t rule, float p0, float p1) {
+  if (!m || !name || !dims) { set_error("add_synthetic: null argument"); return EINVAL_; }
+  return m->m.add_synthetic(name, type, n_dims, dims, seed, rule, p0, p1);
+}
+int32_t b200_model_finalize(b200_model* m) { if (!m) { set_error("null model"); return EINVAL_; } return m->m.finalize(); }
+int32_t b200_model_open_gguf(const char* path, int32_t device, b200_model** out) {
+  if (!path || !out) { set_error("open_gguf: null argument"); return EINVAL_; }
+  auto* bm = new (std::nothrow) b200_model();
+  if (!bm) return ENOMEM_;
+  int s = load_gguf_into(path, device, &bm->m);
+  if (s != OK) { delete bm; return s; }
+  *out = bm;
+  return OK;
+}
+int32_t b200_model_config(const b200_model* m, b200_config* out) { if (!m || !out) return EINVAL_; *out = m->m.c; return OK; }
+int64_t b200_model_weight_bytes(const b200_model* m) { return m ? m->m.weight_bytes : 0; }
+int64_t b200_model_tensor_bytes(const b200_model* m, const char* name) {
+  if (!m || !name) return -1;
+  auto it = m->m.tensors.find(name);
+  if (it == m->m.tensors.end()) return -1;
+  return gguf_row_bytes(it->second.type, it->second.k) * it->second.rows;
+}
+int32_t b200_model_read_tensor(const b200_model* m, const char* name, void* dst, int64_t nbytes) {
+  if (!m || !name || !dst) { set_error("read_tensor: null argument"); return EINVAL_; }
+  return m->m.read_tensor(name, dst, nbytes);
+}
+void b200_model_free(b200_model* m) { delete m; }
+
+int32_t b200_graph_create(b200_model* m, const b200_graph_opts* opts, b200_graph** out) {
+  if (!m || !opts || !out) { set_error("graph_create: null argument"); return EINVAL_; }
+  auto* g = new (std::nothrow) b200_graph();
+  if (!g) return ENOMEM_;
+  int s = g->g.init(&m->m, *opts);
+  if (s != OK) { delete g; return s; }
+  *out = g;
+  return OK;
+}
+void b200_graph_destroy(b200_graph* g) { delete g; }
+int32_t b200_graph_slots(const b200_graph* g) { return g ? g->g.o.slots : 0; }
+int32_t b200_graph_nkv(const b200_graph* g) { return g ? g->g.o.n_kv : 0; }
+int32_t b200_graph_use_slot(b200_graph* g, int32_t slot) {
+  if (!g) return EINVAL_;
+  if (slot < 0 || slot >= g->g.o.slots) { set_error("use_slot: slot " + std::to_string(slot) + " does not exist"); return EINVAL_; }
+  g->g.cur = slot; g->g.spec_n = 0;
+  return OK;
+}
+int32_t b200_graph_reset(b200_graph* g) { if (!g) return EINVAL_; return g->g.reset_slot(g->g.cur); }
+int32_t b200_graph_past(const b200_graph* g) { return g ? g->g.past[g->g.cur] : 0; }
+
+int32_t b200_graph_forward(b200_graph* g, const int32_t* ids, int32_t n, const float** logits, const float** hidden) {
+  if (!g || !ids) { set_error("forward: null argument"); return EINVAL_; }
+  B200_TRY(g->g.reset_slot(g->g.cur));
+  PassFlags f;
+  return g->g.extend(ids, n, f, logits, hidden);
+}
+int32_t b200_graph_extend(b200_graph* g, const int32_t* ids, int32_t n, const float** logits, const float** hidden) {
+  if (!g || !ids) { set_error("extend: null argument"); return EINVAL_; }
+  PassFlags f;
+  return g->g.extend(ids, n, f, logits, hidden);
+}
+int32_t b200_graph_extend_rows(b200_graph* g, const int32_t* ids, int32_t n, const float** logits, const float** residual) {
+  if (!g || !ids) { set_error("extend_rows: null argument"); return EINVAL_; }
+  PassFlags f; f.want_all_logits = true; f.want_residual = true; f.spec = g->g.speculating;
+  return g->g.extend(ids, n, f, logits, residual);
+}
+int32_t b200_graph_extend_residual(b200_graph* g, const int32_t* ids, int32_t n, const float** logits, const float** residual) {
+  if (!g || !ids) { set_error("extend_residual: null argument"); return EINVAL_; }
+  PassFlags f; f.want_residual = true;
+  return g->g.extend(ids, n, f, logits, residual);
+}
+int32_t b200_graph_decode_rows(b200_graph* g, const int32_t* slots, const int32_t* ids, int32_t n, const float** logits) {
+  if (!g || !slots || !ids) { set_error("decode_rows: null argument"); return EINVAL_; }
+  return g->g.decode_rows(slots, ids, n, logits);
+}
+int32_t b200_graph_checkpoint(b200_graph* g, int32_t* handle) { if (!g || !handle) return EINVAL_; return g->g.checkpoint(handle); }
+int32_t b200_graph_restore(b200_graph* g, int32_t handle) { if (!g) return EINVAL_; return g->g.restore(handle); }
+int32_t b200_graph_checkpoint_free(b200_graph* g, int32_t handle) {
+  if (!g) return EINVAL_;
+  auto it = g->g.ckpts.find(handle);
+  if (it == g->g.ckpts.end()) { set_error("checkpoint_free: unknown checkpoint"); return EINVAL_; }
+  cudaSetDevice(g->g.m->device);
+  for (float* p : it->second.state) cudaFree(p);
+  for (float* p : it->second.ring) cudaFree(p);
+  g->g.ckpts.erase(it);
+  return OK;
+}
+int32_t b200_graph_speculate(b200_graph* g, int32_t on) {
+  if (!g) return EINVAL_;
+  if (on && !g->g.o.speculative) { set_error("speculate: the graph was created with speculative = 0"); return ESTATE; }
+  g->g.speculating = on != 0;
+  return OK;
+}
+int32_t b200_graph_keep(b200_graph* g, int32_t k) { if (!g) return EINVAL_; return g->g.keep(k); }
+int32_t b200_graph_commit(b200_graph* g) { if (!g) return EINVAL_; return g->g.keep(g->g.spec_n); }
+int32_t b200_graph_rewind(b200_graph* g) { if (!g) return EINVAL_; return g->g.keep(0); }
+
+int32_t b200_graph_generate_greedy(b200_graph* g, const int32_t* slots, const int32_t* first_ids, int32_t n, int32_t steps, int32_t* out_ids) {
+  if (!g || !slots || !first_ids || !out_ids) { set_error("generate_greedy: null argument"); return EINVAL_; }
+  return g->g.generate_greedy(slots, first_ids, n, steps, out_ids);
+}
+float b200_graph_last_device_ms(const b200_graph* g) { return g ? g->g.last_ms : 0.f; }
+int32_t b200_graph_last_launches(const b200_graph* g) { return g ? g->g.last_launches : 0; }
+int64_t b200_graph_trace(b200_graph* g, int32_t what, void* dst, int64_t nbytes) { if (!g || !dst) return -EINVAL_; return g->g.trace(what, dst, nbytes); }
+
+int32_t b200_draft_rows(b200_graph* g, const float* hs, const int32_t* ids, int32_t n, int32_t vocab_k, const float** residual, const float** logits) {
+  if (!g || !hs || !ids) { set_error("draft_rows: null argument"); return EINVAL_; }
+  return g->g.draft_rows(hs, ids, n, vocab_k, residual, logits);
+}
+int32_t b200_draft_past(const b200_graph* g) { return g ? g->g.draft_past[g->g.cur] : 0; }
+int32_t b200_draft_rewind(b200_graph* g, int32_t past) {
+  if (!g) return EINVAL_;
+  if (past < 0 || past > g->g.draft_past[g->g.cur]) { set_error("draft_rewind: position outside the draft cache"); return EINVAL_; }
+  g->g.draft_past[g->g.cur] = past;
+  return OK;
+}
+
+// ---- unit entry points --------------------------------------------------------------------
+static int need_device() {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) { set_error("no CUDA device: this library has no CPU path"); return ECUDA; }
+  return OK;
+}
+
+int32_t b200_dequantize(uint32_t type, const void* host_data, int64_t n, float* host_out) {
+  B200_TRY(need_device());
+  int e, nb;
+  if (!host_data || !host_out || !block_geometry(type, &e, &nb) || n % e || n <= 0) { set_error("dequantize: bad type or element count"); return EINVAL_; }
+  const int64_t bytes = gguf_row_bytes(type, n);
+  DTensor t; t.type = type; t.k = n; t.rows = 1; t.stride = device_row_stride(type, n);
+  uint8_t *src = nullptr; float* out = nullptr;
+  B200_CUDA(cudaMalloc((void**)&src, (size_t)bytes));
+  B200_CUDA(cudaMalloc((void**)&t.data, (size_t)t.stride + 256));
+  B200_CUDA(cudaMalloc((void**)&out, (size_t)n * sizeof(float)));
+  int s = cudaMemcpy(src, host_data, (size_t)bytes, cudaMemcpyHostToDevice) == cudaSuccess ? OK : ECUDA;
+  if (s == OK) s = repack_rows(type, n, 1, src, t.data, 0);
+  if (s == OK) s = dequant_rows(t, 0, 1, out, 0);
+  if (s == OK && cudaMemcpy(host_out, out, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) { set_error("dequantize: copy back failed"); s = ECUDA; }
+  cudaFree(src); cudaFree(t.data); cudaFree(out);
+  return s;
+}
+
+int32_t b200_qgemv(uint32_t type, const void* host_w, int64_t rows, int64_t k, const float* host_x, int32_t mrows, float* host_y) {
+  B200_TRY(need_device());
+  if (!host_w || !host_x || !host_y || rows <= 0 || mrows <= 0) { set_error("qgemv: bad argument"); return EINVAL_; }
+  const int64_t rb = gguf_row_bytes(type, k);
+  if (rb < 0) { set_error("qgemv: bad type or row length"); return EINVAL_; }
+  DTensor t; t.type = type; t.k = k; t.rows = rows; t.stride = device_row_stride(type, k);
+  uint8_t* src = nullptr; float *xf = nullptr, *y = nullptr; __half* x16 = nullptr;
+  B200_CUDA(cudaMalloc((void**)&src, (size_t)(rb * rows)));
+  B200_CUDA(cudaMalloc((void**)&t.data, (size_t)(t.stride * rows) + 256));
+  B200_CUDA(cudaMalloc((void**)&xf, (size_t)mrows * k * sizeof(float)));
+  B200_CUDA(cudaMalloc((void**)&x16, (size_t)mrows * k * sizeof(__half)));
+  B200_CUDA(cudaMalloc((void**)&y, (size_t)mrows * rows * sizeof(float)));
+  int s = OK;
+  if (cudaMemcpy(src, host_w, (size_t)(rb * rows), cudaMemcpyHostToDevice) != cudaSuccess || cudaMemcpy(xf, host_x, (size_t)mrows * k * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess) s = ECUDA;
+  if (s == OK) s = repack_rows(type, k, rows, src, t.data, 0);
+  if (s == OK) s = quantize_rows_device(T_F16, xf, mrows, k, (uint8_t*)x16, 0);
+  if (s == OK) {
+    QGemvParams p{};
+    p.w[0] = t.data; p.seg_end[0] = (int)rows; p.nseg = 1; p.stride = t.stride; p.K = (int)k; p.N = (int)rows; p.M = mrows; p.xcols = mrows < QG_MAXCOLS ? mrows : QG_MAXCOLS;
+    p.x = x16; p.ldx = k; p.y = y; p.ldy = rows; p.x_div = 1;
+    s = launch_qgemv(type, PRO_F16, EPI_STORE, false, false, p, 0, false, 0);
+  }
+  if (s == OK && cudaMemcpy(host_y, y, (size_t)mrows * rows * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) { set_error(std::string("qgemv: ") + cudaGetErrorString(cudaGetLastError())); s = ECUDA; }
+  cudaFree(src); cudaFree(t.data); cudaFree(xf); cudaFree(x16); cudaFree(y);
+  return s;
+}
+
+int32_t b200_quantize(uint32_t type, const float* host_src, int64_t rows, int64_t k, void* host_dst) {
+  B200_TRY(need_device());
+  const int64_t rb = gguf_row_bytes(type, k);
+  if (!host_src || !host_dst || rb < 0 || rows <= 0) { set_error("quantize: bad argument"); return EINVAL_; }
+  float* f = nullptr; uint8_t* q = nullptr;
+  B200_CUDA(cudaMalloc((void**)&f, (size_t)rows * k * sizeof(float)));
+  B200_CUDA(cudaMalloc((void**)&q, (size_t)(rb * rows)));
+  int s = cudaMemcpy(f, host_src, (size_t)rows * k * sizeof(float), cudaMemcpyHostToDevice) == cudaSuccess ? OK : ECUDA;
+  if (s == OK) s = quantize_rows_device(type, f, rows, k, q, 0);
+  if (s == OK && cudaMemcpy(host_dst, q, (size_t)(rb * rows), cudaMemcpyDeviceToHost) != cudaSuccess) { set_error("quantize: copy back failed"); s = ECUDA; }
+  cudaFree(f); cudaFree(q);
+  return s;
+}
+
+}  // extern "C"

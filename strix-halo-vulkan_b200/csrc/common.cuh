@@ -1,0 +1,116 @@
+// Shared declarations of the B200 token-loop library: status codes, ggml type ids,
+// device-side tensor descriptors and small device helpers.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+namespace b200 {
+
+enum Status : int32_t { OK = 0, EINVAL_ = 1, ECAPACITY = 2, ECUDA = 3, ENCCL = 4, ETIMEOUT = 5, ESTATE = 6, ENOMEM_ = 7, EIO_ = 8 };
+
+// ggml tensor types (reference: gguf/gguf.go:53-88)
+enum : uint32_t { T_F32 = 0, T_F16 = 1, T_Q4_1 = 3, T_Q5_0 = 6, T_Q5_1 = 7, T_Q8_0 = 8, T_Q4_K = 12, T_Q5_K = 13, T_Q6_K = 14, T_IQ4_NL = 20, T_BF16 = 30 };
+
+bool block_geometry(uint32_t type, int* elems, int* nbytes);  // reference: gguf/gguf.go:101-134
+int64_t gguf_row_bytes(uint32_t type, int64_t n);
+
+// A weight matrix on the device. Q4_K / Q5_K keep the checkpoint's own 144 / 176-byte
+// super-blocks (16-byte aligned). Q6_K and Q8_0 blocks are 210 / 34 bytes, which no
+// 128-bit load can address, so each ROW is re-laid as planes (same bytes, permuted):
+//   Q6_K row of nb blocks: ql[nb][128] | qh[nb][64] | scales[nb][16] | d[nb] (fp16)
+//   Q8_0 row of nb blocks: qs[nb][32] | d[nb] (fp16)
+// with the row stride rounded up to 16 bytes.
+struct DTensor {
+  uint32_t type = 0;
+  int64_t k = 0;        // row length (ggml dims[0])
+  int64_t rows = 0;     // product of the remaining dims
+  int64_t stride = 0;   // bytes per row on the device
+  uint8_t* data = nullptr;
+  bool ok() const { return data != nullptr; }
+};
+
+void set_error(const std::string& s);
+const char* last_error();
+
+#define B200_CUDA(expr)                                                                          \
+  do {                                                                                           \
+    cudaError_t _e = (expr);                                                                     \
+    if (_e != cudaSuccess) {                                                                     \
+      b200::set_error(std::string(#expr) + ": " + cudaGetErrorString(_e));                       \
+      return b200::ECUDA;                                                                        \
+    }                                                                                            \
+  } while (0)
+
+#define B200_TRY(expr)                   \
+  do {                                   \
+    int _s = (expr);                     \
+    if (_s != b200::OK) return _s;       \
+  } while (0)
+
+#ifdef __CUDACC__
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid_acc(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Programmatic dependent launch: wait for the producer grid's memory, and let the
+// consumer grid start its prologue.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// D = A(16x16, row) * B(16x8, col) + C, fp16 inputs, f32 accumulate.
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t hfma2_u(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ uint32_t hmul2_u(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t hadd2_u(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t lop3_or_and(uint32_t a, uint32_t mask, uint32_t orv) {  // (a & mask) | orv
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(orv));
+  return d;
+}
+__device__ __forceinline__ uint32_t lop3_or_andb(uint32_t a, uint32_t b, uint32_t mask) {  // a | (b & mask)
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xF8;" : "=r"(d) : "r"(a), "r"(b), "r"(mask));
+  return d;
+}
+__device__ __forceinline__ float h2f_lo(uint32_t h2) { return __half2float(__ushort_as_half((unsigned short)(h2 & 0xffff))); }
+__device__ __forceinline__ float h2f_hi(uint32_t h2) { return __half2float(__ushort_as_half((unsigned short)(h2 >> 16))); }
+#endif
+
+}  // namespace b200

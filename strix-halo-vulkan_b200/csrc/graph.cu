@@ -1,0 +1,522 @@
+// Pass scheduling of the token loop (see graph.h). Layer order follows the reference's
+// layers() loop (llm/graph.go:2330-2466) with a plain pre-norm residual stream in place of
+// its hyper-connection mixers.
+#include "graph.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+namespace b200 {
+
+template <class T>
+int Graph::dalloc(T** p, size_t n, bool zero) {
+  void* q = nullptr;
+  size_t bytes = std::max<size_t>(n, 1) * sizeof(T);
+  cudaError_t e = cudaMalloc(&q, bytes);
+  if (e != cudaSuccess) { set_error(std::string("graph: device allocation of ") + std::to_string(bytes) + " bytes failed: " + cudaGetErrorString(e)); return ENOMEM_; }
+  if (zero) B200_CUDA(cudaMemset(q, 0, bytes));
+  allocs.push_back(q);
+  *p = (T*)q;
+  return OK;
+}
+
+Graph::~Graph() {
+  if (m) cudaSetDevice(m->device);
+  if (st) cudaStreamSynchronize(st);
+  for (auto& kv : decode_graphs) cudaGraphExecDestroy(kv.second);
+  for (auto& kv : greedy_graphs) cudaGraphExecDestroy(kv.second);
+  for (auto& kv : ckpts) { for (float* p : kv.second.state) cudaFree(p); for (float* p : kv.second.ring) cudaFree(p); }
+  for (void* p : allocs) cudaFree(p);
+  if (stage) cudaFreeHost(stage);
+  if (logits_host) cudaFreeHost(logits_host);
+  if (resid_host) cudaFreeHost(resid_host);
+  if (hidden_host) cudaFreeHost(hidden_host);
+  if (ids_host) cudaFreeHost(ids_host);
+  if (ev0) cudaEventDestroy(ev0);
+  if (ev1) cudaEventDestroy(ev1);
+  if (st) cudaStreamDestroy(st);
+}
+
+int Graph::init(Model* model, const b200_graph_opts& opts) {
+  m = model; o = opts;
+  if (!m->finalized) { set_error("graph: model is not finalized"); return ESTATE; }
+  const b200_config& c = m->c;
+  if (o.max_tokens <= 0) o.max_tokens = 64;
+  if (o.slots <= 0) o.slots = 1;
+  if (o.n_kv <= 0) { set_error("graph: n_kv must be positive"); return EINVAL_; }
+  if (o.speculative && o.spec_rows <= 0) o.spec_rows = 3;
+  if (o.spec_rows > DN_RING - 3) { set_error("graph: spec_rows is limited to 5 (the conv ring keeps 8 positions)"); return ECAPACITY; }
+  MR = std::min(o.max_tokens, 512);
+  split_cells = o.attn_split_cells > 0 ? o.attn_split_cells : 128;
+  nsplit = (o.n_kv + split_cells - 1) / split_cells;
+  B200_CUDA(cudaSetDevice(m->device));
+  B200_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+  B200_CUDA(cudaEventCreate(&ev0));
+  B200_CUDA(cudaEventCreate(&ev1));
+  const int H = c.n_embd, D = c.dn_head_dim, qk = c.dn_heads_k * D, vw = c.dn_heads_v * D, cw = 2 * qk + vw;
+  const int hd = c.head_dim, qw = c.n_head * hd, kvw = c.n_head_kv * hd, used = c.n_expert_used, slots1 = used + 1;
+  proj_ld = std::max(cw + vw, 2 * qw + 2 * kvw);
+  const int nl = (int)m->layers.size();
+  dn_index.assign(nl, -1); attn_index.assign(nl, -1);
+  for (int l = 0; l < nl; l++) {
+    if (m->layers[l].is_attn) attn_index[l] = n_attn++;
+    else dn_index[l] = n_dn++;
+  }
+  max_entries = std::min(MR * used, c.n_expert + (MR * used + 7) / 8) + (MR + 7) / 8;
+  B200_TRY(dalloc(&h, (size_t)MR * H)); B200_TRY(dalloc(&proj, (size_t)MR * proj_ld)); B200_TRY(dalloc(&dn_o, (size_t)MR * vw));
+  B200_TRY(dalloc(&xn16, (size_t)MR * H)); B200_TRY(dalloc(&q16, (size_t)MR * qw)); B200_TRY(dalloc(&ctx16, (size_t)MR * qw));
+  B200_TRY(dalloc(&attn_partial, (size_t)MR * c.n_head * nsplit * (hd + 2)));
+  B200_TRY(dalloc(&attn_tickets, (size_t)MR * c.n_head_kv));
+  B200_TRY(dalloc(&r_logits, (size_t)MR * c.n_expert)); B200_TRY(dalloc(&r_probs, (size_t)MR * c.n_expert));
+  B200_TRY(dalloc(&topk, (size_t)MR * used)); B200_TRY(dalloc(&topk_w, (size_t)MR * slots1)); B200_TRY(dalloc(&margin, (size_t)MR));
+  B200_TRY(dalloc(&entries, (size_t)max_entries)); B200_TRY(dalloc(&n_entries, 1)); B200_TRY(dalloc(&cols, (size_t)MR * slots1));
+  B200_TRY(dalloc(&r_ticket, 1));
+  B200_TRY(dalloc(&act16, (size_t)MR * slots1 * c.ffn_expert)); B200_TRY(dalloc(&down, (size_t)MR * slots1 * H));
+  B200_TRY(dalloc(&logits, (size_t)MR * c.vocab));
+  B200_TRY(dalloc(&ids_dev, (size_t)MR)); B200_TRY(dalloc(&next_ids, (size_t)MR)); B200_TRY(dalloc(&row_slot, (size_t)MR));
+  B200_TRY(dalloc(&row_pos, (size_t)MR)); B200_TRY(dalloc(&logit_rows, (size_t)MR)); B200_TRY(dalloc(&seqs, (size_t)MR));
+  B200_TRY(dalloc(&hist_len, 1));
+  if (c.has_draft) { B200_TRY(dalloc(&e_buf, (size_t)MR * H)); B200_TRY(dalloc(&hs_buf, (size_t)MR * H)); }
+  // rotary table, angle walked in f64 like the reference (llm/attn.go:554-584, llm/gpu_attn.go:1440-1477)
+  {
+    const int rot = std::min(c.rope_dims, c.head_dim), half = rot / 2, npos = o.n_kv + 2;
+    std::vector<float> tab((size_t)npos * half * 2);
+    const double scale = std::pow((double)c.rope_base, -2.0 / (double)rot);
+    for (int p = 0; p < npos; p++) {
+      double theta = (double)p;
+      for (int i = 0; i < half; i++) {
+        tab[((size_t)p * half + i) * 2] = (float)std::cos(theta);
+        tab[((size_t)p * half + i) * 2 + 1] = (float)std::sin(theta);
+        theta *= scale;
+      }
+    }
+    B200_TRY(dalloc(&rope, tab.size(), false));
+    B200_CUDA(cudaMemcpy(rope, tab.data(), tab.size() * sizeof(float), cudaMemcpyHostToDevice));
+  }
+  // sequence state
+  state_slot_stride = (int64_t)c.dn_heads_v * D * D;
+  ring_slot_stride = (int64_t)c.dn_heads_v * 4 * DN_RING * DN_RING_W;
+  kv_slot_stride = (int64_t)o.n_kv * kvw;
+  mid_seq_stride = (int64_t)std::max(o.spec_rows, 1) * state_slot_stride;
+  dn_state.resize(n_dn); dn_ring.resize(n_dn); dn_mid.assign(n_dn, nullptr);
+  for (int i = 0; i < n_dn; i++) {
+    B200_TRY(dalloc(&dn_state[i], (size_t)o.slots * state_slot_stride));
+    B200_TRY(dalloc(&dn_ring[i], (size_t)o.slots * ring_slot_stride));
+    if (o.speculative) B200_TRY(dalloc(&dn_mid[i], (size_t)mid_seq_stride));
+  }
+  kcache.resize(n_attn); vcache.resize(n_attn);
+  for (int i = 0; i < n_attn; i++) {
+    B200_TRY(dalloc(&kcache[i], (size_t)o.slots * kv_slot_stride, false));
+    B200_TRY(dalloc(&vcache[i], (size_t)o.slots * kv_slot_stride, false));
+  }
+  past.assign(o.slots, 0); draft_past.assign(o.slots, 0);
+  // host staging
+  stage_bytes = (size_t)MR * (4 * sizeof(int32_t) + sizeof(SeqDesc));
+  B200_CUDA(cudaMallocHost((void**)&stage, stage_bytes));
+  B200_CUDA(cudaMallocHost((void**)&logits_host, (size_t)MR * c.vocab * sizeof(float)));
+  B200_CUDA(cudaMallocHost((void**)&resid_host, (size_t)MR * H * sizeof(float)));
+  B200_CUDA(cudaMallocHost((void**)&hidden_host, (size_t)H * sizeof(float)));
+  B200_CUDA(cudaMallocHost((void**)&ids_host, (size_t)MR * 4096 * sizeof(int32_t)));
+  B200_TRY(dalloc(&history, (size_t)MR * 4096));
+  if (o.trace) {
+    B200_TRY(dalloc(&tr_mid, (size_t)nl * MR * H)); B200_TRY(dalloc(&tr_out, (size_t)nl * MR * H));
+    B200_TRY(dalloc(&tr_topk, (size_t)nl * MR * used)); B200_TRY(dalloc(&tr_w, (size_t)nl * MR * slots1)); B200_TRY(dalloc(&tr_margin, (size_t)nl * MR));
+  }
+  B200_CUDA(cudaDeviceSynchronize());
+  return OK;
+}
+
+int Graph::max_entries_for(int M) const {
+  const int used = m->c.n_expert_used;
+  return std::min(M * used, m->c.n_expert + (M * used + 7) / 8) + (M + 7) / 8;
+}
+
+// ---- one pass over M rows --------------------------------------------------------------
+int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) {
+  const b200_config& c = m->c;
+  const int H = c.n_embd, D = c.dn_head_dim, qk = c.dn_heads_k * D, vw = c.dn_heads_v * D, cw = 2 * qk + vw;
+  const int hd = c.head_dim, qw = c.n_head * hd, kvw = c.n_head_kv * hd, used = c.n_expert_used, slots1 = used + 1;
+  const int xcols = std::min(M, QG_MAXCOLS);
+  launches = 0;
+  bool first = true;
+  auto pdl = [&]() { bool p = !first; first = false; launches++; return p; };
+  auto base = [&](const DTensor& w, int K, int N) {
+    QGemvParams p{};
+    p.w[0] = w.data; p.seg_end[0] = N; p.nseg = 1; p.stride = w.stride; p.K = K; p.N = N; p.M = M; p.xcols = xcols; p.eps = c.eps; p.x_div = 1;
+    return p;
+  };
+  const int l0 = f.draft ? c.n_layer : 0, l1 = f.draft ? c.n_layer + 1 : c.n_layer;
+  if (f.draft) {
+    // nextn seed, embedding first: h = eh_proj . concat(rms(embd, enorm), rms(h_prev, hnorm))  (llm/mtp.go:352-384)
+    const LayerW& L = m->layers[c.n_layer];
+    EmbedParams ep{m->token_embd, ids_dev, e_buf, M, H};
+    B200_TRY(launch_embed(ep, st)); pdl();
+    QGemvParams p = base(L.eh_proj, 2 * H, H);
+    p.x = e_buf; p.ldx = H; p.x2 = hs_buf; p.ldx2 = H; p.gamma = (const float*)L.enorm.data; p.gamma2 = (const float*)L.hnorm.data;
+    p.y = h; p.ldy = H;
+    B200_TRY(launch_qgemv(L.eh_proj.type, PRO_CONCAT_NORM, EPI_STORE, false, false, p, 0, pdl(), st));
+  } else {
+    EmbedParams ep{m->token_embd, ids_dev, h, M, H};
+    B200_TRY(launch_embed(ep, st)); pdl();
+  }
+  for (int l = l0; l < l1; l++) {
+    const LayerW& L = m->layers[l];
+    if (!L.is_attn) {
+      const int di = dn_index[l];
+      QGemvParams p = base(L.qkv, H, cw + vw);
+      p.w[1] = L.z.data; p.seg_end[0] = cw; p.seg_end[1] = cw + vw; p.nseg = 2;
+      p.x = h; p.ldx = H; p.gamma = (const float*)L.attn_norm.data; p.xn_out = xn16; p.y = proj; p.ldy = proj_ld;
+      B200_TRY(launch_qgemv(L.qkv.type, PRO_RMSNORM, EPI_STORE, false, false, p, 0, pdl(), st));
+      DnStepParams d{};
+      d.proj = proj; d.ldp = proj_ld; d.xn = xn16; d.alpha_w = (const float*)L.alpha.data; d.beta_w = (const float*)L.beta.data;
+      d.conv_w = (const float*)L.conv1d.data; d.ssm_a = (const float*)L.ssm_a.data; d.dt_bias = (const float*)L.dt_bias.data;
+      d.state = dn_state[di]; d.state_slot_stride = state_slot_stride; d.ring = dn_ring[di]; d.ring_slot_stride = ring_slot_stride;
+      d.seqs = seqs; d.n_seq = n_seq; d.out = dn_o; d.mid = f.spec ? dn_mid[di] : nullptr; d.mid_stride = state_slot_stride; d.mid_seq_stride = mid_seq_stride;
+      d.H = H; d.Hk = c.dn_heads_k; d.Hv = c.dn_heads_v; d.D = D; d.conv = c.dn_conv; d.eps = c.eps;
+      B200_TRY(launch_dn_step(d, pdl(), st));
+      QGemvParams q = base(L.ssm_out, vw, H);
+      q.x = dn_o; q.ldx = vw; q.z = proj + cw; q.ldz = proj_ld; q.gamma = (const float*)L.ssm_norm.data; q.head_dim = D; q.y = h; q.ldy = H;
+      B200_TRY(launch_qgemv(L.ssm_out.type, PRO_DN_GATED, EPI_RESID, false, false, q, 0, pdl(), st));
+    } else {
+      const int ai = attn_index[l];
+      // fused q|k|v projection; tensors of one type share a launch
+      const DTensor* seg[3] = {&L.q, &L.k, &L.v};
+      const int rows[3] = {2 * qw, kvw, kvw};
+      int off = 0;
+      for (int s = 0; s < 3;) {
+        int e = s + 1;
+        while (e < 3 && seg[e]->type == seg[s]->type) e++;
+        int n = 0;
+        QGemvParams p = base(*seg[s], H, 0);
+        for (int i = s; i < e; i++) { p.w[i - s] = seg[i]->data; n += rows[i]; p.seg_end[i - s] = n; }
+        p.nseg = e - s; p.N = n;
+        p.x = h; p.ldx = H; p.gamma = (const float*)L.attn_norm.data; p.y = proj + off; p.ldy = proj_ld;
+        B200_TRY(launch_qgemv(seg[s]->type, PRO_RMSNORM, EPI_STORE, false, false, p, 0, pdl(), st));
+        off += n; s = e;
+      }
+      AttnParams a{};
+      a.proj = proj; a.ldp = proj_ld; a.q_norm = (const float*)L.q_norm.data; a.k_norm = (const float*)L.k_norm.data; a.rope = rope;
+      a.kcache = kcache[ai]; a.vcache = vcache[ai]; a.slot_stride = kv_slot_stride; a.row_slot = row_slot; a.row_pos = row_pos;
+      a.q16 = q16; a.partial = attn_partial; a.tickets = attn_tickets; a.ctx16 = ctx16;
+      a.M = M; a.Hq = c.n_head; a.Hkv = c.n_head_kv; a.hd = hd; a.rope_dims = std::min(c.rope_dims, hd); a.n_kv = o.n_kv;
+      a.split_cells = split_cells; a.nsplit = nsplit; a.eps = c.eps; a.rope_off = f.draft ? 1 : 0;
+      B200_TRY(launch_attn_pack(a, pdl(), st));
+      B200_TRY(launch_attn_decode(a, pdl(), st));
+      QGemvParams q = base(L.o, qw, H);
+      q.x = ctx16; q.ldx = qw; q.y = h; q.ldy = H;
+      B200_TRY(launch_qgemv(L.o.type, PRO_F16, EPI_RESID, false, false, q, 0, pdl(), st));
+    }
+    if (o.trace) B200_CUDA(cudaMemcpyAsync(tr_mid + (size_t)l * MR * H, h, (size_t)M * H * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    // MoE block
+    RouterParams r{};
+    r.h = h; r.gamma = (const float*)L.ffn_norm.data; r.eps = c.eps; r.router = L.router; r.sh_gate = (const float*)L.sh_gate_inp.data;
+    r.M = M; r.H = H; r.nE = c.n_expert; r.used = used; r.logits = r_logits; r.probs = r_probs; r.topk = topk; r.topk_w = topk_w;
+    r.margin = margin; r.entries = entries; r.n_entries = n_entries; r.cols = cols; r.ticket = r_ticket; r.max_entries = max_entries;
+    B200_TRY(launch_router(r, o.trace ? false : pdl(), st));
+    if (o.trace) { first = false; launches++; }
+    {
+      QGemvParams p = base(L.gate_exps, H, c.ffn_expert);
+      p.w2[0] = L.up_exps.data; p.ws = L.gate_sh.data; p.ws2 = L.up_sh.data; p.expert_stride = (int64_t)c.ffn_expert * L.gate_exps.stride;
+      p.entries = entries; p.n_entries = n_entries; p.cols = cols; p.x_div = slots1;
+      p.x = h; p.ldx = H; p.gamma = (const float*)L.ffn_norm.data; p.y16 = act16; p.ldy = c.ffn_expert;
+      B200_TRY(launch_qgemv(L.gate_exps.type, PRO_RMSNORM, EPI_SWIGLU, true, true, p, max_entries_for(M), pdl(), st));
+      QGemvParams q = base(L.down_exps, c.ffn_expert, H);
+      q.ws = L.down_sh.data; q.expert_stride = (int64_t)H * L.down_exps.stride;
+      q.entries = entries; q.n_entries = n_entries; q.cols = cols; q.x_div = 1;
+      q.x = act16; q.ldx = c.ffn_expert; q.y = down; q.ldy = H;
+      B200_TRY(launch_qgemv(L.down_exps.type, PRO_F16, EPI_STORE, false, true, q, max_entries_for(M), pdl(), st));
+    }
+    CombineParams cb{h, down, topk_w, M, H, used};
+    B200_TRY(launch_moe_combine(cb, pdl(), st));
+    if (o.trace) {
+      B200_CUDA(cudaMemcpyAsync(tr_out + (size_t)l * MR * H, h, (size_t)M * H * sizeof(float), cudaMemcpyDeviceToDevice, st));
+      B200_CUDA(cudaMemcpyAsync(tr_topk + (size_t)l * MR * used, topk, (size_t)M * used * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
+      B200_CUDA(cudaMemcpyAsync(tr_w + (size_t)l * MR * slots1, topk_w, (size_t)M * slots1 * sizeof(float), cudaMemcpyDeviceToDevice, st));
+      B200_CUDA(cudaMemcpyAsync(tr_margin + (size_t)l * MR, margin, (size_t)M * sizeof(float), cudaMemcpyDeviceToDevice, st));
+      first = true;  // a copy sits between this kernel and the next: no programmatic edge
+    }
+  }
+  if (n_logit_rows > 0) {
+    const DTensor& nrm = f.draft ? m->layers[c.n_layer].head_norm : m->output_norm;
+    const int N = f.draft && draft_vocab > 0 ? draft_vocab : c.vocab;
+    QGemvParams p = base(m->output, H, N);
+    p.M = n_logit_rows; p.xcols = std::min(n_logit_rows, QG_MAXCOLS); p.row_ids = logit_rows;
+    p.x = h; p.ldx = H; p.gamma = (const float*)nrm.data; p.y = logits; p.ldy = N;
+    B200_TRY(launch_qgemv(m->output.type, PRO_RMSNORM, EPI_STORE, false, false, p, 0, pdl(), st));
+    if (f.greedy) {
+      B200_TRY(launch_argmax(logits, n_logit_rows, N, next_ids, pdl(), st));
+      B200_TRY(launch_advance(ids_dev, next_ids, row_pos, seqs, M, history, hist_len, st)); launches++;
+    }
+  }
+  last_launches = launches;
+  return OK;
+}
+
+static void fill_stage(uint8_t* stage, int MR, const int32_t* ids, const int* slots, const int* pos, int M, const std::vector<SeqDesc>& sq, const std::vector<int>& lrows) {
+  int32_t* s_ids = (int32_t*)stage; int* s_slot = (int*)stage + MR; int* s_pos = (int*)stage + 2 * MR; int* s_lr = (int*)stage + 3 * MR;
+  SeqDesc* s_sq = (SeqDesc*)((int*)stage + 4 * MR);
+  for (int i = 0; i < M; i++) { s_ids[i] = ids[i]; s_slot[i] = slots[i]; s_pos[i] = pos[i]; }
+  for (size_t i = 0; i < lrows.size(); i++) s_lr[i] = lrows[i];
+  for (size_t i = 0; i < sq.size(); i++) s_sq[i] = sq[i];
+}
+
+static int upload_stage(Graph* g, int M, int n_seq, int n_lr) {
+  const int MR = g->MR;
+  uint8_t* s = g->stage;
+  B200_CUDA(cudaMemcpyAsync(g->ids_dev, s, M * sizeof(int32_t), cudaMemcpyHostToDevice, g->st));
+  B200_CUDA(cudaMemcpyAsync(g->row_slot, (int*)s + MR, M * sizeof(int), cudaMemcpyHostToDevice, g->st));
+  B200_CUDA(cudaMemcpyAsync(g->row_pos, (int*)s + 2 * MR, M * sizeof(int), cudaMemcpyHostToDevice, g->st));
+  if (n_lr > 0) B200_CUDA(cudaMemcpyAsync(g->logit_rows, (int*)s + 3 * MR, n_lr * sizeof(int), cudaMemcpyHostToDevice, g->st));
+  B200_CUDA(cudaMemcpyAsync(g->seqs, (int*)s + 4 * MR, n_seq * sizeof(SeqDesc), cudaMemcpyHostToDevice, g->st));
+  return OK;
+}
+
+int Graph::run_rows(const int32_t* ids, const int* slots, const int* pos, int M, const std::vector<SeqDesc>& sq, const std::vector<int>& lrows, const PassFlags& f) {
+  const b200_config& c = m->c;
+  for (int i = 0; i < M; i++) {
+    if (ids[i] < 0 || ids[i] >= c.vocab) { set_error("token id " + std::to_string(ids[i]) + " is outside the vocabulary"); return EINVAL_; }
+  }
+  B200_CUDA(cudaSetDevice(m->device));
+  fill_stage(stage, MR, ids, slots, pos, M, sq, lrows);
+  const int n_lr = (int)lrows.size(), n_seq = (int)sq.size();
+  const int NV = f.draft && draft_vocab > 0 ? draft_vocab : c.vocab;
+  bool single = !f.spec && !f.draft && !o.trace && o.use_cuda_graph && n_seq == M && n_lr == M && !f.want_residual;
+  if (single) {
+    auto it = decode_graphs.find(M);
+    if (it == decode_graphs.end()) {
+      // the decode step is captured once and replayed, positions living in device memory
+      // (the reference's pre-recorded command buffer: llm/graph.go:238-258)
+      cudaGraph_t graph = nullptr;
+      B200_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+      int s = upload_stage(this, M, n_seq, n_lr);
+      if (s == OK) s = enqueue_pass(M, n_seq, n_lr, f);
+      if (s == OK && cudaMemcpyAsync(logits_host, logits, (size_t)n_lr * NV * sizeof(float), cudaMemcpyDeviceToHost, st) != cudaSuccess) s = ECUDA;
+      cudaError_t e = cudaStreamEndCapture(st, &graph);
+      if (s != OK || e != cudaSuccess) { if (graph) cudaGraphDestroy(graph); if (s == OK) { set_error(std::string("graph capture: ") + cudaGetErrorString(e)); s = ECUDA; } return s; }
+      cudaGraphExec_t exec = nullptr;
+      e = cudaGraphInstantiate(&exec, graph, 0);
+      cudaGraphDestroy(graph);
+      if (e != cudaSuccess) { set_error(std::string("graph instantiate: ") + cudaGetErrorString(e)); return ECUDA; }
+      it = decode_graphs.emplace(M, exec).first;
+    }
+    B200_CUDA(cudaGraphLaunch(it->second, st));
+  } else {
+    B200_TRY(upload_stage(this, M, n_seq, n_lr));
+    B200_TRY(enqueue_pass(M, n_seq, n_lr, f));
+    if (n_lr > 0) B200_CUDA(cudaMemcpyAsync(logits_host, logits, (size_t)n_lr * NV * sizeof(float), cudaMemcpyDeviceToHost, st));
+  }
+  if (f.want_residual) B200_CUDA(cudaMemcpyAsync(resid_host + (size_t)resid_off * c.n_embd, h, (size_t)M * c.n_embd * sizeof(float), cudaMemcpyDeviceToHost, st));
+  B200_CUDA(cudaMemcpyAsync(hidden_host, h + (size_t)(M - 1) * c.n_embd, (size_t)c.n_embd * sizeof(float), cudaMemcpyDeviceToHost, st));
+  B200_CUDA(cudaStreamSynchronize(st));
+  last_rows = M;
+  return OK;
+}
+
+int Graph::extend(const int32_t* ids, int n, const PassFlags& f, const float** logits_out, const float** hidden_out) {
+  if (n <= 0) { set_error("extend: no tokens"); return EINVAL_; }
+  if (f.spec) {
+    if (!o.speculative) { set_error("extend: the graph was not created with speculative = 1"); return ESTATE; }
+    if (n > o.spec_rows) { set_error("extend: a speculative pass holds at most spec_rows rows"); return ECAPACITY; }
+  }
+  if (f.want_all_logits && n > MR) { set_error("extend_rows: more rows than max_tokens"); return ECAPACITY; }
+  if (f.want_residual && n > MR) { set_error("extend_residual: more rows than max_tokens"); return ECAPACITY; }
+  if (past[cur] + n > o.n_kv) { set_error("extend: the slot's context is full (" + std::to_string(past[cur]) + " + " + std::to_string(n) + " > " + std::to_string(o.n_kv) + ")"); return ECAPACITY; }
+  resid_off = 0;
+  for (int off = 0; off < n; off += MR) {
+    const int M = std::min(MR, n - off);
+    std::vector<int> slots(M, cur), pos(M);
+    for (int i = 0; i < M; i++) pos[i] = past[cur] + i;
+    std::vector<SeqDesc> sq{SeqDesc{cur, 0, M, past[cur]}};
+    std::vector<int> lrows;
+    if (f.want_all_logits) for (int i = 0; i < M; i++) lrows.push_back(i);
+    else if (off + M == n) lrows.push_back(M - 1);
+    B200_TRY(run_rows(ids + off, slots.data(), pos.data(), M, sq, lrows, f));
+    if (f.spec) { spec_pos0 = past[cur]; spec_n = M; }
+    else { past[cur] += M; spec_n = 0; }
+    resid_off += M;
+  }
+  if (logits_out) *logits_out = logits_host;
+  if (hidden_out) *hidden_out = f.want_residual ? resid_host : hidden_host;
+  return OK;
+}
+
+int Graph::decode_rows(const int32_t* slots_in, const int32_t* ids, int n, const float** logits_out) {
+  // one token for each of n distinct slots (reference: llm/batch.go:45-63)
+  if (n <= 0 || n > MR) { set_error("decode_rows: 1.." + std::to_string(MR) + " rows"); return ECAPACITY; }
+  std::vector<int> slots(n), pos(n), lrows(n);
+  std::vector<SeqDesc> sq(n);
+  std::vector<char> seen(o.slots, 0);
+  for (int i = 0; i < n; i++) {
+    const int s = slots_in[i];
+    if (s < 0 || s >= o.slots) { set_error("decode_rows: slot " + std::to_string(s) + " does not exist"); return EINVAL_; }
+    if (seen[s]) { set_error("decode_rows: slot " + std::to_string(s) + " appears twice"); return EINVAL_; }
+    if (past[s] + 1 > o.n_kv) { set_error("decode_rows: slot " + std::to_string(s) + " is full"); return ECAPACITY; }
+    seen[s] = 1; slots[i] = s; pos[i] = past[s]; lrows[i] = i; sq[i] = SeqDesc{s, i, 1, past[s]};
+  }
+  PassFlags f; f.want_all_logits = true;
+  B200_TRY(run_rows(ids, slots.data(), pos.data(), n, sq, lrows, f));
+  for (int i = 0; i < n; i++) past[slots[i]] += 1;
+  spec_n = 0;
+  if (logits_out) *logits_out = logits_host;
+  return OK;
+}
+
+int Graph::generate_greedy(const int32_t* slots_in, const int32_t* first, int n, int steps, int32_t* out) {
+  const b200_config& c = m->c;
+  if (n <= 0 || n > MR) { set_error("generate_greedy: 1.." + std::to_string(MR) + " rows"); return ECAPACITY; }
+  if (steps <= 0 || steps > 4096) { set_error("generate_greedy: 1..4096 steps per call"); return ECAPACITY; }
+  std::vector<int> slots(n), pos(n), lrows(n);
+  std::vector<SeqDesc> sq(n);
+  std::vector<char> seen(o.slots, 0);
+  for (int i = 0; i < n; i++) {
+    const int s = slots_in[i];
+    if (s < 0 || s >= o.slots || seen[s]) { set_error("generate_greedy: bad or repeated slot"); return EINVAL_; }
+    if (first[i] < 0 || first[i] >= c.vocab) { set_error("generate_greedy: token id outside the vocabulary"); return EINVAL_; }
+    if (past[s] + steps > o.n_kv) { set_error("generate_greedy: slot " + std::to_string(s) + " would overflow its context"); return ECAPACITY; }
+    seen[s] = 1; slots[i] = s; pos[i] = past[s]; lrows[i] = i; sq[i] = SeqDesc{s, i, 1, past[s]};
+  }
+  B200_CUDA(cudaSetDevice(m->device));
+  fill_stage(stage, MR, first, slots.data(), pos.data(), n, sq, lrows);
+  B200_TRY(upload_stage(this, n, n, n));
+  B200_CUDA(cudaMemsetAsync(hist_len, 0, sizeof(int), st));
+  PassFlags f; f.want_all_logits = true; f.greedy = true;
+  cudaGraphExec_t exec = nullptr;
+  if (o.use_cuda_graph && !o.trace) {
+    auto it = greedy_graphs.find(n);
+    if (it == greedy_graphs.end()) {
+      cudaGraph_t graph = nullptr;
+      B200_CUDA(cudaStreamSynchronize(st));
+      B200_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+      int s = enqueue_pass(n, n, n, f);
+      cudaError_t e = cudaStreamEndCapture(st, &graph);
+      if (s != OK || e != cudaSuccess) { if (graph) cudaGraphDestroy(graph); if (s == OK) { set_error(std::string("graph capture: ") + cudaGetErrorString(e)); s = ECUDA; } return s; }
+      e = cudaGraphInstantiate(&exec, graph, 0);
+      cudaGraphDestroy(graph);
+      if (e != cudaSuccess) { set_error(std::string("graph instantiate: ") + cudaGetErrorString(e)); return ECUDA; }
+      greedy_graphs.emplace(n, exec);
+    } else exec = it->second;
+  }
+  B200_CUDA(cudaEventRecord(ev0, st));
+  for (int s = 0; s < steps; s++) {
+    if (exec) B200_CUDA(cudaGraphLaunch(exec, st));
+    else B200_TRY(enqueue_pass(n, n, n, f));
+  }
+  B200_CUDA(cudaEventRecord(ev1, st));
+  B200_CUDA(cudaMemcpyAsync(ids_host, history, (size_t)steps * n * sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+  B200_CUDA(cudaStreamSynchronize(st));
+  B200_CUDA(cudaEventElapsedTime(&last_ms, ev0, ev1));
+  memcpy(out, ids_host, (size_t)steps * n * sizeof(int32_t));
+  for (int i = 0; i < n; i++) past[slots[i]] += steps;
+  spec_n = 0;
+  return OK;
+}
+
+int Graph::draft_rows(const float* hs, const int32_t* ids, int n, int vocab_k, const float** resid, const float** logits_out) {
+  const b200_config& c = m->c;
+  if (!c.has_draft) { set_error("draft_rows: the checkpoint has no draft layer"); return ESTATE; }
+  if (n <= 0 || n > MR) { set_error("draft_rows: row count out of range"); return ECAPACITY; }
+  if (vocab_k <= 0 || vocab_k > c.vocab) vocab_k = c.vocab;
+  if (vocab_k % 16) { set_error("draft_rows: vocab_k must be a multiple of 16"); return EINVAL_; }
+  if (draft_past[cur] + n + 1 > o.n_kv) { set_error("draft_rows: the draft cache is full"); return ECAPACITY; }
+  B200_CUDA(cudaSetDevice(m->device));
+  B200_CUDA(cudaMemcpyAsync(hs_buf, hs, (size_t)n * c.n_embd * sizeof(float), cudaMemcpyHostToDevice, st));
+  draft_vocab = vocab_k;
+  std::vector<int> slots(n, cur), pos(n), lrows(n);
+  for (int i = 0; i < n; i++) { pos[i] = draft_past[cur] + i; lrows[i] = i; }
+  std::vector<SeqDesc> sq{SeqDesc{cur, 0, n, draft_past[cur]}};
+  PassFlags f; f.draft = true; f.want_all_logits = true; f.want_residual = true;
+  resid_off = 0;
+  B200_TRY(run_rows(ids, slots.data(), pos.data(), n, sq, lrows, f));
+  draft_past[cur] += n;
+  if (resid) *resid = resid_host;
+  if (logits_out) *logits_out = logits_host;
+  return OK;
+}
+
+int Graph::reset_slot(int slot) {
+  // a fresh sequence: zero recurrent state; rings and KV cells are masked by position
+  B200_CUDA(cudaSetDevice(m->device));
+  for (int i = 0; i < n_dn; i++)
+    B200_CUDA(cudaMemsetAsync(dn_state[i] + (size_t)slot * state_slot_stride, 0, (size_t)state_slot_stride * sizeof(float), st));
+  B200_CUDA(cudaStreamSynchronize(st));
+  past[slot] = 0; draft_past[slot] = 0;
+  if (slot == cur) spec_n = 0;
+  return OK;
+}
+
+int Graph::keep(int k) {
+  // keep the first k rows of the last speculative pass (reference: llm/graph.go:1189-1233)
+  if (spec_n <= 0) { set_error("keep: no speculative pass is pending"); return ESTATE; }
+  if (k < 0 || k > spec_n) { set_error("keep: k is outside the pass"); return EINVAL_; }
+  B200_CUDA(cudaSetDevice(m->device));
+  if (k > 0) {
+    for (int i = 0; i < n_dn; i++)
+      B200_CUDA(cudaMemcpyAsync(dn_state[i] + (size_t)cur * state_slot_stride, dn_mid[i] + (size_t)(k - 1) * state_slot_stride,
+                                (size_t)state_slot_stride * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    B200_CUDA(cudaStreamSynchronize(st));
+  }
+  past[cur] = spec_pos0 + k;
+  spec_n = 0;
+  return OK;
+}
+
+int Graph::checkpoint(int* handle) {
+  B200_CUDA(cudaSetDevice(m->device));
+  Ckpt ck; ck.slot = cur; ck.past = past[cur];
+  for (int i = 0; i < n_dn; i++) {
+    float *s = nullptr, *r = nullptr;
+    if (cudaMalloc((void**)&s, (size_t)state_slot_stride * sizeof(float)) != cudaSuccess || cudaMalloc((void**)&r, (size_t)ring_slot_stride * sizeof(float)) != cudaSuccess) {
+      if (s) cudaFree(s);
+      for (float* p : ck.state) cudaFree(p);
+      for (float* p : ck.ring) cudaFree(p);
+      set_error("checkpoint: out of device memory"); return ENOMEM_;
+    }
+    ck.state.push_back(s); ck.ring.push_back(r);
+    B200_CUDA(cudaMemcpyAsync(s, dn_state[i] + (size_t)cur * state_slot_stride, (size_t)state_slot_stride * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    B200_CUDA(cudaMemcpyAsync(r, dn_ring[i] + (size_t)cur * ring_slot_stride, (size_t)ring_slot_stride * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  }
+  B200_CUDA(cudaStreamSynchronize(st));
+  *handle = next_ckpt++;
+  ckpts[*handle] = ck;
+  return OK;
+}
+
+int Graph::restore(int handle) {
+  auto it = ckpts.find(handle);
+  if (it == ckpts.end()) { set_error("restore: unknown checkpoint"); return EINVAL_; }
+  const Ckpt& ck = it->second;
+  // KV cells below the mark are not copied: they must still be this slot's (llm/graph.go:1037-1062)
+  if (ck.slot != cur) { set_error("restore: the checkpoint was taken in another slot"); return ESTATE; }
+  if (past[cur] < ck.past) { set_error("restore: the slot no longer holds the checkpoint's tokens"); return ESTATE; }
+  B200_CUDA(cudaSetDevice(m->device));
+  for (int i = 0; i < n_dn; i++) {
+    B200_CUDA(cudaMemcpyAsync(dn_state[i] + (size_t)cur * state_slot_stride, ck.state[i], (size_t)state_slot_stride * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    B200_CUDA(cudaMemcpyAsync(dn_ring[i] + (size_t)cur * ring_slot_stride, ck.ring[i], (size_t)ring_slot_stride * sizeof(float), cudaMemcpyDeviceToDevice, st));
+  }
+  B200_CUDA(cudaStreamSynchronize(st));
+  past[cur] = ck.past;
+  spec_n = 0;
+  return OK;
+}
+
+int64_t Graph::trace(int what, void* dst, int64_t nbytes) {
+  if (!o.trace) { set_error("trace: the graph was created without trace = 1"); return -ESTATE; }
+  const b200_config& c = m->c;
+  const int nl = c.n_layer, M = last_rows, used = c.n_expert_used;
+  const void* src; size_t row_bytes, ld_bytes;
+  switch (what) {
+    case 0: src = tr_mid; row_bytes = (size_t)M * c.n_embd * 4; ld_bytes = (size_t)MR * c.n_embd * 4; break;
+    case 1: src = tr_out; row_bytes = (size_t)M * c.n_embd * 4; ld_bytes = (size_t)MR * c.n_embd * 4; break;
+    case 2: src = tr_topk; row_bytes = (size_t)M * used * 4; ld_bytes = (size_t)MR * used * 4; break;
+    case 3: src = tr_w; row_bytes = (size_t)M * (used + 1) * 4; ld_bytes = (size_t)MR * (used + 1) * 4; break;
+    case 4: src = tr_margin; row_bytes = (size_t)M * 4; ld_bytes = (size_t)MR * 4; break;
+    default: set_error("trace: unknown selector"); return -EINVAL_;
+  }
+  if ((int64_t)(row_bytes * nl) > nbytes) { set_error("trace: buffer too small"); return -EINVAL_; }
+  cudaSetDevice(m->device);
+  if (cudaMemcpy2D(dst, row_bytes, src, ld_bytes, row_bytes, nl, cudaMemcpyDeviceToHost) != cudaSuccess) { set_error("trace: copy failed"); return -ECUDA; }
+  return (int64_t)(row_bytes * nl);
+}
+
+}  // namespace b200

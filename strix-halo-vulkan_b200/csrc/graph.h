@@ -1,0 +1,83 @@
+// The token-loop graph: per-slot sequence state, pass scheduling, CUDA-graph replay.
+// Host half of the reference's llm.Graph (llm/graph.go:184-289), re-designed for one
+// device arena and one captured CUDA graph per decode step.
+#pragma once
+#include <map>
+#include <vector>
+
+#include "kernels.cuh"
+#include "model.h"
+
+namespace b200 {
+
+struct PassFlags {
+  bool want_all_logits = false;   // logits for every row, else the last row only
+  bool want_residual = false;     // copy every row's residual to the host
+  bool spec = false;              // speculative: write per-row state planes, leave the state untouched
+  bool greedy = false;            // argmax + advance on the device (no host traffic)
+  bool draft = false;             // the pass runs the draft layer only
+};
+
+struct Graph {
+  Model* m = nullptr;
+  b200_graph_opts o{};
+  cudaStream_t st = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  int MR = 0;           // rows per pass
+  int n_dn = 0, n_attn = 0;
+  std::vector<int> dn_index, attn_index;  // layer -> index among its kind (draft layer = last attention)
+  // activations
+  float *h = nullptr, *proj = nullptr, *dn_o = nullptr, *attn_partial = nullptr, *down = nullptr, *logits = nullptr, *e_buf = nullptr, *hs_buf = nullptr;
+  __half *xn16 = nullptr, *q16 = nullptr, *ctx16 = nullptr, *act16 = nullptr;
+  float *r_logits = nullptr, *r_probs = nullptr, *topk_w = nullptr, *margin = nullptr;
+  int32_t *topk = nullptr, *ids_dev = nullptr, *next_ids = nullptr, *history = nullptr;
+  int *attn_tickets = nullptr, *r_ticket = nullptr, *n_entries = nullptr, *cols = nullptr, *row_slot = nullptr, *row_pos = nullptr, *logit_rows = nullptr, *hist_len = nullptr;
+  int4* entries = nullptr;
+  SeqDesc* seqs = nullptr;
+  float* rope = nullptr;
+  int proj_ld = 0, max_entries = 0, nsplit = 0, split_cells = 0;
+  // sequence state
+  std::vector<float*> dn_state, dn_ring, dn_mid;   // per DeltaNet layer
+  std::vector<__half*> kcache, vcache;             // per attention layer (+ draft)
+  int64_t state_slot_stride = 0, ring_slot_stride = 0, kv_slot_stride = 0, mid_seq_stride = 0;
+  std::vector<int> past, draft_past;
+  int cur = 0;
+  // speculation
+  bool speculating = false;
+  int spec_pos0 = -1, spec_n = 0;
+  // host staging (pinned)
+  uint8_t* stage = nullptr; size_t stage_bytes = 0;
+  float *logits_host = nullptr, *resid_host = nullptr, *hidden_host = nullptr;
+  int32_t* ids_host = nullptr;
+  // trace
+  float *tr_mid = nullptr, *tr_out = nullptr, *tr_w = nullptr, *tr_margin = nullptr;
+  int32_t* tr_topk = nullptr;
+  int last_rows = 0;
+  // replay
+  std::map<int, cudaGraphExec_t> decode_graphs, greedy_graphs;
+  int launches = 0, last_launches = 0, draft_vocab = 0, resid_off = 0;
+  float last_ms = 0.f;
+  // checkpoints: DeltaNet state + rings of a slot at a token boundary
+  struct Ckpt { int slot, past; std::vector<float*> state, ring; };
+  std::map<int, Ckpt> ckpts;
+  int next_ckpt = 1;
+  std::vector<void*> allocs;
+
+  ~Graph();
+  int init(Model* model, const b200_graph_opts& opts);
+  int enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f);
+  int max_entries_for(int M) const;
+  int run_rows(const int32_t* ids, const int* slots, const int* pos, int M, const std::vector<SeqDesc>& sq, const std::vector<int>& lrows, const PassFlags& f);
+  int extend(const int32_t* ids, int n, const PassFlags& f, const float** logits_out, const float** hidden_out);
+  int decode_rows(const int32_t* slots, const int32_t* ids, int n, const float** logits_out);
+  int generate_greedy(const int32_t* slots, const int32_t* first, int n, int steps, int32_t* out);
+  int draft_rows(const float* hs, const int32_t* ids, int n, int vocab_k, const float** resid, const float** logits_out);
+  int reset_slot(int slot);
+  int keep(int k);
+  int checkpoint(int* handle);
+  int restore(int handle);
+  int64_t trace(int what, void* dst, int64_t nbytes);
+  template <class T> int dalloc(T** p, size_t n, bool zero = true);
+};
+
+}  // namespace b200

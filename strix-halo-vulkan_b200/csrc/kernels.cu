@@ -1,0 +1,762 @@
+// The token loop's non-projection kernels: embedding gather, router + routing, gated
+// DeltaNet step, attention pre-pass and split-KV decode attention, MoE combine, argmax,
+// and the Q6_K / Q8_0 row re-layout.
+#include "kernels.cuh"
+
+#include <cmath>
+
+namespace b200 {
+
+// =========================================================================================
+// Row layout
+// =========================================================================================
+bool block_geometry(uint32_t t, int* e, int* b) {
+  switch (t) {
+    case T_F32: *e = 1; *b = 4; return true;
+    case T_F16: case T_BF16: *e = 1; *b = 2; return true;
+    case T_Q4_1: *e = 32; *b = 20; return true;
+    case T_Q5_0: *e = 32; *b = 22; return true;
+    case T_Q5_1: *e = 32; *b = 24; return true;
+    case T_Q8_0: *e = 32; *b = 34; return true;
+    case T_IQ4_NL: *e = 32; *b = 18; return true;
+    case T_Q4_K: *e = 256; *b = 144; return true;
+    case T_Q5_K: *e = 256; *b = 176; return true;
+    case T_Q6_K: *e = 256; *b = 210; return true;
+  }
+  return false;
+}
+int64_t gguf_row_bytes(uint32_t t, int64_t n) {
+  int e, b;
+  if (!block_geometry(t, &e, &b) || n % e) return -1;
+  return n / e * b;
+}
+int64_t device_row_stride(uint32_t t, int64_t k) {
+  int64_t rb = gguf_row_bytes(t, k);
+  if (rb < 0) return -1;
+  if (t == T_Q6_K || t == T_Q8_0) return (rb + 15) / 16 * 16;
+  return rb;
+}
+
+// One thread per block. Q6_K: ql | qh | scales | d planes; Q8_0: qs | d planes.
+__global__ void repack_kernel(uint32_t type, int64_t nb, int64_t rows, int64_t stride, const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int inverse) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nb * rows) return;
+  int64_t r = i / nb, b = i - r * nb;
+  uint8_t* drow = dst + (inverse ? 0 : r * stride);
+  const uint8_t* srow = src + (inverse ? r * stride : 0);
+  if (type == T_Q6_K) {
+    const int64_t g = (r * nb + b) * 210;
+    uint8_t* gq = inverse ? dst + g : nullptr;
+    const uint8_t* gs = inverse ? nullptr : src + g;
+    uint8_t* pql = (inverse ? const_cast<uint8_t*>(srow) : drow) + b * 128;
+    uint8_t* pqh = (inverse ? const_cast<uint8_t*>(srow) : drow) + nb * 128 + b * 64;
+    uint8_t* psc = (inverse ? const_cast<uint8_t*>(srow) : drow) + nb * 192 + b * 16;
+    uint8_t* pd = (inverse ? const_cast<uint8_t*>(srow) : drow) + nb * 208 + b * 2;
+    if (!inverse) {
+      for (int j = 0; j < 128; j++) pql[j] = gs[j];
+      for (int j = 0; j < 64; j++) pqh[j] = gs[128 + j];
+      for (int j = 0; j < 16; j++) psc[j] = gs[192 + j];
+      pd[0] = gs[208]; pd[1] = gs[209];
+    } else {
+      for (int j = 0; j < 128; j++) gq[j] = pql[j];
+      for (int j = 0; j < 64; j++) gq[128 + j] = pqh[j];
+      for (int j = 0; j < 16; j++) gq[192 + j] = psc[j];
+      gq[208] = pd[0]; gq[209] = pd[1];
+    }
+  } else {  // Q8_0
+    const int64_t g = (r * nb + b) * 34;
+    uint8_t* base = inverse ? const_cast<uint8_t*>(srow) : drow;
+    uint8_t* pq = base + b * 32;
+    uint8_t* pd = base + nb * 32 + b * 2;
+    if (!inverse) {
+      pd[0] = src[g]; pd[1] = src[g + 1];
+      for (int j = 0; j < 32; j++) pq[j] = src[g + 2 + j];
+    } else {
+      dst[g] = pd[0]; dst[g + 1] = pd[1];
+      for (int j = 0; j < 32; j++) dst[g + 2 + j] = pq[j];
+    }
+  }
+}
+
+int repack_rows(uint32_t type, int64_t k, int64_t rows, const uint8_t* gguf_dev, uint8_t* dst_dev, cudaStream_t st) {
+  int64_t rb = gguf_row_bytes(type, k);
+  if (rb < 0) { set_error("repack: bad type or row length"); return EINVAL_; }
+  if (type != T_Q6_K && type != T_Q8_0) {
+    B200_CUDA(cudaMemcpyAsync(dst_dev, gguf_dev, (size_t)(rb * rows), cudaMemcpyDeviceToDevice, st));
+    return OK;
+  }
+  int64_t nb = k / (type == T_Q6_K ? 256 : 32), n = nb * rows;
+  repack_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(type, nb, rows, device_row_stride(type, k), gguf_dev, dst_dev, 0);
+  B200_CUDA(cudaGetLastError());
+  return OK;
+}
+int unpack_rows(uint32_t type, int64_t k, int64_t rows, const uint8_t* dev, uint8_t* gguf_dev, cudaStream_t st) {
+  int64_t rb = gguf_row_bytes(type, k);
+  if (rb < 0) { set_error("unpack: bad type or row length"); return EINVAL_; }
+  if (type != T_Q6_K && type != T_Q8_0) {
+    B200_CUDA(cudaMemcpyAsync(gguf_dev, dev, (size_t)(rb * rows), cudaMemcpyDeviceToDevice, st));
+    return OK;
+  }
+  int64_t nb = k / (type == T_Q6_K ? 256 : 32), n = nb * rows;
+  repack_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(type, nb, rows, device_row_stride(type, k), dev, gguf_dev, 1);
+  B200_CUDA(cudaGetLastError());
+  return OK;
+}
+
+// =========================================================================================
+// Exact element dequantisation (reference: gguf/dequant.go:128-356), device layout
+// =========================================================================================
+__device__ __forceinline__ float ld_f16(const uint8_t* p) { return __half2float(*reinterpret_cast<const __half*>(p)); }
+
+__device__ __forceinline__ void k4_scale_min(int j, const uint8_t* q, int* sc, int* m) {
+  if (j < 4) { *sc = q[j] & 63; *m = q[j + 4] & 63; }
+  else { *sc = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4); *m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4); }
+}
+
+// value of element k of a device row. __fmul_rn / __fsub_rn keep the reference's
+// unfused `d*sc*q - dmin*m` so the result is bit-identical to the CPU dequantiser.
+__device__ float dequant_elem(uint32_t type, const uint8_t* row, int64_t K, int64_t k) {
+  switch (type) {
+    case T_F32: return reinterpret_cast<const float*>(row)[k];
+    case T_F16: return ld_f16(row + 2 * k);
+    case T_BF16: return __uint_as_float((uint32_t)reinterpret_cast<const unsigned short*>(row)[k] << 16);
+    case T_Q8_0: {
+      int64_t nb = K / 32, b = k / 32;
+      float d = ld_f16(row + nb * 32 + b * 2);
+      return __fmul_rn((float)(int8_t)row[k], d);
+    }
+    case T_Q4_K: {
+      const uint8_t* blk = row + (k / 256) * 144;
+      int e = (int)(k % 256), grp = e / 64, in = e % 64, hi = in / 32, l = in % 32;
+      float d = ld_f16(blk), dmin = ld_f16(blk + 2);
+      int sc, m; k4_scale_min(2 * grp + hi, blk + 4, &sc, &m);
+      int q = hi ? (blk[16 + 32 * grp + l] >> 4) : (blk[16 + 32 * grp + l] & 0xF);
+      return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(dmin, (float)m));
+    }
+    case T_Q5_K: {
+      const uint8_t* blk = row + (k / 256) * 176;
+      int e = (int)(k % 256), grp = e / 64, in = e % 64, hi = in / 32, l = in % 32;
+      float d = ld_f16(blk), dmin = ld_f16(blk + 2);
+      int sc, m; k4_scale_min(2 * grp + hi, blk + 4, &sc, &m);
+      int q = hi ? (blk[48 + 32 * grp + l] >> 4) : (blk[48 + 32 * grp + l] & 0xF);
+      if (blk[16 + l] & (1 << (2 * grp + hi))) q += 16;
+      return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(dmin, (float)m));
+    }
+    case T_Q6_K: {
+      int64_t nb = K / 256, b = k / 256;
+      int e = (int)(k % 256), hf = e / 128, in = e % 128, quarter = in / 32, l = in % 32;
+      const uint8_t* ql = row + b * 128 + 64 * hf + 32 * (quarter & 1) + l;
+      const uint8_t* qh = row + nb * 128 + b * 64 + 32 * hf + l;
+      int8_t sc = (int8_t)row[nb * 192 + b * 16 + 8 * hf + l / 16 + 2 * quarter];
+      float d = ld_f16(row + nb * 208 + b * 2);
+      int nib = quarter >= 2 ? (*ql >> 4) : (*ql & 0xF);
+      int q = (nib | (((*qh >> (2 * quarter)) & 3) << 4)) - 32;
+      return __fmul_rn(__fmul_rn(d, (float)sc), (float)q);
+    }
+  }
+  return 0.f;
+}
+
+__global__ void dequant_rows_kernel(DTensor t, int64_t row0, int64_t rows, float* out) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * t.k) return;
+  int64_t r = i / t.k, k = i - r * t.k;
+  out[i] = dequant_elem(t.type, t.data + (row0 + r) * t.stride, t.k, k);
+}
+int dequant_rows(const DTensor& t, int64_t row0, int64_t rows, float* out, cudaStream_t st) {
+  int64_t n = rows * t.k;
+  dequant_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(t, row0, rows, out);
+  B200_CUDA(cudaGetLastError());
+  return OK;
+}
+
+// Embedding gather on the device (the reference dequantises the row on the host and
+// uploads it: llm/model.go:125-144).
+__global__ void embed_kernel(EmbedParams p) {
+  const int n = blockIdx.x;
+  const int64_t id = p.ids[n];
+  const uint8_t* row = p.embd.data + id * p.embd.stride;
+  for (int k = threadIdx.x; k < p.H; k += blockDim.x) p.h[(size_t)n * p.H + k] = dequant_elem(p.embd.type, row, p.H, k);
+}
+int launch_embed(const EmbedParams& p, cudaStream_t st) {
+  embed_kernel<<<p.M, 256, 0, st>>>(p);
+  B200_CUDA(cudaGetLastError());
+  return OK;
+}
+
+// =========================================================================================
+// PDL launch helper
+// =========================================================================================
+template <class... KArgs, class... Args>
+static int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, bool pdl, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+  B200_CUDA(cudaLaunchKernelEx(&cfg, kernel, args...));
+  return OK;
+}
+
+// =========================================================================================
+// Router: ffn_norm + router GEMV (exact f32 dequant) + softmax + top-k + work list
+// (reference: llm/moe.go:219-282; shaders/llm_moe_router.comp, llm_moe_route_decode.comp)
+// =========================================================================================
+constexpr int RT_ROWS = 8;    // router rows per CTA: one per warp
+constexpr int RT_CHUNK = 32;  // tokens staged in shared memory at a time
+
+__global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  __half* xs = reinterpret_cast<__half*>(smem);  // [chunk][H] normalised activations, fp16
+  __shared__ float scratch[8];
+  __shared__ int is_last;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, H = p.H, M = p.M;
+  pdl_wait();
+  pdl_launch();
+  const int row = blockIdx.x * RT_ROWS + warp;  // of the nE + 1 outputs; the last is the shared-expert gate
+  for (int n0 = 0; n0 < M; n0 += RT_CHUNK) {
+    const int nc = min(RT_CHUNK, M - n0);
+    __syncthreads();
+    for (int n = 0; n < nc; n++) {
+      const float* h = p.h + (size_t)(n0 + n) * H;
+      float s = 0.f;
+      for (int k = tid * 4; k < H; k += 1024) {
+        float4 v = *reinterpret_cast<const float4*>(h + k);
+        s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
+      s = warp_sum(s);
+      __syncthreads();
+      if (lane == 0) scratch[warp] = s;
+      __syncthreads();
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; w++) tot += scratch[w];
+      const float scale = 1.0f / sqrtf(tot / (float)H + p.eps);
+      for (int k = tid; k < H; k += 256) xs[(size_t)n * H + k] = __float2half_rn(h[k] * scale * p.gamma[k]);
+    }
+    __syncthreads();
+    if (row <= p.nE) {
+      for (int n = 0; n < nc; n++) {
+        const __half* x = xs + (size_t)n * H;
+        float acc = 0.f;
+        if (row == p.nE) {
+          for (int k = lane; k < H; k += 32) acc = fmaf(p.sh_gate[k], __half2float(x[k]), acc);
+        } else {
+          const uint8_t* wr = p.router.data + (size_t)row * p.router.stride;
+          if (p.router.type == T_Q8_0) {
+            const int nb = H / 32;
+            for (int k0 = lane * 16; k0 < H; k0 += 512) {
+              uint4 q = *reinterpret_cast<const uint4*>(wr + k0);
+              const float d = ld_f16(wr + nb * 32 + (k0 / 32) * 2);
+              const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+              for (int j = 0; j < 16; j++) {
+                float wv = __fmul_rn((float)(int8_t)((w[j >> 2] >> (8 * (j & 3))) & 0xFF), d);
+                acc = fmaf(wv, __half2float(x[k0 + j]), acc);
+              }
+            }
+          } else {
+            for (int k = lane; k < H; k += 32) acc = fmaf(dequant_elem(p.router.type, wr, H, k), __half2float(x[k]), acc);
+          }
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) {
+          if (row == p.nE) p.topk_w[(size_t)(n0 + n) * (p.used + 1) + p.used] = sigmoid_acc(acc);
+          else p.logits[(size_t)(n0 + n) * p.nE + row] = acc;
+        }
+      }
+    }
+  }
+  // the last CTA to finish routes every token and builds the expert work list
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) is_last = (atomicAdd(p.ticket, 1) == (int)gridDim.x - 1);
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const int nE = p.nE, used = p.used;
+  int* counts = reinterpret_cast<int*>(smem);  // [nE + 1] reuse of xs
+  int* offs = counts + nE + 1;                 // [nE + 1]
+  __syncthreads();
+  for (int n = warp; n < M; n += 8) {
+    const float* lg = p.logits + (size_t)n * nE;
+    float* pr = p.probs + (size_t)n * nE;
+    float mx = -INFINITY;
+    for (int e = lane; e < nE; e += 32) mx = fmaxf(mx, __ldcg(lg + e));
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int e = lane; e < nE; e += 32) { float v = expf(__ldcg(lg + e) - mx); pr[e] = v; sum += v; }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < nE; e += 32) pr[e] *= inv;
+    __syncwarp();
+    // top-k by descending probability, ties to the lower index (llm/moe.go:249-252).
+    // Lane owns experts lane + 32*i; `taken` marks the ones already chosen.
+    float wsum = 0.f, last_p = 0.f;
+    uint32_t taken = 0;
+    for (int k = 0; k <= used; k++) {
+      float bv = -1.f; int bi = 0x7fffffff;
+      for (int e = lane, i = 0; e < nE; e += 32, i++) {
+        if (taken >> i & 1u) continue;
+        float v = pr[e];
+        if (v > bv) { bv = v; bi = e; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      if (k == used) {
+        if (lane == 0 && p.margin) p.margin[n] = last_p > 0.f ? (last_p - fmaxf(bv, 0.f)) / last_p : 0.f;
+        break;
+      }
+      if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+      if (lane == 0) { p.topk[(size_t)n * used + k] = bi; p.topk_w[(size_t)n * (used + 1) + k] = bv; }
+      wsum += bv; last_p = bv;
+    }
+    __syncwarp();
+    // normalise the weights (llm/moe.go:256-282)
+    if (wsum < 6.103515625e-5f) wsum = 6.103515625e-5f;
+    if (lane < used) {
+      float* w = p.topk_w + (size_t)n * (used + 1) + lane;
+      *w = *w / wsum;
+    }
+  }
+  __syncthreads();
+  // work list: pair id = n*(used+1) + slot; slot == used is the shared expert
+  for (int i = tid; i <= nE; i += 256) counts[i] = 0;
+  __syncthreads();
+  for (int i = tid; i < M * used; i += 256) atomicAdd(&counts[p.topk[i]], 1);
+  __syncthreads();
+  if (tid == 0) {
+    int off = 0, ne = 0;
+    for (int e = 0; e < nE; e++) {
+      offs[e] = off;
+      for (int c = 0; c < counts[e]; c += 8) {
+        if (ne < p.max_entries) p.entries[ne] = make_int4(e, off + c, min(8, counts[e] - c), 0);
+        ne++;
+      }
+      off += counts[e];
+      counts[e] = 0;
+    }
+    for (int c = 0; c < M; c += 8) {
+      if (ne < p.max_entries) p.entries[ne] = make_int4(-1, off + c, min(8, M - c), 0);
+      ne++;
+    }
+    offs[nE] = off;
+    *p.n_entries = ne < p.max_entries ? ne : p.max_entries;
+    *p.ticket = 0;
+  }
+  __syncthreads();
+  for (int i = tid; i < M * used; i += 256) {
+    int e = p.topk[i], n = i / used, k = i - n * used;
+    int pos = atomicAdd(&counts[e], 1);
+    p.cols[offs[e] + pos] = n * (used + 1) + k;
+  }
+  for (int n = tid; n < M; n += 256) p.cols[offs[nE] + n] = n * (used + 1) + used;
+}
+
+int launch_router(const RouterParams& p, bool pdl, cudaStream_t st) {
+  size_t smem = (size_t)(p.M < RT_CHUNK ? p.M : RT_CHUNK) * p.H * sizeof(__half);
+  size_t need = (size_t)(2 * (p.nE + 1)) * sizeof(int);
+  if (smem < need) smem = need;
+  static bool attr = false;
+  if (!attr) { cudaFuncSetAttribute(router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr = true; }
+  if (smem > 200 * 1024 || p.nE > 1024 || p.used > 32) { set_error("router: shape outside kernel limits"); return ECAPACITY; }
+  int grid = (p.nE + 1 + RT_ROWS - 1) / RT_ROWS;
+  return launch_k(router_kernel, dim3(grid), dim3(256), smem, pdl, st, p);
+}
+
+// h[n] += sum_k w_k * down[n,k] (slot order) + sigmoid(gate) * shared  (llm/moe.go:347-357, 403-406)
+__global__ void __launch_bounds__(256) moe_combine_kernel(CombineParams p) {
+  pdl_wait();
+  pdl_launch();
+  const int n = blockIdx.y, j = (blockIdx.x * 256 + threadIdx.x) * 4;
+  if (j >= p.H) return;
+  const int slots = p.used + 1;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int k = 0; k < p.used; k++) {
+    const float w = p.topk_w[(size_t)n * slots + k];
+    float4 d = *reinterpret_cast<const float4*>(p.down + ((size_t)n * slots + k) * p.H + j);
+    acc.x += d.x * w; acc.y += d.y * w; acc.z += d.z * w; acc.w += d.w * w;
+  }
+  const float sg = p.topk_w[(size_t)n * slots + p.used];
+  float4 s = *reinterpret_cast<const float4*>(p.down + ((size_t)n * slots + p.used) * p.H + j);
+  float4* hp = reinterpret_cast<float4*>(p.h + (size_t)n * p.H + j);
+  float4 h = *hp;
+  h.x += acc.x + s.x * sg; h.y += acc.y + s.y * sg; h.z += acc.z + s.z * sg; h.w += acc.w + s.w * sg;
+  *hp = h;
+}
+int launch_moe_combine(const CombineParams& p, bool pdl, cudaStream_t st) {
+  return launch_k(moe_combine_kernel, dim3((p.H / 4 + 255) / 256, p.M), dim3(256), 0, pdl, st, p);
+}
+
+// =========================================================================================
+// Gated DeltaNet step: alpha/beta projections, causal conv + SiLU, L2 norm, gates, the
+// delta-rule state update and read-out (reference: llm/deltanet.go:263-321, 365-455;
+// shaders/llm_dn_conv.comp, llm_dn_scan.comp, llm_seq_hist.comp).
+// grid (Hv * 4, n_seq): a CTA owns 32 of the 128 state rows of one value head of one
+// sequence, keeps them in registers and walks the sequence's tokens in order.
+// =========================================================================================
+__device__ __forceinline__ float softplus_ref(float x) {  // llm/deltanet.go:450-455
+  if (x > 20.f) return x;
+  return logf(1.0f + expf(x));
+}
+__device__ __forceinline__ float silu_acc(float x) { return x * sigmoid_acc(x); }
+
+__global__ void __launch_bounds__(128) dn_step_kernel(DnStepParams p) {
+  const int D = 128, RB = 4;
+  const int h = blockIdx.x / RB, rb = blockIdx.x % RB, hk = h % p.Hk;
+  const SeqDesc sq = p.seqs[blockIdx.y];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qk = p.Hk * D, H = p.H;
+  __shared__ float qs[128], ks[128], vs[32], red[16];
+  const int ch_q = hk * D + tid, ch_k = qk + hk * D + tid, ch_v = 2 * qk + h * D + rb * 32 + (tid & 31);
+  const float4 cwq = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch_q * 4);
+  const float4 cwk = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch_k * 4);
+  const float4 cwv = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch_v * 4);
+  const float a_h = p.ssm_a[h], dtb = p.dt_bias[h];
+  pdl_wait();
+  pdl_launch();
+  // conv history: the three inputs before pos0, zeros before the sequence start
+  // Every CTA keeps a private ring of its own 288 conv inputs (q 128 | k 128 | v 32), indexed
+  // by position, so no CTA ever reads what another one writes.
+  float* ring = p.ring + (size_t)sq.slot * p.ring_slot_stride + (size_t)blockIdx.x * (DN_RING * DN_RING_W);
+  float hq[3], hkk[3], hv[3];
+#pragma unroll
+  for (int j = 0; j < 3; j++) {
+    const int pos = sq.pos0 - 3 + j;
+    const float* r = ring + (size_t)(pos & (DN_RING - 1)) * DN_RING_W;
+    hq[j] = pos >= 0 ? r[tid] : 0.f;
+    hkk[j] = pos >= 0 ? r[128 + tid] : 0.f;
+    hv[j] = pos >= 0 ? r[256 + (tid & 31)] : 0.f;
+  }
+  // state rows of this warp: j = rb*32 + warp*8 + r, four floats per lane
+  float* S = p.state + (size_t)sq.slot * p.state_slot_stride + (size_t)h * D * D;
+  const int j0 = rb * 32 + warp * 8;
+  float4 s[8];
+#pragma unroll
+  for (int r = 0; r < 8; r++) s[r] = *reinterpret_cast<const float4*>(S + (size_t)(j0 + r) * D + lane * 4);
+  const float oscale = 1.0f / sqrtf((float)D);
+
+  for (int i = 0; i < sq.n; i++) {
+    const int row = sq.row0 + i, pos = sq.pos0 + i;
+    const float* pr = p.proj + (size_t)row * p.ldp;
+    // alpha / beta: F32 weights against the fp16-rounded block input
+    const __half* xn = p.xn + (size_t)row * H;
+    float pa = 0.f, pb = 0.f;
+    for (int k = tid * 4; k < H; k += 512) {
+      float4 wa = *reinterpret_cast<const float4*>(p.alpha_w + (size_t)h * H + k);
+      float4 wb = *reinterpret_cast<const float4*>(p.beta_w + (size_t)h * H + k);
+      const __half2 x01 = *reinterpret_cast<const __half2*>(xn + k), x23 = *reinterpret_cast<const __half2*>(xn + k + 2);
+      const float2 f01 = __half22float2(x01), f23 = __half22float2(x23);
+      pa += wa.x * f01.x + wa.y * f01.y + wa.z * f23.x + wa.w * f23.y;
+      pb += wb.x * f01.x + wb.y * f01.y + wb.z * f23.x + wb.w * f23.y;
+    }
+    // conv + SiLU for q, k (whole head) and this CTA's 32 v channels
+    const float cq = pr[ch_q], ck = pr[ch_k], cv = pr[ch_v];
+    const float q = silu_acc(hq[0] * cwq.x + hq[1] * cwq.y + hq[2] * cwq.z + cq * cwq.w);
+    const float k = silu_acc(hkk[0] * cwk.x + hkk[1] * cwk.y + hkk[2] * cwk.z + ck * cwk.w);
+    const float v = silu_acc(hv[0] * cwv.x + hv[1] * cwv.y + hv[2] * cwv.z + cv * cwv.w);
+    hq[0] = hq[1]; hq[1] = hq[2]; hq[2] = cq;
+    hkk[0] = hkk[1]; hkk[1] = hkk[2]; hkk[2] = ck;
+    hv[0] = hv[1]; hv[1] = hv[2]; hv[2] = cv;
+    // the ring keeps every token's conv input by position (rollback = moving `past` back)
+    {
+      float* rw = ring + (size_t)(pos & (DN_RING - 1)) * DN_RING_W;
+      rw[tid] = cq; rw[128 + tid] = ck;
+      if (tid < 32) rw[256 + tid] = cv;
+    }
+    float sq2 = warp_sum(q * q), sk2 = warp_sum(k * k);
+    pa = warp_sum(pa); pb = warp_sum(pb);
+    __syncthreads();
+    if (lane == 0) { red[warp] = sq2; red[4 + warp] = sk2; red[8 + warp] = pa; red[12 + warp] = pb; }
+    if (tid < 32) vs[tid] = v;
+    __syncthreads();
+    const float qn = 1.0f / sqrtf(red[0] + red[1] + red[2] + red[3] + p.eps);
+    const float kn = 1.0f / sqrtf(red[4] + red[5] + red[6] + red[7] + p.eps);
+    const float alpha = red[8] + red[9] + red[10] + red[11], betar = red[12] + red[13] + red[14] + red[15];
+    qs[tid] = q * qn;
+    ks[tid] = k * kn;
+    __syncthreads();
+    const float g = expf(softplus_ref(alpha + dtb) * a_h);
+    const float beta = sigmoid_acc(betar);
+    const float4 k4 = *reinterpret_cast<const float4*>(ks + lane * 4);
+    const float4 q4 = *reinterpret_cast<const float4*>(qs + lane * 4);
+    float kv[8], oo[8];
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+      s[r].x *= g; s[r].y *= g; s[r].z *= g; s[r].w *= g;
+      kv[r] = s[r].x * k4.x + s[r].y * k4.y + s[r].z * k4.z + s[r].w * k4.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int r = 0; r < 8; r++) kv[r] += __shfl_xor_sync(0xffffffffu, kv[r], o);
+    }
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+      const float dj = (vs[warp * 8 + r] - kv[r]) * beta;
+      s[r].x += dj * k4.x; s[r].y += dj * k4.y; s[r].z += dj * k4.z; s[r].w += dj * k4.w;
+      oo[r] = s[r].x * q4.x + s[r].y * q4.y + s[r].z * q4.z + s[r].w * q4.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int r = 0; r < 8; r++) oo[r] += __shfl_xor_sync(0xffffffffu, oo[r], o);
+    }
+    if (lane < 8) {
+      float ov = oo[0];
+#pragma unroll
+      for (int r = 1; r < 8; r++) ov = lane == r ? oo[r] : ov;
+      p.out[(size_t)row * (p.Hv * D) + h * D + j0 + lane] = ov * oscale;
+    }
+    if (p.mid != nullptr) {  // state after token i, for keep-prefix speculation
+      float* Sm = p.mid + (size_t)blockIdx.y * p.mid_seq_stride + (size_t)i * p.mid_stride + (size_t)h * D * D;
+#pragma unroll
+      for (int r = 0; r < 8; r++) *reinterpret_cast<float4*>(Sm + (size_t)(j0 + r) * D + lane * 4) = s[r];
+    }
+    __syncthreads();
+  }
+  if (p.mid == nullptr) {
+#pragma unroll
+    for (int r = 0; r < 8; r++) *reinterpret_cast<float4*>(S + (size_t)(j0 + r) * D + lane * 4) = s[r];
+  }
+}
+
+int launch_dn_step(const DnStepParams& p, bool pdl, cudaStream_t st) {
+  if (p.D != 128 || p.conv != 4) { set_error("dn_step: head dim must be 128 and conv kernel 4"); return EINVAL_; }
+  return launch_k(dn_step_kernel, dim3(p.Hv * 4, p.n_seq), dim3(128), 0, pdl, st, p);
+}
+
+// =========================================================================================
+// Attention pre-pass: per-head RMSNorm of q and k, NeoX partial rotary from a host-built
+// table, fp16 K/V into the cache (reference: llm/attn.go:144-184, 510-586;
+// shaders/llm_attn_pack.comp). grid (Hq + 2*Hkv, M), block hd.
+// =========================================================================================
+__global__ void attn_pack_kernel(AttnParams p) {
+  const int hd = p.hd, d = threadIdx.x, n = blockIdx.y, which = blockIdx.x;
+  __shared__ float buf[256], red[8];
+  pdl_wait();
+  pdl_launch();
+  const float* pr = p.proj + (size_t)n * p.ldp;
+  const int pos = p.row_pos[n], slot = p.row_slot[n];
+  const int kv_off = p.Hq * 2 * hd;
+  float x; const float* gamma = nullptr;
+  if (which < p.Hq) { x = pr[which * 2 * hd + d]; gamma = p.q_norm; }
+  else if (which < p.Hq + p.Hkv) { x = pr[kv_off + (which - p.Hq) * hd + d]; gamma = p.k_norm; }
+  else x = pr[kv_off + p.Hkv * hd + (which - p.Hq - p.Hkv) * hd + d];
+  if (gamma != nullptr) {
+    float ss = warp_sum(x * x);
+    if ((d & 31) == 0) red[d >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+    for (int w = 0; w < hd / 32; w++) tot += red[w];
+    x = x * (1.0f / sqrtf(tot / (float)hd + p.eps)) * gamma[d];
+    buf[d] = x;
+    __syncthreads();
+    const int half = p.rope_dims / 2;
+    if (d < p.rope_dims) {
+      const int i = d < half ? d : d - half;
+      const float2 cs = *reinterpret_cast<const float2*>(p.rope + ((size_t)(pos + p.rope_off) * half + i) * 2);
+      const float x0 = buf[i], x1 = buf[i + half];
+      x = d < half ? x0 * cs.x - x1 * cs.y : x0 * cs.y + x1 * cs.x;
+    }
+  }
+  if (which < p.Hq) p.q16[((size_t)n * p.Hq + which) * hd + d] = __float2half_rn(x);
+  else {
+    const bool isk = which < p.Hq + p.Hkv;
+    const int kh = isk ? which - p.Hq : which - p.Hq - p.Hkv;
+    __half* c = (isk ? p.kcache : p.vcache) + (size_t)slot * p.slot_stride + ((size_t)pos * p.Hkv + kh) * hd;
+    c[d] = __float2half_rn(x);
+  }
+}
+int launch_attn_pack(const AttnParams& p, bool pdl, cudaStream_t st) {
+  if (p.hd > 256 || p.hd % 32) { set_error("attn_pack: head dim must be a multiple of 32, at most 256"); return EINVAL_; }
+  return launch_k(attn_pack_kernel, dim3(p.Hq + 2 * p.Hkv, p.M), dim3(p.hd), 0, pdl, st, p);
+}
+
+// =========================================================================================
+// Split-KV decode attention (reference: llm/attn.go:190-217, 444-496;
+// shaders/llm_attn_wmma.comp -DSPLITK, llm_attn_combine.comp). grid (nsplit, Hkv, M):
+// a CTA of 4 warps covers `split_cells` cells of one KV head for the G query heads that
+// share it; a lane owns hd/32 dims. The last CTA of a (row, kv head) merges the splits,
+// applies sigmoid(gate) and writes the fp16 context.
+// =========================================================================================
+template <int DPL, int G>  // dims per lane, query heads per kv head
+__global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
+  const int hd = DPL * 32;
+  const int split = blockIdx.x, kvh = blockIdx.y, n = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  __shared__ float sm_m[4][G], sm_l[4][G];
+  __shared__ float sm_o[4][G][DPL * 32];
+  __shared__ int is_last;
+  pdl_wait();
+  pdl_launch();
+  const int pos = p.row_pos[n], slot = p.row_slot[n];
+  const int ncell = pos + 1;
+  const int c0 = split * p.split_cells, c1 = min(ncell, c0 + p.split_cells);
+  const float scale = 1.0f / sqrtf((float)hd);
+  float q[G][DPL], o[G][DPL], m[G], l[G];
+#pragma unroll
+  for (int hh = 0; hh < G; hh++) {
+    const __half* qp = p.q16 + ((size_t)n * p.Hq + kvh * G + hh) * hd + lane * DPL;
+#pragma unroll
+    for (int d = 0; d < DPL; d++) { q[hh][d] = __half2float(qp[d]); o[hh][d] = 0.f; }
+    m[hh] = -INFINITY; l[hh] = 0.f;
+  }
+  const __half* kc = p.kcache + (size_t)slot * p.slot_stride + (size_t)kvh * hd + lane * DPL;
+  const __half* vc = p.vcache + (size_t)slot * p.slot_stride + (size_t)kvh * hd + lane * DPL;
+  const size_t cell_stride = (size_t)p.Hkv * hd;
+  for (int c = c0 + warp; c < c1; c += 4) {
+    float kf[DPL], vf[DPL];
+    const __half* kp = kc + (size_t)c * cell_stride;
+    const __half* vp = vc + (size_t)c * cell_stride;
+#pragma unroll
+    for (int d = 0; d < DPL; d += 2) {
+      float2 a = __half22float2(*reinterpret_cast<const __half2*>(kp + d));
+      float2 b = __half22float2(*reinterpret_cast<const __half2*>(vp + d));
+      kf[d] = a.x; kf[d + 1] = a.y; vf[d] = b.x; vf[d + 1] = b.y;
+    }
+    float sc[G];
+#pragma unroll
+    for (int hh = 0; hh < G; hh++) {
+      float a = 0.f;
+#pragma unroll
+      for (int d = 0; d < DPL; d++) a = fmaf(q[hh][d], kf[d], a);
+      sc[hh] = a;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+      for (int hh = 0; hh < G; hh++) sc[hh] += __shfl_xor_sync(0xffffffffu, sc[hh], off);
+    }
+#pragma unroll
+    for (int hh = 0; hh < G; hh++) {
+      const float sv = sc[hh] * scale;
+      const float mn = fmaxf(m[hh], sv);
+      const float corr = expf(m[hh] - mn), pw = expf(sv - mn);
+      l[hh] = l[hh] * corr + pw;
+#pragma unroll
+      for (int d = 0; d < DPL; d++) o[hh][d] = fmaf(pw, vf[d], o[hh][d] * corr);
+      m[hh] = mn;
+    }
+  }
+  // merge the four warps, then publish this split's partial
+#pragma unroll
+  for (int hh = 0; hh < G; hh++) {
+    if (lane == 0) { sm_m[warp][hh] = m[hh]; sm_l[warp][hh] = l[hh]; }
+#pragma unroll
+    for (int d = 0; d < DPL; d++) sm_o[warp][hh][lane * DPL + d] = o[hh][d];
+  }
+  __syncthreads();
+  const int PW = hd + 2;
+  for (int i = tid; i < G * hd; i += 128) {
+    const int hh = i / hd, d = i - hh * hd;
+    float mm = fmaxf(fmaxf(sm_m[0][hh], sm_m[1][hh]), fmaxf(sm_m[2][hh], sm_m[3][hh]));
+    float ov = 0.f, lv = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      const float f = sm_m[w][hh] == -INFINITY ? 0.f : expf(sm_m[w][hh] - mm);
+      ov += sm_o[w][hh][d] * f; lv += sm_l[w][hh] * f;
+    }
+    float* part = p.partial + (((size_t)n * p.Hq + kvh * G + hh) * p.nsplit + split) * PW;
+    part[d] = ov;
+    if (d == 0) { part[hd] = mm; part[hd + 1] = lv; }
+  }
+  __threadfence();
+  __syncthreads();
+  int* ticket = p.tickets + (size_t)n * p.Hkv + kvh;
+  if (tid == 0) is_last = (atomicAdd(ticket, 1) == (int)gridDim.x - 1);
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (tid == 0) *ticket = 0;
+  const int nlive = (ncell + p.split_cells - 1) / p.split_cells;
+  const int gate_off = hd;  // per head: hd query dims then hd gate dims
+  for (int i = tid; i < G * hd; i += 128) {
+    const int hh = i / hd, d = i - hh * hd, head = kvh * G + hh;
+    const float* part = p.partial + ((size_t)n * p.Hq + head) * p.nsplit * PW;
+    float mm = -INFINITY;
+    for (int s = 0; s < nlive; s++) mm = fmaxf(mm, __ldcg(part + (size_t)s * PW + hd));
+    float ov = 0.f, lv = 0.f;
+    for (int s = 0; s < nlive; s++) {
+      const float f = expf(__ldcg(part + (size_t)s * PW + hd) - mm);
+      ov += __ldcg(part + (size_t)s * PW + d) * f;
+      lv += __ldcg(part + (size_t)s * PW + hd + 1) * f;
+    }
+    const float gate = p.proj[(size_t)n * p.ldp + head * 2 * hd + gate_off + d];
+    p.ctx16[(size_t)n * p.Hq * hd + head * hd + d] = __float2half_rn(ov / lv * sigmoid_acc(gate));
+  }
+}
+
+int launch_attn_decode(const AttnParams& p, bool pdl, cudaStream_t st) {
+  const int G = p.Hq / p.Hkv;
+  dim3 grid(p.nsplit, p.Hkv, p.M), block(128);
+  if (p.hd == 256 && G == 8) return launch_k(attn_decode_kernel<8, 8>, grid, block, 0, pdl, st, p);
+  if (p.hd == 128 && G == 4) return launch_k(attn_decode_kernel<4, 4>, grid, block, 0, pdl, st, p);
+  if (p.hd == 128 && G == 8) return launch_k(attn_decode_kernel<4, 8>, grid, block, 0, pdl, st, p);
+  if (p.hd == 256 && G == 4) return launch_k(attn_decode_kernel<8, 4>, grid, block, 0, pdl, st, p);
+  set_error("attn_decode: unsupported head_dim / group size");
+  return EINVAL_;
+}
+
+// =========================================================================================
+// Greedy sampling: argmax with ties to the lowest id (reference: llm/sample.go:359-367)
+// =========================================================================================
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* logits, int V, int32_t* out) {
+  __shared__ float bv[32];
+  __shared__ int bi[32];
+  pdl_wait();
+  pdl_launch();
+  const float* lg = logits + (size_t)blockIdx.x * V;
+  float v = -INFINITY; int idx = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += 1024) {
+    float x = lg[i];
+    if (x > v) { v = x; idx = i; }
+  }
+  auto better = [](float a, int ai, float b, int bi2) { return a > b || (a == b && ai < bi2); };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (better(ov, oi, v, idx)) { v = ov; idx = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { bv[threadIdx.x >> 5] = v; bi[threadIdx.x >> 5] = idx; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    v = bv[threadIdx.x]; idx = bi[threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (better(ov, oi, v, idx)) { v = ov; idx = oi; }
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+  }
+}
+int launch_argmax(const float* logits, int M, int V, int32_t* out, bool pdl, cudaStream_t st) {
+  return launch_k(argmax_kernel, dim3(M), dim3(1024), 0, pdl, st, logits, V, out);
+}
+
+__global__ void advance_kernel(int32_t* ids, const int32_t* next, int* row_pos, SeqDesc* seqs, int M, int32_t* history, int* hist_len) {
+  const int i = threadIdx.x;
+  if (i < M) {
+    ids[i] = next[i];
+    row_pos[i] += 1;
+    seqs[i].pos0 += 1;
+    if (history != nullptr) history[(size_t)(*hist_len) * M + i] = next[i];
+  }
+  __syncthreads();
+  if (i == 0 && hist_len != nullptr) *hist_len += 1;
+}
+int launch_advance(int32_t* ids, const int32_t* next, int* row_pos, SeqDesc* seqs, int M, int32_t* history, int* hist_len, cudaStream_t st) {
+  if (M > 1024) { set_error("advance: too many rows"); return ECAPACITY; }
+  advance_kernel<<<1, 1024, 0, st>>>(ids, next, row_pos, seqs, M, history, hist_len);
+  B200_CUDA(cudaGetLastError());
+  return OK;
+}
+
+}  // namespace b200

@@ -1,0 +1,98 @@
+// Launch wrappers of the token-loop kernels (definitions in kernels.cu / qgemv.cu).
+#pragma once
+#include "common.cuh"
+#include "qgemv.cuh"
+
+namespace b200 {
+
+// ---- layout -----------------------------------------------------------------------------
+int64_t device_row_stride(uint32_t type, int64_t k);
+// GGUF rows -> device rows (re-lays Q6_K / Q8_0 rows as planes; plain copy otherwise) and back.
+int repack_rows(uint32_t type, int64_t k, int64_t rows, const uint8_t* gguf_dev, uint8_t* dst_dev, cudaStream_t st);
+int unpack_rows(uint32_t type, int64_t k, int64_t rows, const uint8_t* dev, uint8_t* gguf_dev, cudaStream_t st);
+// f32 values of rows [row0, row0+rows) of a device tensor (bit-exact with gguf/dequant.go)
+int dequant_rows(const DTensor& t, int64_t row0, int64_t rows, float* out, cudaStream_t st);
+
+// ---- pass description ---------------------------------------------------------------------
+// A pass advances `n_seq` sequences; sequence i owns activation rows [row0, row0+n) and
+// its tokens sit at positions pos0, pos0+1, ... of slot `slot`.
+struct SeqDesc {
+  int slot, row0, n, pos0;
+};
+
+struct EmbedParams {
+  DTensor embd;
+  const int32_t* ids;  // [M]
+  float* h;            // [M][H]
+  int M, H;
+};
+int launch_embed(const EmbedParams& p, cudaStream_t st);
+
+// K-quant projections; `pdl` marks the launch as a programmatic dependent of the previous kernel.
+int launch_qgemv(uint32_t type, int pro, int epi, bool dual, bool grouped, const QGemvParams& p, int max_entries, bool pdl, cudaStream_t st);
+
+struct RouterParams {
+  const float* h; const float* gamma; float eps;   // ffn_norm input
+  DTensor router;                                  // [nE][H], F32 / F16 / Q8_0 (planes)
+  const float* sh_gate;                            // [H] F32
+  int M, H, nE, used;
+  float* logits;       // [M][nE]
+  float* probs;        // [M][nE]
+  int32_t* topk;       // [M][used]
+  float* topk_w;       // [M][used+1] (last = sigmoid(shared gate))
+  float* margin;       // [M] optional: (p_k - p_{k+1}) / p_k
+  int4* entries; int* n_entries; int* cols;   // expert work list for the grouped kernels
+  int* ticket;
+  int max_entries;
+};
+int launch_router(const RouterParams& p, bool pdl, cudaStream_t st);
+
+struct CombineParams {
+  float* h; const float* down; const float* topk_w; int M, H, used;
+};
+int launch_moe_combine(const CombineParams& p, bool pdl, cudaStream_t st);
+
+struct DnStepParams {
+  const float* proj; int64_t ldp;            // [M][ldp]: q | k | v | z
+  const __half* xn;                          // [M][H] normalised block input (fp16)
+  const float *alpha_w, *beta_w;             // [Hv][H] F32
+  const float *conv_w, *ssm_a, *dt_bias;     // [cw][K], [Hv], [Hv]
+  float* state;                              // [slots][Hv][D][D], s[j][i] = S[i][j]
+  int64_t state_slot_stride;
+  float* ring;                               // [slots][Hv*4][DN_RING][DN_RING_W]
+  int64_t ring_slot_stride;
+  const SeqDesc* seqs; int n_seq;
+  float* out;                                // [M][Hv*D]
+  float* mid;                                // speculation: [n_seq][rows][Hv][D][D] state after each token; the slot's own state is then left untouched
+  int64_t mid_stride, mid_seq_stride;        // floats between consecutive rows / sequences of mid
+  int H, Hk, Hv, D, conv;
+  float eps;
+};
+constexpr int DN_RING = 8;      // positions kept per ring
+constexpr int DN_RING_W = 288;  // conv inputs per CTA: q 128 | k 128 | v 32
+int launch_dn_step(const DnStepParams& p, bool pdl, cudaStream_t st);
+
+struct AttnParams {
+  const float* proj; int64_t ldp;            // [M][ldp]: per head (q | gate) x Hq, then k, then v
+  const float *q_norm, *k_norm;              // [hd]
+  const float* rope;                         // [n_kv][half][2] cos, sin
+  __half *kcache, *vcache;                   // [slots][n_kv][Hkv][hd]
+  int64_t slot_stride;                       // halves per slot
+  const int* row_slot; const int* row_pos;   // [M]
+  __half* q16;                               // [M][Hq][hd]
+  float* partial;                            // [M][Hq][nsplit][hd+2]
+  int* tickets;                              // [M][Hkv]
+  __half* ctx16;                             // [M][Hq*hd]
+  int M, Hq, Hkv, hd, rope_dims, n_kv, split_cells, nsplit;
+  int rope_off;                              // rotary position = cell + rope_off (1 for the draft layer)
+  float eps;
+};
+int launch_attn_pack(const AttnParams& p, bool pdl, cudaStream_t st);
+int launch_attn_decode(const AttnParams& p, bool pdl, cudaStream_t st);
+
+int launch_argmax(const float* logits, int M, int V, int32_t* out, bool pdl, cudaStream_t st);
+
+// rows of the same pass: ids[i] = next[i], pos[i] += 1 (device-resident greedy loop)
+int launch_advance(int32_t* ids, const int32_t* next, int* row_pos, SeqDesc* seqs, int M, int32_t* history, int* hist_len, cudaStream_t st);
+
+}  // namespace b200

@@ -1,0 +1,570 @@
+// Fused K-quant dequant "GEMV" for 1..8 activation rows per launch column-tile.
+//
+// y[n][r] = sum_k W[r][k] * x16[n][k], W read as the checkpoint's own K-quant blocks.
+//
+// Replaces the reference's dense decode projection and decode expert FFN kernels
+// (shaders/llm_gemv.comp:116-263, shaders/llm_moe_gemv.comp:586-786), keeping their
+// arithmetic: activations staged as fp16, weights never rounded, f32 accumulation.
+//
+// Design (B200): a CTA of 8 warps owns 16-row weight tiles; its warps split K by
+// super-block so that every warp issues all of its 128-bit weight loads before anything
+// else. Nibbles are turned into fp16 A-fragments of mma.sync.m16n8k16 directly in
+// registers as the exact integers sc*q (<= 63*31, exact in fp16); the <= 8 activation
+// rows are the B-fragments, read from shared memory; the super-block scale d, and the
+// min term dmin * sum_s m_s * sum_{k in s} x_k (itself one more mma over the eight
+// sub-block sums, split into fp16 hi + lo parts), are applied in f32 per super-block.
+// Partial sums of the K-slices are added in warp order (deterministic), and a column's
+// result depends on that column alone, so a batched pass equals each row stepped alone.
+//
+// Q6_K has no integer sub-scale small enough: sc*(q-32) can reach 4064 and is rounded to
+// fp16 above 2048 (relative error <= 2^-12 on those weights).
+#pragma once
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int QG_WARPS = 8;
+constexpr int QG_THREADS = QG_WARPS * 32;
+constexpr int QG_MAXCOLS = 8;
+
+enum { PRO_F16 = 0, PRO_RMSNORM = 1, PRO_DN_GATED = 2, PRO_CONCAT_NORM = 3 };
+enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
+
+struct QGemvParams {
+  // weights: up to 4 row segments of one fused projection (same type and K)
+  const uint8_t* w[4];
+  const uint8_t* w2[4];      // DUAL: the second tensor (up), same shape as w
+  int seg_end[4];            // exclusive end row of each segment
+  int nseg;
+  int64_t stride;            // bytes per row
+  int K, N;
+  // grouped (per-expert) mode: entries[e] = {expert (<0: shared expert, uses ws/ws2), col_off, col_cnt, 0}
+  const int4* entries;
+  const int* n_entries;
+  const int* cols;           // column -> x / y row ids
+  int64_t expert_stride;     // bytes between consecutive experts
+  const uint8_t* ws;         // shared expert weights (grouped mode)
+  const uint8_t* ws2;
+  int x_div;                 // grouped: x row = cols[c] / x_div
+  // plain mode columns: rows [ztile*8, ztile*8+8) of M
+  int M;
+  int xcols;                 // columns the shared-memory layout is sized for (1..8)
+  const int* row_ids;        // optional: plain mode column c reads/writes row row_ids[c]
+  // activation source
+  const void* x;             // PRO_F16: half [.][ldx]; others: float [.][ldx]
+  int64_t ldx;
+  const float* gamma;        // RMSNORM: [K]; DN_GATED: [head_dim]
+  const float* gamma2;       // CONCAT_NORM: second half's gamma
+  const void* x2;            // CONCAT_NORM: second source (float [.][ldx2])
+  int64_t ldx2;
+  float eps;
+  const float* z;            // DN_GATED: gate pre-activation, float [.][ldz]
+  int64_t ldz;
+  int head_dim;
+  __half* xn_out;            // RMSNORM: optional side output of the normalised row, [.][K]
+  // epilogue
+  float* y;                  // STORE / RESID: float [.][ldy]
+  int64_t ldy;
+  __half* y16;               // SWIGLU: half [.][ldy]
+};
+
+__host__ __device__ inline int qg_xstride(int K) {
+  int base = 2 * K + 16 * (K / 64);
+  int pad = (64 - base % 128 + 128) % 128;
+  return base + pad;
+}
+__host__ __device__ inline size_t qg_smem_bytes(int K, int xcols, bool dual) {
+  size_t xs = (size_t)xcols * qg_xstride(K);
+  size_t sx = (size_t)xcols * (K / 32) * 2 * sizeof(__half);  // hi and lo planes
+  size_t red = (size_t)QG_WARPS * 16 * 8 * sizeof(float) * (dual ? 2 : 1);
+  return xs + ((sx + 15) & ~(size_t)15) + red;
+}
+
+// byte offset of activation element k inside a staged row: 4-groups hold [x0,x2,x1,x3]
+// (the order the nibble unpack produces pairs in), 16 bytes of padding per 64 elements.
+__device__ __forceinline__ int xs_off(int k) {
+  int k4 = k & 3;
+  int p = (k4 == 1) ? 2 : (k4 == 2) ? 1 : k4;
+  return 2 * ((k & ~3) | p) + 16 * (k >> 6);
+}
+
+struct Frag8 {  // A registers of the 8 mmas one 16-byte quad feeds, for one row
+  uint32_t lo02[4], lo13[4], hi02[4], hi13[4];
+};
+
+constexpr uint32_t H2_1024 = 0x64006400u;
+
+__device__ __forceinline__ uint32_t half2_const(float v) {
+  __half2 h = __float2half2_rn(v);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// ---- Q4_K ---------------------------------------------------------------------------
+// Block: d, dmin (fp16), 12 bytes of packed 6-bit (scale, min), 128 bytes of nibbles
+// (reference: gguf/dequant.go:238-276). Thread t of a quad takes 16-byte quads t and t+4:
+// groups t>>1 and (t>>1)+2, i.e. sub-blocks {2th, 2th+1} and {4+2th, 5+2th}.
+struct Q4KRow {
+  uint4 hdr, qa, qb;
+};
+
+__device__ __forceinline__ void q4k_issue(Q4KRow& r, const uint8_t* blk, int t) {
+  r.hdr = ldg_stream(blk);
+  r.qa = ldg_stream(blk + 16 + 16 * t);
+  r.qb = ldg_stream(blk + 16 + 16 * (t + 4));
+}
+
+// (scale, min) byte pairs of the thread's two groups: *_a for quad a, *_b for quad b.
+__device__ __forceinline__ void k4_scales(const uint4& hdr, int th, uint32_t& sc_a, uint32_t& m_a, uint32_t& sc_b, uint32_t& m_b) {
+  int sel = th * 16;
+  uint32_t s0 = (hdr.y >> sel) & 0xFFFFu, s1 = (hdr.z >> sel) & 0xFFFFu, s2 = (hdr.w >> sel) & 0xFFFFu;
+  sc_a = s0 & 0x3F3Fu;
+  m_a = s1 & 0x3F3Fu;
+  sc_b = (s2 & 0x0F0Fu) | ((s0 >> 2) & 0x3030u);
+  m_b = ((s2 >> 4) & 0x0F0Fu) | ((s1 >> 2) & 0x3030u);
+}
+
+// two bytes (b0, b1) -> half2(b0, b1), exact
+__device__ __forceinline__ uint32_t bytes_to_half2(uint32_t two_bytes) {
+  uint32_t magic = __byte_perm(two_bytes, 0x64646464u, 0x4140);  // (b0, 0x64, b1, 0x64)
+  return hadd2_u(magic, half2_const(-1024.f));
+}
+
+struct ScaleConst {  // per (row, group): constants turning magic halves into sc*q
+  uint32_t sl, ol, sh, oh;
+};
+__device__ __forceinline__ ScaleConst make_scale_const(uint32_t sc_pair_bytes) {
+  uint32_t sc2 = bytes_to_half2(sc_pair_bytes);     // (sc_even, sc_odd)
+  uint32_t se = __byte_perm(sc2, 0, 0x1010);        // (sc_even, sc_even)
+  uint32_t so = __byte_perm(sc2, 0, 0x3232);        // (sc_odd, sc_odd)
+  ScaleConst c;
+  c.sl = se;
+  c.ol = hmul2_u(se, half2_const(-1024.f));         // <= 64512, exact
+  c.sh = hmul2_u(so, half2_const(0.0625f));
+  c.oh = hmul2_u(so, half2_const(-64.f));
+  return c;
+}
+
+// One 32-bit word of nibbles (bytes b0..b3): low nibbles belong to the even sub-block,
+// high nibbles to the odd one. Pairs come out as (b0,b2) and (b1,b3).
+__device__ __forceinline__ void q4_unpack_word(uint32_t w, const ScaleConst& c, uint32_t& lo02, uint32_t& lo13, uint32_t& hi02, uint32_t& hi13) {
+  uint32_t w8 = w >> 8;
+  lo02 = hfma2_u(lop3_or_and(w, 0x000F000Fu, H2_1024), c.sl, c.ol);    // (1024+q)*sc - 1024*sc
+  hi02 = hfma2_u(lop3_or_and(w, 0x00F000F0u, H2_1024), c.sh, c.oh);    // (1024+16q)*sc/16 - 64*sc
+  lo13 = hfma2_u(lop3_or_and(w8, 0x000F000Fu, H2_1024), c.sl, c.ol);
+  hi13 = hfma2_u(lop3_or_and(w8, 0x00F000F0u, H2_1024), c.sh, c.oh);
+}
+
+// ---- Q5_K ---------------------------------------------------------------------------
+// Q4_K plus a 32-byte plane of fifth bits at offset 16; nibbles start at 48
+// (reference: gguf/dequant.go:282-318). Bit s of qh[l] belongs to sub-block s.
+struct Q5KRow {
+  uint4 hdr, qh, qa, qb;
+};
+__device__ __forceinline__ void q5k_issue(Q5KRow& r, const uint8_t* blk, int t) {
+  r.hdr = ldg_stream(blk);
+  r.qh = ldg_stream(blk + 16 + 16 * (t & 1));
+  r.qa = ldg_stream(blk + 48 + 16 * t);
+  r.qb = ldg_stream(blk + 48 + 16 * (t + 4));
+}
+// s_even = 2*group. v5 bytes = nibble | bit<<4, then (b0,b2) / (b1,b3) pairs as magic halves.
+__device__ __forceinline__ void q5_unpack_word(uint32_t w, uint32_t qh, int s_even, const ScaleConst& c, uint32_t& lo02, uint32_t& lo13,
+                                               uint32_t& hi02, uint32_t& hi13) {
+  // bit s of every byte -> bit 4 of that byte: rotate right by (s - 4) mod 32
+  uint32_t rl = __funnelshift_r(qh, qh, (s_even - 4) & 31);
+  uint32_t rh = __funnelshift_r(qh, qh, (s_even - 3) & 31);
+  uint32_t lo = lop3_or_andb(w & 0x0F0F0F0Fu, rl, 0x10101010u);
+  uint32_t hi = lop3_or_andb((w >> 4) & 0x0F0F0F0Fu, rh, 0x10101010u);
+  uint32_t neg = c.ol;  // -1024*sc_even
+  lo02 = hfma2_u(__byte_perm(lo, 0x64646464u, 0x4240), c.sl, neg);
+  lo13 = hfma2_u(__byte_perm(lo, 0x64646464u, 0x4341), c.sl, neg);
+  // odd sub-block: constants (sc_odd, -1024*sc_odd) = (16*sh, 16*oh)
+  uint32_t so = hmul2_u(c.sh, half2_const(16.f)), oo = hmul2_u(c.oh, half2_const(16.f));
+  hi02 = hfma2_u(__byte_perm(hi, 0x64646464u, 0x4240), so, oo);
+  hi13 = hfma2_u(__byte_perm(hi, 0x64646464u, 0x4341), so, oo);
+}
+
+// ---- Q6_K (row planes, see DTensor) ---------------------------------------------------
+// Per block: ql[128], qh[64], 16 int8 scales, fp16 d (reference: gguf/dequant.go:331-356).
+// Unit u = t (+4): half hf = u>>2, lh = (u>>1)&1, l0 = 16*(u&1): low nibbles are quarter lh,
+// high nibbles quarter lh+2, of elements l0..l0+15; element k = 128*hf + 32*quarter + l.
+struct Q6KRow {
+  uint4 qla, qlb, qha, qhb, sc;
+  uint32_t d;
+};
+__device__ __forceinline__ void q6k_issue(Q6KRow& r, const uint8_t* row, int nb, int blk, int t) {
+  const uint8_t* ql = row + (size_t)blk * 128;
+  const uint8_t* qh = row + (size_t)nb * 128 + (size_t)blk * 64;
+  const uint8_t* sc = row + (size_t)nb * 192 + (size_t)blk * 16;
+  const uint8_t* d = row + (size_t)nb * 208 + (size_t)blk * 2;
+  r.qla = ldg_stream(ql + 16 * t);
+  r.qlb = ldg_stream(ql + 64 + 16 * t);
+  r.qha = ldg_stream(qh + 16 * (t & 1));
+  r.qhb = ldg_stream(qh + 32 + 16 * (t & 1));
+  r.sc = ldg_stream(sc);
+  r.d = *reinterpret_cast<const unsigned short*>(d);
+}
+__device__ __forceinline__ int q6_scale(const uint4& sc, int idx) {  // int8 scale idx of the block
+  uint32_t w = idx < 4 ? sc.x : idx < 8 ? sc.y : idx < 12 ? sc.z : sc.w;
+  return (int)(int8_t)((w >> (8 * (idx & 3))) & 0xFF);
+}
+__device__ __forceinline__ void q6_unpack_word(uint32_t w, uint32_t qh, int lh, uint32_t sc_lo2, uint32_t sc_hi2, uint32_t& lo02, uint32_t& lo13,
+                                               uint32_t& hi02, uint32_t& hi13) {
+  // 2-bit field of quarter c sits at bits 2c..2c+1 of the qh byte; move it to bits 4..5
+  uint32_t rl = __funnelshift_r(qh, qh, (2 * lh - 4) & 31);
+  uint32_t rh = __funnelshift_r(qh, qh, (2 * lh) & 31);  // quarter lh+2: (2*(lh+2) - 4)
+  uint32_t lo = lop3_or_andb(w & 0x0F0F0F0Fu, rl, 0x30303030u);
+  uint32_t hi = lop3_or_andb((w >> 4) & 0x0F0F0F0Fu, rh, 0x30303030u);
+  const uint32_t off = half2_const(-1056.f);  // 1024 magic + 32 centre
+  lo02 = hmul2_u(hadd2_u(__byte_perm(lo, 0x64646464u, 0x4240), off), sc_lo2);
+  lo13 = hmul2_u(hadd2_u(__byte_perm(lo, 0x64646464u, 0x4341), off), sc_lo2);
+  hi02 = hmul2_u(hadd2_u(__byte_perm(hi, 0x64646464u, 0x4240), off), sc_hi2);
+  hi13 = hmul2_u(hadd2_u(__byte_perm(hi, 0x64646464u, 0x4341), off), sc_hi2);
+}
+
+// 8 mmas of one quad pair (rows g and g+8): words w0/w1, activations at element base kb
+// (low nibbles) and kb+hi_off (high nibbles).
+template <class Unpack0, class Unpack1>
+__device__ __forceinline__ void quad_mmas(float (&C)[4], const uint8_t* xrow, bool live, int kb, int hi_off, const uint4& q0, const uint4& q1,
+                                          Unpack0 un0, Unpack1 un1) {
+  const uint32_t w0[4] = {q0.x, q0.y, q0.z, q0.w}, w1[4] = {q1.x, q1.y, q1.z, q1.w};
+  uint4 xl0 = make_uint4(0, 0, 0, 0), xl1 = xl0, xh0 = xl0, xh1 = xl0;
+  if (live) {
+    const uint8_t* pl = xrow + 2 * kb + 16 * (kb >> 6);
+    const uint8_t* ph = xrow + 2 * (kb + hi_off) + 16 * ((kb + hi_off) >> 6);
+    xl0 = *reinterpret_cast<const uint4*>(pl);
+    xl1 = *reinterpret_cast<const uint4*>(pl + 16);
+    xh0 = *reinterpret_cast<const uint4*>(ph);
+    xh1 = *reinterpret_cast<const uint4*>(ph + 16);
+  }
+  const uint32_t bl[8] = {xl0.x, xl0.y, xl0.z, xl0.w, xl1.x, xl1.y, xl1.z, xl1.w};
+  const uint32_t bh[8] = {xh0.x, xh0.y, xh0.z, xh0.w, xh1.x, xh1.y, xh1.z, xh1.w};
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    uint32_t a_lo[4], a_hi[4];
+    un0(i, w0[i], a_lo[0], a_lo[2], a_hi[0], a_hi[2]);
+    un1(i, w1[i], a_lo[1], a_lo[3], a_hi[1], a_hi[3]);
+    mma16816(C, a_lo, bl[2 * i], bl[2 * i + 1]);
+    mma16816(C, a_hi, bh[2 * i], bh[2 * i + 1]);
+  }
+}
+
+template <int TYPE>
+struct RowRegs;
+template <> struct RowRegs<T_Q4_K> { using type = Q4KRow; };
+template <> struct RowRegs<T_Q5_K> { using type = Q5KRow; };
+template <> struct RowRegs<T_Q6_K> { using type = Q6KRow; };
+
+template <int TYPE>
+__device__ __forceinline__ void issue_row(typename RowRegs<TYPE>::type& r, const uint8_t* row, int nb, int blk, int t) {
+  if constexpr (TYPE == T_Q4_K) q4k_issue(r, row + (size_t)blk * 144, t);
+  else if constexpr (TYPE == T_Q5_K) q5k_issue(r, row + (size_t)blk * 176, t);
+  else q6k_issue(r, row, nb, blk, t);
+}
+
+// Accumulates one super-block of rows (g, g+8) into acc (C layout: [0],[1] row g cols 2t,2t+1;
+// [2],[3] row g+8).
+template <int TYPE>
+__device__ __forceinline__ void block_accumulate(float (&acc)[4], const typename RowRegs<TYPE>::type& r0, const typename RowRegs<TYPE>::type& r1,
+                                                 const uint8_t* xrow, const __half* sxrow, bool live, int blk, int t) {
+  const int th = t >> 1, hb = t & 1;
+  float C[4] = {0.f, 0.f, 0.f, 0.f};
+  if constexpr (TYPE == T_Q4_K || TYPE == T_Q5_K) {
+    uint32_t sca0, ma0, scb0, mb0, sca1, ma1, scb1, mb1;
+    k4_scales(r0.hdr, th, sca0, ma0, scb0, mb0);
+    k4_scales(r1.hdr, th, sca1, ma1, scb1, mb1);
+    const ScaleConst ca0 = make_scale_const(sca0), cb0 = make_scale_const(scb0);
+    const ScaleConst ca1 = make_scale_const(sca1), cb1 = make_scale_const(scb1);
+    const int ka = blk * 256 + 64 * th + 16 * hb, kb = ka + 128;
+    if constexpr (TYPE == T_Q4_K) {
+      quad_mmas(C, xrow, live, ka, 32, r0.qa, r1.qa,
+                [&](int, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q4_unpack_word(w, ca0, a, b, c, d); },
+                [&](int, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q4_unpack_word(w, ca1, a, b, c, d); });
+      quad_mmas(C, xrow, live, kb, 32, r0.qb, r1.qb,
+                [&](int, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q4_unpack_word(w, cb0, a, b, c, d); },
+                [&](int, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q4_unpack_word(w, cb1, a, b, c, d); });
+    } else {
+      const uint32_t h0[4] = {r0.qh.x, r0.qh.y, r0.qh.z, r0.qh.w}, h1[4] = {r1.qh.x, r1.qh.y, r1.qh.z, r1.qh.w};
+      const int sa = 2 * th, sb = 4 + 2 * th;
+      quad_mmas(C, xrow, live, ka, 32, r0.qa, r1.qa,
+                [&](int i, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q5_unpack_word(w, h0[i], sa, ca0, a, b, c, d); },
+                [&](int i, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q5_unpack_word(w, h1[i], sa, ca1, a, b, c, d); });
+      quad_mmas(C, xrow, live, kb, 32, r0.qb, r1.qb,
+                [&](int i, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q5_unpack_word(w, h0[i], sb, cb0, a, b, c, d); },
+                [&](int i, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q5_unpack_word(w, h1[i], sb, cb1, a, b, c, d); });
+    }
+    // min term: one mma over the 8 sub-block sums; even t carries the hi parts, odd t the lo parts
+    float Cm[4] = {0.f, 0.f, 0.f, 0.f};
+    uint32_t am[4] = {bytes_to_half2(ma0), bytes_to_half2(ma1), bytes_to_half2(mb0), bytes_to_half2(mb1)};
+    uint32_t b0 = 0, b1 = 0;
+    if (live) {
+      const __half* p = sxrow + blk * 8;  // sxrow: this column's hi plane (even t) or lo plane (odd t)
+      b0 = *reinterpret_cast<const uint32_t*>(p + 2 * th);
+      b1 = *reinterpret_cast<const uint32_t*>(p + 4 + 2 * th);
+    }
+    mma16816(Cm, am, b0, b1);
+    const float d0 = h2f_lo(r0.hdr.x), dm0 = h2f_hi(r0.hdr.x), d1 = h2f_lo(r1.hdr.x), dm1 = h2f_hi(r1.hdr.x);
+    acc[0] = fmaf(-dm0, Cm[0], fmaf(d0, C[0], acc[0]));
+    acc[1] = fmaf(-dm0, Cm[1], fmaf(d0, C[1], acc[1]));
+    acc[2] = fmaf(-dm1, Cm[2], fmaf(d1, C[2], acc[2]));
+    acc[3] = fmaf(-dm1, Cm[3], fmaf(d1, C[3], acc[3]));
+  } else {  // Q6_K
+    // unit a = t: hf 0, lh = th, l0 = 16*hb; unit b = t+4: hf 1
+    const int sia = hb + 2 * th, sib = 8 + hb + 2 * th;  // scale index of the low-nibble quarter; high is +4
+    auto sc2 = [](int s) { return half2_const((float)s); };
+    const uint32_t sla0 = sc2(q6_scale(r0.sc, sia)), sha0 = sc2(q6_scale(r0.sc, sia + 4));
+    const uint32_t slb0 = sc2(q6_scale(r0.sc, sib)), shb0 = sc2(q6_scale(r0.sc, sib + 4));
+    const uint32_t sla1 = sc2(q6_scale(r1.sc, sia)), sha1 = sc2(q6_scale(r1.sc, sia + 4));
+    const uint32_t slb1 = sc2(q6_scale(r1.sc, sib)), shb1 = sc2(q6_scale(r1.sc, sib + 4));
+    const uint32_t ha0[4] = {r0.qha.x, r0.qha.y, r0.qha.z, r0.qha.w}, hb0[4] = {r0.qhb.x, r0.qhb.y, r0.qhb.z, r0.qhb.w};
+    const uint32_t ha1[4] = {r1.qha.x, r1.qha.y, r1.qha.z, r1.qha.w}, hb1[4] = {r1.qhb.x, r1.qhb.y, r1.qhb.z, r1.qhb.w};
+    const int ka = blk * 256 + 32 * th + 16 * hb, kb = ka + 128;
+    quad_mmas(C, xrow, live, ka, 64, r0.qla, r1.qla,
+              [&](int i, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q6_unpack_word(w, ha0[i], th, sla0, sha0, a, b, c, d); },
+              [&](int i, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q6_unpack_word(w, ha1[i], th, sla1, sha1, a, b, c, d); });
+    quad_mmas(C, xrow, live, kb, 64, r0.qlb, r1.qlb,
+              [&](int i, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q6_unpack_word(w, hb0[i], th, slb0, shb0, a, b, c, d); },
+              [&](int i, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q6_unpack_word(w, hb1[i], th, slb1, shb1, a, b, c, d); });
+    const float d0 = __half2float(__ushort_as_half((unsigned short)r0.d)), d1 = __half2float(__ushort_as_half((unsigned short)r1.d));
+    acc[0] = fmaf(d0, C[0], acc[0]);
+    acc[1] = fmaf(d0, C[1], acc[1]);
+    acc[2] = fmaf(d1, C[2], acc[2]);
+    acc[3] = fmaf(d1, C[3], acc[3]);
+  }
+}
+
+
+// ---- activation staging ----------------------------------------------------------------
+// Fills xs (fp16, permuted, padded) for `ncols` columns and the sub-block sums (hi/lo fp16
+// planes) used by the min term. All threads of the CTA take part.
+//   sxs layout: [plane(2)][xcols][K/32] halves.
+template <int PRO>
+__device__ __forceinline__ void stage_x(const QGemvParams& p, uint8_t* xs, __half* sxs, float* scratch, int ncols, const int* col_rows, int xstride) {
+  const int K = p.K, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int c = 0; c < ncols; c++) {
+    const int64_t row = col_rows[c];
+    uint8_t* dst = xs + (size_t)c * xstride;
+    if constexpr (PRO == PRO_F16) {
+      const __half* src = reinterpret_cast<const __half*>(p.x) + row * p.ldx;
+      for (int k = tid * 8; k < K; k += QG_THREADS * 8) {
+        uint4 v = *reinterpret_cast<const uint4*>(src + k);
+        uint4 o;
+        o.x = __byte_perm(v.x, v.y, 0x5410); o.y = __byte_perm(v.x, v.y, 0x7632);
+        o.z = __byte_perm(v.z, v.w, 0x5410); o.w = __byte_perm(v.z, v.w, 0x7632);
+        *reinterpret_cast<uint4*>(dst + 2 * k + 16 * (k >> 6)) = o;
+      }
+    } else {
+      float scale0 = 1.f, scale1 = 1.f;
+      const float* src = reinterpret_cast<const float*>(p.x) + row * p.ldx;
+      const float* src2 = PRO == PRO_CONCAT_NORM ? reinterpret_cast<const float*>(p.x2) + row * p.ldx2 : nullptr;
+      if constexpr (PRO == PRO_RMSNORM || PRO == PRO_CONCAT_NORM) {
+        // sum of squares over the row (CONCAT: over each half separately), fixed order
+        const int halfK = PRO == PRO_CONCAT_NORM ? K / 2 : K;
+        float s0 = 0.f, s1 = 0.f;
+        for (int k = tid * 4; k < halfK; k += QG_THREADS * 4) {
+          float4 v = *reinterpret_cast<const float4*>(src + k);
+          s0 += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+          if constexpr (PRO == PRO_CONCAT_NORM) {
+            float4 u = *reinterpret_cast<const float4*>(src2 + k);
+            s1 += u.x * u.x + u.y * u.y + u.z * u.z + u.w * u.w;
+          }
+        }
+        s0 = warp_sum(s0); s1 = warp_sum(s1);
+        __syncthreads();
+        if (lane == 0) { scratch[warp] = s0; scratch[QG_WARPS + warp] = s1; }
+        __syncthreads();
+        float t0 = 0.f, t1 = 0.f;
+#pragma unroll
+        for (int w = 0; w < QG_WARPS; w++) { t0 += scratch[w]; t1 += scratch[QG_WARPS + w]; }
+        scale0 = 1.0f / sqrtf(t0 / (float)halfK + p.eps);
+        scale1 = 1.0f / sqrtf(t1 / (float)halfK + p.eps);
+      }
+      for (int k = tid * 4; k < K; k += QG_THREADS * 4) {
+        float4 v;
+        if constexpr (PRO == PRO_RMSNORM) {
+          float4 h = *reinterpret_cast<const float4*>(src + k);
+          float4 g = *reinterpret_cast<const float4*>(p.gamma + k);
+          v = make_float4(h.x * scale0 * g.x, h.y * scale0 * g.y, h.z * scale0 * g.z, h.w * scale0 * g.w);
+        } else if constexpr (PRO == PRO_CONCAT_NORM) {
+          const int halfK = K / 2;
+          const bool second = k >= halfK;
+          const int kk = second ? k - halfK : k;
+          float4 h = *reinterpret_cast<const float4*>((second ? src2 : src) + kk);
+          float4 g = *reinterpret_cast<const float4*>((second ? p.gamma2 : p.gamma) + kk);
+          float sc = second ? scale1 : scale0;
+          v = make_float4(h.x * sc * g.x, h.y * sc * g.y, h.z * sc * g.z, h.w * sc * g.w);
+        } else {  // PRO_DN_GATED: per-head RMS norm x shared gamma x sigmoid(z)
+          // a head is head_dim (128) values = one warp pass of 32 lanes x 4
+          float4 h = *reinterpret_cast<const float4*>(src + k);
+          float ss = warp_sum(h.x * h.x + h.y * h.y + h.z * h.z + h.w * h.w);
+          float sc = 1.0f / sqrtf(ss / (float)p.head_dim + p.eps);
+          float4 g = *reinterpret_cast<const float4*>(p.gamma + (k & (p.head_dim - 1)));
+          float4 zz = *reinterpret_cast<const float4*>(p.z + row * p.ldz + k);
+          v = make_float4(h.x * sc * g.x * sigmoid_acc(zz.x), h.y * sc * g.y * sigmoid_acc(zz.y), h.z * sc * g.z * sigmoid_acc(zz.z),
+                          h.w * sc * g.w * sigmoid_acc(zz.w));
+        }
+        __half2 a = __floats2half2_rn(v.x, v.z), b = __floats2half2_rn(v.y, v.w);  // stored order [x0,x2,x1,x3]
+        uint2 o = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+        *reinterpret_cast<uint2*>(dst + 2 * k + 16 * (k >> 6)) = o;
+        if (PRO == PRO_RMSNORM && p.xn_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
+          __half2 n0 = __floats2half2_rn(v.x, v.y), n1 = __floats2half2_rn(v.z, v.w);
+          *reinterpret_cast<uint2*>(p.xn_out + row * K + k) = make_uint2(*reinterpret_cast<uint32_t*>(&n0), *reinterpret_cast<uint32_t*>(&n1));
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // sub-block sums of the rounded activations, as fp16 hi + lo
+  const int nsub = K / 32;
+  for (int i = tid; i < ncols * nsub; i += QG_THREADS) {
+    const int c = i / nsub, s = i - c * nsub;
+    const uint8_t* src = xs + (size_t)c * xstride + 64 * s + 16 * (s >> 1);
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      uint4 v = *reinterpret_cast<const uint4*>(src + 16 * j);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; q++) sum += h2f_lo(w[q]) + h2f_hi(w[q]);
+    }
+    __half hi = __float2half_rn(sum);
+    __half lo = __float2half_rn(sum - __half2float(hi));
+    sxs[(size_t)c * nsub + s] = hi;
+    sxs[(size_t)(p.xcols + c) * nsub + s] = lo;
+  }
+  __syncthreads();
+}
+
+// ---- the kernel ------------------------------------------------------------------------
+// grid.x: CTA index over row tiles; grid.y: expert entry (grouped) or 0; grid.z: column tile.
+template <int TYPE, int PRO, int EPI, bool DUAL, bool GROUPED>
+__global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int K = p.K, nb = K / 256;
+  const int wpt = nb >= 8 ? 8 : nb >= 4 ? 4 : nb >= 2 ? 2 : 1;  // warps per tile (K-slices)
+  const int tpc = QG_WARPS / wpt;                               // tiles per CTA
+  const int xstride = qg_xstride(K);
+  uint8_t* xs = smem;
+  __half* sxs = reinterpret_cast<__half*>(smem + (size_t)p.xcols * xstride);
+  float* red = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sxs) + (((size_t)p.xcols * (K / 32) * 2 * sizeof(__half) + 15) & ~(size_t)15));
+  __shared__ float scratch[2 * QG_WARPS];
+  __shared__ int col_rows[QG_MAXCOLS];
+
+  const int tile = blockIdx.x * tpc + warp / wpt;
+  const int kslice = warp % wpt;
+  const bool tile_ok = tile * 16 < p.N;
+  int r0 = tile * 16 + g, r1 = r0 + 8;
+  if (r0 >= p.N) r0 = p.N - 1;
+  if (r1 >= p.N) r1 = p.N - 1;
+
+  // weight base pointers: none of this depends on the producer kernel
+  const uint8_t *wa = nullptr, *wb = nullptr;
+  int ncols = 0, col_off = 0;
+  if constexpr (GROUPED) {
+    // entries are written by the router kernel: wait before reading them
+    pdl_wait();
+    if ((int)blockIdx.y >= *p.n_entries) return;
+    const int4 e = p.entries[blockIdx.y];
+    col_off = e.y; ncols = e.z;
+    wa = e.x >= 0 ? p.w[0] + (size_t)e.x * p.expert_stride : p.ws;
+    if constexpr (DUAL) wb = e.x >= 0 ? p.w2[0] + (size_t)e.x * p.expert_stride : p.ws2;
+  } else {
+    ncols = p.M - (int)blockIdx.z * QG_MAXCOLS;
+    if (ncols > QG_MAXCOLS) ncols = QG_MAXCOLS;
+    col_off = (int)blockIdx.z * QG_MAXCOLS;
+  }
+  int seg_r0 = 0;
+  if constexpr (!GROUPED) {
+    int s = 0;
+    while (s + 1 < p.nseg && tile * 16 >= p.seg_end[s]) s++;
+    seg_r0 = s > 0 ? p.seg_end[s - 1] : 0;
+    wa = p.w[s];
+    if constexpr (DUAL) wb = p.w2[s];
+  }
+  const uint8_t* row0 = wa + (size_t)(r0 - seg_r0) * p.stride;
+  const uint8_t* row1 = wa + (size_t)(r1 - seg_r0) * p.stride;
+
+  // issue this warp's first weight loads before touching activations
+  using Regs = typename RowRegs<TYPE>::type;
+  Regs a0, a1, b0, b1;
+  const int blk0 = kslice;  // this warp takes super-blocks kslice, kslice + wpt, ...
+  if (tile_ok) {
+    issue_row<TYPE>(a0, row0, nb, blk0, t);
+    issue_row<TYPE>(a1, row1, nb, blk0, t);
+    if constexpr (DUAL) {
+      issue_row<TYPE>(b0, wb + (size_t)(r0 - seg_r0) * p.stride, nb, blk0, t);
+      issue_row<TYPE>(b1, wb + (size_t)(r1 - seg_r0) * p.stride, nb, blk0, t);
+    }
+  }
+  if constexpr (!GROUPED) pdl_wait();
+  pdl_launch();
+
+  if (tid < QG_MAXCOLS) {
+    int c = tid < ncols ? tid : 0;
+    int id;
+    if constexpr (GROUPED) id = p.cols[col_off + c];
+    else id = p.row_ids ? p.row_ids[col_off + c] : col_off + c;
+    col_rows[tid] = id;
+  }
+  __syncthreads();
+  {
+    __shared__ int xrows[QG_MAXCOLS];
+    if (tid < QG_MAXCOLS) xrows[tid] = GROUPED ? col_rows[tid] / p.x_div : col_rows[tid];
+    __syncthreads();
+    stage_x<PRO>(p, xs, sxs, scratch, ncols, xrows, xstride);
+  }
+
+  float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
+  const bool live = g < ncols;
+  const uint8_t* xrow = xs + (size_t)(live ? g : 0) * xstride;
+  const __half* sxrow = sxs + (size_t)((t & 1) * p.xcols + (live ? g : 0)) * (K / 32);
+  if (tile_ok) {
+    for (int blk = blk0; blk < nb; blk += wpt) {
+      Regs n0, n1, m0, m1;
+      const bool more = blk + wpt < nb;
+      if (more) {  // prefetch the next super-block of this K-slice
+        issue_row<TYPE>(n0, row0, nb, blk + wpt, t);
+        issue_row<TYPE>(n1, row1, nb, blk + wpt, t);
+        if constexpr (DUAL) {
+          issue_row<TYPE>(m0, wb + (size_t)(r0 - seg_r0) * p.stride, nb, blk + wpt, t);
+          issue_row<TYPE>(m1, wb + (size_t)(r1 - seg_r0) * p.stride, nb, blk + wpt, t);
+        }
+      }
+      block_accumulate<TYPE>(acc, a0, a1, xrow, sxrow, live, blk, t);
+      if constexpr (DUAL) block_accumulate<TYPE>(acc2, b0, b1, xrow, sxrow, live, blk, t);
+      if (more) {
+        a0 = n0; a1 = n1;
+        if constexpr (DUAL) { b0 = m0; b1 = m1; }
+      }
+    }
+  }
+  // cross-warp reduction in warp order
+  float* myred = red + (size_t)warp * 128;
+  myred[g * 8 + 2 * t] = acc[0]; myred[g * 8 + 2 * t + 1] = acc[1];
+  myred[(g + 8) * 8 + 2 * t] = acc[2]; myred[(g + 8) * 8 + 2 * t + 1] = acc[3];
+  if constexpr (DUAL) {
+    float* r2 = myred + QG_WARPS * 128;
+    r2[g * 8 + 2 * t] = acc2[0]; r2[g * 8 + 2 * t + 1] = acc2[1];
+    r2[(g + 8) * 8 + 2 * t] = acc2[2]; r2[(g + 8) * 8 + 2 * t + 1] = acc2[3];
+  }
+  __syncthreads();
+  for (int i = tid; i < tpc * 128; i += QG_THREADS) {
+    const int lt = i >> 7, rc = i & 127, r = rc >> 3, c = rc & 7;
+    const int grow = (blockIdx.x * tpc + lt) * 16 + r;
+    if (grow >= p.N || c >= ncols) continue;
+    float v = 0.f, v2 = 0.f;
+    for (int w = 0; w < wpt; w++) {
+      v += red[(size_t)(lt * wpt + w) * 128 + rc];
+      if constexpr (DUAL) v2 += red[(size_t)(QG_WARPS + lt * wpt + w) * 128 + rc];
+    }
+    const int64_t orow = (!GROUPED && p.row_ids != nullptr) ? col_off + c : col_rows[c];
+    if constexpr (EPI == EPI_STORE) p.y[orow * p.ldy + grow] = v;
+    else if constexpr (EPI == EPI_RESID) p.y[orow * p.ldy + grow] += v;
+    else {  // SwiGLU of (gate, up) rounded to fp16 (reference: shaders/llm_moe_gemv.comp:777-781)
+      float s = v * sigmoid_acc(v) * v2;
+      p.y16[orow * p.ldy + grow] = __float2half_rn(s);
+    }
+  }
+}
+
+}  // namespace b200

@@ -1,0 +1,197 @@
+"""GPU parity of the whole token loop on the tiny hybrid MoE checkpoint against the CPU oracle,
+and the reference's graph invariants (chunk split, batched == solo, checkpoint, speculation),
+all through the C ABI."""
+import numpy as np
+import pytest
+
+import modelgen
+from parity import NEAR_TIE, assert_close, compare, logit_gap
+
+pytestmark = pytest.mark.gpu
+
+N_PROMPT, N_GEN = 128, 128
+
+
+@pytest.fixture(scope="module")
+def tiny(pkg, tiny_path):
+    model = pkg.Model.open(tiny_path)
+    om, cfg, reader = modelgen.oracle_model(tiny_path)
+    return dict(model=model, oracle=om, cfg=cfg, reader=reader)
+
+
+def prompt(cfg, n, seed=1):
+    return np.random.default_rng(seed).integers(0, cfg["vocab"], n).astype(np.int32)
+
+
+def test_cxx_gguf_reader_agrees_with_python_reader(pkg, tiny):
+    for name in ("token_embd.weight", "blk.0.attn_qkv.weight", "blk.3.attn_v.weight", "blk.1.ffn_gate_inp.weight", "blk.2.ssm_a"):
+        assert np.array_equal(tiny["model"].read_tensor(name), tiny["reader"].tensors[name][2]), name
+    assert tiny["model"].cfg == {k: tiny["cfg"][k] for k in tiny["model"].cfg} or \
+        all(abs(tiny["model"].cfg[k] - tiny["cfg"][k]) < 1e-6 * max(1, abs(tiny["cfg"][k])) for k in tiny["model"].cfg)
+
+
+def test_prefill_matches_oracle_layer_by_layer(pkg, tiny):
+    cfg = tiny["cfg"]
+    ids = prompt(cfg, 24)
+    g = pkg.Graph(tiny["model"], n_kv=256, max_tokens=32, trace=True, use_cuda_graph=False)
+    logits, hidden = g.forward(ids)
+    tr = g.trace(len(ids))
+    seq = tiny["oracle"].seq()
+    want_logits, ot = seq.extend(ids, trace=("hidden", "ffn_out", "topk", "topk_w", "margin"))
+    for l in range(cfg["n_layer"]):
+        assert_close(tr["after_mixer"][l], ot["hidden"][:, l] - ot["ffn_out"][:, l], f"layer {l} after the token mixer")
+        assert_close(tr["hidden"][l], ot["hidden"][:, l], f"layer {l} residual")
+        for t in range(len(ids)):
+            if ot["margin"][t, l] < NEAR_TIE:
+                continue   # documented near-tie: the top-k boundary is closer than 1e-3
+            assert np.array_equal(tr["topk"][l, t], ot["topk"][t, l]), (l, t, tr["topk"][l, t], ot["topk"][t, l])
+            assert_close(tr["topk_w"][l, t, :-1], ot["topk_w"][t, l], f"routing weights {l},{t}")
+    assert_close(logits, want_logits, "logits")
+    assert_close(hidden, ot["hidden"][-1, -1], "last residual")
+
+
+def test_greedy_decode_matches_oracle(pkg, tiny):
+    """Config 1's workload: 128 prompt tokens, then 128 greedy tokens at batch 1."""
+    cfg = tiny["cfg"]
+    ids = prompt(cfg, N_PROMPT)
+    g = pkg.Graph(tiny["model"], n_kv=N_PROMPT + N_GEN + 8, max_tokens=64)
+    seq = tiny["oracle"].seq()
+    logits, _ = g.forward(ids)
+    want, _ = seq.extend(ids)
+    near_ties = 0
+    for step in range(N_GEN):
+        assert_close(logits, want, f"logits at step {step}")
+        tok_g, tok_o = int(np.argmax(logits)), int(np.argmax(want))
+        if tok_g != tok_o:
+            assert logit_gap(want) < NEAR_TIE, f"step {step}: greedy id {tok_g} != {tok_o} with gap {logit_gap(want)}"
+            near_ties += 1
+        tok = tok_o          # teacher forcing from the oracle after a documented near-tie
+        logits, _ = g.extend([tok])
+        want, _ = seq.extend([tok])
+    assert near_ties <= 2
+
+
+def test_exact_f32_oracle_is_within_tolerance_too(pkg, tiny):
+    cfg = tiny["cfg"]
+    ids = prompt(cfg, 16, seed=5)
+    g = pkg.Graph(tiny["model"], n_kv=64)
+    logits, _ = g.forward(ids)
+    want, _ = tiny["oracle"].seq().extend(ids, numerics=0)
+    r = compare(logits, want)
+    assert r["max_abs"] <= 1e-2 * r["ref_max"], r
+
+
+def test_chunk_split_is_the_whole_prompt(pkg, tiny):
+    # llm/graph_cache_test.go TestGraphIsAChunkSplit: chunks of 16/9/2/3/1 == whole prompt
+    cfg = tiny["cfg"]
+    ids = prompt(cfg, 31, seed=2)
+    g = pkg.Graph(tiny["model"], n_kv=64, max_tokens=32, use_cuda_graph=False)
+    whole, _ = g.forward(ids)
+    g.reset()
+    o = 0
+    for n in (16, 9, 2, 3, 1):
+        part, _ = g.extend(ids[o:o + n]); o += n
+    assert_close(part, whole, "chunked prefill", tol=1e-4)
+    assert int(np.argmax(part)) == int(np.argmax(whole))
+    # and a chunk larger than max_tokens is cut by the library itself
+    g2 = pkg.Graph(tiny["model"], n_kv=64, max_tokens=8, use_cuda_graph=False)
+    cut, _ = g2.forward(ids)
+    assert_close(cut, whole, "library-cut prefill", tol=1e-4)
+
+
+def test_decode_rows_is_each_slot(pkg, tiny):
+    # llm/graph_batch_test.go TestGraphDecodeRowsIsEachSlot: batched == solo, bit for bit
+    cfg = tiny["cfg"]
+    g = pkg.Graph(tiny["model"], n_kv=64, max_tokens=16, slots=4, use_cuda_graph=False)
+    prompts = [prompt(cfg, n, seed=10 + n) for n in (5, 9, 3)]
+    toks = [7, 11, 13]
+    solo = []
+    for s, p in enumerate(prompts):
+        g.use_slot(s); g.reset(); g.extend(p)
+        ck = g.checkpoint()
+        lg, _ = g.extend([toks[s]])
+        solo.append(lg)
+        g.restore(ck)              # back to the end of the prompt
+    batched = g.decode_rows([0, 1, 2], toks)
+    for s in range(3):
+        assert np.array_equal(batched[s].view(np.uint32), solo[s].view(np.uint32)), f"slot {s}"
+    # refusals before anything is launched (llm/batch.go:45-63)
+    with pytest.raises(pkg.lib.B200Error):
+        g.decode_rows([0, 0], [1, 2])
+    with pytest.raises(pkg.lib.B200Error):
+        g.decode_rows([9], [1])
+    with pytest.raises(pkg.lib.B200Error):
+        g.decode_rows([1], [cfg["vocab"]])
+
+
+def test_checkpoint_is_the_prefill(pkg, tiny):
+    # llm/graph_checkpoint_test.go: restoring a checkpoint and extending == never having left
+    cfg = tiny["cfg"]
+    ids = prompt(cfg, 20, seed=3)
+    g = pkg.Graph(tiny["model"], n_kv=64, use_cuda_graph=False)
+    g.forward(ids[:12])
+    ck = g.checkpoint()
+    a, _ = g.extend(ids[12:])
+    g.restore(ck)
+    assert g.past() == 12
+    b, _ = g.extend(ids[12:])
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_speculative_keep_is_the_sequence(pkg, tiny):
+    # llm/spec_rewind_test.go: a verify pass of n rows, keep k, equals extending by those k rows
+    cfg = tiny["cfg"]
+    ids = prompt(cfg, 12, seed=4)
+    rows = prompt(cfg, 4, seed=6)
+    g = pkg.Graph(tiny["model"], n_kv=64, speculative=True, spec_rows=4, use_cuda_graph=False)
+    for k in (0, 1, 2, 4):
+        g.forward(ids)
+        g.speculate(True)
+        all_logits, _ = g.extend_rows(rows)
+        g.keep(k)
+        g.speculate(False)
+        assert g.past() == len(ids) + k
+        nxt, _ = g.extend([5])
+        plain = pkg.Graph(tiny["model"], n_kv=64, use_cuda_graph=False)
+        plain.forward(ids)
+        for i in range(k):
+            lg, _ = plain.extend([rows[i]])
+            assert_close(all_logits[i], lg, f"verify row {i}", tol=1e-4)
+        want, _ = plain.extend([5])
+        assert_close(nxt, want, f"after keep({k})", tol=1e-4)
+        assert int(np.argmax(nxt)) == int(np.argmax(want))
+
+
+def test_device_greedy_loop_and_cuda_graph_replay(pkg, tiny):
+    # the replayed step is the recorded step (llm/prerecord_test.go:48), and the device-resident
+    # loop emits the ids the host loop picks
+    cfg = tiny["cfg"]
+    ids = prompt(cfg, 16, seed=8)
+    eager = pkg.Graph(tiny["model"], n_kv=96, use_cuda_graph=False)
+    replay = pkg.Graph(tiny["model"], n_kv=96, use_cuda_graph=True)
+    le, _ = eager.forward(ids)
+    lr, _ = replay.forward(ids)
+    host_ids = []
+    for _ in range(24):
+        assert np.array_equal(le.view(np.uint32), lr.view(np.uint32))
+        t = int(np.argmax(le)); host_ids.append(t)
+        le, _ = eager.extend([t])
+        lr, _ = replay.extend([t])
+    dev = pkg.Graph(tiny["model"], n_kv=96, use_cuda_graph=True)
+    l0, _ = dev.forward(ids)
+    out = dev.generate_greedy([0], [int(np.argmax(l0))], 23)
+    assert [int(np.argmax(l0))] + out[:, 0].tolist()[:-1] == host_ids[:23] or out[:, 0].tolist() == host_ids[1:24]
+    assert dev.past() == len(ids) + 23
+    assert dev.last_launches() > 0 and dev.last_device_ms() > 0
+
+
+def test_capacity_and_id_refusals(pkg, tiny):
+    g = pkg.Graph(tiny["model"], n_kv=16)
+    with pytest.raises(pkg.lib.B200Error):
+        g.forward(np.zeros(17, dtype=np.int32))
+    with pytest.raises(pkg.lib.B200Error):
+        g.forward([-1])
+    with pytest.raises(pkg.lib.B200Error):
+        g.use_slot(3)
+    with pytest.raises(pkg.lib.B200Error):
+        g.keep(1)
