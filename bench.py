@@ -1,0 +1,264 @@
+"""Decode benchmark of the B200 token loop.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one greedy decode token at batch 1 of the 80B-A3B-shaped Q4_K hybrid MoE model
+(48 layers, 512 experts top-10 + shared) after a 2048-token random prompt, fp16 KV cache.
+Weights are synthetic (seeded N(0, 0.02), quantised on the device by the library's own
+quantiser); token ids are uniform random. `value` is the device-resident greedy loop (ids never
+leave the GPU); `e2e` is the same step through the reference-facing call: one token id in from
+host memory, the full logits row out to pinned host memory, argmax on the host.
+"""
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PROMPT = 2048
+METRIC = "decode tok/s at batch 1 (Q4_K hybrid MoE, 80B-A3B shape)"
+
+
+def measured_peak_gbs():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def algorithmic_bytes_per_token(pkg, cfg, ctx):
+    """Bytes one decode step has to move: every weight row it needs once, the DeltaNet state
+    read and written, the conv inputs written, and the KV cells read (+1 written)."""
+    gguf, config = pkg.gguf, pkg.config
+    H, nE, used, ff = cfg["n_embd"], cfg["n_expert"], cfg["n_expert_used"], cfg["ffn_expert"]
+    w = 0
+    for name, typ, dims, _ in config.manifest(cfg):
+        nbytes = gguf.tensor_bytes(typ, dims)
+        if name == "token_embd.weight":
+            nbytes = gguf.row_bytes(typ, dims[0])            # one row is gathered
+        elif "_exps." in name:
+            nbytes = nbytes // nE * used                      # only the routed experts stream
+        w += nbytes
+    n_dn = sum(0 if config.is_attention_layer(cfg, l) else 1 for l in range(cfg["n_layer"]))
+    n_at = cfg["n_layer"] - n_dn
+    state = n_dn * cfg["dn_heads_v"] * cfg["dn_head_dim"] ** 2 * 4 * 2
+    ring = n_dn * (2 * cfg["dn_heads_k"] + cfg["dn_heads_v"]) * cfg["dn_head_dim"] * 4
+    kv = n_at * 2 * cfg["n_head_kv"] * cfg["head_dim"] * 2 * (ctx + 1)
+    return w + state + ring + kv
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self._stop, self.index = [], threading.Event(), index
+        self._t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+            "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                                     capture_output=True, text=True, timeout=5).stdout.strip().split(",")
+                self.samples.append([s.strip() for s in out])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=3)
+
+    def summary(self):
+        sm = [float(s[0]) for s in self.samples if len(s) >= 6 and s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in self.samples if len(s) >= 6 and s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for s in self.samples if len(s) >= 6 for n, v in zip(names, s[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def cpu_baseline(pkg, model, cfg, tokens=6):
+    """The CPU oracle (a port of the reference's CPU code) on this host's cores, on a bounded
+    sample: decode on the 4-layer and the 8-layer prefix of the same checkpoint (head included),
+    extrapolated linearly to 48 layers."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import orc
+    orc.build()
+    config = pkg.config
+    times = {}
+    for nl in (4, 8):
+        sub = config.variant(cfg, n_layer=nl)
+        tensors = {}
+        for name, typ, dims, _ in config.manifest(sub):
+            tensors[name] = (typ, dims, model.read_tensor(name))
+        om = orc.Model(config.graph_fields(sub), tensors)
+        seq = om.seq()
+        ids = np.random.default_rng(1).integers(0, cfg["vocab"], 4)
+        seq.extend(ids, numerics=orc.EXACT)
+        t = time.perf_counter()
+        for i in range(tokens):
+            seq.extend([int(ids[i % 4])], numerics=orc.EXACT)
+        times[nl] = (time.perf_counter() - t) / tokens
+        del seq, om, tensors
+    per_token = times[4] + (times[8] - times[4]) * (cfg["n_layer"] - 4) / 4.0
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count()
+    return {"value": 1.0 / per_token, "unit": "tok/s", "cores": cores, "kind": "port",
+            "sample": f"exact-f32 CPU oracle, {tokens} decode tokens each on the 4- and 8-layer prefix (head included) of the same "
+                      f"checkpoint at short context, extrapolated linearly to {cfg['n_layer']} layers "
+                      f"({times[4] * 1e3:.0f} ms and {times[8] * 1e3:.0f} ms per token)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--config", default="a3b", help="a3b (the benchmark) or tiny (a quick functional run)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--prompt", type=int, default=0, help="override the prompt length (profiling runs)")
+    ap.add_argument("--profile", type=int, default=0, help="run N eager decode steps between cudaProfilerStart/Stop and exit")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    pkg = importlib.import_module("strix-halo-vulkan_b200")
+    cfg = pkg.config.CONFIGS[args.config]
+    prompt_len = args.prompt or (PROMPT if args.config == "a3b" else 128)
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    import torch
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(local_rank)
+
+    if args.impl == "reference":
+        # the reference's own CPU implementation of the path (the oracle port), rank 0 only
+        if rank == 0:
+            model = pkg.Model.synthetic(cfg, seed=0, device=local_rank)
+            cb = cpu_baseline(pkg, model, cfg, tokens=max(steps, 4) if steps <= 32 else 8)
+            line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tok/s", "n_gpus": args.gpus, "steps": steps,
+                    "warmup": warmup, "ms_per_step": 1e3 / cb["value"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                    "dtype": "f32", "data": "synthetic",
+                    "config": {"workload": "batch-1 greedy decode, 80B-A3B-shaped Q4_K hybrid MoE", "host": "cpu"},
+                    "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+            print(json.dumps(line))
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    # every rank holds the whole model and decodes its own sequence (replicas); see DESIGN.md for expert parallelism
+    t0 = time.time()
+    model = pkg.Model.synthetic(cfg, seed=0, device=local_rank)
+    t_model = time.time() - t0
+    n_kv = prompt_len + 2 * (steps + warmup) + 64
+    g = pkg.Graph(model, n_kv=n_kv, max_tokens=64, slots=1, use_cuda_graph=not args.profile)
+    rng = np.random.default_rng(1 + rank)
+    prompt = rng.integers(0, cfg["vocab"], prompt_len).astype(np.int32)
+    t0 = time.time()
+    logits, _ = g.forward(prompt)
+    t_prefill = time.time() - t0
+    tok = int(np.argmax(logits))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    if args.profile:
+        for _ in range(3):
+            logits, _ = g.extend([tok]); tok = int(np.argmax(logits))
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        for _ in range(args.profile):
+            logits, _ = g.extend([tok]); tok = int(np.argmax(logits))
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"profiled_steps": args.profile, "context": g.past()}))
+        return
+    # ---- device-resident loop: `value` ----
+    out = g.generate_greedy([0], [tok], warmup)
+    tok = int(out[-1, 0])
+    ctx0 = g.past()
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        out = g.generate_greedy([0], [tok], steps)
+        barrier()
+    dev_ms = g.last_device_ms()
+    launches = g.last_launches()
+    tok = int(out[-1, 0])
+    if world > 1:
+        t = torch.tensor([dev_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms = float(t.item())
+    # ---- end to end through the reference-facing call: id in, logits out, host argmax ----
+    for _ in range(3):
+        logits, _ = g.extend([tok]); tok = int(np.argmax(logits))
+    barrier()
+    e2e_steps = steps
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        logits, _ = g.extend([tok])
+        tok = int(np.argmax(logits))
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+
+    if rank == 0:
+        ms_per_step = dev_ms / steps
+        value = world * steps / (dev_ms / 1e3)
+        bytes_step = algorithmic_bytes_per_token(pkg, cfg, ctx0 + steps // 2)
+        peak, which = measured_peak_gbs()
+        achieved = bytes_step / (ms_per_step / 1e3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": f"batch-1 greedy decode after a {prompt_len}-token random prompt, {cfg['name']} "
+                                   "(48 layers: 36 gated DeltaNet + 12 gated GQA, 512 experts top-10 + shared, Q4_K experts, "
+                                   "Q5_K/Q6_K projections, Q8_0 router, Q6_K head), fp16 KV cache" if args.config == "a3b" else cfg["name"],
+                       "context": ctx0, "weights_gb": model.weight_bytes / 1e9, "l2_policy": "inputs larger than L2 (2.5 GB streamed per step)",
+                       "parallelism": "replicas" if world > 1 else "single GPU", "model_build_s": round(t_model, 1),
+                       "prefill_s": round(t_prefill, 2)},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak_source": which, "kernel": "one decode step (CUDA graph of the token loop)",
+                         "algorithmic_bytes_per_step": bytes_step},
+            "e2e": {"value": world * e2e_steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 + 16 + 16,
+                    "d2h_bytes_per_step": cfg["vocab"] * 4 + cfg["n_embd"] * 4},
+            "gpu_launches": launches * steps,
+            "clocks": clocks.summary(),
+        }
+        if not args.no_cpu_baseline and world == 1:
+            try:
+                line["cpu_baseline"] = cpu_baseline(pkg, model, cfg)
+            except Exception as e:  # the baseline is a reported number, never a reason to lose the line
+                line["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

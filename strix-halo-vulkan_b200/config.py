@@ -47,6 +47,11 @@ def is_attention_layer(cfg, l):
 # Value rules for synthetic tensors: ("normal", mean, std) | ("neg_exp_uniform", lo, hi)
 W = ("normal", 0.0, 0.02)
 G = ("normal", 1.0, 0.01)
+# Depthwise conv taps are O(1) in trained checkpoints. Drawn at 0.02 like the matrices they
+# leave the delta-rule read-out at the level of the gated norm's epsilon, and the layer's
+# output then depends on the order a dot product is summed in (the CPU oracle disagrees with
+# itself by 20% on some tokens when only its summation order is reversed).
+CONV = ("normal", 0.0, 0.5)
 
 
 def _mixer_and_moe(cfg, l, attn):
@@ -72,7 +77,7 @@ def _mixer_and_moe(cfg, l, attn):
             (p + "attn_gate.weight", t["dn"], (H, hv * d), W),
             (p + "ssm_alpha.weight", gguf.F32, (H, hv), W),
             (p + "ssm_beta.weight", gguf.F32, (H, hv), W),
-            (p + "ssm_conv1d.weight", gguf.F32, (K, cw), W),            # taps of one channel contiguous
+            (p + "ssm_conv1d.weight", gguf.F32, (K, cw), CONV),            # taps of one channel contiguous
             (p + "ssm_a", gguf.F32, (hv,), ("neg_exp_uniform", 0.0, math.log(16.0))),  # -exp(A_log)
             (p + "ssm_dt.bias", gguf.F32, (hv,), W),
             (p + "ssm_norm.weight", gguf.F32, (d,), G),

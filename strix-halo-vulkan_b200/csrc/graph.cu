@@ -48,7 +48,7 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   if (o.speculative && o.spec_rows <= 0) o.spec_rows = 3;
   if (o.spec_rows > DN_RING - 3) { set_error("graph: spec_rows is limited to 5 (the conv ring keeps 8 positions)"); return ECAPACITY; }
   MR = std::min(o.max_tokens, 512);
-  split_cells = o.attn_split_cells > 0 ? o.attn_split_cells : 128;
+  split_cells = o.attn_split_cells > 0 ? o.attn_split_cells : 64;
   nsplit = (o.n_kv + split_cells - 1) / split_cells;
   B200_CUDA(cudaSetDevice(m->device));
   B200_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
@@ -64,20 +64,20 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
     else dn_index[l] = n_dn++;
   }
   max_entries = std::min(MR * used, c.n_expert + (MR * used + 7) / 8) + (MR + 7) / 8;
-  B200_TRY(dalloc(&h, (size_t)MR * H)); B200_TRY(dalloc(&proj, (size_t)MR * proj_ld)); B200_TRY(dalloc(&dn_o, (size_t)MR * vw));
+  B200_TRY(dalloc(&h, (size_t)MR * H)); B200_TRY(dalloc(&proj, (size_t)MR * proj_ld));
   B200_TRY(dalloc(&xn16, (size_t)MR * H)); B200_TRY(dalloc(&q16, (size_t)MR * qw)); B200_TRY(dalloc(&ctx16, (size_t)MR * qw));
   B200_TRY(dalloc(&attn_partial, (size_t)MR * c.n_head * nsplit * (hd + 2)));
   B200_TRY(dalloc(&attn_tickets, (size_t)MR * c.n_head_kv));
   B200_TRY(dalloc(&r_logits, (size_t)MR * c.n_expert)); B200_TRY(dalloc(&r_probs, (size_t)MR * c.n_expert));
   B200_TRY(dalloc(&topk, (size_t)MR * used)); B200_TRY(dalloc(&topk_w, (size_t)MR * slots1)); B200_TRY(dalloc(&margin, (size_t)MR));
   B200_TRY(dalloc(&entries, (size_t)max_entries)); B200_TRY(dalloc(&n_entries, 1)); B200_TRY(dalloc(&cols, (size_t)MR * slots1));
-  B200_TRY(dalloc(&r_ticket, 1));
+  B200_TRY(dalloc(&r_ticket, 1)); B200_TRY(dalloc(&tail_ticket, 1)); B200_TRY(dalloc(&y16, (size_t)MR * vw));
   B200_TRY(dalloc(&act16, (size_t)MR * slots1 * c.ffn_expert)); B200_TRY(dalloc(&down, (size_t)MR * slots1 * H));
   B200_TRY(dalloc(&logits, (size_t)MR * c.vocab));
   B200_TRY(dalloc(&ids_dev, (size_t)MR)); B200_TRY(dalloc(&next_ids, (size_t)MR)); B200_TRY(dalloc(&row_slot, (size_t)MR));
   B200_TRY(dalloc(&row_pos, (size_t)MR)); B200_TRY(dalloc(&logit_rows, (size_t)MR)); B200_TRY(dalloc(&seqs, (size_t)MR));
   B200_TRY(dalloc(&hist_len, 1));
-  if (c.has_draft) { B200_TRY(dalloc(&e_buf, (size_t)MR * H)); B200_TRY(dalloc(&hs_buf, (size_t)MR * H)); }
+  if (c.has_draft) { B200_TRY(dalloc(&e_buf, (size_t)MR * H)); B200_TRY(dalloc(&hs_buf, (size_t)MR * H)); B200_TRY(dalloc(&xcat16, (size_t)MR * 2 * H)); }
   // rotary table, angle walked in f64 like the reference (llm/attn.go:554-584, llm/gpu_attn.go:1440-1477)
   {
     const int rot = std::min(c.rope_dims, c.head_dim), half = rot / 2, npos = o.n_kv + 2;
@@ -133,51 +133,71 @@ int Graph::max_entries_for(int M) const {
 }
 
 // ---- one pass over M rows --------------------------------------------------------------
+// Per layer: [in-proj] [DeltaNet step | attention pre-pass + split-KV attention] [out-proj +
+// residual, tail: ffn_norm] [router + top-k + work list] [experts gate/up + SwiGLU] [experts
+// down, tail: weighted combine + residual + next norm]. Every projection reads fp16 rows that
+// the previous kernel's tail already normalised, so no kernel repeats a norm.
 int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) {
   const b200_config& c = m->c;
   const int H = c.n_embd, D = c.dn_head_dim, qk = c.dn_heads_k * D, vw = c.dn_heads_v * D, cw = 2 * qk + vw;
   const int hd = c.head_dim, qw = c.n_head * hd, kvw = c.n_head_kv * hd, used = c.n_expert_used, slots1 = used + 1;
   const int xcols = std::min(M, QG_MAXCOLS);
+  const bool fused_tail = M <= QG_TAIL_ROWS;
   launches = 0;
   bool first = true;
   auto pdl = [&]() { bool p = !first; first = false; launches++; return p; };
-  auto base = [&](const DTensor& w, int K, int N) {
+  auto base = [&](const DTensor& w, int K, int N, const __half* x, int ldx) {
     QGemvParams p{};
-    p.w[0] = w.data; p.seg_end[0] = N; p.nseg = 1; p.stride = w.stride; p.K = K; p.N = N; p.M = M; p.xcols = xcols; p.eps = c.eps; p.x_div = 1;
+    p.w[0] = w.data; p.seg_end[0] = N; p.nseg = 1; p.stride = w.stride; p.K = K; p.N = N; p.M = M; p.xcols = xcols; p.x_div = 1;
+    p.x = x; p.ldx = ldx;
     return p;
+  };
+  auto tail = [&](int mode, const DTensor& gamma) {
+    TailParams t{};
+    t.mode = mode; t.ticket = tail_ticket; t.h = h; t.gamma = (const float*)gamma.data; t.xn = xn16; t.down = down; t.topk_w = topk_w;
+    t.used = used; t.H = H; t.M = M; t.eps = c.eps;
+    return t;
+  };
+  const TailParams no_tail{};
+  // a projection whose last CTA (small passes) or a follow-up kernel (large passes) finishes the rows
+  auto proj_with_tail = [&](uint32_t type, int epi, bool grouped, const QGemvParams& p, const TailParams& t, int ne) -> int {
+    B200_TRY(launch_qgemv(type, epi, false, grouped, p, fused_tail ? t : no_tail, ne, pdl(), st));
+    if (!fused_tail) B200_TRY(launch_row_tail(t, pdl(), st));
+    return OK;
   };
   const int l0 = f.draft ? c.n_layer : 0, l1 = f.draft ? c.n_layer + 1 : c.n_layer;
   if (f.draft) {
     // nextn seed, embedding first: h = eh_proj . concat(rms(embd, enorm), rms(h_prev, hnorm))  (llm/mtp.go:352-384)
     const LayerW& L = m->layers[c.n_layer];
-    EmbedParams ep{m->token_embd, ids_dev, e_buf, M, H};
+    EmbedParams ep{m->token_embd, ids_dev, e_buf, M, H, nullptr, nullptr, c.eps};
     B200_TRY(launch_embed(ep, st)); pdl();
-    QGemvParams p = base(L.eh_proj, 2 * H, H);
-    p.x = e_buf; p.ldx = H; p.x2 = hs_buf; p.ldx2 = H; p.gamma = (const float*)L.enorm.data; p.gamma2 = (const float*)L.hnorm.data;
+    B200_TRY(launch_concat_norm(e_buf, hs_buf, (const float*)L.enorm.data, (const float*)L.hnorm.data, c.eps, H, M, xcat16, pdl(), st));
+    QGemvParams p = base(L.eh_proj, 2 * H, H, xcat16, 2 * H);
     p.y = h; p.ldy = H;
-    B200_TRY(launch_qgemv(L.eh_proj.type, PRO_CONCAT_NORM, EPI_STORE, false, false, p, 0, pdl(), st));
+    B200_TRY(proj_with_tail(L.eh_proj.type, EPI_STORE, false, p, tail(1, L.attn_norm), 0));
   } else {
-    EmbedParams ep{m->token_embd, ids_dev, h, M, H};
+    EmbedParams ep{m->token_embd, ids_dev, h, M, H, (const float*)m->layers[0].attn_norm.data, xn16, c.eps};
     B200_TRY(launch_embed(ep, st)); pdl();
   }
   for (int l = l0; l < l1; l++) {
     const LayerW& L = m->layers[l];
     if (!L.is_attn) {
       const int di = dn_index[l];
-      QGemvParams p = base(L.qkv, H, cw + vw);
+      QGemvParams p = base(L.qkv, H, cw + vw, xn16, H);
       p.w[1] = L.z.data; p.seg_end[0] = cw; p.seg_end[1] = cw + vw; p.nseg = 2;
-      p.x = h; p.ldx = H; p.gamma = (const float*)L.attn_norm.data; p.xn_out = xn16; p.y = proj; p.ldy = proj_ld;
-      B200_TRY(launch_qgemv(L.qkv.type, PRO_RMSNORM, EPI_STORE, false, false, p, 0, pdl(), st));
+      p.y = proj; p.ldy = proj_ld;
+      B200_TRY(launch_qgemv(L.qkv.type, EPI_STORE, false, false, p, no_tail, 0, pdl(), st));
       DnStepParams d{};
       d.proj = proj; d.ldp = proj_ld; d.xn = xn16; d.alpha_w = (const float*)L.alpha.data; d.beta_w = (const float*)L.beta.data;
       d.conv_w = (const float*)L.conv1d.data; d.ssm_a = (const float*)L.ssm_a.data; d.dt_bias = (const float*)L.dt_bias.data;
       d.state = dn_state[di]; d.state_slot_stride = state_slot_stride; d.ring = dn_ring[di]; d.ring_slot_stride = ring_slot_stride;
-      d.seqs = seqs; d.n_seq = n_seq; d.out = dn_o; d.mid = f.spec ? dn_mid[di] : nullptr; d.mid_stride = state_slot_stride; d.mid_seq_stride = mid_seq_stride;
+      d.seqs = seqs; d.n_seq = n_seq; d.norm_w = (const float*)L.ssm_norm.data; d.y16 = y16;
+      d.mid = f.spec ? dn_mid[di] : nullptr; d.mid_stride = state_slot_stride; d.mid_seq_stride = mid_seq_stride;
       d.H = H; d.Hk = c.dn_heads_k; d.Hv = c.dn_heads_v; d.D = D; d.conv = c.dn_conv; d.eps = c.eps;
       B200_TRY(launch_dn_step(d, pdl(), st));
-      QGemvParams q = base(L.ssm_out, vw, H);
-      q.x = dn_o; q.ldx = vw; q.z = proj + cw; q.ldz = proj_ld; q.gamma = (const float*)L.ssm_norm.data; q.head_dim = D; q.y = h; q.ldy = H;
-      B200_TRY(launch_qgemv(L.ssm_out.type, PRO_DN_GATED, EPI_RESID, false, false, q, 0, pdl(), st));
+      QGemvParams q = base(L.ssm_out, vw, H, y16, vw);
+      q.y = h; q.ldy = H;
+      B200_TRY(proj_with_tail(L.ssm_out.type, EPI_RESID, false, q, tail(1, L.ffn_norm), 0));
     } else {
       const int ai = attn_index[l];
       // fused q|k|v projection; tensors of one type share a launch
@@ -188,11 +208,11 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
         int e = s + 1;
         while (e < 3 && seg[e]->type == seg[s]->type) e++;
         int n = 0;
-        QGemvParams p = base(*seg[s], H, 0);
+        QGemvParams p = base(*seg[s], H, 0, xn16, H);
         for (int i = s; i < e; i++) { p.w[i - s] = seg[i]->data; n += rows[i]; p.seg_end[i - s] = n; }
         p.nseg = e - s; p.N = n;
-        p.x = h; p.ldx = H; p.gamma = (const float*)L.attn_norm.data; p.y = proj + off; p.ldy = proj_ld;
-        B200_TRY(launch_qgemv(seg[s]->type, PRO_RMSNORM, EPI_STORE, false, false, p, 0, pdl(), st));
+        p.y = proj + off; p.ldy = proj_ld;
+        B200_TRY(launch_qgemv(seg[s]->type, EPI_STORE, false, false, p, no_tail, 0, pdl(), st));
         off += n; s = e;
       }
       AttnParams a{};
@@ -203,47 +223,44 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       a.split_cells = split_cells; a.nsplit = nsplit; a.eps = c.eps; a.rope_off = f.draft ? 1 : 0;
       B200_TRY(launch_attn_pack(a, pdl(), st));
       B200_TRY(launch_attn_decode(a, pdl(), st));
-      QGemvParams q = base(L.o, qw, H);
-      q.x = ctx16; q.ldx = qw; q.y = h; q.ldy = H;
-      B200_TRY(launch_qgemv(L.o.type, PRO_F16, EPI_RESID, false, false, q, 0, pdl(), st));
+      QGemvParams q = base(L.o, qw, H, ctx16, qw);
+      q.y = h; q.ldy = H;
+      B200_TRY(proj_with_tail(L.o.type, EPI_RESID, false, q, tail(1, L.ffn_norm), 0));
     }
-    if (o.trace) B200_CUDA(cudaMemcpyAsync(tr_mid + (size_t)l * MR * H, h, (size_t)M * H * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    if (o.trace) { B200_CUDA(cudaMemcpyAsync(tr_mid + (size_t)l * MR * H, h, (size_t)M * H * sizeof(float), cudaMemcpyDeviceToDevice, st)); first = true; }
     // MoE block
     RouterParams r{};
-    r.h = h; r.gamma = (const float*)L.ffn_norm.data; r.eps = c.eps; r.router = L.router; r.sh_gate = (const float*)L.sh_gate_inp.data;
-    r.M = M; r.H = H; r.nE = c.n_expert; r.used = used; r.logits = r_logits; r.probs = r_probs; r.topk = topk; r.topk_w = topk_w;
+    r.xn = xn16; r.router = L.router; r.sh_gate = (const float*)L.sh_gate_inp.data;
+    r.M = M; r.H = H; r.nE = c.n_expert; r.used = used; r.logits = r_logits; r.probs = nullptr; r.topk = topk; r.topk_w = topk_w;
     r.margin = margin; r.entries = entries; r.n_entries = n_entries; r.cols = cols; r.ticket = r_ticket; r.max_entries = max_entries;
-    B200_TRY(launch_router(r, o.trace ? false : pdl(), st));
-    if (o.trace) { first = false; launches++; }
-    {
-      QGemvParams p = base(L.gate_exps, H, c.ffn_expert);
-      p.w2[0] = L.up_exps.data; p.ws = L.gate_sh.data; p.ws2 = L.up_sh.data; p.expert_stride = (int64_t)c.ffn_expert * L.gate_exps.stride;
-      p.entries = entries; p.n_entries = n_entries; p.cols = cols; p.x_div = slots1;
-      p.x = h; p.ldx = H; p.gamma = (const float*)L.ffn_norm.data; p.y16 = act16; p.ldy = c.ffn_expert;
-      B200_TRY(launch_qgemv(L.gate_exps.type, PRO_RMSNORM, EPI_SWIGLU, true, true, p, max_entries_for(M), pdl(), st));
-      QGemvParams q = base(L.down_exps, c.ffn_expert, H);
-      q.ws = L.down_sh.data; q.expert_stride = (int64_t)H * L.down_exps.stride;
-      q.entries = entries; q.n_entries = n_entries; q.cols = cols; q.x_div = 1;
-      q.x = act16; q.ldx = c.ffn_expert; q.y = down; q.ldy = H;
-      B200_TRY(launch_qgemv(L.down_exps.type, PRO_F16, EPI_STORE, false, true, q, max_entries_for(M), pdl(), st));
-    }
-    CombineParams cb{h, down, topk_w, M, H, used};
-    B200_TRY(launch_moe_combine(cb, pdl(), st));
+    B200_TRY(launch_router(r, pdl(), st));
+    const int ne = max_entries_for(M);
+    QGemvParams p = base(L.gate_exps, H, c.ffn_expert, xn16, H);
+    p.w2[0] = L.up_exps.data; p.ws = L.gate_sh.data; p.ws2 = L.up_sh.data; p.expert_stride = (int64_t)c.ffn_expert * L.gate_exps.stride;
+    p.entries = entries; p.n_entries = n_entries; p.cols = cols; p.x_div = slots1;
+    p.y16 = act16; p.ldy = c.ffn_expert;
+    B200_TRY(launch_qgemv(L.gate_exps.type, EPI_SWIGLU, true, true, p, no_tail, ne, pdl(), st));
+    QGemvParams q = base(L.down_exps, c.ffn_expert, H, act16, c.ffn_expert);
+    q.ws = L.down_sh.data; q.expert_stride = (int64_t)H * L.down_exps.stride;
+    q.entries = entries; q.n_entries = n_entries; q.cols = cols; q.x_div = 1;
+    q.y = down; q.ldy = H;
+    const DTensor& next_norm = f.draft ? L.head_norm : (l + 1 < c.n_layer ? m->layers[l + 1].attn_norm : m->output_norm);
+    B200_TRY(proj_with_tail(L.down_exps.type, EPI_STORE, true, q, tail(2, next_norm), ne));
     if (o.trace) {
       B200_CUDA(cudaMemcpyAsync(tr_out + (size_t)l * MR * H, h, (size_t)M * H * sizeof(float), cudaMemcpyDeviceToDevice, st));
       B200_CUDA(cudaMemcpyAsync(tr_topk + (size_t)l * MR * used, topk, (size_t)M * used * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
       B200_CUDA(cudaMemcpyAsync(tr_w + (size_t)l * MR * slots1, topk_w, (size_t)M * slots1 * sizeof(float), cudaMemcpyDeviceToDevice, st));
       B200_CUDA(cudaMemcpyAsync(tr_margin + (size_t)l * MR, margin, (size_t)M * sizeof(float), cudaMemcpyDeviceToDevice, st));
-      first = true;  // a copy sits between this kernel and the next: no programmatic edge
+      first = true;  // copies sit between this kernel and the next: no programmatic edge
     }
   }
   if (n_logit_rows > 0) {
-    const DTensor& nrm = f.draft ? m->layers[c.n_layer].head_norm : m->output_norm;
+    // xn16 already holds output_norm(h) (or the draft's shared_head_norm) for every row
     const int N = f.draft && draft_vocab > 0 ? draft_vocab : c.vocab;
-    QGemvParams p = base(m->output, H, N);
+    QGemvParams p = base(m->output, H, N, xn16, H);
     p.M = n_logit_rows; p.xcols = std::min(n_logit_rows, QG_MAXCOLS); p.row_ids = logit_rows;
-    p.x = h; p.ldx = H; p.gamma = (const float*)nrm.data; p.y = logits; p.ldy = N;
-    B200_TRY(launch_qgemv(m->output.type, PRO_RMSNORM, EPI_STORE, false, false, p, 0, pdl(), st));
+    p.y = logits; p.ldy = N;
+    B200_TRY(launch_qgemv(m->output.type, EPI_STORE, false, false, p, no_tail, 0, pdl(), st));
     if (f.greedy) {
       B200_TRY(launch_argmax(logits, n_logit_rows, N, next_ids, pdl(), st));
       B200_TRY(launch_advance(ids_dev, next_ids, row_pos, seqs, M, history, hist_len, st)); launches++;

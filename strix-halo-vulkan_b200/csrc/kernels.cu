@@ -3,7 +3,11 @@
 // and the Q6_K / Q8_0 row re-layout.
 #include "kernels.cuh"
 
+#include <cooperative_groups.h>
+
 #include <cmath>
+
+namespace cg = cooperative_groups;
 
 namespace b200 {
 
@@ -171,15 +175,21 @@ int dequant_rows(const DTensor& t, int64_t row0, int64_t rows, float* out, cudaS
 }
 
 // Embedding gather on the device (the reference dequantises the row on the host and
-// uploads it: llm/model.go:125-144).
-__global__ void embed_kernel(EmbedParams p) {
+// uploads it: llm/model.go:125-144), fused with the first layer's input norm.
+__global__ void __launch_bounds__(QG_THREADS) embed_norm_kernel(EmbedParams p) {
+  __shared__ float scratch[2 * QG_WARPS];
   const int n = blockIdx.x;
   const int64_t id = p.ids[n];
   const uint8_t* row = p.embd.data + id * p.embd.stride;
-  for (int k = threadIdx.x; k < p.H; k += blockDim.x) p.h[(size_t)n * p.H + k] = dequant_elem(p.embd.type, row, p.H, k);
+  float* h = p.h + (size_t)n * p.H;
+  for (int k = threadIdx.x; k < p.H; k += blockDim.x) h[k] = dequant_elem(p.embd.type, row, p.H, k);
+  if (p.gamma != nullptr) {
+    __syncthreads();
+    row_rmsnorm_f16(h, p.gamma, p.eps, p.H, p.xn + (size_t)n * p.H, scratch);
+  }
 }
 int launch_embed(const EmbedParams& p, cudaStream_t st) {
-  embed_kernel<<<p.M, 256, 0, st>>>(p);
+  embed_norm_kernel<<<p.M, QG_THREADS, 0, st>>>(p);
   B200_CUDA(cudaGetLastError());
   return OK;
 }
@@ -203,68 +213,63 @@ static int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem
 // Router: ffn_norm + router GEMV (exact f32 dequant) + softmax + top-k + work list
 // (reference: llm/moe.go:219-282; shaders/llm_moe_router.comp, llm_moe_route_decode.comp)
 // =========================================================================================
-constexpr int RT_ROWS = 8;    // router rows per CTA: one per warp
-constexpr int RT_CHUNK = 32;  // tokens staged in shared memory at a time
+constexpr int RT_ROWS = 8;  // router rows per CTA: one per warp
 
 __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
-  extern __shared__ __align__(16) uint8_t smem[];
-  __half* xs = reinterpret_cast<__half*>(smem);  // [chunk][H] normalised activations, fp16
-  __shared__ float scratch[8];
   __shared__ int is_last;
+  __shared__ int counts[1025], offs[1025], eoff[1025];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, H = p.H, M = p.M;
+  const int row = blockIdx.x * RT_ROWS + warp;  // of the nE + 1 outputs; the last is the shared-expert gate
+  const bool q8 = p.router.type == T_Q8_0 && H % 512 == 0 && H <= 4096;
+  // the row's weights do not depend on the producer kernel: fetch them first
+  uint4 wq[8]; float wd[8];
+  if (row < p.nE && q8) {
+    const uint8_t* wr = p.router.data + (size_t)row * p.router.stride;
+    const int nb = H / 32;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const int k0 = lane * 16 + i * 512;
+      if (k0 < H) { wq[i] = ldg_stream(wr + k0); wd[i] = ld_f16(wr + nb * 32 + (k0 / 32) * 2); }
+    }
+  }
   pdl_wait();
   pdl_launch();
-  const int row = blockIdx.x * RT_ROWS + warp;  // of the nE + 1 outputs; the last is the shared-expert gate
-  for (int n0 = 0; n0 < M; n0 += RT_CHUNK) {
-    const int nc = min(RT_CHUNK, M - n0);
-    __syncthreads();
-    for (int n = 0; n < nc; n++) {
-      const float* h = p.h + (size_t)(n0 + n) * H;
-      float s = 0.f;
-      for (int k = tid * 4; k < H; k += 1024) {
-        float4 v = *reinterpret_cast<const float4*>(h + k);
-        s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-      }
-      s = warp_sum(s);
-      __syncthreads();
-      if (lane == 0) scratch[warp] = s;
-      __syncthreads();
-      float tot = 0.f;
+  if (row <= p.nE) {
+    for (int n = 0; n < M; n++) {
+      const __half* x = p.xn + (size_t)n * H;
+      float acc = 0.f;
+      if (row == p.nE) {
+        for (int k = lane * 8; k < H; k += 256) {
+          uint4 xv = __ldcg(reinterpret_cast<const uint4*>(x + k));
+          const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+          float4 g0 = *reinterpret_cast<const float4*>(p.sh_gate + k), g1 = *reinterpret_cast<const float4*>(p.sh_gate + k + 4);
+          acc = fmaf(g0.x, h2f_lo(xw[0]), acc); acc = fmaf(g0.y, h2f_hi(xw[0]), acc); acc = fmaf(g0.z, h2f_lo(xw[1]), acc); acc = fmaf(g0.w, h2f_hi(xw[1]), acc);
+          acc = fmaf(g1.x, h2f_lo(xw[2]), acc); acc = fmaf(g1.y, h2f_hi(xw[2]), acc); acc = fmaf(g1.z, h2f_lo(xw[3]), acc); acc = fmaf(g1.w, h2f_hi(xw[3]), acc);
+        }
+      } else if (q8) {
 #pragma unroll
-      for (int w = 0; w < 8; w++) tot += scratch[w];
-      const float scale = 1.0f / sqrtf(tot / (float)H + p.eps);
-      for (int k = tid; k < H; k += 256) xs[(size_t)n * H + k] = __float2half_rn(h[k] * scale * p.gamma[k]);
-    }
-    __syncthreads();
-    if (row <= p.nE) {
-      for (int n = 0; n < nc; n++) {
-        const __half* x = xs + (size_t)n * H;
-        float acc = 0.f;
-        if (row == p.nE) {
-          for (int k = lane; k < H; k += 32) acc = fmaf(p.sh_gate[k], __half2float(x[k]), acc);
-        } else {
-          const uint8_t* wr = p.router.data + (size_t)row * p.router.stride;
-          if (p.router.type == T_Q8_0) {
-            const int nb = H / 32;
-            for (int k0 = lane * 16; k0 < H; k0 += 512) {
-              uint4 q = *reinterpret_cast<const uint4*>(wr + k0);
-              const float d = ld_f16(wr + nb * 32 + (k0 / 32) * 2);
-              const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        for (int i = 0; i < 8; i++) {
+          const int k0 = lane * 16 + i * 512;
+          if (k0 < H) {
+            uint4 xa = __ldcg(reinterpret_cast<const uint4*>(x + k0)), xb = __ldcg(reinterpret_cast<const uint4*>(x + k0 + 8));
+            const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+            const uint32_t w[4] = {wq[i].x, wq[i].y, wq[i].z, wq[i].w};
 #pragma unroll
-              for (int j = 0; j < 16; j++) {
-                float wv = __fmul_rn((float)(int8_t)((w[j >> 2] >> (8 * (j & 3))) & 0xFF), d);
-                acc = fmaf(wv, __half2float(x[k0 + j]), acc);
-              }
+            for (int j = 0; j < 16; j++) {
+              const float wv = __fmul_rn((float)(int8_t)((w[j >> 2] >> (8 * (j & 3))) & 0xFF), wd[i]);  // gguf/dequant.go:128-137
+              const float xv = (j & 1) ? h2f_hi(xw[j >> 1]) : h2f_lo(xw[j >> 1]);
+              acc = fmaf(wv, xv, acc);
             }
-          } else {
-            for (int k = lane; k < H; k += 32) acc = fmaf(dequant_elem(p.router.type, wr, H, k), __half2float(x[k]), acc);
           }
         }
-        acc = warp_sum(acc);
-        if (lane == 0) {
-          if (row == p.nE) p.topk_w[(size_t)(n0 + n) * (p.used + 1) + p.used] = sigmoid_acc(acc);
-          else p.logits[(size_t)(n0 + n) * p.nE + row] = acc;
-        }
+      } else {
+        const uint8_t* wr = p.router.data + (size_t)row * p.router.stride;
+        for (int k = lane; k < H; k += 32) acc = fmaf(dequant_elem(p.router.type, wr, H, k), __half2float(x[k]), acc);
+      }
+      acc = warp_sum(acc);
+      if (lane == 0) {
+        if (row == p.nE) p.topk_w[(size_t)n * (p.used + 1) + p.used] = sigmoid_acc(acc);
+        else p.logits[(size_t)n * p.nE + row] = acc;
       }
     }
   }
@@ -275,33 +280,35 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   __syncthreads();
   if (!is_last) return;
   __threadfence();
+  if (tid == 0) *p.ticket = 0;
   const int nE = p.nE, used = p.used;
-  int* counts = reinterpret_cast<int*>(smem);  // [nE + 1] reuse of xs
-  int* offs = counts + nE + 1;                 // [nE + 1]
-  __syncthreads();
   for (int n = warp; n < M; n += 8) {
-    const float* lg = p.logits + (size_t)n * nE;
-    float* pr = p.probs + (size_t)n * nE;
+    // softmax (llm/moe.go:426-443); lane owns experts lane + 32*i, kept in registers
+    float pv[32];
     float mx = -INFINITY;
-    for (int e = lane; e < nE; e += 32) mx = fmaxf(mx, __ldcg(lg + e));
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+      const int e = lane + 32 * i;
+      pv[i] = e < nE ? __ldcg(p.logits + (size_t)n * nE + e) : -INFINITY;
+      mx = fmaxf(mx, pv[i]);
+    }
     mx = warp_max(mx);
     float sum = 0.f;
-    for (int e = lane; e < nE; e += 32) { float v = expf(__ldcg(lg + e) - mx); pr[e] = v; sum += v; }
+#pragma unroll
+    for (int i = 0; i < 32; i++) { pv[i] = lane + 32 * i < nE ? expf(pv[i] - mx) : 0.f; sum += pv[i]; }
     sum = warp_sum(sum);
     const float inv = 1.0f / sum;
-    for (int e = lane; e < nE; e += 32) pr[e] *= inv;
-    __syncwarp();
-    // top-k by descending probability, ties to the lower index (llm/moe.go:249-252).
-    // Lane owns experts lane + 32*i; `taken` marks the ones already chosen.
-    float wsum = 0.f, last_p = 0.f;
-    uint32_t taken = 0;
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+      pv[i] = lane + 32 * i < nE ? pv[i] * inv : -1.f;
+      if (p.probs != nullptr && lane + 32 * i < nE) p.probs[(size_t)n * nE + lane + 32 * i] = pv[i];
+    }
+    // top-k by descending probability, ties to the lower index (llm/moe.go:249-252)
+    float wsum = 0.f, last_p = 0.f, myw = 0.f;
     for (int k = 0; k <= used; k++) {
       float bv = -1.f; int bi = 0x7fffffff;
-      for (int e = lane, i = 0; e < nE; e += 32, i++) {
-        if (taken >> i & 1u) continue;
-        float v = pr[e];
-        if (v > bv) { bv = v; bi = e; }
-      }
+#pragma unroll
+      for (int i = 0; i < 32; i++) if (pv[i] > bv) { bv = pv[i]; bi = lane + 32 * i; }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
         float ov = __shfl_xor_sync(0xffffffffu, bv, o);
@@ -312,85 +319,102 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
         if (lane == 0 && p.margin) p.margin[n] = last_p > 0.f ? (last_p - fmaxf(bv, 0.f)) / last_p : 0.f;
         break;
       }
-      if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
-      if (lane == 0) { p.topk[(size_t)n * used + k] = bi; p.topk_w[(size_t)n * (used + 1) + k] = bv; }
+      if ((bi & 31) == lane) {
+#pragma unroll
+        for (int i = 0; i < 32; i++) if (i == (bi >> 5)) pv[i] = -1.f;
+      }
+      if (lane == k) { myw = bv; p.topk[(size_t)n * used + k] = bi; }
       wsum += bv; last_p = bv;
     }
-    __syncwarp();
     // normalise the weights (llm/moe.go:256-282)
     if (wsum < 6.103515625e-5f) wsum = 6.103515625e-5f;
-    if (lane < used) {
-      float* w = p.topk_w + (size_t)n * (used + 1) + lane;
-      *w = *w / wsum;
-    }
+    if (lane < used) p.topk_w[(size_t)n * (used + 1) + lane] = myw / wsum;
   }
+  __threadfence_block();
   __syncthreads();
   // work list: pair id = n*(used+1) + slot; slot == used is the shared expert
+  if (M == 1) {
+    if (tid < used) { p.entries[tid] = make_int4(p.topk[tid], tid, 1, 0); p.cols[tid] = tid; }
+    if (tid == used) { p.entries[used] = make_int4(-1, used, 1, 0); p.cols[used] = used; *p.n_entries = used + 1; }
+    return;
+  }
   for (int i = tid; i <= nE; i += 256) counts[i] = 0;
   __syncthreads();
   for (int i = tid; i < M * used; i += 256) atomicAdd(&counts[p.topk[i]], 1);
   __syncthreads();
-  if (tid == 0) {
-    int off = 0, ne = 0;
-    for (int e = 0; e < nE; e++) {
-      offs[e] = off;
-      for (int c = 0; c < counts[e]; c += 8) {
-        if (ne < p.max_entries) p.entries[ne] = make_int4(e, off + c, min(8, counts[e] - c), 0);
-        ne++;
-      }
-      off += counts[e];
-      counts[e] = 0;
+  if (warp == 0) {  // exclusive scans of the pair counts and of the entry counts (8 columns per entry)
+    const int per = (nE + 31) / 32;
+    int c = 0, en = 0;
+    for (int i = 0; i < per; i++) { const int e = lane * per + i; if (e < nE) { c += counts[e]; en += (counts[e] + 7) >> 3; } }
+    int cs = c, es = en;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int a = __shfl_up_sync(0xffffffffu, cs, o), b = __shfl_up_sync(0xffffffffu, es, o);
+      if (lane >= o) { cs += a; es += b; }
     }
-    for (int c = 0; c < M; c += 8) {
-      if (ne < p.max_entries) p.entries[ne] = make_int4(-1, off + c, min(8, M - c), 0);
-      ne++;
+    int co = cs - c, eo = es - en;
+    for (int i = 0; i < per; i++) {
+      const int e = lane * per + i;
+      if (e < nE) { offs[e] = co; eoff[e] = eo; co += counts[e]; eo += (counts[e] + 7) >> 3; }
     }
-    offs[nE] = off;
-    *p.n_entries = ne < p.max_entries ? ne : p.max_entries;
-    *p.ticket = 0;
+    const int tot_c = __shfl_sync(0xffffffffu, cs, 31), tot_e = __shfl_sync(0xffffffffu, es, 31);
+    if (lane == 0) { offs[nE] = tot_c; eoff[nE] = tot_e; }
   }
   __syncthreads();
+  for (int e = tid; e < nE; e += 256) {
+    for (int c = 0, i = 0; c < counts[e]; c += 8, i++)
+      if (eoff[e] + i < p.max_entries) p.entries[eoff[e] + i] = make_int4(e, offs[e] + c, min(8, counts[e] - c), 0);
+  }
+  const int nsh = (M + 7) >> 3;
+  for (int i = tid; i < nsh; i += 256)
+    if (eoff[nE] + i < p.max_entries) p.entries[eoff[nE] + i] = make_int4(-1, offs[nE] + 8 * i, min(8, M - 8 * i), 0);
+  if (tid == 0) *p.n_entries = min(eoff[nE] + nsh, p.max_entries);
+  __syncthreads();
+  for (int i = tid; i <= nE; i += 256) counts[i] = 0;
+  __syncthreads();
   for (int i = tid; i < M * used; i += 256) {
-    int e = p.topk[i], n = i / used, k = i - n * used;
-    int pos = atomicAdd(&counts[e], 1);
+    const int e = p.topk[i], n = i / used, k = i - n * used;
+    const int pos = atomicAdd(&counts[e], 1);
     p.cols[offs[e] + pos] = n * (used + 1) + k;
   }
   for (int n = tid; n < M; n += 256) p.cols[offs[nE] + n] = n * (used + 1) + used;
 }
 
 int launch_router(const RouterParams& p, bool pdl, cudaStream_t st) {
-  size_t smem = (size_t)(p.M < RT_CHUNK ? p.M : RT_CHUNK) * p.H * sizeof(__half);
-  size_t need = (size_t)(2 * (p.nE + 1)) * sizeof(int);
-  if (smem < need) smem = need;
-  static bool attr = false;
-  if (!attr) { cudaFuncSetAttribute(router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr = true; }
-  if (smem > 200 * 1024 || p.nE > 1024 || p.used > 32) { set_error("router: shape outside kernel limits"); return ECAPACITY; }
+  if (p.nE > 1024 || p.used > 32 || p.H % 8) { set_error("router: shape outside kernel limits"); return ECAPACITY; }
   int grid = (p.nE + 1 + RT_ROWS - 1) / RT_ROWS;
-  return launch_k(router_kernel, dim3(grid), dim3(256), smem, pdl, st, p);
+  return launch_k(router_kernel, dim3(grid), dim3(256), 0, pdl, st, p);
 }
 
-// h[n] += sum_k w_k * down[n,k] (slot order) + sigmoid(gate) * shared  (llm/moe.go:347-357, 403-406)
-__global__ void __launch_bounds__(256) moe_combine_kernel(CombineParams p) {
+// Stand-alone forms of the row tails, one CTA per row, for passes of more than QG_TAIL_ROWS rows.
+__global__ void __launch_bounds__(QG_THREADS) row_tail_kernel(TailParams tp) {
+  __shared__ float scratch[2 * QG_WARPS];
   pdl_wait();
   pdl_launch();
-  const int n = blockIdx.y, j = (blockIdx.x * 256 + threadIdx.x) * 4;
-  if (j >= p.H) return;
-  const int slots = p.used + 1;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int k = 0; k < p.used; k++) {
-    const float w = p.topk_w[(size_t)n * slots + k];
-    float4 d = *reinterpret_cast<const float4*>(p.down + ((size_t)n * slots + k) * p.H + j);
-    acc.x += d.x * w; acc.y += d.y * w; acc.z += d.z * w; acc.w += d.w * w;
+  const int n = blockIdx.x, slots1 = tp.used + 1;
+  float* hrow = tp.h + (size_t)n * tp.H;
+  if (tp.mode == 2) {
+    row_moe_combine(hrow, tp.down + (size_t)n * slots1 * tp.H, tp.topk_w + (size_t)n * slots1, tp.used, tp.H);
+    __syncthreads();
   }
-  const float sg = p.topk_w[(size_t)n * slots + p.used];
-  float4 s = *reinterpret_cast<const float4*>(p.down + ((size_t)n * slots + p.used) * p.H + j);
-  float4* hp = reinterpret_cast<float4*>(p.h + (size_t)n * p.H + j);
-  float4 h = *hp;
-  h.x += acc.x + s.x * sg; h.y += acc.y + s.y * sg; h.z += acc.z + s.z * sg; h.w += acc.w + s.w * sg;
-  *hp = h;
+  row_rmsnorm_f16(hrow, tp.gamma, tp.eps, tp.H, tp.xn + (size_t)n * tp.H, scratch);
 }
-int launch_moe_combine(const CombineParams& p, bool pdl, cudaStream_t st) {
-  return launch_k(moe_combine_kernel, dim3((p.H / 4 + 255) / 256, p.M), dim3(256), 0, pdl, st, p);
+int launch_row_tail(const TailParams& tp, bool pdl, cudaStream_t st) {
+  return launch_k(row_tail_kernel, dim3(tp.M), dim3(QG_THREADS), 0, pdl, st, tp);
+}
+
+// Draft seed input: xcat[n] = fp16(rms(embd[n], enorm)) | fp16(rms(h_prev[n], hnorm))  (llm/mtp.go:352-384)
+__global__ void __launch_bounds__(QG_THREADS) concat_norm_kernel(const float* e, const float* hs, const float* enorm, const float* hnorm, float eps, int H, __half* xcat) {
+  __shared__ float scratch[2 * QG_WARPS];
+  pdl_wait();
+  pdl_launch();
+  const int n = blockIdx.x;
+  row_rmsnorm_f16(e + (size_t)n * H, enorm, eps, H, xcat + (size_t)n * 2 * H, scratch);
+  __syncthreads();
+  row_rmsnorm_f16(hs + (size_t)n * H, hnorm, eps, H, xcat + (size_t)n * 2 * H + H, scratch);
+}
+int launch_concat_norm(const float* e, const float* hs, const float* enorm, const float* hnorm, float eps, int H, int M, __half* xcat, bool pdl, cudaStream_t st) {
+  return launch_k(concat_norm_kernel, dim3(M), dim3(QG_THREADS), 0, pdl, st, e, hs, enorm, hnorm, eps, H, xcat);
 }
 
 // =========================================================================================
@@ -398,7 +422,10 @@ int launch_moe_combine(const CombineParams& p, bool pdl, cudaStream_t st) {
 // delta-rule state update and read-out (reference: llm/deltanet.go:263-321, 365-455;
 // shaders/llm_dn_conv.comp, llm_dn_scan.comp, llm_seq_hist.comp).
 // grid (Hv * 4, n_seq): a CTA owns 32 of the 128 state rows of one value head of one
-// sequence, keeps them in registers and walks the sequence's tokens in order.
+// sequence, keeps them in registers and walks the sequence's tokens in order. The four CTAs
+// of a head form a thread-block cluster: the gated RMSNorm over the head's 128 outputs
+// (reference: llm/deltanet.go:326-341, shaders/llm_dn_norm.comp) needs their four partial
+// sums of squares, exchanged through distributed shared memory.
 // =========================================================================================
 __device__ __forceinline__ float softplus_ref(float x) {  // llm/deltanet.go:450-455
   if (x > 20.f) return x;
@@ -406,13 +433,14 @@ __device__ __forceinline__ float softplus_ref(float x) {  // llm/deltanet.go:450
 }
 __device__ __forceinline__ float silu_acc(float x) { return x * sigmoid_acc(x); }
 
-__global__ void __launch_bounds__(128) dn_step_kernel(DnStepParams p) {
+__global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(128) dn_step_kernel(DnStepParams p) {
+  cg::cluster_group cluster = cg::this_cluster();
   const int D = 128, RB = 4;
   const int h = blockIdx.x / RB, rb = blockIdx.x % RB, hk = h % p.Hk;
   const SeqDesc sq = p.seqs[blockIdx.y];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qk = p.Hk * D, H = p.H;
-  __shared__ float qs[128], ks[128], vs[32], red[16];
+  __shared__ float qs[128], ks[128], vs[32], red[16], wss[4], cta_ss[2];
   const int ch_q = hk * D + tid, ch_k = qk + hk * D + tid, ch_v = 2 * qk + h * D + rb * 32 + (tid & 31);
   const float4 cwq = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch_q * 4);
   const float4 cwk = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch_k * 4);
@@ -507,11 +535,26 @@ __global__ void __launch_bounds__(128) dn_step_kernel(DnStepParams p) {
 #pragma unroll
       for (int r = 0; r < 8; r++) oo[r] += __shfl_xor_sync(0xffffffffu, oo[r], o);
     }
-    if (lane < 8) {
-      float ov = oo[0];
+    // gated norm: sum of squares over the head's 128 outputs = four CTA partials, added in rank order
+    float ov = oo[0] * oscale, ss = 0.f;
 #pragma unroll
-      for (int r = 1; r < 8; r++) ov = lane == r ? oo[r] : ov;
-      p.out[(size_t)row * (p.Hv * D) + h * D + j0 + lane] = ov * oscale;
+    for (int r = 0; r < 8; r++) {
+      const float orr = oo[r] * oscale;
+      ss += orr * orr;
+      ov = lane == r ? orr : ov;
+    }
+    if (lane == 0) wss[warp] = ss;
+    __syncthreads();
+    if (tid == 0) cta_ss[i & 1] = wss[0] + wss[1] + wss[2] + wss[3];
+    cluster.sync();
+    float tot = 0.f;
+#pragma unroll
+    for (int r = 0; r < 4; r++) tot += *cluster.map_shared_rank(&cta_ss[i & 1], r);
+    if (lane < 8) {
+      const int j = j0 + lane;
+      const float nsc = 1.0f / sqrtf(tot / (float)D + p.eps);
+      const float zz = pr[2 * qk + p.Hv * D + h * D + j];
+      p.y16[(size_t)row * (p.Hv * D) + h * D + j] = __float2half_rn(ov * nsc * p.norm_w[j] * sigmoid_acc(zz));
     }
     if (p.mid != nullptr) {  // state after token i, for keep-prefix speculation
       float* Sm = p.mid + (size_t)blockIdx.y * p.mid_seq_stride + (size_t)i * p.mid_stride + (size_t)h * D * D;
@@ -524,6 +567,7 @@ __global__ void __launch_bounds__(128) dn_step_kernel(DnStepParams p) {
 #pragma unroll
     for (int r = 0; r < 8; r++) *reinterpret_cast<float4*>(S + (size_t)(j0 + r) * D + lane * 4) = s[r];
   }
+  cluster.sync();  // no CTA may leave while a peer can still read its shared memory
 }
 
 int launch_dn_step(const DnStepParams& p, bool pdl, cudaStream_t st) {
@@ -675,25 +719,44 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
   __threadfence();
   if (tid == 0) *ticket = 0;
   const int nlive = (ncell + p.split_cells - 1) / p.split_cells;
+  // merge: O = sum_s O_s * exp(m_s - m*), l likewise (reference: shaders/llm_attn_combine.comp:70-102)
+  float* fac = &sm_o[0][0][0];            // [G][nlive] factors, reusing the warp-merge buffer
+  __shared__ float mm_s[G], ll_s[G];
+  __syncthreads();
+  for (int i = tid; i < G * nlive; i += 128) {
+    const int hh = i / nlive, sp = i - hh * nlive;
+    fac[i] = __ldcg(p.partial + (((size_t)n * p.Hq + kvh * G + hh) * p.nsplit + sp) * PW + hd);
+  }
+  __syncthreads();
+  if (tid < G) {
+    float mm = -INFINITY;
+    for (int sp = 0; sp < nlive; sp++) mm = fmaxf(mm, fac[tid * nlive + sp]);
+    mm_s[tid] = mm;
+  }
+  __syncthreads();
+  for (int i = tid; i < G * nlive; i += 128) fac[i] = expf(fac[i] - mm_s[i / nlive]);
+  __syncthreads();
+  if (tid < G) {
+    float lv = 0.f;
+    for (int sp = 0; sp < nlive; sp++)
+      lv += __ldcg(p.partial + (((size_t)n * p.Hq + kvh * G + tid) * p.nsplit + sp) * PW + hd + 1) * fac[tid * nlive + sp];
+    ll_s[tid] = lv;
+  }
+  __syncthreads();
   const int gate_off = hd;  // per head: hd query dims then hd gate dims
   for (int i = tid; i < G * hd; i += 128) {
     const int hh = i / hd, d = i - hh * hd, head = kvh * G + hh;
     const float* part = p.partial + ((size_t)n * p.Hq + head) * p.nsplit * PW;
-    float mm = -INFINITY;
-    for (int s = 0; s < nlive; s++) mm = fmaxf(mm, __ldcg(part + (size_t)s * PW + hd));
-    float ov = 0.f, lv = 0.f;
-    for (int s = 0; s < nlive; s++) {
-      const float f = expf(__ldcg(part + (size_t)s * PW + hd) - mm);
-      ov += __ldcg(part + (size_t)s * PW + d) * f;
-      lv += __ldcg(part + (size_t)s * PW + hd + 1) * f;
-    }
+    float ov = 0.f;
+    for (int sp = 0; sp < nlive; sp++) ov += __ldcg(part + (size_t)sp * PW + d) * fac[hh * nlive + sp];
     const float gate = p.proj[(size_t)n * p.ldp + head * 2 * hd + gate_off + d];
-    p.ctx16[(size_t)n * p.Hq * hd + head * hd + d] = __float2half_rn(ov / lv * sigmoid_acc(gate));
+    p.ctx16[(size_t)n * p.Hq * hd + head * hd + d] = __float2half_rn(ov / ll_s[hh] * sigmoid_acc(gate));
   }
 }
 
 int launch_attn_decode(const AttnParams& p, bool pdl, cudaStream_t st) {
   const int G = p.Hq / p.Hkv;
+  if (G * p.nsplit > 4 * G * p.hd) { set_error("attn_decode: too many splits for the merge buffer"); return ECAPACITY; }
   dim3 grid(p.nsplit, p.Hkv, p.M), block(128);
   if (p.hd == 256 && G == 8) return launch_k(attn_decode_kernel<8, 8>, grid, block, 0, pdl, st, p);
   if (p.hd == 128 && G == 4) return launch_k(attn_decode_kernel<4, 4>, grid, block, 0, pdl, st, p);

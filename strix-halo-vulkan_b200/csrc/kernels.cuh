@@ -25,14 +25,19 @@ struct EmbedParams {
   const int32_t* ids;  // [M]
   float* h;            // [M][H]
   int M, H;
+  const float* gamma;  // optional: the first consumer's norm weights
+  __half* xn;          // [M][H] fp16 normalised rows (when gamma is given)
+  float eps;
 };
 int launch_embed(const EmbedParams& p, cudaStream_t st);
 
 // K-quant projections; `pdl` marks the launch as a programmatic dependent of the previous kernel.
-int launch_qgemv(uint32_t type, int pro, int epi, bool dual, bool grouped, const QGemvParams& p, int max_entries, bool pdl, cudaStream_t st);
+int launch_qgemv(uint32_t type, int epi, bool dual, bool grouped, const QGemvParams& p, const TailParams& tp, int max_entries, bool pdl, cudaStream_t st);
+int launch_row_tail(const TailParams& tp, bool pdl, cudaStream_t st);
+int launch_concat_norm(const float* e, const float* hs, const float* enorm, const float* hnorm, float eps, int H, int M, __half* xcat, bool pdl, cudaStream_t st);
 
 struct RouterParams {
-  const float* h; const float* gamma; float eps;   // ffn_norm input
+  const __half* xn;                                // [M][H] ffn_norm output, fp16
   DTensor router;                                  // [nE][H], F32 / F16 / Q8_0 (planes)
   const float* sh_gate;                            // [H] F32
   int M, H, nE, used;
@@ -47,10 +52,6 @@ struct RouterParams {
 };
 int launch_router(const RouterParams& p, bool pdl, cudaStream_t st);
 
-struct CombineParams {
-  float* h; const float* down; const float* topk_w; int M, H, used;
-};
-int launch_moe_combine(const CombineParams& p, bool pdl, cudaStream_t st);
 
 struct DnStepParams {
   const float* proj; int64_t ldp;            // [M][ldp]: q | k | v | z
@@ -62,7 +63,8 @@ struct DnStepParams {
   float* ring;                               // [slots][Hv*4][DN_RING][DN_RING_W]
   int64_t ring_slot_stride;
   const SeqDesc* seqs; int n_seq;
-  float* out;                                // [M][Hv*D]
+  const float* norm_w;                       // [D] ssm_norm, shared by all heads
+  __half* y16;                               // [M][Hv*D] gated-norm output: fp16(rms(o) * norm_w * sigmoid(z))
   float* mid;                                // speculation: [n_seq][rows][Hv][D][D] state after each token; the slot's own state is then left untouched
   int64_t mid_stride, mid_seq_stride;        // floats between consecutive rows / sequences of mid
   int H, Hk, Hv, D, conv;

@@ -26,8 +26,8 @@ namespace b200 {
 constexpr int QG_WARPS = 8;
 constexpr int QG_THREADS = QG_WARPS * 32;
 constexpr int QG_MAXCOLS = 8;
+constexpr int QG_TAIL_ROWS = 8;  // rows the in-kernel tail of the last CTA finishes
 
-enum { PRO_F16 = 0, PRO_RMSNORM = 1, PRO_DN_GATED = 2, PRO_CONCAT_NORM = 3 };
 enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
 
 struct QGemvParams {
@@ -49,19 +49,10 @@ struct QGemvParams {
   // plain mode columns: rows [ztile*8, ztile*8+8) of M
   int M;
   int xcols;                 // columns the shared-memory layout is sized for (1..8)
-  const int* row_ids;        // optional: plain mode column c reads/writes row row_ids[c]
-  // activation source
-  const void* x;             // PRO_F16: half [.][ldx]; others: float [.][ldx]
+  const int* row_ids;        // optional: plain mode column c reads row row_ids[c] and writes row c
+  // activations: fp16 rows in natural order
+  const __half* x;
   int64_t ldx;
-  const float* gamma;        // RMSNORM: [K]; DN_GATED: [head_dim]
-  const float* gamma2;       // CONCAT_NORM: second half's gamma
-  const void* x2;            // CONCAT_NORM: second source (float [.][ldx2])
-  int64_t ldx2;
-  float eps;
-  const float* z;            // DN_GATED: gate pre-activation, float [.][ldz]
-  int64_t ldz;
-  int head_dim;
-  __half* xn_out;            // RMSNORM: optional side output of the normalised row, [.][K]
   // epilogue
   float* y;                  // STORE / RESID: float [.][ldy]
   int64_t ldy;
@@ -76,7 +67,7 @@ __host__ __device__ inline int qg_xstride(int K) {
 __host__ __device__ inline size_t qg_smem_bytes(int K, int xcols, bool dual) {
   size_t xs = (size_t)xcols * qg_xstride(K);
   size_t sx = (size_t)xcols * (K / 32) * 2 * sizeof(__half);  // hi and lo planes
-  size_t red = (size_t)QG_WARPS * 16 * 8 * sizeof(float) * (dual ? 2 : 1);
+  size_t red = (size_t)2 * QG_WARPS * 16 * 8 * sizeof(float) * (dual ? 2 : 1);  // double-buffered
   return xs + ((sx + 15) & ~(size_t)15) + red;
 }
 
@@ -333,87 +324,83 @@ __device__ __forceinline__ void block_accumulate(float (&acc)[4], const typename
 }
 
 
-// ---- activation staging ----------------------------------------------------------------
-// Fills xs (fp16, permuted, padded) for `ncols` columns and the sub-block sums (hi/lo fp16
-// planes) used by the min term. All threads of the CTA take part.
-//   sxs layout: [plane(2)][xcols][K/32] halves.
-template <int PRO>
-__device__ __forceinline__ void stage_x(const QGemvParams& p, uint8_t* xs, __half* sxs, float* scratch, int ncols, const int* col_rows, int xstride) {
-  const int K = p.K, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  for (int c = 0; c < ncols; c++) {
-    const int64_t row = col_rows[c];
-    uint8_t* dst = xs + (size_t)c * xstride;
-    if constexpr (PRO == PRO_F16) {
-      const __half* src = reinterpret_cast<const __half*>(p.x) + row * p.ldx;
-      for (int k = tid * 8; k < K; k += QG_THREADS * 8) {
-        uint4 v = *reinterpret_cast<const uint4*>(src + k);
-        uint4 o;
-        o.x = __byte_perm(v.x, v.y, 0x5410); o.y = __byte_perm(v.x, v.y, 0x7632);
-        o.z = __byte_perm(v.z, v.w, 0x5410); o.w = __byte_perm(v.z, v.w, 0x7632);
-        *reinterpret_cast<uint4*>(dst + 2 * k + 16 * (k >> 6)) = o;
-      }
-    } else {
-      float scale0 = 1.f, scale1 = 1.f;
-      const float* src = reinterpret_cast<const float*>(p.x) + row * p.ldx;
-      const float* src2 = PRO == PRO_CONCAT_NORM ? reinterpret_cast<const float*>(p.x2) + row * p.ldx2 : nullptr;
-      if constexpr (PRO == PRO_RMSNORM || PRO == PRO_CONCAT_NORM) {
-        // sum of squares over the row (CONCAT: over each half separately), fixed order
-        const int halfK = PRO == PRO_CONCAT_NORM ? K / 2 : K;
-        float s0 = 0.f, s1 = 0.f;
-        for (int k = tid * 4; k < halfK; k += QG_THREADS * 4) {
-          float4 v = *reinterpret_cast<const float4*>(src + k);
-          s0 += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-          if constexpr (PRO == PRO_CONCAT_NORM) {
-            float4 u = *reinterpret_cast<const float4*>(src2 + k);
-            s1 += u.x * u.x + u.y * u.y + u.z * u.z + u.w * u.w;
-          }
-        }
-        s0 = warp_sum(s0); s1 = warp_sum(s1);
-        __syncthreads();
-        if (lane == 0) { scratch[warp] = s0; scratch[QG_WARPS + warp] = s1; }
-        __syncthreads();
-        float t0 = 0.f, t1 = 0.f;
+// ---- row-level tails ---------------------------------------------------------------------
+// Executed by one whole CTA (QG_THREADS threads) for one activation row. Used both as the
+// tail of the last CTA of a projection kernel (small passes) and as stand-alone kernels
+// (large passes), so both give bit-identical rows.
+
+// xn[k] = fp16(h[k] * gamma[k] / sqrt(mean(h^2) + eps))   (reference: llm/hc.go:176-190)
+__device__ __forceinline__ void row_rmsnorm_f16(const float* h, const float* gamma, float eps, int H, __half* xn, float* scratch) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  float s = 0.f;
+  for (int k = tid * 4; k < H; k += QG_THREADS * 4) {
+    float4 v = *reinterpret_cast<const float4*>(h + k);
+    s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  s = warp_sum(s);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = s;
+  __syncthreads();
+  float tot = 0.f;
 #pragma unroll
-        for (int w = 0; w < QG_WARPS; w++) { t0 += scratch[w]; t1 += scratch[QG_WARPS + w]; }
-        scale0 = 1.0f / sqrtf(t0 / (float)halfK + p.eps);
-        scale1 = 1.0f / sqrtf(t1 / (float)halfK + p.eps);
-      }
-      for (int k = tid * 4; k < K; k += QG_THREADS * 4) {
-        float4 v;
-        if constexpr (PRO == PRO_RMSNORM) {
-          float4 h = *reinterpret_cast<const float4*>(src + k);
-          float4 g = *reinterpret_cast<const float4*>(p.gamma + k);
-          v = make_float4(h.x * scale0 * g.x, h.y * scale0 * g.y, h.z * scale0 * g.z, h.w * scale0 * g.w);
-        } else if constexpr (PRO == PRO_CONCAT_NORM) {
-          const int halfK = K / 2;
-          const bool second = k >= halfK;
-          const int kk = second ? k - halfK : k;
-          float4 h = *reinterpret_cast<const float4*>((second ? src2 : src) + kk);
-          float4 g = *reinterpret_cast<const float4*>((second ? p.gamma2 : p.gamma) + kk);
-          float sc = second ? scale1 : scale0;
-          v = make_float4(h.x * sc * g.x, h.y * sc * g.y, h.z * sc * g.z, h.w * sc * g.w);
-        } else {  // PRO_DN_GATED: per-head RMS norm x shared gamma x sigmoid(z)
-          // a head is head_dim (128) values = one warp pass of 32 lanes x 4
-          float4 h = *reinterpret_cast<const float4*>(src + k);
-          float ss = warp_sum(h.x * h.x + h.y * h.y + h.z * h.z + h.w * h.w);
-          float sc = 1.0f / sqrtf(ss / (float)p.head_dim + p.eps);
-          float4 g = *reinterpret_cast<const float4*>(p.gamma + (k & (p.head_dim - 1)));
-          float4 zz = *reinterpret_cast<const float4*>(p.z + row * p.ldz + k);
-          v = make_float4(h.x * sc * g.x * sigmoid_acc(zz.x), h.y * sc * g.y * sigmoid_acc(zz.y), h.z * sc * g.z * sigmoid_acc(zz.z),
-                          h.w * sc * g.w * sigmoid_acc(zz.w));
-        }
-        __half2 a = __floats2half2_rn(v.x, v.z), b = __floats2half2_rn(v.y, v.w);  // stored order [x0,x2,x1,x3]
-        uint2 o = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
-        *reinterpret_cast<uint2*>(dst + 2 * k + 16 * (k >> 6)) = o;
-        if (PRO == PRO_RMSNORM && p.xn_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
-          __half2 n0 = __floats2half2_rn(v.x, v.y), n1 = __floats2half2_rn(v.z, v.w);
-          *reinterpret_cast<uint2*>(p.xn_out + row * K + k) = make_uint2(*reinterpret_cast<uint32_t*>(&n0), *reinterpret_cast<uint32_t*>(&n1));
-        }
-      }
+  for (int w = 0; w < QG_WARPS; w++) tot += scratch[w];
+  const float scale = 1.0f / sqrtf(tot / (float)H + eps);
+  for (int k = tid * 4; k < H; k += QG_THREADS * 4) {
+    float4 v = *reinterpret_cast<const float4*>(h + k);
+    float4 g = *reinterpret_cast<const float4*>(gamma + k);
+    __half2 a = __floats2half2_rn(v.x * scale * g.x, v.y * scale * g.y), b = __floats2half2_rn(v.z * scale * g.z, v.w * scale * g.w);
+    *reinterpret_cast<uint2*>(xn + k) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+  }
+}
+
+// h += sum_k w_k * down_k (slot order) + sigmoid(gate) * shared   (reference: llm/moe.go:347-357, 403-406)
+__device__ __forceinline__ void row_moe_combine(float* h, const float* down, const float* w, int used, int H) {
+  for (int j = threadIdx.x * 4; j < H; j += QG_THREADS * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < used; k++) {
+      const float wk = w[k];
+      float4 d = __ldcg(reinterpret_cast<const float4*>(down + (size_t)k * H + j));
+      acc.x += d.x * wk; acc.y += d.y * wk; acc.z += d.z * wk; acc.w += d.w * wk;
+    }
+    const float sg = w[used];
+    float4 sh = __ldcg(reinterpret_cast<const float4*>(down + (size_t)used * H + j));
+    float4 hv = *reinterpret_cast<float4*>(h + j);
+    hv.x += acc.x + sh.x * sg; hv.y += acc.y + sh.y * sg; hv.z += acc.z + sh.z * sg; hv.w += acc.w + sh.w * sg;
+    *reinterpret_cast<float4*>(h + j) = hv;
+  }
+}
+
+struct TailParams {
+  int mode;             // 0 none, 1 rmsnorm of the residual rows, 2 MoE combine then rmsnorm
+  int* ticket;
+  float* h;             // [M][H] residual stream
+  const float* gamma;   // norm weights of the consumer
+  __half* xn;           // [M][H] normalised rows, fp16, natural order
+  const float* down;    // mode 2: [M][used+1][H]
+  const float* topk_w;  // mode 2: [M][used+1]
+  int used, H, M;
+  float eps;
+};
+
+// ---- activation staging ------------------------------------------------------------------
+// Copies `ncols` fp16 activation rows into shared memory in the permuted, padded layout the
+// B fragments are read in, and forms the per-sub-block sums (fp16 hi + lo planes) of the min
+// term. sxs layout: [plane(2)][xcols][K/32] halves.
+__device__ __forceinline__ void stage_x_f16(const __half* x, int64_t ldx, int K, int xcols, uint8_t* xs, __half* sxs, int ncols, const int* xrows,
+                                            int xstride) {
+  const int tid = threadIdx.x;
+  for (int c = 0; c < ncols; c++) {
+    const __half* src = x + (int64_t)xrows[c] * ldx;
+    uint8_t* dst = xs + (size_t)c * xstride;
+    for (int k = tid * 8; k < K; k += QG_THREADS * 8) {
+      uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + k));
+      uint4 o;
+      o.x = __byte_perm(v.x, v.y, 0x5410); o.y = __byte_perm(v.x, v.y, 0x7632);
+      o.z = __byte_perm(v.z, v.w, 0x5410); o.w = __byte_perm(v.z, v.w, 0x7632);
+      *reinterpret_cast<uint4*>(dst + 2 * k + 16 * (k >> 6)) = o;
     }
   }
   __syncthreads();
-  // sub-block sums of the rounded activations, as fp16 hi + lo
   const int nsub = K / 32;
   for (int i = tid; i < ncols * nsub; i += QG_THREADS) {
     const int c = i / nsub, s = i - c * nsub;
@@ -429,140 +416,173 @@ __device__ __forceinline__ void stage_x(const QGemvParams& p, uint8_t* xs, __hal
     __half hi = __float2half_rn(sum);
     __half lo = __float2half_rn(sum - __half2float(hi));
     sxs[(size_t)c * nsub + s] = hi;
-    sxs[(size_t)(p.xcols + c) * nsub + s] = lo;
+    sxs[(size_t)(xcols + c) * nsub + s] = lo;
   }
   __syncthreads();
 }
 
-// ---- the kernel ------------------------------------------------------------------------
-// grid.x: CTA index over row tiles; grid.y: expert entry (grouped) or 0; grid.z: column tile.
-template <int TYPE, int PRO, int EPI, bool DUAL, bool GROUPED>
-__global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p) {
+// ---- the kernel ----------------------------------------------------------------------------
+// grid.x: persistent CTAs walking the row-tile groups; grid.y: expert entry (grouped) or 0;
+// grid.z: column tile of 8 activation rows (plain mode).
+template <int TYPE, int EPI, bool DUAL, bool GROUPED>
+__global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, const TailParams tp) {
   extern __shared__ __align__(16) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int K = p.K, nb = K / 256;
   const int wpt = nb >= 8 ? 8 : nb >= 4 ? 4 : nb >= 2 ? 2 : 1;  // warps per tile (K-slices)
-  const int tpc = QG_WARPS / wpt;                               // tiles per CTA
+  const int tpc = QG_WARPS / wpt;                               // tiles per CTA and iteration
   const int xstride = qg_xstride(K);
+  constexpr int RED = QG_WARPS * 128 * (DUAL ? 2 : 1);          // floats per reduction buffer
   uint8_t* xs = smem;
   __half* sxs = reinterpret_cast<__half*>(smem + (size_t)p.xcols * xstride);
   float* red = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sxs) + (((size_t)p.xcols * (K / 32) * 2 * sizeof(__half) + 15) & ~(size_t)15));
   __shared__ float scratch[2 * QG_WARPS];
-  __shared__ int col_rows[QG_MAXCOLS];
+  __shared__ int col_rows[QG_MAXCOLS], xrows[QG_MAXCOLS];
+  __shared__ int is_last;
 
-  const int tile = blockIdx.x * tpc + warp / wpt;
-  const int kslice = warp % wpt;
-  const bool tile_ok = tile * 16 < p.N;
-  int r0 = tile * 16 + g, r1 = r0 + 8;
-  if (r0 >= p.N) r0 = p.N - 1;
-  if (r1 >= p.N) r1 = p.N - 1;
+  const int tiles = (p.N + 15) / 16;
+  const int ngroups = (tiles + tpc - 1) / tpc;
+  const int lt = warp / wpt, kslice = warp % wpt;
 
-  // weight base pointers: none of this depends on the producer kernel
+  // weight base pointers and the first loads: none of this depends on the producer kernel
   const uint8_t *wa = nullptr, *wb = nullptr;
   int ncols = 0, col_off = 0;
+  bool active = true;
   if constexpr (GROUPED) {
-    // entries are written by the router kernel: wait before reading them
-    pdl_wait();
-    if ((int)blockIdx.y >= *p.n_entries) return;
-    const int4 e = p.entries[blockIdx.y];
-    col_off = e.y; ncols = e.z;
-    wa = e.x >= 0 ? p.w[0] + (size_t)e.x * p.expert_stride : p.ws;
-    if constexpr (DUAL) wb = e.x >= 0 ? p.w2[0] + (size_t)e.x * p.expert_stride : p.ws2;
+    pdl_wait();  // the entries are written by the router kernel
+    active = (int)blockIdx.y < *p.n_entries;
+    if (active) {
+      const int4 e = p.entries[blockIdx.y];
+      col_off = e.y; ncols = e.z;
+      wa = e.x >= 0 ? p.w[0] + (size_t)e.x * p.expert_stride : p.ws;
+      if constexpr (DUAL) wb = e.x >= 0 ? p.w2[0] + (size_t)e.x * p.expert_stride : p.ws2;
+    }
   } else {
     ncols = p.M - (int)blockIdx.z * QG_MAXCOLS;
     if (ncols > QG_MAXCOLS) ncols = QG_MAXCOLS;
     col_off = (int)blockIdx.z * QG_MAXCOLS;
   }
-  int seg_r0 = 0;
-  if constexpr (!GROUPED) {
-    int s = 0;
-    while (s + 1 < p.nseg && tile * 16 >= p.seg_end[s]) s++;
-    seg_r0 = s > 0 ? p.seg_end[s - 1] : 0;
-    wa = p.w[s];
-    if constexpr (DUAL) wb = p.w2[s];
-  }
-  const uint8_t* row0 = wa + (size_t)(r0 - seg_r0) * p.stride;
-  const uint8_t* row1 = wa + (size_t)(r1 - seg_r0) * p.stride;
-
-  // issue this warp's first weight loads before touching activations
   using Regs = typename RowRegs<TYPE>::type;
   Regs a0, a1, b0, b1;
-  const int blk0 = kslice;  // this warp takes super-blocks kslice, kslice + wpt, ...
-  if (tile_ok) {
-    issue_row<TYPE>(a0, row0, nb, blk0, t);
-    issue_row<TYPE>(a1, row1, nb, blk0, t);
-    if constexpr (DUAL) {
-      issue_row<TYPE>(b0, wb + (size_t)(r0 - seg_r0) * p.stride, nb, blk0, t);
-      issue_row<TYPE>(b1, wb + (size_t)(r1 - seg_r0) * p.stride, nb, blk0, t);
+  // step s of this warp: tile group grp0 + (s / bpw) * gridDim.x, super-block kslice + (s % bpw) * wpt
+  const int bpw = (nb - kslice + wpt - 1) / wpt;
+  auto rows_of = [&](int grp, const uint8_t*& r0p, const uint8_t*& r1p, const uint8_t*& s0p, const uint8_t*& s1p) {
+    const int tile = grp * tpc + lt;
+    int r0 = tile * 16 + g, r1 = r0 + 8;
+    if (r0 >= p.N) r0 = p.N - 1;
+    if (r1 >= p.N) r1 = p.N - 1;
+    int seg_r0 = 0;
+    const uint8_t *base = wa, *base2 = wb;
+    if constexpr (!GROUPED) {
+      int s = 0;
+      while (s + 1 < p.nseg && tile * 16 >= p.seg_end[s]) s++;
+      seg_r0 = s > 0 ? p.seg_end[s - 1] : 0;
+      base = p.w[s];
+      if constexpr (DUAL) base2 = p.w2[s];
     }
+    r0p = base + (size_t)(r0 - seg_r0) * p.stride; r1p = base + (size_t)(r1 - seg_r0) * p.stride;
+    if constexpr (DUAL) { s0p = base2 + (size_t)(r0 - seg_r0) * p.stride; s1p = base2 + (size_t)(r1 - seg_r0) * p.stride; }
+  };
+  const uint8_t *r0p = nullptr, *r1p = nullptr, *s0p = nullptr, *s1p = nullptr;
+  int grp = blockIdx.x;
+  const bool have = active && grp < ngroups && bpw > 0;
+  if (have) {
+    rows_of(grp, r0p, r1p, s0p, s1p);
+    issue_row<TYPE>(a0, r0p, nb, kslice, t);
+    issue_row<TYPE>(a1, r1p, nb, kslice, t);
+    if constexpr (DUAL) { issue_row<TYPE>(b0, s0p, nb, kslice, t); issue_row<TYPE>(b1, s1p, nb, kslice, t); }
   }
   if constexpr (!GROUPED) pdl_wait();
   pdl_launch();
 
-  if (tid < QG_MAXCOLS) {
-    int c = tid < ncols ? tid : 0;
-    int id;
-    if constexpr (GROUPED) id = p.cols[col_off + c];
-    else id = p.row_ids ? p.row_ids[col_off + c] : col_off + c;
-    col_rows[tid] = id;
-  }
-  __syncthreads();
-  {
-    __shared__ int xrows[QG_MAXCOLS];
-    if (tid < QG_MAXCOLS) xrows[tid] = GROUPED ? col_rows[tid] / p.x_div : col_rows[tid];
+  if (active) {
+    if (tid < QG_MAXCOLS) {
+      const int c = tid < ncols ? tid : 0;
+      int id;
+      if constexpr (GROUPED) id = p.cols[col_off + c];
+      else id = p.row_ids ? p.row_ids[col_off + c] : col_off + c;
+      col_rows[tid] = id;
+      xrows[tid] = GROUPED ? id / p.x_div : id;
+    }
     __syncthreads();
-    stage_x<PRO>(p, xs, sxs, scratch, ncols, xrows, xstride);
-  }
+    stage_x_f16(reinterpret_cast<const __half*>(p.x), p.ldx, K, p.xcols, xs, sxs, ncols, xrows, xstride);
 
-  float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
-  const bool live = g < ncols;
-  const uint8_t* xrow = xs + (size_t)(live ? g : 0) * xstride;
-  const __half* sxrow = sxs + (size_t)((t & 1) * p.xcols + (live ? g : 0)) * (K / 32);
-  if (tile_ok) {
-    for (int blk = blk0; blk < nb; blk += wpt) {
-      Regs n0, n1, m0, m1;
-      const bool more = blk + wpt < nb;
-      if (more) {  // prefetch the next super-block of this K-slice
-        issue_row<TYPE>(n0, row0, nb, blk + wpt, t);
-        issue_row<TYPE>(n1, row1, nb, blk + wpt, t);
-        if constexpr (DUAL) {
-          issue_row<TYPE>(m0, wb + (size_t)(r0 - seg_r0) * p.stride, nb, blk + wpt, t);
-          issue_row<TYPE>(m1, wb + (size_t)(r1 - seg_r0) * p.stride, nb, blk + wpt, t);
+    const bool live = g < ncols;
+    const uint8_t* xrow = xs + (size_t)(live ? g : 0) * xstride;
+    const __half* sxrow = sxs + (size_t)((t & 1) * p.xcols + (live ? g : 0)) * (K / 32);
+    int buf = 0;
+    for (; grp < ngroups; grp += gridDim.x) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int i = 0; i < bpw; i++) {
+        const int blk = kslice + i * wpt;
+        // prefetch the next step: the next super-block of this tile, or the first of the next group
+        Regs n0, n1, m0, m1;
+        bool more = false;
+        if (i + 1 < bpw) {
+          more = true;
+          issue_row<TYPE>(n0, r0p, nb, blk + wpt, t); issue_row<TYPE>(n1, r1p, nb, blk + wpt, t);
+          if constexpr (DUAL) { issue_row<TYPE>(m0, s0p, nb, blk + wpt, t); issue_row<TYPE>(m1, s1p, nb, blk + wpt, t); }
+        } else if (grp + (int)gridDim.x < ngroups) {
+          more = true;
+          rows_of(grp + gridDim.x, r0p, r1p, s0p, s1p);
+          issue_row<TYPE>(n0, r0p, nb, kslice, t); issue_row<TYPE>(n1, r1p, nb, kslice, t);
+          if constexpr (DUAL) { issue_row<TYPE>(m0, s0p, nb, kslice, t); issue_row<TYPE>(m1, s1p, nb, kslice, t); }
+        }
+        block_accumulate<TYPE>(acc, a0, a1, xrow, sxrow, live, blk, t);
+        if constexpr (DUAL) block_accumulate<TYPE>(acc2, b0, b1, xrow, sxrow, live, blk, t);
+        if (more) {
+          a0 = n0; a1 = n1;
+          if constexpr (DUAL) { b0 = m0; b1 = m1; }
         }
       }
-      block_accumulate<TYPE>(acc, a0, a1, xrow, sxrow, live, blk, t);
-      if constexpr (DUAL) block_accumulate<TYPE>(acc2, b0, b1, xrow, sxrow, live, blk, t);
-      if (more) {
-        a0 = n0; a1 = n1;
-        if constexpr (DUAL) { b0 = m0; b1 = m1; }
+      // cross-warp reduction in warp order, double-buffered so one barrier per group suffices
+      float* myred = red + (size_t)buf * RED + (size_t)warp * 128;
+      myred[g * 8 + 2 * t] = acc[0]; myred[g * 8 + 2 * t + 1] = acc[1];
+      myred[(g + 8) * 8 + 2 * t] = acc[2]; myred[(g + 8) * 8 + 2 * t + 1] = acc[3];
+      if constexpr (DUAL) {
+        float* r2 = myred + QG_WARPS * 128;
+        r2[g * 8 + 2 * t] = acc2[0]; r2[g * 8 + 2 * t + 1] = acc2[1];
+        r2[(g + 8) * 8 + 2 * t] = acc2[2]; r2[(g + 8) * 8 + 2 * t + 1] = acc2[3];
       }
+      __syncthreads();
+      const float* rb = red + (size_t)buf * RED;
+      for (int i = tid; i < tpc * 128; i += QG_THREADS) {
+        const int l2 = i >> 7, rc = i & 127, r = rc >> 3, c = rc & 7;
+        const int grow = (grp * tpc + l2) * 16 + r;
+        if (grow >= p.N || c >= ncols) continue;
+        float v = 0.f, v2 = 0.f;
+        for (int w = 0; w < wpt; w++) {
+          v += rb[(size_t)(l2 * wpt + w) * 128 + rc];
+          if constexpr (DUAL) v2 += rb[(size_t)(QG_WARPS + l2 * wpt + w) * 128 + rc];
+        }
+        const int64_t orow = (!GROUPED && p.row_ids != nullptr) ? col_off + c : col_rows[c];
+        if constexpr (EPI == EPI_STORE) p.y[orow * p.ldy + grow] = v;
+        else if constexpr (EPI == EPI_RESID) p.y[orow * p.ldy + grow] += v;
+        else {  // SwiGLU of (gate, up) rounded to fp16 (reference: shaders/llm_moe_gemv.comp:777-781)
+          float sw = v * sigmoid_acc(v) * v2;
+          p.y16[orow * p.ldy + grow] = __float2half_rn(sw);
+        }
+      }
+      buf ^= 1;
     }
   }
-  // cross-warp reduction in warp order
-  float* myred = red + (size_t)warp * 128;
-  myred[g * 8 + 2 * t] = acc[0]; myred[g * 8 + 2 * t + 1] = acc[1];
-  myred[(g + 8) * 8 + 2 * t] = acc[2]; myred[(g + 8) * 8 + 2 * t + 1] = acc[3];
-  if constexpr (DUAL) {
-    float* r2 = myred + QG_WARPS * 128;
-    r2[g * 8 + 2 * t] = acc2[0]; r2[g * 8 + 2 * t + 1] = acc2[1];
-    r2[(g + 8) * 8 + 2 * t] = acc2[2]; r2[(g + 8) * 8 + 2 * t + 1] = acc2[3];
-  }
-  __syncthreads();
-  for (int i = tid; i < tpc * 128; i += QG_THREADS) {
-    const int lt = i >> 7, rc = i & 127, r = rc >> 3, c = rc & 7;
-    const int grow = (blockIdx.x * tpc + lt) * 16 + r;
-    if (grow >= p.N || c >= ncols) continue;
-    float v = 0.f, v2 = 0.f;
-    for (int w = 0; w < wpt; w++) {
-      v += red[(size_t)(lt * wpt + w) * 128 + rc];
-      if constexpr (DUAL) v2 += red[(size_t)(QG_WARPS + lt * wpt + w) * 128 + rc];
-    }
-    const int64_t orow = (!GROUPED && p.row_ids != nullptr) ? col_off + c : col_rows[c];
-    if constexpr (EPI == EPI_STORE) p.y[orow * p.ldy + grow] = v;
-    else if constexpr (EPI == EPI_RESID) p.y[orow * p.ldy + grow] += v;
-    else {  // SwiGLU of (gate, up) rounded to fp16 (reference: shaders/llm_moe_gemv.comp:777-781)
-      float s = v * sigmoid_acc(v) * v2;
-      p.y16[orow * p.ldy + grow] = __float2half_rn(s);
+  // tail: the last CTA of the grid finishes the rows (residual norm / MoE combine + norm)
+  if (tp.mode != 0) {
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) is_last = (atomicAdd(tp.ticket, 1) == (int)(gridDim.x * gridDim.y * gridDim.z) - 1);
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (tid == 0) *tp.ticket = 0;
+    const int slots1 = tp.used + 1;
+    for (int n = 0; n < tp.M; n++) {
+      float* hrow = tp.h + (size_t)n * tp.H;
+      if (tp.mode == 2) {
+        row_moe_combine(hrow, tp.down + (size_t)n * slots1 * tp.H, tp.topk_w + (size_t)n * slots1, tp.used, tp.H);
+        __syncthreads();
+      }
+      row_rmsnorm_f16(hrow, tp.gamma, tp.eps, tp.H, tp.xn + (size_t)n * tp.H, scratch);
     }
   }
 }

@@ -227,7 +227,7 @@ __global__ void quantize_q6k_kernel(const float* src, int64_t nblocks, uint8_t* 
   if (max_abs < 1e-15f) { for (int i = 0; i < 210; i++) blk[i] = 0; return; }
   float iscale = -128.f / max_scale;
   __half d16 = __float2half_rn(1 / iscale);
-  blk[208] = (uint8_t)(__half_as_ushort(d16) & 0xFF); blk[209] = (uint8_t)(__half_as_ushort(d16) >> 8);
+  *reinterpret_cast<__half*>(blk + 208) = d16;  // 210 * b + 208 is even
   int8_t* sc = (int8_t*)(blk + 192);
   for (int ib = 0; ib < 16; ib++) {
     float v = nearest_int_f(iscale * scales[ib]);
@@ -263,8 +263,7 @@ __global__ void quantize_q80_kernel(const float* src, int64_t nblocks, uint8_t* 
   for (int i = 0; i < 32; i++) amax = fmaxf(amax, fabsf(x[i]));
   float d = amax / 127.f;
   float id = d != 0 ? 1.f / d : 0.f;
-  unsigned short h = __half_as_ushort(__float2half_rn(d));
-  blk[0] = (uint8_t)(h & 0xFF); blk[1] = (uint8_t)(h >> 8);
+  *reinterpret_cast<__half*>(blk) = __float2half_rn(d);  // 34 * b is even
   for (int i = 0; i < 32; i++) blk[2 + i] = (uint8_t)(int8_t)roundf(x[i] * id);
 }
 
