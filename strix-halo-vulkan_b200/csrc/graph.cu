@@ -32,6 +32,7 @@ Graph::~Graph() {
   if (logits_host) cudaFreeHost(logits_host);
   if (resid_host) cudaFreeHost(resid_host);
   if (hidden_host) cudaFreeHost(hidden_host);
+  if (err_host) cudaFreeHost(err_host);
   if (ids_host) cudaFreeHost(ids_host);
   if (ev0) cudaEventDestroy(ev0);
   if (ev1) cudaEventDestroy(ev1);
@@ -71,7 +72,7 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   B200_TRY(dalloc(&r_logits, (size_t)MR * c.n_expert)); B200_TRY(dalloc(&r_probs, (size_t)MR * c.n_expert));
   B200_TRY(dalloc(&topk, (size_t)MR * used)); B200_TRY(dalloc(&topk_w, (size_t)MR * slots1)); B200_TRY(dalloc(&margin, (size_t)MR));
   B200_TRY(dalloc(&entries, (size_t)max_entries)); B200_TRY(dalloc(&n_entries, 1)); B200_TRY(dalloc(&cols, (size_t)MR * slots1));
-  B200_TRY(dalloc(&r_ticket, 1)); B200_TRY(dalloc(&tail_ticket, 1)); B200_TRY(dalloc(&y16, (size_t)MR * vw));
+  B200_TRY(dalloc(&r_ticket, 1)); B200_TRY(dalloc(&tail_ticket, 1)); B200_TRY(dalloc(&err_flag, 1)); B200_TRY(dalloc(&y16, (size_t)MR * vw));
   B200_TRY(dalloc(&act16, (size_t)MR * slots1 * c.ffn_expert)); B200_TRY(dalloc(&down, (size_t)MR * slots1 * H));
   B200_TRY(dalloc(&logits, (size_t)MR * c.vocab));
   B200_TRY(dalloc(&ids_dev, (size_t)MR)); B200_TRY(dalloc(&next_ids, (size_t)MR)); B200_TRY(dalloc(&row_slot, (size_t)MR));
@@ -117,6 +118,8 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   B200_CUDA(cudaMallocHost((void**)&logits_host, (size_t)MR * c.vocab * sizeof(float)));
   B200_CUDA(cudaMallocHost((void**)&resid_host, (size_t)MR * H * sizeof(float)));
   B200_CUDA(cudaMallocHost((void**)&hidden_host, (size_t)H * sizeof(float)));
+  B200_CUDA(cudaMallocHost((void**)&err_host, sizeof(int)));
+  *err_host = 0;
   B200_CUDA(cudaMallocHost((void**)&ids_host, (size_t)MR * 4096 * sizeof(int32_t)));
   B200_TRY(dalloc(&history, (size_t)MR * 4096));
   if (o.trace) {
@@ -149,7 +152,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
   auto base = [&](const DTensor& w, int K, int N, const __half* x, int ldx) {
     QGemvParams p{};
     p.w[0] = w.data; p.seg_end[0] = N; p.nseg = 1; p.stride = w.stride; p.K = K; p.N = N; p.M = M; p.xcols = xcols; p.x_div = 1;
-    p.x = x; p.ldx = ldx;
+    p.x = x; p.ldx = ldx; p.err = err_flag;
     return p;
   };
   auto tail = [&](int mode, const DTensor& gamma) {
@@ -325,7 +328,9 @@ int Graph::run_rows(const int32_t* ids, const int* slots, const int* pos, int M,
   }
   if (f.want_residual) B200_CUDA(cudaMemcpyAsync(resid_host + (size_t)resid_off * c.n_embd, h, (size_t)M * c.n_embd * sizeof(float), cudaMemcpyDeviceToHost, st));
   B200_CUDA(cudaMemcpyAsync(hidden_host, h + (size_t)(M - 1) * c.n_embd, (size_t)c.n_embd * sizeof(float), cudaMemcpyDeviceToHost, st));
+  B200_CUDA(cudaMemcpyAsync(err_host, err_flag, sizeof(int), cudaMemcpyDeviceToHost, st));
   B200_CUDA(cudaStreamSynchronize(st));
+  if (*err_host != 0) { set_error("a kernel gave up a bounded wait for its weight copies"); return ETIMEOUT; }
   last_rows = M;
   return OK;
 }
@@ -421,7 +426,9 @@ int Graph::generate_greedy(const int32_t* slots_in, const int32_t* first, int n,
   }
   B200_CUDA(cudaEventRecord(ev1, st));
   B200_CUDA(cudaMemcpyAsync(ids_host, history, (size_t)steps * n * sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+  B200_CUDA(cudaMemcpyAsync(err_host, err_flag, sizeof(int), cudaMemcpyDeviceToHost, st));
   B200_CUDA(cudaStreamSynchronize(st));
+  if (*err_host != 0) { set_error("a kernel gave up a bounded wait for its weight copies"); return ETIMEOUT; }
   B200_CUDA(cudaEventElapsedTime(&last_ms, ev0, ev1));
   memcpy(out, ids_host, (size_t)steps * n * sizeof(int32_t));
   for (int i = 0; i < n; i++) past[slots[i]] += steps;

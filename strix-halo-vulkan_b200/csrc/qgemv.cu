@@ -8,38 +8,47 @@ static int g_sm_count = 0;
 template <int TYPE, int EPI, bool DUAL, bool GROUPED>
 static int launch_one(const QGemvParams& p, const TailParams& tp, int max_entries, bool pdl, cudaStream_t st) {
   auto kernel = qgemv_kernel<TYPE, EPI, DUAL, GROUPED>;
-  const size_t smem = qg_smem_bytes(p.K, p.xcols, DUAL);
-  static size_t configured = 0;
-  if (smem > configured) {
-    if (smem > 220 * 1024) { set_error("qgemv: row length too large for shared memory"); return ECAPACITY; }
-    B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = smem;
-  }
   if (g_sm_count == 0) {
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
     B200_CUDA(cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
-  int occ = 1;
-  B200_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, QG_THREADS, smem));
-  if (occ < 1) occ = 1;
   const int nb = p.K / 256;
   const int wpt = nb >= 8 ? 8 : nb >= 4 ? 4 : nb >= 2 ? 2 : 1;
   const int tpc = QG_WARPS / wpt;
   const int tiles = (p.N + 15) / 16;
   const int groups = (tiles + tpc - 1) / tpc;
   const int ny = GROUPED ? max_entries : 1, nz = GROUPED ? 1 : (p.M + QG_MAXCOLS - 1) / QG_MAXCOLS;
-  // persistent CTAs: no more than fit on the device at once, shared between the y / z slices
+  // Two CTAs per SM when the ring fits twice, else one; persistent CTAs share the device
+  // between the y / z slices, and the ring is as deep as a CTA has groups to walk (at most 8).
+  const size_t fixed = qg_fixed_smem(p.K, p.xcols, DUAL), stage = qg_stage_bytes(p.K, p.stride, DUAL);
+  const size_t budget2 = 110 * 1024, budget1 = 220 * 1024;
+  if (fixed + stage > budget1) { set_error("qgemv: row length too large for shared memory"); return ECAPACITY; }
+  const int occ = fixed + 2 * stage <= budget2 ? 2 : 1;
   int cap = g_sm_count * occ / (ny * nz);
   if (cap < 1) cap = 1;
-  dim3 grid(groups < cap ? groups : cap, ny, nz);
+  const int gx = groups < cap ? groups : cap;
+  const int per_cta = (groups + gx - 1) / gx;
+  int ns = (int)(((occ == 2 ? budget2 : budget1) - fixed) / stage);
+  if (ns > QG_MAX_STAGES) ns = QG_MAX_STAGES;
+  if (ns > per_cta) ns = per_cta;
+  if (ns < 1) ns = 1;
+  const size_t smem = fixed + (size_t)ns * stage;
+  static size_t configured = 0;
+  if (smem > configured) {
+    B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(budget1 + 4096)));
+    configured = budget1 + 4096;
+  }
+  QGemvParams pp = p;
+  pp.nstage = ns;
+  dim3 grid(gx, ny, nz);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid; cfg.blockDim = dim3(QG_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
-  B200_CUDA(cudaLaunchKernelEx(&cfg, kernel, p, tp));
+  B200_CUDA(cudaLaunchKernelEx(&cfg, kernel, pp, tp));
   return OK;
 }
 

@@ -49,6 +49,8 @@ struct QGemvParams {
   // plain mode columns: rows [ztile*8, ztile*8+8) of M
   int M;
   int xcols;                 // columns the shared-memory layout is sized for (1..8)
+  int nstage;                // weight pipeline stages in shared memory (1..QG_MAX_STAGES)
+  int* err;                  // device error word: set when a bounded wait gives up
   const int* row_ids;        // optional: plain mode column c reads row row_ids[c] and writes row c
   // activations: fp16 rows in natural order
   const __half* x;
@@ -64,11 +66,18 @@ __host__ __device__ inline int qg_xstride(int K) {
   int pad = (64 - base % 128 + 128) % 128;
   return base + pad;
 }
-__host__ __device__ inline size_t qg_smem_bytes(int K, int xcols, bool dual) {
+constexpr int QG_MAX_STAGES = 8;
+// bytes of one pipeline stage: the tiles one CTA works on per iteration, copied whole
+__host__ __device__ inline size_t qg_stage_bytes(int K, int64_t stride, bool dual) {
+  const int nb = K / 256;
+  const int wpt = nb >= 8 ? 8 : nb >= 4 ? 4 : nb >= 2 ? 2 : 1;
+  return (size_t)(QG_WARPS / wpt) * 16 * (size_t)stride * (dual ? 2 : 1);
+}
+__host__ __device__ inline size_t qg_fixed_smem(int K, int xcols, bool dual) {
   size_t xs = (size_t)xcols * qg_xstride(K);
   size_t sx = (size_t)xcols * (K / 32) * 2 * sizeof(__half);  // hi and lo planes
   size_t red = (size_t)2 * QG_WARPS * 16 * 8 * sizeof(float) * (dual ? 2 : 1);  // double-buffered
-  return xs + ((sx + 15) & ~(size_t)15) + red;
+  return ((xs + ((sx + 15) & ~(size_t)15) + red) + 127) & ~(size_t)127;
 }
 
 // byte offset of activation element k inside a staged row: 4-groups hold [x0,x2,x1,x3]
@@ -99,9 +108,9 @@ struct Q4KRow {
 };
 
 __device__ __forceinline__ void q4k_issue(Q4KRow& r, const uint8_t* blk, int t) {
-  r.hdr = ldg_stream(blk);
-  r.qa = ldg_stream(blk + 16 + 16 * t);
-  r.qb = ldg_stream(blk + 16 + 16 * (t + 4));
+  r.hdr = lds128(blk);
+  r.qa = lds128(blk + 16 + 16 * t);
+  r.qb = lds128(blk + 16 + 16 * (t + 4));
 }
 
 // (scale, min) byte pairs of the thread's two groups: *_a for quad a, *_b for quad b.
@@ -152,10 +161,10 @@ struct Q5KRow {
   uint4 hdr, qh, qa, qb;
 };
 __device__ __forceinline__ void q5k_issue(Q5KRow& r, const uint8_t* blk, int t) {
-  r.hdr = ldg_stream(blk);
-  r.qh = ldg_stream(blk + 16 + 16 * (t & 1));
-  r.qa = ldg_stream(blk + 48 + 16 * t);
-  r.qb = ldg_stream(blk + 48 + 16 * (t + 4));
+  r.hdr = lds128(blk);
+  r.qh = lds128(blk + 16 + 16 * (t & 1));
+  r.qa = lds128(blk + 48 + 16 * t);
+  r.qb = lds128(blk + 48 + 16 * (t + 4));
 }
 // s_even = 2*group. v5 bytes = nibble | bit<<4, then (b0,b2) / (b1,b3) pairs as magic halves.
 __device__ __forceinline__ void q5_unpack_word(uint32_t w, uint32_t qh, int s_even, const ScaleConst& c, uint32_t& lo02, uint32_t& lo13,
@@ -187,11 +196,11 @@ __device__ __forceinline__ void q6k_issue(Q6KRow& r, const uint8_t* row, int nb,
   const uint8_t* qh = row + (size_t)nb * 128 + (size_t)blk * 64;
   const uint8_t* sc = row + (size_t)nb * 192 + (size_t)blk * 16;
   const uint8_t* d = row + (size_t)nb * 208 + (size_t)blk * 2;
-  r.qla = ldg_stream(ql + 16 * t);
-  r.qlb = ldg_stream(ql + 64 + 16 * t);
-  r.qha = ldg_stream(qh + 16 * (t & 1));
-  r.qhb = ldg_stream(qh + 32 + 16 * (t & 1));
-  r.sc = ldg_stream(sc);
+  r.qla = lds128(ql + 16 * t);
+  r.qlb = lds128(ql + 64 + 16 * t);
+  r.qha = lds128(qh + 16 * (t & 1));
+  r.qhb = lds128(qh + 32 + 16 * (t & 1));
+  r.sc = lds128(sc);
   r.d = *reinterpret_cast<const unsigned short*>(d);
 }
 __device__ __forceinline__ int q6_scale(const uint4& sc, int idx) {  // int8 scale idx of the block
@@ -424,9 +433,13 @@ __device__ __forceinline__ void stage_x_f16(const __half* x, int64_t ldx, int K,
 // ---- the kernel ----------------------------------------------------------------------------
 // grid.x: persistent CTAs walking the row-tile groups; grid.y: expert entry (grouped) or 0;
 // grid.z: column tile of 8 activation rows (plain mode).
+//
+// Weights reach the SM as whole tiles (16 consecutive rows are one contiguous run of the
+// checkpoint's own blocks) through cp.async.bulk into a ring of shared-memory stages, each
+// completing on its mbarrier, so many tiles are in flight per SM without holding registers.
 template <int TYPE, int EPI, bool DUAL, bool GROUPED>
 __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, const TailParams tp) {
-  extern __shared__ __align__(16) uint8_t smem[];
+  extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int K = p.K, nb = K / 256;
   const int wpt = nb >= 8 ? 8 : nb >= 4 ? 4 : nb >= 2 ? 2 : 1;  // warps per tile (K-slices)
@@ -436,15 +449,25 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
   uint8_t* xs = smem;
   __half* sxs = reinterpret_cast<__half*>(smem + (size_t)p.xcols * xstride);
   float* red = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sxs) + (((size_t)p.xcols * (K / 32) * 2 * sizeof(__half) + 15) & ~(size_t)15));
+  uint8_t* stages = smem + qg_fixed_smem(K, p.xcols, DUAL);
+  const size_t tile_bytes = (size_t)16 * p.stride;
+  const size_t stage_bytes = (size_t)tpc * tile_bytes * (DUAL ? 2 : 1);
+  const int NS = p.nstage;
   __shared__ float scratch[2 * QG_WARPS];
   __shared__ int col_rows[QG_MAXCOLS], xrows[QG_MAXCOLS];
   __shared__ int is_last;
+  __shared__ __align__(8) uint64_t full_bar[QG_MAX_STAGES];
 
   const int tiles = (p.N + 15) / 16;
   const int ngroups = (tiles + tpc - 1) / tpc;
   const int lt = warp / wpt, kslice = warp % wpt;
 
-  // weight base pointers and the first loads: none of this depends on the producer kernel
+  if (tid == 0) {
+    for (int s = 0; s < NS; s++) mbar_init(&full_bar[s], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
   const uint8_t *wa = nullptr, *wb = nullptr;
   int ncols = 0, col_off = 0;
   bool active = true;
@@ -462,35 +485,35 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
     if (ncols > QG_MAXCOLS) ncols = QG_MAXCOLS;
     col_off = (int)blockIdx.z * QG_MAXCOLS;
   }
-  using Regs = typename RowRegs<TYPE>::type;
-  Regs a0, a1, b0, b1;
-  // step s of this warp: tile group grp0 + (s / bpw) * gridDim.x, super-block kslice + (s % bpw) * wpt
-  const int bpw = (nb - kslice + wpt - 1) / wpt;
-  auto rows_of = [&](int grp, const uint8_t*& r0p, const uint8_t*& r1p, const uint8_t*& s0p, const uint8_t*& s1p) {
-    const int tile = grp * tpc + lt;
-    int r0 = tile * 16 + g, r1 = r0 + 8;
-    if (r0 >= p.N) r0 = p.N - 1;
-    if (r1 >= p.N) r1 = p.N - 1;
-    int seg_r0 = 0;
-    const uint8_t *base = wa, *base2 = wb;
-    if constexpr (!GROUPED) {
-      int s = 0;
-      while (s + 1 < p.nseg && tile * 16 >= p.seg_end[s]) s++;
-      seg_r0 = s > 0 ? p.seg_end[s - 1] : 0;
-      base = p.w[s];
-      if constexpr (DUAL) base2 = p.w2[s];
+  // thread 0 is the producer: one bulk copy per tile (and per tensor when DUAL)
+  auto issue_group = [&](int grp, int s) {
+    uint32_t total = 0;
+    for (int l = 0; l < tpc; l++) {
+      const int tile = grp * tpc + l;
+      if (tile < tiles) total += (uint32_t)(min(16, p.N - tile * 16) * p.stride) * (DUAL ? 2 : 1);
     }
-    r0p = base + (size_t)(r0 - seg_r0) * p.stride; r1p = base + (size_t)(r1 - seg_r0) * p.stride;
-    if constexpr (DUAL) { s0p = base2 + (size_t)(r0 - seg_r0) * p.stride; s1p = base2 + (size_t)(r1 - seg_r0) * p.stride; }
+    mbar_expect_tx(&full_bar[s], total);
+    for (int l = 0; l < tpc; l++) {
+      const int tile = grp * tpc + l;
+      if (tile >= tiles) continue;
+      const uint32_t bytes = (uint32_t)(min(16, p.N - tile * 16) * p.stride);
+      const uint8_t *base = wa, *base2 = wb;
+      int seg_r0 = 0;
+      if constexpr (!GROUPED) {
+        int sg = 0;
+        while (sg + 1 < p.nseg && tile * 16 >= p.seg_end[sg]) sg++;
+        seg_r0 = sg > 0 ? p.seg_end[sg - 1] : 0;
+        base = p.w[sg];
+        if constexpr (DUAL) base2 = p.w2[sg];
+      }
+      uint8_t* dst = stages + (size_t)s * stage_bytes + (size_t)l * tile_bytes * (DUAL ? 2 : 1);
+      bulk_copy_g2s(dst, base + (size_t)(tile * 16 - seg_r0) * p.stride, bytes, &full_bar[s]);
+      if constexpr (DUAL) bulk_copy_g2s(dst + tile_bytes, base2 + (size_t)(tile * 16 - seg_r0) * p.stride, bytes, &full_bar[s]);
+    }
   };
-  const uint8_t *r0p = nullptr, *r1p = nullptr, *s0p = nullptr, *s1p = nullptr;
-  int grp = blockIdx.x;
-  const bool have = active && grp < ngroups && bpw > 0;
-  if (have) {
-    rows_of(grp, r0p, r1p, s0p, s1p);
-    issue_row<TYPE>(a0, r0p, nb, kslice, t);
-    issue_row<TYPE>(a1, r1p, nb, kslice, t);
-    if constexpr (DUAL) { issue_row<TYPE>(b0, s0p, nb, kslice, t); issue_row<TYPE>(b1, s1p, nb, kslice, t); }
+  if (active && tid == 0) {
+    int grp = blockIdx.x;
+    for (int s = 0; s < NS && grp < ngroups; s++, grp += gridDim.x) issue_group(grp, s);
   }
   if constexpr (!GROUPED) pdl_wait();
   pdl_launch();
@@ -505,34 +528,36 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
       xrows[tid] = GROUPED ? id / p.x_div : id;
     }
     __syncthreads();
-    stage_x_f16(reinterpret_cast<const __half*>(p.x), p.ldx, K, p.xcols, xs, sxs, ncols, xrows, xstride);
+    stage_x_f16(p.x, p.ldx, K, p.xcols, xs, sxs, ncols, xrows, xstride);
 
     const bool live = g < ncols;
     const uint8_t* xrow = xs + (size_t)(live ? g : 0) * xstride;
     const __half* sxrow = sxs + (size_t)((t & 1) * p.xcols + (live ? g : 0)) * (K / 32);
-    int buf = 0;
-    for (; grp < ngroups; grp += gridDim.x) {
+    int buf = 0, it = 0;
+    for (int grp = blockIdx.x; grp < ngroups; grp += gridDim.x, it++) {
+      const int s = it % NS;
+      if (!mbar_wait(&full_bar[s], (uint32_t)((it / NS) & 1))) {
+        if (p.err != nullptr && tid == 0) atomicExch(p.err, 1);  // a copy never landed: report and leave
+        return;
+      }
       float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int i = 0; i < bpw; i++) {
-        const int blk = kslice + i * wpt;
-        // prefetch the next step: the next super-block of this tile, or the first of the next group
-        Regs n0, n1, m0, m1;
-        bool more = false;
-        if (i + 1 < bpw) {
-          more = true;
-          issue_row<TYPE>(n0, r0p, nb, blk + wpt, t); issue_row<TYPE>(n1, r1p, nb, blk + wpt, t);
-          if constexpr (DUAL) { issue_row<TYPE>(m0, s0p, nb, blk + wpt, t); issue_row<TYPE>(m1, s1p, nb, blk + wpt, t); }
-        } else if (grp + (int)gridDim.x < ngroups) {
-          more = true;
-          rows_of(grp + gridDim.x, r0p, r1p, s0p, s1p);
-          issue_row<TYPE>(n0, r0p, nb, kslice, t); issue_row<TYPE>(n1, r1p, nb, kslice, t);
-          if constexpr (DUAL) { issue_row<TYPE>(m0, s0p, nb, kslice, t); issue_row<TYPE>(m1, s1p, nb, kslice, t); }
-        }
-        block_accumulate<TYPE>(acc, a0, a1, xrow, sxrow, live, blk, t);
-        if constexpr (DUAL) block_accumulate<TYPE>(acc2, b0, b1, xrow, sxrow, live, blk, t);
-        if (more) {
-          a0 = n0; a1 = n1;
-          if constexpr (DUAL) { b0 = m0; b1 = m1; }
+      const int tile = grp * tpc + lt;
+      if (tile < tiles) {
+        int r0 = g, r1 = g + 8;
+        const int nrows = min(16, p.N - tile * 16);
+        if (r0 >= nrows) r0 = nrows - 1;
+        if (r1 >= nrows) r1 = nrows - 1;
+        const uint8_t* tb = stages + (size_t)s * stage_bytes + (size_t)lt * tile_bytes * (DUAL ? 2 : 1);
+        for (int blk = kslice; blk < nb; blk += wpt) {
+          typename RowRegs<TYPE>::type a0, a1;
+          issue_row<TYPE>(a0, tb + (size_t)r0 * p.stride, nb, blk, t);
+          issue_row<TYPE>(a1, tb + (size_t)r1 * p.stride, nb, blk, t);
+          block_accumulate<TYPE>(acc, a0, a1, xrow, sxrow, live, blk, t);
+          if constexpr (DUAL) {
+            issue_row<TYPE>(a0, tb + tile_bytes + (size_t)r0 * p.stride, nb, blk, t);
+            issue_row<TYPE>(a1, tb + tile_bytes + (size_t)r1 * p.stride, nb, blk, t);
+            block_accumulate<TYPE>(acc2, a0, a1, xrow, sxrow, live, blk, t);
+          }
         }
       }
       // cross-warp reduction in warp order, double-buffered so one barrier per group suffices
@@ -545,6 +570,11 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
         r2[(g + 8) * 8 + 2 * t] = acc2[2]; r2[(g + 8) * 8 + 2 * t + 1] = acc2[3];
       }
       __syncthreads();
+      // every warp is done with stage s: refill it with the group NS iterations ahead
+      if (tid == 0) {
+        const int next = grp + NS * (int)gridDim.x;
+        if (next < ngroups) { fence_proxy_async(); issue_group(next, s); }
+      }
       const float* rb = red + (size_t)buf * RED;
       for (int i = tid; i < tpc * 128; i += QG_THREADS) {
         const int l2 = i >> 7, rc = i & 127, r = rc >> 3, c = rc & 7;
