@@ -215,6 +215,60 @@ static int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem
 // =========================================================================================
 constexpr int RT_ROWS = 8;  // router rows per CTA: one per warp
 
+// softmax + top-k + weights of one token by one warp; a lane owns experts lane + 32*i in registers
+// (reference: llm/moe.go:219-282, 426-443; shaders/llm_moe_route_decode.comp:84-213)
+template <int NPL>
+__device__ __forceinline__ void route_token(const RouterParams& p, int n, int lane) {
+  const int nE = p.nE, used = p.used;
+  float pv[NPL];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < NPL; i++) {
+    const int e = lane + 32 * i;
+    pv[i] = e < nE ? __ldcg(p.logits + (size_t)n * nE + e) : -INFINITY;
+    mx = fmaxf(mx, pv[i]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < NPL; i++) { pv[i] = lane + 32 * i < nE ? expf(pv[i] - mx) : 0.f; sum += pv[i]; }
+  sum = warp_sum(sum);
+  const float inv = 1.0f / sum;
+#pragma unroll
+  for (int i = 0; i < NPL; i++) {
+    pv[i] = lane + 32 * i < nE ? pv[i] * inv : -1.f;
+    if (p.probs != nullptr && lane + 32 * i < nE) p.probs[(size_t)n * nE + lane + 32 * i] = pv[i];
+  }
+  // top-k by descending probability, ties to the lower index (llm/moe.go:249-252)
+  float wsum = 0.f, last_p = 0.f, myw = 0.f;
+  for (int k = 0; k <= used; k++) {
+    float bv = pv[0]; int bi = 0;
+#pragma unroll
+    for (int i = 1; i < NPL; i++) if (pv[i] > bv) { bv = pv[i]; bi = i; }
+    bi = lane + 32 * bi;
+    if (bv < 0.f) bi = 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (k == used) {
+      if (lane == 0 && p.margin) p.margin[n] = last_p > 0.f ? (last_p - fmaxf(bv, 0.f)) / last_p : 0.f;
+      break;
+    }
+    if ((bi & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < NPL; i++) if (i == (bi >> 5)) pv[i] = -1.f;
+    }
+    if (lane == k) { myw = bv; p.topk[(size_t)n * used + k] = bi; }
+    wsum += bv; last_p = bv;
+  }
+  // normalise the weights (llm/moe.go:256-282)
+  if (wsum < 6.103515625e-5f) wsum = 6.103515625e-5f;
+  if (lane < used) p.topk_w[(size_t)n * (used + 1) + lane] = myw / wsum;
+}
+
 __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   __shared__ int is_last;
   __shared__ int counts[1025], offs[1025], eoff[1025];
@@ -283,52 +337,8 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   if (tid == 0) *p.ticket = 0;
   const int nE = p.nE, used = p.used;
   for (int n = warp; n < M; n += 8) {
-    // softmax (llm/moe.go:426-443); lane owns experts lane + 32*i, kept in registers
-    float pv[32];
-    float mx = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < 32; i++) {
-      const int e = lane + 32 * i;
-      pv[i] = e < nE ? __ldcg(p.logits + (size_t)n * nE + e) : -INFINITY;
-      mx = fmaxf(mx, pv[i]);
-    }
-    mx = warp_max(mx);
-    float sum = 0.f;
-#pragma unroll
-    for (int i = 0; i < 32; i++) { pv[i] = lane + 32 * i < nE ? expf(pv[i] - mx) : 0.f; sum += pv[i]; }
-    sum = warp_sum(sum);
-    const float inv = 1.0f / sum;
-#pragma unroll
-    for (int i = 0; i < 32; i++) {
-      pv[i] = lane + 32 * i < nE ? pv[i] * inv : -1.f;
-      if (p.probs != nullptr && lane + 32 * i < nE) p.probs[(size_t)n * nE + lane + 32 * i] = pv[i];
-    }
-    // top-k by descending probability, ties to the lower index (llm/moe.go:249-252)
-    float wsum = 0.f, last_p = 0.f, myw = 0.f;
-    for (int k = 0; k <= used; k++) {
-      float bv = -1.f; int bi = 0x7fffffff;
-#pragma unroll
-      for (int i = 0; i < 32; i++) if (pv[i] > bv) { bv = pv[i]; bi = lane + 32 * i; }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-      }
-      if (k == used) {
-        if (lane == 0 && p.margin) p.margin[n] = last_p > 0.f ? (last_p - fmaxf(bv, 0.f)) / last_p : 0.f;
-        break;
-      }
-      if ((bi & 31) == lane) {
-#pragma unroll
-        for (int i = 0; i < 32; i++) if (i == (bi >> 5)) pv[i] = -1.f;
-      }
-      if (lane == k) { myw = bv; p.topk[(size_t)n * used + k] = bi; }
-      wsum += bv; last_p = bv;
-    }
-    // normalise the weights (llm/moe.go:256-282)
-    if (wsum < 6.103515625e-5f) wsum = 6.103515625e-5f;
-    if (lane < used) p.topk_w[(size_t)n * (used + 1) + lane] = myw / wsum;
+    if (nE <= 512) route_token<16>(p, n, lane);
+    else route_token<32>(p, n, lane);
   }
   __threadfence_block();
   __syncthreads();
@@ -446,8 +456,15 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(128) dn_step_kernel(
   const float4 cwk = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch_k * 4);
   const float4 cwv = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch_v * 4);
   const float a_h = p.ssm_a[h], dtb = p.dt_bias[h];
-  pdl_wait();
-  pdl_launch();
+  // everything that does not depend on the producer kernel is fetched before waiting for it:
+  // the first token's alpha / beta weight slices, the conv history and the state rows
+  float4 pwa[4], pwb[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int k = tid * 4 + 512 * i;
+    pwa[i] = k < p.H ? *reinterpret_cast<const float4*>(p.alpha_w + (size_t)h * p.H + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+    pwb[i] = k < p.H ? *reinterpret_cast<const float4*>(p.beta_w + (size_t)h * p.H + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   // conv history: the three inputs before pos0, zeros before the sequence start
   // Every CTA keeps a private ring of its own 288 conv inputs (q 128 | k 128 | v 32), indexed
   // by position, so no CTA ever reads what another one writes.
@@ -468,6 +485,8 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(128) dn_step_kernel(
 #pragma unroll
   for (int r = 0; r < 8; r++) s[r] = *reinterpret_cast<const float4*>(S + (size_t)(j0 + r) * D + lane * 4);
   const float oscale = 1.0f / sqrtf((float)D);
+  pdl_wait();
+  pdl_launch();
 
   for (int i = 0; i < sq.n; i++) {
     const int row = sq.row0 + i, pos = sq.pos0 + i;
@@ -475,14 +494,22 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(128) dn_step_kernel(
     // alpha / beta: F32 weights against the fp16-rounded block input
     const __half* xn = p.xn + (size_t)row * H;
     float pa = 0.f, pb = 0.f;
-    for (int k = tid * 4; k < H; k += 512) {
-      float4 wa = *reinterpret_cast<const float4*>(p.alpha_w + (size_t)h * H + k);
-      float4 wb = *reinterpret_cast<const float4*>(p.beta_w + (size_t)h * H + k);
+    auto ab_dot = [&](int k, const float4& wa, const float4& wb) {
       const __half2 x01 = *reinterpret_cast<const __half2*>(xn + k), x23 = *reinterpret_cast<const __half2*>(xn + k + 2);
       const float2 f01 = __half22float2(x01), f23 = __half22float2(x23);
       pa += wa.x * f01.x + wa.y * f01.y + wa.z * f23.x + wa.w * f23.y;
       pb += wb.x * f01.x + wb.y * f01.y + wb.z * f23.x + wb.w * f23.y;
+    };
+#pragma unroll
+    for (int ki = 0; ki < 4; ki++) {
+      const int k = tid * 4 + 512 * ki;
+      if (k < H) {
+        if (i == 0) ab_dot(k, pwa[ki], pwb[ki]);
+        else ab_dot(k, *reinterpret_cast<const float4*>(p.alpha_w + (size_t)h * H + k), *reinterpret_cast<const float4*>(p.beta_w + (size_t)h * H + k));
+      }
     }
+    for (int k = tid * 4 + 2048; k < H; k += 512)
+      ab_dot(k, *reinterpret_cast<const float4*>(p.alpha_w + (size_t)h * H + k), *reinterpret_cast<const float4*>(p.beta_w + (size_t)h * H + k));
     // conv + SiLU for q, k (whole head) and this CTA's 32 v channels
     const float cq = pr[ch_q], ck = pr[ch_k], cv = pr[ch_v];
     const float q = silu_acc(hq[0] * cwq.x + hq[1] * cwq.y + hq[2] * cwq.z + cq * cwq.w);
@@ -625,17 +652,19 @@ int launch_attn_pack(const AttnParams& p, bool pdl, cudaStream_t st) {
 // =========================================================================================
 // Split-KV decode attention (reference: llm/attn.go:190-217, 444-496;
 // shaders/llm_attn_wmma.comp -DSPLITK, llm_attn_combine.comp). grid (nsplit, Hkv, M):
-// a CTA of 4 warps covers `split_cells` cells of one KV head for the G query heads that
+// a CTA of 8 warps covers `split_cells` cells of one KV head for the G query heads that
 // share it; a lane owns hd/32 dims. The last CTA of a (row, kv head) merges the splits,
 // applies sigmoid(gate) and writes the fp16 context.
 // =========================================================================================
+constexpr int AT_WARPS = 8, AT_THREADS = AT_WARPS * 32;
 template <int DPL, int G>  // dims per lane, query heads per kv head
-__global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
+__global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnParams p) {
   const int hd = DPL * 32;
   const int split = blockIdx.x, kvh = blockIdx.y, n = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  __shared__ float sm_m[4][G], sm_l[4][G];
-  __shared__ float sm_o[4][G][DPL * 32];
+  __shared__ float sm_m[AT_WARPS][G], sm_l[AT_WARPS][G];
+  extern __shared__ __align__(16) float sm_o_dyn[];  // [AT_WARPS][G][hd]
+  float (*sm_o)[G][DPL * 32] = reinterpret_cast<float (*)[G][DPL * 32]>(sm_o_dyn);
   __shared__ int is_last;
   pdl_wait();
   pdl_launch();
@@ -654,7 +683,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
   const __half* kc = p.kcache + (size_t)slot * p.slot_stride + (size_t)kvh * hd + lane * DPL;
   const __half* vc = p.vcache + (size_t)slot * p.slot_stride + (size_t)kvh * hd + lane * DPL;
   const size_t cell_stride = (size_t)p.Hkv * hd;
-  for (int c = c0 + warp; c < c1; c += 4) {
+  for (int c = c0 + warp; c < c1; c += AT_WARPS) {
     float kf[DPL], vf[DPL];
     const __half* kp = kc + (size_t)c * cell_stride;
     const __half* vp = vc + (size_t)c * cell_stride;
@@ -688,7 +717,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
       m[hh] = mn;
     }
   }
-  // merge the four warps, then publish this split's partial
+  // merge the warps, then publish this split's partial
 #pragma unroll
   for (int hh = 0; hh < G; hh++) {
     if (lane == 0) { sm_m[warp][hh] = m[hh]; sm_l[warp][hh] = l[hh]; }
@@ -697,12 +726,14 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
   }
   __syncthreads();
   const int PW = hd + 2;
-  for (int i = tid; i < G * hd; i += 128) {
+  for (int i = tid; i < G * hd; i += AT_THREADS) {
     const int hh = i / hd, d = i - hh * hd;
-    float mm = fmaxf(fmaxf(sm_m[0][hh], sm_m[1][hh]), fmaxf(sm_m[2][hh], sm_m[3][hh]));
+    float mm = sm_m[0][hh];
+#pragma unroll
+    for (int w = 1; w < AT_WARPS; w++) mm = fmaxf(mm, sm_m[w][hh]);
     float ov = 0.f, lv = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; w++) {
+    for (int w = 0; w < AT_WARPS; w++) {
       const float f = sm_m[w][hh] == -INFINITY ? 0.f : expf(sm_m[w][hh] - mm);
       ov += sm_o[w][hh][d] * f; lv += sm_l[w][hh] * f;
     }
@@ -720,10 +751,10 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
   if (tid == 0) *ticket = 0;
   const int nlive = (ncell + p.split_cells - 1) / p.split_cells;
   // merge: O = sum_s O_s * exp(m_s - m*), l likewise (reference: shaders/llm_attn_combine.comp:70-102)
-  float* fac = &sm_o[0][0][0];            // [G][nlive] factors, reusing the warp-merge buffer
+  float* fac = sm_o_dyn;                  // [G][nlive] factors, reusing the warp-merge buffer
   __shared__ float mm_s[G], ll_s[G];
   __syncthreads();
-  for (int i = tid; i < G * nlive; i += 128) {
+  for (int i = tid; i < G * nlive; i += AT_THREADS) {
     const int hh = i / nlive, sp = i - hh * nlive;
     fac[i] = __ldcg(p.partial + (((size_t)n * p.Hq + kvh * G + hh) * p.nsplit + sp) * PW + hd);
   }
@@ -734,7 +765,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
     mm_s[tid] = mm;
   }
   __syncthreads();
-  for (int i = tid; i < G * nlive; i += 128) fac[i] = expf(fac[i] - mm_s[i / nlive]);
+  for (int i = tid; i < G * nlive; i += AT_THREADS) fac[i] = expf(fac[i] - mm_s[i / nlive]);
   __syncthreads();
   if (tid < G) {
     float lv = 0.f;
@@ -744,7 +775,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
   }
   __syncthreads();
   const int gate_off = hd;  // per head: hd query dims then hd gate dims
-  for (int i = tid; i < G * hd; i += 128) {
+  for (int i = tid; i < G * hd; i += AT_THREADS) {
     const int hh = i / hd, d = i - hh * hd, head = kvh * G + hh;
     const float* part = p.partial + ((size_t)n * p.Hq + head) * p.nsplit * PW;
     float ov = 0.f;
@@ -754,18 +785,27 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(AttnParams p) {
   }
 }
 
+template <int DPL, int G>
+static int launch_attn_t(const AttnParams& p, bool pdl, cudaStream_t st) {
+  const size_t smem = (size_t)AT_WARPS * G * DPL * 32 * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    B200_CUDA(cudaFuncSetAttribute(attn_decode_kernel<DPL, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  return launch_k(attn_decode_kernel<DPL, G>, dim3(p.nsplit, p.Hkv, p.M), dim3(AT_THREADS), smem, pdl, st, p);
+}
+
 int launch_attn_decode(const AttnParams& p, bool pdl, cudaStream_t st) {
   const int G = p.Hq / p.Hkv;
-  if (G * p.nsplit > 4 * G * p.hd) { set_error("attn_decode: too many splits for the merge buffer"); return ECAPACITY; }
-  dim3 grid(p.nsplit, p.Hkv, p.M), block(128);
-  if (p.hd == 256 && G == 8) return launch_k(attn_decode_kernel<8, 8>, grid, block, 0, pdl, st, p);
-  if (p.hd == 128 && G == 4) return launch_k(attn_decode_kernel<4, 4>, grid, block, 0, pdl, st, p);
-  if (p.hd == 128 && G == 8) return launch_k(attn_decode_kernel<4, 8>, grid, block, 0, pdl, st, p);
-  if (p.hd == 256 && G == 4) return launch_k(attn_decode_kernel<8, 4>, grid, block, 0, pdl, st, p);
+  if (p.nsplit > AT_WARPS * p.hd) { set_error("attn_decode: too many splits for the merge buffer"); return ECAPACITY; }
+  if (p.hd == 256 && G == 8) return launch_attn_t<8, 8>(p, pdl, st);
+  if (p.hd == 128 && G == 4) return launch_attn_t<4, 4>(p, pdl, st);
+  if (p.hd == 128 && G == 8) return launch_attn_t<4, 8>(p, pdl, st);
+  if (p.hd == 256 && G == 4) return launch_attn_t<8, 4>(p, pdl, st);
   set_error("attn_decode: unsupported head_dim / group size");
   return EINVAL_;
 }
-
 // =========================================================================================
 // Greedy sampling: argmax with ties to the lowest id (reference: llm/sample.go:359-367)
 // =========================================================================================

@@ -267,7 +267,7 @@ template <int TYPE>
 __device__ __forceinline__ void block_accumulate(float (&acc)[4], const typename RowRegs<TYPE>::type& r0, const typename RowRegs<TYPE>::type& r1,
                                                  const uint8_t* xrow, const __half* sxrow, bool live, int blk, int t) {
   const int th = t >> 1, hb = t & 1;
-  float C[4] = {0.f, 0.f, 0.f, 0.f};
+  float C[4] = {0.f, 0.f, 0.f, 0.f}, C2[4] = {0.f, 0.f, 0.f, 0.f};
   if constexpr (TYPE == T_Q4_K || TYPE == T_Q5_K) {
     uint32_t sca0, ma0, scb0, mb0, sca1, ma1, scb1, mb1;
     k4_scales(r0.hdr, th, sca0, ma0, scb0, mb0);
@@ -279,7 +279,7 @@ __device__ __forceinline__ void block_accumulate(float (&acc)[4], const typename
       quad_mmas(C, xrow, live, ka, 32, r0.qa, r1.qa,
                 [&](int, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q4_unpack_word(w, ca0, a, b, c, d); },
                 [&](int, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q4_unpack_word(w, ca1, a, b, c, d); });
-      quad_mmas(C, xrow, live, kb, 32, r0.qb, r1.qb,
+      quad_mmas(C2, xrow, live, kb, 32, r0.qb, r1.qb,
                 [&](int, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q4_unpack_word(w, cb0, a, b, c, d); },
                 [&](int, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q4_unpack_word(w, cb1, a, b, c, d); });
     } else {
@@ -288,7 +288,7 @@ __device__ __forceinline__ void block_accumulate(float (&acc)[4], const typename
       quad_mmas(C, xrow, live, ka, 32, r0.qa, r1.qa,
                 [&](int i, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q5_unpack_word(w, h0[i], sa, ca0, a, b, c, d); },
                 [&](int i, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q5_unpack_word(w, h1[i], sa, ca1, a, b, c, d); });
-      quad_mmas(C, xrow, live, kb, 32, r0.qb, r1.qb,
+      quad_mmas(C2, xrow, live, kb, 32, r0.qb, r1.qb,
                 [&](int i, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q5_unpack_word(w, h0[i], sb, cb0, a, b, c, d); },
                 [&](int i, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q5_unpack_word(w, h1[i], sb, cb1, a, b, c, d); });
     }
@@ -302,6 +302,8 @@ __device__ __forceinline__ void block_accumulate(float (&acc)[4], const typename
       b1 = *reinterpret_cast<const uint32_t*>(p + 4 + 2 * th);
     }
     mma16816(Cm, am, b0, b1);
+#pragma unroll
+    for (int i = 0; i < 4; i++) C[i] += C2[i];
     const float d0 = h2f_lo(r0.hdr.x), dm0 = h2f_hi(r0.hdr.x), d1 = h2f_lo(r1.hdr.x), dm1 = h2f_hi(r1.hdr.x);
     acc[0] = fmaf(-dm0, Cm[0], fmaf(d0, C[0], acc[0]));
     acc[1] = fmaf(-dm0, Cm[1], fmaf(d0, C[1], acc[1]));
@@ -321,9 +323,11 @@ __device__ __forceinline__ void block_accumulate(float (&acc)[4], const typename
     quad_mmas(C, xrow, live, ka, 64, r0.qla, r1.qla,
               [&](int i, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q6_unpack_word(w, ha0[i], th, sla0, sha0, a, b, c, d); },
               [&](int i, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q6_unpack_word(w, ha1[i], th, sla1, sha1, a, b, c, d); });
-    quad_mmas(C, xrow, live, kb, 64, r0.qlb, r1.qlb,
+    quad_mmas(C2, xrow, live, kb, 64, r0.qlb, r1.qlb,
               [&](int i, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q6_unpack_word(w, hb0[i], th, slb0, shb0, a, b, c, d); },
               [&](int i, uint32_t w, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) { q6_unpack_word(w, hb1[i], th, slb1, shb1, a, b, c, d); });
+#pragma unroll
+    for (int i = 0; i < 4; i++) C[i] += C2[i];
     const float d0 = __half2float(__ushort_as_half((unsigned short)r0.d)), d1 = __half2float(__ushort_as_half((unsigned short)r1.d));
     acc[0] = fmaf(d0, C[0], acc[0]);
     acc[1] = fmaf(d0, C[1], acc[1]);
