@@ -136,6 +136,16 @@ int32_t b200_draft_rewind(b200_graph* g, int32_t past);
 int32_t b200_dequantize(uint32_t type, const void* host_data, int64_t n, float* host_out);
 /* y[m][rows] = W[rows][k] . fp16(x[m][k]) through the fused K-quant projection kernel. */
 int32_t b200_qgemv(uint32_t type, const void* host_w, int64_t rows, int64_t k, const float* host_x, int32_t m, float* host_y);
+/* No counterpart in the reference. The same projection for callers that cannot allocate device
+ * memory (inside a stream capture, on a thread that may not take the allocator's lock, or under
+ * a fixed memory budget): all pointers are DEVICE pointers the caller already owns, and the fp16
+ * staging of the activations lives in a 256 KiB file-scope device array that every GPU loading
+ * the library holds until exit. Limits: Q4_K / Q5_K weights in checkpoint block layout, 16-byte
+ * aligned; m <= 8 rows; k a multiple of 256, at most 16384; larger sizes are refused. The first
+ * call on a device looks the array's address up (make it before any stream capture). All calls
+ * share the array, so calls that overlap on the device race; the call returns after its work is
+ * done and calls no cudaMalloc / cudaFree. */
+int32_t b200_qgemv_static(uint32_t type, const void* dev_w, int64_t rows, int64_t k, const float* dev_x, int32_t m, float* dev_y);
 /* The repo's quantiser on the device (llm/quantk.go:87-179): rows x k f32 -> GGUF blocks. */
 int32_t b200_quantize(uint32_t type, const float* host_src, int64_t rows, int64_t k, void* host_dst);
 

@@ -203,6 +203,11 @@ int32_t b200_qgemv(uint32_t type, const void* host_w, int64_t rows, int64_t k, c
   return s;
 }
 
+int32_t b200_qgemv_static(uint32_t type, const void* dev_w, int64_t rows, int64_t k, const float* dev_x, int32_t m, float* dev_y) {
+  B200_TRY(need_device());
+  return qgemv_static(type, dev_w, rows, k, dev_x, m, dev_y);
+}
+
 int32_t b200_quantize(uint32_t type, const float* host_src, int64_t rows, int64_t k, void* host_dst) {
   B200_TRY(need_device());
   const int64_t rb = gguf_row_bytes(type, k);

@@ -43,4 +43,7 @@ int load_gguf_into(const char* path, int device, Model* m);
 int synth_fill(float* dst, int64_t n, uint64_t seed, int rule, float p0, float p1, cudaStream_t st);
 int quantize_rows_device(uint32_t type, const float* src, int64_t rows, int64_t k, uint8_t* gguf_dst, cudaStream_t st);
 
+// projection through a file-scope device staging array (static_scratch.cu)
+int qgemv_static(uint32_t type, const void* dev_w, int64_t rows, int64_t k, const float* dev_x, int32_t m, float* dev_y);
+
 }  // namespace b200

@@ -73,6 +73,7 @@ SYMBOLS = {
     "b200_draft_rewind": (I32, [P, I32]),
     "b200_dequantize": (I32, [U32, P, I64, P]),
     "b200_qgemv": (I32, [U32, P, I64, I64, P, I32, P]),
+    "b200_qgemv_static": (I32, [U32, P, I64, I64, P, I32, P]),
     "b200_quantize": (I32, [U32, P, I64, I64, P]),
 }
 
