@@ -116,6 +116,12 @@ float b200_graph_last_device_ms(const b200_graph* g);
 /* Kernel launches issued by the last pass (or per step of the last generate_greedy). */
 int32_t b200_graph_last_launches(const b200_graph* g);
 
+/* Phase timestamps of the last pass, when the process was started with B200_TIMELINE set (the
+ * reference keeps a GPU timestamp per dispatch, vk/shim.h:222-229): dst [launch][8] globaltimer ns,
+ * phases 0 start, 1 producer done, 2 activations staged, 3 first weights landed, 4 main loop done,
+ * 5 tail start, 6 tail end. Returns the number of launches written, 0 when off. */
+int32_t b200_graph_timeline(b200_graph* g, int64_t* dst, int32_t max_launches);
+
 /* Trace of the last pass (opts.trace = 1): what = 0 residual after the token mixer
  * [n_layer][rows][n_embd], 1 residual after the MoE block, 2 routed experts
  * [n_layer][rows][used] (int32), 3 routing weights [n_layer][rows][used+1], 4 top-k margin

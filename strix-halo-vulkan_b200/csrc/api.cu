@@ -136,6 +136,15 @@ int32_t b200_graph_generate_greedy(b200_graph* g, const int32_t* slots, const in
 }
 float b200_graph_last_device_ms(const b200_graph* g) { return g ? g->g.last_ms : 0.f; }
 int32_t b200_graph_last_launches(const b200_graph* g) { return g ? g->g.last_launches : 0; }
+int32_t b200_graph_timeline(b200_graph* g, int64_t* dst, int32_t max_launches) {
+  if (!g || !dst) return -1;
+  if (!g->g.timeline) return 0;
+  cudaSetDevice(g->g.m->device);
+  int n = g->g.last_launches < g->g.timeline_cap ? g->g.last_launches : g->g.timeline_cap;
+  if (n > max_launches) n = max_launches;
+  if (cudaMemcpy(dst, g->g.timeline, (size_t)n * 8 * sizeof(long long), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  return n;
+}
 int64_t b200_graph_trace(b200_graph* g, int32_t what, void* dst, int64_t nbytes) { if (!g || !dst) return -EINVAL_; return g->g.trace(what, dst, nbytes); }
 
 int32_t b200_draft_rows(b200_graph* g, const float* hs, const int32_t* ids, int32_t n, int32_t vocab_k, const float** residual, const float** logits) {

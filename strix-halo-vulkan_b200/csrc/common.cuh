@@ -50,7 +50,21 @@ const char* last_error();
     if (_s != b200::OK) return _s;       \
   } while (0)
 
+// Optional per-launch phase timestamps (the reference keeps GPU timestamps per dispatch:
+// vk/shim.h:222-229, llm/graph.go:527-589). buf == nullptr switches them off.
+struct Timeline {
+  long long* buf;  // [launch][8] globaltimer nanoseconds
+  int slot;
+};
+
 #ifdef __CUDACC__
+__device__ __forceinline__ void tl_mark(const Timeline& t, int phase, bool any_block = false) {
+  if (t.buf != nullptr && threadIdx.x == 0 && (any_block || (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0))) {
+    long long v;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
+    t.buf[t.slot * 8 + phase] = v;
+  }
+}
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + __expf(-x)); }
 __device__ __forceinline__ float sigmoid_acc(float x) { return 1.0f / (1.0f + expf(-x)); }
 

@@ -5,6 +5,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 namespace b200 {
@@ -126,6 +127,7 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
     B200_TRY(dalloc(&tr_mid, (size_t)nl * MR * H)); B200_TRY(dalloc(&tr_out, (size_t)nl * MR * H));
     B200_TRY(dalloc(&tr_topk, (size_t)nl * MR * used)); B200_TRY(dalloc(&tr_w, (size_t)nl * MR * slots1)); B200_TRY(dalloc(&tr_margin, (size_t)nl * MR));
   }
+  if (getenv("B200_TIMELINE") != nullptr) { timeline_cap = 1024; B200_TRY(dalloc(&timeline, (size_t)timeline_cap * 8)); }
   B200_CUDA(cudaDeviceSynchronize());
   return OK;
 }
@@ -149,10 +151,12 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
   launches = 0;
   bool first = true;
   auto pdl = [&]() { bool p = !first; first = false; launches++; return p; };
+  // timestamps slot of the NEXT launch (launches counts the ones already issued)
+  auto tl = [&]() { Timeline t{timeline, launches < timeline_cap ? launches : 0}; if (launches >= timeline_cap) t.buf = nullptr; return t; };
   auto base = [&](const DTensor& w, int K, int N, const __half* x, int ldx) {
     QGemvParams p{};
     p.w[0] = w.data; p.seg_end[0] = N; p.nseg = 1; p.stride = w.stride; p.K = K; p.N = N; p.M = M; p.xcols = xcols; p.x_div = 1;
-    p.x = x; p.ldx = ldx; p.err = err_flag;
+    p.x = x; p.ldx = ldx; p.err = err_flag; p.tl = tl();
     return p;
   };
   auto tail = [&](int mode, const DTensor& gamma) {
@@ -196,7 +200,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       d.state = dn_state[di]; d.state_slot_stride = state_slot_stride; d.ring = dn_ring[di]; d.ring_slot_stride = ring_slot_stride;
       d.seqs = seqs; d.n_seq = n_seq; d.norm_w = (const float*)L.ssm_norm.data; d.y16 = y16;
       d.mid = f.spec ? dn_mid[di] : nullptr; d.mid_stride = state_slot_stride; d.mid_seq_stride = mid_seq_stride;
-      d.H = H; d.Hk = c.dn_heads_k; d.Hv = c.dn_heads_v; d.D = D; d.conv = c.dn_conv; d.eps = c.eps;
+      d.H = H; d.Hk = c.dn_heads_k; d.Hv = c.dn_heads_v; d.D = D; d.conv = c.dn_conv; d.eps = c.eps; d.tl = tl();
       B200_TRY(launch_dn_step(d, pdl(), st));
       QGemvParams q = base(L.ssm_out, vw, H, y16, vw);
       q.y = h; q.ldy = H;
@@ -225,6 +229,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       a.M = M; a.Hq = c.n_head; a.Hkv = c.n_head_kv; a.hd = hd; a.rope_dims = std::min(c.rope_dims, hd); a.n_kv = o.n_kv;
       a.split_cells = split_cells; a.nsplit = nsplit; a.eps = c.eps; a.rope_off = f.draft ? 1 : 0;
       B200_TRY(launch_attn_pack(a, pdl(), st));
+      a.tl = tl();
       B200_TRY(launch_attn_decode(a, pdl(), st));
       QGemvParams q = base(L.o, qw, H, ctx16, qw);
       q.y = h; q.ldy = H;
@@ -235,7 +240,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     RouterParams r{};
     r.xn = xn16; r.router = L.router; r.sh_gate = (const float*)L.sh_gate_inp.data;
     r.M = M; r.H = H; r.nE = c.n_expert; r.used = used; r.logits = r_logits; r.probs = nullptr; r.topk = topk; r.topk_w = topk_w;
-    r.margin = margin; r.entries = entries; r.n_entries = n_entries; r.cols = cols; r.ticket = r_ticket; r.max_entries = max_entries;
+    r.tl = tl(); r.margin = margin; r.entries = entries; r.n_entries = n_entries; r.cols = cols; r.ticket = r_ticket; r.max_entries = max_entries;
     B200_TRY(launch_router(r, pdl(), st));
     const int ne = max_entries_for(M);
     QGemvParams p = base(L.gate_exps, H, c.ffn_expert, xn16, H);

@@ -55,6 +55,8 @@ struct Graph {
   int last_rows = 0;
   // replay
   std::map<int, cudaGraphExec_t> decode_graphs, greedy_graphs;
+  long long* timeline = nullptr;  // [launch][8] phase timestamps when B200_TIMELINE is set
+  int timeline_cap = 0;
   int launches = 0, last_launches = 0, draft_vocab = 0, resid_off = 0;
   float last_ms = 0.f;
   // checkpoints: DeltaNet state + rings of a slot at a token boundary

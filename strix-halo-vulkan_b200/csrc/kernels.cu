@@ -274,6 +274,7 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   __shared__ int counts[1025], offs[1025], eoff[1025];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, H = p.H, M = p.M;
   const int row = blockIdx.x * RT_ROWS + warp;  // of the nE + 1 outputs; the last is the shared-expert gate
+  tl_mark(p.tl, 0);
   const bool q8 = p.router.type == T_Q8_0 && H % 512 == 0 && H <= 4096;
   // the row's weights do not depend on the producer kernel: fetch them first
   uint4 wq[8]; float wd[8];
@@ -288,6 +289,7 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   }
   pdl_wait();
   pdl_launch();
+  tl_mark(p.tl, 1);
   if (row <= p.nE) {
     for (int n = 0; n < M; n++) {
       const __half* x = p.xn + (size_t)n * H;
@@ -327,6 +329,7 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
       }
     }
   }
+  tl_mark(p.tl, 4);
   // the last CTA to finish routes every token and builds the expert work list
   __threadfence();
   __syncthreads();
@@ -335,6 +338,7 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   if (!is_last) return;
   __threadfence();
   if (tid == 0) *p.ticket = 0;
+  tl_mark(p.tl, 5, true);
   const int nE = p.nE, used = p.used;
   for (int n = warp; n < M; n += 8) {
     if (nE <= 512) route_token<16>(p, n, lane);
@@ -346,6 +350,7 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   if (M == 1) {
     if (tid < used) { p.entries[tid] = make_int4(p.topk[tid], tid, 1, 0); p.cols[tid] = tid; }
     if (tid == used) { p.entries[used] = make_int4(-1, used, 1, 0); p.cols[used] = used; *p.n_entries = used + 1; }
+    tl_mark(p.tl, 6, true);
     return;
   }
   for (int i = tid; i <= nE; i += 256) counts[i] = 0;
@@ -485,8 +490,10 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(128) dn_step_kernel(
 #pragma unroll
   for (int r = 0; r < 8; r++) s[r] = *reinterpret_cast<const float4*>(S + (size_t)(j0 + r) * D + lane * 4);
   const float oscale = 1.0f / sqrtf((float)D);
+  tl_mark(p.tl, 0);
   pdl_wait();
   pdl_launch();
+  tl_mark(p.tl, 1);
 
   for (int i = 0; i < sq.n; i++) {
     const int row = sq.row0 + i, pos = sq.pos0 + i;
@@ -595,6 +602,7 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(128) dn_step_kernel(
     for (int r = 0; r < 8; r++) *reinterpret_cast<float4*>(S + (size_t)(j0 + r) * D + lane * 4) = s[r];
   }
   cluster.sync();  // no CTA may leave while a peer can still read its shared memory
+  tl_mark(p.tl, 4);
 }
 
 int launch_dn_step(const DnStepParams& p, bool pdl, cudaStream_t st) {
@@ -666,8 +674,10 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnParams p) {
   extern __shared__ __align__(16) float sm_o_dyn[];  // [AT_WARPS][G][hd]
   float (*sm_o)[G][DPL * 32] = reinterpret_cast<float (*)[G][DPL * 32]>(sm_o_dyn);
   __shared__ int is_last;
+  tl_mark(p.tl, 0);
   pdl_wait();
   pdl_launch();
+  tl_mark(p.tl, 1);
   const int pos = p.row_pos[n], slot = p.row_slot[n];
   const int ncell = pos + 1;
   const int c0 = split * p.split_cells, c1 = min(ncell, c0 + p.split_cells);
@@ -741,6 +751,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnParams p) {
     part[d] = ov;
     if (d == 0) { part[hd] = mm; part[hd + 1] = lv; }
   }
+  tl_mark(p.tl, 4);
   __threadfence();
   __syncthreads();
   int* ticket = p.tickets + (size_t)n * p.Hkv + kvh;
@@ -783,6 +794,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnParams p) {
     const float gate = p.proj[(size_t)n * p.ldp + head * 2 * hd + gate_off + d];
     p.ctx16[(size_t)n * p.Hq * hd + head * hd + d] = __float2half_rn(ov / ll_s[hh] * sigmoid_acc(gate));
   }
+  tl_mark(p.tl, 6, true);
 }
 
 template <int DPL, int G>

@@ -49,6 +49,7 @@ struct RouterParams {
   int4* entries; int* n_entries; int* cols;   // expert work list for the grouped kernels
   int* ticket;
   int max_entries;
+  Timeline tl;
 };
 int launch_router(const RouterParams& p, bool pdl, cudaStream_t st);
 
@@ -69,6 +70,7 @@ struct DnStepParams {
   int64_t mid_stride, mid_seq_stride;        // floats between consecutive rows / sequences of mid
   int H, Hk, Hv, D, conv;
   float eps;
+  Timeline tl;
 };
 constexpr int DN_RING = 8;      // positions kept per ring
 constexpr int DN_RING_W = 288;  // conv inputs per CTA: q 128 | k 128 | v 32
@@ -88,6 +90,7 @@ struct AttnParams {
   int M, Hq, Hkv, hd, rope_dims, n_kv, split_cells, nsplit;
   int rope_off;                              // rotary position = cell + rope_off (1 for the draft layer)
   float eps;
+  Timeline tl;
 };
 int launch_attn_pack(const AttnParams& p, bool pdl, cudaStream_t st);
 int launch_attn_decode(const AttnParams& p, bool pdl, cudaStream_t st);

@@ -51,6 +51,7 @@ struct QGemvParams {
   int xcols;                 // columns the shared-memory layout is sized for (1..8)
   int nstage;                // weight pipeline stages in shared memory (1..QG_MAX_STAGES)
   int* err;                  // device error word: set when a bounded wait gives up
+  Timeline tl;
   const int* row_ids;        // optional: plain mode column c reads row row_ids[c] and writes row c
   // activations: fp16 rows in natural order
   const __half* x;
@@ -466,6 +467,7 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
   const int ngroups = (tiles + tpc - 1) / tpc;
   const int lt = warp / wpt, kslice = warp % wpt;
 
+  tl_mark(p.tl, 0);
   if (tid == 0) {
     for (int s = 0; s < NS; s++) mbar_init(&full_bar[s], 1);
     mbar_fence_init();
@@ -521,6 +523,7 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
   }
   if constexpr (!GROUPED) pdl_wait();
   pdl_launch();
+  tl_mark(p.tl, 1);
 
   if (active) {
     if (tid < QG_MAXCOLS) {
@@ -533,6 +536,7 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
     }
     __syncthreads();
     stage_x_f16(p.x, p.ldx, K, p.xcols, xs, sxs, ncols, xrows, xstride);
+    tl_mark(p.tl, 2);
 
     const bool live = g < ncols;
     const uint8_t* xrow = xs + (size_t)(live ? g : 0) * xstride;
@@ -544,6 +548,7 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
         if (p.err != nullptr && tid == 0) atomicExch(p.err, 1);  // a copy never landed: report and leave
         return;
       }
+      if (it == 0) tl_mark(p.tl, 3);
       float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
       const int tile = grp * tpc + lt;
       if (tile < tiles) {
@@ -600,6 +605,7 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
       buf ^= 1;
     }
   }
+  tl_mark(p.tl, 4);
   // tail: the last CTA of the grid finishes the rows (residual norm / MoE combine + norm)
   if (tp.mode != 0) {
     __threadfence();
@@ -609,6 +615,7 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
     if (!is_last) return;
     __threadfence();
     if (tid == 0) *tp.ticket = 0;
+    tl_mark(p.tl, 5, true);
     const int slots1 = tp.used + 1;
     for (int n = 0; n < tp.M; n++) {
       float* hrow = tp.h + (size_t)n * tp.H;
@@ -618,6 +625,7 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
       }
       row_rmsnorm_f16(hrow, tp.gamma, tp.eps, tp.H, tp.xn + (size_t)n * tp.H, scratch);
     }
+    tl_mark(p.tl, 6, true);
   }
 }
 

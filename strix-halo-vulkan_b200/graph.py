@@ -218,6 +218,12 @@ class Graph:
     def draft_rewind(self, past):
         _lib.check(_lib.load().b200_draft_rewind(self._h, past))
 
+    def timeline(self, max_launches=1024):
+        """[launches][8] globaltimer ns of the last pass (process started with B200_TIMELINE=1)."""
+        a = np.zeros((max_launches, 8), dtype=np.int64)
+        n = _lib.load().b200_graph_timeline(self._h, a.ctypes.data, max_launches)
+        return a[:max(n, 0)]
+
     # -- trace --------------------------------------------------------------------------------
     def trace(self, rows):
         """Per-layer tensors of the last pass (graph created with trace=True)."""

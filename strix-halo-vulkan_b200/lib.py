@@ -67,6 +67,7 @@ SYMBOLS = {
     "b200_graph_generate_greedy": (I32, [P, P, P, I32, I32, P]),
     "b200_graph_last_device_ms": (F32, [P]),
     "b200_graph_last_launches": (I32, [P]),
+    "b200_graph_timeline": (I32, [P, P, I32]),
     "b200_graph_trace": (I64, [P, I32, P, I64]),
     "b200_draft_rows": (I32, [P, P, P, I32, I32, PP, PP]),
     "b200_draft_past": (I32, [P]),
