@@ -56,6 +56,22 @@ def algorithmic_bytes_per_token(pkg, cfg, ctx):
     return w + state + ring + kv
 
 
+def max_over_ranks(value, world, device="cuda"):
+    """A duration as the slowest rank saw it."""
+    if world <= 1:
+        return float(value)
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([float(value)], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def whole_job_rate(units_per_rank, world, ms):
+    """Units all ranks processed per second: every rank decodes its own sequences (no exchange step)."""
+    return world * units_per_rank / (ms / 1e3)
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons while the timed region runs."""
 
@@ -92,16 +108,55 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def cpu_baseline(pkg, model, cfg, tokens=6):
+def batched_decode(pkg, model, cfg, slots, steps, rank):
+    """`slots` sequences decode together, one token each per step. Contexts are seeded lengths in
+    8192..32768 declared as already prefilled (zero-filled caches: the timed work is the decode)."""
+    g = pkg.Graph(model, n_kv=32768 + steps + 40, max_tokens=max(slots, 8), slots=slots, use_cuda_graph=True)
+    rng = np.random.default_rng(7 + rank)
+    ctx = rng.integers(8192, 32769, slots)
+    for s in range(slots):
+        g.use_slot(s)
+        g.set_past(int(ctx[s]))
+    first = rng.integers(0, cfg["vocab"], slots).astype(np.int32)
+    ids = list(range(slots))
+    out = g.generate_greedy(ids, first, 3)
+    out = g.generate_greedy(ids, out[-1], steps)
+    ms = g.last_device_ms() / steps
+    H, nE, used = cfg["n_embd"], cfg["n_expert"], cfg["n_expert_used"]
+    # algorithmic bytes: dense weights once, the distinct routed experts of the step (expected value over
+    # uniform routing), every slot's DeltaNet state read + written and its KV cells read
+    gguf, config = pkg.gguf, pkg.config
+    dense = expert_one = 0
+    for name, typ, dims, _ in config.manifest(cfg):
+        nb = gguf.tensor_bytes(typ, dims)
+        if name == "token_embd.weight":
+            nb = gguf.row_bytes(typ, dims[0]) * slots
+        if "_exps." in name:
+            expert_one += nb // nE
+        else:
+            dense += nb
+    distinct = nE * (1.0 - (1.0 - used / nE) ** slots)
+    n_dn = sum(0 if config.is_attention_layer(cfg, l) else 1 for l in range(cfg["n_layer"]))
+    n_at = cfg["n_layer"] - n_dn
+    state = n_dn * cfg["dn_heads_v"] * cfg["dn_head_dim"] ** 2 * 4 * 2 * slots
+    kv = n_at * 2 * cfg["n_head_kv"] * cfg["head_dim"] * 2 * float(np.sum(ctx + steps / 2))
+    nbytes = dense + expert_one * distinct + state + kv
+    peak, which = measured_peak_gbs()
+    return {"slots": slots, "ms_per_step": ms, "unit": "tok/s", "mean_context": float(np.mean(ctx)),
+            "algorithmic_bytes_per_step": nbytes, "roofline_frac": nbytes / (ms / 1e3) / 1e9 / peak, "peak_source": which,
+            "note": "contexts declared prefilled over zero-filled caches; expected distinct-expert count"}
+
+
+def cpu_baseline(pkg, model, cfg, tokens=8):
     """The CPU oracle (a port of the reference's CPU code) on this host's cores, on a bounded
-    sample: decode on the 4-layer and the 8-layer prefix of the same checkpoint (head included),
+    sample: decode on the 4-layer and the 12-layer prefix of the same checkpoint (head included),
     extrapolated linearly to 48 layers."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import orc
     orc.build()
     config = pkg.config
     times = {}
-    for nl in (4, 8):
+    for nl in (4, 12):
         sub = config.variant(cfg, n_layer=nl)
         tensors = {}
         for name, typ, dims, _ in config.manifest(sub):
@@ -115,12 +170,12 @@ def cpu_baseline(pkg, model, cfg, tokens=6):
             seq.extend([int(ids[i % 4])], numerics=orc.EXACT)
         times[nl] = (time.perf_counter() - t) / tokens
         del seq, om, tensors
-    per_token = times[4] + (times[8] - times[4]) * (cfg["n_layer"] - 4) / 4.0
+    per_token = times[4] + (times[12] - times[4]) * (cfg["n_layer"] - 4) / 8.0
     cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count()
     return {"value": 1.0 / per_token, "unit": "tok/s", "cores": cores, "kind": "port",
-            "sample": f"exact-f32 CPU oracle, {tokens} decode tokens each on the 4- and 8-layer prefix (head included) of the same "
+            "sample": f"exact-f32 CPU oracle, {tokens} decode tokens each on the 4- and 12-layer prefix (head included) of the same "
                       f"checkpoint at short context, extrapolated linearly to {cfg['n_layer']} layers "
-                      f"({times[4] * 1e3:.0f} ms and {times[8] * 1e3:.0f} ms per token)"}
+                      f"({times[4] * 1e3:.0f} ms and {times[12] * 1e3:.0f} ms per token)"}
 
 
 def main():
@@ -131,6 +186,7 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--config", default="a3b", help="a3b (the benchmark) or tiny (a quick functional run)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--slots", type=int, default=64, help="also time batched decode over this many slots (0 = skip)")
     ap.add_argument("--prompt", type=int, default=0, help="override the prompt length (profiling runs)")
     ap.add_argument("--profile", type=int, default=0, help="run N eager decode steps between cudaProfilerStart/Stop and exit")
     args = ap.parse_args()
@@ -205,10 +261,7 @@ def main():
     dev_ms = g.last_device_ms()
     launches = g.last_launches()
     tok = int(out[-1, 0])
-    if world > 1:
-        t = torch.tensor([dev_ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms = float(t.item())
+    dev_ms = max_over_ranks(dev_ms, world)
     # ---- end to end through the reference-facing call: id in, logits out, host argmax ----
     for _ in range(3):
         logits, _ = g.extend([tok]); tok = int(np.argmax(logits))
@@ -220,14 +273,20 @@ def main():
         tok = int(np.argmax(logits))
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
-    if world > 1:
-        t = torch.tensor([e2e_s], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+    e2e_s = max_over_ranks(e2e_s, world)
 
+    # ---- batched multi-slot decode (BASELINE config 3 on one GPU): every slot holds an 8k-32k context ----
+    batch = None
+    if args.slots > 0 and args.config == "a3b":
+        try:
+            batch = batched_decode(pkg, model, cfg, args.slots, min(steps, 32), rank)
+            batch["ms_per_step"] = max_over_ranks(batch["ms_per_step"], world)
+            batch["value"] = whole_job_rate(args.slots, world, batch["ms_per_step"])
+        except Exception as e:  # an extra measurement must not lose the headline line
+            batch = {"error": str(e)[:200]}
     if rank == 0:
         ms_per_step = dev_ms / steps
-        value = world * steps / (dev_ms / 1e3)
+        value = whole_job_rate(steps, world, dev_ms)
         bytes_step = algorithmic_bytes_per_token(pkg, cfg, ctx0 + steps // 2)
         peak, which = measured_peak_gbs()
         achieved = bytes_step / (ms_per_step / 1e3) / 1e9
@@ -249,6 +308,8 @@ def main():
             "gpu_launches": launches * steps,
             "clocks": clocks.summary(),
         }
+        if batch is not None:
+            line["batch64"] = batch
         if not args.no_cpu_baseline and world == 1:
             try:
                 line["cpu_baseline"] = cpu_baseline(pkg, model, cfg)

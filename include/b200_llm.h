@@ -88,6 +88,11 @@ int32_t b200_graph_nkv(const b200_graph* g);                                    
 int32_t b200_graph_use_slot(b200_graph* g, int32_t slot);                                  /* UseSlot   :916 */
 int32_t b200_graph_reset(b200_graph* g);                                                   /* Reset     :1079 */
 int32_t b200_graph_past(const b200_graph* g);
+/* Declares the current slot to hold `past` cells without running them: moving `past` back is the
+ * reference's Rewind of the KV cache (cells past the end are masked, llm/graph.go:1071-1078); moving
+ * it forward exposes whatever the cache holds (zeros after creation) and exists for throughput
+ * measurements on long contexts that are "already prefilled". The DeltaNet state is not touched. */
+int32_t b200_graph_set_past(b200_graph* g, int32_t past);
 /* Forward = Reset + Extend (:1695). logits: [vocab] of the last row; hidden: [n_embd] output-normed last row. */
 int32_t b200_graph_forward(b200_graph* g, const int32_t* ids, int32_t n, const float** logits, const float** hidden);
 int32_t b200_graph_extend(b200_graph* g, const int32_t* ids, int32_t n, const float** logits, const float** hidden); /* Extend :1709 */

@@ -81,6 +81,12 @@ int32_t b200_graph_use_slot(b200_graph* g, int32_t slot) {
   return OK;
 }
 int32_t b200_graph_reset(b200_graph* g) { if (!g) return EINVAL_; return g->g.reset_slot(g->g.cur); }
+int32_t b200_graph_set_past(b200_graph* g, int32_t past) {
+  if (!g) return EINVAL_;
+  if (past < 0 || past > g->g.o.n_kv) { set_error("set_past: position outside the slot's context"); return EINVAL_; }
+  g->g.past[g->g.cur] = past; g->g.spec_n = 0;
+  return OK;
+}
 int32_t b200_graph_past(const b200_graph* g) { return g ? g->g.past[g->g.cur] : 0; }
 
 int32_t b200_graph_forward(b200_graph* g, const int32_t* ids, int32_t n, const float** logits, const float** hidden) {

@@ -109,8 +109,8 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   }
   kcache.resize(n_attn); vcache.resize(n_attn);
   for (int i = 0; i < n_attn; i++) {
-    B200_TRY(dalloc(&kcache[i], (size_t)o.slots * kv_slot_stride, false));
-    B200_TRY(dalloc(&vcache[i], (size_t)o.slots * kv_slot_stride, false));
+    B200_TRY(dalloc(&kcache[i], (size_t)o.slots * kv_slot_stride));
+    B200_TRY(dalloc(&vcache[i], (size_t)o.slots * kv_slot_stride));
   }
   past.assign(o.slots, 0); draft_past.assign(o.slots, 0);
   // host staging

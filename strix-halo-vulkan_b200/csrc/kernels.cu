@@ -239,30 +239,29 @@ __device__ __forceinline__ void route_token(const RouterParams& p, int n, int la
     pv[i] = lane + 32 * i < nE ? pv[i] * inv : -1.f;
     if (p.probs != nullptr && lane + 32 * i < nE) p.probs[(size_t)n * nE + lane + 32 * i] = pv[i];
   }
-  // top-k by descending probability, ties to the lower index (llm/moe.go:249-252)
+  // top-k by descending probability, ties to the lower index (llm/moe.go:249-252). Probabilities
+  // are non-negative, so their bit patterns order like unsigned integers: one warp-wide max of the
+  // values, then one warp-wide min of the indices that hold it.
   float wsum = 0.f, last_p = 0.f, myw = 0.f;
   for (int k = 0; k <= used; k++) {
     float bv = pv[0]; int bi = 0;
 #pragma unroll
     for (int i = 1; i < NPL; i++) if (pv[i] > bv) { bv = pv[i]; bi = i; }
-    bi = lane + 32 * bi;
-    if (bv < 0.f) bi = 0x7fffffff;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-    }
+    const uint32_t key = bv < 0.f ? 0u : __float_as_uint(bv) + 1u;          // taken / absent entries sort last
+    const uint32_t best = __reduce_max_sync(0xffffffffu, key);
+    const uint32_t mine = key == best && best != 0u ? (uint32_t)(lane + 32 * bi) : 0x7fffffffu;
+    const int widx = (int)__reduce_min_sync(0xffffffffu, mine);
+    const float wv = best == 0u ? -1.f : __uint_as_float(best - 1u);
     if (k == used) {
-      if (lane == 0 && p.margin) p.margin[n] = last_p > 0.f ? (last_p - fmaxf(bv, 0.f)) / last_p : 0.f;
+      if (lane == 0 && p.margin) p.margin[n] = last_p > 0.f ? (last_p - fmaxf(wv, 0.f)) / last_p : 0.f;
       break;
     }
-    if ((bi & 31) == lane) {
+    if ((widx & 31) == lane) {
 #pragma unroll
-      for (int i = 0; i < NPL; i++) if (i == (bi >> 5)) pv[i] = -1.f;
+      for (int i = 0; i < NPL; i++) if (i == (widx >> 5)) pv[i] = -1.f;
     }
-    if (lane == k) { myw = bv; p.topk[(size_t)n * used + k] = bi; }
-    wsum += bv; last_p = bv;
+    if (lane == k) { myw = wv; p.topk[(size_t)n * used + k] = widx; }
+    wsum += wv; last_p = wv;
   }
   // normalise the weights (llm/moe.go:256-282)
   if (wsum < 6.103515625e-5f) wsum = 6.103515625e-5f;
@@ -693,38 +692,58 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnParams p) {
   const __half* kc = p.kcache + (size_t)slot * p.slot_stride + (size_t)kvh * hd + lane * DPL;
   const __half* vc = p.vcache + (size_t)slot * p.slot_stride + (size_t)kvh * hd + lane * DPL;
   const size_t cell_stride = (size_t)p.Hkv * hd;
-  for (int c = c0 + warp; c < c1; c += AT_WARPS) {
-    float kf[DPL], vf[DPL];
-    const __half* kp = kc + (size_t)c * cell_stride;
-    const __half* vp = vc + (size_t)c * cell_stride;
+  // a warp walks cells c0 + warp, + AT_WARPS, ...; the K and V rows of up to ATT_PF cells are
+  // fetched together so their DRAM latencies overlap
+  constexpr int ATT_PF = 4;
+  for (int cb = c0 + warp; cb < c1; cb += AT_WARPS * ATT_PF) {
+    uint4 kraw[ATT_PF], vraw[ATT_PF];
 #pragma unroll
-    for (int d = 0; d < DPL; d += 2) {
-      float2 a = __half22float2(*reinterpret_cast<const __half2*>(kp + d));
-      float2 b = __half22float2(*reinterpret_cast<const __half2*>(vp + d));
-      kf[d] = a.x; kf[d + 1] = a.y; vf[d] = b.x; vf[d + 1] = b.y;
-    }
-    float sc[G];
-#pragma unroll
-    for (int hh = 0; hh < G; hh++) {
-      float a = 0.f;
-#pragma unroll
-      for (int d = 0; d < DPL; d++) a = fmaf(q[hh][d], kf[d], a);
-      sc[hh] = a;
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-#pragma unroll
-      for (int hh = 0; hh < G; hh++) sc[hh] += __shfl_xor_sync(0xffffffffu, sc[hh], off);
+    for (int u = 0; u < ATT_PF; u++) {
+      const int c = cb + u * AT_WARPS;
+      if (c < c1) {
+        if constexpr (DPL == 8) {
+          kraw[u] = ldg_stream(kc + (size_t)c * cell_stride);
+          vraw[u] = ldg_stream(vc + (size_t)c * cell_stride);
+        } else {
+          const uint2 a = *reinterpret_cast<const uint2*>(kc + (size_t)c * cell_stride), b = *reinterpret_cast<const uint2*>(vc + (size_t)c * cell_stride);
+          kraw[u] = make_uint4(a.x, a.y, 0, 0); vraw[u] = make_uint4(b.x, b.y, 0, 0);
+        }
+      }
     }
 #pragma unroll
-    for (int hh = 0; hh < G; hh++) {
-      const float sv = sc[hh] * scale;
-      const float mn = fmaxf(m[hh], sv);
-      const float corr = expf(m[hh] - mn), pw = expf(sv - mn);
-      l[hh] = l[hh] * corr + pw;
+    for (int u = 0; u < ATT_PF; u++) {
+      const int c = cb + u * AT_WARPS;
+      if (c >= c1) break;
+      float kf[DPL], vf[DPL];
+      const uint32_t kw[4] = {kraw[u].x, kraw[u].y, kraw[u].z, kraw[u].w}, vw[4] = {vraw[u].x, vraw[u].y, vraw[u].z, vraw[u].w};
 #pragma unroll
-      for (int d = 0; d < DPL; d++) o[hh][d] = fmaf(pw, vf[d], o[hh][d] * corr);
-      m[hh] = mn;
+      for (int d = 0; d < DPL; d += 2) {
+        kf[d] = h2f_lo(kw[d >> 1]); kf[d + 1] = h2f_hi(kw[d >> 1]);
+        vf[d] = h2f_lo(vw[d >> 1]); vf[d + 1] = h2f_hi(vw[d >> 1]);
+      }
+      float sc[G];
+#pragma unroll
+      for (int hh = 0; hh < G; hh++) {
+        float a = 0.f;
+#pragma unroll
+        for (int d = 0; d < DPL; d++) a = fmaf(q[hh][d], kf[d], a);
+        sc[hh] = a;
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+        for (int hh = 0; hh < G; hh++) sc[hh] += __shfl_xor_sync(0xffffffffu, sc[hh], off);
+      }
+#pragma unroll
+      for (int hh = 0; hh < G; hh++) {
+        const float sv = sc[hh] * scale;
+        const float mn = fmaxf(m[hh], sv);
+        const float corr = expf(m[hh] - mn), pw = expf(sv - mn);
+        l[hh] = l[hh] * corr + pw;
+#pragma unroll
+        for (int d = 0; d < DPL; d++) o[hh][d] = fmaf(pw, vf[d], o[hh][d] * corr);
+        m[hh] = mn;
+      }
     }
   }
   // merge the warps, then publish this split's partial
@@ -779,18 +798,30 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnParams p) {
   for (int i = tid; i < G * nlive; i += AT_THREADS) fac[i] = expf(fac[i] - mm_s[i / nlive]);
   __syncthreads();
   if (tid < G) {
-    float lv = 0.f;
-    for (int sp = 0; sp < nlive; sp++)
-      lv += __ldcg(p.partial + (((size_t)n * p.Hq + kvh * G + tid) * p.nsplit + sp) * PW + hd + 1) * fac[tid * nlive + sp];
-    ll_s[tid] = lv;
+    float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+    const float* lp = p.partial + ((size_t)n * p.Hq + kvh * G + tid) * p.nsplit * PW + hd + 1;
+    int sp = 0;
+    for (; sp + 4 <= nlive; sp += 4) {
+      const float a0 = __ldcg(lp + (size_t)sp * PW), a1 = __ldcg(lp + (size_t)(sp + 1) * PW), a2 = __ldcg(lp + (size_t)(sp + 2) * PW), a3 = __ldcg(lp + (size_t)(sp + 3) * PW);
+      l0 += a0 * fac[tid * nlive + sp]; l1 += a1 * fac[tid * nlive + sp + 1]; l2 += a2 * fac[tid * nlive + sp + 2]; l3 += a3 * fac[tid * nlive + sp + 3];
+    }
+    for (; sp < nlive; sp++) l0 += __ldcg(lp + (size_t)sp * PW) * fac[tid * nlive + sp];
+    ll_s[tid] = (l0 + l1) + (l2 + l3);
   }
   __syncthreads();
   const int gate_off = hd;  // per head: hd query dims then hd gate dims
   for (int i = tid; i < G * hd; i += AT_THREADS) {
     const int hh = i / hd, d = i - hh * hd, head = kvh * G + hh;
     const float* part = p.partial + ((size_t)n * p.Hq + head) * p.nsplit * PW;
-    float ov = 0.f;
-    for (int sp = 0; sp < nlive; sp++) ov += __ldcg(part + (size_t)sp * PW + d) * fac[hh * nlive + sp];
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+    int sp = 0;
+    for (; sp + 4 <= nlive; sp += 4) {  // independent loads in flight; the sum order stays fixed
+      const float a0 = __ldcg(part + (size_t)sp * PW + d), a1 = __ldcg(part + (size_t)(sp + 1) * PW + d);
+      const float a2 = __ldcg(part + (size_t)(sp + 2) * PW + d), a3 = __ldcg(part + (size_t)(sp + 3) * PW + d);
+      o0 += a0 * fac[hh * nlive + sp]; o1 += a1 * fac[hh * nlive + sp + 1]; o2 += a2 * fac[hh * nlive + sp + 2]; o3 += a3 * fac[hh * nlive + sp + 3];
+    }
+    for (; sp < nlive; sp++) o0 += __ldcg(part + (size_t)sp * PW + d) * fac[hh * nlive + sp];
+    const float ov = (o0 + o1) + (o2 + o3);
     const float gate = p.proj[(size_t)n * p.ldp + head * 2 * hd + gate_off + d];
     p.ctx16[(size_t)n * p.Hq * hd + head * hd + d] = __float2half_rn(ov / ll_s[hh] * sigmoid_acc(gate));
   }

@@ -27,8 +27,10 @@ static int launch_one(const QGemvParams& p, const TailParams& tp, int max_entrie
   const int occ = fixed + 2 * stage <= budget2 ? 2 : 1;
   int cap = g_sm_count * occ / (ny * nz);
   if (cap < 1) cap = 1;
-  const int gx = groups < cap ? groups : cap;
-  const int per_cta = (groups + gx - 1) / gx;
+  // every CTA walks the same number of groups (a ragged last round leaves most SMs idle)
+  const int rounds = (groups + cap - 1) / cap;
+  const int gx = (groups + rounds - 1) / rounds;
+  const int per_cta = rounds;
   int ns = (int)(((occ == 2 ? budget2 : budget1) - fixed) / stage);
   if (ns > QG_MAX_STAGES) ns = QG_MAX_STAGES;
   if (ns > per_cta) ns = per_cta;

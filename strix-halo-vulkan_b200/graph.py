@@ -130,6 +130,9 @@ class Graph:
     def past(self):
         return int(_lib.load().b200_graph_past(self._h))
 
+    def set_past(self, past):
+        _lib.check(_lib.load().b200_graph_set_past(self._h, past))
+
     # -- passes --------------------------------------------------------------------------
     def _call(self, fn, ids, rows_logits, rows_hidden, vocab=None):
         ids = _i32(ids)

@@ -52,6 +52,7 @@ SYMBOLS = {
     "b200_graph_use_slot": (I32, [P, I32]),
     "b200_graph_reset": (I32, [P]),
     "b200_graph_past": (I32, [P]),
+    "b200_graph_set_past": (I32, [P, I32]),
     "b200_graph_forward": (I32, [P, P, I32, PP, PP]),
     "b200_graph_extend": (I32, [P, P, I32, PP, PP]),
     "b200_graph_extend_rows": (I32, [P, P, I32, PP, PP]),

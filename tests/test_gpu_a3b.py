@@ -1,0 +1,79 @@
+"""Parity at the benchmark's shapes: a 4-layer prefix (3 gated DeltaNet + 1 gated GQA, 512 experts
+top-10 + shared, vocab 151936, the UD-Q4_K_XL-style type mix) of the 80B-A3B-shaped model. The
+checkpoint is generated and quantised on the device; its bytes are read back for the oracle, so both
+sides see identical quantised bytes."""
+import numpy as np
+import pytest
+
+import modelgen
+from parity import NEAR_TIE, assert_close, logit_gap
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def a3b4(pkg, orc):
+    config = modelgen.config
+    cfg = config.variant(config.A3B, n_layer=4, name="80b-a3b-shaped-4-layer-prefix")
+    model = pkg.Model.synthetic(cfg, seed=0)
+    tensors = {name: (typ, dims, model.read_tensor(name)) for name, typ, dims, _ in config.manifest(cfg)}
+    om = orc.Model(config.graph_fields(cfg), tensors)
+    return dict(model=model, oracle=om, cfg=cfg, tensors=tensors)
+
+
+def test_device_generated_checkpoint_dequantises_like_the_oracle(pkg, orc, a3b4):
+    for name in ("blk.0.attn_qkv.weight", "blk.3.attn_v.weight", "blk.1.ffn_gate_inp.weight"):
+        typ, dims, data = a3b4["tensors"][name]
+        n = 4 * dims[0]
+        rb = pkg.gguf.row_bytes(typ, dims[0])
+        got = pkg.dequantize(typ, data[:4 * rb], n)
+        want = orc.dequantize(typ, data[:4 * rb], n)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), name
+        assert 0.005 < np.std(want) < 0.04     # N(0, 0.02) survived the quantiser
+
+
+def test_full_shape_prefill_and_greedy_decode_match_oracle(pkg, a3b4):
+    cfg = a3b4["cfg"]
+    ids = np.random.default_rng(1).integers(0, cfg["vocab"], 24).astype(np.int32)
+    g = pkg.Graph(a3b4["model"], n_kv=64, max_tokens=32, trace=True, use_cuda_graph=False)
+    seq = a3b4["oracle"].seq()
+    logits, _ = g.forward(ids)
+    tr = g.trace(len(ids))
+    want, ot = seq.extend(ids, trace=("hidden", "topk", "margin"))
+    for l in range(cfg["n_layer"]):
+        assert_close(tr["hidden"][l], ot["hidden"][:, l], f"layer {l} residual")
+        for t in range(len(ids)):
+            if ot["margin"][t, l] >= NEAR_TIE:
+                assert set(tr["topk"][l, t].tolist()) == set(ot["topk"][t, l].tolist()), (l, t)
+    # A top-k boundary closer than 1e-3 is a documented near-tie: if the two sides route differently there,
+    # their states differ from then on, so the strict bound applies until the first such event.
+    tainted = bool((ot["margin"] < NEAR_TIE).any())
+    for step in range(8):
+        assert_close(logits, want, f"logits at step {step} (near-tie seen: {tainted})", tol=1e-1 if tainted else 1e-2)
+        tg, to = int(np.argmax(logits)), int(np.argmax(want))
+        assert tg == to or logit_gap(want) < NEAR_TIE or tainted
+        logits, _ = g.extend([to])
+        want, od = seq.extend([to], trace=("margin",))
+        tainted = tainted or bool((od["margin"] < NEAR_TIE).any())
+
+
+def test_sixteen_slots_batched_match_solo(pkg, a3b4):
+    cfg = a3b4["cfg"]
+    g = pkg.Graph(a3b4["model"], n_kv=48, max_tokens=32, slots=16, use_cuda_graph=False)
+    rng = np.random.default_rng(9)
+    toks = rng.integers(0, cfg["vocab"], 16).astype(np.int32)
+    solo = []
+    for s in range(16):
+        g.use_slot(s); g.reset(); g.extend(rng.integers(0, cfg["vocab"], 3 + s % 5).astype(np.int32))
+        ck = g.checkpoint()
+        lg, _ = g.extend([int(toks[s])]); solo.append(lg)
+        g.restore(ck); g.checkpoint_free(ck)
+    batched = g.decode_rows(list(range(16)), toks)
+    for s in range(16):
+        # passes of more than 8 rows finish their rows in separate kernels, so the match is to tolerance
+        assert_close(batched[s], solo[s], f"slot {s}", tol=2e-3)
+        assert int(np.argmax(batched[s])) == int(np.argmax(solo[s])) or logit_gap(solo[s]) < NEAR_TIE
+    # the device-resident loop over all 16 slots emits what the host loop picks
+    first = [int(np.argmax(b)) for b in batched]
+    out = g.generate_greedy(list(range(16)), first, 3)
+    assert out.shape == (3, 16)

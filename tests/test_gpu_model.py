@@ -44,8 +44,11 @@ def test_prefill_matches_oracle_layer_by_layer(pkg, tiny):
         for t in range(len(ids)):
             if ot["margin"][t, l] < NEAR_TIE:
                 continue   # documented near-tie: the top-k boundary is closer than 1e-3
-            assert np.array_equal(tr["topk"][l, t], ot["topk"][t, l]), (l, t, tr["topk"][l, t], ot["topk"][t, l])
-            assert_close(tr["topk_w"][l, t, :-1], ot["topk_w"][t, l], f"routing weights {l},{t}")
+            # the routed set is exact; the order inside it may differ where two probabilities tie
+            assert set(tr["topk"][l, t].tolist()) == set(ot["topk"][t, l].tolist()), (l, t, tr["topk"][l, t], ot["topk"][t, l])
+            wg = dict(zip(tr["topk"][l, t].tolist(), tr["topk_w"][l, t, :-1].tolist()))
+            wo = dict(zip(ot["topk"][t, l].tolist(), ot["topk_w"][t, l].tolist()))
+            assert_close([wg[e] for e in sorted(wg)], [wo[e] for e in sorted(wo)], f"routing weights {l},{t}")
     assert_close(logits, want_logits, "logits")
     assert_close(hidden, ot["hidden"][-1, -1], "last residual")
 
