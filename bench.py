@@ -188,6 +188,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--slots", type=int, default=64, help="also time batched decode over this many slots (0 = skip)")
     ap.add_argument("--prompt", type=int, default=0, help="override the prompt length (profiling runs)")
+    ap.add_argument("--profile-batch", type=int, default=0, help="run N eager batched decode steps over --slots slots between cudaProfilerStart/Stop and exit")
     ap.add_argument("--profile", type=int, default=0, help="run N eager decode steps between cudaProfilerStart/Stop and exit")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -226,6 +227,8 @@ def main():
     t_model = time.time() - t0
     n_kv = prompt_len + 2 * (steps + warmup) + 64
     g = pkg.Graph(model, n_kv=n_kv, max_tokens=64, slots=1, use_cuda_graph=not args.profile)
+    if args.profile_batch:
+        g.destroy()
     rng = np.random.default_rng(1 + rank)
     prompt = rng.integers(0, cfg["vocab"], prompt_len).astype(np.int32)
     t0 = time.time()
@@ -239,6 +242,20 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.profile_batch:
+        gb = pkg.Graph(model, n_kv=32768 + 64, max_tokens=max(args.slots, 8), slots=args.slots, use_cuda_graph=False)
+        ctx = np.random.default_rng(7).integers(8192, 32769, args.slots)
+        for s_ in range(args.slots):
+            gb.use_slot(s_); gb.set_past(int(ctx[s_]))
+        sl = list(range(args.slots))
+        out = gb.generate_greedy(sl, [1] * args.slots, 2)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        out = gb.generate_greedy(sl, out[-1], args.profile_batch)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"profiled_batch_steps": args.profile_batch, "slots": args.slots}))
+        return
     if args.profile:
         for _ in range(3):
             logits, _ = g.extend([tok]); tok = int(np.argmax(logits))

@@ -73,7 +73,7 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   B200_TRY(dalloc(&r_logits, (size_t)MR * c.n_expert)); B200_TRY(dalloc(&r_probs, (size_t)MR * c.n_expert));
   B200_TRY(dalloc(&topk, (size_t)MR * used)); B200_TRY(dalloc(&topk_w, (size_t)MR * slots1)); B200_TRY(dalloc(&margin, (size_t)MR));
   B200_TRY(dalloc(&entries, (size_t)max_entries)); B200_TRY(dalloc(&n_entries, 1)); B200_TRY(dalloc(&cols, (size_t)MR * slots1));
-  B200_TRY(dalloc(&r_ticket, 1)); B200_TRY(dalloc(&tail_ticket, 1)); B200_TRY(dalloc(&err_flag, 1)); B200_TRY(dalloc(&y16, (size_t)MR * vw));
+  B200_TRY(dalloc(&r_ticket, 1)); B200_TRY(dalloc(&tail_ticket, 1)); B200_TRY(dalloc(&err_flag, 1)); B200_TRY(dalloc(&ss_part, (size_t)MR * SS_LD)); B200_TRY(dalloc(&col_tickets, 1024)); B200_TRY(dalloc(&y16, (size_t)MR * vw));
   B200_TRY(dalloc(&act16, (size_t)MR * slots1 * c.ffn_expert)); B200_TRY(dalloc(&down, (size_t)MR * slots1 * H));
   B200_TRY(dalloc(&logits, (size_t)MR * c.vocab));
   B200_TRY(dalloc(&ids_dev, (size_t)MR)); B200_TRY(dalloc(&next_ids, (size_t)MR)); B200_TRY(dalloc(&row_slot, (size_t)MR));
@@ -138,53 +138,58 @@ int Graph::max_entries_for(int M) const {
 }
 
 // ---- one pass over M rows --------------------------------------------------------------
-// Per layer: [in-proj] [DeltaNet step | attention pre-pass + split-KV attention] [out-proj +
-// residual, tail: ffn_norm] [router + top-k + work list] [experts gate/up + SwiGLU] [experts
-// down, tail: weighted combine + residual + next norm]. Every projection reads fp16 rows that
-// the previous kernel's tail already normalised, so no kernel repeats a norm.
+// Per layer: [in-proj] [DeltaNet step | attention pre-pass + split-KV attention] [out-proj + residual]
+// [router + top-k + work list] [experts gate/up + SwiGLU] [experts down + weighted combine + residual].
+// Passes of at most 8 rows never materialise a norm: the kernel that writes the residual leaves per-CTA
+// partial sums of squares, and each consumer normalises the rows while it stages them. Larger passes
+// finish their rows in stand-alone row kernels and read fp16 rows.
 int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) {
   const b200_config& c = m->c;
   const int H = c.n_embd, D = c.dn_head_dim, qk = c.dn_heads_k * D, vw = c.dn_heads_v * D, cw = 2 * qk + vw;
   const int hd = c.head_dim, qw = c.n_head * hd, kvw = c.n_head_kv * hd, used = c.n_expert_used, slots1 = used + 1;
   const int xcols = std::min(M, QG_MAXCOLS);
-  const bool fused_tail = M <= QG_TAIL_ROWS;
+  const bool fused = M <= QG_TAIL_ROWS;
   launches = 0;
   bool first = true;
+  int ss_n = 1;  // partial sums of squares the current residual rows carry
   auto pdl = [&]() { bool p = !first; first = false; launches++; return p; };
   // timestamps slot of the NEXT launch (launches counts the ones already issued)
   auto tl = [&]() { Timeline t{timeline, launches < timeline_cap ? launches : 0}; if (launches >= timeline_cap) t.buf = nullptr; return t; };
   auto base = [&](const DTensor& w, int K, int N, const __half* x, int ldx) {
     QGemvParams p{};
     p.w[0] = w.data; p.seg_end[0] = N; p.nseg = 1; p.stride = w.stride; p.K = K; p.N = N; p.M = M; p.xcols = xcols; p.x_div = 1;
-    p.x = x; p.ldx = ldx; p.err = err_flag; p.tl = tl();
+    p.x = x; p.ldx = ldx; p.err = err_flag; p.tl = tl(); p.eps = c.eps;
     return p;
   };
-  auto tail = [&](int mode, const DTensor& gamma) {
+  // a projection of the normalised residual: fused passes normalise while staging, others read xn16
+  auto normed = [&](QGemvParams& p, const DTensor& gamma, __half* xn_copy) {
+    if (fused) { p.hsrc = h; p.gamma = (const float*)gamma.data; p.ss_in = ss_part; p.ss_n = ss_n; p.xn_out = xn_copy; return (int)PRO_NORM; }
+    return (int)PRO_F16;
+  };
+  auto row_tail = [&](int mode, const DTensor& gamma) {
     TailParams t{};
-    t.mode = mode; t.ticket = tail_ticket; t.h = h; t.gamma = (const float*)gamma.data; t.xn = xn16; t.down = down; t.topk_w = topk_w;
+    t.mode = mode; t.h = h; t.gamma = (const float*)gamma.data; t.xn = xn16; t.down = down; t.topk_w = topk_w;
     t.used = used; t.H = H; t.M = M; t.eps = c.eps;
     return t;
   };
   const TailParams no_tail{};
-  // a projection whose last CTA (small passes) or a follow-up kernel (large passes) finishes the rows
-  auto proj_with_tail = [&](uint32_t type, int epi, bool grouped, const QGemvParams& p, const TailParams& t, int ne) -> int {
-    B200_TRY(launch_qgemv(type, epi, false, grouped, p, fused_tail ? t : no_tail, ne, pdl(), st));
-    if (!fused_tail) B200_TRY(launch_row_tail(t, pdl(), st));
-    return OK;
-  };
   const int l0 = f.draft ? c.n_layer : 0, l1 = f.draft ? c.n_layer + 1 : c.n_layer;
   if (f.draft) {
     // nextn seed, embedding first: h = eh_proj . concat(rms(embd, enorm), rms(h_prev, hnorm))  (llm/mtp.go:352-384)
     const LayerW& L = m->layers[c.n_layer];
-    EmbedParams ep{m->token_embd, ids_dev, e_buf, M, H, nullptr, nullptr, c.eps};
+    EmbedParams ep{m->token_embd, ids_dev, e_buf, M, H, nullptr, nullptr, c.eps, nullptr};
     B200_TRY(launch_embed(ep, st)); pdl();
     B200_TRY(launch_concat_norm(e_buf, hs_buf, (const float*)L.enorm.data, (const float*)L.hnorm.data, c.eps, H, M, xcat16, pdl(), st));
     QGemvParams p = base(L.eh_proj, 2 * H, H, xcat16, 2 * H);
     p.y = h; p.ldy = H;
-    B200_TRY(proj_with_tail(L.eh_proj.type, EPI_STORE, false, p, tail(1, L.attn_norm), 0));
+    if (fused) { p.ss_out = ss_part; ss_n = qgemv_groups(2 * H, H); }
+    B200_TRY(launch_qgemv(L.eh_proj.type, PRO_F16, EPI_STORE, false, false, p, no_tail, 0, pdl(), st));
+    if (!fused) B200_TRY(launch_row_tail(row_tail(1, L.attn_norm), pdl(), st));
   } else {
-    EmbedParams ep{m->token_embd, ids_dev, h, M, H, (const float*)m->layers[0].attn_norm.data, xn16, c.eps};
+    const LayerW& L0 = m->layers[0];
+    EmbedParams ep{m->token_embd, ids_dev, h, M, H, fused ? nullptr : (const float*)L0.attn_norm.data, xn16, c.eps, fused ? ss_part : nullptr};
     B200_TRY(launch_embed(ep, st)); pdl();
+    ss_n = 1;
   }
   for (int l = l0; l < l1; l++) {
     const LayerW& L = m->layers[l];
@@ -193,7 +198,8 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       QGemvParams p = base(L.qkv, H, cw + vw, xn16, H);
       p.w[1] = L.z.data; p.seg_end[0] = cw; p.seg_end[1] = cw + vw; p.nseg = 2;
       p.y = proj; p.ldy = proj_ld;
-      B200_TRY(launch_qgemv(L.qkv.type, EPI_STORE, false, false, p, no_tail, 0, pdl(), st));
+      const int pro = normed(p, L.attn_norm, xn16);  // the DeltaNet step reads the fp16 rows for alpha / beta
+      B200_TRY(launch_qgemv(L.qkv.type, pro, EPI_STORE, false, false, p, no_tail, 0, pdl(), st));
       DnStepParams d{};
       d.proj = proj; d.ldp = proj_ld; d.xn = xn16; d.alpha_w = (const float*)L.alpha.data; d.beta_w = (const float*)L.beta.data;
       d.conv_w = (const float*)L.conv1d.data; d.ssm_a = (const float*)L.ssm_a.data; d.dt_bias = (const float*)L.dt_bias.data;
@@ -204,7 +210,8 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       B200_TRY(launch_dn_step(d, pdl(), st));
       QGemvParams q = base(L.ssm_out, vw, H, y16, vw);
       q.y = h; q.ldy = H;
-      B200_TRY(proj_with_tail(L.ssm_out.type, EPI_RESID, false, q, tail(1, L.ffn_norm), 0));
+      if (fused) { q.ss_out = ss_part; ss_n = qgemv_groups(vw, H); }
+      B200_TRY(launch_qgemv(L.ssm_out.type, PRO_F16, EPI_RESID, false, false, q, no_tail, 0, pdl(), st));
     } else {
       const int ai = attn_index[l];
       // fused q|k|v projection; tensors of one type share a launch
@@ -219,7 +226,8 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
         for (int i = s; i < e; i++) { p.w[i - s] = seg[i]->data; n += rows[i]; p.seg_end[i - s] = n; }
         p.nseg = e - s; p.N = n;
         p.y = proj + off; p.ldy = proj_ld;
-        B200_TRY(launch_qgemv(seg[s]->type, EPI_STORE, false, false, p, no_tail, 0, pdl(), st));
+        const int pro = normed(p, L.attn_norm, nullptr);
+        B200_TRY(launch_qgemv(seg[s]->type, pro, EPI_STORE, false, false, p, no_tail, 0, pdl(), st));
         off += n; s = e;
       }
       AttnParams a{};
@@ -233,12 +241,15 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       B200_TRY(launch_attn_decode(a, pdl(), st));
       QGemvParams q = base(L.o, qw, H, ctx16, qw);
       q.y = h; q.ldy = H;
-      B200_TRY(proj_with_tail(L.o.type, EPI_RESID, false, q, tail(1, L.ffn_norm), 0));
+      if (fused) { q.ss_out = ss_part; ss_n = qgemv_groups(qw, H); }
+      B200_TRY(launch_qgemv(L.o.type, PRO_F16, EPI_RESID, false, false, q, no_tail, 0, pdl(), st));
     }
+    if (!fused) B200_TRY(launch_row_tail(row_tail(1, L.ffn_norm), pdl(), st));
     if (o.trace) { B200_CUDA(cudaMemcpyAsync(tr_mid + (size_t)l * MR * H, h, (size_t)M * H * sizeof(float), cudaMemcpyDeviceToDevice, st)); first = true; }
     // MoE block
     RouterParams r{};
     r.xn = xn16; r.router = L.router; r.sh_gate = (const float*)L.sh_gate_inp.data;
+    if (fused) { r.h = h; r.gamma = (const float*)L.ffn_norm.data; r.ss_in = ss_part; r.ss_n = ss_n; r.eps = c.eps; r.xn_out = xn16; }
     r.M = M; r.H = H; r.nE = c.n_expert; r.used = used; r.logits = r_logits; r.probs = nullptr; r.topk = topk; r.topk_w = topk_w;
     r.tl = tl(); r.margin = margin; r.entries = entries; r.n_entries = n_entries; r.cols = cols; r.ticket = r_ticket; r.max_entries = max_entries;
     B200_TRY(launch_router(r, pdl(), st));
@@ -247,13 +258,21 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     p.w2[0] = L.up_exps.data; p.ws = L.gate_sh.data; p.ws2 = L.up_sh.data; p.expert_stride = (int64_t)c.ffn_expert * L.gate_exps.stride;
     p.entries = entries; p.n_entries = n_entries; p.cols = cols; p.x_div = slots1;
     p.y16 = act16; p.ldy = c.ffn_expert;
-    B200_TRY(launch_qgemv(L.gate_exps.type, EPI_SWIGLU, true, true, p, no_tail, ne, pdl(), st));
+    B200_TRY(launch_qgemv(L.gate_exps.type, PRO_F16, EPI_SWIGLU, true, true, p, no_tail, ne, pdl(), st));
     QGemvParams q = base(L.down_exps, c.ffn_expert, H, act16, c.ffn_expert);
     q.ws = L.down_sh.data; q.expert_stride = (int64_t)H * L.down_exps.stride;
     q.entries = entries; q.n_entries = n_entries; q.cols = cols; q.x_div = 1;
     q.y = down; q.ldy = H;
-    const DTensor& next_norm = f.draft ? L.head_norm : (l + 1 < c.n_layer ? m->layers[l + 1].attn_norm : m->output_norm);
-    B200_TRY(proj_with_tail(L.down_exps.type, EPI_STORE, true, q, tail(2, next_norm), ne));
+    TailParams ct{};
+    if (fused) {
+      ct.mode = 1; ct.col_tickets = col_tickets; ct.h = h; ct.down = down; ct.topk_w = topk_w; ct.ss_part = ss_part; ct.used = used; ct.H = H; ct.M = M;
+      ss_n = qgemv_groups(c.ffn_expert, H);
+    }
+    B200_TRY(launch_qgemv(L.down_exps.type, PRO_F16, EPI_STORE, false, true, q, ct, ne, pdl(), st));
+    if (!fused) {
+      const DTensor& next_norm = f.draft ? L.head_norm : (l + 1 < c.n_layer ? m->layers[l + 1].attn_norm : m->output_norm);
+      B200_TRY(launch_row_tail(row_tail(2, next_norm), pdl(), st));
+    }
     if (o.trace) {
       B200_CUDA(cudaMemcpyAsync(tr_out + (size_t)l * MR * H, h, (size_t)M * H * sizeof(float), cudaMemcpyDeviceToDevice, st));
       B200_CUDA(cudaMemcpyAsync(tr_topk + (size_t)l * MR * used, topk, (size_t)M * used * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
@@ -263,12 +282,13 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     }
   }
   if (n_logit_rows > 0) {
-    // xn16 already holds output_norm(h) (or the draft's shared_head_norm) for every row
+    const DTensor& nrm = f.draft ? m->layers[c.n_layer].head_norm : m->output_norm;
     const int N = f.draft && draft_vocab > 0 ? draft_vocab : c.vocab;
     QGemvParams p = base(m->output, H, N, xn16, H);
     p.M = n_logit_rows; p.xcols = std::min(n_logit_rows, QG_MAXCOLS); p.row_ids = logit_rows;
     p.y = logits; p.ldy = N;
-    B200_TRY(launch_qgemv(m->output.type, EPI_STORE, false, false, p, no_tail, 0, pdl(), st));
+    const int pro = normed(p, nrm, nullptr);
+    B200_TRY(launch_qgemv(m->output.type, pro, EPI_STORE, false, false, p, no_tail, 0, pdl(), st));
     if (f.greedy) {
       B200_TRY(launch_argmax(logits, n_logit_rows, N, next_ids, pdl(), st));
       B200_TRY(launch_advance(ids_dev, next_ids, row_pos, seqs, M, history, hist_len, st)); launches++;

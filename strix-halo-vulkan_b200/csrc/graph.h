@@ -29,6 +29,8 @@ struct Graph {
   // activations
   float *h = nullptr, *proj = nullptr, *attn_partial = nullptr, *down = nullptr, *logits = nullptr, *e_buf = nullptr, *hs_buf = nullptr;
   __half *xn16 = nullptr, *q16 = nullptr, *ctx16 = nullptr, *act16 = nullptr, *y16 = nullptr, *xcat16 = nullptr;
+  float* ss_part = nullptr;   // [rows][SS_LD] partial sums of squares of the residual rows
+  int* col_tickets = nullptr;
   float *r_logits = nullptr, *r_probs = nullptr, *topk_w = nullptr, *margin = nullptr;
   int32_t *topk = nullptr, *ids_dev = nullptr, *next_ids = nullptr, *history = nullptr;
   int *attn_tickets = nullptr, *r_ticket = nullptr, *tail_ticket = nullptr, *err_flag = nullptr, *err_host = nullptr, *n_entries = nullptr, *cols = nullptr, *row_slot = nullptr, *row_pos = nullptr, *logit_rows = nullptr, *hist_len = nullptr;

@@ -182,7 +182,18 @@ __global__ void __launch_bounds__(QG_THREADS) embed_norm_kernel(EmbedParams p) {
   const int64_t id = p.ids[n];
   const uint8_t* row = p.embd.data + id * p.embd.stride;
   float* h = p.h + (size_t)n * p.H;
-  for (int k = threadIdx.x; k < p.H; k += blockDim.x) h[k] = dequant_elem(p.embd.type, row, p.H, k);
+  float sq = 0.f;
+  for (int k = threadIdx.x; k < p.H; k += blockDim.x) { const float v = dequant_elem(p.embd.type, row, p.H, k); h[k] = v; sq += v * v; }
+  if (p.ss_out != nullptr) {  // the first projection normalises from this
+    sq = warp_sum(sq);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = sq;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int w = 0; w < QG_WARPS; w++) t += scratch[w];
+      p.ss_out[(size_t)n * SS_LD] = t;
+    }
+  }
   if (p.gamma != nullptr) {
     __syncthreads();
     row_rmsnorm_f16(h, p.gamma, p.eps, p.H, p.xn + (size_t)n * p.H, scratch);
@@ -289,13 +300,35 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   pdl_wait();
   pdl_launch();
   tl_mark(p.tl, 1);
+  extern __shared__ __align__(16) __half rxs[];  // [M][H] when the rows are normalised here
+  __shared__ float rscale[8];
+  const bool staged = p.h != nullptr;
+  if (staged) {  // ffn_norm fused into the router (M <= 8): every CTA normalises the rows, CTA 0 keeps a copy
+    if (warp < M) {
+      const float sc = scale_from_parts(p.ss_in, p.ss_n, warp, H, p.eps);
+      if (lane == 0) rscale[warp] = sc;
+    }
+    __syncthreads();
+    for (int n = 0; n < M; n++) {
+      const float scale = rscale[n];
+      for (int k = tid * 4; k < H; k += 1024) {
+        const float4 hv = __ldcg(reinterpret_cast<const float4*>(p.h + (size_t)n * H + k));
+        const float4 g = *reinterpret_cast<const float4*>(p.gamma + k);
+        __half2 a = __floats2half2_rn(hv.x * scale * g.x, hv.y * scale * g.y), b = __floats2half2_rn(hv.z * scale * g.z, hv.w * scale * g.w);
+        const uint2 o = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+        *reinterpret_cast<uint2*>(rxs + (size_t)n * H + k) = o;
+        if (blockIdx.x == 0 && p.xn_out != nullptr) *reinterpret_cast<uint2*>(p.xn_out + (size_t)n * H + k) = o;
+      }
+    }
+    __syncthreads();
+  }
   if (row <= p.nE) {
     for (int n = 0; n < M; n++) {
-      const __half* x = p.xn + (size_t)n * H;
+      const __half* x = staged ? rxs + (size_t)n * H : p.xn + (size_t)n * H;
       float acc = 0.f;
       if (row == p.nE) {
         for (int k = lane * 8; k < H; k += 256) {
-          uint4 xv = __ldcg(reinterpret_cast<const uint4*>(x + k));
+          uint4 xv = *reinterpret_cast<const uint4*>(x + k);
           const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
           float4 g0 = *reinterpret_cast<const float4*>(p.sh_gate + k), g1 = *reinterpret_cast<const float4*>(p.sh_gate + k + 4);
           acc = fmaf(g0.x, h2f_lo(xw[0]), acc); acc = fmaf(g0.y, h2f_hi(xw[0]), acc); acc = fmaf(g0.z, h2f_lo(xw[1]), acc); acc = fmaf(g0.w, h2f_hi(xw[1]), acc);
@@ -306,7 +339,7 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
         for (int i = 0; i < 8; i++) {
           const int k0 = lane * 16 + i * 512;
           if (k0 < H) {
-            uint4 xa = __ldcg(reinterpret_cast<const uint4*>(x + k0)), xb = __ldcg(reinterpret_cast<const uint4*>(x + k0 + 8));
+            uint4 xa = *reinterpret_cast<const uint4*>(x + k0), xb = *reinterpret_cast<const uint4*>(x + k0 + 8);
             const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
             const uint32_t w[4] = {wq[i].x, wq[i].y, wq[i].z, wq[i].w};
 #pragma unroll
@@ -397,7 +430,15 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
 int launch_router(const RouterParams& p, bool pdl, cudaStream_t st) {
   if (p.nE > 1024 || p.used > 32 || p.H % 8) { set_error("router: shape outside kernel limits"); return ECAPACITY; }
   int grid = (p.nE + 1 + RT_ROWS - 1) / RT_ROWS;
-  return launch_k(router_kernel, dim3(grid), dim3(256), 0, pdl, st, p);
+  size_t smem = 0;
+  if (p.h != nullptr) {
+    if (p.M > 8) { set_error("router: the fused norm handles at most 8 rows"); return EINVAL_; }
+    smem = (size_t)p.M * p.H * sizeof(__half);
+    static size_t configured = 0;
+    if (smem > configured) { B200_CUDA(cudaFuncSetAttribute(router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); configured = 200 * 1024; }
+    if (smem > 200 * 1024) { set_error("router: rows too long for shared memory"); return ECAPACITY; }
+  }
+  return launch_k(router_kernel, dim3(grid), dim3(256), smem, pdl, st, p);
 }
 
 // Stand-alone forms of the row tails, one CTA per row, for passes of more than QG_TAIL_ROWS rows.

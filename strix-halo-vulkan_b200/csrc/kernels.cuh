@@ -28,16 +28,20 @@ struct EmbedParams {
   const float* gamma;  // optional: the first consumer's norm weights
   __half* xn;          // [M][H] fp16 normalised rows (when gamma is given)
   float eps;
+  float* ss_out;       // optional: sum of squares of each row, [M][SS_LD] part 0
 };
 int launch_embed(const EmbedParams& p, cudaStream_t st);
 
 // K-quant projections; `pdl` marks the launch as a programmatic dependent of the previous kernel.
-int launch_qgemv(uint32_t type, int epi, bool dual, bool grouped, const QGemvParams& p, const TailParams& tp, int max_entries, bool pdl, cudaStream_t st);
+int launch_qgemv(uint32_t type, int pro, int epi, bool dual, bool grouped, const QGemvParams& p, const TailParams& tp, int max_entries, bool pdl, cudaStream_t st);
+int qgemv_groups(int K, int N);
 int launch_row_tail(const TailParams& tp, bool pdl, cudaStream_t st);
 int launch_concat_norm(const float* e, const float* hs, const float* enorm, const float* hnorm, float eps, int H, int M, __half* xcat, bool pdl, cudaStream_t st);
 
 struct RouterParams {
-  const __half* xn;                                // [M][H] ffn_norm output, fp16
+  const __half* xn;                                // [M][H] ffn_norm output, fp16 (when h is null)
+  const float* h; const float* gamma; const float* ss_in; int ss_n; float eps;  // or: normalise the residual rows here
+  __half* xn_out;                                  // ... and leave the fp16 rows for the expert kernels (CTA 0)
   DTensor router;                                  // [nE][H], F32 / F16 / Q8_0 (planes)
   const float* sh_gate;                            // [H] F32
   int M, H, nE, used;

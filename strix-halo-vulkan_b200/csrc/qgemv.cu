@@ -5,9 +5,9 @@ namespace b200 {
 
 static int g_sm_count = 0;
 
-template <int TYPE, int EPI, bool DUAL, bool GROUPED>
+template <int TYPE, int PRO, int EPI, bool DUAL, bool GROUPED>
 static int launch_one(const QGemvParams& p, const TailParams& tp, int max_entries, bool pdl, cudaStream_t st) {
-  auto kernel = qgemv_kernel<TYPE, EPI, DUAL, GROUPED>;
+  auto kernel = qgemv_kernel<TYPE, PRO, EPI, DUAL, GROUPED>;
   if (g_sm_count == 0) {
     int dev = 0;
     B200_CUDA(cudaGetDevice(&dev));
@@ -55,26 +55,36 @@ static int launch_one(const QGemvParams& p, const TailParams& tp, int max_entrie
 }
 
 template <int TYPE>
-static int launch_type(int epi, bool dual, bool grouped, const QGemvParams& p, const TailParams& tp, int max_entries, bool pdl, cudaStream_t st) {
+static int launch_type(int pro, int epi, bool dual, bool grouped, const QGemvParams& p, const TailParams& tp, int max_entries, bool pdl, cudaStream_t st) {
   if (!grouped && !dual) {
-    if (epi == EPI_STORE) return launch_one<TYPE, EPI_STORE, false, false>(p, tp, 0, pdl, st);
-    if (epi == EPI_RESID) return launch_one<TYPE, EPI_RESID, false, false>(p, tp, 0, pdl, st);
-  } else if (grouped) {
-    if (dual && epi == EPI_SWIGLU) return launch_one<TYPE, EPI_SWIGLU, true, true>(p, tp, max_entries, pdl, st);
-    if (!dual && epi == EPI_STORE) return launch_one<TYPE, EPI_STORE, false, true>(p, tp, max_entries, pdl, st);
+    if (pro == PRO_NORM && epi == EPI_STORE) return launch_one<TYPE, PRO_NORM, EPI_STORE, false, false>(p, tp, 0, pdl, st);
+    if (pro == PRO_F16 && epi == EPI_STORE) return launch_one<TYPE, PRO_F16, EPI_STORE, false, false>(p, tp, 0, pdl, st);
+    if (pro == PRO_F16 && epi == EPI_RESID) return launch_one<TYPE, PRO_F16, EPI_RESID, false, false>(p, tp, 0, pdl, st);
+  } else if (grouped && pro == PRO_F16) {
+    if (dual && epi == EPI_SWIGLU) return launch_one<TYPE, PRO_F16, EPI_SWIGLU, true, true>(p, tp, max_entries, pdl, st);
+    if (!dual && epi == EPI_STORE) return launch_one<TYPE, PRO_F16, EPI_STORE, false, true>(p, tp, max_entries, pdl, st);
   }
-  set_error("qgemv: this epilogue combination is not built");
+  set_error("qgemv: this prologue / epilogue combination is not built");
   return EINVAL_;
 }
 
-int launch_qgemv(uint32_t type, int epi, bool dual, bool grouped, const QGemvParams& p, const TailParams& tp, int max_entries, bool pdl, cudaStream_t st) {
+// tile groups a projection of N rows of length K is cut into (= partial sums of squares it leaves per row)
+int qgemv_groups(int K, int N) {
+  const int nb = K / 256;
+  const int wpt = nb >= 8 ? 8 : nb >= 4 ? 4 : nb >= 2 ? 2 : 1;
+  const int tpc = QG_WARPS / wpt;
+  return ((N + 15) / 16 + tpc - 1) / tpc;
+}
+
+int launch_qgemv(uint32_t type, int pro, int epi, bool dual, bool grouped, const QGemvParams& p, const TailParams& tp, int max_entries, bool pdl, cudaStream_t st) {
   if (p.K % 256 != 0 || p.K <= 0) { set_error("qgemv: row length must be a multiple of 256"); return EINVAL_; }
   if (p.xcols < 1 || p.xcols > QG_MAXCOLS) { set_error("qgemv: xcols out of range"); return EINVAL_; }
-  if (tp.mode != 0 && tp.M > QG_TAIL_ROWS) { set_error("qgemv: the in-kernel tail handles at most 8 rows"); return EINVAL_; }
+  if ((p.ss_out != nullptr || tp.mode == 1) && qgemv_groups(p.K, p.N) > SS_LD) { set_error("qgemv: more tile groups than partial-sum slots"); return ECAPACITY; }
+  if (pro == PRO_NORM && (p.ss_n < 1 || p.ss_n > SS_LD)) { set_error("qgemv: bad partial-sum count"); return EINVAL_; }
   switch (type) {
-    case T_Q4_K: return launch_type<T_Q4_K>(epi, dual, grouped, p, tp, max_entries, pdl, st);
-    case T_Q5_K: return launch_type<T_Q5_K>(epi, dual, grouped, p, tp, max_entries, pdl, st);
-    case T_Q6_K: return launch_type<T_Q6_K>(epi, dual, grouped, p, tp, max_entries, pdl, st);
+    case T_Q4_K: return launch_type<T_Q4_K>(pro, epi, dual, grouped, p, tp, max_entries, pdl, st);
+    case T_Q5_K: return launch_type<T_Q5_K>(pro, epi, dual, grouped, p, tp, max_entries, pdl, st);
+    case T_Q6_K: return launch_type<T_Q6_K>(pro, epi, dual, grouped, p, tp, max_entries, pdl, st);
   }
   set_error("qgemv: weight type has no fused projection kernel (Q4_K, Q5_K, Q6_K only)");
   return EINVAL_;

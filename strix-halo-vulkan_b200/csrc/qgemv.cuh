@@ -29,6 +29,8 @@ constexpr int QG_MAXCOLS = 8;
 constexpr int QG_TAIL_ROWS = 8;  // rows the in-kernel tail of the last CTA finishes
 
 enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
+enum { PRO_F16 = 0, PRO_NORM = 1 };
+constexpr int SS_LD = 512;  // partial sums of squares kept per activation row
 
 struct QGemvParams {
   // weights: up to 4 row segments of one fused projection (same type and K)
@@ -53,9 +55,18 @@ struct QGemvParams {
   int* err;                  // device error word: set when a bounded wait gives up
   Timeline tl;
   const int* row_ids;        // optional: plain mode column c reads row row_ids[c] and writes row c
-  // activations: fp16 rows in natural order
+  // activations. PRO_F16: fp16 rows in natural order. PRO_NORM: the f32 residual rows `hsrc`, normalised
+  // while they are staged: x = fp16(h * gamma / sqrt(sum(ss_in[row][0..ss_n)) / K + eps)); the sums of
+  // squares arrive as per-CTA partials from the kernel that wrote h, added in a fixed order
   const __half* x;
   int64_t ldx;
+  const float* hsrc;
+  const float* gamma;
+  const float* ss_in;
+  int ss_n;
+  float eps;
+  __half* xn_out;            // PRO_NORM: optional copy of the normalised rows, [.][K], written by CTA 0
+  float* ss_out;             // STORE / RESID: optional partial sums of squares of the rows written, [.][SS_LD], part = tile group
   // epilogue
   float* y;                  // STORE / RESID: float [.][ldy]
   int64_t ldy;
@@ -385,14 +396,17 @@ __device__ __forceinline__ void row_moe_combine(float* h, const float* down, con
 }
 
 struct TailParams {
-  int mode;             // 0 none, 1 rmsnorm of the residual rows, 2 MoE combine then rmsnorm
-  int* ticket;
+  int mode;             // 0 none; 1 (grouped down projection): the last CTA of each grid column adds the
+                        // weighted expert outputs of its rows into the residual and leaves their sum of squares
+  int* col_tickets;     // [gridDim.x]
   float* h;             // [M][H] residual stream
-  const float* gamma;   // norm weights of the consumer
-  __half* xn;           // [M][H] normalised rows, fp16, natural order
-  const float* down;    // mode 2: [M][used+1][H]
-  const float* topk_w;  // mode 2: [M][used+1]
+  const float* down;    // [M][used+1][H]
+  const float* topk_w;  // [M][used+1]
+  float* ss_part;       // [M][SS_LD]
   int used, H, M;
+  // stand-alone row tails (row_tail_kernel): 1 rmsnorm, 2 combine + rmsnorm
+  const float* gamma;
+  __half* xn;
   float eps;
 };
 
@@ -400,23 +414,10 @@ struct TailParams {
 // Copies `ncols` fp16 activation rows into shared memory in the permuted, padded layout the
 // B fragments are read in, and forms the per-sub-block sums (fp16 hi + lo planes) of the min
 // term. sxs layout: [plane(2)][xcols][K/32] halves.
-__device__ __forceinline__ void stage_x_f16(const __half* x, int64_t ldx, int K, int xcols, uint8_t* xs, __half* sxs, int ncols, const int* xrows,
-                                            int xstride) {
-  const int tid = threadIdx.x;
-  for (int c = 0; c < ncols; c++) {
-    const __half* src = x + (int64_t)xrows[c] * ldx;
-    uint8_t* dst = xs + (size_t)c * xstride;
-    for (int k = tid * 8; k < K; k += QG_THREADS * 8) {
-      uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + k));
-      uint4 o;
-      o.x = __byte_perm(v.x, v.y, 0x5410); o.y = __byte_perm(v.x, v.y, 0x7632);
-      o.z = __byte_perm(v.z, v.w, 0x5410); o.w = __byte_perm(v.z, v.w, 0x7632);
-      *reinterpret_cast<uint4*>(dst + 2 * k + 16 * (k >> 6)) = o;
-    }
-  }
-  __syncthreads();
+// sub-block sums of the staged fp16 values, as fp16 hi + lo planes
+__device__ __forceinline__ void stage_sx(int K, int xcols, const uint8_t* xs, __half* sxs, int ncols, int xstride) {
   const int nsub = K / 32;
-  for (int i = tid; i < ncols * nsub; i += QG_THREADS) {
+  for (int i = threadIdx.x; i < ncols * nsub; i += QG_THREADS) {
     const int c = i / nsub, s = i - c * nsub;
     const uint8_t* src = xs + (size_t)c * xstride + 64 * s + 16 * (s >> 1);
     float sum = 0.f;
@@ -435,6 +436,73 @@ __device__ __forceinline__ void stage_x_f16(const __half* x, int64_t ldx, int K,
   __syncthreads();
 }
 
+__device__ __forceinline__ void stage_x_f16(const __half* x, int64_t ldx, int K, int xcols, uint8_t* xs, __half* sxs, int ncols, const int* xrows,
+                                            int xstride) {
+  const int tid = threadIdx.x;
+  for (int c = 0; c < ncols; c++) {
+    const __half* src = x + (int64_t)xrows[c] * ldx;
+    uint8_t* dst = xs + (size_t)c * xstride;
+    for (int k = tid * 8; k < K; k += QG_THREADS * 8) {
+      uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + k));
+      uint4 o;
+      o.x = __byte_perm(v.x, v.y, 0x5410); o.y = __byte_perm(v.x, v.y, 0x7632);
+      o.z = __byte_perm(v.z, v.w, 0x5410); o.w = __byte_perm(v.z, v.w, 0x7632);
+      *reinterpret_cast<uint4*>(dst + 2 * k + 16 * (k >> 6)) = o;
+    }
+  }
+  __syncthreads();
+  stage_sx(K, xcols, xs, sxs, ncols, xstride);
+}
+
+// 1 / sqrt(mean(h^2) + eps) of row `row` from the partial sums its producer left, by one warp
+__device__ __forceinline__ float scale_from_parts(const float* ss_in, int ss_n, int64_t row, int K, float eps) {
+  float s = 0.f;
+  for (int i = threadIdx.x & 31; i < ss_n; i += 32) s += __ldcg(ss_in + row * SS_LD + i);
+  s = warp_sum(s);
+  return 1.0f / sqrtf(s / (float)K + eps);
+}
+
+// RMSNorm fused into the staging (reference: llm/hc.go:176-190): each CTA normalises the rows it needs
+__device__ __forceinline__ void stage_x_norm(const QGemvParams& p, uint8_t* xs, __half* sxs, float* scratch, int ncols, const int* xrows, int xstride,
+                                             bool write_xn) {
+  const int tid = threadIdx.x, warp = tid >> 5, K = p.K;
+  // the residual values do not depend on the scale: fetch the first batch before reducing the partials
+  constexpr int PRE = 2;
+  float4 hpre[PRE], gpre[PRE];
+  const float* src0 = p.hsrc + (int64_t)xrows[0] * K;
+#pragma unroll
+  for (int i = 0; i < PRE; i++) {
+    const int k = tid * 4 + i * QG_THREADS * 4;
+    if (k < K) { hpre[i] = __ldcg(reinterpret_cast<const float4*>(src0 + k)); gpre[i] = *reinterpret_cast<const float4*>(p.gamma + k); }
+  }
+  if (warp < ncols) {
+    const float sc = scale_from_parts(p.ss_in, p.ss_n, xrows[warp], K, p.eps);
+    if ((tid & 31) == 0) scratch[warp] = sc;
+  }
+  __syncthreads();
+  for (int c = 0; c < ncols; c++) {
+    const int64_t row = xrows[c];
+    const float* src = p.hsrc + row * (int64_t)K;
+    const float scale = scratch[c];
+    uint8_t* dst = xs + (size_t)c * xstride;
+    int i = 0;
+    for (int k = tid * 4; k < K; k += QG_THREADS * 4, i++) {
+      float4 h, g;
+      if (c == 0 && i < PRE) { h = hpre[i < PRE ? i : 0]; g = gpre[i < PRE ? i : 0]; }
+      else { h = __ldcg(reinterpret_cast<const float4*>(src + k)); g = *reinterpret_cast<const float4*>(p.gamma + k); }
+      const float v0 = h.x * scale * g.x, v1 = h.y * scale * g.y, v2 = h.z * scale * g.z, v3 = h.w * scale * g.w;
+      __half2 a = __floats2half2_rn(v0, v2), b = __floats2half2_rn(v1, v3);  // stored order [x0,x2,x1,x3]
+      *reinterpret_cast<uint2*>(dst + 2 * k + 16 * (k >> 6)) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+      if (write_xn) {
+        __half2 n0 = __floats2half2_rn(v0, v1), n1 = __floats2half2_rn(v2, v3);
+        *reinterpret_cast<uint2*>(p.xn_out + row * K + k) = make_uint2(*reinterpret_cast<uint32_t*>(&n0), *reinterpret_cast<uint32_t*>(&n1));
+      }
+    }
+  }
+  __syncthreads();
+  stage_sx(K, p.xcols, xs, sxs, ncols, xstride);
+}
+
 // ---- the kernel ----------------------------------------------------------------------------
 // grid.x: persistent CTAs walking the row-tile groups; grid.y: expert entry (grouped) or 0;
 // grid.z: column tile of 8 activation rows (plain mode).
@@ -442,7 +510,7 @@ __device__ __forceinline__ void stage_x_f16(const __half* x, int64_t ldx, int K,
 // Weights reach the SM as whole tiles (16 consecutive rows are one contiguous run of the
 // checkpoint's own blocks) through cp.async.bulk into a ring of shared-memory stages, each
 // completing on its mbarrier, so many tiles are in flight per SM without holding registers.
-template <int TYPE, int EPI, bool DUAL, bool GROUPED>
+template <int TYPE, int PRO, int EPI, bool DUAL, bool GROUPED>
 __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, const TailParams tp) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -459,6 +527,7 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
   const size_t stage_bytes = (size_t)tpc * tile_bytes * (DUAL ? 2 : 1);
   const int NS = p.nstage;
   __shared__ float scratch[2 * QG_WARPS];
+  __shared__ float ssq[2][QG_WARPS][8];
   __shared__ int col_rows[QG_MAXCOLS], xrows[QG_MAXCOLS];
   __shared__ int is_last;
   __shared__ __align__(8) uint64_t full_bar[QG_MAX_STAGES];
@@ -535,7 +604,8 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
       xrows[tid] = GROUPED ? id / p.x_div : id;
     }
     __syncthreads();
-    stage_x_f16(p.x, p.ldx, K, p.xcols, xs, sxs, ncols, xrows, xstride);
+    if constexpr (PRO == PRO_NORM) stage_x_norm(p, xs, sxs, scratch, ncols, xrows, xstride, p.xn_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0);
+    else stage_x_f16(p.x, p.ldx, K, p.xcols, xs, sxs, ncols, xrows, xstride);
     tl_mark(p.tl, 2);
 
     const bool live = g < ncols;
@@ -585,6 +655,7 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
         if (next < ngroups) { fence_proxy_async(); issue_group(next, s); }
       }
       const float* rb = red + (size_t)buf * RED;
+      float sq = 0.f;  // this thread's column is tid & 7 in every iteration
       for (int i = tid; i < tpc * 128; i += QG_THREADS) {
         const int l2 = i >> 7, rc = i & 127, r = rc >> 3, c = rc & 7;
         const int grow = (grp * tpc + l2) * 16 + r;
@@ -595,37 +666,75 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
           if constexpr (DUAL) v2 += rb[(size_t)(QG_WARPS + l2 * wpt + w) * 128 + rc];
         }
         const int64_t orow = (!GROUPED && p.row_ids != nullptr) ? col_off + c : col_rows[c];
-        if constexpr (EPI == EPI_STORE) p.y[orow * p.ldy + grow] = v;
-        else if constexpr (EPI == EPI_RESID) p.y[orow * p.ldy + grow] += v;
+        if constexpr (EPI == EPI_STORE) { p.y[orow * p.ldy + grow] = v; sq += v * v; }
+        else if constexpr (EPI == EPI_RESID) { const float nv = p.y[orow * p.ldy + grow] + v; p.y[orow * p.ldy + grow] = nv; sq += nv * nv; }
         else {  // SwiGLU of (gate, up) rounded to fp16 (reference: shaders/llm_moe_gemv.comp:777-781)
           float sw = v * sigmoid_acc(v) * v2;
           p.y16[orow * p.ldy + grow] = __float2half_rn(sw);
+        }
+      }
+      if constexpr (EPI != EPI_SWIGLU && !GROUPED) {
+        if (p.ss_out != nullptr) {  // sum of squares of this group's rows per column, in a fixed order
+          sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+          sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+          if (lane < 8) ssq[buf][warp][lane] = sq;
+          __syncthreads();
+          if (tid < ncols) {
+            float t2 = 0.f;
+#pragma unroll
+            for (int w = 0; w < QG_WARPS; w++) t2 += ssq[buf][w][tid];
+            const int64_t orow = p.row_ids != nullptr ? col_off + tid : col_rows[tid];
+            p.ss_out[orow * SS_LD + grp] = t2;
+          }
         }
       }
       buf ^= 1;
     }
   }
   tl_mark(p.tl, 4);
-  // tail: the last CTA of the grid finishes the rows (residual norm / MoE combine + norm)
-  if (tp.mode != 0) {
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) is_last = (atomicAdd(tp.ticket, 1) == (int)(gridDim.x * gridDim.y * gridDim.z) - 1);
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    if (tid == 0) *tp.ticket = 0;
-    tl_mark(p.tl, 5, true);
-    const int slots1 = tp.used + 1;
-    for (int n = 0; n < tp.M; n++) {
-      float* hrow = tp.h + (size_t)n * tp.H;
-      if (tp.mode == 2) {
-        row_moe_combine(hrow, tp.down + (size_t)n * slots1 * tp.H, tp.topk_w + (size_t)n * slots1, tp.used, tp.H);
-        __syncthreads();
+  // tail of the expert down projection: the last CTA of each grid column owns that column's row groups
+  // for every expert, so it can add the weighted expert outputs into the residual (slot order, then the
+  // gated shared expert: llm/moe.go:347-357, 403-406) without waiting for the other columns
+  if constexpr (GROUPED && EPI == EPI_STORE) {
+    if (tp.mode == 1) {
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) is_last = (atomicAdd(tp.col_tickets + blockIdx.x, 1) == (int)gridDim.y - 1);
+      __syncthreads();
+      if (!is_last) return;
+      __threadfence();
+      if (tid == 0) tp.col_tickets[blockIdx.x] = 0;
+      tl_mark(p.tl, 5, true);
+      const int slots1 = tp.used + 1, rows_per_group = tpc * 16;
+      for (int grp = blockIdx.x; grp < ngroups; grp += gridDim.x) {
+        for (int n = 0; n < tp.M; n++) {
+          float sq = 0.f;
+          for (int r = tid; r < rows_per_group; r += QG_THREADS) {
+            const int row = grp * rows_per_group + r;
+            if (row < tp.H) {
+              const float* dn = tp.down + (size_t)n * slots1 * tp.H + row;
+              const float* w = tp.topk_w + (size_t)n * slots1;
+              float acc = 0.f;
+              for (int k = 0; k < tp.used; k++) acc += __ldcg(dn + (size_t)k * tp.H) * w[k];
+              const float nv = tp.h[(size_t)n * tp.H + row] + (acc + __ldcg(dn + (size_t)tp.used * tp.H) * w[tp.used]);
+              tp.h[(size_t)n * tp.H + row] = nv;
+              sq += nv * nv;
+            }
+          }
+          sq = warp_sum(sq);
+          __syncthreads();
+          if (lane == 0) scratch[warp] = sq;
+          __syncthreads();
+          if (tid == 0) {
+            float t2 = 0.f;
+#pragma unroll
+            for (int w = 0; w < QG_WARPS; w++) t2 += scratch[w];
+            tp.ss_part[(size_t)n * SS_LD + grp] = t2;
+          }
+        }
       }
-      row_rmsnorm_f16(hrow, tp.gamma, tp.eps, tp.H, tp.xn + (size_t)n * tp.H, scratch);
+      tl_mark(p.tl, 6, true);
     }
-    tl_mark(p.tl, 6, true);
   }
 }
 
