@@ -225,23 +225,6 @@ def main():
     t0 = time.time()
     model = pkg.Model.synthetic(cfg, seed=0, device=local_rank)
     t_model = time.time() - t0
-    n_kv = prompt_len + 2 * (steps + warmup) + 64
-    g = pkg.Graph(model, n_kv=n_kv, max_tokens=64, slots=1, use_cuda_graph=not args.profile)
-    if args.profile_batch:
-        g.destroy()
-    rng = np.random.default_rng(1 + rank)
-    prompt = rng.integers(0, cfg["vocab"], prompt_len).astype(np.int32)
-    t0 = time.time()
-    logits, _ = g.forward(prompt)
-    t_prefill = time.time() - t0
-    tok = int(np.argmax(logits))
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
     if args.profile_batch:
         gb = pkg.Graph(model, n_kv=32768 + 64, max_tokens=max(args.slots, 8), slots=args.slots, use_cuda_graph=False)
         ctx = np.random.default_rng(7).integers(8192, 32769, args.slots)
@@ -256,6 +239,21 @@ def main():
         torch.cuda.profiler.stop()
         print(json.dumps({"profiled_batch_steps": args.profile_batch, "slots": args.slots}))
         return
+    n_kv = prompt_len + 2 * (steps + warmup) + 64
+    g = pkg.Graph(model, n_kv=n_kv, max_tokens=64, slots=1, use_cuda_graph=not args.profile)
+    rng = np.random.default_rng(1 + rank)
+    prompt = rng.integers(0, cfg["vocab"], prompt_len).astype(np.int32)
+    t0 = time.time()
+    logits, _ = g.forward(prompt)
+    t_prefill = time.time() - t0
+    tok = int(np.argmax(logits))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
     if args.profile:
         for _ in range(3):
             logits, _ = g.extend([tok]); tok = int(np.argmax(logits))

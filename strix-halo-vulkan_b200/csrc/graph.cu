@@ -50,7 +50,8 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   if (o.speculative && o.spec_rows <= 0) o.spec_rows = 3;
   if (o.spec_rows > DN_RING - 3) { set_error("graph: spec_rows is limited to 5 (the conv ring keeps 8 positions)"); return ECAPACITY; }
   MR = std::min(o.max_tokens, 512);
-  split_cells = o.attn_split_cells > 0 ? o.attn_split_cells : 64;
+  // a CTA's four warps take 16 cells each per round; longer contexts get longer splits so the merge stays short
+  split_cells = o.attn_split_cells > 0 ? (o.attn_split_cells + 15) / 16 * 16 : (o.n_kv <= 4096 ? 64 : o.n_kv <= 8192 ? 128 : o.n_kv <= 16384 ? 256 : 512);
   nsplit = (o.n_kv + split_cells - 1) / split_cells;
   B200_CUDA(cudaSetDevice(m->device));
   B200_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
@@ -239,6 +240,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       B200_TRY(launch_attn_pack(a, pdl(), st));
       a.tl = tl();
       B200_TRY(launch_attn_decode(a, pdl(), st));
+      B200_TRY(launch_attn_merge(a, pdl(), st));
       QGemvParams q = base(L.o, qw, H, ctx16, qw);
       q.y = h; q.ldy = H;
       if (fused) { q.ss_out = ss_part; ss_n = qgemv_groups(qw, H); }

@@ -700,20 +700,33 @@ int launch_attn_pack(const AttnParams& p, bool pdl, cudaStream_t st) {
 // =========================================================================================
 // Split-KV decode attention (reference: llm/attn.go:190-217, 444-496;
 // shaders/llm_attn_wmma.comp -DSPLITK, llm_attn_combine.comp). grid (nsplit, Hkv, M):
-// a CTA of 8 warps covers `split_cells` cells of one KV head for the G query heads that
-// share it; a lane owns hd/32 dims. The last CTA of a (row, kv head) merges the splits,
-// applies sigmoid(gate) and writes the fp16 context.
+// a CTA of 4 warps covers `split_cells` cells of one KV head for the G query heads that
+// share it.
 // =========================================================================================
-constexpr int AT_WARPS = 8, AT_THREADS = AT_WARPS * 32;
-template <int DPL, int G>  // dims per lane, query heads per kv head
-__global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnParams p) {
-  const int hd = DPL * 32;
+// -----------------------------------------------------------------------------------------
+// Tensor-core form of the same split-KV decode attention. A warp walks 16 cells at a time:
+//   S = Q K^T   as mma.m16n8k16 with the G query heads of the KV group on the M axis (the reference's
+//               HROWS idea, shaders/llm_attn_wmma.comp:161-190) and 8 cells on N; a lane reads 16 bytes
+//               of a K row (the dot product does not care which head dims share a k-slot, so the k-slots
+//               are assigned to whatever 8 dims a lane's load covers, in Q and K alike);
+//   P = exp(S * scale - m), rounded to fp16 (reference: shaders/llm_attn_wmma.comp:860);
+//   O += P V    with the score tile's C registers reused as the A fragment, and V pairs of two cells
+//               packed per dim with byte permutes (an in-register transpose; no shared-memory staging).
+// Online softmax per warp, warps merged in shared memory, splits merged by attn_merge_kernel.
+// -----------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int HD, int G>
+__global__ void __launch_bounds__(128) attn_mma_kernel(AttnParams p) {
+  constexpr int KS = HD / 16;   // k-steps of the score mma
+  constexpr int NB = HD / 64;   // 64-dim blocks of the value mma
   const int split = blockIdx.x, kvh = blockIdx.y, n = blockIdx.z;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  __shared__ float sm_m[AT_WARPS][G], sm_l[AT_WARPS][G];
-  extern __shared__ __align__(16) float sm_o_dyn[];  // [AT_WARPS][G][hd]
-  float (*sm_o)[G][DPL * 32] = reinterpret_cast<float (*)[G][DPL * 32]>(sm_o_dyn);
-  __shared__ int is_last;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  __shared__ float sm_m[4][G], sm_l[4][G];
+  __shared__ float sm_o[4][G][HD];
   tl_mark(p.tl, 0);
   pdl_wait();
   pdl_launch();
@@ -721,175 +734,158 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnParams p) {
   const int pos = p.row_pos[n], slot = p.row_slot[n];
   const int ncell = pos + 1;
   const int c0 = split * p.split_cells, c1 = min(ncell, c0 + p.split_cells);
-  const float scale = 1.0f / sqrtf((float)hd);
-  float q[G][DPL], o[G][DPL], m[G], l[G];
+  const float scale = 1.0f / sqrtf((float)HD);
+  const size_t cell_stride = (size_t)p.Hkv * HD;
+  const __half* kbase = p.kcache + (size_t)slot * p.slot_stride + (size_t)kvh * HD;
+  const __half* vbase = p.vcache + (size_t)slot * p.slot_stride + (size_t)kvh * HD;
+  // query A fragments: head g of the group on row g; rows 8..15 stay zero
+  uint32_t qa[KS][2];
 #pragma unroll
-  for (int hh = 0; hh < G; hh++) {
-    const __half* qp = p.q16 + ((size_t)n * p.Hq + kvh * G + hh) * hd + lane * DPL;
-#pragma unroll
-    for (int d = 0; d < DPL; d++) { q[hh][d] = __half2float(qp[d]); o[hh][d] = 0.f; }
-    m[hh] = -INFINITY; l[hh] = 0.f;
+  for (int j = 0; j < KS / 2; j++) {
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (g < G) v = *reinterpret_cast<const uint4*>(p.q16 + ((size_t)n * p.Hq + kvh * G + g) * HD + 8 * (t + 4 * j));
+    qa[2 * j][0] = v.x; qa[2 * j][1] = v.y; qa[2 * j + 1][0] = v.z; qa[2 * j + 1][1] = v.w;
   }
-  const __half* kc = p.kcache + (size_t)slot * p.slot_stride + (size_t)kvh * hd + lane * DPL;
-  const __half* vc = p.vcache + (size_t)slot * p.slot_stride + (size_t)kvh * hd + lane * DPL;
-  const size_t cell_stride = (size_t)p.Hkv * hd;
-  // a warp walks cells c0 + warp, + AT_WARPS, ...; the K and V rows of up to ATT_PF cells are
-  // fetched together so their DRAM latencies overlap
-  constexpr int ATT_PF = 4;
-  for (int cb = c0 + warp; cb < c1; cb += AT_WARPS * ATT_PF) {
-    uint4 kraw[ATT_PF], vraw[ATT_PF];
+  float o[HD / 8][2];
 #pragma unroll
-    for (int u = 0; u < ATT_PF; u++) {
-      const int c = cb + u * AT_WARPS;
-      if (c < c1) {
-        if constexpr (DPL == 8) {
-          kraw[u] = ldg_stream(kc + (size_t)c * cell_stride);
-          vraw[u] = ldg_stream(vc + (size_t)c * cell_stride);
-        } else {
-          const uint2 a = *reinterpret_cast<const uint2*>(kc + (size_t)c * cell_stride), b = *reinterpret_cast<const uint2*>(vc + (size_t)c * cell_stride);
-          kraw[u] = make_uint4(a.x, a.y, 0, 0); vraw[u] = make_uint4(b.x, b.y, 0, 0);
-        }
-      }
+  for (int i = 0; i < HD / 8; i++) { o[i][0] = 0.f; o[i][1] = 0.f; }
+  float m = -INFINITY, l = 0.f;
+  for (int cb = c0 + warp * 16; cb < c1; cb += 64) {
+    // ---- scores of 16 cells ----
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+    const int ka = min(cb + g, c1 - 1), kb = min(cb + 8 + g, c1 - 1);  // clamped rows are masked below
+    const __half* kra = kbase + (size_t)ka * cell_stride;
+    const __half* krb = kbase + (size_t)kb * cell_stride;
+    uint4 ka4[KS / 2], kb4[KS / 2];
+#pragma unroll
+    for (int j = 0; j < KS / 2; j++) {
+      ka4[j] = ldg_stream(kra + 8 * (t + 4 * j));
+      kb4[j] = ldg_stream(krb + 8 * (t + 4 * j));
     }
 #pragma unroll
-    for (int u = 0; u < ATT_PF; u++) {
-      const int c = cb + u * AT_WARPS;
-      if (c >= c1) break;
-      float kf[DPL], vf[DPL];
-      const uint32_t kw[4] = {kraw[u].x, kraw[u].y, kraw[u].z, kraw[u].w}, vw[4] = {vraw[u].x, vraw[u].y, vraw[u].z, vraw[u].w};
+    for (int j = 0; j < KS / 2; j++) {
+      const uint32_t a0[4] = {qa[2 * j][0], 0u, qa[2 * j][1], 0u}, a1[4] = {qa[2 * j + 1][0], 0u, qa[2 * j + 1][1], 0u};
+      mma16816(s0, a0, ka4[j].x, ka4[j].y);
+      mma16816(s0, a1, ka4[j].z, ka4[j].w);
+      mma16816(s1, a0, kb4[j].x, kb4[j].y);
+      mma16816(s1, a1, kb4[j].z, kb4[j].w);
+    }
+    // row g, cells cb + 2t, +1 (tile 0) and cb + 8 + 2t, +1 (tile 1)
+    float sc[4] = {s0[0] * scale, s0[1] * scale, s1[0] * scale, s1[1] * scale};
+    const int cell[4] = {cb + 2 * t, cb + 2 * t + 1, cb + 8 + 2 * t, cb + 9 + 2 * t};
 #pragma unroll
-      for (int d = 0; d < DPL; d += 2) {
-        kf[d] = h2f_lo(kw[d >> 1]); kf[d + 1] = h2f_hi(kw[d >> 1]);
-        vf[d] = h2f_lo(vw[d >> 1]); vf[d + 1] = h2f_hi(vw[d >> 1]);
-      }
-      float sc[G];
+    for (int i = 0; i < 4; i++) if (cell[i] >= c1) sc[i] = -INFINITY;
+    float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float mn = fmaxf(m, mx);                       // finite: a block always holds at least one live cell
+    const float corr = expf(m - mn);
+    float pv[4];
 #pragma unroll
-      for (int hh = 0; hh < G; hh++) {
-        float a = 0.f;
+    for (int i = 0; i < 4; i++) pv[i] = expf(sc[i] - mn);
+    l = l * corr + ((pv[0] + pv[1]) + (pv[2] + pv[3]));
+    m = mn;
+    const uint32_t pa[4] = {pack_half2(pv[0], pv[1]), 0u, pack_half2(pv[2], pv[3]), 0u};
+    // ---- O = O * corr + P V ----
+    const int va_c = min(cell[0], c1 - 1), vb_c = min(cell[1], c1 - 1), vc_c = min(cell[2], c1 - 1), vd_c = min(cell[3], c1 - 1);
 #pragma unroll
-        for (int d = 0; d < DPL; d++) a = fmaf(q[hh][d], kf[d], a);
-        sc[hh] = a;
-      }
+    for (int b = 0; b < NB; b++) {
+      const int doff = 8 * (g + 8 * b);
+      const uint4 va = ldg_stream(vbase + (size_t)va_c * cell_stride + doff), vb = ldg_stream(vbase + (size_t)vb_c * cell_stride + doff);
+      const uint4 vc = ldg_stream(vbase + (size_t)vc_c * cell_stride + doff), vd = ldg_stream(vbase + (size_t)vd_c * cell_stride + doff);
+      const uint32_t ra[4] = {va.x, va.y, va.z, va.w}, rb[4] = {vb.x, vb.y, vb.z, vb.w}, rc[4] = {vc.x, vc.y, vc.z, vc.w}, rd[4] = {vd.x, vd.y, vd.z, vd.w};
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) {
-#pragma unroll
-        for (int hh = 0; hh < G; hh++) sc[hh] += __shfl_xor_sync(0xffffffffu, sc[hh], off);
-      }
-#pragma unroll
-      for (int hh = 0; hh < G; hh++) {
-        const float sv = sc[hh] * scale;
-        const float mn = fmaxf(m[hh], sv);
-        const float corr = expf(m[hh] - mn), pw = expf(sv - mn);
-        l[hh] = l[hh] * corr + pw;
-#pragma unroll
-        for (int d = 0; d < DPL; d++) o[hh][d] = fmaf(pw, vf[d], o[hh][d] * corr);
-        m[hh] = mn;
+      for (int j = 0; j < 4; j++) {
+        float acc_e[4] = {o[b * 8 + 2 * j][0] * corr, o[b * 8 + 2 * j][1] * corr, 0.f, 0.f};
+        float acc_o[4] = {o[b * 8 + 2 * j + 1][0] * corr, o[b * 8 + 2 * j + 1][1] * corr, 0.f, 0.f};
+        mma16816(acc_e, pa, __byte_perm(ra[j], rb[j], 0x5410), __byte_perm(rc[j], rd[j], 0x5410));
+        mma16816(acc_o, pa, __byte_perm(ra[j], rb[j], 0x7632), __byte_perm(rc[j], rd[j], 0x7632));
+        o[b * 8 + 2 * j][0] = acc_e[0]; o[b * 8 + 2 * j][1] = acc_e[1];
+        o[b * 8 + 2 * j + 1][0] = acc_o[0]; o[b * 8 + 2 * j + 1][1] = acc_o[1];
       }
     }
   }
-  // merge the warps, then publish this split's partial
+  // row sums live as per-lane partials over the four t lanes
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+  // n-tile (b, i) column n' holds dim 8 * (n' + 8b) + i; this lane has columns 2t and 2t + 1 of head g
+  if (g < G) {
+    if (t == 0) { sm_m[warp][g] = m; sm_l[warp][g] = l; }
 #pragma unroll
-  for (int hh = 0; hh < G; hh++) {
-    if (lane == 0) { sm_m[warp][hh] = m[hh]; sm_l[warp][hh] = l[hh]; }
+    for (int b = 0; b < NB; b++) {
 #pragma unroll
-    for (int d = 0; d < DPL; d++) sm_o[warp][hh][lane * DPL + d] = o[hh][d];
+      for (int i = 0; i < 8; i++) {
+        sm_o[warp][g][8 * (2 * t + 8 * b) + i] = o[b * 8 + i][0];
+        sm_o[warp][g][8 * (2 * t + 1 + 8 * b) + i] = o[b * 8 + i][1];
+      }
+    }
   }
   __syncthreads();
-  const int PW = hd + 2;
-  for (int i = tid; i < G * hd; i += AT_THREADS) {
-    const int hh = i / hd, d = i - hh * hd;
-    float mm = sm_m[0][hh];
-#pragma unroll
-    for (int w = 1; w < AT_WARPS; w++) mm = fmaxf(mm, sm_m[w][hh]);
+  const int PW = HD + 2;
+  for (int i = tid; i < G * HD; i += 128) {
+    const int hh = i / HD, d = i - hh * HD;
+    float mm = fmaxf(fmaxf(sm_m[0][hh], sm_m[1][hh]), fmaxf(sm_m[2][hh], sm_m[3][hh]));
     float ov = 0.f, lv = 0.f;
 #pragma unroll
-    for (int w = 0; w < AT_WARPS; w++) {
+    for (int w = 0; w < 4; w++) {
       const float f = sm_m[w][hh] == -INFINITY ? 0.f : expf(sm_m[w][hh] - mm);
       ov += sm_o[w][hh][d] * f; lv += sm_l[w][hh] * f;
     }
     float* part = p.partial + (((size_t)n * p.Hq + kvh * G + hh) * p.nsplit + split) * PW;
     part[d] = ov;
-    if (d == 0) { part[hd] = mm; part[hd + 1] = lv; }
+    if (d == 0) { part[HD] = mm; part[HD + 1] = lv; }
   }
   tl_mark(p.tl, 4);
-  __threadfence();
-  __syncthreads();
-  int* ticket = p.tickets + (size_t)n * p.Hkv + kvh;
-  if (tid == 0) is_last = (atomicAdd(ticket, 1) == (int)gridDim.x - 1);
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  if (tid == 0) *ticket = 0;
-  const int nlive = (ncell + p.split_cells - 1) / p.split_cells;
-  // merge: O = sum_s O_s * exp(m_s - m*), l likewise (reference: shaders/llm_attn_combine.comp:70-102)
-  float* fac = sm_o_dyn;                  // [G][nlive] factors, reusing the warp-merge buffer
-  __shared__ float mm_s[G], ll_s[G];
-  __syncthreads();
-  for (int i = tid; i < G * nlive; i += AT_THREADS) {
-    const int hh = i / nlive, sp = i - hh * nlive;
-    fac[i] = __ldcg(p.partial + (((size_t)n * p.Hq + kvh * G + hh) * p.nsplit + sp) * PW + hd);
-  }
-  __syncthreads();
-  if (tid < G) {
-    float mm = -INFINITY;
-    for (int sp = 0; sp < nlive; sp++) mm = fmaxf(mm, fac[tid * nlive + sp]);
-    mm_s[tid] = mm;
-  }
-  __syncthreads();
-  for (int i = tid; i < G * nlive; i += AT_THREADS) fac[i] = expf(fac[i] - mm_s[i / nlive]);
-  __syncthreads();
-  if (tid < G) {
-    float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-    const float* lp = p.partial + ((size_t)n * p.Hq + kvh * G + tid) * p.nsplit * PW + hd + 1;
-    int sp = 0;
-    for (; sp + 4 <= nlive; sp += 4) {
-      const float a0 = __ldcg(lp + (size_t)sp * PW), a1 = __ldcg(lp + (size_t)(sp + 1) * PW), a2 = __ldcg(lp + (size_t)(sp + 2) * PW), a3 = __ldcg(lp + (size_t)(sp + 3) * PW);
-      l0 += a0 * fac[tid * nlive + sp]; l1 += a1 * fac[tid * nlive + sp + 1]; l2 += a2 * fac[tid * nlive + sp + 2]; l3 += a3 * fac[tid * nlive + sp + 3];
-    }
-    for (; sp < nlive; sp++) l0 += __ldcg(lp + (size_t)sp * PW) * fac[tid * nlive + sp];
-    ll_s[tid] = (l0 + l1) + (l2 + l3);
-  }
-  __syncthreads();
-  const int gate_off = hd;  // per head: hd query dims then hd gate dims
-  for (int i = tid; i < G * hd; i += AT_THREADS) {
-    const int hh = i / hd, d = i - hh * hd, head = kvh * G + hh;
-    const float* part = p.partial + ((size_t)n * p.Hq + head) * p.nsplit * PW;
-    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-    int sp = 0;
-    for (; sp + 4 <= nlive; sp += 4) {  // independent loads in flight; the sum order stays fixed
-      const float a0 = __ldcg(part + (size_t)sp * PW + d), a1 = __ldcg(part + (size_t)(sp + 1) * PW + d);
-      const float a2 = __ldcg(part + (size_t)(sp + 2) * PW + d), a3 = __ldcg(part + (size_t)(sp + 3) * PW + d);
-      o0 += a0 * fac[hh * nlive + sp]; o1 += a1 * fac[hh * nlive + sp + 1]; o2 += a2 * fac[hh * nlive + sp + 2]; o3 += a3 * fac[hh * nlive + sp + 3];
-    }
-    for (; sp < nlive; sp++) o0 += __ldcg(part + (size_t)sp * PW + d) * fac[hh * nlive + sp];
-    const float ov = (o0 + o1) + (o2 + o3);
-    const float gate = p.proj[(size_t)n * p.ldp + head * 2 * hd + gate_off + d];
-    p.ctx16[(size_t)n * p.Hq * hd + head * hd + d] = __float2half_rn(ov / ll_s[hh] * sigmoid_acc(gate));
-  }
-  tl_mark(p.tl, 6, true);
 }
 
-template <int DPL, int G>
-static int launch_attn_t(const AttnParams& p, bool pdl, cudaStream_t st) {
-  const size_t smem = (size_t)AT_WARPS * G * DPL * 32 * sizeof(float);
-  static bool configured = false;
-  if (!configured) {
-    B200_CUDA(cudaFuncSetAttribute(attn_decode_kernel<DPL, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = true;
+// Merge of the splits: O = sum_s O_s * exp(m_s - m*), divide by the merged row sum, times
+// sigmoid(gate), to fp16 (reference: shaders/llm_attn_combine.comp:43-102). grid (Hq, M), block hd.
+__global__ void attn_merge_kernel(AttnParams p) {
+  const int head = blockIdx.x, n = blockIdx.y, d = threadIdx.x, hd = p.hd, PW = hd + 2;
+  pdl_wait();
+  pdl_launch();
+  const int nlive = (p.row_pos[n] + 1 + p.split_cells - 1) / p.split_cells;
+  const float* part = p.partial + ((size_t)n * p.Hq + head) * p.nsplit * PW;
+  float mm = -INFINITY;
+  for (int sp = 0; sp < nlive; sp++) mm = fmaxf(mm, __ldcg(part + (size_t)sp * PW + hd));
+  float ov = 0.f, lv = 0.f;
+  int sp = 0;
+  for (; sp + 4 <= nlive; sp += 4) {  // four independent loads in flight, summed in split order
+    float a[4], f[4], ls[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      a[u] = __ldcg(part + (size_t)(sp + u) * PW + d);
+      f[u] = __ldcg(part + (size_t)(sp + u) * PW + hd);
+      ls[u] = __ldcg(part + (size_t)(sp + u) * PW + hd + 1);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++) { const float e = f[u] == -INFINITY ? 0.f : expf(f[u] - mm); ov += a[u] * e; lv += ls[u] * e; }
   }
-  return launch_k(attn_decode_kernel<DPL, G>, dim3(p.nsplit, p.Hkv, p.M), dim3(AT_THREADS), smem, pdl, st, p);
+  for (; sp < nlive; sp++) {
+    const float ms = __ldcg(part + (size_t)sp * PW + hd);
+    const float e = ms == -INFINITY ? 0.f : expf(ms - mm);
+    ov += __ldcg(part + (size_t)sp * PW + d) * e; lv += __ldcg(part + (size_t)sp * PW + hd + 1) * e;
+  }
+  const float gate = p.proj[(size_t)n * p.ldp + head * 2 * hd + hd + d];
+  p.ctx16[(size_t)n * p.Hq * hd + head * hd + d] = __float2half_rn(ov / lv * sigmoid_acc(gate));
+  tl_mark(p.tl, 6, true);
 }
 
 int launch_attn_decode(const AttnParams& p, bool pdl, cudaStream_t st) {
   const int G = p.Hq / p.Hkv;
-  if (p.nsplit > AT_WARPS * p.hd) { set_error("attn_decode: too many splits for the merge buffer"); return ECAPACITY; }
-  if (p.hd == 256 && G == 8) return launch_attn_t<8, 8>(p, pdl, st);
-  if (p.hd == 128 && G == 4) return launch_attn_t<4, 4>(p, pdl, st);
-  if (p.hd == 128 && G == 8) return launch_attn_t<4, 8>(p, pdl, st);
-  if (p.hd == 256 && G == 4) return launch_attn_t<8, 4>(p, pdl, st);
-  set_error("attn_decode: unsupported head_dim / group size");
-  return EINVAL_;
+  dim3 grid(p.nsplit, p.Hkv, p.M), block(128);
+  int s;
+  if (p.hd == 256 && G == 8) s = launch_k(attn_mma_kernel<256, 8>, grid, block, 0, pdl, st, p);
+  else if (p.hd == 128 && G == 4) s = launch_k(attn_mma_kernel<128, 4>, grid, block, 0, pdl, st, p);
+  else if (p.hd == 128 && G == 8) s = launch_k(attn_mma_kernel<128, 8>, grid, block, 0, pdl, st, p);
+  else if (p.hd == 256 && G == 4) s = launch_k(attn_mma_kernel<256, 4>, grid, block, 0, pdl, st, p);
+  else { set_error("attn_decode: unsupported head_dim / group size (128 or 256 dims, 4 or 8 query heads per KV head)"); return EINVAL_; }
+  return s;
 }
+int launch_attn_merge(const AttnParams& p, bool pdl, cudaStream_t st) {
+  return launch_k(attn_merge_kernel, dim3(p.Hq, p.M), dim3(p.hd), 0, pdl, st, p);
+}
+
 // =========================================================================================
 // Greedy sampling: argmax with ties to the lowest id (reference: llm/sample.go:359-367)
 // =========================================================================================

@@ -98,6 +98,7 @@ struct AttnParams {
 };
 int launch_attn_pack(const AttnParams& p, bool pdl, cudaStream_t st);
 int launch_attn_decode(const AttnParams& p, bool pdl, cudaStream_t st);
+int launch_attn_merge(const AttnParams& p, bool pdl, cudaStream_t st);
 
 int launch_argmax(const float* logits, int M, int V, int32_t* out, bool pdl, cudaStream_t st);
 
