@@ -240,6 +240,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       B200_TRY(launch_attn_pack(a, pdl(), st));
       a.tl = tl();
       B200_TRY(launch_attn_decode(a, pdl(), st));
+      a.tl = tl();
       B200_TRY(launch_attn_merge(a, pdl(), st));
       QGemvParams q = base(L.o, qw, H, ctx16, qw);
       q.y = h; q.ldy = H;

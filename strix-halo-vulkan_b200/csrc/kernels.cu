@@ -323,7 +323,9 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
     __syncthreads();
   }
   if (row <= p.nE) {
-    for (int n = 0; n < M; n++) {
+    // rows of the pass are spread over blockIdx.y in groups of 8 so a many-slot pass fills the machine
+    const int n_lo = blockIdx.y * 8, n_hi = min(M, n_lo + 8);
+    for (int n = n_lo; n < n_hi; n++) {
       const __half* x = staged ? rxs + (size_t)n * H : p.xn + (size_t)n * H;
       float acc = 0.f;
       if (row == p.nE) {
@@ -365,7 +367,7 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   // the last CTA to finish routes every token and builds the expert work list
   __threadfence();
   __syncthreads();
-  if (tid == 0) is_last = (atomicAdd(p.ticket, 1) == (int)gridDim.x - 1);
+  if (tid == 0) is_last = (atomicAdd(p.ticket, 1) == (int)(gridDim.x * gridDim.y) - 1);
   __syncthreads();
   if (!is_last) return;
   __threadfence();
@@ -438,7 +440,7 @@ int launch_router(const RouterParams& p, bool pdl, cudaStream_t st) {
     if (smem > configured) { B200_CUDA(cudaFuncSetAttribute(router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); configured = 200 * 1024; }
     if (smem > 200 * 1024) { set_error("router: rows too long for shared memory"); return ECAPACITY; }
   }
-  return launch_k(router_kernel, dim3(grid), dim3(256), smem, pdl, st, p);
+  return launch_k(router_kernel, dim3(grid, p.h != nullptr ? 1 : (p.M + 7) / 8), dim3(256), smem, pdl, st, p);
 }
 
 // Stand-alone forms of the row tails, one CTA per row, for passes of more than QG_TAIL_ROWS rows.
