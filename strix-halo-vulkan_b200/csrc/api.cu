@@ -210,8 +210,7 @@ int32_t b200_qgemv(uint32_t type, const void* host_w, int64_t rows, int64_t k, c
     QGemvParams p{};
     p.w[0] = t.data; p.seg_end[0] = (int)rows; p.nseg = 1; p.stride = t.stride; p.K = (int)k; p.N = (int)rows; p.M = mrows; p.xcols = mrows < QG_MAXCOLS ? mrows : QG_MAXCOLS;
     p.x = x16; p.ldx = k; p.y = y; p.ldy = rows; p.x_div = 1;
-    TailParams no_tail{};
-    s = launch_qgemv(type, PRO_F16, EPI_STORE, false, false, p, no_tail, 0, false, 0);
+    s = launch_qgemv(type, PRO_F16, EPI_STORE, false, false, p, 0, false, 0);
   }
   if (s == OK && cudaMemcpy(host_y, y, (size_t)mrows * rows * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) { set_error(std::string("qgemv: ") + cudaGetErrorString(cudaGetLastError())); s = ECUDA; }
   cudaFree(src); cudaFree(t.data); cudaFree(xf); cudaFree(x16); cudaFree(y);

@@ -67,14 +67,14 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
     else dn_index[l] = n_dn++;
   }
   max_entries = std::min(MR * used, c.n_expert + (MR * used + 7) / 8) + (MR + 7) / 8;
-  B200_TRY(dalloc(&h, (size_t)MR * H)); B200_TRY(dalloc(&proj, (size_t)MR * proj_ld));
+  B200_TRY(dalloc(&hbuf[0], (size_t)MR * H)); B200_TRY(dalloc(&hbuf[1], (size_t)MR * H)); h = hbuf[0]; B200_TRY(dalloc(&proj, (size_t)MR * proj_ld));
   B200_TRY(dalloc(&xn16, (size_t)MR * H)); B200_TRY(dalloc(&q16, (size_t)MR * qw)); B200_TRY(dalloc(&ctx16, (size_t)MR * qw));
   B200_TRY(dalloc(&attn_partial, (size_t)MR * c.n_head * nsplit * (hd + 2)));
   B200_TRY(dalloc(&attn_tickets, (size_t)MR * c.n_head_kv));
   B200_TRY(dalloc(&r_logits, (size_t)MR * c.n_expert)); B200_TRY(dalloc(&r_probs, (size_t)MR * c.n_expert));
   B200_TRY(dalloc(&topk, (size_t)MR * used)); B200_TRY(dalloc(&topk_w, (size_t)MR * slots1)); B200_TRY(dalloc(&margin, (size_t)MR));
   B200_TRY(dalloc(&entries, (size_t)max_entries)); B200_TRY(dalloc(&n_entries, 1)); B200_TRY(dalloc(&cols, (size_t)MR * slots1));
-  B200_TRY(dalloc(&r_ticket, 1)); B200_TRY(dalloc(&tail_ticket, 1)); B200_TRY(dalloc(&err_flag, 1)); B200_TRY(dalloc(&ss_part, (size_t)MR * SS_LD)); B200_TRY(dalloc(&col_tickets, 1024)); B200_TRY(dalloc(&y16, (size_t)MR * vw));
+  B200_TRY(dalloc(&r_ticket, 1)); B200_TRY(dalloc(&tail_ticket, 1)); B200_TRY(dalloc(&err_flag, 1)); B200_TRY(dalloc(&ss_part, (size_t)MR * SS_LD)); B200_TRY(dalloc(&y16, (size_t)MR * vw));
   B200_TRY(dalloc(&act16, (size_t)MR * slots1 * c.ffn_expert)); B200_TRY(dalloc(&down, (size_t)MR * slots1 * H));
   B200_TRY(dalloc(&logits, (size_t)MR * c.vocab));
   B200_TRY(dalloc(&ids_dev, (size_t)MR)); B200_TRY(dalloc(&next_ids, (size_t)MR)); B200_TRY(dalloc(&row_slot, (size_t)MR));
@@ -149,7 +149,11 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
   const int H = c.n_embd, D = c.dn_head_dim, qk = c.dn_heads_k * D, vw = c.dn_heads_v * D, cw = 2 * qk + vw;
   const int hd = c.head_dim, qw = c.n_head * hd, kvw = c.n_head_kv * hd, used = c.n_expert_used, slots1 = used + 1;
   const int xcols = std::min(M, QG_MAXCOLS);
-  const bool fused = M <= QG_TAIL_ROWS;
+  const bool fused = M <= QG_TAIL_ROWS && H <= QG_COMBINE_MAX_K;
+  float* hc = hbuf[0];      // residual rows of this pass
+  bool pending = false;     // fused passes: the MoE output of the last layer is not in hc yet; the next
+                            // projection of the residual folds it in while staging and writes the other buffer
+  int trace_layer = -1;     // layer whose post-MoE residual is still to be traced
   launches = 0;
   bool first = true;
   int ss_n = 1;  // partial sums of squares the current residual rows carry
@@ -164,16 +168,28 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
   };
   // a projection of the normalised residual: fused passes normalise while staging, others read xn16
   auto normed = [&](QGemvParams& p, const DTensor& gamma, __half* xn_copy) {
-    if (fused) { p.hsrc = h; p.gamma = (const float*)gamma.data; p.ss_in = ss_part; p.ss_n = ss_n; p.xn_out = xn_copy; return (int)PRO_NORM; }
-    return (int)PRO_F16;
+    if (!fused) return (int)PRO_F16;
+    p.hsrc = hc; p.gamma = (const float*)gamma.data; p.xn_out = xn_copy;
+    if (!pending) { p.ss_in = ss_part; p.ss_n = ss_n; return (int)PRO_NORM; }
+    p.down = down; p.topk_w = topk_w; p.used = used; p.h_out = hc == hbuf[0] ? hbuf[1] : hbuf[0];
+    return (int)PRO_COMBINE;
+  };
+  // after a PRO_COMBINE launch the rows live in the other buffer
+  auto combined = [&](int pro) {
+    if (pro != PRO_COMBINE) return OK;
+    hc = hc == hbuf[0] ? hbuf[1] : hbuf[0]; pending = false;
+    if (o.trace && trace_layer >= 0) {
+      B200_CUDA(cudaMemcpyAsync(tr_out + (size_t)trace_layer * MR * H, hc, (size_t)M * H * sizeof(float), cudaMemcpyDeviceToDevice, st));
+      first = true; trace_layer = -1;
+    }
+    return OK;
   };
   auto row_tail = [&](int mode, const DTensor& gamma) {
     TailParams t{};
-    t.mode = mode; t.h = h; t.gamma = (const float*)gamma.data; t.xn = xn16; t.down = down; t.topk_w = topk_w;
+    t.mode = mode; t.h = hc; t.gamma = (const float*)gamma.data; t.xn = xn16; t.down = down; t.topk_w = topk_w;
     t.used = used; t.H = H; t.M = M; t.eps = c.eps;
     return t;
   };
-  const TailParams no_tail{};
   const int l0 = f.draft ? c.n_layer : 0, l1 = f.draft ? c.n_layer + 1 : c.n_layer;
   if (f.draft) {
     // nextn seed, embedding first: h = eh_proj . concat(rms(embd, enorm), rms(h_prev, hnorm))  (llm/mtp.go:352-384)
@@ -182,13 +198,13 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     B200_TRY(launch_embed(ep, st)); pdl();
     B200_TRY(launch_concat_norm(e_buf, hs_buf, (const float*)L.enorm.data, (const float*)L.hnorm.data, c.eps, H, M, xcat16, pdl(), st));
     QGemvParams p = base(L.eh_proj, 2 * H, H, xcat16, 2 * H);
-    p.y = h; p.ldy = H;
+    p.y = hc; p.ldy = H;
     if (fused) { p.ss_out = ss_part; ss_n = qgemv_groups(2 * H, H); }
-    B200_TRY(launch_qgemv(L.eh_proj.type, PRO_F16, EPI_STORE, false, false, p, no_tail, 0, pdl(), st));
+    B200_TRY(launch_qgemv(L.eh_proj.type, PRO_F16, EPI_STORE, false, false, p, 0, pdl(), st));
     if (!fused) B200_TRY(launch_row_tail(row_tail(1, L.attn_norm), pdl(), st));
   } else {
     const LayerW& L0 = m->layers[0];
-    EmbedParams ep{m->token_embd, ids_dev, h, M, H, fused ? nullptr : (const float*)L0.attn_norm.data, xn16, c.eps, fused ? ss_part : nullptr};
+    EmbedParams ep{m->token_embd, ids_dev, hc, M, H, fused ? nullptr : (const float*)L0.attn_norm.data, xn16, c.eps, fused ? ss_part : nullptr};
     B200_TRY(launch_embed(ep, st)); pdl();
     ss_n = 1;
   }
@@ -200,7 +216,8 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       p.w[1] = L.z.data; p.seg_end[0] = cw; p.seg_end[1] = cw + vw; p.nseg = 2;
       p.y = proj; p.ldy = proj_ld;
       const int pro = normed(p, L.attn_norm, xn16);  // the DeltaNet step reads the fp16 rows for alpha / beta
-      B200_TRY(launch_qgemv(L.qkv.type, pro, EPI_STORE, false, false, p, no_tail, 0, pdl(), st));
+      B200_TRY(launch_qgemv(L.qkv.type, pro, EPI_STORE, false, false, p, 0, pdl(), st));
+      B200_TRY(combined(pro));
       DnStepParams d{};
       d.proj = proj; d.ldp = proj_ld; d.xn = xn16; d.alpha_w = (const float*)L.alpha.data; d.beta_w = (const float*)L.beta.data;
       d.conv_w = (const float*)L.conv1d.data; d.ssm_a = (const float*)L.ssm_a.data; d.dt_bias = (const float*)L.dt_bias.data;
@@ -210,15 +227,16 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       d.H = H; d.Hk = c.dn_heads_k; d.Hv = c.dn_heads_v; d.D = D; d.conv = c.dn_conv; d.eps = c.eps; d.tl = tl();
       B200_TRY(launch_dn_step(d, pdl(), st));
       QGemvParams q = base(L.ssm_out, vw, H, y16, vw);
-      q.y = h; q.ldy = H;
+      q.y = hc; q.ldy = H;
       if (fused) { q.ss_out = ss_part; ss_n = qgemv_groups(vw, H); }
-      B200_TRY(launch_qgemv(L.ssm_out.type, PRO_F16, EPI_RESID, false, false, q, no_tail, 0, pdl(), st));
+      B200_TRY(launch_qgemv(L.ssm_out.type, PRO_F16, EPI_RESID, false, false, q, 0, pdl(), st));
     } else {
       const int ai = attn_index[l];
       // fused q|k|v projection; tensors of one type share a launch
       const DTensor* seg[3] = {&L.q, &L.k, &L.v};
       const int rows[3] = {2 * qw, kvw, kvw};
       int off = 0;
+      bool xn_ready = false;
       for (int s = 0; s < 3;) {
         int e = s + 1;
         while (e < 3 && seg[e]->type == seg[s]->type) e++;
@@ -227,8 +245,10 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
         for (int i = s; i < e; i++) { p.w[i - s] = seg[i]->data; n += rows[i]; p.seg_end[i - s] = n; }
         p.nseg = e - s; p.N = n;
         p.y = proj + off; p.ldy = proj_ld;
-        const int pro = normed(p, L.attn_norm, nullptr);
-        B200_TRY(launch_qgemv(seg[s]->type, pro, EPI_STORE, false, false, p, no_tail, 0, pdl(), st));
+        // the launch that folds the MoE output in also leaves the fp16 rows for the launches after it
+        const int pro = normed(p, L.attn_norm, pending ? xn16 : nullptr);
+        if (xn_ready) { B200_TRY(launch_qgemv(seg[s]->type, PRO_F16, EPI_STORE, false, false, p, 0, pdl(), st)); }
+        else { B200_TRY(launch_qgemv(seg[s]->type, pro, EPI_STORE, false, false, p, 0, pdl(), st)); xn_ready = pro == PRO_COMBINE; B200_TRY(combined(pro)); }
         off += n; s = e;
       }
       AttnParams a{};
@@ -243,16 +263,16 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       a.tl = tl();
       B200_TRY(launch_attn_merge(a, pdl(), st));
       QGemvParams q = base(L.o, qw, H, ctx16, qw);
-      q.y = h; q.ldy = H;
+      q.y = hc; q.ldy = H;
       if (fused) { q.ss_out = ss_part; ss_n = qgemv_groups(qw, H); }
-      B200_TRY(launch_qgemv(L.o.type, PRO_F16, EPI_RESID, false, false, q, no_tail, 0, pdl(), st));
+      B200_TRY(launch_qgemv(L.o.type, PRO_F16, EPI_RESID, false, false, q, 0, pdl(), st));
     }
     if (!fused) B200_TRY(launch_row_tail(row_tail(1, L.ffn_norm), pdl(), st));
-    if (o.trace) { B200_CUDA(cudaMemcpyAsync(tr_mid + (size_t)l * MR * H, h, (size_t)M * H * sizeof(float), cudaMemcpyDeviceToDevice, st)); first = true; }
+    if (o.trace) { B200_CUDA(cudaMemcpyAsync(tr_mid + (size_t)l * MR * H, hc, (size_t)M * H * sizeof(float), cudaMemcpyDeviceToDevice, st)); first = true; }
     // MoE block
     RouterParams r{};
     r.xn = xn16; r.router = L.router; r.sh_gate = (const float*)L.sh_gate_inp.data;
-    if (fused) { r.h = h; r.gamma = (const float*)L.ffn_norm.data; r.ss_in = ss_part; r.ss_n = ss_n; r.eps = c.eps; r.xn_out = xn16; }
+    if (fused) { r.h = hc; r.gamma = (const float*)L.ffn_norm.data; r.ss_in = ss_part; r.ss_n = ss_n; r.eps = c.eps; r.xn_out = xn16; }
     r.M = M; r.H = H; r.nE = c.n_expert; r.used = used; r.logits = r_logits; r.probs = nullptr; r.topk = topk; r.topk_w = topk_w;
     r.tl = tl(); r.margin = margin; r.entries = entries; r.n_entries = n_entries; r.cols = cols; r.ticket = r_ticket; r.max_entries = max_entries;
     B200_TRY(launch_router(r, pdl(), st));
@@ -261,42 +281,48 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     p.w2[0] = L.up_exps.data; p.ws = L.gate_sh.data; p.ws2 = L.up_sh.data; p.expert_stride = (int64_t)c.ffn_expert * L.gate_exps.stride;
     p.entries = entries; p.n_entries = n_entries; p.cols = cols; p.x_div = slots1;
     p.y16 = act16; p.ldy = c.ffn_expert;
-    B200_TRY(launch_qgemv(L.gate_exps.type, PRO_F16, EPI_SWIGLU, true, true, p, no_tail, ne, pdl(), st));
+    B200_TRY(launch_qgemv(L.gate_exps.type, PRO_F16, EPI_SWIGLU, true, true, p, ne, pdl(), st));
     QGemvParams q = base(L.down_exps, c.ffn_expert, H, act16, c.ffn_expert);
     q.ws = L.down_sh.data; q.expert_stride = (int64_t)H * L.down_exps.stride;
     q.entries = entries; q.n_entries = n_entries; q.cols = cols; q.x_div = 1;
     q.y = down; q.ldy = H;
-    TailParams ct{};
-    if (fused) {
-      ct.mode = 1; ct.col_tickets = col_tickets; ct.h = h; ct.down = down; ct.topk_w = topk_w; ct.ss_part = ss_part; ct.used = used; ct.H = H; ct.M = M;
-      ss_n = qgemv_groups(c.ffn_expert, H);
-    }
-    B200_TRY(launch_qgemv(L.down_exps.type, PRO_F16, EPI_STORE, false, true, q, ct, ne, pdl(), st));
-    if (!fused) {
+    B200_TRY(launch_qgemv(L.down_exps.type, PRO_F16, EPI_STORE, false, true, q, ne, pdl(), st));
+    if (fused) pending = true;
+    else {
       const DTensor& next_norm = f.draft ? L.head_norm : (l + 1 < c.n_layer ? m->layers[l + 1].attn_norm : m->output_norm);
       B200_TRY(launch_row_tail(row_tail(2, next_norm), pdl(), st));
     }
     if (o.trace) {
-      B200_CUDA(cudaMemcpyAsync(tr_out + (size_t)l * MR * H, h, (size_t)M * H * sizeof(float), cudaMemcpyDeviceToDevice, st));
+      if (fused) trace_layer = l;
+      else B200_CUDA(cudaMemcpyAsync(tr_out + (size_t)l * MR * H, hc, (size_t)M * H * sizeof(float), cudaMemcpyDeviceToDevice, st));
       B200_CUDA(cudaMemcpyAsync(tr_topk + (size_t)l * MR * used, topk, (size_t)M * used * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
       B200_CUDA(cudaMemcpyAsync(tr_w + (size_t)l * MR * slots1, topk_w, (size_t)M * slots1 * sizeof(float), cudaMemcpyDeviceToDevice, st));
       B200_CUDA(cudaMemcpyAsync(tr_margin + (size_t)l * MR, margin, (size_t)M * sizeof(float), cudaMemcpyDeviceToDevice, st));
       first = true;  // copies sit between this kernel and the next: no programmatic edge
     }
   }
+  const DTensor& nrm = f.draft ? m->layers[c.n_layer].head_norm : m->output_norm;
+  bool head_reads_xn = false;
+  if (pending && n_logit_rows != M) {
+    // the head stages only some of the rows (or none): finish every row in place first
+    B200_TRY(launch_row_tail(row_tail(2, nrm), pdl(), st));
+    pending = false; head_reads_xn = true;
+    if (o.trace && trace_layer >= 0) { B200_CUDA(cudaMemcpyAsync(tr_out + (size_t)trace_layer * MR * H, hc, (size_t)M * H * sizeof(float), cudaMemcpyDeviceToDevice, st)); first = true; trace_layer = -1; }
+  }
   if (n_logit_rows > 0) {
-    const DTensor& nrm = f.draft ? m->layers[c.n_layer].head_norm : m->output_norm;
     const int N = f.draft && draft_vocab > 0 ? draft_vocab : c.vocab;
     QGemvParams p = base(m->output, H, N, xn16, H);
     p.M = n_logit_rows; p.xcols = std::min(n_logit_rows, QG_MAXCOLS); p.row_ids = logit_rows;
     p.y = logits; p.ldy = N;
-    const int pro = normed(p, nrm, nullptr);
-    B200_TRY(launch_qgemv(m->output.type, pro, EPI_STORE, false, false, p, no_tail, 0, pdl(), st));
+    const int pro = head_reads_xn ? (int)PRO_F16 : normed(p, nrm, nullptr);
+    B200_TRY(launch_qgemv(m->output.type, pro, EPI_STORE, false, false, p, 0, pdl(), st));
+    B200_TRY(combined(pro));
     if (f.greedy) {
       B200_TRY(launch_argmax(logits, n_logit_rows, N, next_ids, pdl(), st));
       B200_TRY(launch_advance(ids_dev, next_ids, row_pos, seqs, M, history, hist_len, st)); launches++;
     }
   }
+  h = hc;
   last_launches = launches;
   return OK;
 }
@@ -347,8 +373,10 @@ int Graph::run_rows(const int32_t* ids, const int* slots, const int* pos, int M,
       cudaGraphDestroy(graph);
       if (e != cudaSuccess) { set_error(std::string("graph instantiate: ") + cudaGetErrorString(e)); return ECUDA; }
       it = decode_graphs.emplace(M, exec).first;
+      decode_h[M] = h;
     }
     B200_CUDA(cudaGraphLaunch(it->second, st));
+    h = decode_h[M];
   } else {
     B200_TRY(upload_stage(this, M, n_seq, n_lr));
     B200_TRY(enqueue_pass(M, n_seq, n_lr, f));

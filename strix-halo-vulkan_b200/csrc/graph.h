@@ -27,10 +27,11 @@ struct Graph {
   int n_dn = 0, n_attn = 0;
   std::vector<int> dn_index, attn_index;  // layer -> index among its kind (draft layer = last attention)
   // activations
-  float *h = nullptr, *proj = nullptr, *attn_partial = nullptr, *down = nullptr, *logits = nullptr, *e_buf = nullptr, *hs_buf = nullptr;
+  // the residual stream alternates between two buffers: the kernel that folds the MoE output into it
+  // reads one and writes the other. h is the one the last pass finished in.
+  float *hbuf[2] = {nullptr, nullptr}, *h = nullptr, *proj = nullptr, *attn_partial = nullptr, *down = nullptr, *logits = nullptr, *e_buf = nullptr, *hs_buf = nullptr;
   __half *xn16 = nullptr, *q16 = nullptr, *ctx16 = nullptr, *act16 = nullptr, *y16 = nullptr, *xcat16 = nullptr;
   float* ss_part = nullptr;   // [rows][SS_LD] partial sums of squares of the residual rows
-  int* col_tickets = nullptr;
   float *r_logits = nullptr, *r_probs = nullptr, *topk_w = nullptr, *margin = nullptr;
   int32_t *topk = nullptr, *ids_dev = nullptr, *next_ids = nullptr, *history = nullptr;
   int *attn_tickets = nullptr, *r_ticket = nullptr, *tail_ticket = nullptr, *err_flag = nullptr, *err_host = nullptr, *n_entries = nullptr, *cols = nullptr, *row_slot = nullptr, *row_pos = nullptr, *logit_rows = nullptr, *hist_len = nullptr;
@@ -57,6 +58,7 @@ struct Graph {
   int last_rows = 0;
   // replay
   std::map<int, cudaGraphExec_t> decode_graphs, greedy_graphs;
+  std::map<int, float*> decode_h;  // residual buffer a replayed decode graph of M rows finishes in
   long long* timeline = nullptr;  // [launch][8] phase timestamps when B200_TIMELINE is set
   int timeline_cap = 0;
   int launches = 0, last_launches = 0, draft_vocab = 0, resid_off = 0;

@@ -6,7 +6,7 @@ namespace b200 {
 static int g_sm_count = 0;
 
 template <int TYPE, int PRO, int EPI, bool DUAL, bool GROUPED>
-static int launch_one(const QGemvParams& p, const TailParams& tp, int max_entries, bool pdl, cudaStream_t st) {
+static int launch_one(const QGemvParams& p, int max_entries, bool pdl, cudaStream_t st) {
   auto kernel = qgemv_kernel<TYPE, PRO, EPI, DUAL, GROUPED>;
   if (g_sm_count == 0) {
     int dev = 0;
@@ -38,8 +38,8 @@ static int launch_one(const QGemvParams& p, const TailParams& tp, int max_entrie
   const size_t smem = fixed + (size_t)ns * stage;
   static size_t configured = 0;
   if (smem > configured) {
-    B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(budget1 + 4096)));
-    configured = budget1 + 4096;
+    B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(220 * 1024 + 4096)));
+    configured = 220 * 1024 + 4096;
   }
   QGemvParams pp = p;
   pp.nstage = ns;
@@ -50,19 +50,20 @@ static int launch_one(const QGemvParams& p, const TailParams& tp, int max_entrie
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
-  B200_CUDA(cudaLaunchKernelEx(&cfg, kernel, pp, tp));
+  B200_CUDA(cudaLaunchKernelEx(&cfg, kernel, pp));
   return OK;
 }
 
 template <int TYPE>
-static int launch_type(int pro, int epi, bool dual, bool grouped, const QGemvParams& p, const TailParams& tp, int max_entries, bool pdl, cudaStream_t st) {
+static int launch_type(int pro, int epi, bool dual, bool grouped, const QGemvParams& p, int max_entries, bool pdl, cudaStream_t st) {
   if (!grouped && !dual) {
-    if (pro == PRO_NORM && epi == EPI_STORE) return launch_one<TYPE, PRO_NORM, EPI_STORE, false, false>(p, tp, 0, pdl, st);
-    if (pro == PRO_F16 && epi == EPI_STORE) return launch_one<TYPE, PRO_F16, EPI_STORE, false, false>(p, tp, 0, pdl, st);
-    if (pro == PRO_F16 && epi == EPI_RESID) return launch_one<TYPE, PRO_F16, EPI_RESID, false, false>(p, tp, 0, pdl, st);
+    if (pro == PRO_NORM && epi == EPI_STORE) return launch_one<TYPE, PRO_NORM, EPI_STORE, false, false>(p, 0, pdl, st);
+    if (pro == PRO_COMBINE && epi == EPI_STORE) return launch_one<TYPE, PRO_COMBINE, EPI_STORE, false, false>(p, 0, pdl, st);
+    if (pro == PRO_F16 && epi == EPI_STORE) return launch_one<TYPE, PRO_F16, EPI_STORE, false, false>(p, 0, pdl, st);
+    if (pro == PRO_F16 && epi == EPI_RESID) return launch_one<TYPE, PRO_F16, EPI_RESID, false, false>(p, 0, pdl, st);
   } else if (grouped && pro == PRO_F16) {
-    if (dual && epi == EPI_SWIGLU) return launch_one<TYPE, PRO_F16, EPI_SWIGLU, true, true>(p, tp, max_entries, pdl, st);
-    if (!dual && epi == EPI_STORE) return launch_one<TYPE, PRO_F16, EPI_STORE, false, true>(p, tp, max_entries, pdl, st);
+    if (dual && epi == EPI_SWIGLU) return launch_one<TYPE, PRO_F16, EPI_SWIGLU, true, true>(p, max_entries, pdl, st);
+    if (!dual && epi == EPI_STORE) return launch_one<TYPE, PRO_F16, EPI_STORE, false, true>(p, max_entries, pdl, st);
   }
   set_error("qgemv: this prologue / epilogue combination is not built");
   return EINVAL_;
@@ -76,15 +77,16 @@ int qgemv_groups(int K, int N) {
   return ((N + 15) / 16 + tpc - 1) / tpc;
 }
 
-int launch_qgemv(uint32_t type, int pro, int epi, bool dual, bool grouped, const QGemvParams& p, const TailParams& tp, int max_entries, bool pdl, cudaStream_t st) {
+int launch_qgemv(uint32_t type, int pro, int epi, bool dual, bool grouped, const QGemvParams& p, int max_entries, bool pdl, cudaStream_t st) {
   if (p.K % 256 != 0 || p.K <= 0) { set_error("qgemv: row length must be a multiple of 256"); return EINVAL_; }
   if (p.xcols < 1 || p.xcols > QG_MAXCOLS) { set_error("qgemv: xcols out of range"); return EINVAL_; }
-  if ((p.ss_out != nullptr || tp.mode == 1) && qgemv_groups(p.K, p.N) > SS_LD) { set_error("qgemv: more tile groups than partial-sum slots"); return ECAPACITY; }
+  if (p.ss_out != nullptr && qgemv_groups(p.K, p.N) > SS_LD) { set_error("qgemv: more tile groups than partial-sum slots"); return ECAPACITY; }
+  if (pro == PRO_COMBINE && (p.K > QG_COMBINE_MAX_K || p.used < 0 || p.used > 32 || p.M > QG_MAXCOLS || p.h_out == nullptr || p.h_out == p.hsrc)) { set_error("qgemv: combine prologue outside its limits"); return EINVAL_; }
   if (pro == PRO_NORM && (p.ss_n < 1 || p.ss_n > SS_LD)) { set_error("qgemv: bad partial-sum count"); return EINVAL_; }
   switch (type) {
-    case T_Q4_K: return launch_type<T_Q4_K>(pro, epi, dual, grouped, p, tp, max_entries, pdl, st);
-    case T_Q5_K: return launch_type<T_Q5_K>(pro, epi, dual, grouped, p, tp, max_entries, pdl, st);
-    case T_Q6_K: return launch_type<T_Q6_K>(pro, epi, dual, grouped, p, tp, max_entries, pdl, st);
+    case T_Q4_K: return launch_type<T_Q4_K>(pro, epi, dual, grouped, p, max_entries, pdl, st);
+    case T_Q5_K: return launch_type<T_Q5_K>(pro, epi, dual, grouped, p, max_entries, pdl, st);
+    case T_Q6_K: return launch_type<T_Q6_K>(pro, epi, dual, grouped, p, max_entries, pdl, st);
   }
   set_error("qgemv: weight type has no fused projection kernel (Q4_K, Q5_K, Q6_K only)");
   return EINVAL_;

@@ -29,7 +29,8 @@ constexpr int QG_MAXCOLS = 8;
 constexpr int QG_TAIL_ROWS = 8;  // rows the in-kernel tail of the last CTA finishes
 
 enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
-enum { PRO_F16 = 0, PRO_NORM = 1 };
+enum { PRO_F16 = 0, PRO_NORM = 1, PRO_COMBINE = 2 };
+constexpr int QG_COMBINE_MAX_K = 2048;  // PRO_COMBINE keeps a row's values in registers: 8 per thread
 constexpr int SS_LD = 512;  // partial sums of squares kept per activation row
 
 struct QGemvParams {
@@ -65,7 +66,16 @@ struct QGemvParams {
   const float* ss_in;
   int ss_n;
   float eps;
-  __half* xn_out;            // PRO_NORM: optional copy of the normalised rows, [.][K], written by CTA 0
+  __half* xn_out;            // PRO_NORM / PRO_COMBINE: optional copy of the normalised rows, [.][K], written by CTA 0
+  // PRO_COMBINE: the rows are the residual `hsrc` plus the MoE block's output that the expert down
+  // projection left per slot: v = h + (sum_s down[row][s] * topk_w[row][s] in slot order, then the gated
+  // shared expert) (reference: llm/moe.go:347-357, 403-406). Every CTA forms the rows it needs and their
+  // sums of squares itself; CTA 0 also writes them to `h_out`, which must not alias `hsrc` (other CTAs
+  // are still reading it).
+  const float* down;         // [.][used+1][K]
+  const float* topk_w;       // [.][used+1]
+  int used;
+  float* h_out;              // [.][K]
   float* ss_out;             // STORE / RESID: optional partial sums of squares of the rows written, [.][SS_LD], part = tile group
   // epilogue
   float* y;                  // STORE / RESID: float [.][ldy]
@@ -395,16 +405,13 @@ __device__ __forceinline__ void row_moe_combine(float* h, const float* down, con
   }
 }
 
+// Stand-alone row kernels (row_tail_kernel) for passes of more than QG_TAIL_ROWS rows
 struct TailParams {
-  int mode;             // 0 none; 1 (grouped down projection): the last CTA of each grid column adds the
-                        // weighted expert outputs of its rows into the residual and leaves their sum of squares
-  int* col_tickets;     // [gridDim.x]
+  int mode;             // 1 rmsnorm, 2 MoE combine + rmsnorm
   float* h;             // [M][H] residual stream
   const float* down;    // [M][used+1][H]
   const float* topk_w;  // [M][used+1]
-  float* ss_part;       // [M][SS_LD]
   int used, H, M;
-  // stand-alone row tails (row_tail_kernel): 1 rmsnorm, 2 combine + rmsnorm
   const float* gamma;
   __half* xn;
   float eps;
@@ -503,6 +510,81 @@ __device__ __forceinline__ void stage_x_norm(const QGemvParams& p, uint8_t* xs, 
   stage_sx(K, p.xcols, xs, sxs, ncols, xstride);
 }
 
+// The MoE combine and the RMSNorm that follows it, fused into the staging: columns go four at a time,
+// a thread keeping its 8 values of each in registers between the sum of squares and the scaling.
+__device__ __forceinline__ void stage_x_combine(const QGemvParams& p, uint8_t* xs, __half* sxs, float* scratch, float* wsm, int ncols, const int* xrows,
+                                                int xstride, bool writer) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, K = p.K, slots1 = p.used + 1;
+  for (int i = tid; i < ncols * slots1; i += QG_THREADS) wsm[i] = __ldcg(p.topk_w + (size_t)xrows[i / slots1] * slots1 + (i % slots1));
+  __syncthreads();
+  for (int c0 = 0; c0 < ncols; c0 += 4) {
+    float4 v[4][2];
+    float sq[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int cc = 0; cc < 4; cc++) {
+      const int c = c0 + cc < ncols ? c0 + cc : ncols - 1;
+      const int64_t row = xrows[c];
+      const float* hrow = p.hsrc + row * K;
+      const float* dn = p.down + row * slots1 * K;
+      const float* w = wsm + c * slots1;
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        const int k = tid * 4 + i * QG_THREADS * 4;
+        v[cc][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k < K && c0 + cc < ncols) {
+          const float4 hv = __ldcg(reinterpret_cast<const float4*>(hrow + k));
+          const float4 sh = __ldcg(reinterpret_cast<const float4*>(dn + (size_t)p.used * K + k));
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 5
+          for (int s = 0; s < p.used; s++) {
+            const float4 d = __ldcg(reinterpret_cast<const float4*>(dn + (size_t)s * K + k));
+            const float wk = w[s];
+            acc.x += d.x * wk; acc.y += d.y * wk; acc.z += d.z * wk; acc.w += d.w * wk;
+          }
+          const float sg = w[p.used];
+          float4 r;
+          r.x = hv.x + (acc.x + sh.x * sg); r.y = hv.y + (acc.y + sh.y * sg); r.z = hv.z + (acc.z + sh.z * sg); r.w = hv.w + (acc.w + sh.w * sg);
+          v[cc][i] = r;
+          sq[cc] += (r.x * r.x + r.y * r.y) + (r.z * r.z + r.w * r.w);
+          if (writer) *reinterpret_cast<float4*>(p.h_out + row * K + k) = r;
+        }
+      }
+    }
+#pragma unroll
+    for (int cc = 0; cc < 4; cc++) {
+      sq[cc] = warp_sum(sq[cc]);
+      if (lane == 0) scratch[warp * 4 + cc] = sq[cc];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int cc = 0; cc < 4; cc++) {
+      if (c0 + cc >= ncols) break;
+      float t2 = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < QG_WARPS; w2++) t2 += scratch[w2 * 4 + cc];
+      const float scale = 1.0f / sqrtf(t2 / (float)K + p.eps);
+      uint8_t* dst = xs + (size_t)(c0 + cc) * xstride;
+      const int64_t row = xrows[c0 + cc];
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        const int k = tid * 4 + i * QG_THREADS * 4;
+        if (k < K) {
+          const float4 g = *reinterpret_cast<const float4*>(p.gamma + k);
+          const float v0 = v[cc][i].x * scale * g.x, v1 = v[cc][i].y * scale * g.y, v2 = v[cc][i].z * scale * g.z, v3 = v[cc][i].w * scale * g.w;
+          __half2 a = __floats2half2_rn(v0, v2), b = __floats2half2_rn(v1, v3);  // stored order [x0,x2,x1,x3]
+          *reinterpret_cast<uint2*>(dst + 2 * k + 16 * (k >> 6)) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+          if (writer && p.xn_out != nullptr) {
+            __half2 n0 = __floats2half2_rn(v0, v1), n1 = __floats2half2_rn(v2, v3);
+            *reinterpret_cast<uint2*>(p.xn_out + row * K + k) = make_uint2(*reinterpret_cast<uint32_t*>(&n0), *reinterpret_cast<uint32_t*>(&n1));
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  stage_sx(K, p.xcols, xs, sxs, ncols, xstride);
+}
+
 // ---- the kernel ----------------------------------------------------------------------------
 // grid.x: persistent CTAs walking the row-tile groups; grid.y: expert entry (grouped) or 0;
 // grid.z: column tile of 8 activation rows (plain mode).
@@ -511,7 +593,7 @@ __device__ __forceinline__ void stage_x_norm(const QGemvParams& p, uint8_t* xs, 
 // checkpoint's own blocks) through cp.async.bulk into a ring of shared-memory stages, each
 // completing on its mbarrier, so many tiles are in flight per SM without holding registers.
 template <int TYPE, int PRO, int EPI, bool DUAL, bool GROUPED>
-__global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, const TailParams tp) {
+__global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int K = p.K, nb = K / 256;
@@ -526,10 +608,10 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
   const size_t tile_bytes = (size_t)16 * p.stride;
   const size_t stage_bytes = (size_t)tpc * tile_bytes * (DUAL ? 2 : 1);
   const int NS = p.nstage;
-  __shared__ float scratch[2 * QG_WARPS];
+  __shared__ float scratch[4 * QG_WARPS];
   __shared__ float ssq[2][QG_WARPS][8];
+  __shared__ float wsm[PRO == PRO_COMBINE ? QG_MAXCOLS * 33 : 1];
   __shared__ int col_rows[QG_MAXCOLS], xrows[QG_MAXCOLS];
-  __shared__ int is_last;
   __shared__ __align__(8) uint64_t full_bar[QG_MAX_STAGES];
 
   const int tiles = (p.N + 15) / 16;
@@ -604,7 +686,8 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
       xrows[tid] = GROUPED ? id / p.x_div : id;
     }
     __syncthreads();
-    if constexpr (PRO == PRO_NORM) stage_x_norm(p, xs, sxs, scratch, ncols, xrows, xstride, p.xn_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0);
+    if constexpr (PRO == PRO_COMBINE) stage_x_combine(p, xs, sxs, scratch, wsm, ncols, xrows, xstride, blockIdx.x == 0 && blockIdx.y == 0);
+    else if constexpr (PRO == PRO_NORM) stage_x_norm(p, xs, sxs, scratch, ncols, xrows, xstride, p.xn_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0);
     else stage_x_f16(p.x, p.ldx, K, p.xcols, xs, sxs, ncols, xrows, xstride);
     tl_mark(p.tl, 2);
 
@@ -692,50 +775,6 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p, 
     }
   }
   tl_mark(p.tl, 4);
-  // tail of the expert down projection: the last CTA of each grid column owns that column's row groups
-  // for every expert, so it can add the weighted expert outputs into the residual (slot order, then the
-  // gated shared expert: llm/moe.go:347-357, 403-406) without waiting for the other columns
-  if constexpr (GROUPED && EPI == EPI_STORE) {
-    if (tp.mode == 1) {
-      __threadfence();
-      __syncthreads();
-      if (tid == 0) is_last = (atomicAdd(tp.col_tickets + blockIdx.x, 1) == (int)gridDim.y - 1);
-      __syncthreads();
-      if (!is_last) return;
-      __threadfence();
-      if (tid == 0) tp.col_tickets[blockIdx.x] = 0;
-      tl_mark(p.tl, 5, true);
-      const int slots1 = tp.used + 1, rows_per_group = tpc * 16;
-      for (int grp = blockIdx.x; grp < ngroups; grp += gridDim.x) {
-        for (int n = 0; n < tp.M; n++) {
-          float sq = 0.f;
-          for (int r = tid; r < rows_per_group; r += QG_THREADS) {
-            const int row = grp * rows_per_group + r;
-            if (row < tp.H) {
-              const float* dn = tp.down + (size_t)n * slots1 * tp.H + row;
-              const float* w = tp.topk_w + (size_t)n * slots1;
-              float acc = 0.f;
-              for (int k = 0; k < tp.used; k++) acc += __ldcg(dn + (size_t)k * tp.H) * w[k];
-              const float nv = tp.h[(size_t)n * tp.H + row] + (acc + __ldcg(dn + (size_t)tp.used * tp.H) * w[tp.used]);
-              tp.h[(size_t)n * tp.H + row] = nv;
-              sq += nv * nv;
-            }
-          }
-          sq = warp_sum(sq);
-          __syncthreads();
-          if (lane == 0) scratch[warp] = sq;
-          __syncthreads();
-          if (tid == 0) {
-            float t2 = 0.f;
-#pragma unroll
-            for (int w = 0; w < QG_WARPS; w++) t2 += scratch[w];
-            tp.ss_part[(size_t)n * SS_LD + grp] = t2;
-          }
-        }
-      }
-      tl_mark(p.tl, 6, true);
-    }
-  }
 }
 
 }  // namespace b200

@@ -50,8 +50,7 @@ int qgemv_static(uint32_t type, const void* dev_w, int64_t rows, int64_t k, cons
   QGemvParams p{};
   p.w[0] = (const uint8_t*)dev_w; p.seg_end[0] = (int)rows; p.nseg = 1; p.stride = device_row_stride(type, k);
   p.K = (int)k; p.N = (int)rows; p.M = m; p.xcols = m; p.x = x16; p.ldx = k; p.y = dev_y; p.ldy = rows; p.x_div = 1;
-  TailParams no_tail{};
-  B200_TRY(launch_qgemv(type, PRO_F16, EPI_STORE, false, false, p, no_tail, 0, false, 0));
+  B200_TRY(launch_qgemv(type, PRO_F16, EPI_STORE, false, false, p, 0, false, 0));
   B200_CUDA(cudaStreamSynchronize(0));
   return OK;
 }
