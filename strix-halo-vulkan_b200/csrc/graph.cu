@@ -257,6 +257,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       a.q16 = q16; a.partial = attn_partial; a.tickets = attn_tickets; a.ctx16 = ctx16;
       a.M = M; a.Hq = c.n_head; a.Hkv = c.n_head_kv; a.hd = hd; a.rope_dims = std::min(c.rope_dims, hd); a.n_kv = o.n_kv;
       a.split_cells = split_cells; a.nsplit = nsplit; a.eps = c.eps; a.rope_off = f.draft ? 1 : 0;
+      a.tl = tl();
       B200_TRY(launch_attn_pack(a, pdl(), st));
       a.tl = tl();
       B200_TRY(launch_attn_decode(a, pdl(), st));
@@ -275,12 +276,14 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     if (fused) { r.h = hc; r.gamma = (const float*)L.ffn_norm.data; r.ss_in = ss_part; r.ss_n = ss_n; r.eps = c.eps; r.xn_out = xn16; }
     r.M = M; r.H = H; r.nE = c.n_expert; r.used = used; r.logits = r_logits; r.probs = nullptr; r.topk = topk; r.topk_w = topk_w;
     r.tl = tl(); r.margin = margin; r.entries = entries; r.n_entries = n_entries; r.cols = cols; r.ticket = r_ticket; r.max_entries = max_entries;
+    r.defer = fused && M == 1;
     B200_TRY(launch_router(r, pdl(), st));
     const int ne = max_entries_for(M);
     QGemvParams p = base(L.gate_exps, H, c.ffn_expert, xn16, H);
     p.w2[0] = L.up_exps.data; p.ws = L.gate_sh.data; p.ws2 = L.up_sh.data; p.expert_stride = (int64_t)c.ffn_expert * L.gate_exps.stride;
     p.entries = entries; p.n_entries = n_entries; p.cols = cols; p.x_div = slots1;
     p.y16 = act16; p.ldy = c.ffn_expert;
+    p.route_here = r.defer; p.route = r;
     B200_TRY(launch_qgemv(L.gate_exps.type, PRO_F16, EPI_SWIGLU, true, true, p, ne, pdl(), st));
     QGemvParams q = base(L.down_exps, c.ffn_expert, H, act16, c.ffn_expert);
     q.ws = L.down_sh.data; q.expert_stride = (int64_t)H * L.down_exps.stride;

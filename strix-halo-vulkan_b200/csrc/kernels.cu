@@ -226,59 +226,6 @@ static int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem
 // =========================================================================================
 constexpr int RT_ROWS = 8;  // router rows per CTA: one per warp
 
-// softmax + top-k + weights of one token by one warp; a lane owns experts lane + 32*i in registers
-// (reference: llm/moe.go:219-282, 426-443; shaders/llm_moe_route_decode.comp:84-213)
-template <int NPL>
-__device__ __forceinline__ void route_token(const RouterParams& p, int n, int lane) {
-  const int nE = p.nE, used = p.used;
-  float pv[NPL];
-  float mx = -INFINITY;
-#pragma unroll
-  for (int i = 0; i < NPL; i++) {
-    const int e = lane + 32 * i;
-    pv[i] = e < nE ? __ldcg(p.logits + (size_t)n * nE + e) : -INFINITY;
-    mx = fmaxf(mx, pv[i]);
-  }
-  mx = warp_max(mx);
-  float sum = 0.f;
-#pragma unroll
-  for (int i = 0; i < NPL; i++) { pv[i] = lane + 32 * i < nE ? expf(pv[i] - mx) : 0.f; sum += pv[i]; }
-  sum = warp_sum(sum);
-  const float inv = 1.0f / sum;
-#pragma unroll
-  for (int i = 0; i < NPL; i++) {
-    pv[i] = lane + 32 * i < nE ? pv[i] * inv : -1.f;
-    if (p.probs != nullptr && lane + 32 * i < nE) p.probs[(size_t)n * nE + lane + 32 * i] = pv[i];
-  }
-  // top-k by descending probability, ties to the lower index (llm/moe.go:249-252). Probabilities
-  // are non-negative, so their bit patterns order like unsigned integers: one warp-wide max of the
-  // values, then one warp-wide min of the indices that hold it.
-  float wsum = 0.f, last_p = 0.f, myw = 0.f;
-  for (int k = 0; k <= used; k++) {
-    float bv = pv[0]; int bi = 0;
-#pragma unroll
-    for (int i = 1; i < NPL; i++) if (pv[i] > bv) { bv = pv[i]; bi = i; }
-    const uint32_t key = bv < 0.f ? 0u : __float_as_uint(bv) + 1u;          // taken / absent entries sort last
-    const uint32_t best = __reduce_max_sync(0xffffffffu, key);
-    const uint32_t mine = key == best && best != 0u ? (uint32_t)(lane + 32 * bi) : 0x7fffffffu;
-    const int widx = (int)__reduce_min_sync(0xffffffffu, mine);
-    const float wv = best == 0u ? -1.f : __uint_as_float(best - 1u);
-    if (k == used) {
-      if (lane == 0 && p.margin) p.margin[n] = last_p > 0.f ? (last_p - fmaxf(wv, 0.f)) / last_p : 0.f;
-      break;
-    }
-    if ((widx & 31) == lane) {
-#pragma unroll
-      for (int i = 0; i < NPL; i++) if (i == (widx >> 5)) pv[i] = -1.f;
-    }
-    if (lane == k) { myw = wv; p.topk[(size_t)n * used + k] = widx; }
-    wsum += wv; last_p = wv;
-  }
-  // normalise the weights (llm/moe.go:256-282)
-  if (wsum < 6.103515625e-5f) wsum = 6.103515625e-5f;
-  if (lane < used) p.topk_w[(size_t)n * (used + 1) + lane] = myw / wsum;
-}
-
 __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   __shared__ int is_last;
   __shared__ int counts[1025], offs[1025], eoff[1025];
@@ -364,6 +311,7 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
     }
   }
   tl_mark(p.tl, 4);
+  if (p.defer) return;  // the expert kernel selects the experts itself
   // the last CTA to finish routes every token and builds the expert work list
   __threadfence();
   __syncthreads();
@@ -660,8 +608,10 @@ int launch_dn_step(const DnStepParams& p, bool pdl, cudaStream_t st) {
 __global__ void attn_pack_kernel(AttnParams p) {
   const int hd = p.hd, d = threadIdx.x, n = blockIdx.y, which = blockIdx.x;
   __shared__ float buf[256], red[8];
+  tl_mark(p.tl, 0);
   pdl_wait();
   pdl_launch();
+  tl_mark(p.tl, 1);
   const float* pr = p.proj + (size_t)n * p.ldp;
   const int pos = p.row_pos[n], slot = p.row_slot[n];
   const int kv_off = p.Hq * 2 * hd;
@@ -844,8 +794,10 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(AttnParams p) {
 // sigmoid(gate), to fp16 (reference: shaders/llm_attn_combine.comp:43-102). grid (Hq, M), block hd.
 __global__ void attn_merge_kernel(AttnParams p) {
   const int head = blockIdx.x, n = blockIdx.y, d = threadIdx.x, hd = p.hd, PW = hd + 2;
+  tl_mark(p.tl, 0);
   pdl_wait();
   pdl_launch();
+  tl_mark(p.tl, 1);
   const int nlive = (p.row_pos[n] + 1 + p.split_cells - 1) / p.split_cells;
   const float* part = p.partial + ((size_t)n * p.Hq + head) * p.nsplit * PW;
   float mm = -INFINITY;

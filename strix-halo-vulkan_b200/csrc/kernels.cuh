@@ -38,23 +38,6 @@ int qgemv_groups(int K, int N);
 int launch_row_tail(const TailParams& tp, bool pdl, cudaStream_t st);
 int launch_concat_norm(const float* e, const float* hs, const float* enorm, const float* hnorm, float eps, int H, int M, __half* xcat, bool pdl, cudaStream_t st);
 
-struct RouterParams {
-  const __half* xn;                                // [M][H] ffn_norm output, fp16 (when h is null)
-  const float* h; const float* gamma; const float* ss_in; int ss_n; float eps;  // or: normalise the residual rows here
-  __half* xn_out;                                  // ... and leave the fp16 rows for the expert kernels (CTA 0)
-  DTensor router;                                  // [nE][H], F32 / F16 / Q8_0 (planes)
-  const float* sh_gate;                            // [H] F32
-  int M, H, nE, used;
-  float* logits;       // [M][nE]
-  float* probs;        // [M][nE]
-  int32_t* topk;       // [M][used]
-  float* topk_w;       // [M][used+1] (last = sigmoid(shared gate))
-  float* margin;       // [M] optional: (p_k - p_{k+1}) / p_k
-  int4* entries; int* n_entries; int* cols;   // expert work list for the grouped kernels
-  int* ticket;
-  int max_entries;
-  Timeline tl;
-};
 int launch_router(const RouterParams& p, bool pdl, cudaStream_t st);
 
 

@@ -20,6 +20,7 @@
 // fp16 above 2048 (relative error <= 2^-12 on those weights).
 #pragma once
 #include "common.cuh"
+#include "router.cuh"
 
 namespace b200 {
 
@@ -49,6 +50,11 @@ struct QGemvParams {
   const uint8_t* ws;         // shared expert weights (grouped mode)
   const uint8_t* ws2;
   int x_div;                 // grouped: x row = cols[c] / x_div
+  // grouped, single-row passes: the router kernel stopped after the logits (route.defer); every CTA
+  // selects the experts itself (one warp, a few hundred instructions) instead of waiting for a last
+  // router CTA to do it, and CTA (0,0) leaves the selection and the work list for the kernels after it
+  int route_here;
+  RouterParams route;
   // plain mode columns: rows [ztile*8, ztile*8+8) of M
   int M;
   int xcols;                 // columns the shared-memory layout is sized for (1..8)
@@ -612,6 +618,7 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p) 
   __shared__ float ssq[2][QG_WARPS][8];
   __shared__ float wsm[PRO == PRO_COMBINE ? QG_MAXCOLS * 33 : 1];
   __shared__ int col_rows[QG_MAXCOLS], xrows[QG_MAXCOLS];
+  __shared__ int route_expert, route_topk[32];
   __shared__ __align__(8) uint64_t full_bar[QG_MAX_STAGES];
 
   const int tiles = (p.N + 15) / 16;
@@ -629,10 +636,27 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p) 
   int ncols = 0, col_off = 0;
   bool active = true;
   if constexpr (GROUPED) {
-    pdl_wait();  // the entries are written by the router kernel
-    active = (int)blockIdx.y < *p.n_entries;
+    pdl_wait();  // the entries (or the logits) are written by the router kernel
+    int4 e;
+    if (p.route_here) {
+      const int used = p.route.used, y = blockIdx.y;
+      const bool writer = blockIdx.x == 0 && y == 0;
+      active = y <= used;
+      if (warp == 0 && (active || writer)) {
+        const int ex = p.route.nE <= 512 ? route_token<16>(p.route, 0, lane, writer, y, route_topk) : route_token<32>(p.route, 0, lane, writer, y, route_topk);
+        if (lane == 0) route_expert = y < used ? ex : -1;
+      }
+      __syncthreads();
+      e = make_int4(route_expert, y, 1, 0);
+      if (writer) {  // the work list of a single row: one entry per slot, the shared expert last
+        if (tid < used) { p.route.entries[tid] = make_int4(route_topk[tid], tid, 1, 0); p.route.cols[tid] = tid; }
+        if (tid == used) { p.route.entries[used] = make_int4(-1, used, 1, 0); p.route.cols[used] = used; *p.route.n_entries = used + 1; }
+      }
+    } else {
+      active = (int)blockIdx.y < *p.n_entries;
+      if (active) e = p.entries[blockIdx.y];
+    }
     if (active) {
-      const int4 e = p.entries[blockIdx.y];
       col_off = e.y; ncols = e.z;
       wa = e.x >= 0 ? p.w[0] + (size_t)e.x * p.expert_stride : p.ws;
       if constexpr (DUAL) wb = e.x >= 0 ? p.w2[0] + (size_t)e.x * p.expert_stride : p.ws2;
@@ -680,7 +704,7 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p) 
     if (tid < QG_MAXCOLS) {
       const int c = tid < ncols ? tid : 0;
       int id;
-      if constexpr (GROUPED) id = p.cols[col_off + c];
+      if constexpr (GROUPED) id = p.route_here ? col_off + c : p.cols[col_off + c];
       else id = p.row_ids ? p.row_ids[col_off + c] : col_off + c;
       col_rows[tid] = id;
       xrows[tid] = GROUPED ? id / p.x_div : id;
