@@ -714,6 +714,11 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(AttnParams p) {
       ka4[j] = ldg_stream(kra + 8 * (t + 4 * j));
       kb4[j] = ldg_stream(krb + 8 * (t + 4 * j));
     }
+    // the first value block does not depend on the scores: fetch it while the score mma runs
+    const int cell_a = cb + 2 * t, cell_c = cb + 8 + 2 * t;
+    const int va_c = min(cell_a, c1 - 1), vb_c = min(cell_a + 1, c1 - 1), vc_c = min(cell_c, c1 - 1), vd_c = min(cell_c + 1, c1 - 1);
+    uint4 va = ldg_stream(vbase + (size_t)va_c * cell_stride + 8 * g), vb = ldg_stream(vbase + (size_t)vb_c * cell_stride + 8 * g);
+    uint4 vc = ldg_stream(vbase + (size_t)vc_c * cell_stride + 8 * g), vd = ldg_stream(vbase + (size_t)vd_c * cell_stride + 8 * g);
 #pragma unroll
     for (int j = 0; j < KS / 2; j++) {
       const uint32_t a0[4] = {qa[2 * j][0], 0u, qa[2 * j][1], 0u}, a1[4] = {qa[2 * j + 1][0], 0u, qa[2 * j + 1][1], 0u};
@@ -739,13 +744,15 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(AttnParams p) {
     m = mn;
     const uint32_t pa[4] = {pack_half2(pv[0], pv[1]), 0u, pack_half2(pv[2], pv[3]), 0u};
     // ---- O = O * corr + P V ----
-    const int va_c = min(cell[0], c1 - 1), vb_c = min(cell[1], c1 - 1), vc_c = min(cell[2], c1 - 1), vd_c = min(cell[3], c1 - 1);
 #pragma unroll
     for (int b = 0; b < NB; b++) {
-      const int doff = 8 * (g + 8 * b);
-      const uint4 va = ldg_stream(vbase + (size_t)va_c * cell_stride + doff), vb = ldg_stream(vbase + (size_t)vb_c * cell_stride + doff);
-      const uint4 vc = ldg_stream(vbase + (size_t)vc_c * cell_stride + doff), vd = ldg_stream(vbase + (size_t)vd_c * cell_stride + doff);
-      const uint32_t ra[4] = {va.x, va.y, va.z, va.w}, rb[4] = {vb.x, vb.y, vb.z, vb.w}, rc[4] = {vc.x, vc.y, vc.z, vc.w}, rd[4] = {vd.x, vd.y, vd.z, vd.w};
+      const uint4 wa = va, wb = vb, wc = vc, wd = vd;
+      if (b + 1 < NB) {  // next block's loads go out before this block's mma
+        const int doff = 8 * (g + 8 * (b + 1));
+        va = ldg_stream(vbase + (size_t)va_c * cell_stride + doff); vb = ldg_stream(vbase + (size_t)vb_c * cell_stride + doff);
+        vc = ldg_stream(vbase + (size_t)vc_c * cell_stride + doff); vd = ldg_stream(vbase + (size_t)vd_c * cell_stride + doff);
+      }
+      const uint32_t ra[4] = {wa.x, wa.y, wa.z, wa.w}, rb[4] = {wb.x, wb.y, wb.z, wb.w}, rc[4] = {wc.x, wc.y, wc.z, wc.w}, rd[4] = {wd.x, wd.y, wd.z, wd.w};
 #pragma unroll
       for (int j = 0; j < 4; j++) {
         float acc_e[4] = {o[b * 8 + 2 * j][0] * corr, o[b * 8 + 2 * j][1] * corr, 0.f, 0.f};
@@ -794,31 +801,43 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(AttnParams p) {
 // sigmoid(gate), to fp16 (reference: shaders/llm_attn_combine.comp:43-102). grid (Hq, M), block hd.
 __global__ void attn_merge_kernel(AttnParams p) {
   const int head = blockIdx.x, n = blockIdx.y, d = threadIdx.x, hd = p.hd, PW = hd + 2;
+  extern __shared__ float mg_f[];  // [nsplit] factors exp(m_s - m*), then [nsplit] row sums
+  __shared__ float mg_red[8];
   tl_mark(p.tl, 0);
   pdl_wait();
   pdl_launch();
   tl_mark(p.tl, 1);
   const int nlive = (p.row_pos[n] + 1 + p.split_cells - 1) / p.split_cells;
   const float* part = p.partial + ((size_t)n * p.Hq + head) * p.nsplit * PW;
+  // one round of loads for every split's maximum and row sum, shared through shared memory
+  float mloc = -INFINITY;
+  for (int sp = d; sp < nlive; sp += blockDim.x) {
+    const float ms = __ldcg(part + (size_t)sp * PW + hd);
+    mg_f[sp] = ms; mg_f[p.nsplit + sp] = __ldcg(part + (size_t)sp * PW + hd + 1);
+    mloc = fmaxf(mloc, ms);
+  }
+  mloc = warp_max(mloc);
+  if ((d & 31) == 0) mg_red[d >> 5] = mloc;
+  __syncthreads();
   float mm = -INFINITY;
-  for (int sp = 0; sp < nlive; sp++) mm = fmaxf(mm, __ldcg(part + (size_t)sp * PW + hd));
+  for (int w = 0; w < (int)(blockDim.x + 31) / 32; w++) mm = fmaxf(mm, mg_red[w]);
   float ov = 0.f, lv = 0.f;
   int sp = 0;
-  for (; sp + 4 <= nlive; sp += 4) {  // four independent loads in flight, summed in split order
-    float a[4], f[4], ls[4];
+  for (; sp + 8 <= nlive; sp += 8) {  // eight independent loads in flight, summed in split order
+    float a[8];
 #pragma unroll
-    for (int u = 0; u < 4; u++) {
-      a[u] = __ldcg(part + (size_t)(sp + u) * PW + d);
-      f[u] = __ldcg(part + (size_t)(sp + u) * PW + hd);
-      ls[u] = __ldcg(part + (size_t)(sp + u) * PW + hd + 1);
+    for (int u = 0; u < 8; u++) a[u] = __ldcg(part + (size_t)(sp + u) * PW + d);
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const float ms = mg_f[sp + u];
+      const float e = ms == -INFINITY ? 0.f : expf(ms - mm);
+      ov += a[u] * e; lv += mg_f[p.nsplit + sp + u] * e;
     }
-#pragma unroll
-    for (int u = 0; u < 4; u++) { const float e = f[u] == -INFINITY ? 0.f : expf(f[u] - mm); ov += a[u] * e; lv += ls[u] * e; }
   }
   for (; sp < nlive; sp++) {
-    const float ms = __ldcg(part + (size_t)sp * PW + hd);
+    const float ms = mg_f[sp];
     const float e = ms == -INFINITY ? 0.f : expf(ms - mm);
-    ov += __ldcg(part + (size_t)sp * PW + d) * e; lv += __ldcg(part + (size_t)sp * PW + hd + 1) * e;
+    ov += __ldcg(part + (size_t)sp * PW + d) * e; lv += mg_f[p.nsplit + sp] * e;
   }
   const float gate = p.proj[(size_t)n * p.ldp + head * 2 * hd + hd + d];
   p.ctx16[(size_t)n * p.Hq * hd + head * hd + d] = __float2half_rn(ov / lv * sigmoid_acc(gate));
@@ -837,7 +856,7 @@ int launch_attn_decode(const AttnParams& p, bool pdl, cudaStream_t st) {
   return s;
 }
 int launch_attn_merge(const AttnParams& p, bool pdl, cudaStream_t st) {
-  return launch_k(attn_merge_kernel, dim3(p.Hq, p.M), dim3(p.hd), 0, pdl, st, p);
+  return launch_k(attn_merge_kernel, dim3(p.Hq, p.M), dim3(p.hd), (size_t)2 * p.nsplit * sizeof(float), pdl, st, p);
 }
 
 // =========================================================================================
