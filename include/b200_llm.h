@@ -147,6 +147,10 @@ int32_t b200_draft_rewind(b200_graph* g, int32_t past);
 int32_t b200_dequantize(uint32_t type, const void* host_data, int64_t n, float* host_out);
 /* y[m][rows] = W[rows][k] . fp16(x[m][k]) through the fused K-quant projection kernel. */
 int32_t b200_qgemv(uint32_t type, const void* host_w, int64_t rows, int64_t k, const float* host_x, int32_t m, float* host_y);
+/* y[m][rows] = fp16(W[rows][k]) . fp16(x[m][k]) through the tensor-core (tcgen05 / TMEM) projection of
+ * many-row passes; tile_rows = activation rows per tile (64, 128 or 256). The reference's prefill GEMM
+ * arithmetic: dequantised weights rounded to fp16 (shaders/llm_gemm.comp MODE 2). */
+int32_t b200_qgemm(uint32_t type, const void* host_w, int64_t rows, int64_t k, const float* host_x, int32_t m, int32_t tile_rows, float* host_y);
 /* No counterpart in the reference. The same projection for callers that cannot allocate device
  * memory (inside a stream capture, on a thread that may not take the allocator's lock, or under
  * a fixed memory budget): all pointers are DEVICE pointers the caller already owns, and the fp16

@@ -217,6 +217,40 @@ int32_t b200_qgemv(uint32_t type, const void* host_w, int64_t rows, int64_t k, c
   return s;
 }
 
+int32_t b200_qgemm(uint32_t type, const void* host_w, int64_t rows, int64_t k, const float* host_x, int32_t mrows, int32_t tile_rows, float* host_y) {
+  B200_TRY(need_device());
+  if (!host_w || !host_x || !host_y || rows <= 0 || mrows <= 0) { set_error("qgemm: bad argument"); return EINVAL_; }
+  const int64_t rb = gguf_row_bytes(type, k);
+  if (rb < 0) { set_error("qgemm: bad type or row length"); return EINVAL_; }
+  DTensor t; t.type = type; t.k = k; t.rows = rows; t.stride = device_row_stride(type, k);
+  uint8_t* src = nullptr; float *xf = nullptr, *y = nullptr; __half* x16 = nullptr;
+  B200_CUDA(cudaMalloc((void**)&src, (size_t)(rb * rows)));
+  B200_CUDA(cudaMalloc((void**)&t.data, (size_t)(t.stride * rows) + 256));
+  B200_CUDA(cudaMalloc((void**)&xf, (size_t)mrows * k * sizeof(float)));
+  B200_CUDA(cudaMalloc((void**)&x16, (size_t)mrows * k * sizeof(__half)));
+  B200_CUDA(cudaMalloc((void**)&y, (size_t)mrows * rows * sizeof(float)));
+  int s = OK;
+  if (cudaMemcpy(src, host_w, (size_t)(rb * rows), cudaMemcpyHostToDevice) != cudaSuccess || cudaMemcpy(xf, host_x, (size_t)mrows * k * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess) s = ECUDA;
+  if (s == OK) s = repack_rows(type, k, rows, src, t.data, 0);
+  if (s == OK) s = quantize_rows_device(T_F16, xf, mrows, k, (uint8_t*)x16, 0);
+  alignas(64) unsigned char tmap[128];
+  if (s == OK) s = make_x_tensor_map(x16, mrows, (int)k, tile_rows, tmap);
+  int* err = nullptr;
+  if (s == OK && (cudaMalloc((void**)&err, sizeof(int)) != cudaSuccess || cudaMemset(err, 0, sizeof(int)) != cudaSuccess)) s = ECUDA;
+  if (s == OK) {
+    QGemmParams p{};
+    p.one.w = t.data; p.one.x_row0 = 0; p.one.count = mrows; p.one.y_row0 = 0; p.max_problems = 1;
+    p.stride = t.stride; p.K = (int)k; p.N = (int)rows; p.y = y; p.ldy = rows; p.err = err;
+    s = launch_qgemm(type, GEMM_STORE, tile_rows, p, tmap, false, 0);
+  }
+  int herr = 0;
+  if (s == OK && cudaMemcpy(&herr, err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) { set_error(std::string("qgemm: ") + cudaGetErrorString(cudaGetLastError())); s = ECUDA; }
+  if (s == OK && herr != 0) { set_error("qgemm: a bounded barrier wait gave up"); s = ETIMEOUT; }
+  if (s == OK && cudaMemcpy(host_y, y, (size_t)mrows * rows * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) { set_error(std::string("qgemm: ") + cudaGetErrorString(cudaGetLastError())); s = ECUDA; }
+  cudaFree(src); cudaFree(t.data); cudaFree(xf); cudaFree(x16); cudaFree(y); cudaFree(err);
+  return s;
+}
+
 int32_t b200_qgemv_static(uint32_t type, const void* dev_w, int64_t rows, int64_t k, const float* dev_x, int32_t m, float* dev_y) {
   B200_TRY(need_device());
   return qgemv_static(type, dev_w, rows, k, dev_x, m, dev_y);

@@ -2,6 +2,7 @@
 #pragma once
 #include "common.cuh"
 #include "qgemv.cuh"
+#include "qgemm.cuh"
 
 namespace b200 {
 

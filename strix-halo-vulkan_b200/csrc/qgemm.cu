@@ -1,0 +1,410 @@
+// tcgen05 / TMEM GEMM for many-row K-quant projections (see qgemm.cuh).
+#include <cuda.h>
+
+#include <algorithm>
+#include <cstring>
+#include <string>
+
+#include "qgemm.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int GM_THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5: dequant + epilogue
+constexpr int GM_ROWS = 128;      // weight rows per tile = UMMA M = TMEM lanes
+constexpr int GM_KSTEP = 64;      // fp16 elements per K step = one 128-byte swizzle row
+constexpr int A_BYTES = GM_ROWS * 128;
+
+__host__ __device__ constexpr int gm_stages(int tn, bool dual) { return tn >= 256 ? (dual ? 3 : 4) : tn >= 128 ? (dual ? 4 : 6) : (dual ? 5 : 8); }
+__host__ __device__ constexpr int gm_stage_bytes(int tn, bool dual) { return A_BYTES * (dual ? 2 : 1) + tn * 128; }
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory"); }
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tm, int c0, int c1, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_u32(dst)), "l"(tm), "r"(c0),
+               "r"(c1), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc], fp16 x fp16 -> f32
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// 32 consecutive f32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+        "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+        "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile of 128-byte rows, 128-byte swizzle: rows 128 bytes
+// apart, groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// kind::f16 instruction descriptor: f32 accumulate, fp16 A and B, both K-major, M 128, N tn
+__host__ __device__ constexpr uint32_t idesc_f16(int tn) { return (1u << 4) | ((uint32_t)(tn >> 3) << 17) | ((uint32_t)(GM_ROWS >> 4) << 24); }
+
+__device__ __forceinline__ uint4 ldg128(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// ---- dequantisation of 64 consecutive elements of one weight row ------------------------------
+// Each returns the values as eight 16-byte chunks of fp16 (chunk c = elements 8c..8c+7 of the K step).
+// Arithmetic follows gguf/dequant.go (unfused multiply, subtract), then one rounding to fp16.
+struct RowCache {  // what a thread keeps of its row's current super-block between K steps
+  uint4 hdr;       // Q4_K / Q5_K: d, dmin, 12 scale bytes. Q6_K: 16 int8 scales
+  uint4 qh0, qh1;  // Q5_K: the 32 fifth-bit bytes
+  float d;         // Q6_K
+};
+
+__device__ __forceinline__ void k4_scale_min_dev(int j, const uint4& hdr, int& sc, int& m) {  // gguf/dequant.go:238-243
+  const uint32_t w[3] = {hdr.y, hdr.z, hdr.w};
+  auto byte_at = [&](int i) { return (int)((w[i >> 2] >> (8 * (i & 3))) & 0xFF); };
+  if (j < 4) { sc = byte_at(j) & 63; m = byte_at(j + 4) & 63; }
+  else { sc = (byte_at(j + 4) & 0xF) | ((byte_at(j - 4) >> 6) << 4); m = (byte_at(j + 4) >> 4) | ((byte_at(j) >> 6) << 4); }
+}
+
+template <int TYPE>
+__device__ __forceinline__ void dequant64(const uint8_t* row, int nb, int ks, RowCache& rc, uint4 (&out)[8]) {
+  const int blk = ks >> 2, j = ks & 3;
+  if constexpr (TYPE == T_Q4_K || TYPE == T_Q5_K) {
+    constexpr int BS = TYPE == T_Q4_K ? 144 : 176, QOFF = TYPE == T_Q4_K ? 16 : 48;
+    const uint8_t* b = row + (size_t)blk * BS;
+    if (j == 0) {
+      rc.hdr = ldg128(b);
+      if constexpr (TYPE == T_Q5_K) { rc.qh0 = ldg128(b + 16); rc.qh1 = ldg128(b + 32); }
+    }
+    const uint4 q0 = ldg128(b + QOFF + 32 * j), q1 = ldg128(b + QOFF + 32 * j + 16);
+    const float d = h2f_lo(rc.hdr.x), dmin = h2f_hi(rc.hdr.x);
+    int sc0, m0, sc1, m1;
+    k4_scale_min_dev(2 * j, rc.hdr, sc0, m0);
+    k4_scale_min_dev(2 * j + 1, rc.hdr, sc1, m1);
+    const float d0 = __fmul_rn(d, (float)sc0), mm0 = __fmul_rn(dmin, (float)m0), d1 = __fmul_rn(d, (float)sc1), mm1 = __fmul_rn(dmin, (float)m1);
+    const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    uint32_t hb[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if constexpr (TYPE == T_Q5_K) {
+      hb[0] = rc.qh0.x; hb[1] = rc.qh0.y; hb[2] = rc.qh0.z; hb[3] = rc.qh0.w; hb[4] = rc.qh1.x; hb[5] = rc.qh1.y; hb[6] = rc.qh1.z; hb[7] = rc.qh1.w;
+    }
+    // low nibbles: sub-block 2j (chunks 0..3), high nibbles: sub-block 2j+1 (chunks 4..7); word w holds bytes 4w..4w+3
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+      uint32_t lo[4], hi[4];
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        const uint32_t w = qw[2 * c + h], hw = hb[2 * c + h];
+        float vl[4], vh[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          int ql = (w >> (8 * e)) & 0xF, qh = (w >> (8 * e + 4)) & 0xF;
+          if constexpr (TYPE == T_Q5_K) {
+            const uint32_t hbyte = hw >> (8 * e);
+            ql += ((hbyte >> (2 * j)) & 1) << 4;
+            qh += ((hbyte >> (2 * j + 1)) & 1) << 4;
+          }
+          vl[e] = __fsub_rn(__fmul_rn(d0, (float)ql), mm0);
+          vh[e] = __fsub_rn(__fmul_rn(d1, (float)qh), mm1);
+        }
+        lo[2 * h] = pack_h2(vl[0], vl[1]); lo[2 * h + 1] = pack_h2(vl[2], vl[3]);
+        hi[2 * h] = pack_h2(vh[0], vh[1]); hi[2 * h + 1] = pack_h2(vh[2], vh[3]);
+      }
+      out[c] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      out[4 + c] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    }
+  } else {  // Q6_K row planes: ql[nb][128] | qh[nb][64] | scales[nb][16] | d[nb]
+    const int hf = j >> 1, up = j & 1;  // quarters 2*up, 2*up+1 of half hf
+    const uint8_t* ql = row + (size_t)blk * 128 + 64 * hf;
+    const uint8_t* qh = row + (size_t)nb * 128 + (size_t)blk * 64 + 32 * hf;
+    if (j == 0) {
+      rc.hdr = ldg128(row + (size_t)nb * 192 + (size_t)blk * 16);
+      rc.d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(row + (size_t)nb * 208 + (size_t)blk * 2)));
+    }
+    const uint4 la0 = ldg128(ql), la1 = ldg128(ql + 16), lb0 = ldg128(ql + 32), lb1 = ldg128(ql + 48), h0 = ldg128(qh), h1 = ldg128(qh + 16);
+    const uint32_t lw[2][8] = {{la0.x, la0.y, la0.z, la0.w, la1.x, la1.y, la1.z, la1.w}, {lb0.x, lb0.y, lb0.z, lb0.w, lb1.x, lb1.y, lb1.z, lb1.w}};
+    const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+    const uint32_t scw[4] = {rc.hdr.x, rc.hdr.y, rc.hdr.z, rc.hdr.w};
+#pragma unroll
+    for (int qq = 0; qq < 2; qq++) {      // quarter 2*up + qq: elements l = 0..31, chunks 4*qq .. 4*qq+3
+      const int quarter = 2 * up + qq;
+#pragma unroll
+      for (int c = 0; c < 4; c++) {       // l = 8c .. 8c+7: words 2c, 2c+1; scale index 8*hf + l/16 + 2*quarter
+        const int si = 8 * hf + (c >> 1) + 2 * quarter;
+        const float ds = __fmul_rn(rc.d, (float)(int)(int8_t)((scw[si >> 2] >> (8 * (si & 3))) & 0xFF));
+        uint32_t o[4];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+          const uint32_t w = lw[qq][2 * c + h], hb = hw[2 * c + h];
+          float v[4];
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const int nib = up ? (w >> (8 * e + 4)) & 0xF : (w >> (8 * e)) & 0xF;
+            const int q = (nib | ((int)((hb >> (8 * e + 2 * quarter)) & 3) << 4)) - 32;
+            v[e] = __fmul_rn(ds, (float)q);
+          }
+          o[2 * h] = pack_h2(v[0], v[1]); o[2 * h + 1] = pack_h2(v[2], v[3]);
+        }
+        out[4 * qq + c] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+}
+
+// chunk c of row r of a [rows][128-byte] tile under the 128-byte swizzle
+__device__ __forceinline__ void store_swizzled(uint8_t* tile, int r, const uint4 (&v)[8]) {
+#pragma unroll
+  for (int c = 0; c < 8; c++) *reinterpret_cast<uint4*>(tile + r * 128 + ((c ^ (r & 7)) << 4)) = v[c];
+}
+
+template <int TYPE, int TN, int EPI>
+__global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant__ CUtensorMap tmx, const QGemmParams p) {
+  constexpr bool DUAL = EPI == GEMM_SWIGLU;
+  constexpr int NS = gm_stages(TN, DUAL), STAGE = gm_stage_bytes(TN, DUAL), B_OFF = A_BYTES * (DUAL ? 2 : 1);
+  constexpr uint32_t TCOLS = (DUAL ? 2 : 1) * TN < 32 ? 32 : (DUAL ? 2 : 1) * TN;  // 64, 128, 256 or 512: a power of two
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_a[NS], full_b[NS], empty[NS], acc_full, acc_empty;
+  __shared__ uint32_t tmem_base_sm;
+  __shared__ volatile int failed;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    for (int s = 0; s < NS; s++) { mbar_init(&full_a[s], 4); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(&acc_full, 1); mbar_init(&acc_empty, 4);
+    mbar_fence_init();
+    failed = 0;
+  }
+  if (warp == 1) tmem_alloc(&tmem_base_sm, TCOLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_sm;
+  pdl_wait();
+  pdl_launch();
+
+  const int n_prob = p.n_problems != nullptr ? *p.n_problems : 1;
+  const bool have = (int)blockIdx.y < n_prob;
+  GemmProblem pr = p.one;
+  if (have && p.problems != nullptr) pr = p.problems[blockIdx.y];
+  const int K = p.K, nb = K / 256, ksteps = K / GM_KSTEP;
+  const int n_tiles = (p.N + GM_ROWS - 1) / GM_ROWS, t_tiles = have ? (pr.count + TN - 1) / TN : 0, tiles = n_tiles * t_tiles;
+  auto give_up = [&]() { if (p.err != nullptr) atomicExch(p.err, 1); failed = 1; };
+
+  if (warp == 0) {
+    // ---- activation tiles by TMA -----------------------------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < tiles && !failed; tile += gridDim.x) {
+        const int tt = tile / n_tiles;
+        for (int ks = 0; ks < ksteps; ks++, it++) {
+          const int s = it % NS;
+          if (!mbar_wait(&empty[s], ((it / NS) & 1) ^ 1)) { give_up(); break; }
+          mbar_expect_tx(&full_b[s], TN * 128);
+          tma_load_2d(smem + (size_t)s * STAGE + B_OFF, &tmx, ks * GM_KSTEP, pr.x_row0 + tt * TN, &full_b[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issue ---------------------------------------------------------------------------
+    if (lane == 0) {
+      uint32_t it = 0, tcount = 0;
+      constexpr uint32_t idesc = idesc_f16(TN);
+      for (int tile = blockIdx.x; tile < tiles && !failed; tile += gridDim.x, tcount++) {
+        if (!mbar_wait(&acc_empty, (tcount & 1) ^ 1)) { give_up(); break; }  // the epilogue has drained the accumulator
+        tc_fence_after();
+        bool ok = true;
+        for (int ks = 0; ks < ksteps; ks++, it++) {
+          const int s = it % NS;
+          const uint32_t ph = (it / NS) & 1;
+          if (!mbar_wait(&full_a[s], ph) || !mbar_wait(&full_b[s], ph)) { give_up(); ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE), b_addr = a_addr + B_OFF;
+          const uint64_t adesc = smem_desc_sw128(a_addr), bdesc = smem_desc_sw128(b_addr);
+#pragma unroll
+          for (int k4 = 0; k4 < GM_KSTEP / 16; k4++) {  // 32 bytes along K per instruction: +2 in the address field
+            tc_mma_f16(tmem_base, adesc + 2 * k4, bdesc + 2 * k4, idesc, (ks | k4) != 0);
+            if constexpr (DUAL) tc_mma_f16(tmem_base + TN, smem_desc_sw128(a_addr + A_BYTES) + 2 * k4, bdesc + 2 * k4, idesc, (ks | k4) != 0);
+          }
+          tc_commit(&empty[s]);  // arrives when the instructions above have read the stage
+        }
+        if (!ok) break;
+        tc_commit(&acc_full);
+      }
+    }
+  } else {
+    // ---- dequantisation, then the epilogue ------------------------------------------------------
+    const int r = (warp - 2) * 32 + lane;          // weight row of the tile this thread dequantises
+    const int q = warp & 3;                        // TMEM lane quarter this warp may read
+    uint32_t it = 0, tcount = 0;
+    RowCache rc{}, rc2{};
+    for (int tile = blockIdx.x; tile < tiles && !failed; tile += gridDim.x, tcount++) {
+      const int nt = tile % n_tiles, tt = tile / n_tiles;
+      const int wrow = min(nt * GM_ROWS + r, p.N - 1);
+      const uint8_t* row = pr.w + (size_t)wrow * p.stride;
+      const uint8_t* row2 = DUAL ? pr.w2 + (size_t)wrow * p.stride : nullptr;
+      bool ok = true;
+      for (int ks = 0; ks < ksteps; ks++, it++) {
+        const int s = it % NS;
+        uint4 v[8];
+        dequant64<TYPE>(row, nb, ks, rc, v);       // global loads and arithmetic overlap the wait for the stage
+        if (!mbar_wait(&empty[s], ((it / NS) & 1) ^ 1)) { give_up(); ok = false; break; }
+        uint8_t* a = smem + (size_t)s * STAGE;
+        store_swizzled(a, r, v);
+        if constexpr (DUAL) {
+          dequant64<TYPE>(row2, nb, ks, rc2, v);
+          store_swizzled(a + A_BYTES, r, v);
+        }
+        fence_proxy_async();                       // make the generic-proxy stores visible to the tensor core
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full_a[s]);
+      }
+      if (!ok) break;
+      if (!mbar_wait(&acc_full, tcount & 1)) { give_up(); break; }
+      tc_fence_after();
+      const int orow = nt * GM_ROWS + q * 32 + lane;  // TMEM lane = weight row
+      const int t0 = tt * TN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TN; c0 += 32) {
+        uint32_t acc[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, acc);
+        if constexpr (DUAL) {
+          uint32_t up[32];
+          tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + TN + c0, up);
+#pragma unroll
+          for (int i = 0; i < 32; i++) {
+            const int t = t0 + c0 + i;
+            if (t < pr.count && orow < p.N) {
+              const float g = __uint_as_float(acc[i]), u = __uint_as_float(up[i]);
+              const int64_t yr = p.y_rows != nullptr ? p.y_rows[pr.y_row0 + t] : pr.y_row0 + t;
+              p.y16[yr * p.ldy + orow] = __float2half_rn(g * sigmoid_acc(g) * u);  // shaders/llm_moe_gemv.comp:777-781
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i++) {
+            const int t = t0 + c0 + i;
+            if (t < pr.count && orow < p.N) {
+              const int64_t yr = p.y_rows != nullptr ? p.y_rows[pr.y_row0 + t] : pr.y_row0 + t;
+              float* dst = p.y + yr * p.ldy + orow;
+              if constexpr (EPI == GEMM_RESID) *dst = *dst + __uint_as_float(acc[i]);
+              else *dst = __uint_as_float(acc[i]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty);
+    }
+  }
+  // ---- teardown: every thread arrives; tensor memory is released by the warp that took it -------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TCOLS);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+template <int TYPE, int TN, int EPI>
+int launch_t(const QGemmParams& p, const CUtensorMap& tm, bool pdl, cudaStream_t st) {
+  constexpr bool DUAL = EPI == GEMM_SWIGLU;
+  auto kernel = qgemm_kernel<TYPE, TN, EPI>;
+  const size_t smem = (size_t)gm_stages(TN, DUAL) * gm_stage_bytes(TN, DUAL) + 1024;
+  static bool configured = false;
+  if (!configured) { B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = true; }
+  static int sm_count = 0;
+  if (sm_count == 0) { int dev = 0; B200_CUDA(cudaGetDevice(&dev)); B200_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev)); }
+  const int n_tiles = (p.N + GM_ROWS - 1) / GM_ROWS;
+  int gx, gy;
+  if (p.problems == nullptr) { gx = std::min(n_tiles * ((p.one.count + TN - 1) / TN), sm_count); gy = 1; }
+  else { gx = n_tiles; gy = p.max_problems; }
+  if (gx < 1) gx = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(gx, gy); cfg.blockDim = dim3(GM_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+  B200_CUDA(cudaLaunchKernelEx(&cfg, kernel, tm, p));
+  return OK;
+}
+
+template <int TYPE, int TN>
+int launch_epi(int epi, const QGemmParams& p, const CUtensorMap& tm, bool pdl, cudaStream_t st) {
+  switch (epi) {
+    case GEMM_STORE: return launch_t<TYPE, TN, GEMM_STORE>(p, tm, pdl, st);
+    case GEMM_RESID: return launch_t<TYPE, TN, GEMM_RESID>(p, tm, pdl, st);
+    case GEMM_SWIGLU: return launch_t<TYPE, TN, GEMM_SWIGLU>(p, tm, pdl, st);
+  }
+  set_error("qgemm: unknown epilogue");
+  return EINVAL_;
+}
+template <int TYPE>
+int launch_tn(int epi, int tn, const QGemmParams& p, const CUtensorMap& tm, bool pdl, cudaStream_t st) {
+  if (tn == 64) return launch_epi<TYPE, 64>(epi, p, tm, pdl, st);
+  if (tn == 128) return launch_epi<TYPE, 128>(epi, p, tm, pdl, st);
+  if (tn == 256 && epi != GEMM_SWIGLU) return launch_epi<TYPE, 256>(epi, p, tm, pdl, st);
+  set_error("qgemm: activation tile must be 64, 128 or 256 rows (128 at most for the gated pair)");
+  return EINVAL_;
+}
+
+}  // namespace
+
+int make_x_tensor_map(const __half* x, int64_t rows, int K, int tn, void* out) {
+  static EncodeTiledFn encode = nullptr;
+  if (encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    B200_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (fn == nullptr || qres != cudaDriverEntryPointSuccess) { set_error("qgemm: the driver does not export cuTensorMapEncodeTiled"); return ECUDA; }
+    encode = (EncodeTiledFn)fn;
+  }
+  if (K % GM_KSTEP != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0) { set_error("qgemm: activations must be 16-byte aligned with a row length that is a multiple of 64"); return EINVAL_; }
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * sizeof(__half)};
+  const cuuint32_t box[2] = {(cuuint32_t)GM_KSTEP, (cuuint32_t)tn};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(x), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("qgemm: cuTensorMapEncodeTiled failed with code " + std::to_string((int)r)); return ECUDA; }
+  return OK;
+}
+
+int launch_qgemm(uint32_t type, int epi, int tn, const QGemmParams& p, const void* tmap_host, bool pdl, cudaStream_t st) {
+  if (p.K % 256 != 0 || p.K <= 0) { set_error("qgemm: row length must be a multiple of 256"); return EINVAL_; }
+  CUtensorMap tm;
+  memcpy(&tm, tmap_host, sizeof(tm));
+  switch (type) {
+    case T_Q4_K: return launch_tn<T_Q4_K>(epi, tn, p, tm, pdl, st);
+    case T_Q5_K: return launch_tn<T_Q5_K>(epi, tn, p, tm, pdl, st);
+    case T_Q6_K: return launch_tn<T_Q6_K>(epi, tn, p, tm, pdl, st);
+  }
+  set_error("qgemm: weight type has no tensor-core projection kernel (Q4_K, Q5_K, Q6_K only)");
+  return EINVAL_;
+}
+
+}  // namespace b200

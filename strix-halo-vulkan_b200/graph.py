@@ -261,6 +261,15 @@ def qgemv(typ, w, rows, k, x):
     return y
 
 
+def qgemm(typ, w, rows, k, x, tile_rows=64):
+    """Many-row projection through the tensor-core kernel (weights rounded to fp16 after dequantisation)."""
+    w = np.ascontiguousarray(np.frombuffer(w, dtype=np.uint8))
+    x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, k)
+    y = np.empty((x.shape[0], rows), dtype=np.float32)
+    _lib.check(_lib.load().b200_qgemm(typ, w.ctypes.data, rows, k, x.ctypes.data, x.shape[0], tile_rows, y.ctypes.data))
+    return y
+
+
 def quantize(typ, x):
     x = np.ascontiguousarray(x, dtype=np.float32)
     rows, k = int(np.prod(x.shape[:-1])), x.shape[-1]

@@ -76,6 +76,7 @@ SYMBOLS = {
     "b200_dequantize": (I32, [U32, P, I64, P]),
     "b200_qgemv": (I32, [U32, P, I64, I64, P, I32, P]),
     "b200_qgemv_static": (I32, [U32, P, I64, I64, P, I32, P]),
+    "b200_qgemm": (I32, [U32, P, I64, I64, P, I32, I32, P]),
     "b200_quantize": (I32, [U32, P, I64, I64, P]),
 }
 

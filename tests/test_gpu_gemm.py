@@ -1,0 +1,40 @@
+"""GPU parity of the tensor-core (tcgen05 / TMEM) many-row projection against a CPU restatement of the
+reference's prefill GEMM arithmetic: K-quant weights dequantised in f32, rounded to fp16, multiplied
+with fp16 activations, accumulated in f32 (shaders/llm_gemm.comp MODE 2)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+# accumulation order differs from the CPU sum, inputs are identical fp16 values: 2e-4 of the row scale
+TOL = 2e-4
+
+
+def _want(orc, typ, q, rows, k, x):
+    w16 = orc.dequantize(typ, q, rows * k).reshape(rows, k).astype(np.float16).astype(np.float64)
+    x16 = x.astype(np.float16).astype(np.float64)
+    return (x16 @ w16.T).astype(np.float32)
+
+
+@pytest.mark.parametrize("typ", [12, 13, 14])
+@pytest.mark.parametrize("rows,k,m,tile", [(128, 256, 64, 64), (256, 512, 100, 64), (384, 2048, 300, 128), (200, 768, 33, 64),
+                                           (1024, 2048, 520, 256), (128, 4096, 17, 128)])
+def test_qgemm_matches_fp16_weight_product(pkg, orc, typ, rows, k, m, tile):
+    rng = np.random.default_rng(rows * 7 + k + m)
+    w = (0.02 * rng.standard_normal((rows, k))).astype(np.float32)
+    q = orc.quantize(typ, w)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    got = pkg.qgemm(typ, q, rows, k, x, tile)
+    want = _want(orc, typ, q, rows, k, x)
+    scale = np.abs(want).max()
+    assert np.abs(got - want).max() <= TOL * scale, (np.abs(got - want).max(), scale)
+
+
+def test_qgemm_agrees_with_the_few_row_kernel(pkg, orc):
+    # the two projection kernels differ only by the fp16 rounding of the weights
+    rng = np.random.default_rng(5)
+    rows, k, m = 256, 2048, 8
+    q = orc.quantize(12, (0.02 * rng.standard_normal((rows, k))).astype(np.float32))
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    a, b = pkg.qgemm(12, q, rows, k, x, 64), pkg.qgemv(12, q, rows, k, x)
+    assert np.abs(a - b).max() <= 2e-3 * np.abs(b).max()
