@@ -188,6 +188,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--slots", type=int, default=64, help="also time batched decode over this many slots (0 = skip)")
     ap.add_argument("--prompt", type=int, default=0, help="override the prompt length (profiling runs)")
+    ap.add_argument("--chunk", type=int, default=512, help="rows per prefill pass (the graph's max_tokens)")
     ap.add_argument("--profile-batch", type=int, default=0, help="run N eager batched decode steps over --slots slots between cudaProfilerStart/Stop and exit")
     ap.add_argument("--profile", type=int, default=0, help="run N eager decode steps between cudaProfilerStart/Stop and exit")
     args = ap.parse_args()
@@ -240,7 +241,7 @@ def main():
         print(json.dumps({"profiled_batch_steps": args.profile_batch, "slots": args.slots}))
         return
     n_kv = prompt_len + 2 * (steps + warmup) + 64
-    g = pkg.Graph(model, n_kv=n_kv, max_tokens=64, slots=1, use_cuda_graph=not args.profile)
+    g = pkg.Graph(model, n_kv=n_kv, max_tokens=args.chunk, slots=1, use_cuda_graph=not args.profile)
     rng = np.random.default_rng(1 + rank)
     prompt = rng.integers(0, cfg["vocab"], prompt_len).astype(np.int32)
     t0 = time.time()

@@ -239,7 +239,7 @@ int32_t b200_qgemm(uint32_t type, const void* host_w, int64_t rows, int64_t k, c
   if (s == OK && (cudaMalloc((void**)&err, sizeof(int)) != cudaSuccess || cudaMemset(err, 0, sizeof(int)) != cudaSuccess)) s = ECUDA;
   if (s == OK) {
     QGemmParams p{};
-    p.one.w = t.data; p.one.x_row0 = 0; p.one.count = mrows; p.one.y_row0 = 0; p.max_problems = 1;
+    p.w = t.data; p.one.expert = 0; p.one.x_row0 = 0; p.one.count = mrows; p.one.y_row0 = 0; p.max_problems = 1; p.max_count = mrows;
     p.stride = t.stride; p.K = (int)k; p.N = (int)rows; p.y = y; p.ldy = rows; p.err = err;
     s = launch_qgemm(type, GEMM_STORE, tile_rows, p, tmap, false, 0);
   }

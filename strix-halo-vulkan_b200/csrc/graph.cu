@@ -74,9 +74,19 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   B200_TRY(dalloc(&r_logits, (size_t)MR * c.n_expert)); B200_TRY(dalloc(&r_probs, (size_t)MR * c.n_expert));
   B200_TRY(dalloc(&topk, (size_t)MR * used)); B200_TRY(dalloc(&topk_w, (size_t)MR * slots1)); B200_TRY(dalloc(&margin, (size_t)MR));
   B200_TRY(dalloc(&entries, (size_t)max_entries)); B200_TRY(dalloc(&n_entries, 1)); B200_TRY(dalloc(&cols, (size_t)MR * slots1));
-  B200_TRY(dalloc(&r_ticket, 1)); B200_TRY(dalloc(&tail_ticket, 1)); B200_TRY(dalloc(&err_flag, 1)); B200_TRY(dalloc(&ss_part, (size_t)MR * SS_LD)); B200_TRY(dalloc(&y16, (size_t)MR * vw));
+  B200_TRY(dalloc(&r_ticket, (size_t)2 + MR / 8)); B200_TRY(dalloc(&tail_ticket, 1)); B200_TRY(dalloc(&err_flag, 1)); B200_TRY(dalloc(&ss_part, (size_t)MR * SS_LD)); B200_TRY(dalloc(&y16, (size_t)MR * vw));
   B200_TRY(dalloc(&act16, (size_t)MR * slots1 * c.ffn_expert)); B200_TRY(dalloc(&down, (size_t)MR * slots1 * H));
   B200_TRY(dalloc(&logits, (size_t)MR * c.vocab));
+  B200_TRY(dalloc(&xperm16, (size_t)MR * used * H)); B200_TRY(dalloc(&gprob, (size_t)c.n_expert)); B200_TRY(dalloc(&n_expert_dev, 1));
+  B200_CUDA(cudaMemcpy(n_expert_dev, &c.n_expert, sizeof(int), cudaMemcpyHostToDevice));
+  for (int i = 0; i < 3; i++) {
+    const int tn = 64 << i;
+    B200_TRY(make_x_tensor_map(xperm16, (int64_t)MR * used, H, tn, tm_xperm[i]));
+    B200_TRY(make_x_tensor_map(act16, (int64_t)MR * slots1, c.ffn_expert, tn, tm_act[i]));
+    B200_TRY(make_x_tensor_map(xn16, MR, H, tn, tm_xn[i]));
+    B200_TRY(make_x_tensor_map(y16, MR, vw, tn, tm_y16[i]));
+    B200_TRY(make_x_tensor_map(ctx16, MR, qw, tn, tm_ctx[i]));
+  }
   B200_TRY(dalloc(&ids_dev, (size_t)MR)); B200_TRY(dalloc(&next_ids, (size_t)MR)); B200_TRY(dalloc(&row_slot, (size_t)MR));
   B200_TRY(dalloc(&row_pos, (size_t)MR)); B200_TRY(dalloc(&logit_rows, (size_t)MR)); B200_TRY(dalloc(&seqs, (size_t)MR));
   B200_TRY(dalloc(&hist_len, 1));
@@ -190,6 +200,14 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     t.used = used; t.H = H; t.M = M; t.eps = c.eps;
     return t;
   };
+  // passes of 16 rows and more run their dense projections on the tensor cores
+  const bool use_gemm = !fused && M >= 16;
+  const int tn = M <= 64 ? 64 : M <= 128 ? 128 : 256, ti = tn == 64 ? 0 : tn == 128 ? 1 : 2;
+  auto gemm = [&](const DTensor& w, int K, int N, const unsigned char* tmap, float* y, int64_t ldy, int epi) {
+    QGemmParams g{};
+    g.w = w.data; g.one = GemmProblem{0, 0, M, 0}; g.max_problems = 1; g.max_count = M; g.stride = w.stride; g.K = K; g.N = N; g.y = y; g.ldy = ldy; g.err = err_flag;
+    return launch_qgemm(w.type, epi, tn, g, tmap, pdl(), st);
+  };
   const int l0 = f.draft ? c.n_layer : 0, l1 = f.draft ? c.n_layer + 1 : c.n_layer;
   if (f.draft) {
     // nextn seed, embedding first: h = eh_proj . concat(rms(embd, enorm), rms(h_prev, hnorm))  (llm/mtp.go:352-384)
@@ -215,9 +233,14 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       QGemvParams p = base(L.qkv, H, cw + vw, xn16, H);
       p.w[1] = L.z.data; p.seg_end[0] = cw; p.seg_end[1] = cw + vw; p.nseg = 2;
       p.y = proj; p.ldy = proj_ld;
-      const int pro = normed(p, L.attn_norm, xn16);  // the DeltaNet step reads the fp16 rows for alpha / beta
-      B200_TRY(launch_qgemv(L.qkv.type, pro, EPI_STORE, false, false, p, 0, pdl(), st));
-      B200_TRY(combined(pro));
+      if (use_gemm) {
+        B200_TRY(gemm(L.qkv, H, cw, tm_xn[ti], proj, proj_ld, GEMM_STORE));
+        B200_TRY(gemm(L.z, H, vw, tm_xn[ti], proj + cw, proj_ld, GEMM_STORE));
+      } else {
+        const int pro = normed(p, L.attn_norm, xn16);  // the DeltaNet step reads the fp16 rows for alpha / beta
+        B200_TRY(launch_qgemv(L.qkv.type, pro, EPI_STORE, false, false, p, 0, pdl(), st));
+        B200_TRY(combined(pro));
+      }
       DnStepParams d{};
       d.proj = proj; d.ldp = proj_ld; d.xn = xn16; d.alpha_w = (const float*)L.alpha.data; d.beta_w = (const float*)L.beta.data;
       d.conv_w = (const float*)L.conv1d.data; d.ssm_a = (const float*)L.ssm_a.data; d.dt_bias = (const float*)L.dt_bias.data;
@@ -229,7 +252,8 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       QGemvParams q = base(L.ssm_out, vw, H, y16, vw);
       q.y = hc; q.ldy = H;
       if (fused) { q.ss_out = ss_part; ss_n = qgemv_groups(vw, H); }
-      B200_TRY(launch_qgemv(L.ssm_out.type, PRO_F16, EPI_RESID, false, false, q, 0, pdl(), st));
+      if (use_gemm) B200_TRY(gemm(L.ssm_out, vw, H, tm_y16[ti], hc, H, GEMM_RESID));
+      else B200_TRY(launch_qgemv(L.ssm_out.type, PRO_F16, EPI_RESID, false, false, q, 0, pdl(), st));
     } else {
       const int ai = attn_index[l];
       // fused q|k|v projection; tensors of one type share a launch
@@ -237,7 +261,8 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       const int rows[3] = {2 * qw, kvw, kvw};
       int off = 0;
       bool xn_ready = false;
-      for (int s = 0; s < 3;) {
+      for (int s = 0; s < 3 && use_gemm; s++) { B200_TRY(gemm(*seg[s], H, rows[s], tm_xn[ti], proj + off, proj_ld, GEMM_STORE)); off += rows[s]; }
+      for (int s = 0; s < 3 && !use_gemm;) {
         int e = s + 1;
         while (e < 3 && seg[e]->type == seg[s]->type) e++;
         int n = 0;
@@ -266,7 +291,8 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       QGemvParams q = base(L.o, qw, H, ctx16, qw);
       q.y = hc; q.ldy = H;
       if (fused) { q.ss_out = ss_part; ss_n = qgemv_groups(qw, H); }
-      B200_TRY(launch_qgemv(L.o.type, PRO_F16, EPI_RESID, false, false, q, 0, pdl(), st));
+      if (use_gemm) B200_TRY(gemm(L.o, qw, H, tm_ctx[ti], hc, H, GEMM_RESID));
+      else B200_TRY(launch_qgemv(L.o.type, PRO_F16, EPI_RESID, false, false, q, 0, pdl(), st));
     }
     if (!fused) B200_TRY(launch_row_tail(row_tail(1, L.ffn_norm), pdl(), st));
     if (o.trace) { B200_CUDA(cudaMemcpyAsync(tr_mid + (size_t)l * MR * H, hc, (size_t)M * H * sizeof(float), cudaMemcpyDeviceToDevice, st)); first = true; }
@@ -277,8 +303,33 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     r.M = M; r.H = H; r.nE = c.n_expert; r.used = used; r.logits = r_logits; r.probs = nullptr; r.topk = topk; r.topk_w = topk_w;
     r.tl = tl(); r.margin = margin; r.entries = entries; r.n_entries = n_entries; r.cols = cols; r.ticket = r_ticket; r.max_entries = max_entries;
     r.defer = fused && M == 1;
+    // enough rows per expert: the experts run as grouped tensor-core GEMMs over expert-sorted rows
+    const bool moe_gemm = use_gemm && (int64_t)M * used >= 4 * (int64_t)c.n_expert && L.gate_exps.type == L.gate_sh.type && L.down_exps.type == L.down_sh.type;
+    r.gprob = moe_gemm ? gprob : nullptr;
     B200_TRY(launch_router(r, pdl(), st));
     const int ne = max_entries_for(M);
+    if (moe_gemm) {
+      const int avg = M * used / c.n_expert, tne = avg <= 40 ? 64 : 128, tie = tne == 64 ? 0 : 1;
+      B200_TRY(launch_moe_gather(xn16, cols, M * used, slots1, H, xperm16, pdl(), st));
+      QGemmParams g{};
+      g.problems = reinterpret_cast<const GemmProblem*>(gprob); g.n_problems = n_expert_dev; g.max_problems = c.n_expert; g.max_count = M;
+      g.w = L.gate_exps.data; g.w2 = L.up_exps.data; g.expert_stride = (int64_t)c.ffn_expert * L.gate_exps.stride; g.stride = L.gate_exps.stride;
+      g.K = H; g.N = c.ffn_expert; g.y16 = act16; g.ldy = c.ffn_expert; g.err = err_flag;
+      B200_TRY(launch_qgemm(L.gate_exps.type, GEMM_SWIGLU, tne, g, tm_xperm[tie], pdl(), st));
+      QGemmParams sh{};  // the shared expert: every row, outputs after the routed pairs
+      sh.one = GemmProblem{0, 0, M, M * used}; sh.max_problems = 1; sh.max_count = M; sh.w = L.gate_sh.data; sh.w2 = L.up_sh.data; sh.stride = L.gate_sh.stride;
+      sh.K = H; sh.N = c.ffn_expert; sh.y16 = act16; sh.ldy = c.ffn_expert; sh.err = err_flag;
+      B200_TRY(launch_qgemm(L.gate_sh.type, GEMM_SWIGLU, std::min(tn, 128), sh, tm_xn[std::min(ti, 1)], pdl(), st));
+      QGemmParams d{};   // down projections: sorted rows in, pair rows out (cols maps sorted row -> pair)
+      d.problems = g.problems; d.n_problems = n_expert_dev; d.max_problems = c.n_expert; d.max_count = M;
+      d.w = L.down_exps.data; d.expert_stride = (int64_t)H * L.down_exps.stride; d.stride = L.down_exps.stride;
+      d.K = c.ffn_expert; d.N = H; d.y = down; d.ldy = H; d.y_rows = cols; d.err = err_flag;
+      B200_TRY(launch_qgemm(L.down_exps.type, GEMM_STORE, tne, d, tm_act[tie], pdl(), st));
+      QGemmParams ds{};
+      ds.one = GemmProblem{0, M * used, M, M * used}; ds.max_problems = 1; ds.max_count = M; ds.w = L.down_sh.data; ds.stride = L.down_sh.stride;
+      ds.K = c.ffn_expert; ds.N = H; ds.y = down; ds.ldy = H; ds.y_rows = cols; ds.err = err_flag;
+      B200_TRY(launch_qgemm(L.down_sh.type, GEMM_STORE, tn, ds, tm_act[ti], pdl(), st));
+    } else {
     QGemvParams p = base(L.gate_exps, H, c.ffn_expert, xn16, H);
     p.w2[0] = L.up_exps.data; p.ws = L.gate_sh.data; p.ws2 = L.up_sh.data; p.expert_stride = (int64_t)c.ffn_expert * L.gate_exps.stride;
     p.entries = entries; p.n_entries = n_entries; p.cols = cols; p.x_div = slots1;
@@ -290,6 +341,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     q.entries = entries; q.n_entries = n_entries; q.cols = cols; q.x_div = 1;
     q.y = down; q.ldy = H;
     B200_TRY(launch_qgemv(L.down_exps.type, PRO_F16, EPI_STORE, false, true, q, ne, pdl(), st));
+    }
     if (fused) pending = true;
     else {
       const DTensor& next_norm = f.draft ? L.head_norm : (l + 1 < c.n_layer ? m->layers[l + 1].attn_norm : m->output_norm);
@@ -317,9 +369,13 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     QGemvParams p = base(m->output, H, N, xn16, H);
     p.M = n_logit_rows; p.xcols = std::min(n_logit_rows, QG_MAXCOLS); p.row_ids = logit_rows;
     p.y = logits; p.ldy = N;
-    const int pro = head_reads_xn ? (int)PRO_F16 : normed(p, nrm, nullptr);
-    B200_TRY(launch_qgemv(m->output.type, pro, EPI_STORE, false, false, p, 0, pdl(), st));
-    B200_TRY(combined(pro));
+    if (use_gemm && n_logit_rows == M) {
+      B200_TRY(gemm(m->output, H, N, tm_xn[ti], logits, N, GEMM_STORE));
+    } else {
+      const int pro = head_reads_xn ? (int)PRO_F16 : normed(p, nrm, nullptr);
+      B200_TRY(launch_qgemv(m->output.type, pro, EPI_STORE, false, false, p, 0, pdl(), st));
+      B200_TRY(combined(pro));
+    }
     if (f.greedy) {
       B200_TRY(launch_argmax(logits, n_logit_rows, N, next_ids, pdl(), st));
       B200_TRY(launch_advance(ids_dev, next_ids, row_pos, seqs, M, history, hist_len, st)); launches++;

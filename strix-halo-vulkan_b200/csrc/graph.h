@@ -31,6 +31,11 @@ struct Graph {
   // reads one and writes the other. h is the one the last pass finished in.
   float *hbuf[2] = {nullptr, nullptr}, *h = nullptr, *proj = nullptr, *attn_partial = nullptr, *down = nullptr, *logits = nullptr, *e_buf = nullptr, *hs_buf = nullptr;
   __half *xn16 = nullptr, *q16 = nullptr, *ctx16 = nullptr, *act16 = nullptr, *y16 = nullptr, *xcat16 = nullptr;
+  // TMA tensor maps of the fp16 activation buffers for the many-row GEMM, per tile height 64 / 128 / 256
+  alignas(64) unsigned char tm_xn[3][128], tm_y16[3][128], tm_ctx[3][128], tm_xperm[3][128], tm_act[3][128];
+  __half* xperm16 = nullptr;   // [rows * used][H]: activation rows in expert-sorted order
+  int4* gprob = nullptr;       // [n_expert] GEMM problem per expert
+  int* n_expert_dev = nullptr;
   float* ss_part = nullptr;   // [rows][SS_LD] partial sums of squares of the residual rows
   float *r_logits = nullptr, *r_probs = nullptr, *topk_w = nullptr, *margin = nullptr;
   int32_t *topk = nullptr, *ids_dev = nullptr, *next_ids = nullptr, *history = nullptr;

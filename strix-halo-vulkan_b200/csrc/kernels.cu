@@ -313,21 +313,31 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   tl_mark(p.tl, 4);
   if (p.defer) return;  // the expert kernel selects the experts itself
   // the last CTA to finish routes every token and builds the expert work list
+  // Two levels of tickets: the last CTA of a row group (blockIdx.y) routes that group's eight rows, one
+  // per warp; the last group to finish builds the work list of the whole pass.
   __threadfence();
   __syncthreads();
-  if (tid == 0) is_last = (atomicAdd(p.ticket, 1) == (int)(gridDim.x * gridDim.y) - 1);
+  if (tid == 0) is_last = (atomicAdd(p.ticket + 1 + blockIdx.y, 1) == (int)gridDim.x - 1);
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (tid == 0) p.ticket[1 + blockIdx.y] = 0;
+  tl_mark(p.tl, 5, true);
+  const int nE = p.nE, used = p.used;
+  {
+    const int n = blockIdx.y * 8 + warp;
+    if (n < M) {
+      if (nE <= 512) route_token<16>(p, n, lane);
+      else route_token<32>(p, n, lane);
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) is_last = (atomicAdd(p.ticket, 1) == (int)gridDim.y - 1);
   __syncthreads();
   if (!is_last) return;
   __threadfence();
   if (tid == 0) *p.ticket = 0;
-  tl_mark(p.tl, 5, true);
-  const int nE = p.nE, used = p.used;
-  for (int n = warp; n < M; n += 8) {
-    if (nE <= 512) route_token<16>(p, n, lane);
-    else route_token<32>(p, n, lane);
-  }
-  __threadfence_block();
-  __syncthreads();
   // work list: pair id = n*(used+1) + slot; slot == used is the shared expert
   if (M == 1) {
     if (tid < used) { p.entries[tid] = make_int4(p.topk[tid], tid, 1, 0); p.cols[tid] = tid; }
@@ -337,7 +347,7 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   }
   for (int i = tid; i <= nE; i += 256) counts[i] = 0;
   __syncthreads();
-  for (int i = tid; i < M * used; i += 256) atomicAdd(&counts[p.topk[i]], 1);
+  for (int i = tid; i < M * used; i += 256) atomicAdd(&counts[__ldcg(p.topk + i)], 1);
   __syncthreads();
   if (warp == 0) {  // exclusive scans of the pair counts and of the entry counts (8 columns per entry)
     const int per = (nE + 31) / 32;
@@ -362,6 +372,8 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
     for (int c = 0, i = 0; c < counts[e]; c += 8, i++)
       if (eoff[e] + i < p.max_entries) p.entries[eoff[e] + i] = make_int4(e, offs[e] + c, min(8, counts[e] - c), 0);
   }
+  // one GEMM problem per expert for the tensor-core expert kernels: rows [offs, offs + count) of the expert-sorted order
+  if (p.gprob != nullptr) for (int e = tid; e < nE; e += 256) p.gprob[e] = make_int4(e, offs[e], counts[e], offs[e]);
   const int nsh = (M + 7) >> 3;
   for (int i = tid; i < nsh; i += 256)
     if (eoff[nE] + i < p.max_entries) p.entries[eoff[nE] + i] = make_int4(-1, offs[nE] + 8 * i, min(8, M - 8 * i), 0);
@@ -370,7 +382,7 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   for (int i = tid; i <= nE; i += 256) counts[i] = 0;
   __syncthreads();
   for (int i = tid; i < M * used; i += 256) {
-    const int e = p.topk[i], n = i / used, k = i - n * used;
+    const int e = __ldcg(p.topk + i), n = i / used, k = i - n * used;
     const int pos = atomicAdd(&counts[e], 1);
     p.cols[offs[e] + pos] = n * (used + 1) + k;
   }
@@ -389,6 +401,20 @@ int launch_router(const RouterParams& p, bool pdl, cudaStream_t st) {
     if (smem > 200 * 1024) { set_error("router: rows too long for shared memory"); return ECAPACITY; }
   }
   return launch_k(router_kernel, dim3(grid, p.h != nullptr ? 1 : (p.M + 7) / 8), dim3(256), smem, pdl, st, p);
+}
+
+// Expert-sorted copy of the activation rows for the tensor-core expert kernels (the reference's
+// shaders/llm_moe_perm.comp): sorted row i holds the row of token cols[i] / (used + 1).
+__global__ void __launch_bounds__(256) moe_gather_kernel(const __half* xn, const int* cols, int slots1, int H, __half* xperm) {
+  pdl_wait();
+  pdl_launch();
+  const int i = blockIdx.x;
+  const uint4* src = reinterpret_cast<const uint4*>(xn + (size_t)(cols[i] / slots1) * H);
+  uint4* dst = reinterpret_cast<uint4*>(xperm + (size_t)i * H);
+  for (int k = threadIdx.x; k < H / 8; k += 256) dst[k] = __ldcg(src + k);
+}
+int launch_moe_gather(const __half* xn, const int* cols, int pairs, int slots1, int H, __half* xperm, bool pdl, cudaStream_t st) {
+  return launch_k(moe_gather_kernel, dim3(pairs), dim3(256), 0, pdl, st, xn, cols, slots1, H, xperm);
 }
 
 // Stand-alone forms of the row tails, one CTA per row, for passes of more than QG_TAIL_ROWS rows.

@@ -15,6 +15,7 @@ constexpr int GM_THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, warp
 constexpr int GM_ROWS = 128;      // weight rows per tile = UMMA M = TMEM lanes
 constexpr int GM_KSTEP = 64;      // fp16 elements per K step = one 128-byte swizzle row
 constexpr int A_BYTES = GM_ROWS * 128;
+constexpr int GM_SPROB = 512;     // problems cached in shared memory
 
 __host__ __device__ constexpr int gm_stages(int tn, bool dual) { return tn >= 256 ? (dual ? 3 : 4) : tn >= 128 ? (dual ? 4 : 6) : (dual ? 5 : 8); }
 __host__ __device__ constexpr int gm_stage_bytes(int tn, bool dual) { return A_BYTES * (dual ? 2 : 1) + tn * 128; }
@@ -76,10 +77,14 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 // ---- dequantisation of 64 consecutive elements of one weight row ------------------------------
 // Each returns the values as eight 16-byte chunks of fp16 (chunk c = elements 8c..8c+7 of the K step).
 // Arithmetic follows gguf/dequant.go (unfused multiply, subtract), then one rounding to fp16.
-struct RowCache {  // what a thread keeps of its row's current super-block between K steps
-  uint4 hdr;       // Q4_K / Q5_K: d, dmin, 12 scale bytes. Q6_K: 16 int8 scales
-  uint4 qh0, qh1;  // Q5_K: the 32 fifth-bit bytes
-  float d;         // Q6_K
+// What a thread holds of its row: one whole super-block (four K steps), fetched one super-block ahead
+// of its use so that a block's bytes are requested together (whole DRAM lines, many loads in flight).
+template <int TYPE>
+struct RawBlock {
+  // Q4_K: header, 8 x 16 nibble bytes. Q5_K: header, 2 x 16 fifth-bit bytes, 8 x 16 nibble bytes.
+  // Q6_K (row planes): 8 x 16 ql bytes, 4 x 16 qh bytes, 16 int8 scales; d apart.
+  uint4 q[TYPE == T_Q4_K ? 9 : TYPE == T_Q5_K ? 11 : 13];
+  uint32_t d;
 };
 
 __device__ __forceinline__ void k4_scale_min_dev(int j, const uint4& hdr, int& sc, int& m) {  // gguf/dequant.go:238-243
@@ -90,25 +95,62 @@ __device__ __forceinline__ void k4_scale_min_dev(int j, const uint4& hdr, int& s
 }
 
 template <int TYPE>
-__device__ __forceinline__ void dequant64(const uint8_t* row, int nb, int ks, RowCache& rc, uint4 (&out)[8]) {
-  const int blk = ks >> 2, j = ks & 3;
+__device__ __forceinline__ void load_raw(const uint8_t* row, int nb, int blk, RawBlock<TYPE>& r) {
   if constexpr (TYPE == T_Q4_K || TYPE == T_Q5_K) {
-    constexpr int BS = TYPE == T_Q4_K ? 144 : 176, QOFF = TYPE == T_Q4_K ? 16 : 48;
-    const uint8_t* b = row + (size_t)blk * BS;
-    if (j == 0) {
-      rc.hdr = ldg128(b);
-      if constexpr (TYPE == T_Q5_K) { rc.qh0 = ldg128(b + 16); rc.qh1 = ldg128(b + 32); }
-    }
-    const uint4 q0 = ldg128(b + QOFF + 32 * j), q1 = ldg128(b + QOFF + 32 * j + 16);
-    const float d = h2f_lo(rc.hdr.x), dmin = h2f_hi(rc.hdr.x);
+    constexpr int NQ = TYPE == T_Q4_K ? 9 : 11;
+    const uint8_t* b = row + (size_t)blk * (16 * NQ);
+#pragma unroll
+    for (int i = 0; i < NQ; i++) r.q[i] = ldg128(b + 16 * i);
+  } else {  // Q6_K row planes: ql[nb][128] | qh[nb][64] | scales[nb][16] | d[nb]
+    const uint8_t* ql = row + (size_t)blk * 128;
+    const uint8_t* qh = row + (size_t)nb * 128 + (size_t)blk * 64;
+#pragma unroll
+    for (int i = 0; i < 8; i++) r.q[i] = ldg128(ql + 16 * i);
+#pragma unroll
+    for (int i = 0; i < 4; i++) r.q[8 + i] = ldg128(qh + 16 * i);
+    r.q[12] = ldg128(row + (size_t)nb * 192 + (size_t)blk * 16);
+    r.d = __ldg(reinterpret_cast<const unsigned short*>(row + (size_t)nb * 208 + (size_t)blk * 2));
+  }
+}
+
+// 64 weights -> eight 16-byte chunks of fp16. The quants become exact fp16 integers through the
+// 0x6400 exponent trick (1024 + q, minus 1024). The f32 factors d*sc and dmin*m are carried as fp16
+// hi + lo pairs, so that the value q*(d*sc) - dmin*m is formed as fma(q, hi, -mhi) + fma(q, lo, -mlo):
+// the first term is rounded once, the second is a correction far below its ulp. Against rounding the f32
+// value once (the reference's prefill GEMM) this differs by at most one fp16 ulp, independently per weight
+// (a single fp16 factor would put the same rounding error on all 32 weights of a sub-block).
+__device__ __forceinline__ uint32_t h2_bcast(float v) {
+  __half2 h = __float2half2_rn(v);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void h2_split(float v, uint32_t& hi, uint32_t& lo) {
+  const __half h = __float2half_rn(v);
+  hi = h2_bcast(__half2float(h));
+  lo = h2_bcast(v - __half2float(h));
+}
+// bytes (b0, b1) and (b2, b3) of a word of 0..63 values -> half2 pairs of the exact integers
+__device__ __forceinline__ void bytes_to_h2(uint32_t w, uint32_t off, uint32_t& p01, uint32_t& p23) {
+  p01 = hadd2_u(__byte_perm(w, 0x64646464u, 0x4140), off);
+  p23 = hadd2_u(__byte_perm(w, 0x64646464u, 0x4342), off);
+}
+
+template <int TYPE>
+__device__ __forceinline__ void dequant64(const RawBlock<TYPE>& r, int j, uint4 (&out)[8]) {
+  const uint32_t m1024 = h2_bcast(-1024.f);
+  if constexpr (TYPE == T_Q4_K || TYPE == T_Q5_K) {
+    constexpr int QS = TYPE == T_Q4_K ? 1 : 3;  // first nibble quad
+    const float d = h2f_lo(r.q[0].x), dmin = h2f_hi(r.q[0].x);
     int sc0, m0, sc1, m1;
-    k4_scale_min_dev(2 * j, rc.hdr, sc0, m0);
-    k4_scale_min_dev(2 * j + 1, rc.hdr, sc1, m1);
-    const float d0 = __fmul_rn(d, (float)sc0), mm0 = __fmul_rn(dmin, (float)m0), d1 = __fmul_rn(d, (float)sc1), mm1 = __fmul_rn(dmin, (float)m1);
-    const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    k4_scale_min_dev(2 * j, r.q[0], sc0, m0);
+    k4_scale_min_dev(2 * j + 1, r.q[0], sc1, m1);
+    uint32_t d0, d0l, n0, n0l, d1, d1l, n1, n1l;
+    h2_split(__fmul_rn(d, (float)sc0), d0, d0l); h2_split(-__fmul_rn(dmin, (float)m0), n0, n0l);
+    h2_split(__fmul_rn(d, (float)sc1), d1, d1l); h2_split(-__fmul_rn(dmin, (float)m1), n1, n1l);
+    const uint4 qa = r.q[QS + 2 * j], qb = r.q[QS + 2 * j + 1];
+    const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
     uint32_t hb[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if constexpr (TYPE == T_Q5_K) {
-      hb[0] = rc.qh0.x; hb[1] = rc.qh0.y; hb[2] = rc.qh0.z; hb[3] = rc.qh0.w; hb[4] = rc.qh1.x; hb[5] = rc.qh1.y; hb[6] = rc.qh1.z; hb[7] = rc.qh1.w;
+      hb[0] = r.q[1].x; hb[1] = r.q[1].y; hb[2] = r.q[1].z; hb[3] = r.q[1].w; hb[4] = r.q[2].x; hb[5] = r.q[2].y; hb[6] = r.q[2].z; hb[7] = r.q[2].w;
     }
     // low nibbles: sub-block 2j (chunks 0..3), high nibbles: sub-block 2j+1 (chunks 4..7); word w holds bytes 4w..4w+3
 #pragma unroll
@@ -116,56 +158,47 @@ __device__ __forceinline__ void dequant64(const uint8_t* row, int nb, int ks, Ro
       uint32_t lo[4], hi[4];
 #pragma unroll
       for (int h = 0; h < 2; h++) {
-        const uint32_t w = qw[2 * c + h], hw = hb[2 * c + h];
-        float vl[4], vh[4];
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-          int ql = (w >> (8 * e)) & 0xF, qh = (w >> (8 * e + 4)) & 0xF;
-          if constexpr (TYPE == T_Q5_K) {
-            const uint32_t hbyte = hw >> (8 * e);
-            ql += ((hbyte >> (2 * j)) & 1) << 4;
-            qh += ((hbyte >> (2 * j + 1)) & 1) << 4;
-          }
-          vl[e] = __fsub_rn(__fmul_rn(d0, (float)ql), mm0);
-          vh[e] = __fsub_rn(__fmul_rn(d1, (float)qh), mm1);
+        const uint32_t w = qw[2 * c + h];
+        uint32_t wl = w & 0x0F0F0F0Fu, wh = (w >> 4) & 0x0F0F0F0Fu;
+        if constexpr (TYPE == T_Q5_K) {  // bit 2j / 2j+1 of the fifth-bit byte -> bit 4 of the value
+          const uint32_t hw = hb[2 * c + h];
+          wl |= ((hw >> (2 * j)) & 0x01010101u) << 4;
+          wh |= ((hw >> (2 * j + 1)) & 0x01010101u) << 4;
         }
-        lo[2 * h] = pack_h2(vl[0], vl[1]); lo[2 * h + 1] = pack_h2(vl[2], vl[3]);
-        hi[2 * h] = pack_h2(vh[0], vh[1]); hi[2 * h + 1] = pack_h2(vh[2], vh[3]);
+        uint32_t a, b;
+        bytes_to_h2(wl, m1024, a, b);
+        lo[2 * h] = hadd2_u(hfma2_u(a, d0, n0), hfma2_u(a, d0l, n0l)); lo[2 * h + 1] = hadd2_u(hfma2_u(b, d0, n0), hfma2_u(b, d0l, n0l));
+        bytes_to_h2(wh, m1024, a, b);
+        hi[2 * h] = hadd2_u(hfma2_u(a, d1, n1), hfma2_u(a, d1l, n1l)); hi[2 * h + 1] = hadd2_u(hfma2_u(b, d1, n1), hfma2_u(b, d1l, n1l));
       }
       out[c] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
       out[4 + c] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
     }
-  } else {  // Q6_K row planes: ql[nb][128] | qh[nb][64] | scales[nb][16] | d[nb]
+  } else {
     const int hf = j >> 1, up = j & 1;  // quarters 2*up, 2*up+1 of half hf
-    const uint8_t* ql = row + (size_t)blk * 128 + 64 * hf;
-    const uint8_t* qh = row + (size_t)nb * 128 + (size_t)blk * 64 + 32 * hf;
-    if (j == 0) {
-      rc.hdr = ldg128(row + (size_t)nb * 192 + (size_t)blk * 16);
-      rc.d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(row + (size_t)nb * 208 + (size_t)blk * 2)));
-    }
-    const uint4 la0 = ldg128(ql), la1 = ldg128(ql + 16), lb0 = ldg128(ql + 32), lb1 = ldg128(ql + 48), h0 = ldg128(qh), h1 = ldg128(qh + 16);
-    const uint32_t lw[2][8] = {{la0.x, la0.y, la0.z, la0.w, la1.x, la1.y, la1.z, la1.w}, {lb0.x, lb0.y, lb0.z, lb0.w, lb1.x, lb1.y, lb1.z, lb1.w}};
-    const uint32_t hw[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
-    const uint32_t scw[4] = {rc.hdr.x, rc.hdr.y, rc.hdr.z, rc.hdr.w};
+    const float dd = __half2float(__ushort_as_half((unsigned short)r.d));
+    const uint4 l0 = r.q[4 * hf], l1 = r.q[4 * hf + 1], l2 = r.q[4 * hf + 2], l3 = r.q[4 * hf + 3], g0 = r.q[8 + 2 * hf], g1 = r.q[9 + 2 * hf];
+    const uint32_t lw[2][8] = {{l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w}, {l2.x, l2.y, l2.z, l2.w, l3.x, l3.y, l3.z, l3.w}};
+    const uint32_t hw[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+    const uint32_t scw[4] = {r.q[12].x, r.q[12].y, r.q[12].z, r.q[12].w};
+    const uint32_t m1056 = h2_bcast(-1056.f);  // the 1024 of the exponent trick and the format's centre 32
 #pragma unroll
     for (int qq = 0; qq < 2; qq++) {      // quarter 2*up + qq: elements l = 0..31, chunks 4*qq .. 4*qq+3
       const int quarter = 2 * up + qq;
 #pragma unroll
       for (int c = 0; c < 4; c++) {       // l = 8c .. 8c+7: words 2c, 2c+1; scale index 8*hf + l/16 + 2*quarter
         const int si = 8 * hf + (c >> 1) + 2 * quarter;
-        const float ds = __fmul_rn(rc.d, (float)(int)(int8_t)((scw[si >> 2] >> (8 * (si & 3))) & 0xFF));
+        uint32_t ds, dsl;
+        h2_split(__fmul_rn(dd, (float)(int)(int8_t)((scw[si >> 2] >> (8 * (si & 3))) & 0xFF)), ds, dsl);
         uint32_t o[4];
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-          const uint32_t w = lw[qq][2 * c + h], hb = hw[2 * c + h];
-          float v[4];
-#pragma unroll
-          for (int e = 0; e < 4; e++) {
-            const int nib = up ? (w >> (8 * e + 4)) & 0xF : (w >> (8 * e)) & 0xF;
-            const int q = (nib | ((int)((hb >> (8 * e + 2 * quarter)) & 3) << 4)) - 32;
-            v[e] = __fmul_rn(ds, (float)q);
-          }
-          o[2 * h] = pack_h2(v[0], v[1]); o[2 * h + 1] = pack_h2(v[2], v[3]);
+          const uint32_t w = lw[qq][2 * c + h];
+          const uint32_t nib = up ? (w >> 4) & 0x0F0F0F0Fu : w & 0x0F0F0F0Fu;
+          const uint32_t v = nib | (((hw[2 * c + h] >> (2 * quarter)) & 0x03030303u) << 4);
+          uint32_t a, b;
+          bytes_to_h2(v, m1056, a, b);
+          o[2 * h] = hfma2_u(a, ds, hmul2_u(a, dsl)); o[2 * h + 1] = hfma2_u(b, ds, hmul2_u(b, dsl));
         }
         out[4 * qq + c] = make_uint4(o[0], o[1], o[2], o[3]);
       }
@@ -189,6 +222,7 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
   __shared__ __align__(8) uint64_t full_a[NS], full_b[NS], empty[NS], acc_full, acc_empty;
   __shared__ uint32_t tmem_base_sm;
   __shared__ volatile int failed;
+  __shared__ GemmProblem sprob[GM_SPROB];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   if (tid == 0) {
@@ -205,20 +239,32 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
   pdl_wait();
   pdl_launch();
 
-  const int n_prob = p.n_problems != nullptr ? *p.n_problems : 1;
-  const bool have = (int)blockIdx.y < n_prob;
-  GemmProblem pr = p.one;
-  if (have && p.problems != nullptr) pr = p.problems[blockIdx.y];
+  const int n_prob = p.n_problems != nullptr ? min(*p.n_problems, p.max_problems) : 1;
   const int K = p.K, nb = K / 256, ksteps = K / GM_KSTEP;
-  const int n_tiles = (p.N + GM_ROWS - 1) / GM_ROWS, t_tiles = have ? (pr.count + TN - 1) / TN : 0, tiles = n_tiles * t_tiles;
+  // work items: (activation-row tile, problem, weight-row tile), the weight tile fastest; items past a
+  // problem's rows are skipped, and since every problem has a first activation tile the live items of a
+  // grouped launch sit together at the front, spread evenly over the CTAs
+  const int n_tiles = (p.N + GM_ROWS - 1) / GM_ROWS, t_max = (p.max_count + TN - 1) / TN, per_tt = n_prob * n_tiles, total = t_max * per_tt;
+  auto item = [&](int idx, GemmProblem& pr, int& nt, int& tt) {
+    tt = idx / per_tt;
+    const int rem = idx - tt * per_tt, e = rem / n_tiles;
+    nt = rem - e * n_tiles;
+    pr = p.problems == nullptr ? p.one : e < GM_SPROB ? sprob[e] : p.problems[e];
+    return tt * TN < pr.count;
+  };
+  if (p.problems != nullptr) {  // the problem list is scanned by three roles: keep it in shared memory
+    for (int e = tid; e < n_prob && e < GM_SPROB; e += GM_THREADS) sprob[e] = p.problems[e];
+    __syncthreads();
+  }
   auto give_up = [&]() { if (p.err != nullptr) atomicExch(p.err, 1); failed = 1; };
 
   if (warp == 0) {
     // ---- activation tiles by TMA -----------------------------------------------------------
     if (lane == 0) {
       uint32_t it = 0;
-      for (int tile = blockIdx.x; tile < tiles && !failed; tile += gridDim.x) {
-        const int tt = tile / n_tiles;
+      for (int idx = blockIdx.x; idx < total && !failed; idx += gridDim.x) {
+        GemmProblem pr; int nt, tt;
+        if (!item(idx, pr, nt, tt)) continue;
         for (int ks = 0; ks < ksteps; ks++, it++) {
           const int s = it % NS;
           if (!mbar_wait(&empty[s], ((it / NS) & 1) ^ 1)) { give_up(); break; }
@@ -232,7 +278,9 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
     if (lane == 0) {
       uint32_t it = 0, tcount = 0;
       constexpr uint32_t idesc = idesc_f16(TN);
-      for (int tile = blockIdx.x; tile < tiles && !failed; tile += gridDim.x, tcount++) {
+      for (int idx = blockIdx.x; idx < total && !failed; idx += gridDim.x) {
+        GemmProblem pr; int nt, tt;
+        if (!item(idx, pr, nt, tt)) continue;
         if (!mbar_wait(&acc_empty, (tcount & 1) ^ 1)) { give_up(); break; }  // the epilogue has drained the accumulator
         tc_fence_after();
         bool ok = true;
@@ -252,6 +300,7 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
         }
         if (!ok) break;
         tc_commit(&acc_full);
+        tcount++;
       }
     }
   } else {
@@ -259,27 +308,43 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
     const int r = (warp - 2) * 32 + lane;          // weight row of the tile this thread dequantises
     const int q = warp & 3;                        // TMEM lane quarter this warp may read
     uint32_t it = 0, tcount = 0;
-    RowCache rc{}, rc2{};
-    for (int tile = blockIdx.x; tile < tiles && !failed; tile += gridDim.x, tcount++) {
-      const int nt = tile % n_tiles, tt = tile / n_tiles;
+    for (int idx = blockIdx.x; idx < total && !failed; idx += gridDim.x) {
+      GemmProblem pr; int nt, tt;
+      if (!item(idx, pr, nt, tt)) continue;
       const int wrow = min(nt * GM_ROWS + r, p.N - 1);
-      const uint8_t* row = pr.w + (size_t)wrow * p.stride;
-      const uint8_t* row2 = DUAL ? pr.w2 + (size_t)wrow * p.stride : nullptr;
+      const uint8_t* row = p.w + (size_t)pr.expert * p.expert_stride + (size_t)wrow * p.stride;
+      const uint8_t* row2 = DUAL ? p.w2 + (size_t)pr.expert * p.expert_stride + (size_t)wrow * p.stride : nullptr;
       bool ok = true;
-      for (int ks = 0; ks < ksteps; ks++, it++) {
+      // one K step: dequantise, wait for the stage to be free, store the swizzled tile, signal the MMA warp
+      auto step = [&](const RawBlock<TYPE>& ra, const RawBlock<TYPE>& rb, int j) {
         const int s = it % NS;
         uint4 v[8];
-        dequant64<TYPE>(row, nb, ks, rc, v);       // global loads and arithmetic overlap the wait for the stage
-        if (!mbar_wait(&empty[s], ((it / NS) & 1) ^ 1)) { give_up(); ok = false; break; }
+        dequant64<TYPE>(ra, j, v);
+        if (!mbar_wait(&empty[s], ((it / NS) & 1) ^ 1)) { give_up(); ok = false; return; }
         uint8_t* a = smem + (size_t)s * STAGE;
         store_swizzled(a, r, v);
         if constexpr (DUAL) {
-          dequant64<TYPE>(row2, nb, ks, rc2, v);
+          dequant64<TYPE>(rb, j, v);
           store_swizzled(a + A_BYTES, r, v);
         }
         fence_proxy_async();                       // make the generic-proxy stores visible to the tensor core
         __syncwarp();
         if (lane == 0) mbar_arrive(&full_a[s]);
+        it++;
+      };
+      auto fetch = [&](RawBlock<TYPE>& ra, RawBlock<TYPE>& rb, int blk) {
+        if (blk < nb) { load_raw<TYPE>(row, nb, blk, ra); if constexpr (DUAL) load_raw<TYPE>(row2, nb, blk, rb); }
+      };
+      auto block = [&](const RawBlock<TYPE>& ra, const RawBlock<TYPE>& rb) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) if (ok) step(ra, rb, j);
+      };
+      RawBlock<TYPE> a0, a1, b0, b1;
+      fetch(a0, b0, 0);
+      for (int blk = 0; blk < nb && ok; blk += 2) {
+        fetch(a1, b1, blk + 1);
+        block(a0, b0);
+        if (blk + 1 < nb && ok) { fetch(a0, b0, blk + 2); block(a1, b1); }
       }
       if (!ok) break;
       if (!mbar_wait(&acc_full, tcount & 1)) { give_up(); break; }
@@ -318,6 +383,7 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty);
+      tcount++;
     }
   }
   // ---- teardown: every thread arrives; tensor memory is released by the warp that took it -------
@@ -339,10 +405,8 @@ int launch_t(const QGemmParams& p, const CUtensorMap& tm, bool pdl, cudaStream_t
   static int sm_count = 0;
   if (sm_count == 0) { int dev = 0; B200_CUDA(cudaGetDevice(&dev)); B200_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev)); }
   const int n_tiles = (p.N + GM_ROWS - 1) / GM_ROWS;
-  int gx, gy;
-  if (p.problems == nullptr) { gx = std::min(n_tiles * ((p.one.count + TN - 1) / TN), sm_count); gy = 1; }
-  else { gx = n_tiles; gy = p.max_problems; }
-  if (gx < 1) gx = 1;
+  const int64_t total = (int64_t)(p.problems != nullptr ? p.max_problems : 1) * n_tiles * ((p.max_count + TN - 1) / TN);
+  const int gx = (int)std::max<int64_t>(1, std::min<int64_t>(total, sm_count)), gy = 1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(gx, gy); cfg.blockDim = dim3(GM_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute attr[1];

@@ -25,19 +25,21 @@ enum { GEMM_STORE = 0, GEMM_RESID = 1, GEMM_SWIGLU = 2 };
 
 // One GEMM problem of a launch (a dense projection has one; the expert kernels one per expert).
 struct GemmProblem {
-  const uint8_t* w;    // weight rows [N][K] in device layout
-  const uint8_t* w2;   // GEMM_SWIGLU: the `up` tensor (w is `gate`)
+  int expert;          // weights start at w + expert * expert_stride (0 for a dense projection)
   int x_row0;          // first activation row (into the tensor map's row axis)
   int count;           // activation rows
   int y_row0;          // first output row
-  int pad;
 };
 
 struct QGemmParams {
   const GemmProblem* problems;  // device array; null: the single problem `one`
   const int* n_problems;        // device count (grouped), null: 1
   GemmProblem one;
-  int max_problems;             // upper bound of *n_problems (grid sizing)
+  int max_problems;             // upper bound of *n_problems
+  int max_count;                // upper bound of a problem's activation rows
+  const uint8_t* w;             // weight rows [N][K] in device layout
+  const uint8_t* w2;            // GEMM_SWIGLU: the `up` tensor (w is `gate`)
+  int64_t expert_stride;        // bytes between consecutive experts
   int64_t stride;               // bytes per weight row
   int K, N;
   float* y; int64_t ldy;        // STORE / RESID: f32 [.][ldy]

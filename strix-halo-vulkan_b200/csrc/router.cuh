@@ -18,7 +18,8 @@ struct RouterParams {
   float* topk_w;       // [M][used+1] (last = sigmoid(shared gate))
   float* margin;       // [M] optional: (p_k - p_{k+1}) / p_k
   int4* entries; int* n_entries; int* cols;   // expert work list for the grouped kernels
-  int* ticket;
+  int* ticket;         // [1 + ceil(M / 8)]: all rows, then one per group of eight rows
+  int4* gprob;         // optional [nE]: {expert, first sorted row, rows, first sorted row} per expert (GemmProblem)
   int max_entries;
   int defer;           // 1: stop after the logits; the expert kernel that follows selects the experts itself
   Timeline tl;

@@ -13,6 +13,11 @@ import numpy as np
 # device-like modes differ from each other by more than the CUDA path differs from either).
 REL_TOL = 1e-2
 NEAR_TIE = 1e-3
+# Passes of 16 rows and more run on the tensor cores with the reference's prefill arithmetic: every
+# dequantised weight is rounded to fp16 (shaders/llm_gemm.comp MODE 2). That moves hidden states by about
+# 1e-3 of their scale against the exact-weight oracle, and with them the router's probabilities, so a
+# top-k boundary is only safe from flipping when it is wider than a few times that.
+NEAR_TIE_MANY_ROWS = 5e-3
 
 
 def compare(got, want):

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 import modelgen
-from parity import NEAR_TIE, assert_close, logit_gap
+from parity import NEAR_TIE, NEAR_TIE_MANY_ROWS, assert_close, logit_gap
 
 pytestmark = pytest.mark.gpu
 
@@ -40,14 +40,25 @@ def test_full_shape_prefill_and_greedy_decode_match_oracle(pkg, a3b4):
     logits, _ = g.forward(ids)
     tr = g.trace(len(ids))
     want, ot = seq.extend(ids, trace=("hidden", "topk", "margin"))
+    # A top-k boundary closer than the near-tie margin (the wider one: 24 rows take the tensor-core path)
+    # is a documented near-tie: the two sides may route differently there,
+    # and everything that depends on that row (the same and later tokens, from that layer on) then differs.
+    # Rows no near-tie can have reached keep the strict bound, the others a loose one.
+    T = len(ids)
+    first_tie = np.full(cfg["n_layer"], T)          # first token with a near-tie at or before each layer
     for l in range(cfg["n_layer"]):
-        assert_close(tr["hidden"][l], ot["hidden"][:, l], f"layer {l} residual")
-        for t in range(len(ids)):
-            if ot["margin"][t, l] >= NEAR_TIE:
+        ties = np.nonzero(ot["margin"][:, l] < NEAR_TIE_MANY_ROWS)[0]
+        here = int(ties[0]) if len(ties) else T
+        first_tie[l] = min(here, int(first_tie[l - 1]) if l else T)
+        clean = int(first_tie[l])
+        if clean > 0:
+            assert_close(tr["hidden"][l][:clean], ot["hidden"][:clean, l], f"layer {l} residual, rows before any near-tie")
+        if clean < T:
+            assert_close(tr["hidden"][l][clean:], ot["hidden"][clean:, l], f"layer {l} residual, rows after a near-tie", tol=1e-1)
+        for t in range(T):
+            if ot["margin"][t, l] >= NEAR_TIE_MANY_ROWS and t < clean:
                 assert set(tr["topk"][l, t].tolist()) == set(ot["topk"][t, l].tolist()), (l, t)
-    # A top-k boundary closer than 1e-3 is a documented near-tie: if the two sides route differently there,
-    # their states differ from then on, so the strict bound applies until the first such event.
-    tainted = bool((ot["margin"] < NEAR_TIE).any())
+    tainted = bool((ot["margin"] < NEAR_TIE_MANY_ROWS).any())
     for step in range(8):
         assert_close(logits, want, f"logits at step {step} (near-tie seen: {tainted})", tol=1e-1 if tainted else 1e-2)
         tg, to = int(np.argmax(logits)), int(np.argmax(want))

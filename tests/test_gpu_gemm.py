@@ -6,8 +6,9 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 
-# accumulation order differs from the CPU sum, inputs are identical fp16 values: 2e-4 of the row scale
-TOL = 2e-4
+# The kernel forms each weight in fp16 arithmetic (within about one fp16 ulp of the f32 value rounded
+# once) and sums in a different order: 5e-4 of the output scale.
+TOL = 5e-4
 
 
 def _want(orc, typ, q, rows, k, x):

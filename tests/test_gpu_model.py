@@ -94,14 +94,15 @@ def test_chunk_split_is_the_whole_prompt(pkg, tiny):
     o = 0
     for n in (16, 9, 2, 3, 1):
         part, _ = g.extend(ids[o:o + n]); o += n
-    # passes of at most 8 rows normalise while staging, larger ones in a row kernel: same arithmetic, another
-    # summation order, so the match is to tolerance (pinned schedules are bit-equal: see decode_rows below)
-    assert_close(part, whole, "chunked prefill", tol=2e-3)
+    # passes of at most 8 rows normalise while staging, larger ones in a row kernel, and passes of 16 rows
+    # and more run on the tensor cores with every dequantised weight rounded to fp16 (the reference's
+    # prefill arithmetic): the schedules agree to a tolerance that covers that rounding
+    assert_close(part, whole, "chunked prefill", tol=5e-3)
     assert int(np.argmax(part)) == int(np.argmax(whole))
     # and a chunk larger than max_tokens is cut by the library itself
     g2 = pkg.Graph(tiny["model"], n_kv=64, max_tokens=8, use_cuda_graph=False)
     cut, _ = g2.forward(ids)
-    assert_close(cut, whole, "library-cut prefill", tol=2e-3)
+    assert_close(cut, whole, "library-cut prefill", tol=5e-3)
 
 
 def test_decode_rows_is_each_slot(pkg, tiny):
