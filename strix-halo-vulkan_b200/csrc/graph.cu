@@ -77,6 +77,7 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   B200_TRY(dalloc(&r_ticket, (size_t)2 + MR / 8)); B200_TRY(dalloc(&tail_ticket, 1)); B200_TRY(dalloc(&err_flag, 1)); B200_TRY(dalloc(&ss_part, (size_t)MR * SS_LD)); B200_TRY(dalloc(&y16, (size_t)MR * vw));
   B200_TRY(dalloc(&act16, (size_t)MR * slots1 * c.ffn_expert)); B200_TRY(dalloc(&down, (size_t)MR * slots1 * H));
   B200_TRY(dalloc(&logits, (size_t)MR * c.vocab));
+  { B200_TRY(dalloc(&dn_pre, (size_t)c.dn_heads_v * 4 * MR * 292)); B200_TRY(dalloc(&dn_oraw, (size_t)MR * vw)); }
   B200_TRY(dalloc(&xperm16, (size_t)MR * used * H)); B200_TRY(dalloc(&gprob, (size_t)c.n_expert)); B200_TRY(dalloc(&n_expert_dev, 1));
   B200_CUDA(cudaMemcpy(n_expert_dev, &c.n_expert, sizeof(int), cudaMemcpyHostToDevice));
   for (int i = 0; i < 3; i++) {
@@ -203,7 +204,11 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
   // passes of 16 rows and more run their dense projections on the tensor cores
   const bool use_gemm = !fused && M >= 16;
   const int tn = M <= 64 ? 64 : M <= 128 ? 128 : 256, ti = tn == 64 ? 0 : tn == 128 ? 1 : 2;
-  auto gemm = [&](const DTensor& w, int K, int N, const unsigned char* tmap, float* y, int64_t ldy, int epi) {
+  // tile height per projection: as tall as the pass allows, shrunk while the launch would leave SMs idle
+  auto gemm = [&](const DTensor& w, int K, int N, const unsigned char (*tmaps)[128], float* y, int64_t ldy, int epi) {
+    int tn = M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    while (tn > 64 && ((N + 127) / 128) * ((M + tn - 1) / tn) < 120) tn /= 2;
+    const unsigned char* tmap = tmaps[tn == 64 ? 0 : tn == 128 ? 1 : 2];
     QGemmParams g{};
     g.w = w.data; g.one = GemmProblem{0, 0, M, 0}; g.max_problems = 1; g.max_count = M; g.stride = w.stride; g.K = K; g.N = N; g.y = y; g.ldy = ldy; g.err = err_flag;
     return launch_qgemm(w.type, epi, tn, g, tmap, pdl(), st);
@@ -234,8 +239,8 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       p.w[1] = L.z.data; p.seg_end[0] = cw; p.seg_end[1] = cw + vw; p.nseg = 2;
       p.y = proj; p.ldy = proj_ld;
       if (use_gemm) {
-        B200_TRY(gemm(L.qkv, H, cw, tm_xn[ti], proj, proj_ld, GEMM_STORE));
-        B200_TRY(gemm(L.z, H, vw, tm_xn[ti], proj + cw, proj_ld, GEMM_STORE));
+        B200_TRY(gemm(L.qkv, H, cw, tm_xn, proj, proj_ld, GEMM_STORE));
+        B200_TRY(gemm(L.z, H, vw, tm_xn, proj + cw, proj_ld, GEMM_STORE));
       } else {
         const int pro = normed(p, L.attn_norm, xn16);  // the DeltaNet step reads the fp16 rows for alpha / beta
         B200_TRY(launch_qgemv(L.qkv.type, pro, EPI_STORE, false, false, p, 0, pdl(), st));
@@ -248,11 +253,16 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       d.seqs = seqs; d.n_seq = n_seq; d.norm_w = (const float*)L.ssm_norm.data; d.y16 = y16;
       d.mid = f.spec ? dn_mid[di] : nullptr; d.mid_stride = state_slot_stride; d.mid_seq_stride = mid_seq_stride;
       d.H = H; d.Hk = c.dn_heads_k; d.Hv = c.dn_heads_v; d.D = D; d.conv = c.dn_conv; d.eps = c.eps; d.tl = tl();
-      B200_TRY(launch_dn_step(d, pdl(), st));
+      if (!fused && !f.spec && M > n_seq) {  // some sequence is long: state-independent part in parallel, then the scan
+        d.pre = dn_pre; d.pre_rows = MR; d.o_raw = dn_oraw;
+        B200_TRY(launch_dn_scan(d, M, pass_max_n, pdl(), st)); launches += 2;
+      } else {
+        B200_TRY(launch_dn_step(d, pdl(), st));
+      }
       QGemvParams q = base(L.ssm_out, vw, H, y16, vw);
       q.y = hc; q.ldy = H;
       if (fused) { q.ss_out = ss_part; ss_n = qgemv_groups(vw, H); }
-      if (use_gemm) B200_TRY(gemm(L.ssm_out, vw, H, tm_y16[ti], hc, H, GEMM_RESID));
+      if (use_gemm) B200_TRY(gemm(L.ssm_out, vw, H, tm_y16, hc, H, GEMM_RESID));
       else B200_TRY(launch_qgemv(L.ssm_out.type, PRO_F16, EPI_RESID, false, false, q, 0, pdl(), st));
     } else {
       const int ai = attn_index[l];
@@ -261,7 +271,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       const int rows[3] = {2 * qw, kvw, kvw};
       int off = 0;
       bool xn_ready = false;
-      for (int s = 0; s < 3 && use_gemm; s++) { B200_TRY(gemm(*seg[s], H, rows[s], tm_xn[ti], proj + off, proj_ld, GEMM_STORE)); off += rows[s]; }
+      for (int s = 0; s < 3 && use_gemm; s++) { B200_TRY(gemm(*seg[s], H, rows[s], tm_xn, proj + off, proj_ld, GEMM_STORE)); off += rows[s]; }
       for (int s = 0; s < 3 && !use_gemm;) {
         int e = s + 1;
         while (e < 3 && seg[e]->type == seg[s]->type) e++;
@@ -291,7 +301,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       QGemvParams q = base(L.o, qw, H, ctx16, qw);
       q.y = hc; q.ldy = H;
       if (fused) { q.ss_out = ss_part; ss_n = qgemv_groups(qw, H); }
-      if (use_gemm) B200_TRY(gemm(L.o, qw, H, tm_ctx[ti], hc, H, GEMM_RESID));
+      if (use_gemm) B200_TRY(gemm(L.o, qw, H, tm_ctx, hc, H, GEMM_RESID));
       else B200_TRY(launch_qgemv(L.o.type, PRO_F16, EPI_RESID, false, false, q, 0, pdl(), st));
     }
     if (!fused) B200_TRY(launch_row_tail(row_tail(1, L.ffn_norm), pdl(), st));
@@ -319,7 +329,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       QGemmParams sh{};  // the shared expert: every row, outputs after the routed pairs
       sh.one = GemmProblem{0, 0, M, M * used}; sh.max_problems = 1; sh.max_count = M; sh.w = L.gate_sh.data; sh.w2 = L.up_sh.data; sh.stride = L.gate_sh.stride;
       sh.K = H; sh.N = c.ffn_expert; sh.y16 = act16; sh.ldy = c.ffn_expert; sh.err = err_flag;
-      B200_TRY(launch_qgemm(L.gate_sh.type, GEMM_SWIGLU, std::min(tn, 128), sh, tm_xn[std::min(ti, 1)], pdl(), st));
+      B200_TRY(launch_qgemm(L.gate_sh.type, GEMM_SWIGLU, 64, sh, tm_xn[0], pdl(), st));  // few weight tiles: short activation tiles fill more SMs
       QGemmParams d{};   // down projections: sorted rows in, pair rows out (cols maps sorted row -> pair)
       d.problems = g.problems; d.n_problems = n_expert_dev; d.max_problems = c.n_expert; d.max_count = M;
       d.w = L.down_exps.data; d.expert_stride = (int64_t)H * L.down_exps.stride; d.stride = L.down_exps.stride;
@@ -328,7 +338,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       QGemmParams ds{};
       ds.one = GemmProblem{0, M * used, M, M * used}; ds.max_problems = 1; ds.max_count = M; ds.w = L.down_sh.data; ds.stride = L.down_sh.stride;
       ds.K = c.ffn_expert; ds.N = H; ds.y = down; ds.ldy = H; ds.y_rows = cols; ds.err = err_flag;
-      B200_TRY(launch_qgemm(L.down_sh.type, GEMM_STORE, tn, ds, tm_act[ti], pdl(), st));
+      B200_TRY(launch_qgemm(L.down_sh.type, GEMM_STORE, 64, ds, tm_act[0], pdl(), st));
     } else {
     QGemvParams p = base(L.gate_exps, H, c.ffn_expert, xn16, H);
     p.w2[0] = L.up_exps.data; p.ws = L.gate_sh.data; p.ws2 = L.up_sh.data; p.expert_stride = (int64_t)c.ffn_expert * L.gate_exps.stride;
@@ -370,7 +380,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     p.M = n_logit_rows; p.xcols = std::min(n_logit_rows, QG_MAXCOLS); p.row_ids = logit_rows;
     p.y = logits; p.ldy = N;
     if (use_gemm && n_logit_rows == M) {
-      B200_TRY(gemm(m->output, H, N, tm_xn[ti], logits, N, GEMM_STORE));
+      B200_TRY(gemm(m->output, H, N, tm_xn, logits, N, GEMM_STORE));
     } else {
       const int pro = head_reads_xn ? (int)PRO_F16 : normed(p, nrm, nullptr);
       B200_TRY(launch_qgemv(m->output.type, pro, EPI_STORE, false, false, p, 0, pdl(), st));
@@ -412,6 +422,8 @@ int Graph::run_rows(const int32_t* ids, const int* slots, const int* pos, int M,
   }
   B200_CUDA(cudaSetDevice(m->device));
   fill_stage(stage, MR, ids, slots, pos, M, sq, lrows);
+  pass_max_n = 1;
+  for (const SeqDesc& s : sq) pass_max_n = std::max(pass_max_n, s.n);
   const int n_lr = (int)lrows.size(), n_seq = (int)sq.size();
   const int NV = f.draft && draft_vocab > 0 ? draft_vocab : c.vocab;
   bool single = !f.spec && !f.draft && !o.trace && o.use_cuda_graph && n_seq == M && n_lr == M && !f.want_residual;

@@ -621,6 +621,187 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(128) dn_step_kernel(
   tl_mark(p.tl, 4);
 }
 
+// -----------------------------------------------------------------------------------------
+// The same layer for sequences of many tokens (prefill), as three kernels: everything that does not
+// depend on the recurrent state (alpha / beta, conv + SiLU, L2 norms, gates) is computed for all tokens
+// in parallel and packed per (head, row block) and token; the scan then walks the tokens with no
+// block-wide synchronisation at all, each warp owning eight state rows; the gated norm runs per token
+// afterwards. Thread mappings and summation orders are those of dn_step_kernel, so the two forms give
+// the same bits.
+// -----------------------------------------------------------------------------------------
+constexpr int DN_PACK = 292;   // floats per (CTA id, token): q 128 | k 128 | v 32 | decay | beta | pad 2
+constexpr int DN_PRE_TOKENS = 16;
+
+__global__ void __launch_bounds__(128) dn_pre_kernel(DnStepParams p) {
+  const int D = 128, RB = 4;
+  const int h = blockIdx.x / RB, rb = blockIdx.x % RB, hk = h % p.Hk;
+  const SeqDesc sq = p.seqs[blockIdx.y];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qk = p.Hk * D, H = p.H;
+  __shared__ float red[16];
+  const int i0 = blockIdx.z * DN_PRE_TOKENS, i1 = min(sq.n, i0 + DN_PRE_TOKENS);
+  if (i0 >= sq.n) return;
+  const int ch_q = hk * D + tid, ch_k = qk + hk * D + tid, ch_v = 2 * qk + h * D + rb * 32 + (tid & 31);
+  const float4 cwq = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch_q * 4);
+  const float4 cwk = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch_k * 4);
+  const float4 cwv = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch_v * 4);
+  const float a_h = p.ssm_a[h], dtb = p.dt_bias[h];
+  float* ring = p.ring + (size_t)sq.slot * p.ring_slot_stride + (size_t)blockIdx.x * (DN_RING * DN_RING_W);
+  pdl_wait();
+  pdl_launch();
+  // conv input of token index ii (may be negative: before this pass): the projection row, else the ring
+  auto input = [&](int ii, int ch, int ring_off) {
+    if (ii >= 0) return p.proj[(size_t)(sq.row0 + ii) * p.ldp + ch];
+    const int pos = sq.pos0 + ii;
+    return pos >= 0 ? ring[(size_t)(pos & (DN_RING - 1)) * DN_RING_W + ring_off] : 0.f;
+  };
+  float hq[3], hkk[3], hv[3];
+#pragma unroll
+  for (int j = 0; j < 3; j++) {
+    hq[j] = input(i0 - 3 + j, ch_q, tid);
+    hkk[j] = input(i0 - 3 + j, ch_k, 128 + tid);
+    hv[j] = input(i0 - 3 + j, ch_v, 256 + (tid & 31));
+  }
+  for (int i = i0; i < i1; i++) {
+    const int row = sq.row0 + i;
+    const float* pr = p.proj + (size_t)row * p.ldp;
+    const __half* xn = p.xn + (size_t)row * H;
+    float pa = 0.f, pb = 0.f;
+    for (int k = tid * 4; k < H; k += 512) {
+      const float4 wa = *reinterpret_cast<const float4*>(p.alpha_w + (size_t)h * H + k), wb = *reinterpret_cast<const float4*>(p.beta_w + (size_t)h * H + k);
+      const __half2 x01 = *reinterpret_cast<const __half2*>(xn + k), x23 = *reinterpret_cast<const __half2*>(xn + k + 2);
+      const float2 f01 = __half22float2(x01), f23 = __half22float2(x23);
+      pa += wa.x * f01.x + wa.y * f01.y + wa.z * f23.x + wa.w * f23.y;
+      pb += wb.x * f01.x + wb.y * f01.y + wb.z * f23.x + wb.w * f23.y;
+    }
+    const float cq = pr[ch_q], ck = pr[ch_k], cv = pr[ch_v];
+    const float q = silu_acc(hq[0] * cwq.x + hq[1] * cwq.y + hq[2] * cwq.z + cq * cwq.w);
+    const float k = silu_acc(hkk[0] * cwk.x + hkk[1] * cwk.y + hkk[2] * cwk.z + ck * cwk.w);
+    const float v = silu_acc(hv[0] * cwv.x + hv[1] * cwv.y + hv[2] * cwv.z + cv * cwv.w);
+    hq[0] = hq[1]; hq[1] = hq[2]; hq[2] = cq;
+    hkk[0] = hkk[1]; hkk[1] = hkk[2]; hkk[2] = ck;
+    hv[0] = hv[1]; hv[1] = hv[2]; hv[2] = cv;
+    const float sq2 = warp_sum(q * q), sk2 = warp_sum(k * k);
+    pa = warp_sum(pa); pb = warp_sum(pb);
+    __syncthreads();
+    if (lane == 0) { red[warp] = sq2; red[4 + warp] = sk2; red[8 + warp] = pa; red[12 + warp] = pb; }
+    __syncthreads();
+    const float qn = 1.0f / sqrtf(red[0] + red[1] + red[2] + red[3] + p.eps);
+    const float kn = 1.0f / sqrtf(red[4] + red[5] + red[6] + red[7] + p.eps);
+    const float alpha = red[8] + red[9] + red[10] + red[11], betar = red[12] + red[13] + red[14] + red[15];
+    float* out = p.pre + ((size_t)blockIdx.x * p.pre_rows + row) * DN_PACK;
+    out[tid] = q * qn;
+    out[128 + tid] = k * kn;
+    if (tid < 32) out[256 + tid] = v;
+    if (tid == 0) { out[288] = expf(softplus_ref(alpha + dtb) * a_h); out[289] = sigmoid_acc(betar); }
+  }
+}
+
+__global__ void __launch_bounds__(128) dn_scan_kernel(DnStepParams p) {
+  const int D = 128, RB = 4;
+  const int h = blockIdx.x / RB, rb = blockIdx.x % RB;
+  const SeqDesc sq = p.seqs[blockIdx.y];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  float* S = p.state + (size_t)sq.slot * p.state_slot_stride + (size_t)h * D * D;
+  const int j0 = rb * 32 + warp * 8;
+  float4 s[8];
+#pragma unroll
+  for (int r = 0; r < 8; r++) s[r] = *reinterpret_cast<const float4*>(S + (size_t)(j0 + r) * D + lane * 4);
+  const float oscale = 1.0f / sqrtf((float)D);
+  pdl_wait();
+  pdl_launch();
+  const float* pp = p.pre + ((size_t)blockIdx.x * p.pre_rows + sq.row0) * DN_PACK;
+  auto fetch = [&](int i, float4& q4, float4& k4, float& vv, float2& gb) {
+    const float* t = pp + (size_t)i * DN_PACK;
+    q4 = __ldcg(reinterpret_cast<const float4*>(t + lane * 4));
+    k4 = __ldcg(reinterpret_cast<const float4*>(t + 128 + lane * 4));
+    vv = __ldcg(t + 256 + warp * 8 + (lane & 7));
+    gb = __ldcg(reinterpret_cast<const float2*>(t + 288));
+  };
+  float4 q4, k4, nq4, nk4; float vv, nvv; float2 gb, ngb;
+  fetch(0, q4, k4, vv, gb);
+  for (int i = 0; i < sq.n; i++) {
+    if (i + 1 < sq.n) fetch(i + 1, nq4, nk4, nvv, ngb);
+    const float g = gb.x, beta = gb.y;
+    float kv[8], oo[8];
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+      s[r].x *= g; s[r].y *= g; s[r].z *= g; s[r].w *= g;
+      kv[r] = s[r].x * k4.x + s[r].y * k4.y + s[r].z * k4.z + s[r].w * k4.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int r = 0; r < 8; r++) kv[r] += __shfl_xor_sync(0xffffffffu, kv[r], o);
+    }
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+      const float dj = (__shfl_sync(0xffffffffu, vv, r) - kv[r]) * beta;
+      s[r].x += dj * k4.x; s[r].y += dj * k4.y; s[r].z += dj * k4.z; s[r].w += dj * k4.w;
+      oo[r] = s[r].x * q4.x + s[r].y * q4.y + s[r].z * q4.z + s[r].w * q4.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int r = 0; r < 8; r++) oo[r] += __shfl_xor_sync(0xffffffffu, oo[r], o);
+    }
+    float ov = oo[0] * oscale;
+#pragma unroll
+    for (int r = 0; r < 8; r++) ov = lane == r ? oo[r] * oscale : ov;
+    if (lane < 8) p.o_raw[(size_t)(sq.row0 + i) * (p.Hv * D) + h * D + j0 + lane] = ov;
+    q4 = nq4; k4 = nk4; vv = nvv; gb = ngb;
+  }
+#pragma unroll
+  for (int r = 0; r < 8; r++) *reinterpret_cast<float4*>(S + (size_t)(j0 + r) * D + lane * 4) = s[r];
+  // the ring keeps the last positions' conv inputs (written here, after every read of the old ring)
+  {
+    const int hk = h % p.Hk, qk = p.Hk * D;
+    const int ch_q = hk * D + tid, ch_k = qk + hk * D + tid, ch_v = 2 * qk + h * D + rb * 32 + (tid & 31);
+    float* ring = p.ring + (size_t)sq.slot * p.ring_slot_stride + (size_t)blockIdx.x * (DN_RING * DN_RING_W);
+    for (int i = max(0, sq.n - DN_RING); i < sq.n; i++) {
+      const float* pr = p.proj + (size_t)(sq.row0 + i) * p.ldp;
+      float* rw = ring + (size_t)((sq.pos0 + i) & (DN_RING - 1)) * DN_RING_W;
+      rw[tid] = pr[ch_q]; rw[128 + tid] = pr[ch_k];
+      if (tid < 32) rw[256 + tid] = pr[ch_v];
+    }
+  }
+}
+
+// gated RMSNorm of one token's head: sums of squares grouped as the step kernel groups them (eight rows
+// per warp in order, four warps per row block, four row blocks)
+__global__ void __launch_bounds__(128) dn_post_kernel(DnStepParams p, int M) {
+  const int D = 128, row = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
+  __shared__ float sq[128], wss[16], tot_sm;
+  pdl_wait();
+  pdl_launch();
+  const float ov = p.o_raw[(size_t)row * (p.Hv * D) + h * D + j];
+  sq[j] = ov * ov;
+  __syncthreads();
+  if (j < 16) {
+    float ss = 0.f;
+    for (int r = 0; r < 8; r++) ss += sq[j * 8 + r];
+    wss[j] = ss;
+  }
+  __syncthreads();
+  if (j == 0) {
+    float tot = 0.f;
+    for (int rb = 0; rb < 4; rb++) tot += wss[4 * rb] + wss[4 * rb + 1] + wss[4 * rb + 2] + wss[4 * rb + 3];
+    tot_sm = tot;
+  }
+  __syncthreads();
+  const float nsc = 1.0f / sqrtf(tot_sm / (float)D + p.eps);
+  const float zz = p.proj[(size_t)row * p.ldp + 2 * p.Hk * D + p.Hv * D + h * D + j];
+  p.y16[(size_t)row * (p.Hv * D) + h * D + j] = __float2half_rn(ov * nsc * p.norm_w[j] * sigmoid_acc(zz));
+}
+
+int launch_dn_scan(const DnStepParams& p, int M, int max_n, bool pdl, cudaStream_t st) {
+  if (p.D != 128 || p.conv != 4) { set_error("dn_scan: head dim must be 128 and conv kernel 4"); return EINVAL_; }
+  if (p.mid != nullptr || p.pre == nullptr || p.o_raw == nullptr) { set_error("dn_scan: not available for speculative passes"); return EINVAL_; }
+  B200_TRY(launch_k(dn_pre_kernel, dim3(p.Hv * 4, p.n_seq, (max_n + DN_PRE_TOKENS - 1) / DN_PRE_TOKENS), dim3(128), 0, pdl, st, p));
+  B200_TRY(launch_k(dn_scan_kernel, dim3(p.Hv * 4, p.n_seq), dim3(128), 0, true, st, p));
+  return launch_k(dn_post_kernel, dim3(M, p.Hv), dim3(128), 0, true, st, p, M);
+}
+
 int launch_dn_step(const DnStepParams& p, bool pdl, cudaStream_t st) {
   if (p.D != 128 || p.conv != 4) { set_error("dn_step: head dim must be 128 and conv kernel 4"); return EINVAL_; }
   return launch_k(dn_step_kernel, dim3(p.Hv * 4, p.n_seq), dim3(128), 0, pdl, st, p);

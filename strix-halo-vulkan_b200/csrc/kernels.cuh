@@ -57,6 +57,10 @@ struct DnStepParams {
   __half* y16;                               // [M][Hv*D] gated-norm output: fp16(rms(o) * norm_w * sigmoid(z))
   float* mid;                                // speculation: [n_seq][rows][Hv][D][D] state after each token; the slot's own state is then left untouched
   int64_t mid_stride, mid_seq_stride;        // floats between consecutive rows / sequences of mid
+  // many-token form (launch_dn_scan): packed per (CTA id, row) inputs of the scan, and its raw outputs
+  float* pre;                                // [Hv*4][pre_rows][292]
+  int64_t pre_rows;
+  float* o_raw;                              // [M][Hv*D]
   int H, Hk, Hv, D, conv;
   float eps;
   Timeline tl;
@@ -64,6 +68,8 @@ struct DnStepParams {
 constexpr int DN_RING = 8;      // positions kept per ring
 constexpr int DN_RING_W = 288;  // conv inputs per CTA: q 128 | k 128 | v 32
 int launch_dn_step(const DnStepParams& p, bool pdl, cudaStream_t st);
+// three launches: state-independent part for all tokens, the scan, the gated norm (max_n = longest sequence)
+int launch_dn_scan(const DnStepParams& p, int M, int max_n, bool pdl, cudaStream_t st);
 
 struct AttnParams {
   const float* proj; int64_t ldp;            // [M][ldp]: per head (q | gate) x Hq, then k, then v
