@@ -205,9 +205,15 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
   const bool use_gemm = !fused && M >= 16;
   const int tn = M <= 64 ? 64 : M <= 128 ? 128 : 256, ti = tn == 64 ? 0 : tn == 128 ? 1 : 2;
   // tile height per projection: as tall as the pass allows, shrunk while the launch would leave SMs idle
-  auto gemm = [&](const DTensor& w, int K, int N, const unsigned char (*tmaps)[128], float* y, int64_t ldy, int epi) {
+  // a projection whose tiles would cover under a third of the SMs stays on the column-tiled kernel
+  auto gemm = [&](const DTensor& w, int K, int N, const __half* x, const unsigned char (*tmaps)[128], float* y, int64_t ldy, int epi) {
     int tn = M <= 64 ? 64 : M <= 128 ? 128 : 256;
     while (tn > 64 && ((N + 127) / 128) * ((M + tn - 1) / tn) < 120) tn /= 2;
+    if (((N + 127) / 128) * ((M + tn - 1) / tn) < 48) {
+      QGemvParams q = base(w, K, N, x, K);
+      q.y = y; q.ldy = ldy;
+      return launch_qgemv(w.type, PRO_F16, epi == GEMM_RESID ? EPI_RESID : EPI_STORE, false, false, q, 0, pdl(), st);
+    }
     const unsigned char* tmap = tmaps[tn == 64 ? 0 : tn == 128 ? 1 : 2];
     QGemmParams g{};
     g.w = w.data; g.one = GemmProblem{0, 0, M, 0}; g.max_problems = 1; g.max_count = M; g.stride = w.stride; g.K = K; g.N = N; g.y = y; g.ldy = ldy; g.err = err_flag;
@@ -239,8 +245,8 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       p.w[1] = L.z.data; p.seg_end[0] = cw; p.seg_end[1] = cw + vw; p.nseg = 2;
       p.y = proj; p.ldy = proj_ld;
       if (use_gemm) {
-        B200_TRY(gemm(L.qkv, H, cw, tm_xn, proj, proj_ld, GEMM_STORE));
-        B200_TRY(gemm(L.z, H, vw, tm_xn, proj + cw, proj_ld, GEMM_STORE));
+        B200_TRY(gemm(L.qkv, H, cw, xn16, tm_xn, proj, proj_ld, GEMM_STORE));
+        B200_TRY(gemm(L.z, H, vw, xn16, tm_xn, proj + cw, proj_ld, GEMM_STORE));
       } else {
         const int pro = normed(p, L.attn_norm, xn16);  // the DeltaNet step reads the fp16 rows for alpha / beta
         B200_TRY(launch_qgemv(L.qkv.type, pro, EPI_STORE, false, false, p, 0, pdl(), st));
@@ -262,7 +268,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       QGemvParams q = base(L.ssm_out, vw, H, y16, vw);
       q.y = hc; q.ldy = H;
       if (fused) { q.ss_out = ss_part; ss_n = qgemv_groups(vw, H); }
-      if (use_gemm) B200_TRY(gemm(L.ssm_out, vw, H, tm_y16, hc, H, GEMM_RESID));
+      if (use_gemm) B200_TRY(gemm(L.ssm_out, vw, H, y16, tm_y16, hc, H, GEMM_RESID));
       else B200_TRY(launch_qgemv(L.ssm_out.type, PRO_F16, EPI_RESID, false, false, q, 0, pdl(), st));
     } else {
       const int ai = attn_index[l];
@@ -271,7 +277,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       const int rows[3] = {2 * qw, kvw, kvw};
       int off = 0;
       bool xn_ready = false;
-      for (int s = 0; s < 3 && use_gemm; s++) { B200_TRY(gemm(*seg[s], H, rows[s], tm_xn, proj + off, proj_ld, GEMM_STORE)); off += rows[s]; }
+      for (int s = 0; s < 3 && use_gemm; s++) { B200_TRY(gemm(*seg[s], H, rows[s], xn16, tm_xn, proj + off, proj_ld, GEMM_STORE)); off += rows[s]; }
       for (int s = 0; s < 3 && !use_gemm;) {
         int e = s + 1;
         while (e < 3 && seg[e]->type == seg[s]->type) e++;
@@ -301,7 +307,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       QGemvParams q = base(L.o, qw, H, ctx16, qw);
       q.y = hc; q.ldy = H;
       if (fused) { q.ss_out = ss_part; ss_n = qgemv_groups(qw, H); }
-      if (use_gemm) B200_TRY(gemm(L.o, qw, H, tm_ctx, hc, H, GEMM_RESID));
+      if (use_gemm) B200_TRY(gemm(L.o, qw, H, ctx16, tm_ctx, hc, H, GEMM_RESID));
       else B200_TRY(launch_qgemv(L.o.type, PRO_F16, EPI_RESID, false, false, q, 0, pdl(), st));
     }
     if (!fused) B200_TRY(launch_row_tail(row_tail(1, L.ffn_norm), pdl(), st));
@@ -313,8 +319,9 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     r.M = M; r.H = H; r.nE = c.n_expert; r.used = used; r.logits = r_logits; r.probs = nullptr; r.topk = topk; r.topk_w = topk_w;
     r.tl = tl(); r.margin = margin; r.entries = entries; r.n_entries = n_entries; r.cols = cols; r.ticket = r_ticket; r.max_entries = max_entries;
     r.defer = fused && M == 1;
-    // enough rows per expert: the experts run as grouped tensor-core GEMMs over expert-sorted rows
-    const bool moe_gemm = use_gemm && (int64_t)M * used >= 4 * (int64_t)c.n_expert && L.gate_exps.type == L.gate_sh.type && L.down_exps.type == L.down_sh.type;
+    // 32 rows per expert on average and more: the experts run as grouped tensor-core GEMMs over expert-sorted
+    // rows (below that the column-tiled kernel, which streams each expert's weights in whole tiles, is faster)
+    const bool moe_gemm = use_gemm && (int64_t)M * used >= 32 * (int64_t)c.n_expert && L.gate_exps.type == L.gate_sh.type && L.down_exps.type == L.down_sh.type;
     r.gprob = moe_gemm ? gprob : nullptr;
     B200_TRY(launch_router(r, pdl(), st));
     const int ne = max_entries_for(M);
@@ -380,7 +387,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     p.M = n_logit_rows; p.xcols = std::min(n_logit_rows, QG_MAXCOLS); p.row_ids = logit_rows;
     p.y = logits; p.ldy = N;
     if (use_gemm && n_logit_rows == M) {
-      B200_TRY(gemm(m->output, H, N, tm_xn, logits, N, GEMM_STORE));
+      B200_TRY(gemm(m->output, H, N, xn16, tm_xn, logits, N, GEMM_STORE));
     } else {
       const int pro = head_reads_xn ? (int)PRO_F16 : normed(p, nrm, nullptr);
       B200_TRY(launch_qgemv(m->output.type, pro, EPI_STORE, false, false, p, 0, pdl(), st));
