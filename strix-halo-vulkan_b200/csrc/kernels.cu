@@ -226,6 +226,62 @@ static int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem
 // =========================================================================================
 constexpr int RT_ROWS = 8;  // router rows per CTA: one per warp
 
+// Expert work list of a pass from its routing, by one CTA of 256 threads: pair id = n*(used+1) + slot,
+// slot == used is the shared expert; entries of at most 8 columns per expert for the column-tiled kernels,
+// one GEMM problem per expert for the tensor-core kernels, cols = pairs in expert-sorted order.
+__device__ void build_work_list(const RouterParams& p, int* counts, int* offs, int* eoff) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, M = p.M, nE = p.nE, used = p.used;
+  // work list: pair id = n*(used+1) + slot; slot == used is the shared expert
+  if (M == 1) {
+    if (tid < used) { p.entries[tid] = make_int4(p.topk[tid], tid, 1, 0); p.cols[tid] = tid; }
+    if (tid == used) { p.entries[used] = make_int4(-1, used, 1, 0); p.cols[used] = used; *p.n_entries = used + 1; }
+    tl_mark(p.tl, 6, true);
+    return;
+  }
+  for (int i = tid; i <= nE; i += 256) counts[i] = 0;
+  __syncthreads();
+  for (int i = tid; i < M * used; i += 256) atomicAdd(&counts[__ldcg(p.topk + i)], 1);
+  __syncthreads();
+  if (warp == 0) {  // exclusive scans of the pair counts and of the entry counts (8 columns per entry)
+    const int per = (nE + 31) / 32;
+    int c = 0, en = 0;
+    for (int i = 0; i < per; i++) { const int e = lane * per + i; if (e < nE) { c += counts[e]; en += (counts[e] + 7) >> 3; } }
+    int cs = c, es = en;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int a = __shfl_up_sync(0xffffffffu, cs, o), b = __shfl_up_sync(0xffffffffu, es, o);
+      if (lane >= o) { cs += a; es += b; }
+    }
+    int co = cs - c, eo = es - en;
+    for (int i = 0; i < per; i++) {
+      const int e = lane * per + i;
+      if (e < nE) { offs[e] = co; eoff[e] = eo; co += counts[e]; eo += (counts[e] + 7) >> 3; }
+    }
+    const int tot_c = __shfl_sync(0xffffffffu, cs, 31), tot_e = __shfl_sync(0xffffffffu, es, 31);
+    if (lane == 0) { offs[nE] = tot_c; eoff[nE] = tot_e; }
+  }
+  __syncthreads();
+  for (int e = tid; e < nE; e += 256) {
+    for (int c = 0, i = 0; c < counts[e]; c += 8, i++)
+      if (eoff[e] + i < p.max_entries) p.entries[eoff[e] + i] = make_int4(e, offs[e] + c, min(8, counts[e] - c), 0);
+  }
+  // one GEMM problem per expert for the tensor-core expert kernels: rows [offs, offs + count) of the expert-sorted order
+  if (p.gprob != nullptr) for (int e = tid; e < nE; e += 256) p.gprob[e] = make_int4(e, offs[e], counts[e], offs[e]);
+  const int nsh = (M + 7) >> 3;
+  for (int i = tid; i < nsh; i += 256)
+    if (eoff[nE] + i < p.max_entries) p.entries[eoff[nE] + i] = make_int4(-1, offs[nE] + 8 * i, min(8, M - 8 * i), 0);
+  if (tid == 0) *p.n_entries = min(eoff[nE] + nsh, p.max_entries);
+  __syncthreads();
+  for (int i = tid; i <= nE; i += 256) counts[i] = 0;
+  __syncthreads();
+  for (int i = tid; i < M * used; i += 256) {
+    const int e = __ldcg(p.topk + i), n = i / used, k = i - n * used;
+    const int pos = atomicAdd(&counts[e], 1);
+    p.cols[offs[e] + pos] = n * (used + 1) + k;
+  }
+  for (int n = tid; n < M; n += 256) p.cols[offs[nE] + n] = n * (used + 1) + used;
+}
+
 __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   __shared__ int is_last;
   __shared__ int counts[1025], offs[1025], eoff[1025];
@@ -338,55 +394,46 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   if (!is_last) return;
   __threadfence();
   if (tid == 0) *p.ticket = 0;
-  // work list: pair id = n*(used+1) + slot; slot == used is the shared expert
-  if (M == 1) {
-    if (tid < used) { p.entries[tid] = make_int4(p.topk[tid], tid, 1, 0); p.cols[tid] = tid; }
-    if (tid == used) { p.entries[used] = make_int4(-1, used, 1, 0); p.cols[used] = used; *p.n_entries = used + 1; }
-    tl_mark(p.tl, 6, true);
-    return;
-  }
-  for (int i = tid; i <= nE; i += 256) counts[i] = 0;
-  __syncthreads();
-  for (int i = tid; i < M * used; i += 256) atomicAdd(&counts[__ldcg(p.topk + i)], 1);
-  __syncthreads();
-  if (warp == 0) {  // exclusive scans of the pair counts and of the entry counts (8 columns per entry)
-    const int per = (nE + 31) / 32;
-    int c = 0, en = 0;
-    for (int i = 0; i < per; i++) { const int e = lane * per + i; if (e < nE) { c += counts[e]; en += (counts[e] + 7) >> 3; } }
-    int cs = c, es = en;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      int a = __shfl_up_sync(0xffffffffu, cs, o), b = __shfl_up_sync(0xffffffffu, es, o);
-      if (lane >= o) { cs += a; es += b; }
+  build_work_list(p, counts, offs, eoff);
+}
+
+// Routing of a many-row pass whose router logits came from the tensor-core GEMM: one warp per row
+// computes the shared-expert gate (f32 weights against the fp16 row) and selects the experts; the last
+// CTA builds the work list. grid ceil(M / 8), block 256.
+__global__ void __launch_bounds__(256) route_rows_kernel(RouterParams p) {
+  __shared__ int is_last;
+  __shared__ int counts[1025], offs[1025], eoff[1025];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, H = p.H;
+  pdl_wait();
+  pdl_launch();
+  const int n = blockIdx.x * 8 + warp;
+  if (n < p.M) {
+    const __half* x = p.xn + (size_t)n * H;
+    float acc = 0.f;
+    for (int k = lane * 8; k < H; k += 256) {
+      uint4 xv = *reinterpret_cast<const uint4*>(x + k);
+      const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+      float4 g0 = *reinterpret_cast<const float4*>(p.sh_gate + k), g1 = *reinterpret_cast<const float4*>(p.sh_gate + k + 4);
+      acc = fmaf(g0.x, h2f_lo(xw[0]), acc); acc = fmaf(g0.y, h2f_hi(xw[0]), acc); acc = fmaf(g0.z, h2f_lo(xw[1]), acc); acc = fmaf(g0.w, h2f_hi(xw[1]), acc);
+      acc = fmaf(g1.x, h2f_lo(xw[2]), acc); acc = fmaf(g1.y, h2f_hi(xw[2]), acc); acc = fmaf(g1.z, h2f_lo(xw[3]), acc); acc = fmaf(g1.w, h2f_hi(xw[3]), acc);
     }
-    int co = cs - c, eo = es - en;
-    for (int i = 0; i < per; i++) {
-      const int e = lane * per + i;
-      if (e < nE) { offs[e] = co; eoff[e] = eo; co += counts[e]; eo += (counts[e] + 7) >> 3; }
-    }
-    const int tot_c = __shfl_sync(0xffffffffu, cs, 31), tot_e = __shfl_sync(0xffffffffu, es, 31);
-    if (lane == 0) { offs[nE] = tot_c; eoff[nE] = tot_e; }
+    acc = warp_sum(acc);
+    if (lane == 0) p.topk_w[(size_t)n * (p.used + 1) + p.used] = sigmoid_acc(acc);
+    if (p.nE <= 512) route_token<16>(p, n, lane);
+    else route_token<32>(p, n, lane);
   }
+  __threadfence();
   __syncthreads();
-  for (int e = tid; e < nE; e += 256) {
-    for (int c = 0, i = 0; c < counts[e]; c += 8, i++)
-      if (eoff[e] + i < p.max_entries) p.entries[eoff[e] + i] = make_int4(e, offs[e] + c, min(8, counts[e] - c), 0);
-  }
-  // one GEMM problem per expert for the tensor-core expert kernels: rows [offs, offs + count) of the expert-sorted order
-  if (p.gprob != nullptr) for (int e = tid; e < nE; e += 256) p.gprob[e] = make_int4(e, offs[e], counts[e], offs[e]);
-  const int nsh = (M + 7) >> 3;
-  for (int i = tid; i < nsh; i += 256)
-    if (eoff[nE] + i < p.max_entries) p.entries[eoff[nE] + i] = make_int4(-1, offs[nE] + 8 * i, min(8, M - 8 * i), 0);
-  if (tid == 0) *p.n_entries = min(eoff[nE] + nsh, p.max_entries);
+  if (tid == 0) is_last = (atomicAdd(p.ticket, 1) == (int)gridDim.x - 1);
   __syncthreads();
-  for (int i = tid; i <= nE; i += 256) counts[i] = 0;
-  __syncthreads();
-  for (int i = tid; i < M * used; i += 256) {
-    const int e = __ldcg(p.topk + i), n = i / used, k = i - n * used;
-    const int pos = atomicAdd(&counts[e], 1);
-    p.cols[offs[e] + pos] = n * (used + 1) + k;
-  }
-  for (int n = tid; n < M; n += 256) p.cols[offs[nE] + n] = n * (used + 1) + used;
+  if (!is_last) return;
+  __threadfence();
+  if (tid == 0) *p.ticket = 0;
+  build_work_list(p, counts, offs, eoff);
+}
+int launch_route_rows(const RouterParams& p, bool pdl, cudaStream_t st) {
+  if (p.nE > 1024 || p.used > 32 || p.H % 8 || p.xn == nullptr) { set_error("route_rows: shape outside kernel limits"); return ECAPACITY; }
+  return launch_k(route_rows_kernel, dim3((p.M + 7) / 8), dim3(256), 0, pdl, st, p);
 }
 
 int launch_router(const RouterParams& p, bool pdl, cudaStream_t st) {

@@ -40,6 +40,8 @@ int launch_row_tail(const TailParams& tp, bool pdl, cudaStream_t st);
 int launch_concat_norm(const float* e, const float* hs, const float* enorm, const float* hnorm, float eps, int H, int M, __half* xcat, bool pdl, cudaStream_t st);
 
 int launch_router(const RouterParams& p, bool pdl, cudaStream_t st);
+// selection + work list only, for passes whose logits come from launch_qgemm (the shared gate is computed here)
+int launch_route_rows(const RouterParams& p, bool pdl, cudaStream_t st);
 int launch_moe_gather(const __half* xn, const int* cols, int pairs, int slots1, int H, __half* xperm, bool pdl, cudaStream_t st);
 
 

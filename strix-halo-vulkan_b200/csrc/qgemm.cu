@@ -83,7 +83,8 @@ template <int TYPE>
 struct RawBlock {
   // Q4_K: header, 8 x 16 nibble bytes. Q5_K: header, 2 x 16 fifth-bit bytes, 8 x 16 nibble bytes.
   // Q6_K (row planes): 8 x 16 ql bytes, 4 x 16 qh bytes, 16 int8 scales; d apart.
-  uint4 q[TYPE == T_Q4_K ? 9 : TYPE == T_Q5_K ? 11 : 13];
+  // Q8_0 (row planes): 16 x 16 int8 bytes (eight 32-element blocks), their eight fp16 d.
+  uint4 q[TYPE == T_Q4_K ? 9 : TYPE == T_Q5_K ? 11 : TYPE == T_Q8_0 ? 17 : 13];
   uint32_t d;
 };
 
@@ -101,6 +102,11 @@ __device__ __forceinline__ void load_raw(const uint8_t* row, int nb, int blk, Ra
     const uint8_t* b = row + (size_t)blk * (16 * NQ);
 #pragma unroll
     for (int i = 0; i < NQ; i++) r.q[i] = ldg128(b + 16 * i);
+  } else if constexpr (TYPE == T_Q8_0) {  // row planes: qs[K] | d[K/32] fp16
+    const uint8_t* qs = row + (size_t)blk * 256;
+#pragma unroll
+    for (int i = 0; i < 16; i++) r.q[i] = ldg128(qs + 16 * i);
+    r.q[16] = ldg128(row + (size_t)nb * 256 + (size_t)blk * 16);
   } else {  // Q6_K row planes: ql[nb][128] | qh[nb][64] | scales[nb][16] | d[nb]
     const uint8_t* ql = row + (size_t)blk * 128;
     const uint8_t* qh = row + (size_t)nb * 128 + (size_t)blk * 64;
@@ -173,6 +179,26 @@ __device__ __forceinline__ void dequant64(const RawBlock<TYPE>& r, int j, uint4 
       }
       out[c] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
       out[4 + c] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    }
+  } else if constexpr (TYPE == T_Q8_0) {
+    // bytes are int8: flip the sign bit (b + 128 as unsigned), ride the exponent trick, take 1152 off
+    const uint32_t m1152 = h2_bcast(-1152.f);
+    const uint32_t dw[4] = {r.q[16].x, r.q[16].y, r.q[16].z, r.q[16].w};
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++) {  // 32-element block 2j + hh: chunks 4*hh .. 4*hh+3
+      const int bi = 2 * j + hh;
+      const float dv = (bi & 1) ? h2f_hi(dw[bi >> 1]) : h2f_lo(dw[bi >> 1]);
+      uint32_t ds, dsl;
+      h2_split(dv, ds, dsl);
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        const uint4 qv = r.q[4 * j + 2 * hh + (c >> 1)];
+        const uint32_t w0 = ((c & 1) ? qv.z : qv.x) ^ 0x80808080u, w1 = ((c & 1) ? qv.w : qv.y) ^ 0x80808080u;
+        uint32_t a, b, e, f;
+        bytes_to_h2(w0, m1152, a, b);
+        bytes_to_h2(w1, m1152, e, f);
+        out[4 * hh + c] = make_uint4(hfma2_u(a, ds, hmul2_u(a, dsl)), hfma2_u(b, ds, hmul2_u(b, dsl)), hfma2_u(e, ds, hmul2_u(e, dsl)), hfma2_u(f, ds, hmul2_u(f, dsl)));
+      }
     }
   } else {
     const int hf = j >> 1, up = j & 1;  // quarters 2*up, 2*up+1 of half hf
@@ -466,8 +492,11 @@ int launch_qgemm(uint32_t type, int epi, int tn, const QGemmParams& p, const voi
     case T_Q4_K: return launch_tn<T_Q4_K>(epi, tn, p, tm, pdl, st);
     case T_Q5_K: return launch_tn<T_Q5_K>(epi, tn, p, tm, pdl, st);
     case T_Q6_K: return launch_tn<T_Q6_K>(epi, tn, p, tm, pdl, st);
+    case T_Q8_0:
+      if (epi == GEMM_STORE && tn == 64) return launch_t<T_Q8_0, 64, GEMM_STORE>(p, tm, pdl, st);
+      break;
   }
-  set_error("qgemm: weight type has no tensor-core projection kernel (Q4_K, Q5_K, Q6_K only)");
+  set_error("qgemm: weight type has no tensor-core projection kernel (Q4_K, Q5_K, Q6_K; Q8_0 with 64-row tiles and a plain store)");
   return EINVAL_;
 }
 

@@ -31,6 +31,17 @@ def test_qgemm_matches_fp16_weight_product(pkg, orc, typ, rows, k, m, tile):
     assert np.abs(got - want).max() <= TOL * scale, (np.abs(got - want).max(), scale)
 
 
+@pytest.mark.parametrize("rows,k,m", [(512, 2048, 300), (128, 256, 5), (96, 1024, 70)])
+def test_qgemm_q8_0_router_weights(pkg, orc, rows, k, m):
+    # the router's weight type, 64-row tiles only (many-row passes compute the router logits this way)
+    rng = np.random.default_rng(rows + k + m)
+    q = orc.quantize(8, (0.02 * rng.standard_normal((rows, k))).astype(np.float32))
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    got = pkg.qgemm(8, q, rows, k, x, 64)
+    want = _want(orc, 8, q, rows, k, x)
+    assert np.abs(got - want).max() <= TOL * np.abs(want).max()
+
+
 def test_qgemm_agrees_with_the_few_row_kernel(pkg, orc):
     # the two projection kernels differ only by the fp16 rounding of the weights
     rng = np.random.default_rng(5)
