@@ -449,21 +449,22 @@ __device__ __forceinline__ void stage_sx(int K, int xcols, const uint8_t* xs, __
   __syncthreads();
 }
 
-__device__ __forceinline__ void stage_x_f16(const __half* x, int64_t ldx, int K, int xcols, uint8_t* xs, __half* sxs, int ncols, const int* xrows,
-                                            int xstride) {
-  const int tid = threadIdx.x;
-  for (int c = 0; c < ncols; c++) {
-    const __half* src = x + (int64_t)xrows[c] * ldx;
-    uint8_t* dst = xs + (size_t)c * xstride;
-    for (int k = tid * 8; k < K; k += QG_THREADS * 8) {
-      uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + k));
-      uint4 o;
-      o.x = __byte_perm(v.x, v.y, 0x5410); o.y = __byte_perm(v.x, v.y, 0x7632);
-      o.z = __byte_perm(v.z, v.w, 0x5410); o.w = __byte_perm(v.z, v.w, 0x7632);
-      *reinterpret_cast<uint4*>(dst + 2 * k + 16 * (k >> 6)) = o;
-    }
+// one fp16 row into the permuted layout, by threads t of nt
+__device__ __forceinline__ void copy_x_row(const __half* src, int K, uint8_t* dst, int t, int nt) {
+  for (int k = t * 8; k < K; k += nt * 8) {
+    uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + k));
+    uint4 o;
+    o.x = __byte_perm(v.x, v.y, 0x5410); o.y = __byte_perm(v.x, v.y, 0x7632);
+    o.z = __byte_perm(v.z, v.w, 0x5410); o.w = __byte_perm(v.z, v.w, 0x7632);
+    *reinterpret_cast<uint4*>(dst + 2 * k + 16 * (k >> 6)) = o;
   }
-  __syncthreads();
+}
+__device__ __forceinline__ void stage_x_f16(const __half* x, int64_t ldx, int K, int xcols, uint8_t* xs, __half* sxs, int ncols, const int* xrows,
+                                            int xstride, bool copied = false) {
+  if (!copied) {
+    for (int c = 0; c < ncols; c++) copy_x_row(x + (int64_t)xrows[c] * ldx, K, xs + (size_t)c * xstride, threadIdx.x, QG_THREADS);
+    __syncthreads();
+  }
   stage_sx(K, xcols, xs, sxs, ncols, xstride);
 }
 
@@ -634,7 +635,7 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p) 
 
   const uint8_t *wa = nullptr, *wb = nullptr;
   int ncols = 0, col_off = 0;
-  bool active = true;
+  bool active = true, x_copied = false;
   if constexpr (GROUPED) {
     pdl_wait();  // the entries (or the logits) are written by the router kernel
     int4 e;
@@ -642,10 +643,16 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p) 
       const int used = p.route.used, y = blockIdx.y;
       const bool writer = blockIdx.x == 0 && y == 0;
       active = y <= used;
-      if (warp == 0 && (active || writer)) {
-        const int ex = p.route.nE <= 512 ? route_token<16>(p.route, 0, lane, writer, y, route_topk) : route_token<32>(p.route, 0, lane, writer, y, route_topk);
-        if (lane == 0) route_expert = y < used ? ex : -1;
+      if (warp == 0) {
+        if (active || writer) {
+          const int ex = p.route.nE <= 512 ? route_token<16>(p.route, 0, lane, writer, y, route_topk) : route_token<32>(p.route, 0, lane, writer, y, route_topk);
+          if (lane == 0) route_expert = y < used ? ex : -1;
+        }
+      } else if constexpr (PRO == PRO_F16) {
+        // meanwhile the other warps stage the pass's single activation row (it does not depend on the routing)
+        copy_x_row(p.x, K, xs, tid - 32, QG_THREADS - 32);
       }
+      x_copied = PRO == PRO_F16;  // for every thread alike: the barrier below covers the copy
       __syncthreads();
       e = make_int4(route_expert, y, 1, 0);
       if (writer) {  // the work list of a single row: one entry per slot, the shared expert last
@@ -712,7 +719,7 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p) 
     __syncthreads();
     if constexpr (PRO == PRO_COMBINE) stage_x_combine(p, xs, sxs, scratch, wsm, ncols, xrows, xstride, blockIdx.x == 0 && blockIdx.y == 0);
     else if constexpr (PRO == PRO_NORM) stage_x_norm(p, xs, sxs, scratch, ncols, xrows, xstride, p.xn_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0);
-    else stage_x_f16(p.x, p.ldx, K, p.xcols, xs, sxs, ncols, xrows, xstride);
+    else stage_x_f16(p.x, p.ldx, K, p.xcols, xs, sxs, ncols, xrows, xstride, x_copied);
     tl_mark(p.tl, 2);
 
     const bool live = g < ncols;

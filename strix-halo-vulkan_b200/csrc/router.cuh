@@ -56,9 +56,20 @@ __device__ __forceinline__ int route_token(const RouterParams& p, int n, int lan
   // values, then one warp-wide min of the indices that hold it.
   float wsum = 0.f, last_p = 0.f, myw = 0.f;
   for (int k = 0; k <= used; k++) {
-    float bv = pv[0]; int bi = 0;
+    // the lane's maximum by a tree (depth log2 NPL), then the lowest of its slots that holds it
+    float t[NPL];
 #pragma unroll
-    for (int i = 1; i < NPL; i++) if (pv[i] > bv) { bv = pv[i]; bi = i; }
+    for (int i = 0; i < NPL; i++) t[i] = pv[i];
+#pragma unroll
+    for (int w = NPL / 2; w >= 1; w >>= 1) {
+#pragma unroll
+      for (int i = 0; i < w; i++) t[i] = fmaxf(t[i], t[i + w]);
+    }
+    const float bv = t[0];
+    uint32_t eq = 0;
+#pragma unroll
+    for (int i = 0; i < NPL; i++) eq |= (pv[i] == bv ? 1u : 0u) << i;
+    const int bi = __ffs((int)eq) - 1;
     const uint32_t key = bv < 0.f ? 0u : __float_as_uint(bv) + 1u;          // taken / absent entries sort last
     const uint32_t best = __reduce_max_sync(0xffffffffu, key);
     const uint32_t mine = key == best && best != 0u ? (uint32_t)(lane + 32 * bi) : 0x7fffffffu;
