@@ -672,9 +672,7 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(128) dn_step_kernel(
 // The same layer for sequences of many tokens (prefill), as three kernels: everything that does not
 // depend on the recurrent state (alpha / beta, conv + SiLU, L2 norms, gates) is computed for all tokens
 // in parallel and packed per (head, row block) and token; the scan then walks the tokens with no
-// block-wide synchronisation at all, each warp owning eight state rows; the gated norm runs per token
-// afterwards. Thread mappings and summation orders are those of dn_step_kernel, so the two forms give
-// the same bits.
+// block-wide synchronisation at all; the gated norm runs per token afterwards.
 // -----------------------------------------------------------------------------------------
 constexpr int DN_PACK = 292;   // floats per (CTA id, token): q 128 | k 128 | v 32 | decay | beta | pad 2
 constexpr int DN_PRE_TOKENS = 16;
@@ -744,62 +742,73 @@ __global__ void __launch_bounds__(128) dn_pre_kernel(DnStepParams p) {
   }
 }
 
+// The recurrence itself. A thread owns a quarter (32 of the 128 key dims) of one of the CTA's 32 state
+// rows, in registers; per token it needs that quarter of k and q (fetched one token ahead), 32-term dot
+// products as four interleaved partial sums, and two shuffles over the four lanes of a row. No shared
+// memory and no barrier: every group of four lanes advances on its own. (The summation order differs from
+// dn_step_kernel's, so the two forms agree to rounding, not to the bit.)
 __global__ void __launch_bounds__(128) dn_scan_kernel(DnStepParams p) {
   const int D = 128, RB = 4;
   const int h = blockIdx.x / RB, rb = blockIdx.x % RB;
   const SeqDesc sq = p.seqs[blockIdx.y];
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  float* S = p.state + (size_t)sq.slot * p.state_slot_stride + (size_t)h * D * D;
-  const int j0 = rb * 32 + warp * 8;
-  float4 s[8];
+  const int tid = threadIdx.x, jl = tid >> 2, part = tid & 3;
+  const int j = rb * 32 + jl;
+  float* Srow = p.state + (size_t)sq.slot * p.state_slot_stride + (size_t)h * D * D + (size_t)j * D + 32 * part;
+  float s[32];
 #pragma unroll
-  for (int r = 0; r < 8; r++) s[r] = *reinterpret_cast<const float4*>(S + (size_t)(j0 + r) * D + lane * 4);
+  for (int i = 0; i < 8; i++) {
+    const float4 v = *reinterpret_cast<const float4*>(Srow + 4 * i);
+    s[4 * i] = v.x; s[4 * i + 1] = v.y; s[4 * i + 2] = v.z; s[4 * i + 3] = v.w;
+  }
   const float oscale = 1.0f / sqrtf((float)D);
   pdl_wait();
   pdl_launch();
   const float* pp = p.pre + ((size_t)blockIdx.x * p.pre_rows + sq.row0) * DN_PACK;
-  auto fetch = [&](int i, float4& q4, float4& k4, float& vv, float2& gb) {
+  float4 kq[16], nkq[16];  // k quarter (8 float4) then q quarter
+  float vv, nvv = 0.f; float2 gb, ngb = make_float2(0.f, 0.f);
+  auto fetch = [&](int i, float4 (&dst)[16], float& v, float2& g) {
     const float* t = pp + (size_t)i * DN_PACK;
-    q4 = __ldcg(reinterpret_cast<const float4*>(t + lane * 4));
-    k4 = __ldcg(reinterpret_cast<const float4*>(t + 128 + lane * 4));
-    vv = __ldcg(t + 256 + warp * 8 + (lane & 7));
-    gb = __ldcg(reinterpret_cast<const float2*>(t + 288));
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      dst[u] = __ldcg(reinterpret_cast<const float4*>(t + 128 + 32 * part + 4 * u));
+      dst[8 + u] = __ldcg(reinterpret_cast<const float4*>(t + 32 * part + 4 * u));
+    }
+    v = __ldcg(t + 256 + jl);
+    g = __ldcg(reinterpret_cast<const float2*>(t + 288));
   };
-  float4 q4, k4, nq4, nk4; float vv, nvv; float2 gb, ngb;
-  fetch(0, q4, k4, vv, gb);
+  fetch(0, kq, vv, gb);
   for (int i = 0; i < sq.n; i++) {
-    if (i + 1 < sq.n) fetch(i + 1, nq4, nk4, nvv, ngb);
+    if (i + 1 < sq.n) fetch(i + 1, nkq, nvv, ngb);
     const float g = gb.x, beta = gb.y;
-    float kv[8], oo[8];
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-    for (int r = 0; r < 8; r++) {
-      s[r].x *= g; s[r].y *= g; s[r].z *= g; s[r].w *= g;
-      kv[r] = s[r].x * k4.x + s[r].y * k4.y + s[r].z * k4.z + s[r].w * k4.w;
+    for (int u = 0; u < 8; u++) {
+      a0 = fmaf(s[4 * u], kq[u].x, a0); a1 = fmaf(s[4 * u + 1], kq[u].y, a1);
+      a2 = fmaf(s[4 * u + 2], kq[u].z, a2); a3 = fmaf(s[4 * u + 3], kq[u].w, a3);
     }
+    float kv = (a0 + a1) + (a2 + a3);
+    kv += __shfl_xor_sync(0xffffffffu, kv, 1);
+    kv += __shfl_xor_sync(0xffffffffu, kv, 2);
+    // S *= g; u = (v - S^T k) * beta; S += k u^T   (llm/deltanet.go:365-418), with g factored out of the dot
+    const float dj = (vv - g * kv) * beta;
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-      for (int r = 0; r < 8; r++) kv[r] += __shfl_xor_sync(0xffffffffu, kv[r], o);
+    for (int u = 0; u < 8; u++) {
+      s[4 * u] = fmaf(dj, kq[u].x, s[4 * u] * g); s[4 * u + 1] = fmaf(dj, kq[u].y, s[4 * u + 1] * g);
+      s[4 * u + 2] = fmaf(dj, kq[u].z, s[4 * u + 2] * g); s[4 * u + 3] = fmaf(dj, kq[u].w, s[4 * u + 3] * g);
+      o0 = fmaf(s[4 * u], kq[8 + u].x, o0); o1 = fmaf(s[4 * u + 1], kq[8 + u].y, o1);
+      o2 = fmaf(s[4 * u + 2], kq[8 + u].z, o2); o3 = fmaf(s[4 * u + 3], kq[8 + u].w, o3);
     }
+    float ov = (o0 + o1) + (o2 + o3);
+    ov += __shfl_xor_sync(0xffffffffu, ov, 1);
+    ov += __shfl_xor_sync(0xffffffffu, ov, 2);
+    if (part == 0) p.o_raw[(size_t)(sq.row0 + i) * (p.Hv * D) + h * D + j] = ov * oscale;
 #pragma unroll
-    for (int r = 0; r < 8; r++) {
-      const float dj = (__shfl_sync(0xffffffffu, vv, r) - kv[r]) * beta;
-      s[r].x += dj * k4.x; s[r].y += dj * k4.y; s[r].z += dj * k4.z; s[r].w += dj * k4.w;
-      oo[r] = s[r].x * q4.x + s[r].y * q4.y + s[r].z * q4.z + s[r].w * q4.w;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-      for (int r = 0; r < 8; r++) oo[r] += __shfl_xor_sync(0xffffffffu, oo[r], o);
-    }
-    float ov = oo[0] * oscale;
-#pragma unroll
-    for (int r = 0; r < 8; r++) ov = lane == r ? oo[r] * oscale : ov;
-    if (lane < 8) p.o_raw[(size_t)(sq.row0 + i) * (p.Hv * D) + h * D + j0 + lane] = ov;
-    q4 = nq4; k4 = nk4; vv = nvv; gb = ngb;
+    for (int u = 0; u < 16; u++) kq[u] = nkq[u];
+    vv = nvv; gb = ngb;
   }
 #pragma unroll
-  for (int r = 0; r < 8; r++) *reinterpret_cast<float4*>(S + (size_t)(j0 + r) * D + lane * 4) = s[r];
+  for (int i = 0; i < 8; i++) *reinterpret_cast<float4*>(Srow + 4 * i) = make_float4(s[4 * i], s[4 * i + 1], s[4 * i + 2], s[4 * i + 3]);
   // the ring keeps the last positions' conv inputs (written here, after every read of the old ring)
   {
     const int hk = h % p.Hk, qk = p.Hk * D;

@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <cstring>
 #include <string>
+#include <type_traits>
 
 #include "qgemm.cuh"
 
@@ -11,7 +12,7 @@ namespace b200 {
 
 namespace {
 
-constexpr int GM_THREADS = 192;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..5: dequant + epilogue
+constexpr int GM_THREADS = 320;   // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2..9: dequant + epilogue
 constexpr int GM_ROWS = 128;      // weight rows per tile = UMMA M = TMEM lanes
 constexpr int GM_KSTEP = 64;      // fp16 elements per K step = one 128-byte swizzle row
 constexpr int A_BYTES = GM_ROWS * 128;
@@ -140,102 +141,89 @@ __device__ __forceinline__ void bytes_to_h2(uint32_t w, uint32_t off, uint32_t& 
   p23 = hadd2_u(__byte_perm(w, 0x64646464u, 0x4342), off);
 }
 
-template <int TYPE>
-__device__ __forceinline__ void dequant64(const RawBlock<TYPE>& r, int j, uint4 (&out)[8]) {
-  const uint32_t m1024 = h2_bcast(-1024.f);
+// HALF selects which 32 of the K step's 64 elements a thread forms: chunks 4*HALF .. 4*HALF+3.
+template <int TYPE, int HALF>
+__device__ __forceinline__ void dequant32(const RawBlock<TYPE>& r, int j, uint4 (&out)[4]) {
   if constexpr (TYPE == T_Q4_K || TYPE == T_Q5_K) {
+    // low nibbles are sub-block 2j (HALF 0), high nibbles sub-block 2j+1 (HALF 1); word w holds bytes 4w..4w+3
     constexpr int QS = TYPE == T_Q4_K ? 1 : 3;  // first nibble quad
+    const uint32_t m1024 = h2_bcast(-1024.f);
     const float d = h2f_lo(r.q[0].x), dmin = h2f_hi(r.q[0].x);
-    int sc0, m0, sc1, m1;
-    k4_scale_min_dev(2 * j, r.q[0], sc0, m0);
-    k4_scale_min_dev(2 * j + 1, r.q[0], sc1, m1);
-    uint32_t d0, d0l, n0, n0l, d1, d1l, n1, n1l;
-    h2_split(__fmul_rn(d, (float)sc0), d0, d0l); h2_split(-__fmul_rn(dmin, (float)m0), n0, n0l);
-    h2_split(__fmul_rn(d, (float)sc1), d1, d1l); h2_split(-__fmul_rn(dmin, (float)m1), n1, n1l);
+    int sc, m;
+    k4_scale_min_dev(2 * j + HALF, r.q[0], sc, m);
+    uint32_t dh, dl, nh, nl;
+    h2_split(__fmul_rn(d, (float)sc), dh, dl);
+    h2_split(-__fmul_rn(dmin, (float)m), nh, nl);
     const uint4 qa = r.q[QS + 2 * j], qb = r.q[QS + 2 * j + 1];
     const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
     uint32_t hb[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     if constexpr (TYPE == T_Q5_K) {
       hb[0] = r.q[1].x; hb[1] = r.q[1].y; hb[2] = r.q[1].z; hb[3] = r.q[1].w; hb[4] = r.q[2].x; hb[5] = r.q[2].y; hb[6] = r.q[2].z; hb[7] = r.q[2].w;
     }
-    // low nibbles: sub-block 2j (chunks 0..3), high nibbles: sub-block 2j+1 (chunks 4..7); word w holds bytes 4w..4w+3
 #pragma unroll
     for (int c = 0; c < 4; c++) {
-      uint32_t lo[4], hi[4];
+      uint32_t o[4];
 #pragma unroll
       for (int h = 0; h < 2; h++) {
-        const uint32_t w = qw[2 * c + h];
-        uint32_t wl = w & 0x0F0F0F0Fu, wh = (w >> 4) & 0x0F0F0F0Fu;
-        if constexpr (TYPE == T_Q5_K) {  // bit 2j / 2j+1 of the fifth-bit byte -> bit 4 of the value
-          const uint32_t hw = hb[2 * c + h];
-          wl |= ((hw >> (2 * j)) & 0x01010101u) << 4;
-          wh |= ((hw >> (2 * j + 1)) & 0x01010101u) << 4;
-        }
+        uint32_t w = (qw[2 * c + h] >> (4 * HALF)) & 0x0F0F0F0Fu;
+        if constexpr (TYPE == T_Q5_K) w |= ((hb[2 * c + h] >> (2 * j + HALF)) & 0x01010101u) << 4;  // fifth bit -> bit 4
         uint32_t a, b;
-        bytes_to_h2(wl, m1024, a, b);
-        lo[2 * h] = hadd2_u(hfma2_u(a, d0, n0), hfma2_u(a, d0l, n0l)); lo[2 * h + 1] = hadd2_u(hfma2_u(b, d0, n0), hfma2_u(b, d0l, n0l));
-        bytes_to_h2(wh, m1024, a, b);
-        hi[2 * h] = hadd2_u(hfma2_u(a, d1, n1), hfma2_u(a, d1l, n1l)); hi[2 * h + 1] = hadd2_u(hfma2_u(b, d1, n1), hfma2_u(b, d1l, n1l));
+        bytes_to_h2(w, m1024, a, b);
+        o[2 * h] = hadd2_u(hfma2_u(a, dh, nh), hfma2_u(a, dl, nl));
+        o[2 * h + 1] = hadd2_u(hfma2_u(b, dh, nh), hfma2_u(b, dl, nl));
       }
-      out[c] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-      out[4 + c] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      out[c] = make_uint4(o[0], o[1], o[2], o[3]);
     }
   } else if constexpr (TYPE == T_Q8_0) {
     // bytes are int8: flip the sign bit (b + 128 as unsigned), ride the exponent trick, take 1152 off
     const uint32_t m1152 = h2_bcast(-1152.f);
     const uint32_t dw[4] = {r.q[16].x, r.q[16].y, r.q[16].z, r.q[16].w};
+    const int bi = 2 * j + HALF;  // 32-element block of the super-block
+    const float dv = (bi & 1) ? h2f_hi(dw[bi >> 1]) : h2f_lo(dw[bi >> 1]);
+    uint32_t ds, dsl;
+    h2_split(dv, ds, dsl);
 #pragma unroll
-    for (int hh = 0; hh < 2; hh++) {  // 32-element block 2j + hh: chunks 4*hh .. 4*hh+3
-      const int bi = 2 * j + hh;
-      const float dv = (bi & 1) ? h2f_hi(dw[bi >> 1]) : h2f_lo(dw[bi >> 1]);
-      uint32_t ds, dsl;
-      h2_split(dv, ds, dsl);
-#pragma unroll
-      for (int c = 0; c < 4; c++) {
-        const uint4 qv = r.q[4 * j + 2 * hh + (c >> 1)];
-        const uint32_t w0 = ((c & 1) ? qv.z : qv.x) ^ 0x80808080u, w1 = ((c & 1) ? qv.w : qv.y) ^ 0x80808080u;
-        uint32_t a, b, e, f;
-        bytes_to_h2(w0, m1152, a, b);
-        bytes_to_h2(w1, m1152, e, f);
-        out[4 * hh + c] = make_uint4(hfma2_u(a, ds, hmul2_u(a, dsl)), hfma2_u(b, ds, hmul2_u(b, dsl)), hfma2_u(e, ds, hmul2_u(e, dsl)), hfma2_u(f, ds, hmul2_u(f, dsl)));
-      }
+    for (int c = 0; c < 4; c++) {
+      const uint4 qv = r.q[4 * j + 2 * HALF + (c >> 1)];
+      const uint32_t w0 = ((c & 1) ? qv.z : qv.x) ^ 0x80808080u, w1 = ((c & 1) ? qv.w : qv.y) ^ 0x80808080u;
+      uint32_t a, b, e, f;
+      bytes_to_h2(w0, m1152, a, b);
+      bytes_to_h2(w1, m1152, e, f);
+      out[c] = make_uint4(hfma2_u(a, ds, hmul2_u(a, dsl)), hfma2_u(b, ds, hmul2_u(b, dsl)), hfma2_u(e, ds, hmul2_u(e, dsl)), hfma2_u(f, ds, hmul2_u(f, dsl)));
     }
   } else {
-    const int hf = j >> 1, up = j & 1;  // quarters 2*up, 2*up+1 of half hf
+    const int hf = j >> 1, up = j & 1, quarter = 2 * up + HALF;  // half hf, quarter: elements l = 0..31
     const float dd = __half2float(__ushort_as_half((unsigned short)r.d));
-    const uint4 l0 = r.q[4 * hf], l1 = r.q[4 * hf + 1], l2 = r.q[4 * hf + 2], l3 = r.q[4 * hf + 3], g0 = r.q[8 + 2 * hf], g1 = r.q[9 + 2 * hf];
-    const uint32_t lw[2][8] = {{l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w}, {l2.x, l2.y, l2.z, l2.w, l3.x, l3.y, l3.z, l3.w}};
+    const uint4 l0 = r.q[4 * hf + 2 * HALF], l1 = r.q[4 * hf + 2 * HALF + 1], g0 = r.q[8 + 2 * hf], g1 = r.q[9 + 2 * hf];
+    const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
     const uint32_t hw[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
     const uint32_t scw[4] = {r.q[12].x, r.q[12].y, r.q[12].z, r.q[12].w};
     const uint32_t m1056 = h2_bcast(-1056.f);  // the 1024 of the exponent trick and the format's centre 32
 #pragma unroll
-    for (int qq = 0; qq < 2; qq++) {      // quarter 2*up + qq: elements l = 0..31, chunks 4*qq .. 4*qq+3
-      const int quarter = 2 * up + qq;
+    for (int c = 0; c < 4; c++) {         // l = 8c .. 8c+7: words 2c, 2c+1; scale index 8*hf + l/16 + 2*quarter
+      const int si = 8 * hf + (c >> 1) + 2 * quarter;
+      uint32_t ds, dsl;
+      h2_split(__fmul_rn(dd, (float)(int)(int8_t)((scw[si >> 2] >> (8 * (si & 3))) & 0xFF)), ds, dsl);
+      uint32_t o[4];
 #pragma unroll
-      for (int c = 0; c < 4; c++) {       // l = 8c .. 8c+7: words 2c, 2c+1; scale index 8*hf + l/16 + 2*quarter
-        const int si = 8 * hf + (c >> 1) + 2 * quarter;
-        uint32_t ds, dsl;
-        h2_split(__fmul_rn(dd, (float)(int)(int8_t)((scw[si >> 2] >> (8 * (si & 3))) & 0xFF)), ds, dsl);
-        uint32_t o[4];
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-          const uint32_t w = lw[qq][2 * c + h];
-          const uint32_t nib = up ? (w >> 4) & 0x0F0F0F0Fu : w & 0x0F0F0F0Fu;
-          const uint32_t v = nib | (((hw[2 * c + h] >> (2 * quarter)) & 0x03030303u) << 4);
-          uint32_t a, b;
-          bytes_to_h2(v, m1056, a, b);
-          o[2 * h] = hfma2_u(a, ds, hmul2_u(a, dsl)); o[2 * h + 1] = hfma2_u(b, ds, hmul2_u(b, dsl));
-        }
-        out[4 * qq + c] = make_uint4(o[0], o[1], o[2], o[3]);
+      for (int h = 0; h < 2; h++) {
+        const uint32_t w = lw[2 * c + h];
+        const uint32_t nib = up ? (w >> 4) & 0x0F0F0F0Fu : w & 0x0F0F0F0Fu;
+        const uint32_t v = nib | (((hw[2 * c + h] >> (2 * quarter)) & 0x03030303u) << 4);
+        uint32_t a, b;
+        bytes_to_h2(v, m1056, a, b);
+        o[2 * h] = hfma2_u(a, ds, hmul2_u(a, dsl)); o[2 * h + 1] = hfma2_u(b, ds, hmul2_u(b, dsl));
       }
+      out[c] = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
 }
 
-// chunk c of row r of a [rows][128-byte] tile under the 128-byte swizzle
-__device__ __forceinline__ void store_swizzled(uint8_t* tile, int r, const uint4 (&v)[8]) {
+// chunks 4*HALF .. 4*HALF+3 of row r of a [rows][128-byte] tile under the 128-byte swizzle
+template <int HALF>
+__device__ __forceinline__ void store_swizzled(uint8_t* tile, int r, const uint4 (&v)[4]) {
 #pragma unroll
-  for (int c = 0; c < 8; c++) *reinterpret_cast<uint4*>(tile + r * 128 + ((c ^ (r & 7)) << 4)) = v[c];
+  for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(tile + r * 128 + (((4 * HALF + c) ^ (r & 7)) << 4)) = v[c];
 }
 
 template <int TYPE, int TN, int EPI>
@@ -252,8 +240,8 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   if (tid == 0) {
-    for (int s = 0; s < NS; s++) { mbar_init(&full_a[s], 4); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
-    mbar_init(&acc_full, 1); mbar_init(&acc_empty, 4);
+    for (int s = 0; s < NS; s++) { mbar_init(&full_a[s], 8); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(&acc_full, 1); mbar_init(&acc_empty, 8);
     mbar_fence_init();
     failed = 0;
   }
@@ -331,7 +319,11 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
     }
   } else {
     // ---- dequantisation, then the epilogue ------------------------------------------------------
-    const int r = (warp - 2) * 32 + lane;          // weight row of the tile this thread dequantises
+    // warps 2..5 form the first 32 elements of every row's K step and drain the first half of the
+    // accumulator's columns, warps 6..9 the second halves: two warps per scheduler hide each other's latencies
+    auto role = [&](auto half_c) {
+    constexpr int HALF = decltype(half_c)::value;
+    const int r = ((warp - 2) & 3) * 32 + lane;    // weight row of the tile this thread dequantises
     const int q = warp & 3;                        // TMEM lane quarter this warp may read
     uint32_t it = 0, tcount = 0;
     for (int idx = blockIdx.x; idx < total && !failed; idx += gridDim.x) {
@@ -341,36 +333,37 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
       const uint8_t* row = p.w + (size_t)pr.expert * p.expert_stride + (size_t)wrow * p.stride;
       const uint8_t* row2 = DUAL ? p.w2 + (size_t)pr.expert * p.expert_stride + (size_t)wrow * p.stride : nullptr;
       bool ok = true;
-      // one K step: dequantise, wait for the stage to be free, store the swizzled tile, signal the MMA warp
-      auto step = [&](const RawBlock<TYPE>& ra, const RawBlock<TYPE>& rb, int j) {
+      // one K step: dequantise, wait for the stage to be free, store the swizzled tile, signal the MMA warp.
+      // Gated pair: warps 2..5 form the whole K step of the gate tensor, warps 6..9 that of the up tensor
+      // (a thread then holds super-blocks of one tensor only).
+      const uint8_t* myrow = DUAL && HALF ? row2 : row;
+      auto step = [&](const RawBlock<TYPE>& ra, int j) {
         const int s = it % NS;
-        uint4 v[8];
-        dequant64<TYPE>(ra, j, v);
+        uint4 v[4], v2[4];
+        if constexpr (DUAL) { dequant32<TYPE, 0>(ra, j, v); dequant32<TYPE, 1>(ra, j, v2); }
+        else dequant32<TYPE, HALF>(ra, j, v);
         if (!mbar_wait(&empty[s], ((it / NS) & 1) ^ 1)) { give_up(); ok = false; return; }
         uint8_t* a = smem + (size_t)s * STAGE;
-        store_swizzled(a, r, v);
-        if constexpr (DUAL) {
-          dequant64<TYPE>(rb, j, v);
-          store_swizzled(a + A_BYTES, r, v);
-        }
+        if constexpr (DUAL) { store_swizzled<0>(a + HALF * A_BYTES, r, v); store_swizzled<1>(a + HALF * A_BYTES, r, v2); }
+        else store_swizzled<HALF>(a, r, v);
         fence_proxy_async();                       // make the generic-proxy stores visible to the tensor core
         __syncwarp();
         if (lane == 0) mbar_arrive(&full_a[s]);
         it++;
       };
-      auto fetch = [&](RawBlock<TYPE>& ra, RawBlock<TYPE>& rb, int blk) {
-        if (blk < nb) { load_raw<TYPE>(row, nb, blk, ra); if constexpr (DUAL) load_raw<TYPE>(row2, nb, blk, rb); }
+      auto fetch = [&](RawBlock<TYPE>& ra, int blk) {
+        if (blk < nb) load_raw<TYPE>(myrow, nb, blk, ra);
       };
-      auto block = [&](const RawBlock<TYPE>& ra, const RawBlock<TYPE>& rb) {
+      auto block = [&](const RawBlock<TYPE>& ra) {
 #pragma unroll
-        for (int j = 0; j < 4; j++) if (ok) step(ra, rb, j);
+        for (int j = 0; j < 4; j++) if (ok) step(ra, j);
       };
-      RawBlock<TYPE> a0, a1, b0, b1;
-      fetch(a0, b0, 0);
+      RawBlock<TYPE> a0, a1;
+      fetch(a0, 0);
       for (int blk = 0; blk < nb && ok; blk += 2) {
-        fetch(a1, b1, blk + 1);
-        block(a0, b0);
-        if (blk + 1 < nb && ok) { fetch(a0, b0, blk + 2); block(a1, b1); }
+        fetch(a1, blk + 1);
+        block(a0);
+        if (blk + 1 < nb && ok) { fetch(a0, blk + 2); block(a1); }
       }
       if (!ok) break;
       if (!mbar_wait(&acc_full, tcount & 1)) { give_up(); break; }
@@ -378,7 +371,7 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
       const int orow = nt * GM_ROWS + q * 32 + lane;  // TMEM lane = weight row
       const int t0 = tt * TN;
 #pragma unroll 1
-      for (int c0 = 0; c0 < TN; c0 += 32) {
+      for (int c0 = HALF * (TN / 2); c0 < (HALF + 1) * (TN / 2); c0 += 32) {
         uint32_t acc[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, acc);
         if constexpr (DUAL) {
@@ -411,6 +404,9 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
       if (lane == 0) mbar_arrive(&acc_empty);
       tcount++;
     }
+    };
+    if (warp < 6) role(std::integral_constant<int, 0>{});
+    else role(std::integral_constant<int, 1>{});
   }
   // ---- teardown: every thread arrives; tensor memory is released by the warp that took it -------
   tc_fence_before();
