@@ -78,6 +78,7 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   B200_TRY(dalloc(&act16, (size_t)MR * slots1 * c.ffn_expert)); B200_TRY(dalloc(&down, (size_t)MR * slots1 * H));
   B200_TRY(dalloc(&logits, (size_t)MR * c.vocab));
   { B200_TRY(dalloc(&dn_pre, (size_t)c.dn_heads_v * 4 * MR * 292)); B200_TRY(dalloc(&dn_oraw, (size_t)MR * vw)); }
+  { const float one[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f}; B200_TRY(dalloc(&ones, 8)); B200_CUDA(cudaMemcpy(ones, one, sizeof(one), cudaMemcpyHostToDevice)); }
   B200_TRY(dalloc(&xperm16, (size_t)MR * used * H)); B200_TRY(dalloc(&gprob, (size_t)c.n_expert)); B200_TRY(dalloc(&n_expert_dev, 1));
   B200_CUDA(cudaMemcpy(n_expert_dev, &c.n_expert, sizeof(int), cudaMemcpyHostToDevice));
   for (int i = 0; i < 3; i++) {
@@ -165,6 +166,8 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
   bool pending = false;     // fused passes: the MoE output of the last layer is not in hc yet; the next
                             // projection of the residual folds it in while staging and writes the other buffer
   int trace_layer = -1;     // layer whose post-MoE residual is still to be traced
+  int comb_used = used;     // what the pending combine adds: comb_used + 1 rows of `down` with weights comb_w
+  const float* comb_w = topk_w;
   launches = 0;
   bool first = true;
   int ss_n = 1;  // partial sums of squares the current residual rows carry
@@ -182,7 +185,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     if (!fused) return (int)PRO_F16;
     p.hsrc = hc; p.gamma = (const float*)gamma.data; p.xn_out = xn_copy;
     if (!pending) { p.ss_in = ss_part; p.ss_n = ss_n; return (int)PRO_NORM; }
-    p.down = down; p.topk_w = topk_w; p.used = used; p.h_out = hc == hbuf[0] ? hbuf[1] : hbuf[0];
+    p.down = down; p.topk_w = comb_w; p.used = comb_used; p.h_out = hc == hbuf[0] ? hbuf[1] : hbuf[0];
     return (int)PRO_COMBINE;
   };
   // after a PRO_COMBINE launch the rows live in the other buffer
@@ -197,8 +200,8 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
   };
   auto row_tail = [&](int mode, const DTensor& gamma) {
     TailParams t{};
-    t.mode = mode; t.h = hc; t.gamma = (const float*)gamma.data; t.xn = xn16; t.down = down; t.topk_w = topk_w;
-    t.used = used; t.H = H; t.M = M; t.eps = c.eps;
+    t.mode = mode; t.h = hc; t.gamma = (const float*)gamma.data; t.xn = xn16; t.down = down; t.topk_w = fused ? comb_w : topk_w;
+    t.used = fused ? comb_used : used; t.H = H; t.M = M; t.eps = c.eps;
     return t;
   };
   // passes of 16 rows and more run their dense projections on the tensor cores
@@ -335,6 +338,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       B200_TRY(launch_router(r, pdl(), st));
     }
     const int ne = max_entries_for(M);
+    comb_used = used; comb_w = topk_w;
     if (moe_gemm) {
       const int avg = M * used / c.n_expert, tne = avg <= 40 ? 64 : 128, tie = tne == 64 ? 0 : 1;
       B200_TRY(launch_moe_gather(xn16, cols, M * used, slots1, H, xperm16, pdl(), st));
@@ -367,7 +371,18 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     q.ws = L.down_sh.data; q.expert_stride = (int64_t)H * L.down_exps.stride;
     q.entries = entries; q.n_entries = n_entries; q.cols = cols; q.x_div = 1;
     q.y = down; q.ldy = H;
-    B200_TRY(launch_qgemv(L.down_exps.type, PRO_F16, EPI_STORE, false, true, q, ne, pdl(), st));
+    if (fused && M == 1 && L.down_exps.type == L.down_sh.type && slots1 <= 16) {
+      // one row: the routing weights are applied inside the down projection, which leaves a few partial rows
+      // (one per CTA of a tile) for the next projection to add, instead of used + 1 expert rows
+      MoeDown1Params d1{};
+      d1.w = L.down_exps.data; d1.ws = L.down_sh.data; d1.expert_stride = (int64_t)H * L.down_exps.stride; d1.stride = L.down_exps.stride;
+      d1.K = c.ffn_expert; d1.N = H; d1.used = used; d1.topk = topk; d1.topk_w = topk_w; d1.act = act16; d1.part = down;
+      d1.split = moe_down1_split(used, c.ffn_expert); d1.err = err_flag; d1.tl = tl();
+      B200_TRY(launch_moe_down1(L.down_exps.type, d1, pdl(), st));
+      comb_used = d1.split - 1; comb_w = ones;
+    } else {
+      B200_TRY(launch_qgemv(L.down_exps.type, PRO_F16, EPI_STORE, false, true, q, ne, pdl(), st));
+    }
     }
     if (fused) pending = true;
     else {
@@ -375,7 +390,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       B200_TRY(launch_row_tail(row_tail(2, next_norm), pdl(), st));
     }
     if (o.trace) {
-      if (fused) trace_layer = l;
+      if (fused && pending) trace_layer = l;
       else B200_CUDA(cudaMemcpyAsync(tr_out + (size_t)l * MR * H, hc, (size_t)M * H * sizeof(float), cudaMemcpyDeviceToDevice, st));
       B200_CUDA(cudaMemcpyAsync(tr_topk + (size_t)l * MR * used, topk, (size_t)M * used * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
       B200_CUDA(cudaMemcpyAsync(tr_w + (size_t)l * MR * slots1, topk_w, (size_t)M * slots1 * sizeof(float), cudaMemcpyDeviceToDevice, st));

@@ -35,6 +35,7 @@ struct Graph {
   alignas(64) unsigned char tm_xn[3][128], tm_y16[3][128], tm_ctx[3][128], tm_xperm[3][128], tm_act[3][128];
   float *dn_pre = nullptr, *dn_oraw = nullptr;   // many-token DeltaNet: packed scan inputs [Hv*4][rows][292], raw outputs [rows][Hv*D]
   int pass_max_n = 1;                            // longest sequence of the pass being enqueued
+  float* ones = nullptr;       // [8] weights 1.0 (the combine of pre-weighted partial rows)
   __half* xperm16 = nullptr;   // [rows * used][H]: activation rows in expert-sorted order
   int4* gprob = nullptr;       // [n_expert] GEMM problem per expert
   int* n_expert_dev = nullptr;

@@ -1,3 +1,4 @@
+#include <algorithm>
 // Instantiations and launcher of the fused K-quant projection kernel (qgemv.cuh).
 #include "kernels.cuh"
 
@@ -75,6 +76,41 @@ int qgemv_groups(int K, int N) {
   const int wpt = nb >= 8 ? 8 : nb >= 4 ? 4 : nb >= 2 ? 2 : 1;
   const int tpc = QG_WARPS / wpt;
   return ((N + 15) / 16 + tpc - 1) / tpc;
+}
+
+// CTAs per tile so that every warp has one (slot, super-block) unit, at most 4
+int moe_down1_split(int used, int K) {
+  const int units = (used + 1) * (K / 256);
+  return std::max(1, std::min(4, (units + QG_WARPS - 1) / QG_WARPS));
+}
+
+template <int TYPE>
+static int launch_md(const MoeDown1Params& p, bool pdl, cudaStream_t st) {
+  auto kernel = moe_down1_kernel<TYPE>;
+  const int slots1 = p.used + 1, cl = p.split;
+  const size_t smem = md_smem(p.K, (slots1 + cl - 1) / cl, p.stride);
+  if (smem > 200 * 1024) { set_error("moe_down1: tiles too large for shared memory"); return ECAPACITY; }
+  static bool configured = false;
+  if (!configured) { B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); configured = true; }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(((p.N + 15) / 16) * cl); cfg.blockDim = dim3(QG_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+  B200_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
+  return OK;
+}
+
+int launch_moe_down1(uint32_t type, const MoeDown1Params& p, bool pdl, cudaStream_t st) {
+  if (p.K % 256 != 0 || p.K <= 0 || p.used + 1 > MD_MAXSLOTS || p.split < 1 || p.split > 4 || p.part == nullptr) { set_error("moe_down1: shape outside kernel limits"); return EINVAL_; }
+  switch (type) {
+    case T_Q4_K: return launch_md<T_Q4_K>(p, pdl, st);
+    case T_Q5_K: return launch_md<T_Q5_K>(p, pdl, st);
+    case T_Q6_K: return launch_md<T_Q6_K>(p, pdl, st);
+  }
+  set_error("moe_down1: weight type has no fused projection kernel (Q4_K, Q5_K, Q6_K only)");
+  return EINVAL_;
 }
 
 int launch_qgemv(uint32_t type, int pro, int epi, bool dual, bool grouped, const QGemvParams& p, int max_entries, bool pdl, cudaStream_t st) {

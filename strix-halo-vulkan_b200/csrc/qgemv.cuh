@@ -21,6 +21,9 @@
 #pragma once
 #include "common.cuh"
 #include "router.cuh"
+#ifdef __CUDACC__
+#include <cooperative_groups.h>
+#endif
 
 namespace b200 {
 
@@ -804,6 +807,108 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p) 
       }
       buf ^= 1;
     }
+  }
+  tl_mark(p.tl, 4);
+}
+
+// -----------------------------------------------------------------------------------------
+// Expert down projections of a single-row pass with the routing weights applied: part[r][row] =
+// sum over the slots s of CTA r of w_s * (W_down[e_s][row] . act[s]) (reference: llm/moe.go:347-357,
+// 403-406; shaders/llm_moe_combine.comp:48-63). The consumer then adds `split` partial rows instead of
+// used + 1 expert rows. `split` CTAs share a tile (one (slot, super-block) unit per warp); the weighted
+// sums are added in warp order. grid N / 16 * split, block QG_THREADS.
+// -----------------------------------------------------------------------------------------
+struct MoeDown1Params {
+  const uint8_t* w;         // routed down weights [nE][N][K]
+  const uint8_t* ws;        // shared expert
+  int64_t expert_stride, stride;
+  int K, N, used;
+  const int32_t* topk;      // [used]
+  const float* topk_w;      // [used + 1]
+  const __half* act;        // [used + 1][K]
+  float* part;              // [split][N] weighted partial sums, one row per CTA of a tile
+  int split;                // CTAs per tile (1..4)
+  int* err;
+  Timeline tl;
+};
+constexpr int MD_MAXSLOTS = 16;
+
+// shared memory of a CTA that holds `maxloc` slots
+__host__ __device__ inline size_t md_smem(int K, int maxloc, int64_t stride) {
+  size_t xs = (size_t)maxloc * qg_xstride(K);
+  size_t sx = (((size_t)maxloc * (K / 32) * 2 * sizeof(__half)) + 15) & ~(size_t)15;
+  return ((xs + sx + 127) & ~(size_t)127) + (size_t)maxloc * 16 * (size_t)stride;
+}
+
+template <int TYPE>
+__global__ void __launch_bounds__(QG_THREADS) moe_down1_kernel(const MoeDown1Params p) {
+  // `split` CTAs share one 16-row tile: CTA r of them takes the slots s = r, r + split, ... and leaves its
+  // weighted sum as partial row r; the next projection adds the partial rows to the residual while staging
+  const int CL = p.split, rank = blockIdx.x % CL;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int K = p.K, nb = K / 256, slots1 = p.used + 1, xstride = qg_xstride(K);
+  const int nloc = (slots1 - rank + CL - 1) / CL;   // slots of this CTA
+  const int maxloc = (slots1 + CL - 1) / CL;
+  uint8_t* xs = smem;
+  __half* sxs = reinterpret_cast<__half*>(smem + (size_t)maxloc * xstride);
+  uint8_t* tiles = smem + (((size_t)maxloc * xstride + ((((size_t)maxloc * (K / 32) * 2 * sizeof(__half)) + 15) & ~(size_t)15) + 127) & ~(size_t)127);
+  const size_t tile_bytes = (size_t)16 * p.stride;
+  __shared__ float red[QG_WARPS][16], wgt[MD_MAXSLOTS];
+  __shared__ int expert[MD_MAXSLOTS];
+  __shared__ __align__(8) uint64_t bar;
+  tl_mark(p.tl, 0);
+  if (tid == 0) { mbar_init(&bar, 1); mbar_fence_init(); }
+  pdl_wait();   // the selection and the activations come from the kernel before
+  pdl_launch();
+  tl_mark(p.tl, 1);
+  if (tid < nloc) {
+    const int s = rank + tid * CL;
+    expert[tid] = s < p.used ? __ldcg(p.topk + s) : -1;
+    wgt[tid] = __ldcg(p.topk_w + s);
+  }
+  __syncthreads();
+  const int tile = blockIdx.x / CL, nrows = min(16, p.N - tile * 16);
+  if (tid == 0 && nloc > 0) {
+    mbar_expect_tx(&bar, (uint32_t)(nloc * nrows * p.stride));
+    for (int i = 0; i < nloc; i++) {
+      const uint8_t* base = expert[i] >= 0 ? p.w + (size_t)expert[i] * p.expert_stride : p.ws;
+      bulk_copy_g2s(tiles + (size_t)i * tile_bytes, base + (size_t)tile * 16 * p.stride, (uint32_t)(nrows * p.stride), &bar);
+    }
+  }
+  for (int i = 0; i < nloc; i++) copy_x_row(p.act + (size_t)(rank + i * CL) * K, K, xs + (size_t)i * xstride, tid, QG_THREADS);
+  __syncthreads();
+  stage_sx(K, maxloc, xs, sxs, nloc, xstride);
+  tl_mark(p.tl, 2);
+  bool ok = true;
+  if (nloc > 0 && !mbar_wait(&bar, 0)) {
+    if (p.err != nullptr && tid == 0) atomicExch(p.err, 1);  // a copy never landed: report, contribute nothing
+    ok = false;
+  }
+  tl_mark(p.tl, 3);
+  int r0 = g, r1 = g + 8;
+  if (r0 >= nrows) r0 = nrows - 1;
+  if (r1 >= nrows) r1 = nrows - 1;
+  const bool live = g == 0;  // the single activation row sits in column 0 of the mma's N axis
+  float tot0 = 0.f, tot1 = 0.f;
+  for (int u = warp; ok && u < nloc * nb; u += QG_WARPS) {
+    const int i = u / nb, blk = u - i * nb;
+    const uint8_t* tb = tiles + (size_t)i * tile_bytes;
+    typename RowRegs<TYPE>::type a0, a1;
+    issue_row<TYPE>(a0, tb + (size_t)r0 * p.stride, nb, blk, t);
+    issue_row<TYPE>(a1, tb + (size_t)r1 * p.stride, nb, blk, t);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    block_accumulate<TYPE>(acc, a0, a1, xs + (size_t)i * xstride, sxs + (size_t)((t & 1) * maxloc + i) * (K / 32), live, blk, t);
+    tot0 = fmaf(wgt[i], acc[0], tot0);   // column 0: rows g and g + 8 on the lanes with t == 0
+    tot1 = fmaf(wgt[i], acc[2], tot1);
+  }
+  if (t == 0) { red[warp][g] = tot0; red[warp][g + 8] = tot1; }
+  __syncthreads();
+  if (tid < nrows) {
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < QG_WARPS; w++) v += red[w][tid];
+    p.part[(size_t)rank * p.N + (size_t)tile * 16 + tid] = v;
   }
   tl_mark(p.tl, 4);
 }
