@@ -307,21 +307,33 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   __shared__ float rscale[8];
   const bool staged = p.h != nullptr;
   if (staged) {  // ffn_norm fused into the router (M <= 8): every CTA normalises the rows, CTA 0 keeps a copy
+    // the first row's values and the norm weights do not depend on the scale: fetch them before reducing the partials
+    float4 hpre[2], gpre[2];
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+      const int k = tid * 4 + i * 1024;
+      if (k < H) { hpre[i] = __ldcg(reinterpret_cast<const float4*>(p.h + k)); gpre[i] = *reinterpret_cast<const float4*>(p.gamma + k); }
+    }
     if (warp < M) {
       const float sc = scale_from_parts(p.ss_in, p.ss_n, warp, H, p.eps);
       if (lane == 0) rscale[warp] = sc;
     }
     __syncthreads();
+    auto put = [&](int n, int k, const float4& hv, const float4& g, float scale) {
+      __half2 a = __floats2half2_rn(hv.x * scale * g.x, hv.y * scale * g.y), b = __floats2half2_rn(hv.z * scale * g.z, hv.w * scale * g.w);
+      const uint2 o = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+      *reinterpret_cast<uint2*>(rxs + (size_t)n * H + k) = o;
+      if (blockIdx.x == 0 && p.xn_out != nullptr) *reinterpret_cast<uint2*>(p.xn_out + (size_t)n * H + k) = o;
+    };
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+      const int k = tid * 4 + i * 1024;
+      if (k < H) put(0, k, hpre[i], gpre[i], rscale[0]);
+    }
     for (int n = 0; n < M; n++) {
       const float scale = rscale[n];
-      for (int k = tid * 4; k < H; k += 1024) {
-        const float4 hv = __ldcg(reinterpret_cast<const float4*>(p.h + (size_t)n * H + k));
-        const float4 g = *reinterpret_cast<const float4*>(p.gamma + k);
-        __half2 a = __floats2half2_rn(hv.x * scale * g.x, hv.y * scale * g.y), b = __floats2half2_rn(hv.z * scale * g.z, hv.w * scale * g.w);
-        const uint2 o = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
-        *reinterpret_cast<uint2*>(rxs + (size_t)n * H + k) = o;
-        if (blockIdx.x == 0 && p.xn_out != nullptr) *reinterpret_cast<uint2*>(p.xn_out + (size_t)n * H + k) = o;
-      }
+      for (int k = tid * 4 + (n == 0 ? 2048 : 0); k < H; k += 1024)
+        put(n, k, __ldcg(reinterpret_cast<const float4*>(p.h + (size_t)n * H + k)), *reinterpret_cast<const float4*>(p.gamma + k), scale);
     }
     __syncthreads();
   }

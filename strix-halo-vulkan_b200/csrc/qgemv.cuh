@@ -454,6 +454,9 @@ __device__ __forceinline__ void stage_sx(int K, int xcols, const uint8_t* xs, __
 
 // one fp16 row into the permuted layout, by threads t of nt
 __device__ __forceinline__ void copy_x_row(const __half* src, int K, uint8_t* dst, int t, int nt) {
+  // every CTA reads the same row: each starts at another 128-byte line so the L2 slices are not all asked for
+  // the same line at the same moment
+  t = (t + 8 * (int)((blockIdx.x + blockIdx.y) % (unsigned)(nt / 8))) % nt;
   for (int k = t * 8; k < K; k += nt * 8) {
     uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + k));
     uint4 o;
@@ -482,7 +485,9 @@ __device__ __forceinline__ float scale_from_parts(const float* ss_in, int ss_n, 
 // RMSNorm fused into the staging (reference: llm/hc.go:176-190): each CTA normalises the rows it needs
 __device__ __forceinline__ void stage_x_norm(const QGemvParams& p, uint8_t* xs, __half* sxs, float* scratch, int ncols, const int* xrows, int xstride,
                                              bool write_xn) {
-  const int tid = threadIdx.x, warp = tid >> 5, K = p.K;
+  const int warp = threadIdx.x >> 5, K = p.K;
+  // element index of this thread, rotated by whole 128-byte lines per CTA (every CTA reads the same rows)
+  const int tid = (threadIdx.x + 8 * (int)((blockIdx.x + blockIdx.y) & 31)) & (QG_THREADS - 1);
   // the residual values do not depend on the scale: fetch the first batch before reducing the partials
   constexpr int PRE = 2;
   float4 hpre[PRE], gpre[PRE];
@@ -494,7 +499,7 @@ __device__ __forceinline__ void stage_x_norm(const QGemvParams& p, uint8_t* xs, 
   }
   if (warp < ncols) {
     const float sc = scale_from_parts(p.ss_in, p.ss_n, xrows[warp], K, p.eps);
-    if ((tid & 31) == 0) scratch[warp] = sc;
+    if ((threadIdx.x & 31) == 0) scratch[warp] = sc;
   }
   __syncthreads();
   for (int c = 0; c < ncols; c++) {
@@ -522,11 +527,18 @@ __device__ __forceinline__ void stage_x_norm(const QGemvParams& p, uint8_t* xs, 
 
 // The MoE combine and the RMSNorm that follows it, fused into the staging: columns go four at a time,
 // a thread keeping its 8 values of each in registers between the sum of squares and the scaling.
-__device__ __forceinline__ void stage_x_combine(const QGemvParams& p, uint8_t* xs, __half* sxs, float* scratch, float* wsm, int ncols, const int* xrows,
+__device__ __forceinline__ void stage_x_combine(const QGemvParams& p, uint8_t* xs, __half* sxs, float* scratch, int ncols, const int* xrows,
                                                 int xstride, bool writer) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, K = p.K, slots1 = p.used + 1;
-  for (int i = tid; i < ncols * slots1; i += QG_THREADS) wsm[i] = __ldcg(p.topk_w + (size_t)xrows[i / slots1] * slots1 + (i % slots1));
-  __syncthreads();
+  // element index of this thread, rotated by whole 128-byte lines per CTA (every CTA reads the same rows)
+  const int et = (tid + 8 * (int)((blockIdx.x + blockIdx.y) & 31)) & (QG_THREADS - 1);
+  // the norm weights are fetched with the first loads, not after the reduction
+  float4 gam[2];
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+    const int k = et * 4 + i * QG_THREADS * 4;
+    gam[i] = k < K ? *reinterpret_cast<const float4*>(p.gamma + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   for (int c0 = 0; c0 < ncols; c0 += 4) {
     float4 v[4][2];
     float sq[4] = {0.f, 0.f, 0.f, 0.f};
@@ -536,10 +548,10 @@ __device__ __forceinline__ void stage_x_combine(const QGemvParams& p, uint8_t* x
       const int64_t row = xrows[c];
       const float* hrow = p.hsrc + row * K;
       const float* dn = p.down + row * slots1 * K;
-      const float* w = wsm + c * slots1;
+      const float* w = p.topk_w + row * slots1;   // read by every thread alongside its rows (one trip to L2, not two)
 #pragma unroll
       for (int i = 0; i < 2; i++) {
-        const int k = tid * 4 + i * QG_THREADS * 4;
+        const int k = et * 4 + i * QG_THREADS * 4;
         v[cc][i] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (k < K && c0 + cc < ncols) {
           const float4 hv = __ldcg(reinterpret_cast<const float4*>(hrow + k));
@@ -548,10 +560,10 @@ __device__ __forceinline__ void stage_x_combine(const QGemvParams& p, uint8_t* x
 #pragma unroll 5
           for (int s = 0; s < p.used; s++) {
             const float4 d = __ldcg(reinterpret_cast<const float4*>(dn + (size_t)s * K + k));
-            const float wk = w[s];
+            const float wk = __ldcg(w + s);
             acc.x += d.x * wk; acc.y += d.y * wk; acc.z += d.z * wk; acc.w += d.w * wk;
           }
-          const float sg = w[p.used];
+          const float sg = __ldcg(w + p.used);
           float4 r;
           r.x = hv.x + (acc.x + sh.x * sg); r.y = hv.y + (acc.y + sh.y * sg); r.z = hv.z + (acc.z + sh.z * sg); r.w = hv.w + (acc.w + sh.w * sg);
           v[cc][i] = r;
@@ -577,9 +589,9 @@ __device__ __forceinline__ void stage_x_combine(const QGemvParams& p, uint8_t* x
       const int64_t row = xrows[c0 + cc];
 #pragma unroll
       for (int i = 0; i < 2; i++) {
-        const int k = tid * 4 + i * QG_THREADS * 4;
+        const int k = et * 4 + i * QG_THREADS * 4;
         if (k < K) {
-          const float4 g = *reinterpret_cast<const float4*>(p.gamma + k);
+          const float4 g = gam[i];
           const float v0 = v[cc][i].x * scale * g.x, v1 = v[cc][i].y * scale * g.y, v2 = v[cc][i].z * scale * g.z, v3 = v[cc][i].w * scale * g.w;
           __half2 a = __floats2half2_rn(v0, v2), b = __floats2half2_rn(v1, v3);  // stored order [x0,x2,x1,x3]
           *reinterpret_cast<uint2*>(dst + 2 * k + 16 * (k >> 6)) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
@@ -620,7 +632,6 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p) 
   const int NS = p.nstage;
   __shared__ float scratch[4 * QG_WARPS];
   __shared__ float ssq[2][QG_WARPS][8];
-  __shared__ float wsm[PRO == PRO_COMBINE ? QG_MAXCOLS * 33 : 1];
   __shared__ int col_rows[QG_MAXCOLS], xrows[QG_MAXCOLS];
   __shared__ int route_expert, route_topk[32];
   __shared__ __align__(8) uint64_t full_bar[QG_MAX_STAGES];
@@ -720,7 +731,7 @@ __global__ void __launch_bounds__(QG_THREADS) qgemv_kernel(const QGemvParams p) 
       xrows[tid] = GROUPED ? id / p.x_div : id;
     }
     __syncthreads();
-    if constexpr (PRO == PRO_COMBINE) stage_x_combine(p, xs, sxs, scratch, wsm, ncols, xrows, xstride, blockIdx.x == 0 && blockIdx.y == 0);
+    if constexpr (PRO == PRO_COMBINE) stage_x_combine(p, xs, sxs, scratch, ncols, xrows, xstride, blockIdx.x == 0 && blockIdx.y == 0);
     else if constexpr (PRO == PRO_NORM) stage_x_norm(p, xs, sxs, scratch, ncols, xrows, xstride, p.xn_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0);
     else stage_x_f16(p.x, p.ldx, K, p.xcols, xs, sxs, ncols, xrows, xstride, x_copied);
     tl_mark(p.tl, 2);
