@@ -989,11 +989,18 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(AttnParams p) {
       ka4[j] = ldg_stream(kra + 8 * (t + 4 * j));
       kb4[j] = ldg_stream(krb + 8 * (t + 4 * j));
     }
-    // the first value block does not depend on the scores: fetch it while the score mma runs
+    // the value rows do not depend on the scores: the first two 64-dim blocks are fetched while the score mma
+    // runs, the rest as soon as the key registers are free, so every value load is in flight before the softmax
     const int cell_a = cb + 2 * t, cell_c = cb + 8 + 2 * t;
     const int va_c = min(cell_a, c1 - 1), vb_c = min(cell_a + 1, c1 - 1), vc_c = min(cell_c, c1 - 1), vd_c = min(cell_c + 1, c1 - 1);
-    uint4 va = ldg_stream(vbase + (size_t)va_c * cell_stride + 8 * g), vb = ldg_stream(vbase + (size_t)vb_c * cell_stride + 8 * g);
-    uint4 vc = ldg_stream(vbase + (size_t)vc_c * cell_stride + 8 * g), vd = ldg_stream(vbase + (size_t)vd_c * cell_stride + 8 * g);
+    uint4 vv[NB][4];
+    auto fetch_v = [&](int b) {
+      const int doff = 8 * (g + 8 * b);
+      vv[b][0] = ldg_stream(vbase + (size_t)va_c * cell_stride + doff); vv[b][1] = ldg_stream(vbase + (size_t)vb_c * cell_stride + doff);
+      vv[b][2] = ldg_stream(vbase + (size_t)vc_c * cell_stride + doff); vv[b][3] = ldg_stream(vbase + (size_t)vd_c * cell_stride + doff);
+    };
+#pragma unroll
+    for (int b = 0; b < NB && b < 2; b++) fetch_v(b);
 #pragma unroll
     for (int j = 0; j < KS / 2; j++) {
       const uint32_t a0[4] = {qa[2 * j][0], 0u, qa[2 * j][1], 0u}, a1[4] = {qa[2 * j + 1][0], 0u, qa[2 * j + 1][1], 0u};
@@ -1002,6 +1009,8 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(AttnParams p) {
       mma16816(s1, a0, kb4[j].x, kb4[j].y);
       mma16816(s1, a1, kb4[j].z, kb4[j].w);
     }
+#pragma unroll
+    for (int b = 2; b < NB; b++) fetch_v(b);
     // row g, cells cb + 2t, +1 (tile 0) and cb + 8 + 2t, +1 (tile 1)
     float sc[4] = {s0[0] * scale, s0[1] * scale, s1[0] * scale, s1[1] * scale};
     const int cell[4] = {cb + 2 * t, cb + 2 * t + 1, cb + 8 + 2 * t, cb + 9 + 2 * t};
@@ -1021,12 +1030,7 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(AttnParams p) {
     // ---- O = O * corr + P V ----
 #pragma unroll
     for (int b = 0; b < NB; b++) {
-      const uint4 wa = va, wb = vb, wc = vc, wd = vd;
-      if (b + 1 < NB) {  // next block's loads go out before this block's mma
-        const int doff = 8 * (g + 8 * (b + 1));
-        va = ldg_stream(vbase + (size_t)va_c * cell_stride + doff); vb = ldg_stream(vbase + (size_t)vb_c * cell_stride + doff);
-        vc = ldg_stream(vbase + (size_t)vc_c * cell_stride + doff); vd = ldg_stream(vbase + (size_t)vd_c * cell_stride + doff);
-      }
+      const uint4 wa = vv[b][0], wb = vv[b][1], wc = vv[b][2], wd = vv[b][3];
       const uint32_t ra[4] = {wa.x, wa.y, wa.z, wa.w}, rb[4] = {wb.x, wb.y, wb.z, wb.w}, rc[4] = {wc.x, wc.y, wc.z, wc.w}, rd[4] = {wd.x, wd.y, wd.z, wd.w};
 #pragma unroll
       for (int j = 0; j < 4; j++) {
@@ -1098,12 +1102,12 @@ __global__ void attn_merge_kernel(AttnParams p) {
   for (int w = 0; w < (int)(blockDim.x + 31) / 32; w++) mm = fmaxf(mm, mg_red[w]);
   float ov = 0.f, lv = 0.f;
   int sp = 0;
-  for (; sp + 8 <= nlive; sp += 8) {  // eight independent loads in flight, summed in split order
-    float a[8];
+  for (; sp + 16 <= nlive; sp += 16) {  // sixteen independent loads in flight, summed in split order
+    float a[16];
 #pragma unroll
-    for (int u = 0; u < 8; u++) a[u] = __ldcg(part + (size_t)(sp + u) * PW + d);
+    for (int u = 0; u < 16; u++) a[u] = __ldcg(part + (size_t)(sp + u) * PW + d);
 #pragma unroll
-    for (int u = 0; u < 8; u++) {
+    for (int u = 0; u < 16; u++) {
       const float ms = mg_f[sp + u];
       const float e = ms == -INFINITY ? 0.f : expf(ms - mm);
       ov += a[u] * e; lv += mg_f[p.nsplit + sp + u] * e;
