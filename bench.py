@@ -23,6 +23,10 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode step at context 2052, from an ncu capture of the
+# 4-layer prefix scaled to 36 DeltaNet + 12 attention layers + head (profiles/decode_step_a3b_dram_traffic.md):
+# 36 x 47.28 MB + 12 x 44.70 MB + 255.91 MB. It is 98.6 % of the algorithmic bytes: nothing is read twice.
+A3B_DRAM_BYTES_PER_STEP = 2494.4e6
 PROMPT = 2048
 METRIC = "decode tok/s at batch 1 (Q4_K hybrid MoE, 80B-A3B shape)"
 
@@ -334,7 +338,8 @@ def main():
                        "context": ctx0, "weights_gb": model.weight_bytes / 1e9, "l2_policy": "inputs larger than L2 (2.5 GB streamed per step)",
                        "parallelism": "replicas" if world > 1 else "single GPU", "model_build_s": round(t_model, 1),
                        "prefill_s": round(t_prefill, 3), "prefill_tok_s": round(prompt_len / t_prefill, 1), "prefill_chunk": args.chunk},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": A3B_DRAM_BYTES_PER_STEP if args.config == "a3b" and not args.layers else None,
                          "peak_source": which, "kernel": "one decode step (CUDA graph of the token loop)",
                          "algorithmic_bytes_per_step": bytes_step},
             "e2e": {"value": world * e2e_steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 + 16 + 16,
