@@ -20,19 +20,27 @@ static int launch_one(const QGemvParams& p, int max_entries, bool pdl, cudaStrea
   const int tiles = (p.N + 15) / 16;
   const int groups = (tiles + tpc - 1) / tpc;
   const int ny = GROUPED ? max_entries : 1, nz = GROUPED ? 1 : (p.M + QG_MAXCOLS - 1) / QG_MAXCOLS;
-  // Two CTAs per SM when the ring fits twice, else one; persistent CTAs share the device
-  // between the y / z slices, and the ring is as deep as a CTA has groups to walk (at most 8).
+  // As many CTAs per SM (up to three: 80 registers per thread) as still leave each a ring of two stages, or of
+  // one when it has a single group to walk: more resident warps hide the dequantisation's latencies, and a
+  // grid that fits at once needs no second round. Three per SM only for the expert kernels: elsewhere the register cap costs more than
+  // the extra warps give, and every CTA of a projection reads the same activation rows out of L2 - the more
+  // CTAs ask at once the longer each waits. Persistent CTAs share the device between the y / z slices.
   const size_t fixed = qg_fixed_smem(p.K, p.xcols, DUAL), stage = qg_stage_bytes(p.K, p.stride, DUAL);
-  const size_t budget2 = 110 * 1024, budget1 = 220 * 1024;
-  if (fixed + stage > budget1) { set_error("qgemv: row length too large for shared memory"); return ECAPACITY; }
-  const int occ = fixed + 2 * stage <= budget2 ? 2 : 1;
-  int cap = g_sm_count * occ / (ny * nz);
-  if (cap < 1) cap = 1;
-  // every CTA walks the same number of groups (a ragged last round leaves most SMs idle)
-  const int rounds = (groups + cap - 1) / cap;
-  const int gx = (groups + rounds - 1) / rounds;
+  const size_t budgets[4] = {0, 220 * 1024, 110 * 1024, 72 * 1024};
+  if (fixed + stage > budgets[1]) { set_error("qgemv: row length too large for shared memory"); return ECAPACITY; }
+  int occ = 1, rounds = 1, gx = 1;
+  for (int o = 3; o >= 1; o--) {
+    if (o == 3 && !GROUPED) continue;  // the plain kernels are compiled for two CTAs per SM
+    int cap = g_sm_count * o / (ny * nz);
+    if (cap < 1) cap = 1;
+    // every CTA walks the same number of groups (a ragged last round leaves most SMs idle)
+    rounds = (groups + cap - 1) / cap;
+    gx = (groups + rounds - 1) / rounds;
+    occ = o;
+    if (fixed + (size_t)std::min(rounds, 2) * stage <= budgets[o]) break;
+  }
   const int per_cta = rounds;
-  int ns = (int)(((occ == 2 ? budget2 : budget1) - fixed) / stage);
+  int ns = (int)((budgets[occ] - fixed) / stage);
   if (ns > QG_MAX_STAGES) ns = QG_MAX_STAGES;
   if (ns > per_cta) ns = per_cta;
   if (ns < 1) ns = 1;

@@ -50,3 +50,15 @@ def test_qgemm_agrees_with_the_few_row_kernel(pkg, orc):
     x = rng.standard_normal((m, k)).astype(np.float32)
     a, b = pkg.qgemm(12, q, rows, k, x, 64), pkg.qgemv(12, q, rows, k, x)
     assert np.abs(a - b).max() <= 2e-3 * np.abs(b).max()
+
+
+def test_qgemm_refusals(pkg, orc):
+    # refused on the host before anything is launched
+    q = orc.quantize(12, np.zeros((128, 256), dtype=np.float32))
+    x = np.zeros((4, 256), dtype=np.float32)
+    with pytest.raises(pkg.lib.B200Error):
+        pkg.qgemm(12, q, 128, 256, x, 96)          # tiles are 64, 128 or 256 rows
+    with pytest.raises(pkg.lib.B200Error):
+        pkg.qgemm(8, orc.quantize(8, np.zeros((128, 256), dtype=np.float32)), 128, 256, x, 128)   # Q8_0: 64-row tiles only
+    with pytest.raises(pkg.lib.B200Error):
+        pkg.qgemm(0, np.zeros(128 * 256 * 4, dtype=np.uint8), 128, 256, x, 64)   # F32 weights have no kernel
