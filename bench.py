@@ -230,7 +230,7 @@ def main():
             dist.destroy_process_group()
         return
 
-    # every rank holds the whole model and decodes its own sequence (replicas); see DESIGN.md for expert parallelism
+    # every rank holds the whole model and decodes its own sequence: the path shards by sequences, no data crosses NVLink
     t0 = time.time()
     model = pkg.Model.synthetic(cfg, seed=0, device=local_rank)
     t_model = time.time() - t0

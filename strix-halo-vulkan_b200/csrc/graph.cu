@@ -70,11 +70,10 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   B200_TRY(dalloc(&hbuf[0], (size_t)MR * H)); B200_TRY(dalloc(&hbuf[1], (size_t)MR * H)); h = hbuf[0]; B200_TRY(dalloc(&proj, (size_t)MR * proj_ld));
   B200_TRY(dalloc(&xn16, (size_t)MR * H)); B200_TRY(dalloc(&q16, (size_t)MR * qw)); B200_TRY(dalloc(&ctx16, (size_t)MR * qw));
   B200_TRY(dalloc(&attn_partial, (size_t)MR * c.n_head * nsplit * (hd + 2)));
-  B200_TRY(dalloc(&attn_tickets, (size_t)MR * c.n_head_kv));
-  B200_TRY(dalloc(&r_logits, (size_t)MR * c.n_expert)); B200_TRY(dalloc(&r_probs, (size_t)MR * c.n_expert));
+  B200_TRY(dalloc(&r_logits, (size_t)MR * c.n_expert));
   B200_TRY(dalloc(&topk, (size_t)MR * used)); B200_TRY(dalloc(&topk_w, (size_t)MR * slots1)); B200_TRY(dalloc(&margin, (size_t)MR));
   B200_TRY(dalloc(&entries, (size_t)max_entries)); B200_TRY(dalloc(&n_entries, 1)); B200_TRY(dalloc(&cols, (size_t)MR * slots1));
-  B200_TRY(dalloc(&r_ticket, (size_t)2 + MR / 8)); B200_TRY(dalloc(&tail_ticket, 1)); B200_TRY(dalloc(&err_flag, 1)); B200_TRY(dalloc(&ss_part, (size_t)MR * SS_LD)); B200_TRY(dalloc(&y16, (size_t)MR * vw));
+  B200_TRY(dalloc(&r_ticket, (size_t)2 + MR / 8)); B200_TRY(dalloc(&err_flag, 1)); B200_TRY(dalloc(&ss_part, (size_t)MR * SS_LD)); B200_TRY(dalloc(&y16, (size_t)MR * vw));
   B200_TRY(dalloc(&act16, (size_t)MR * slots1 * c.ffn_expert)); B200_TRY(dalloc(&down, (size_t)MR * slots1 * H));
   B200_TRY(dalloc(&logits, (size_t)MR * c.vocab));
   { B200_TRY(dalloc(&dn_pre, (size_t)c.dn_heads_v * 4 * MR * 292)); B200_TRY(dalloc(&dn_oraw, (size_t)MR * vw)); }
@@ -161,7 +160,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
   const int H = c.n_embd, D = c.dn_head_dim, qk = c.dn_heads_k * D, vw = c.dn_heads_v * D, cw = 2 * qk + vw;
   const int hd = c.head_dim, qw = c.n_head * hd, kvw = c.n_head_kv * hd, used = c.n_expert_used, slots1 = used + 1;
   const int xcols = std::min(M, QG_MAXCOLS);
-  const bool fused = M <= QG_TAIL_ROWS && H <= QG_COMBINE_MAX_K;
+  const bool fused = M <= QG_FUSED_ROWS && H <= QG_COMBINE_MAX_K;
   float* hc = hbuf[0];      // residual rows of this pass
   bool pending = false;     // fused passes: the MoE output of the last layer is not in hc yet; the next
                             // projection of the residual folds it in while staging and writes the other buffer
@@ -298,7 +297,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       AttnParams a{};
       a.proj = proj; a.ldp = proj_ld; a.q_norm = (const float*)L.q_norm.data; a.k_norm = (const float*)L.k_norm.data; a.rope = rope;
       a.kcache = kcache[ai]; a.vcache = vcache[ai]; a.slot_stride = kv_slot_stride; a.row_slot = row_slot; a.row_pos = row_pos;
-      a.q16 = q16; a.partial = attn_partial; a.tickets = attn_tickets; a.ctx16 = ctx16;
+      a.q16 = q16; a.partial = attn_partial; a.ctx16 = ctx16;
       a.M = M; a.Hq = c.n_head; a.Hkv = c.n_head_kv; a.hd = hd; a.rope_dims = std::min(c.rope_dims, hd); a.n_kv = o.n_kv;
       a.split_cells = split_cells; a.nsplit = nsplit; a.eps = c.eps; a.rope_off = f.draft ? 1 : 0;
       a.tl = tl();

@@ -40,9 +40,9 @@ struct Graph {
   int4* gprob = nullptr;       // [n_expert] GEMM problem per expert
   int* n_expert_dev = nullptr;
   float* ss_part = nullptr;   // [rows][SS_LD] partial sums of squares of the residual rows
-  float *r_logits = nullptr, *r_probs = nullptr, *topk_w = nullptr, *margin = nullptr;
+  float *r_logits = nullptr, *topk_w = nullptr, *margin = nullptr;
   int32_t *topk = nullptr, *ids_dev = nullptr, *next_ids = nullptr, *history = nullptr;
-  int *attn_tickets = nullptr, *r_ticket = nullptr, *tail_ticket = nullptr, *err_flag = nullptr, *err_host = nullptr, *n_entries = nullptr, *cols = nullptr, *row_slot = nullptr, *row_pos = nullptr, *logit_rows = nullptr, *hist_len = nullptr;
+  int *r_ticket = nullptr, *err_flag = nullptr, *err_host = nullptr, *n_entries = nullptr, *cols = nullptr, *row_slot = nullptr, *row_pos = nullptr, *logit_rows = nullptr, *hist_len = nullptr;
   int4* entries = nullptr;
   SeqDesc* seqs = nullptr;
   float* rope = nullptr;

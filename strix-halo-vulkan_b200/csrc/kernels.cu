@@ -380,7 +380,6 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   }
   tl_mark(p.tl, 4);
   if (p.defer) return;  // the expert kernel selects the experts itself
-  // the last CTA to finish routes every token and builds the expert work list
   // Two levels of tickets: the last CTA of a row group (blockIdx.y) routes that group's eight rows, one
   // per warp; the last group to finish builds the work list of the whole pass.
   __threadfence();
@@ -476,7 +475,7 @@ int launch_moe_gather(const __half* xn, const int* cols, int pairs, int slots1, 
   return launch_k(moe_gather_kernel, dim3(pairs), dim3(256), 0, pdl, st, xn, cols, slots1, H, xperm);
 }
 
-// Stand-alone forms of the row tails, one CTA per row, for passes of more than QG_TAIL_ROWS rows.
+// Row kernels, one CTA per row, for passes of more than QG_FUSED_ROWS rows: RMSNorm, or MoE combine + RMSNorm.
 __global__ void __launch_bounds__(QG_THREADS) row_tail_kernel(TailParams tp) {
   __shared__ float scratch[2 * QG_WARPS];
   pdl_wait();

@@ -85,7 +85,6 @@ struct AttnParams {
   const int* row_slot; const int* row_pos;   // [M]
   __half* q16;                               // [M][Hq][hd]
   float* partial;                            // [M][Hq][nsplit][hd+2]
-  int* tickets;                              // [M][Hkv]
   __half* ctx16;                             // [M][Hq*hd]
   int M, Hq, Hkv, hd, rope_dims, n_kv, split_cells, nsplit;
   int rope_off;                              // rotary position = cell + rope_off (1 for the draft layer)

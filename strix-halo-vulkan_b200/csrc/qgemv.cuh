@@ -30,7 +30,7 @@ namespace b200 {
 constexpr int QG_WARPS = 8;
 constexpr int QG_THREADS = QG_WARPS * 32;
 constexpr int QG_MAXCOLS = 8;
-constexpr int QG_TAIL_ROWS = 8;  // rows the in-kernel tail of the last CTA finishes
+constexpr int QG_FUSED_ROWS = 8;  // passes of at most this many rows fold norms and the MoE combine into the staging of the consumers
 
 enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2 };
 enum { PRO_F16 = 0, PRO_NORM = 1, PRO_COMBINE = 2 };
@@ -368,10 +368,9 @@ __device__ __forceinline__ void block_accumulate(float (&acc)[4], const typename
 }
 
 
-// ---- row-level tails ---------------------------------------------------------------------
-// Executed by one whole CTA (QG_THREADS threads) for one activation row. Used both as the
-// tail of the last CTA of a projection kernel (small passes) and as stand-alone kernels
-// (large passes), so both give bit-identical rows.
+// ---- row-level helpers -------------------------------------------------------------------
+// Executed by one whole CTA (QG_THREADS threads) for one activation row: the row kernels of passes of
+// more than QG_FUSED_ROWS rows, the embedding gather and the draft head's input use them.
 
 // xn[k] = fp16(h[k] * gamma[k] / sqrt(mean(h^2) + eps))   (reference: llm/hc.go:176-190)
 __device__ __forceinline__ void row_rmsnorm_f16(const float* h, const float* gamma, float eps, int H, __half* xn, float* scratch) {
@@ -414,7 +413,7 @@ __device__ __forceinline__ void row_moe_combine(float* h, const float* down, con
   }
 }
 
-// Stand-alone row kernels (row_tail_kernel) for passes of more than QG_TAIL_ROWS rows
+// Row kernels (row_tail_kernel) for passes of more than QG_FUSED_ROWS rows
 struct TailParams {
   int mode;             // 1 rmsnorm, 2 MoE combine + rmsnorm
   float* h;             // [M][H] residual stream

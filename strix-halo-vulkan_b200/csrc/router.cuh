@@ -13,7 +13,7 @@ struct RouterParams {
   const float* sh_gate;                            // [H] F32
   int M, H, nE, used;
   float* logits;       // [M][nE]
-  float* probs;        // [M][nE]
+  float* probs;        // optional [M][nE]: the softmax, for inspection
   int32_t* topk;       // [M][used]
   float* topk_w;       // [M][used+1] (last = sigmoid(shared gate))
   float* margin;       // [M] optional: (p_k - p_{k+1}) / p_k
