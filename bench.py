@@ -24,7 +24,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode step at context 2052, from an ncu capture of the
-# 4-layer prefix scaled to 36 DeltaNet + 12 attention layers + head (profiles/decode_step_a3b_dram_traffic.md):
+# 4-layer prefix (`--profile 1 --layers 4` under ncu's dram byte counters) scaled to 36 DeltaNet + 12 attention layers + head:
 # 36 x 47.28 MB + 12 x 44.70 MB + 255.91 MB. It is 98.6 % of the algorithmic bytes: nothing is read twice.
 A3B_DRAM_BYTES_PER_STEP = 2494.4e6
 PROMPT = 2048
