@@ -198,6 +198,11 @@ def main():
     ap.add_argument("--profile-batch", type=int, default=0, help="run N eager batched decode steps over --slots slots between cudaProfilerStart/Stop and exit")
     ap.add_argument("--profile", type=int, default=0, help="run N eager decode steps between cudaProfilerStart/Stop and exit")
     args = ap.parse_args()
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU legs (rank 0 only) are meant to use every core
+    # the process may run on, and libgomp reads the variable when the oracle library is loaded
+    ncores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    if int(os.environ.get("OMP_NUM_THREADS", "0") or 0) < ncores:
+        os.environ["OMP_NUM_THREADS"] = str(ncores)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
