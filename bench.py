@@ -182,6 +182,27 @@ def cpu_baseline(pkg, model, cfg, tokens=8):
                       f"({times[4] * 1e3:.0f} ms and {times[12] * 1e3:.0f} ms per token)"}
 
 
+def verify_pass_times(pkg, model, cfg, prompt, torch):
+    """MTP speculation: time of one verify pass of 1..5 rows on the trunk through the
+    speculative API (rows written to per-row state planes, then rewound). With random draft and trunk weights
+    acceptance is ~1/vocab, so only the rows -> pass-time ratio is reported, never a speed-up."""
+    g = pkg.Graph(model, n_kv=len(prompt) + 64, max_tokens=512, slots=1, speculative=True, spec_rows=5, use_cuda_graph=False)
+    g.forward(prompt)
+    ids = np.random.default_rng(5).integers(0, cfg["vocab"], 5).astype(np.int32)
+    out = {}
+    for rows in (1, 2, 3, 5):
+        g.speculate(True)
+        for it in range(3 + 12):
+            if it == 3:
+                torch.cuda.synchronize(); t0 = time.perf_counter()
+            g.extend_rows(ids[:rows]); g.rewind()
+        torch.cuda.synchronize()
+        out[str(rows)] = round((time.perf_counter() - t0) / 12 * 1e3, 3)
+        g.speculate(False)
+    return {"verify_pass_ms_by_rows": out, "context": len(prompt),
+            "note": "host-timed through extend_rows (every row's logits copied to the host); rows -> time ratio only"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -318,7 +339,7 @@ def main():
     e2e_s = time.perf_counter() - t0
     e2e_s = max_over_ranks(e2e_s, world)
 
-    # ---- batched multi-slot decode (BASELINE config 3 on one GPU): every slot holds an 8k-32k context ----
+    # ---- batched multi-slot decode on one GPU: every slot holds an 8k-32k context ----
     batch = None
     if args.slots > 0 and args.config == "a3b":
         try:
@@ -327,6 +348,12 @@ def main():
             batch["value"] = whole_job_rate(args.slots, world, batch["ms_per_step"])
         except Exception as e:  # an extra measurement must not lose the headline line
             batch = {"error": str(e)[:200]}
+    spec = None
+    if rank == 0 and args.slots > 0 and args.config == "a3b":
+        try:
+            spec = verify_pass_times(pkg, model, cfg, prompt, torch)
+        except Exception as e:  # an extra measurement must not lose the headline line
+            spec = {"error": str(e)[:200]}
     if rank == 0:
         ms_per_step = dev_ms / steps
         value = whole_job_rate(steps, world, dev_ms)
@@ -352,6 +379,8 @@ def main():
             "gpu_launches": launches * steps,
             "clocks": clocks.summary(),
         }
+        if spec is not None:
+            line["spec"] = spec
         if batch is not None:
             line["batch64"] = batch
         if not args.no_cpu_baseline and world == 1:
