@@ -165,6 +165,9 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
   bool pending = false;     // fused passes: the MoE output of the last layer is not in hc yet; the next
                             // projection of the residual folds it in while staging and writes the other buffer
   int trace_layer = -1;     // layer whose post-MoE residual is still to be traced
+  bool xn_valid = false;    // fused passes of 2..8 rows: a row kernel finished the MoE block and left the next
+                            // layer's normalised fp16 rows in xn16 (reading (used + 1) x M expert rows in every
+                            // CTA's staging costs more than that one launch)
   int comb_used = used;     // what the pending combine adds: comb_used + 1 rows of `down` with weights comb_w
   const float* comb_w = topk_w;
   launches = 0;
@@ -181,7 +184,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
   };
   // a projection of the normalised residual: fused passes normalise while staging, others read xn16
   auto normed = [&](QGemvParams& p, const DTensor& gamma, __half* xn_copy) {
-    if (!fused) return (int)PRO_F16;
+    if (!fused || xn_valid) return (int)PRO_F16;
     p.hsrc = hc; p.gamma = (const float*)gamma.data; p.xn_out = xn_copy;
     if (!pending) { p.ss_in = ss_part; p.ss_n = ss_n; return (int)PRO_NORM; }
     p.down = down; p.topk_w = comb_w; p.used = comb_used; p.h_out = hc == hbuf[0] ? hbuf[1] : hbuf[0];
@@ -315,6 +318,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     if (!fused) B200_TRY(launch_row_tail(row_tail(1, L.ffn_norm), pdl(), st));
     if (o.trace) { B200_CUDA(cudaMemcpyAsync(tr_mid + (size_t)l * MR * H, hc, (size_t)M * H * sizeof(float), cudaMemcpyDeviceToDevice, st)); first = true; }
     // MoE block
+    xn_valid = false;  // the router leaves its own normalised rows in xn16
     RouterParams r{};
     r.xn = xn16; r.router = L.router; r.sh_gate = (const float*)L.sh_gate_inp.data;
     if (fused) { r.h = hc; r.gamma = (const float*)L.ffn_norm.data; r.ss_in = ss_part; r.ss_n = ss_n; r.eps = c.eps; r.xn_out = xn16; }
@@ -383,10 +387,11 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       B200_TRY(launch_qgemv(L.down_exps.type, PRO_F16, EPI_STORE, false, true, q, ne, pdl(), st));
     }
     }
-    if (fused) pending = true;
+    if (fused && M == 1) pending = true;
     else {
       const DTensor& next_norm = f.draft ? L.head_norm : (l + 1 < c.n_layer ? m->layers[l + 1].attn_norm : m->output_norm);
       B200_TRY(launch_row_tail(row_tail(2, next_norm), pdl(), st));
+      xn_valid = fused;
     }
     if (o.trace) {
       if (fused && pending) trace_layer = l;
