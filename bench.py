@@ -213,7 +213,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--slots", type=int, default=64, help="also time batched decode over this many slots (0 = skip)")
     ap.add_argument("--prompt", type=int, default=0, help="override the prompt length (profiling runs)")
-    ap.add_argument("--chunk", type=int, default=512, help="rows per prefill pass (the graph's max_tokens)")
+    ap.add_argument("--chunk", type=int, default=2048, help="rows per prefill pass (the graph's max_tokens)")
     ap.add_argument("--layers", type=int, default=0, help="keep only the first N layers (small cases for profiler captures)")
     ap.add_argument("--profile-prefill", type=int, default=0, help="run one prefill pass of N rows between cudaProfilerStart/Stop and exit")
     ap.add_argument("--profile-batch", type=int, default=0, help="run N eager batched decode steps over --slots slots between cudaProfilerStart/Stop and exit")

@@ -49,7 +49,8 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   if (o.n_kv <= 0) { set_error("graph: n_kv must be positive"); return EINVAL_; }
   if (o.speculative && o.spec_rows <= 0) o.spec_rows = 3;
   if (o.spec_rows > DN_RING - 3) { set_error("graph: spec_rows is limited to 5 (the conv ring keeps 8 positions)"); return ECAPACITY; }
-  MR = std::min(o.max_tokens, 512);
+  MR = std::min(o.max_tokens, 2048);   // rows per pass (the attention kernel keeps per-row split partials)
+  LR = std::min(MR, 512);              // rows whose logits a pass can return
   // a CTA's four warps take 16 cells each per round; longer contexts get longer splits so the merge stays short
   split_cells = o.attn_split_cells > 0 ? (o.attn_split_cells + 15) / 16 * 16 : (o.n_kv <= 4096 ? 64 : o.n_kv <= 8192 ? 128 : o.n_kv <= 16384 ? 256 : 512);
   nsplit = (o.n_kv + split_cells - 1) / split_cells;
@@ -75,7 +76,7 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   B200_TRY(dalloc(&entries, (size_t)max_entries)); B200_TRY(dalloc(&n_entries, 1)); B200_TRY(dalloc(&cols, (size_t)MR * slots1));
   B200_TRY(dalloc(&r_ticket, (size_t)2 + MR / 8)); B200_TRY(dalloc(&err_flag, 1)); B200_TRY(dalloc(&ss_part, (size_t)MR * SS_LD)); B200_TRY(dalloc(&y16, (size_t)MR * vw));
   B200_TRY(dalloc(&act16, (size_t)MR * slots1 * c.ffn_expert)); B200_TRY(dalloc(&down, (size_t)MR * slots1 * H));
-  B200_TRY(dalloc(&logits, (size_t)MR * c.vocab));
+  B200_TRY(dalloc(&logits, (size_t)LR * c.vocab));
   { B200_TRY(dalloc(&dn_pre, (size_t)c.dn_heads_v * 4 * MR * 292)); B200_TRY(dalloc(&dn_oraw, (size_t)MR * vw)); }
   { const float one[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f}; B200_TRY(dalloc(&ones, 8)); B200_CUDA(cudaMemcpy(ones, one, sizeof(one), cudaMemcpyHostToDevice)); }
   B200_TRY(dalloc(&xperm16, (size_t)MR * used * H)); B200_TRY(dalloc(&gprob, (size_t)c.n_expert)); B200_TRY(dalloc(&n_expert_dev, 1));
@@ -128,7 +129,7 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   // host staging
   stage_bytes = (size_t)MR * (4 * sizeof(int32_t) + sizeof(SeqDesc));
   B200_CUDA(cudaMallocHost((void**)&stage, stage_bytes));
-  B200_CUDA(cudaMallocHost((void**)&logits_host, (size_t)MR * c.vocab * sizeof(float)));
+  B200_CUDA(cudaMallocHost((void**)&logits_host, (size_t)LR * c.vocab * sizeof(float)));
   B200_CUDA(cudaMallocHost((void**)&resid_host, (size_t)MR * H * sizeof(float)));
   B200_CUDA(cudaMallocHost((void**)&hidden_host, (size_t)H * sizeof(float)));
   B200_CUDA(cudaMallocHost((void**)&err_host, sizeof(int)));
@@ -504,7 +505,7 @@ int Graph::extend(const int32_t* ids, int n, const PassFlags& f, const float** l
     if (!o.speculative) { set_error("extend: the graph was not created with speculative = 1"); return ESTATE; }
     if (n > o.spec_rows) { set_error("extend: a speculative pass holds at most spec_rows rows"); return ECAPACITY; }
   }
-  if (f.want_all_logits && n > MR) { set_error("extend_rows: more rows than max_tokens"); return ECAPACITY; }
+  if (f.want_all_logits && n > LR) { set_error("extend_rows: more rows than max_tokens (logits of at most 512 rows per pass)"); return ECAPACITY; }
   if (f.want_residual && n > MR) { set_error("extend_residual: more rows than max_tokens"); return ECAPACITY; }
   if (past[cur] + n > o.n_kv) { set_error("extend: the slot's context is full (" + std::to_string(past[cur]) + " + " + std::to_string(n) + " > " + std::to_string(o.n_kv) + ")"); return ECAPACITY; }
   resid_off = 0;
@@ -528,7 +529,7 @@ int Graph::extend(const int32_t* ids, int n, const PassFlags& f, const float** l
 
 int Graph::decode_rows(const int32_t* slots_in, const int32_t* ids, int n, const float** logits_out) {
   // one token for each of n distinct slots (reference: llm/batch.go:45-63)
-  if (n <= 0 || n > MR) { set_error("decode_rows: 1.." + std::to_string(MR) + " rows"); return ECAPACITY; }
+  if (n <= 0 || n > LR) { set_error("decode_rows: 1.." + std::to_string(LR) + " rows"); return ECAPACITY; }
   std::vector<int> slots(n), pos(n), lrows(n);
   std::vector<SeqDesc> sq(n);
   std::vector<char> seen(o.slots, 0);
@@ -549,7 +550,7 @@ int Graph::decode_rows(const int32_t* slots_in, const int32_t* ids, int n, const
 
 int Graph::generate_greedy(const int32_t* slots_in, const int32_t* first, int n, int steps, int32_t* out) {
   const b200_config& c = m->c;
-  if (n <= 0 || n > MR) { set_error("generate_greedy: 1.." + std::to_string(MR) + " rows"); return ECAPACITY; }
+  if (n <= 0 || n > LR) { set_error("generate_greedy: 1.." + std::to_string(LR) + " rows"); return ECAPACITY; }
   if (steps <= 0 || steps > 4096) { set_error("generate_greedy: 1..4096 steps per call"); return ECAPACITY; }
   std::vector<int> slots(n), pos(n), lrows(n);
   std::vector<SeqDesc> sq(n);
@@ -602,7 +603,7 @@ int Graph::generate_greedy(const int32_t* slots_in, const int32_t* first, int n,
 int Graph::draft_rows(const float* hs, const int32_t* ids, int n, int vocab_k, const float** resid, const float** logits_out) {
   const b200_config& c = m->c;
   if (!c.has_draft) { set_error("draft_rows: the checkpoint has no draft layer"); return ESTATE; }
-  if (n <= 0 || n > MR) { set_error("draft_rows: row count out of range"); return ECAPACITY; }
+  if (n <= 0 || n > LR) { set_error("draft_rows: row count out of range"); return ECAPACITY; }
   if (vocab_k <= 0 || vocab_k > c.vocab) vocab_k = c.vocab;
   if (vocab_k % 16) { set_error("draft_rows: vocab_k must be a multiple of 16"); return EINVAL_; }
   if (draft_past[cur] + n + 1 > o.n_kv) { set_error("draft_rows: the draft cache is full"); return ECAPACITY; }

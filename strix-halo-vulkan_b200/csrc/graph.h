@@ -24,6 +24,7 @@ struct Graph {
   cudaStream_t st = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   int MR = 0;           // rows per pass
+  int LR = 0;           // rows whose logits one pass can return
   int n_dn = 0, n_attn = 0;
   std::vector<int> dn_index, attn_index;  // layer -> index among its kind (draft layer = last attention)
   // activations

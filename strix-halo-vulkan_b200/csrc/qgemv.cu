@@ -22,7 +22,7 @@ static int launch_one(const QGemvParams& p, int max_entries, bool pdl, cudaStrea
   const int ny = GROUPED ? max_entries : 1, nz = GROUPED ? 1 : (p.M + QG_MAXCOLS - 1) / QG_MAXCOLS;
   // As many CTAs per SM (up to three: 80 registers per thread) as still leave each a ring of two stages, or of
   // one when it has a single group to walk: more resident warps hide the dequantisation's latencies, and a
-  // grid that fits at once needs no second round. Three per SM only for the expert kernels: elsewhere the register cap costs more than
+  // grid that fits at once needs no second round. Three per SM only for the expert kernels and the Q6_K ones (the head's long walk): elsewhere the register cap costs more than
   // the extra warps give, and every CTA of a projection reads the same activation rows out of L2 - the more
   // CTAs ask at once the longer each waits. Persistent CTAs share the device between the y / z slices.
   const size_t fixed = qg_fixed_smem(p.K, p.xcols, DUAL), stage = qg_stage_bytes(p.K, p.stride, DUAL);
@@ -30,7 +30,7 @@ static int launch_one(const QGemvParams& p, int max_entries, bool pdl, cudaStrea
   if (fixed + stage > budgets[1]) { set_error("qgemv: row length too large for shared memory"); return ECAPACITY; }
   int occ = 1, rounds = 1, gx = 1;
   for (int o = 3; o >= 1; o--) {
-    if (o == 3 && !GROUPED) continue;  // the plain kernels are compiled for two CTAs per SM
+    if (o == 3 && !GROUPED && TYPE != T_Q6_K) continue;  // the other plain kernels are compiled for two CTAs per SM
     int cap = g_sm_count * o / (ny * nz);
     if (cap < 1) cap = 1;
     // every CTA walks the same number of groups (a ragged last round leaves most SMs idle)

@@ -614,7 +614,7 @@ __device__ __forceinline__ void stage_x_combine(const QGemvParams& p, uint8_t* x
 // checkpoint's own blocks) through cp.async.bulk into a ring of shared-memory stages, each
 // completing on its mbarrier, so many tiles are in flight per SM without holding registers.
 template <int TYPE, int PRO, int EPI, bool DUAL, bool GROUPED>
-__global__ void __launch_bounds__(QG_THREADS, GROUPED ? 3 : 2) qgemv_kernel(const QGemvParams p) {
+__global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 2) qgemv_kernel(const QGemvParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int K = p.K, nb = K / 256;
