@@ -303,7 +303,11 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       a.kcache = kcache[ai]; a.vcache = vcache[ai]; a.slot_stride = kv_slot_stride; a.row_slot = row_slot; a.row_pos = row_pos;
       a.q16 = q16; a.partial = attn_partial; a.ctx16 = ctx16;
       a.M = M; a.Hq = c.n_head; a.Hkv = c.n_head_kv; a.hd = hd; a.rope_dims = std::min(c.rope_dims, hd); a.n_kv = o.n_kv;
-      a.split_cells = split_cells; a.nsplit = nsplit; a.eps = c.eps; a.rope_off = f.draft ? 1 : 0;
+      // many rows: longer splits while the grid still fills the device several times over (fewer partial
+      // results to write and merge); the buffer is sized for the shortest split
+      int sc = split_cells;
+      if (o.attn_split_cells <= 0) while (sc < 2048 && (int64_t)M * c.n_head_kv * ((o.n_kv + sc - 1) / sc) >= 4096) sc *= 2;
+      a.split_cells = sc; a.nsplit = (o.n_kv + sc - 1) / sc; a.eps = c.eps; a.rope_off = f.draft ? 1 : 0;
       a.tl = tl();
       B200_TRY(launch_attn_pack(a, pdl(), st));
       a.tl = tl();
