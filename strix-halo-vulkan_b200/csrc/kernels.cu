@@ -1079,6 +1079,158 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(AttnParams p) {
   tl_mark(p.tl, 4);
 }
 
+// -----------------------------------------------------------------------------------------
+// Long-split form of the same kernel: eight warps, and the key and value rows reach shared memory by
+// bulk copies (one per 16-cell tile row, completing on an mbarrier) instead of passing through registers.
+// A warp owns a ring of three tile slots and keeps a whole block (16 keys + 16 values) in flight ahead of
+// the block it computes on, so the bytes in flight per SM no longer depend on registers or on which phase
+// the warps are in. Row pitches are padded (keys +64 bytes, values +16) so the 16-byte fragment reads of
+// a quarter warp fall on distinct banks. Arithmetic and fragment layout are those of attn_mma_kernel.
+// -----------------------------------------------------------------------------------------
+template <int HD, int G>
+__global__ void __launch_bounds__(256, 1) attn_ring_kernel(AttnParams p) {
+  constexpr int KS = HD / 16, NB = HD / 64, NW = 8, NSLOT = 3;
+  constexpr int KP = HD * 2 + 64, VP = HD * 2 + 16;  // row pitches in bytes
+  constexpr int SLOT = 16 * KP;                      // a slot holds the key or the value rows of 16 cells
+  extern __shared__ __align__(128) uint8_t ar_ring[];  // [NW][NSLOT][SLOT]; reused for the warps' outputs at the end
+  __shared__ uint64_t bars[NW][NSLOT];
+  __shared__ float sm_m[NW][G], sm_l[NW][G];
+  const int split = blockIdx.x, kvh = blockIdx.y, n = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  tl_mark(p.tl, 0);
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < NSLOT; s++) mbar_init(&bars[warp][s], 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  pdl_wait();
+  pdl_launch();
+  tl_mark(p.tl, 1);
+  const int pos = p.row_pos[n], slot = p.row_slot[n];
+  const int ncell = pos + 1;
+  const int c0 = split * p.split_cells, c1 = min(ncell, c0 + p.split_cells);
+  const float scale = 1.0f / sqrtf((float)HD);
+  const size_t cell_stride = (size_t)p.Hkv * HD;
+  const __half* kbase = p.kcache + (size_t)slot * p.slot_stride + (size_t)kvh * HD;
+  const __half* vbase = p.vcache + (size_t)slot * p.slot_stride + (size_t)kvh * HD;
+  uint8_t* ring = ar_ring + (size_t)warp * NSLOT * SLOT;
+  const int cb0 = c0 + warp * 16;
+  // tile j of this warp: keys (j even) or values (j odd) of block j / 2, in slot j % 3
+  auto issue = [&](int j) {
+    const int cb = cb0 + (NW * 16) * (j >> 1);
+    if (cb >= c1) return;
+    const bool isv = j & 1;
+    uint64_t* bar = &bars[warp][j % NSLOT];
+    uint8_t* dst = ring + (j % NSLOT) * SLOT;
+    if (lane == 0) mbar_expect_tx(bar, 16 * HD * 2);
+    __syncwarp();  // every lane is done with the slot's previous tile, and the byte count is posted
+    if (lane < 16) {
+      const int row = min(cb + lane, c1 - 1);  // clamped rows are masked below
+      bulk_copy_g2s(dst + lane * (isv ? VP : KP), (isv ? vbase : kbase) + (size_t)row * cell_stride, HD * 2, bar);
+    }
+  };
+  issue(0); issue(1); issue(2);
+  uint32_t qa[KS][2];
+#pragma unroll
+  for (int j = 0; j < KS / 2; j++) {
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (g < G) v = *reinterpret_cast<const uint4*>(p.q16 + ((size_t)n * p.Hq + kvh * G + g) * HD + 8 * (t + 4 * j));
+    qa[2 * j][0] = v.x; qa[2 * j][1] = v.y; qa[2 * j + 1][0] = v.z; qa[2 * j + 1][1] = v.w;
+  }
+  float o[HD / 8][2];
+#pragma unroll
+  for (int i = 0; i < HD / 8; i++) { o[i][0] = 0.f; o[i][1] = 0.f; }
+  float m = -INFINITY, l = 0.f;
+  bool lost = false;
+  for (int i = 0, cb = cb0; cb < c1; i++, cb += NW * 16) {
+    // ---- scores of 16 cells ----
+    const int jk = 2 * i, jv = 2 * i + 1;
+    if (!mbar_wait(&bars[warp][jk % NSLOT], (jk / NSLOT) & 1)) { lost = true; break; }
+    const uint8_t* kt = ring + (jk % NSLOT) * SLOT + g * KP + t * 16;
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < KS / 2; j++) {
+      const uint4 ka = lds128(kt + j * 64), kb = lds128(kt + 8 * KP + j * 64);
+      const uint32_t a0[4] = {qa[2 * j][0], 0u, qa[2 * j][1], 0u}, a1[4] = {qa[2 * j + 1][0], 0u, qa[2 * j + 1][1], 0u};
+      mma16816(s0, a0, ka.x, ka.y);
+      mma16816(s0, a1, ka.z, ka.w);
+      mma16816(s1, a0, kb.x, kb.y);
+      mma16816(s1, a1, kb.z, kb.w);
+    }
+    issue(jk + 3);  // the next block's values, into the slot the keys just left
+    // row g, cells cb + 2t, +1 (tile 0) and cb + 8 + 2t, +1 (tile 1)
+    float sc[4] = {s0[0] * scale, s0[1] * scale, s1[0] * scale, s1[1] * scale};
+    const int cell[4] = {cb + 2 * t, cb + 2 * t + 1, cb + 8 + 2 * t, cb + 9 + 2 * t};
+#pragma unroll
+    for (int u = 0; u < 4; u++) if (cell[u] >= c1) sc[u] = -INFINITY;
+    float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float mn = fmaxf(m, mx);                       // finite: a block always holds at least one live cell
+    const float corr = expf(m - mn);
+    float pv[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) pv[u] = expf(sc[u] - mn);
+    l = l * corr + ((pv[0] + pv[1]) + (pv[2] + pv[3]));
+    m = mn;
+    const uint32_t pa[4] = {pack_half2(pv[0], pv[1]), 0u, pack_half2(pv[2], pv[3]), 0u};
+    // ---- O = O * corr + P V ----
+    if (!mbar_wait(&bars[warp][jv % NSLOT], (jv / NSLOT) & 1)) { lost = true; break; }
+    const uint8_t* vt = ring + (jv % NSLOT) * SLOT + (2 * t) * VP + g * 16;
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+      const uint4 wa = lds128(vt + b * 128), wb = lds128(vt + VP + b * 128), wc = lds128(vt + 8 * VP + b * 128), wd = lds128(vt + 9 * VP + b * 128);
+      const uint32_t ra[4] = {wa.x, wa.y, wa.z, wa.w}, rb[4] = {wb.x, wb.y, wb.z, wb.w}, rc[4] = {wc.x, wc.y, wc.z, wc.w}, rd[4] = {wd.x, wd.y, wd.z, wd.w};
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float acc_e[4] = {o[b * 8 + 2 * j][0] * corr, o[b * 8 + 2 * j][1] * corr, 0.f, 0.f};
+        float acc_o[4] = {o[b * 8 + 2 * j + 1][0] * corr, o[b * 8 + 2 * j + 1][1] * corr, 0.f, 0.f};
+        mma16816(acc_e, pa, __byte_perm(ra[j], rb[j], 0x5410), __byte_perm(rc[j], rd[j], 0x5410));
+        mma16816(acc_o, pa, __byte_perm(ra[j], rb[j], 0x7632), __byte_perm(rc[j], rd[j], 0x7632));
+        o[b * 8 + 2 * j][0] = acc_e[0]; o[b * 8 + 2 * j][1] = acc_e[1];
+        o[b * 8 + 2 * j + 1][0] = acc_o[0]; o[b * 8 + 2 * j + 1][1] = acc_o[1];
+      }
+    }
+    issue(jv + 3);  // the keys two blocks ahead, into the slot the values just left
+  }
+  if (lost && p.err != nullptr && lane == 0) atomicExch(p.err, 1);  // a copy never landed: report; the result is void
+  // row sums live as per-lane partials over the four t lanes
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+  __syncthreads();  // every warp has consumed what it issued: the ring becomes the warps' output buffer
+  float (*sm_o)[G][HD] = reinterpret_cast<float (*)[G][HD]>(ar_ring);
+  if (g < G) {
+    if (t == 0) { sm_m[warp][g] = m; sm_l[warp][g] = l; }
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        sm_o[warp][g][8 * (2 * t + 8 * b) + i] = o[b * 8 + i][0];
+        sm_o[warp][g][8 * (2 * t + 1 + 8 * b) + i] = o[b * 8 + i][1];
+      }
+    }
+  }
+  __syncthreads();
+  const int PW = HD + 2;
+  for (int i = tid; i < G * HD; i += 256) {
+    const int hh = i / HD, d = i - hh * HD;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NW; w++) mm = fmaxf(mm, sm_m[w][hh]);
+    float ov = 0.f, lv = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; w++) {
+      const float f = sm_m[w][hh] == -INFINITY ? 0.f : expf(sm_m[w][hh] - mm);
+      ov += sm_o[w][hh][d] * f; lv += sm_l[w][hh] * f;
+    }
+    float* part = p.partial + (((size_t)n * p.Hq + kvh * G + hh) * p.nsplit + split) * PW;
+    part[d] = ov;
+    if (d == 0) { part[HD] = mm; part[HD + 1] = lv; }
+  }
+  tl_mark(p.tl, 4);
+}
+
 // Merge of the splits: O = sum_s O_s * exp(m_s - m*), divide by the merged row sum, times
 // sigmoid(gate), to fp16 (reference: shaders/llm_attn_combine.comp:43-102). grid (Hq, M), block hd.
 __global__ void attn_merge_kernel(AttnParams p) {
@@ -1130,6 +1282,18 @@ int launch_attn_decode(const AttnParams& p, bool pdl, cudaStream_t st) {
   const int G = p.Hq / p.Hkv;
   dim3 grid(p.nsplit, p.Hkv, p.M), block(128);
   int s;
+  if (p.split_cells >= 256 && ((p.hd == 256 && G == 8) || (p.hd == 128 && G == 4))) {
+    // long splits: eight warps fed by bulk copies
+    static bool configured = false;
+    const size_t smem = (size_t)8 * 3 * 16 * (p.hd * 2 + 64);
+    if (!configured) {
+      B200_CUDA(cudaFuncSetAttribute(attn_ring_kernel<256, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * 16 * (256 * 2 + 64)));
+      B200_CUDA(cudaFuncSetAttribute(attn_ring_kernel<128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * 16 * (128 * 2 + 64)));
+      configured = true;
+    }
+    return p.hd == 256 ? launch_k(attn_ring_kernel<256, 8>, grid, dim3(256), smem, pdl, st, p)
+                       : launch_k(attn_ring_kernel<128, 4>, grid, dim3(256), smem, pdl, st, p);
+  }
   if (p.hd == 256 && G == 8) s = launch_k(attn_mma_kernel<256, 8>, grid, block, 0, pdl, st, p);
   else if (p.hd == 128 && G == 4) s = launch_k(attn_mma_kernel<128, 4>, grid, block, 0, pdl, st, p);
   else if (p.hd == 128 && G == 8) s = launch_k(attn_mma_kernel<128, 8>, grid, block, 0, pdl, st, p);

@@ -89,6 +89,7 @@ struct AttnParams {
   int M, Hq, Hkv, hd, rope_dims, n_kv, split_cells, nsplit;
   int rope_off;                              // rotary position = cell + rope_off (1 for the draft layer)
   float eps;
+  int* err;                                  // device error word: set when a bounded wait gives up
   Timeline tl;
 };
 int launch_attn_pack(const AttnParams& p, bool pdl, cudaStream_t st);

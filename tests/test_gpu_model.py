@@ -128,6 +128,31 @@ def test_long_pass_on_the_tensor_cores_is_the_few_row_schedule(pkg, tiny):
     assert r["max_abs"] <= 5e-2 * r["ref_max"], r
 
 
+def test_long_attention_splits_are_the_short_ones(pkg, tiny):
+    """Splits of 256 cells and more run on the bulk-copy-fed attention kernel: same logits as 64-cell splits
+    and as the oracle, for ragged ends and for decode steps. Between split lengths the running maximum that the
+    fp16 probabilities are rounded against differs, so the two schedules agree to 1e-3 of the largest logit."""
+    cfg = tiny["cfg"]
+    ids = prompt(cfg, 333, seed=11)
+    seq = tiny["oracle"].seq()
+    want, _ = seq.extend(ids)
+    outs = []
+    for split in (64, 256, 512):
+        g = pkg.Graph(tiny["model"], n_kv=400, max_tokens=64, attn_split_cells=split, use_cuda_graph=False)
+        logits, _ = g.forward(ids)
+        assert_close(logits, want, f"prefill logits at split {split}")
+        steps = [logits]
+        for tok in (5, 17, 4093):
+            steps.append(g.extend([tok])[0])
+        outs.append(steps)
+    for tok in (5, 17, 4093):
+        want, _ = seq.extend([tok])
+    assert_close(outs[1][-1], want, "decode logits at split 256")
+    for other in outs[1:]:
+        for a, b in zip(outs[0], other):
+            assert_close(b, a, "long splits against short ones", tol=1e-3)
+
+
 def test_decode_rows_is_each_slot(pkg, tiny):
     # llm/graph_batch_test.go TestGraphDecodeRowsIsEachSlot: batched == solo. A single row sums its experts'
     # down projections inside one kernel (per warp, then per rank), a pass of several rows in the consumer's
