@@ -683,6 +683,147 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(128, MINB) dn_step_k
 }
 
 // -----------------------------------------------------------------------------------------
+// Many sequences of one or a few tokens (batched decode): one CTA of sixteen warps per (value head,
+// sequence) instead of a cluster of four. The alpha / beta projections and the q / k convolutions are
+// computed once per head rather than once per row block, the gated norm's sum of squares is a
+// shared-memory reduction rather than a cluster barrier, and the state rows, the conv rings and the
+// grouping of every partial sum are those of dn_step_kernel (warp W here is warp W % 4 of row block W / 4).
+// -----------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(512, 2) dn_head_kernel(DnStepParams p) {
+  const int D = 128, RB = 4;
+  const int h = blockIdx.x, hk = h % p.Hk;
+  const SeqDesc sq = p.seqs[blockIdx.y];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qk = p.Hk * D, H = p.H;
+  __shared__ float qs[128], ks[128], vs[128], red[40], wss[16];
+  // conv roles: threads 0..127 the q channels, 128..255 k, 256..383 the head's v channels; the rest idle there
+  const int role = tid >> 7, c = tid & 127;
+  const int ch = role == 0 ? hk * D + c : role == 1 ? qk + hk * D + c : 2 * qk + h * D + c;
+  // ring of row block rb: [pos][q 128 | k 128 | v 32]; q and k are kept in all four, read from the first
+  float* ring0 = p.ring + (size_t)sq.slot * p.ring_slot_stride + (size_t)(h * RB) * (DN_RING * DN_RING_W);
+  const int ring_off = role == 0 ? c : role == 1 ? 128 + c : (c >> 5) * (DN_RING * DN_RING_W) + 256 + (c & 31);
+  float4 cw = make_float4(0.f, 0.f, 0.f, 0.f);
+  float hist[3] = {0.f, 0.f, 0.f};
+  if (role < 3) {
+    cw = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch * 4);
+#pragma unroll
+    for (int j = 0; j < 3; j++) {
+      const int pos = sq.pos0 - 3 + j;
+      hist[j] = pos >= 0 ? ring0[(size_t)(pos & (DN_RING - 1)) * DN_RING_W + ring_off] : 0.f;
+    }
+  }
+  const float a_h = p.ssm_a[h], dtb = p.dt_bias[h];
+  // state rows of this warp: j = warp*8 + r, four floats per lane
+  float* S = p.state + (size_t)sq.slot * p.state_slot_stride + (size_t)h * D * D;
+  const int j0 = warp * 8;
+  float4 s[8];
+#pragma unroll
+  for (int r = 0; r < 8; r++) s[r] = *reinterpret_cast<const float4*>(S + (size_t)(j0 + r) * D + lane * 4);
+  const float oscale = 1.0f / sqrtf((float)D);
+  tl_mark(p.tl, 0);
+  pdl_wait();
+  pdl_launch();
+  tl_mark(p.tl, 1);
+
+  for (int i = 0; i < sq.n; i++) {
+    const int row = sq.row0 + i, pos = sq.pos0 + i;
+    const float* pr = p.proj + (size_t)row * p.ldp;
+    const __half* xn = p.xn + (size_t)row * H;
+    float pa = 0.f, pb = 0.f;
+    for (int k = tid * 4; k < H; k += 2048) {
+      const float4 wa = *reinterpret_cast<const float4*>(p.alpha_w + (size_t)h * H + k), wb = *reinterpret_cast<const float4*>(p.beta_w + (size_t)h * H + k);
+      const __half2 x01 = *reinterpret_cast<const __half2*>(xn + k), x23 = *reinterpret_cast<const __half2*>(xn + k + 2);
+      const float2 f01 = __half22float2(x01), f23 = __half22float2(x23);
+      pa += wa.x * f01.x + wa.y * f01.y + wa.z * f23.x + wa.w * f23.y;
+      pb += wb.x * f01.x + wb.y * f01.y + wb.z * f23.x + wb.w * f23.y;
+    }
+    float cv = 0.f, act = 0.f;
+    if (role < 3) {
+      cv = pr[ch];
+      act = silu_acc(hist[0] * cw.x + hist[1] * cw.y + hist[2] * cw.z + cv * cw.w);
+      hist[0] = hist[1]; hist[1] = hist[2]; hist[2] = cv;
+      // the rings keep every token's conv input by position (rollback = moving `past` back)
+      float* rw = ring0 + (size_t)(pos & (DN_RING - 1)) * DN_RING_W + ring_off;
+      if (role == 2) rw[0] = cv;
+      else {
+#pragma unroll
+        for (int rb = 0; rb < RB; rb++) rw[(size_t)rb * (DN_RING * DN_RING_W)] = cv;
+      }
+    }
+    const float a2 = warp_sum(act * act);  // warps 0..3: q, 4..7: k
+    pa = warp_sum(pa); pb = warp_sum(pb);
+    __syncthreads();
+    if (lane == 0) { red[warp] = pa; red[16 + warp] = pb; if (warp < 8) red[32 + warp] = a2; }
+    if (role == 2) vs[c] = act;
+    __syncthreads();
+    const float qn = 1.0f / sqrtf(red[32] + red[33] + red[34] + red[35] + p.eps);
+    const float kn = 1.0f / sqrtf(red[36] + red[37] + red[38] + red[39] + p.eps);
+    float alpha = 0.f, betar = 0.f;
+#pragma unroll
+    for (int w = 0; w < 16; w++) { alpha += red[w]; betar += red[16 + w]; }
+    if (role == 0) qs[c] = act * qn;
+    if (role == 1) ks[c] = act * kn;
+    __syncthreads();
+    const float g = expf(softplus_ref(alpha + dtb) * a_h);
+    const float beta = sigmoid_acc(betar);
+    const float4 k4 = *reinterpret_cast<const float4*>(ks + lane * 4);
+    const float4 q4 = *reinterpret_cast<const float4*>(qs + lane * 4);
+    float kv[8], oo[8];
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+      s[r].x *= g; s[r].y *= g; s[r].z *= g; s[r].w *= g;
+      kv[r] = s[r].x * k4.x + s[r].y * k4.y + s[r].z * k4.z + s[r].w * k4.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int r = 0; r < 8; r++) kv[r] += __shfl_xor_sync(0xffffffffu, kv[r], o);
+    }
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+      const float dj = (vs[j0 + r] - kv[r]) * beta;
+      s[r].x += dj * k4.x; s[r].y += dj * k4.y; s[r].z += dj * k4.z; s[r].w += dj * k4.w;
+      oo[r] = s[r].x * q4.x + s[r].y * q4.y + s[r].z * q4.z + s[r].w * q4.w;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int r = 0; r < 8; r++) oo[r] += __shfl_xor_sync(0xffffffffu, oo[r], o);
+    }
+    // gated norm: sum of squares over the head's 128 outputs, warp partials grouped by four as the row blocks were
+    float ov = oo[0] * oscale, ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+      const float orr = oo[r] * oscale;
+      ss += orr * orr;
+      ov = lane == r ? orr : ov;
+    }
+    if (lane == 0) wss[warp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int rb = 0; rb < RB; rb++) tot += wss[4 * rb] + wss[4 * rb + 1] + wss[4 * rb + 2] + wss[4 * rb + 3];
+    if (lane < 8) {
+      const int j = j0 + lane;
+      const float nsc = 1.0f / sqrtf(tot / (float)D + p.eps);
+      const float zz = pr[2 * qk + p.Hv * D + h * D + j];
+      p.y16[(size_t)row * (p.Hv * D) + h * D + j] = __float2half_rn(ov * nsc * p.norm_w[j] * sigmoid_acc(zz));
+    }
+    if (p.mid != nullptr) {  // state after token i, for keep-prefix speculation
+      float* Sm = p.mid + (size_t)blockIdx.y * p.mid_seq_stride + (size_t)i * p.mid_stride + (size_t)h * D * D;
+#pragma unroll
+      for (int r = 0; r < 8; r++) *reinterpret_cast<float4*>(Sm + (size_t)(j0 + r) * D + lane * 4) = s[r];
+    }
+    __syncthreads();
+  }
+  if (p.mid == nullptr) {
+#pragma unroll
+    for (int r = 0; r < 8; r++) *reinterpret_cast<float4*>(S + (size_t)(j0 + r) * D + lane * 4) = s[r];
+  }
+  tl_mark(p.tl, 4);
+}
+
+// -----------------------------------------------------------------------------------------
 // The same layer for sequences of many tokens (prefill), as three kernels: everything that does not
 // depend on the recurrent state (alpha / beta, conv + SiLU, L2 norms, gates) is computed for all tokens
 // in parallel and packed per (head, row block) and token; the scan then walks the tokens with no
@@ -874,7 +1015,7 @@ int launch_dn_scan(const DnStepParams& p, int M, int max_n, bool pdl, cudaStream
 
 int launch_dn_step(const DnStepParams& p, bool pdl, cudaStream_t st) {
   if (p.D != 128 || p.conv != 4) { set_error("dn_step: head dim must be 128 and conv kernel 4"); return EINVAL_; }
-  if (p.n_seq >= 16) return launch_k(dn_step_kernel<6>, dim3(p.Hv * 4, p.n_seq), dim3(128), 0, pdl, st, p);
+  if (p.n_seq >= 16) return launch_k(dn_head_kernel, dim3(p.Hv, p.n_seq), dim3(512), 0, pdl, st, p);
   return launch_k(dn_step_kernel<1>, dim3(p.Hv * 4, p.n_seq), dim3(128), 0, pdl, st, p);
 }
 

@@ -86,5 +86,16 @@ def test_sixteen_slots_batched_match_solo(pkg, a3b4):
         assert int(np.argmax(batched[s])) == int(np.argmax(solo[s])) or logit_gap(solo[s]) < NEAR_TIE
     # the device-resident loop over all 16 slots emits what the host loop picks
     first = [int(np.argmax(b)) for b in batched]
+    # second step: the states and conv histories that the 16-row pass left are read by single-row passes
+    # (a different DeltaNet kernel) and by another 16-row pass alike
+    solo2 = []
+    for s in range(16):
+        g.use_slot(s)
+        ck = g.checkpoint()
+        lg, _ = g.extend([first[s]]); solo2.append(lg)
+        g.restore(ck); g.checkpoint_free(ck)
+    batched2 = g.decode_rows(list(range(16)), np.asarray(first, np.int32))
+    for s in range(16):
+        assert_close(batched2[s], solo2[s], f"second step, slot {s}", tol=2e-3)
     out = g.generate_greedy(list(range(16)), first, 3)
     assert out.shape == (3, 16)
