@@ -334,13 +334,15 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     // rows (below that the column-tiled kernel, which streams each expert's weights in whole tiles, is faster)
     const bool moe_gemm = use_gemm && (int64_t)M * used >= 32 * (int64_t)c.n_expert && L.gate_exps.type == L.gate_sh.type && L.down_exps.type == L.down_sh.type;
     r.gprob = moe_gemm ? gprob : nullptr;
-    if (use_gemm && M >= 256 && L.router.type == T_Q8_0) {
+    if (use_gemm && M >= 64 && L.router.type == T_Q8_0) {
       // many rows: the router logits are one more tensor-core GEMM (the reference's prefill router is an fp16
       // GEMM too: llm_gemm MODE 2 + llm_moe_route), selection and work list in a kernel of their own
       QGemmParams g{};
       g.w = L.router.data; g.one = GemmProblem{0, 0, M, 0}; g.max_problems = 1; g.max_count = M; g.stride = L.router.stride;
       g.K = H; g.N = c.n_expert; g.y = r_logits; g.ldy = c.n_expert; g.err = err_flag;
-      B200_TRY(launch_qgemm(T_Q8_0, GEMM_STORE, 64, g, tm_xn[0], pdl(), st));
+      // up to a few hundred rows the four 128-expert tiles leave the device idle: column-tiled mma instead
+      if (M < 256 && router_mma_fits(r)) { B200_TRY(launch_router_mma(r, pdl(), st)); }
+      else B200_TRY(launch_qgemm(T_Q8_0, GEMM_STORE, 64, g, tm_xn[0], pdl(), st));
       B200_TRY(launch_route_rows(r, pdl(), st));
     } else {
       B200_TRY(launch_router(r, pdl(), st));

@@ -408,6 +408,89 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   build_work_list(p, counts, offs, eoff);
 }
 
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Router logits of a pass of some tens to hundreds of rows (batched decode): too few rows for the 128-row
+// tensor-memory tiles to fill the device (512 experts are four tiles), too many for the per-row dot products
+// above. A CTA takes 16 experts x 64 rows; each warp an eighth of the hidden dimension, with the experts on the
+// M axis of mma.m16n8k16 and eight column tiles reusing every dequantised fragment. Q8_0 weights become
+// fp16(d * q), as in the tensor-core GEMM the longer passes use. A lane reads 16 contiguous weight bytes and the
+// matching 32 bytes of an activation row; the k-slots of the four mma steps are assigned to those bytes in A
+// and B alike. Warp partials are summed in warp order. grid (nE / 16, ceil(M / 64)), block 256.
+__global__ void __launch_bounds__(256) router_mma_kernel(RouterParams p) {
+  __shared__ float part[8][16][65];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int H = p.H, M = p.M, e0 = blockIdx.x * 16, n0 = blockIdx.y * 64;
+  const int ks = H / 8, nc = ks / 64, k_lo = warp * ks + 16 * t;
+  const uint8_t* wa = p.router.data + (size_t)(e0 + g) * p.router.stride;
+  const uint8_t* wb = p.router.data + (size_t)(e0 + g + 8) * p.router.stride;
+  // the weights do not depend on the producer kernel: fetch them first
+  uint4 qa[8], qb[8]; float da[8], db[8];
+#pragma unroll
+  for (int c = 0; c < 8; c++) {
+    if (c < nc) {
+      const int k0 = k_lo + 64 * c;
+      qa[c] = ldg_stream(wa + k0); qb[c] = ldg_stream(wb + k0);
+      da[c] = ld_f16(wa + H + (k0 / 32) * 2); db[c] = ld_f16(wb + H + (k0 / 32) * 2);
+    }
+  }
+  pdl_wait();
+  pdl_launch();
+  float acc[8][4];
+#pragma unroll
+  for (int nt = 0; nt < 8; nt++) { acc[nt][0] = 0.f; acc[nt][1] = 0.f; acc[nt][2] = 0.f; acc[nt][3] = 0.f; }
+  auto deq2 = [](uint32_t w, int sh, float d) {  // bytes sh, sh + 1 of w as fp16(d * q) pairs
+    const float lo = __fmul_rn((float)(int8_t)((w >> (8 * sh)) & 0xFF), d), hi = __fmul_rn((float)(int8_t)((w >> (8 * sh + 8)) & 0xFF), d);
+    return pack_half2(lo, hi);
+  };
+#pragma unroll
+  for (int c = 0; c < 8; c++) {
+    if (c < nc) {
+      const int k0 = k_lo + 64 * c;
+      const uint32_t wav[4] = {qa[c].x, qa[c].y, qa[c].z, qa[c].w}, wbv[4] = {qb[c].x, qb[c].y, qb[c].z, qb[c].w};
+      uint32_t a[4][4];
+#pragma unroll
+      for (int s = 0; s < 4; s++) {
+        a[s][0] = deq2(wav[s], 0, da[c]); a[s][1] = deq2(wbv[s], 0, db[c]);
+        a[s][2] = deq2(wav[s], 2, da[c]); a[s][3] = deq2(wbv[s], 2, db[c]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 8; nt++) {
+        const int row = min(n0 + nt * 8 + g, M - 1);  // rows past the end are not written
+        const __half* x = p.xn + (size_t)row * H + k0;
+        const uint4 x0 = *reinterpret_cast<const uint4*>(x), x1 = *reinterpret_cast<const uint4*>(x + 8);
+        mma16816(acc[nt], a[0], x0.x, x0.y);
+        mma16816(acc[nt], a[1], x0.z, x0.w);
+        mma16816(acc[nt], a[2], x1.x, x1.y);
+        mma16816(acc[nt], a[3], x1.z, x1.w);
+      }
+    }
+  }
+#pragma unroll
+  for (int nt = 0; nt < 8; nt++) {
+    part[warp][g][nt * 8 + 2 * t] = acc[nt][0]; part[warp][g][nt * 8 + 2 * t + 1] = acc[nt][1];
+    part[warp][g + 8][nt * 8 + 2 * t] = acc[nt][2]; part[warp][g + 8][nt * 8 + 2 * t + 1] = acc[nt][3];
+  }
+  __syncthreads();
+  for (int i = tid; i < 16 * 64; i += 256) {
+    const int e = i & 15, n = i >> 4;
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) v += part[w][e][n];
+    if (n0 + n < M) p.logits[(size_t)(n0 + n) * p.nE + e0 + e] = v;
+  }
+}
+bool router_mma_fits(const RouterParams& p) {
+  return p.router.type == T_Q8_0 && p.H % 512 == 0 && p.H <= 4096 && p.nE % 16 == 0 && p.xn != nullptr;
+}
+int launch_router_mma(const RouterParams& p, bool pdl, cudaStream_t st) {
+  if (!router_mma_fits(p)) { set_error("router_mma: shape outside kernel limits"); return EINVAL_; }
+  return launch_k(router_mma_kernel, dim3(p.nE / 16, (p.M + 63) / 64), dim3(256), 0, pdl, st, p);
+}
+
 // Routing of a many-row pass whose router logits came from the tensor-core GEMM: one warp per row
 // computes the shared-expert gate (f32 weights against the fp16 row) and selects the experts; the last
 // CTA builds the work list. grid ceil(M / 8), block 256.
@@ -1085,10 +1168,6 @@ int launch_attn_pack(const AttnParams& p, bool pdl, cudaStream_t st) {
 //               packed per dim with byte permutes (an in-register transpose; no shared-memory staging).
 // Online softmax per warp, warps merged in shared memory, splits merged by attn_merge_kernel.
 // -----------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
-  __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
 
 template <int HD, int G>
 __global__ void __launch_bounds__(128) attn_mma_kernel(AttnParams p) {

@@ -44,6 +44,8 @@ int launch_concat_norm(const float* e, const float* hs, const float* enorm, cons
 
 int launch_router(const RouterParams& p, bool pdl, cudaStream_t st);
 // selection + work list only, for passes whose logits come from launch_qgemm (the shared gate is computed here)
+bool router_mma_fits(const RouterParams& p);
+int launch_router_mma(const RouterParams& p, bool pdl, cudaStream_t st);
 int launch_route_rows(const RouterParams& p, bool pdl, cudaStream_t st);
 int launch_moe_gather(const __half* xn, const int* cols, int pairs, int slots1, int H, __half* xperm, bool pdl, cudaStream_t st);
 
