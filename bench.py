@@ -274,11 +274,13 @@ def main():
         return
     if args.profile_batch:
         gb = pkg.Graph(model, n_kv=32768 + 64, max_tokens=max(args.slots, 8), slots=args.slots, use_cuda_graph=False)
-        ctx = np.random.default_rng(7).integers(8192, 32769, args.slots)
+        rng_b = np.random.default_rng(7)   # the contexts and first tokens of batched_decode (rank 0)
+        ctx = rng_b.integers(8192, 32769, args.slots)
         for s_ in range(args.slots):
             gb.use_slot(s_); gb.set_past(int(ctx[s_]))
         sl = list(range(args.slots))
-        out = gb.generate_greedy(sl, [1] * args.slots, 2)
+        # distinct random first tokens: identical rows would all select the same ten experts
+        out = gb.generate_greedy(sl, rng_b.integers(0, cfg["vocab"], args.slots).astype(np.int32), 2)
         torch.cuda.synchronize()
         torch.cuda.profiler.start()
         out = gb.generate_greedy(sl, out[-1], args.profile_batch)
