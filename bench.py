@@ -236,7 +236,12 @@ def main():
 
     import torch
     import torch.distributed as dist
-    if world > 1:
+    if args.impl == "reference" and rank != 0:
+        # rank 0 alone times the CPU implementation. The other ranks leave at once, before any process group
+        # exists: a rank parked in a barrier spins on a host core, and every OpenMP barrier of the timed code
+        # would then wait for the thread that shares that core.
+        return
+    if world > 1 and args.impl != "reference":
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     torch.cuda.set_device(local_rank)
 
@@ -251,9 +256,6 @@ def main():
                     "config": {"workload": "batch-1 greedy decode, 80B-A3B-shaped Q4_K hybrid MoE", "host": "cpu"},
                     "cpu_baseline": cb, "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
             print(json.dumps(line))
-        if world > 1:
-            dist.barrier()
-            dist.destroy_process_group()
         return
 
     # every rank holds the whole model and decodes its own sequence: the path shards by sequences, no data crosses NVLink
