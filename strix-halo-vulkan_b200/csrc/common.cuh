@@ -50,12 +50,6 @@ const char* last_error();
     if (_s != b200::OK) return _s;       \
   } while (0)
 
-// Every kernel of the library asks for the largest shared-memory carve-out. An SM changes its split between
-// L1 and shared memory only when it is idle; with back-to-back launches (and dependents that start under their
-// predecessor) it never is, so a kernel that wants three 72 KB CTAs per SM would otherwise inherit whatever
-// carve-out the small kernels before it left and run one CTA per SM for its whole life.
-int prefer_max_shared(const void* kernel);
-
 // Optional per-launch phase timestamps (the reference keeps GPU timestamps per dispatch:
 // vk/shim.h:222-229, llm/graph.go:527-589). buf == nullptr switches them off.
 struct Timeline {

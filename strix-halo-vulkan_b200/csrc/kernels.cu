@@ -1,8 +1,6 @@
 // The token loop's non-projection kernels: embedding gather, router + routing, gated
 // DeltaNet step, attention pre-pass and split-KV decode attention, MoE combine, argmax,
 // and the Q6_K / Q8_0 row re-layout.
-#include <mutex>
-#include <set>
 #include "kernels.cuh"
 
 #include <cooperative_groups.h>
@@ -202,7 +200,6 @@ __global__ void __launch_bounds__(QG_THREADS) embed_norm_kernel(EmbedParams p) {
   }
 }
 int launch_embed(const EmbedParams& p, cudaStream_t st) {
-  B200_TRY(prefer_max_shared((const void*)embed_norm_kernel));
   embed_norm_kernel<<<p.M, QG_THREADS, 0, st>>>(p);
   B200_CUDA(cudaGetLastError());
   return OK;
@@ -211,19 +208,8 @@ int launch_embed(const EmbedParams& p, cudaStream_t st) {
 // =========================================================================================
 // PDL launch helper
 // =========================================================================================
-int prefer_max_shared(const void* kernel) {
-  static std::mutex mu;
-  static std::set<const void*> done;
-  std::lock_guard<std::mutex> lock(mu);
-  if (done.count(kernel)) return OK;
-  B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
-  done.insert(kernel);
-  return OK;
-}
-
 template <class... KArgs, class... Args>
 static int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, bool pdl, cudaStream_t st, Args... args) {
-  B200_TRY(prefer_max_shared((const void*)kernel));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -1590,7 +1576,6 @@ __global__ void advance_kernel(int32_t* ids, const int32_t* next, int* row_pos, 
 }
 int launch_advance(int32_t* ids, const int32_t* next, int* row_pos, SeqDesc* seqs, int M, int32_t* history, int* hist_len, cudaStream_t st) {
   if (M > 1024) { set_error("advance: too many rows"); return ECAPACITY; }
-  B200_TRY(prefer_max_shared((const void*)advance_kernel));
   advance_kernel<<<1, 1024, 0, st>>>(ids, next, row_pos, seqs, M, history, hist_len);
   B200_CUDA(cudaGetLastError());
   return OK;

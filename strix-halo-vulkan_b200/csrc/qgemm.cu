@@ -424,7 +424,6 @@ int launch_t(const QGemmParams& p, const CUtensorMap& tm, bool pdl, cudaStream_t
   const size_t smem = (size_t)gm_stages(TN, DUAL) * gm_stage_bytes(TN, DUAL) + 1024;
   static bool configured = false;
   if (!configured) { B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = true; }
-  B200_TRY(prefer_max_shared((const void*)kernel));
   static int sm_count = 0;
   if (sm_count == 0) { int dev = 0; B200_CUDA(cudaGetDevice(&dev)); B200_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev)); }
   const int n_tiles = (p.N + GM_ROWS - 1) / GM_ROWS;

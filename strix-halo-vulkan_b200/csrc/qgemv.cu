@@ -50,7 +50,6 @@ static int launch_one(const QGemvParams& p, int max_entries, bool pdl, cudaStrea
     B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(220 * 1024 + 4096)));
     configured = 220 * 1024 + 4096;
   }
-  B200_TRY(prefer_max_shared((const void*)kernel));
   QGemvParams pp = p;
   pp.nstage = ns;
   dim3 grid(gx, ny, nz);
@@ -101,7 +100,6 @@ static int launch_md(const MoeDown1Params& p, bool pdl, cudaStream_t st) {
   if (smem > 200 * 1024) { set_error("moe_down1: tiles too large for shared memory"); return ECAPACITY; }
   static bool configured = false;
   if (!configured) { B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); configured = true; }
-  B200_TRY(prefer_max_shared((const void*)kernel));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(((p.N + 15) / 16) * cl); cfg.blockDim = dim3(QG_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute attr[1];
