@@ -37,7 +37,10 @@ static int launch_one(const QGemvParams& p, int max_entries, bool pdl, cudaStrea
     rounds = (groups + cap - 1) / cap;
     gx = (groups + rounds - 1) / rounds;
     occ = o;
-    if (fixed + (size_t)std::min(rounds, 2) * stage <= budgets[o]) break;
+    // more work-list entries than SMs (a many-row pass over the experts): two CTAs per SM with one stage each
+    // beat one CTA with a deep ring - the walk is bound by the latencies inside a CTA, not by the copies
+    const int need = (GROUPED && ny > g_sm_count) ? 1 : std::min(rounds, 2);
+    if (fixed + (size_t)need * stage <= budgets[o]) break;
   }
   const int per_cta = rounds;
   int ns = (int)((budgets[occ] - fixed) / stage);
