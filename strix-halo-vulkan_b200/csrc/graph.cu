@@ -67,7 +67,7 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
     if (m->layers[l].is_attn) attn_index[l] = n_attn++;
     else dn_index[l] = n_dn++;
   }
-  max_entries = std::min(MR * used, c.n_expert + (MR * used + 7) / 8) + (MR + 7) / 8;
+  max_entries = std::max(max_entries_for(MR), max_entries_for(std::min(MR, 128)));
   B200_TRY(dalloc(&hbuf[0], (size_t)MR * H)); B200_TRY(dalloc(&hbuf[1], (size_t)MR * H)); h = hbuf[0]; B200_TRY(dalloc(&proj, (size_t)MR * proj_ld));
   B200_TRY(dalloc(&xn16, (size_t)MR * H)); B200_TRY(dalloc(&q16, (size_t)MR * qw)); B200_TRY(dalloc(&ctx16, (size_t)MR * qw));
   B200_TRY(dalloc(&attn_partial, (size_t)MR * c.n_head * nsplit * (hd + 2)));
@@ -145,9 +145,13 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   return OK;
 }
 
+// Columns per work-list entry. A pass of some tens of rows leaves one or two rows per touched expert: entries of
+// four columns halve the activation staging of the expert kernels, which then fit three to an SM.
+int Graph::entry_cols(int M) { return M >= 32 && M <= 128 ? 4 : 8; }
+
 int Graph::max_entries_for(int M) const {
-  const int used = m->c.n_expert_used;
-  return std::min(M * used, m->c.n_expert + (M * used + 7) / 8) + (M + 7) / 8;
+  const int used = m->c.n_expert_used, ec = entry_cols(M);
+  return std::min(M * used, m->c.n_expert + (M * used + ec - 1) / ec) + (M + ec - 1) / ec;
 }
 
 // ---- one pass over M rows --------------------------------------------------------------
@@ -329,7 +333,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     if (fused) { r.h = hc; r.gamma = (const float*)L.ffn_norm.data; r.ss_in = ss_part; r.ss_n = ss_n; r.eps = c.eps; r.xn_out = xn16; }
     r.M = M; r.H = H; r.nE = c.n_expert; r.used = used; r.logits = r_logits; r.probs = nullptr; r.topk = topk; r.topk_w = topk_w;
     r.tl = tl(); r.margin = margin; r.entries = entries; r.n_entries = n_entries; r.cols = cols; r.ticket = r_ticket; r.max_entries = max_entries;
-    r.defer = fused && M == 1;
+    r.defer = fused && M == 1; r.ecols = entry_cols(M);
     // 32 rows per expert on average and more: the experts run as grouped tensor-core GEMMs over expert-sorted
     // rows (below that the column-tiled kernel, which streams each expert's weights in whole tiles, is faster)
     const bool moe_gemm = use_gemm && (int64_t)M * used >= 32 * (int64_t)c.n_expert && L.gate_exps.type == L.gate_sh.type && L.down_exps.type == L.down_sh.type;
@@ -373,13 +377,13 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     } else {
     QGemvParams p = base(L.gate_exps, H, c.ffn_expert, xn16, H);
     p.w2[0] = L.up_exps.data; p.ws = L.gate_sh.data; p.ws2 = L.up_sh.data; p.expert_stride = (int64_t)c.ffn_expert * L.gate_exps.stride;
-    p.entries = entries; p.n_entries = n_entries; p.cols = cols; p.x_div = slots1;
+    p.entries = entries; p.n_entries = n_entries; p.cols = cols; p.x_div = slots1; p.xcols = std::min(xcols, entry_cols(M));
     p.y16 = act16; p.ldy = c.ffn_expert;
     p.route_here = r.defer; p.route = r;
     B200_TRY(launch_qgemv(L.gate_exps.type, PRO_F16, EPI_SWIGLU, true, true, p, ne, pdl(), st));
     QGemvParams q = base(L.down_exps, c.ffn_expert, H, act16, c.ffn_expert);
     q.ws = L.down_sh.data; q.expert_stride = (int64_t)H * L.down_exps.stride;
-    q.entries = entries; q.n_entries = n_entries; q.cols = cols; q.x_div = 1;
+    q.entries = entries; q.n_entries = n_entries; q.cols = cols; q.x_div = 1; q.xcols = std::min(xcols, entry_cols(M));
     q.y = down; q.ldy = H;
     if (fused && M == 1 && L.down_exps.type == L.down_sh.type && slots1 <= 16) {
       // one row: the routing weights are applied inside the down projection, which leaves a few partial rows

@@ -81,6 +81,7 @@ struct Graph {
   ~Graph();
   int init(Model* model, const b200_graph_opts& opts);
   int enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f);
+  static int entry_cols(int M);
   int max_entries_for(int M) const;
   int run_rows(const int32_t* ids, const int* slots, const int* pos, int M, const std::vector<SeqDesc>& sq, const std::vector<int>& lrows, const PassFlags& f);
   int extend(const int32_t* ids, int n, const PassFlags& f, const float** logits_out, const float** hidden_out);

@@ -231,6 +231,7 @@ constexpr int RT_ROWS = 8;  // router rows per CTA: one per warp
 // one GEMM problem per expert for the tensor-core kernels, cols = pairs in expert-sorted order.
 __device__ void build_work_list(const RouterParams& p, int* counts, int* offs, int* eoff) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, M = p.M, nE = p.nE, used = p.used;
+  const int EC = p.ecols > 0 ? p.ecols : 8;  // columns per entry
   // work list: pair id = n*(used+1) + slot; slot == used is the shared expert
   if (M == 1) {
     if (tid < used) { p.entries[tid] = make_int4(p.topk[tid], tid, 1, 0); p.cols[tid] = tid; }
@@ -242,10 +243,10 @@ __device__ void build_work_list(const RouterParams& p, int* counts, int* offs, i
   __syncthreads();
   for (int i = tid; i < M * used; i += 256) atomicAdd(&counts[__ldcg(p.topk + i)], 1);
   __syncthreads();
-  if (warp == 0) {  // exclusive scans of the pair counts and of the entry counts (8 columns per entry)
+  if (warp == 0) {  // exclusive scans of the pair counts and of the entry counts (EC columns per entry)
     const int per = (nE + 31) / 32;
     int c = 0, en = 0;
-    for (int i = 0; i < per; i++) { const int e = lane * per + i; if (e < nE) { c += counts[e]; en += (counts[e] + 7) >> 3; } }
+    for (int i = 0; i < per; i++) { const int e = lane * per + i; if (e < nE) { c += counts[e]; en += (counts[e] + EC - 1) / EC; } }
     int cs = c, es = en;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -255,21 +256,21 @@ __device__ void build_work_list(const RouterParams& p, int* counts, int* offs, i
     int co = cs - c, eo = es - en;
     for (int i = 0; i < per; i++) {
       const int e = lane * per + i;
-      if (e < nE) { offs[e] = co; eoff[e] = eo; co += counts[e]; eo += (counts[e] + 7) >> 3; }
+      if (e < nE) { offs[e] = co; eoff[e] = eo; co += counts[e]; eo += (counts[e] + EC - 1) / EC; }
     }
     const int tot_c = __shfl_sync(0xffffffffu, cs, 31), tot_e = __shfl_sync(0xffffffffu, es, 31);
     if (lane == 0) { offs[nE] = tot_c; eoff[nE] = tot_e; }
   }
   __syncthreads();
   for (int e = tid; e < nE; e += 256) {
-    for (int c = 0, i = 0; c < counts[e]; c += 8, i++)
-      if (eoff[e] + i < p.max_entries) p.entries[eoff[e] + i] = make_int4(e, offs[e] + c, min(8, counts[e] - c), 0);
+    for (int c = 0, i = 0; c < counts[e]; c += EC, i++)
+      if (eoff[e] + i < p.max_entries) p.entries[eoff[e] + i] = make_int4(e, offs[e] + c, min(EC, counts[e] - c), 0);
   }
   // one GEMM problem per expert for the tensor-core expert kernels: rows [offs, offs + count) of the expert-sorted order
   if (p.gprob != nullptr) for (int e = tid; e < nE; e += 256) p.gprob[e] = make_int4(e, offs[e], counts[e], offs[e]);
-  const int nsh = (M + 7) >> 3;
+  const int nsh = (M + EC - 1) / EC;
   for (int i = tid; i < nsh; i += 256)
-    if (eoff[nE] + i < p.max_entries) p.entries[eoff[nE] + i] = make_int4(-1, offs[nE] + 8 * i, min(8, M - 8 * i), 0);
+    if (eoff[nE] + i < p.max_entries) p.entries[eoff[nE] + i] = make_int4(-1, offs[nE] + EC * i, min(EC, M - EC * i), 0);
   if (tid == 0) *p.n_entries = min(eoff[nE] + nsh, p.max_entries);
   __syncthreads();
   for (int i = tid; i <= nE; i += 256) counts[i] = 0;

@@ -22,6 +22,7 @@ struct RouterParams {
   int4* gprob;         // optional [nE]: {expert, first sorted row, rows, first sorted row} per expert (GemmProblem)
   int max_entries;
   int defer;           // 1: stop after the logits; the expert kernel that follows selects the experts itself
+  int ecols;           // columns per work-list entry (8, or 4 for passes of some tens of rows; 0 means 8)
   Timeline tl;
 };
 
