@@ -153,6 +153,25 @@ def test_long_attention_splits_are_the_short_ones(pkg, tiny):
             assert_close(b, a, "long splits against short ones", tol=1e-3)
 
 
+def test_work_list_entry_width_boundaries(pkg, tiny):
+    """Passes of 32 to 128 rows build expert work-list entries of four columns, the others of eight: passes on
+    both sides of each boundary (129 | 128 | 33 and 32 | 31 rows) give the oracle's logits."""
+    cfg = tiny["cfg"]
+    ids = prompt(cfg, 129 + 128 + 33, seed=13)
+    want, _ = tiny["oracle"].seq().extend(ids)
+    outs = []
+    for max_tokens in (129, 128, 32, 31):
+        g = pkg.Graph(tiny["model"], n_kv=320, max_tokens=max_tokens, use_cuda_graph=False)
+        if max_tokens == 129:
+            g.extend(ids[:129]); g.extend(ids[129:257]); logits, _ = g.extend(ids[257:])
+        else:
+            logits, _ = g.forward(ids)
+        assert_close(logits, want, f"passes of at most {max_tokens} rows")
+        outs.append(logits)
+    for o in outs[1:]:
+        assert_close(o, outs[0], "pass lengths against each other", tol=5e-3)
+
+
 def test_decode_rows_is_each_slot(pkg, tiny):
     # llm/graph_batch_test.go TestGraphDecodeRowsIsEachSlot: batched == solo. A single row sums its experts'
     # down projections inside one kernel (per warp, then per rank), a pass of several rows in the consumer's
