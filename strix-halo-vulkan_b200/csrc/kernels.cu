@@ -606,10 +606,8 @@ __device__ __forceinline__ float softplus_ref(float x) {  // llm/deltanet.go:450
 }
 __device__ __forceinline__ float silu_acc(float x) { return x * sigmoid_acc(x); }
 
-// MINB: minimum CTAs per SM. Many sequences are throughput-bound by how many CTAs are resident (each is a
-// latency chain), so that form trades a few spilled registers for six CTAs per SM.
-template <int MINB>
-__global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(128, MINB) dn_step_kernel(DnStepParams p) {
+// (Passes of 16 sequences and more use dn_head_kernel below instead.)
+__global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(128, 1) dn_step_kernel(DnStepParams p) {
   cg::cluster_group cluster = cg::this_cluster();
   const int D = 128, RB = 4;
   const int h = blockIdx.x / RB, rb = blockIdx.x % RB, hk = h % p.Hk;
@@ -1100,7 +1098,7 @@ int launch_dn_scan(const DnStepParams& p, int M, int max_n, bool pdl, cudaStream
 int launch_dn_step(const DnStepParams& p, bool pdl, cudaStream_t st) {
   if (p.D != 128 || p.conv != 4) { set_error("dn_step: head dim must be 128 and conv kernel 4"); return EINVAL_; }
   if (p.n_seq >= 16) return launch_k(dn_head_kernel, dim3(p.Hv, p.n_seq), dim3(512), 0, pdl, st, p);
-  return launch_k(dn_step_kernel<1>, dim3(p.Hv * 4, p.n_seq), dim3(128), 0, pdl, st, p);
+  return launch_k(dn_step_kernel, dim3(p.Hv * 4, p.n_seq), dim3(128), 0, pdl, st, p);
 }
 
 // =========================================================================================
