@@ -312,7 +312,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       int sc = split_cells;
       if (o.attn_split_cells <= 0) while (sc < 2048 && (int64_t)M * c.n_head_kv * ((o.n_kv + sc - 1) / sc) >= 4096) sc *= 2;
       a.split_cells = sc; a.nsplit = (o.n_kv + sc - 1) / sc; a.eps = c.eps; a.rope_off = f.draft ? 1 : 0;
-      a.err = err_flag; a.tl = tl();
+      a.one_row_per_seq = M == n_seq && !f.spec; a.err = err_flag; a.tl = tl();
       B200_TRY(launch_attn_pack(a, pdl(), st));
       a.tl = tl();
       B200_TRY(launch_attn_decode(a, pdl(), st));

@@ -1174,12 +1174,13 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(AttnParams p) {
   constexpr int NB = HD / 64;   // 64-dim blocks of the value mma
   const int split = blockIdx.x, kvh = blockIdx.y, n = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  __shared__ float sm_m[4][G], sm_l[4][G];
-  __shared__ float sm_o[4][G][HD];
+  __shared__ float sm_m[4][G], sm_l[4][G], sm_f[4][G];
+  __shared__ __align__(16) float sm_o[4][G][HD + 4];  // padded: the 16-byte stores of a quarter warp spread over the banks
   tl_mark(p.tl, 0);
-  pdl_wait();
-  pdl_launch();
-  tl_mark(p.tl, 1);
+  // The row's position and slot were written before this pass began. When every sequence has one row in the pass,
+  // every cell but the newest was written by earlier passes too: both can be read before the producer kernel
+  // (which writes the newest cell and the query) is known to be complete. A warp whose first block lies wholly
+  // below the newest cell fetches its keys now.
   const int pos = p.row_pos[n], slot = p.row_slot[n];
   const int ncell = pos + 1;
   const int c0 = split * p.split_cells, c1 = min(ncell, c0 + p.split_cells);
@@ -1187,6 +1188,23 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(AttnParams p) {
   const size_t cell_stride = (size_t)p.Hkv * HD;
   const __half* kbase = p.kcache + (size_t)slot * p.slot_stride + (size_t)kvh * HD;
   const __half* vbase = p.vcache + (size_t)slot * p.slot_stride + (size_t)kvh * HD;
+  uint4 ka4[KS / 2], kb4[KS / 2];
+  auto fetch_k = [&](int cb) {
+    const int ka = min(cb + g, c1 - 1), kb = min(cb + 8 + g, c1 - 1);  // clamped rows are masked below
+    const __half* kra = kbase + (size_t)ka * cell_stride;
+    const __half* krb = kbase + (size_t)kb * cell_stride;
+#pragma unroll
+    for (int j = 0; j < KS / 2; j++) {
+      ka4[j] = ldg_stream(kra + 8 * (t + 4 * j));
+      kb4[j] = ldg_stream(krb + 8 * (t + 4 * j));
+    }
+  };
+  const int cb_first = c0 + warp * 16;
+  const bool early = p.one_row_per_seq && cb_first + 16 <= pos;   // (then also cb_first < c1)
+  if (early) fetch_k(cb_first);
+  pdl_wait();
+  pdl_launch();
+  tl_mark(p.tl, 1);
   // query A fragments: head g of the group on row g; rows 8..15 stay zero
   uint32_t qa[KS][2];
 #pragma unroll
@@ -1202,15 +1220,7 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(AttnParams p) {
   for (int cb = c0 + warp * 16; cb < c1; cb += 64) {
     // ---- scores of 16 cells ----
     float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-    const int ka = min(cb + g, c1 - 1), kb = min(cb + 8 + g, c1 - 1);  // clamped rows are masked below
-    const __half* kra = kbase + (size_t)ka * cell_stride;
-    const __half* krb = kbase + (size_t)kb * cell_stride;
-    uint4 ka4[KS / 2], kb4[KS / 2];
-#pragma unroll
-    for (int j = 0; j < KS / 2; j++) {
-      ka4[j] = ldg_stream(kra + 8 * (t + 4 * j));
-      kb4[j] = ldg_stream(krb + 8 * (t + 4 * j));
-    }
+    if (!(early && cb == cb_first)) fetch_k(cb);
     // the value rows do not depend on the scores: the first two 64-dim blocks are fetched while the score mma
     // runs, the rest as soon as the key registers are free, so every value load is in flight before the softmax
     const int cell_a = cb + 2 * t, cell_c = cb + 8 + 2 * t;
@@ -1273,27 +1283,37 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(AttnParams p) {
     if (t == 0) { sm_m[warp][g] = m; sm_l[warp][g] = l; }
 #pragma unroll
     for (int b = 0; b < NB; b++) {
-#pragma unroll
-      for (int i = 0; i < 8; i++) {
-        sm_o[warp][g][8 * (2 * t + 8 * b) + i] = o[b * 8 + i][0];
-        sm_o[warp][g][8 * (2 * t + 1 + 8 * b) + i] = o[b * 8 + i][1];
-      }
+      float* d0 = &sm_o[warp][g][8 * (2 * t + 8 * b)];
+      float* d1 = &sm_o[warp][g][8 * (2 * t + 1 + 8 * b)];
+      *reinterpret_cast<float4*>(d0) = make_float4(o[b * 8 + 0][0], o[b * 8 + 1][0], o[b * 8 + 2][0], o[b * 8 + 3][0]);
+      *reinterpret_cast<float4*>(d0 + 4) = make_float4(o[b * 8 + 4][0], o[b * 8 + 5][0], o[b * 8 + 6][0], o[b * 8 + 7][0]);
+      *reinterpret_cast<float4*>(d1) = make_float4(o[b * 8 + 0][1], o[b * 8 + 1][1], o[b * 8 + 2][1], o[b * 8 + 3][1]);
+      *reinterpret_cast<float4*>(d1 + 4) = make_float4(o[b * 8 + 4][1], o[b * 8 + 5][1], o[b * 8 + 6][1], o[b * 8 + 7][1]);
     }
+  }
+  __syncthreads();
+  // the warps' factors exp(m_w - m*) once per head, not once per output element
+  if (tid < 4 * G) {
+    const int w = tid / G, hh = tid - w * G;
+    const float mm = fmaxf(fmaxf(sm_m[0][hh], sm_m[1][hh]), fmaxf(sm_m[2][hh], sm_m[3][hh]));
+    sm_f[w][hh] = sm_m[w][hh] == -INFINITY ? 0.f : expf(sm_m[w][hh] - mm);
   }
   __syncthreads();
   const int PW = HD + 2;
   for (int i = tid; i < G * HD; i += 128) {
     const int hh = i / HD, d = i - hh * HD;
-    float mm = fmaxf(fmaxf(sm_m[0][hh], sm_m[1][hh]), fmaxf(sm_m[2][hh], sm_m[3][hh]));
-    float ov = 0.f, lv = 0.f;
+    float ov = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; w++) {
-      const float f = sm_m[w][hh] == -INFINITY ? 0.f : expf(sm_m[w][hh] - mm);
-      ov += sm_o[w][hh][d] * f; lv += sm_l[w][hh] * f;
-    }
+    for (int w = 0; w < 4; w++) ov += sm_o[w][hh][d] * sm_f[w][hh];
     float* part = p.partial + (((size_t)n * p.Hq + kvh * G + hh) * p.nsplit + split) * PW;
     part[d] = ov;
-    if (d == 0) { part[HD] = mm; part[HD + 1] = lv; }
+    if (d == 0) {
+      float lv = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; w++) lv += sm_l[w][hh] * sm_f[w][hh];
+      part[HD] = fmaxf(fmaxf(sm_m[0][hh], sm_m[1][hh]), fmaxf(sm_m[2][hh], sm_m[3][hh]));
+      part[HD + 1] = lv;
+    }
   }
   tl_mark(p.tl, 4);
 }
@@ -1313,7 +1333,7 @@ __global__ void __launch_bounds__(256, 1) attn_ring_kernel(AttnParams p) {
   constexpr int SLOT = 16 * KP;                      // a slot holds the key or the value rows of 16 cells
   extern __shared__ __align__(128) uint8_t ar_ring[];  // [NW][NSLOT][SLOT]; reused for the warps' outputs at the end
   __shared__ uint64_t bars[NW][NSLOT];
-  __shared__ float sm_m[NW][G], sm_l[NW][G];
+  __shared__ float sm_m[NW][G], sm_l[NW][G], sm_f[NW][G];
   const int split = blockIdx.x, kvh = blockIdx.y, n = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   tl_mark(p.tl, 0);
@@ -1418,34 +1438,43 @@ __global__ void __launch_bounds__(256, 1) attn_ring_kernel(AttnParams p) {
   l += __shfl_xor_sync(0xffffffffu, l, 1);
   l += __shfl_xor_sync(0xffffffffu, l, 2);
   __syncthreads();  // every warp has consumed what it issued: the ring becomes the warps' output buffer
-  float (*sm_o)[G][HD] = reinterpret_cast<float (*)[G][HD]>(ar_ring);
+  float (*sm_o)[G][HD + 4] = reinterpret_cast<float (*)[G][HD + 4]>(ar_ring);  // padded like attn_mma_kernel's
   if (g < G) {
     if (t == 0) { sm_m[warp][g] = m; sm_l[warp][g] = l; }
 #pragma unroll
     for (int b = 0; b < NB; b++) {
-#pragma unroll
-      for (int i = 0; i < 8; i++) {
-        sm_o[warp][g][8 * (2 * t + 8 * b) + i] = o[b * 8 + i][0];
-        sm_o[warp][g][8 * (2 * t + 1 + 8 * b) + i] = o[b * 8 + i][1];
-      }
+      float* d0 = &sm_o[warp][g][8 * (2 * t + 8 * b)];
+      float* d1 = &sm_o[warp][g][8 * (2 * t + 1 + 8 * b)];
+      *reinterpret_cast<float4*>(d0) = make_float4(o[b * 8 + 0][0], o[b * 8 + 1][0], o[b * 8 + 2][0], o[b * 8 + 3][0]);
+      *reinterpret_cast<float4*>(d0 + 4) = make_float4(o[b * 8 + 4][0], o[b * 8 + 5][0], o[b * 8 + 6][0], o[b * 8 + 7][0]);
+      *reinterpret_cast<float4*>(d1) = make_float4(o[b * 8 + 0][1], o[b * 8 + 1][1], o[b * 8 + 2][1], o[b * 8 + 3][1]);
+      *reinterpret_cast<float4*>(d1 + 4) = make_float4(o[b * 8 + 4][1], o[b * 8 + 5][1], o[b * 8 + 6][1], o[b * 8 + 7][1]);
     }
+  }
+  __syncthreads();
+  // the warps' factors exp(m_w - m*) once per head, not once per output element
+  if (tid < NW * G) {
+    const int w = tid / G, hh = tid - w * G;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int v = 0; v < NW; v++) mm = fmaxf(mm, sm_m[v][hh]);
+    sm_f[w][hh] = sm_m[w][hh] == -INFINITY ? 0.f : expf(sm_m[w][hh] - mm);
   }
   __syncthreads();
   const int PW = HD + 2;
   for (int i = tid; i < G * HD; i += 256) {
     const int hh = i / HD, d = i - hh * HD;
-    float mm = -INFINITY;
+    float ov = 0.f;
 #pragma unroll
-    for (int w = 0; w < NW; w++) mm = fmaxf(mm, sm_m[w][hh]);
-    float ov = 0.f, lv = 0.f;
-#pragma unroll
-    for (int w = 0; w < NW; w++) {
-      const float f = sm_m[w][hh] == -INFINITY ? 0.f : expf(sm_m[w][hh] - mm);
-      ov += sm_o[w][hh][d] * f; lv += sm_l[w][hh] * f;
-    }
+    for (int w = 0; w < NW; w++) ov += sm_o[w][hh][d] * sm_f[w][hh];
     float* part = p.partial + (((size_t)n * p.Hq + kvh * G + hh) * p.nsplit + split) * PW;
     part[d] = ov;
-    if (d == 0) { part[HD] = mm; part[HD + 1] = lv; }
+    if (d == 0) {
+      float mm = -INFINITY, lv = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; w++) { mm = fmaxf(mm, sm_m[w][hh]); lv += sm_l[w][hh] * sm_f[w][hh]; }
+      part[HD] = mm; part[HD + 1] = lv;
+    }
   }
   tl_mark(p.tl, 4);
 }

@@ -90,6 +90,7 @@ struct AttnParams {
   __half* ctx16;                             // [M][Hq*hd]
   int M, Hq, Hkv, hd, rope_dims, n_kv, split_cells, nsplit;
   int rope_off;                              // rotary position = cell + rope_off (1 for the draft layer)
+  int one_row_per_seq;                       // every sequence has exactly one row in this pass (plain decode)
   float eps;
   int* err;                                  // device error word: set when a bounded wait gives up
   Timeline tl;
