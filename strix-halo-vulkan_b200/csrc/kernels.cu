@@ -1110,15 +1110,21 @@ __global__ void attn_pack_kernel(AttnParams p) {
   const int hd = p.hd, d = threadIdx.x, n = blockIdx.y, which = blockIdx.x;
   __shared__ float buf[256], red[8];
   tl_mark(p.tl, 0);
+  // what the producer kernel does not write (position, slot, norm weight, rotary entry) is fetched before waiting for it
+  const int pos = p.row_pos[n], slot = p.row_slot[n];
+  const float* gamma = which < p.Hq ? p.q_norm : which < p.Hq + p.Hkv ? p.k_norm : nullptr;
+  const float gamma_d = gamma != nullptr ? gamma[d] : 0.f;
+  const int half = p.rope_dims / 2;
+  float2 cs = make_float2(1.f, 0.f);
+  if (gamma != nullptr && d < p.rope_dims) cs = *reinterpret_cast<const float2*>(p.rope + ((size_t)(pos + p.rope_off) * half + (d < half ? d : d - half)) * 2);
   pdl_wait();
   pdl_launch();
   tl_mark(p.tl, 1);
   const float* pr = p.proj + (size_t)n * p.ldp;
-  const int pos = p.row_pos[n], slot = p.row_slot[n];
   const int kv_off = p.Hq * 2 * hd;
-  float x; const float* gamma = nullptr;
-  if (which < p.Hq) { x = pr[which * 2 * hd + d]; gamma = p.q_norm; }
-  else if (which < p.Hq + p.Hkv) { x = pr[kv_off + (which - p.Hq) * hd + d]; gamma = p.k_norm; }
+  float x;
+  if (which < p.Hq) x = pr[which * 2 * hd + d];
+  else if (which < p.Hq + p.Hkv) x = pr[kv_off + (which - p.Hq) * hd + d];
   else x = pr[kv_off + p.Hkv * hd + (which - p.Hq - p.Hkv) * hd + d];
   if (gamma != nullptr) {
     float ss = warp_sum(x * x);
@@ -1126,13 +1132,11 @@ __global__ void attn_pack_kernel(AttnParams p) {
     __syncthreads();
     float tot = 0.f;
     for (int w = 0; w < hd / 32; w++) tot += red[w];
-    x = x * (1.0f / sqrtf(tot / (float)hd + p.eps)) * gamma[d];
+    x = x * (1.0f / sqrtf(tot / (float)hd + p.eps)) * gamma_d;
     buf[d] = x;
     __syncthreads();
-    const int half = p.rope_dims / 2;
     if (d < p.rope_dims) {
       const int i = d < half ? d : d - half;
-      const float2 cs = *reinterpret_cast<const float2*>(p.rope + ((size_t)(pos + p.rope_off) * half + i) * 2);
       const float x0 = buf[i], x1 = buf[i + half];
       x = d < half ? x0 * cs.x - x1 * cs.y : x0 * cs.y + x1 * cs.x;
     }
@@ -1486,10 +1490,12 @@ __global__ void attn_merge_kernel(AttnParams p) {
   extern __shared__ float mg_f[];  // [nsplit] factors exp(m_s - m*), then [nsplit] row sums
   __shared__ float mg_red[8];
   tl_mark(p.tl, 0);
+  // the row's position and its gate (written by the in-projection, three kernels back) do not wait for the splits
+  const int nlive = (p.row_pos[n] + 1 + p.split_cells - 1) / p.split_cells;
+  const float gate = p.proj[(size_t)n * p.ldp + head * 2 * hd + hd + d];
   pdl_wait();
   pdl_launch();
   tl_mark(p.tl, 1);
-  const int nlive = (p.row_pos[n] + 1 + p.split_cells - 1) / p.split_cells;
   const float* part = p.partial + ((size_t)n * p.Hq + head) * p.nsplit * PW;
   // one round of loads for every split's maximum and row sum, shared through shared memory
   float mloc = -INFINITY;
@@ -1521,7 +1527,6 @@ __global__ void attn_merge_kernel(AttnParams p) {
     const float e = ms == -INFINITY ? 0.f : expf(ms - mm);
     ov += __ldcg(part + (size_t)sp * PW + d) * e; lv += mg_f[p.nsplit + sp] * e;
   }
-  const float gate = p.proj[(size_t)n * p.ldp + head * 2 * hd + hd + d];
   p.ctx16[(size_t)n * p.Hq * hd + head * hd + d] = __float2half_rn(ov / lv * sigmoid_acc(gate));
   tl_mark(p.tl, 6, true);
 }
