@@ -301,19 +301,26 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
       if (k0 < H) { wq[i] = ldg_stream(wr + k0); wd[i] = ld_f16(wr + nb * 32 + (k0 / 32) * 2); }
     }
   }
+  const bool staged = p.h != nullptr;
+  float4 hpre[2], gpre[2];
+  if (staged) {  // the norm weights do not depend on the producer kernel either
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+      const int k = tid * 4 + i * 1024;
+      if (k < H) gpre[i] = *reinterpret_cast<const float4*>(p.gamma + k);
+    }
+  }
   pdl_wait();
   pdl_launch();
   tl_mark(p.tl, 1);
   extern __shared__ __align__(16) __half rxs[];  // [M][H] when the rows are normalised here
   __shared__ float rscale[8];
-  const bool staged = p.h != nullptr;
   if (staged) {  // ffn_norm fused into the router (M <= 8): every CTA normalises the rows, CTA 0 keeps a copy
-    // the first row's values and the norm weights do not depend on the scale: fetch them before reducing the partials
-    float4 hpre[2], gpre[2];
+    // the first row's values do not depend on the scale: fetch them before reducing the partials
 #pragma unroll
     for (int i = 0; i < 2; i++) {
       const int k = tid * 4 + i * 1024;
-      if (k < H) { hpre[i] = __ldcg(reinterpret_cast<const float4*>(p.h + k)); gpre[i] = *reinterpret_cast<const float4*>(p.gamma + k); }
+      if (k < H) hpre[i] = __ldcg(reinterpret_cast<const float4*>(p.h + k));
     }
     if (warp < M) {
       const float sc = scale_from_parts(p.ss_in, p.ss_n, warp, H, p.eps);

@@ -527,7 +527,7 @@ __device__ __forceinline__ void stage_x_norm(const QGemvParams& p, uint8_t* xs, 
 // The MoE combine and the RMSNorm that follows it, fused into the staging: columns go four at a time,
 // a thread keeping its 8 values of each in registers between the sum of squares and the scaling.
 __device__ __forceinline__ void stage_x_combine(const QGemvParams& p, uint8_t* xs, __half* sxs, float* scratch, int ncols, const int* xrows,
-                                                int xstride, bool writer) {
+                                                int xstride, bool writer, const float4* pre_gam = nullptr, const float4* pre_h = nullptr) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, K = p.K, slots1 = p.used + 1;
   // element index of this thread, rotated by whole 128-byte lines per CTA (every CTA reads the same rows)
   const int et = (tid + 8 * (int)((blockIdx.x + blockIdx.y) & 31)) & (QG_THREADS - 1);
@@ -536,7 +536,7 @@ __device__ __forceinline__ void stage_x_combine(const QGemvParams& p, uint8_t* x
 #pragma unroll
   for (int i = 0; i < 2; i++) {
     const int k = et * 4 + i * QG_THREADS * 4;
-    gam[i] = k < K ? *reinterpret_cast<const float4*>(p.gamma + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+    gam[i] = pre_gam != nullptr ? pre_gam[i] : k < K ? *reinterpret_cast<const float4*>(p.gamma + k) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   for (int c0 = 0; c0 < ncols; c0 += 4) {
     float4 v[4][2];
@@ -553,7 +553,7 @@ __device__ __forceinline__ void stage_x_combine(const QGemvParams& p, uint8_t* x
         const int k = et * 4 + i * QG_THREADS * 4;
         v[cc][i] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (k < K && c0 + cc < ncols) {
-          const float4 hv = __ldcg(reinterpret_cast<const float4*>(hrow + k));
+          const float4 hv = pre_h != nullptr ? pre_h[i] : __ldcg(reinterpret_cast<const float4*>(hrow + k));
           const float4 sh = __ldcg(reinterpret_cast<const float4*>(dn + (size_t)p.used * K + k));
           float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 5
@@ -716,6 +716,22 @@ __global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 
     int grp = blockIdx.x;
     for (int s = 0; s < NS && grp < ngroups; s++, grp += gridDim.x) issue_group(grp, s);
   }
+  // Single-row combine: the norm weights and the residual row (final four kernels back) are fetched before the
+  // wait, so that only the partial rows of the down projection are asked of L2 once it is over.
+  float4 pre_g[2], pre_h[2];
+  bool pre = false;
+  if constexpr (PRO == PRO_COMBINE) {
+    if (p.M == 1) {
+      pre = true;
+      const int et = (tid + 8 * (int)((blockIdx.x + blockIdx.y) & 31)) & (QG_THREADS - 1);
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        const int k = et * 4 + i * QG_THREADS * 4;
+        pre_g[i] = k < K ? *reinterpret_cast<const float4*>(p.gamma + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+        pre_h[i] = k < K ? __ldcg(reinterpret_cast<const float4*>(p.hsrc + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+  }
   if constexpr (!GROUPED) pdl_wait();
   pdl_launch();
   tl_mark(p.tl, 1);
@@ -730,7 +746,7 @@ __global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 
       xrows[tid] = GROUPED ? id / p.x_div : id;
     }
     __syncthreads();
-    if constexpr (PRO == PRO_COMBINE) stage_x_combine(p, xs, sxs, scratch, ncols, xrows, xstride, blockIdx.x == 0 && blockIdx.y == 0);
+    if constexpr (PRO == PRO_COMBINE) stage_x_combine(p, xs, sxs, scratch, ncols, xrows, xstride, blockIdx.x == 0 && blockIdx.y == 0, pre ? pre_g : nullptr, pre ? pre_h : nullptr);
     else if constexpr (PRO == PRO_NORM) stage_x_norm(p, xs, sxs, scratch, ncols, xrows, xstride, p.xn_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0);
     else stage_x_f16(p.x, p.ldx, K, p.xcols, xs, sxs, ncols, xrows, xstride, x_copied);
     tl_mark(p.tl, 2);
