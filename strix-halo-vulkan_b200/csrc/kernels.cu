@@ -621,7 +621,7 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(128, 1) dn_step_kern
   const SeqDesc sq = p.seqs[blockIdx.y];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qk = p.Hk * D, H = p.H;
-  __shared__ float qs[128], ks[128], vs[32], red[16], wss[4], cta_ss[2];
+  __shared__ float qs[128], ks[128], vs[32], red[16], wss[4], cta_ss[2][4];  // cta_ss[token parity][row block]
   const int ch_q = hk * D + tid, ch_k = qk + hk * D + tid, ch_v = 2 * qk + h * D + rb * 32 + (tid & 31);
   const float4 cwq = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch_q * 4);
   const float4 cwk = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch_k * 4);
@@ -745,11 +745,14 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(128, 1) dn_step_kern
     }
     if (lane == 0) wss[warp] = ss;
     __syncthreads();
-    if (tid == 0) cta_ss[i & 1] = wss[0] + wss[1] + wss[2] + wss[3];
+    // each CTA pushes its partial into the four CTAs' shared memory (thread r writes to rank r), one cluster
+    // barrier, then everyone adds the four local copies in rank order: no CTA reads a peer's memory, so none
+    // has to outlive a peer's reads
+    if (tid < 4) *cluster.map_shared_rank(&cta_ss[i & 1][rb], tid) = wss[0] + wss[1] + wss[2] + wss[3];
     cluster.sync();
     float tot = 0.f;
 #pragma unroll
-    for (int r = 0; r < 4; r++) tot += *cluster.map_shared_rank(&cta_ss[i & 1], r);
+    for (int r = 0; r < 4; r++) tot += cta_ss[i & 1][r];
     if (lane < 8) {
       const int j = j0 + lane;
       const float nsc = 1.0f / sqrtf(tot / (float)D + p.eps);
@@ -767,7 +770,6 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(128, 1) dn_step_kern
 #pragma unroll
     for (int r = 0; r < 8; r++) *reinterpret_cast<float4*>(S + (size_t)(j0 + r) * D + lane * 4) = s[r];
   }
-  cluster.sync();  // no CTA may leave while a peer can still read its shared memory
   tl_mark(p.tl, 4);
 }
 
