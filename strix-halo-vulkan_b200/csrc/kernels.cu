@@ -1577,9 +1577,28 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* logits, int V
   pdl_launch();
   const float* lg = logits + (size_t)blockIdx.x * V;
   float v = -INFINITY; int idx = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += 1024) {
-    float x = lg[i];
-    if (x > v) { v = x; idx = i; }
+  if ((V & 3) == 0 && (reinterpret_cast<uintptr_t>(lg) & 15) == 0) {
+    // four independent 16-byte loads in flight per thread; a thread's indices still rise, so `>` keeps the lowest
+    const float4* lg4 = reinterpret_cast<const float4*>(lg);
+    const int V4 = V >> 2;
+    for (int i0 = threadIdx.x; i0 < V4; i0 += 4 * 1024) {
+      float4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) { const int i = i0 + u * 1024; x[u] = i < V4 ? __ldcg(lg4 + i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY); }
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int e = 4 * (i0 + u * 1024);
+        if (x[u].x > v) { v = x[u].x; idx = e; }
+        if (x[u].y > v) { v = x[u].y; idx = e + 1; }
+        if (x[u].z > v) { v = x[u].z; idx = e + 2; }
+        if (x[u].w > v) { v = x[u].w; idx = e + 3; }
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += 1024) {
+      float x = lg[i];
+      if (x > v) { v = x; idx = i; }
+    }
   }
   auto better = [](float a, int ai, float b, int bi2) { return a > b || (a == b && ai < bi2); };
 #pragma unroll
