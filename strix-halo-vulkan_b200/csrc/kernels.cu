@@ -656,6 +656,7 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(128, 1) dn_step_kern
 #pragma unroll
   for (int r = 0; r < 8; r++) s[r] = *reinterpret_cast<const float4*>(S + (size_t)(j0 + r) * D + lane * 4);
   const float oscale = 1.0f / sqrtf((float)D);
+  const float nw = lane < 8 ? p.norm_w[j0 + lane] : 0.f;  // gated-norm weight of the row this lane writes
   tl_mark(p.tl, 0);
   pdl_wait();
   pdl_launch();
@@ -685,6 +686,7 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(128, 1) dn_step_kern
       ab_dot(k, *reinterpret_cast<const float4*>(p.alpha_w + (size_t)h * H + k), *reinterpret_cast<const float4*>(p.beta_w + (size_t)h * H + k));
     // conv + SiLU for q, k (whole head) and this CTA's 32 v channels
     const float cq = pr[ch_q], ck = pr[ch_k], cv = pr[ch_v];
+    const float zz = lane < 8 ? pr[2 * qk + p.Hv * D + h * D + j0 + lane] : 0.f;  // the gate, asked for with the other inputs
     const float q = silu_acc(hq[0] * cwq.x + hq[1] * cwq.y + hq[2] * cwq.z + cq * cwq.w);
     const float k = silu_acc(hkk[0] * cwk.x + hkk[1] * cwk.y + hkk[2] * cwk.z + ck * cwk.w);
     const float v = silu_acc(hv[0] * cwv.x + hv[1] * cwv.y + hv[2] * cwv.z + cv * cwv.w);
@@ -756,8 +758,7 @@ __global__ void __cluster_dims__(4, 1, 1) __launch_bounds__(128, 1) dn_step_kern
     if (lane < 8) {
       const int j = j0 + lane;
       const float nsc = 1.0f / sqrtf(tot / (float)D + p.eps);
-      const float zz = pr[2 * qk + p.Hv * D + h * D + j];
-      p.y16[(size_t)row * (p.Hv * D) + h * D + j] = __float2half_rn(ov * nsc * p.norm_w[j] * sigmoid_acc(zz));
+      p.y16[(size_t)row * (p.Hv * D) + h * D + j] = __float2half_rn(ov * nsc * nw * sigmoid_acc(zz));
     }
     if (p.mid != nullptr) {  // state after token i, for keep-prefix speculation
       float* Sm = p.mid + (size_t)blockIdx.y * p.mid_seq_stride + (size_t)i * p.mid_stride + (size_t)h * D * D;
