@@ -56,6 +56,25 @@ typedef struct {
   int32_t trace;            /* 1: keep per-layer hidden states and routing for b200_graph_trace */
 } b200_graph_opts;
 
+/* Running totals of a graph (llm.GraphStats, llm/graph.go:527-589, reduced to what one CUDA stream can tell). */
+typedef struct {
+  int64_t passes;        /* passes run (Runs) */
+  int64_t rows;          /* activation rows those passes carried */
+  int64_t launches;      /* kernel launches or graph nodes issued (Dispatches) */
+  double device_ms;      /* device time between the first and the last kernel of every pass (GPU) */
+  double host_ms;        /* host wall clock around enqueue + wait of every pass (Submit) */
+  int32_t last_rows, last_launches;
+  float last_device_ms;
+} b200_graph_stats;
+
+/* Graph.ExtendInput's argument (llm/graph.go:1716): token ids plus, in the reference, image spans.
+ * The vision tower is not part of this library: n_images must be 0. */
+typedef struct {
+  const int32_t* ids;
+  int32_t n;
+  int32_t n_images;
+} b200_input;
+
 typedef struct b200_model b200_model;
 typedef struct b200_graph b200_graph;
 
@@ -93,9 +112,14 @@ int32_t b200_graph_past(const b200_graph* g);
  * it forward exposes whatever the cache holds (zeros after creation) and exists for throughput
  * measurements on long contexts that are "already prefilled". The DeltaNet state is not touched. */
 int32_t b200_graph_set_past(b200_graph* g, int32_t past);
-/* Forward = Reset + Extend (:1695). logits: [vocab] of the last row; hidden: [n_embd] output-normed last row. */
+/* Forward = Reset + Extend (:1695). logits: [vocab] of the last row; hidden: [n_embd], the last row of the
+ * residual stream BEFORE output_norm. (The reference's Extend returns `norm`, the head mixer's output, i.e. the
+ * tensor the head reads, llm/graph.go:1775; here the normalisation happens inside the head kernel's staging and
+ * is never materialised, so the un-normed row is what comes back. A host that wants the reference's quantity
+ * applies output_norm to it.) */
 int32_t b200_graph_forward(b200_graph* g, const int32_t* ids, int32_t n, const float** logits, const float** hidden);
 int32_t b200_graph_extend(b200_graph* g, const int32_t* ids, int32_t n, const float** logits, const float** hidden); /* Extend :1709 */
+int32_t b200_graph_extend_input(b200_graph* g, const b200_input* in, const float** logits, const float** hidden);    /* ExtendInput :1716 */
 /* Every row's logits [n][vocab] and residual [n][n_embd]; n <= spec_rows when speculating (ExtendRows :1383). */
 int32_t b200_graph_extend_rows(b200_graph* g, const int32_t* ids, int32_t n, const float** logits, const float** residual);
 /* Last row's logits plus every row's residual (ExtendResidual :1468). */
@@ -109,9 +133,23 @@ int32_t b200_graph_restore(b200_graph* g, int32_t handle);
 int32_t b200_graph_checkpoint_free(b200_graph* g, int32_t handle);
 /* Speculation (Speculate/Keep/Commit/Rewind :1122-1302). */
 int32_t b200_graph_speculate(b200_graph* g, int32_t on);
+int32_t b200_graph_speculating(const b200_graph* g);                                      /* Speculating :1157 */
+/* SpeculateFirst (:1166): a speculative pass is then ended by Commit (all rows) or KeepFirst (row 0 only), never
+ * by Rewind. Here every row of a speculative pass already leaves its own state plane, so the switch costs nothing
+ * and only arms that rule. */
+int32_t b200_graph_speculate_first(b200_graph* g, int32_t on);
+int32_t b200_graph_keep_first(b200_graph* g);
 int32_t b200_graph_keep(b200_graph* g, int32_t k);
 int32_t b200_graph_commit(b200_graph* g);
 int32_t b200_graph_rewind(b200_graph* g);
+
+/* Row r of the residual the last pass left, [n_embd] into dst (ResidualRow :1454): after a one-token Extend
+ * row 0 is that token's, after DecodeRows row r is slot r's. */
+int32_t b200_graph_residual_row(b200_graph* g, int32_t r, float* dst);
+/* Distinct experts the last pass's last layer routed to, over all its rows (PassExperts :1677). */
+int32_t b200_graph_pass_experts(b200_graph* g, int32_t* out);
+int32_t b200_graph_stats_get(const b200_graph* g, b200_graph_stats* out);                  /* Stats :527-589 */
+int32_t b200_graph_stats_reset(b200_graph* g);
 
 /* Device-resident greedy decoding: only token ids cross the bus. Each of n slots advances
  * `steps` tokens starting from first_ids; out_ids is [steps][n]. */
@@ -138,6 +176,15 @@ int64_t b200_graph_trace(b200_graph* g, int32_t what, void* dst, int64_t nbytes)
  * one position ahead), runs the draft layer on the current slot's draft cache, returns the
  * draft's residual [n][n_embd] and logits over the first `vocab_k` ids [n][vocab_k]. */
 int32_t b200_draft_rows(b200_graph* g, const float* hs, const int32_t* ids, int32_t n, int32_t vocab_k, const float** residual, const float** logits);
+/* The draft's lm head projects onto the first k ids only for calls that pass vocab_k = 0 (SetVocab, llm/mtp.go:675);
+ * k a multiple of 16, 0 = the whole vocabulary. */
+int32_t b200_draft_set_vocab(b200_graph* g, int32_t k);
+/* Slot whose draft cache the draft calls use (MTPHead.UseSlot :514); b200_graph_use_slot moves it along too. */
+int32_t b200_draft_use_slot(b200_graph* g, int32_t slot);
+int32_t b200_draft_slots(const b200_graph* g);                                            /* Slots :512 */
+int32_t b200_draft_reset(b200_graph* g);                                                  /* Reset :508 */
+int32_t b200_draft_max_rows(const b200_graph* g);                                         /* MaxRows :536 */
+int32_t b200_draft_wide(const b200_graph* g);                                             /* Wide / NEmbd :440: one residual stream, so both are n_embd */
 int32_t b200_draft_past(const b200_graph* g);
 int32_t b200_draft_rewind(b200_graph* g, int32_t past);
 
@@ -152,15 +199,29 @@ int32_t b200_qgemv(uint32_t type, const void* host_w, int64_t rows, int64_t k, c
  * arithmetic: dequantised weights rounded to fp16 (shaders/llm_gemm.comp MODE 2). */
 int32_t b200_qgemm(uint32_t type, const void* host_w, int64_t rows, int64_t k, const float* host_x, int32_t m, int32_t tile_rows, float* host_y);
 /* No counterpart in the reference. The same projection for callers that cannot allocate device
- * memory (inside a stream capture, on a thread that may not take the allocator's lock, or under
- * a fixed memory budget): all pointers are DEVICE pointers the caller already owns, and the fp16
- * staging of the activations lives in a 256 KiB file-scope device array that every GPU loading
- * the library holds until exit. Limits: Q4_K / Q5_K weights in checkpoint block layout, 16-byte
- * aligned; m <= 8 rows; k a multiple of 256, at most 16384; larger sizes are refused. The first
- * call on a device looks the array's address up (make it before any stream capture). All calls
- * share the array, so calls that overlap on the device race; the call returns after its work is
- * done and calls no cudaMalloc / cudaFree. */
+ * memory when they need it: a latency-critical thread that must not block on the allocator's lock
+ * (cudaMalloc / cudaFree serialise on it and may synchronise the device), or a process whose
+ * device memory was budgeted up front. All pointers are DEVICE pointers the caller already owns;
+ * the fp16 staging of the activations (256 KiB) and the word a timed-out wait is reported through
+ * live in file-scope device arrays that every GPU loading the library holds until exit.
+ * Limits: Q4_K / Q5_K weights in checkpoint block layout, 16-byte aligned; m <= 8 rows; k a
+ * multiple of 256, at most 16384; and m staged rows of k elements plus one stage of 16 weight rows
+ * must fit the kernel's 220 KiB of shared memory (e.g. Q4_K: 8 rows up to k = 7680, 1 row up to
+ * k = 16384; Q5_K: 8 rows up to k = 7168, 1 row up to k = 16128). Anything larger is refused with
+ * B200_ECAPACITY and a message that names the largest m that fits that k.
+ * The work is queued on the legacy default stream and the call returns after it is done; what the
+ * caller queued on a non-blocking stream to produce dev_x must have finished before the call. The
+ * first call on a device looks the arrays' addresses up: make it before any stream capture. All
+ * calls share the arrays, which keep the last call's contents (the error word is cleared by every
+ * call, the staging is overwritten where it is read), so calls that overlap on the device race.
+ * Calls no cudaMalloc, cudaFree or other allocating routine. B200_ETIMEOUT: a bounded wait inside
+ * the kernel gave up and dev_y is not valid. */
 int32_t b200_qgemv_static(uint32_t type, const void* dev_w, int64_t rows, int64_t k, const float* dev_x, int32_t m, float* dev_y);
+/* Failure-detection check that faults nothing: queues, on the graph's stream, a small kernel whose bounded
+ * wait can never be satisfied (its barrier expects more bytes than are copied). It gives up after its limit,
+ * sets the graph's error word and returns; the next pass on the graph then reports B200_ETIMEOUT and clears
+ * the word, after which the graph is usable again. */
+int32_t b200_graph_inject_wait_timeout(b200_graph* g);
 /* The repo's quantiser on the device (llm/quantk.go:87-179): rows x k f32 -> GGUF blocks. */
 int32_t b200_quantize(uint32_t type, const float* host_src, int64_t rows, int64_t k, void* host_dst);
 

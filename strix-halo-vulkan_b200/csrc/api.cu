@@ -1,6 +1,7 @@
 // extern "C" surface of libb200llm.so (include/b200_llm.h).
 #include <cstring>
 #include <new>
+#include <vector>
 
 #include "graph.h"
 
@@ -8,6 +9,21 @@ using namespace b200;
 
 struct b200_model { Model m; };
 struct b200_graph { Graph g; };
+
+namespace {
+struct Scratch {   // device temporaries of one call
+  std::vector<void*> ptrs;
+  ~Scratch() { for (void* p : ptrs) cudaFree(p); }
+  template <class T> int get(T** out, size_t bytes) {
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes ? bytes : 1);
+    if (e != cudaSuccess) { set_error(std::string("device allocation of ") + std::to_string(bytes) + " bytes failed: " + cudaGetErrorString(e)); return ENOMEM_; }
+    ptrs.push_back(p);
+    *out = (T*)p;
+    return OK;
+  }
+};
+}  // namespace
 
 extern "C" {
 
@@ -77,7 +93,7 @@ int32_t b200_graph_nkv(const b200_graph* g) { return g ? g->g.o.n_kv : 0; }
 int32_t b200_graph_use_slot(b200_graph* g, int32_t slot) {
   if (!g) return EINVAL_;
   if (slot < 0 || slot >= g->g.o.slots) { set_error("use_slot: slot " + std::to_string(slot) + " does not exist"); return EINVAL_; }
-  g->g.cur = slot; g->g.spec_n = 0;
+  g->g.cur = slot; g->g.dcur = slot; g->g.spec_n = 0;
   return OK;
 }
 int32_t b200_graph_reset(b200_graph* g) { if (!g) return EINVAL_; return g->g.reset_slot(g->g.cur); }
@@ -99,6 +115,12 @@ int32_t b200_graph_extend(b200_graph* g, const int32_t* ids, int32_t n, const fl
   if (!g || !ids) { set_error("extend: null argument"); return EINVAL_; }
   PassFlags f;
   return g->g.extend(ids, n, f, logits, hidden);
+}
+int32_t b200_graph_extend_input(b200_graph* g, const b200_input* in, const float** logits, const float** hidden) {
+  if (!g || !in || !in->ids) { set_error("extend_input: null argument"); return EINVAL_; }
+  if (in->n_images != 0) { set_error("extend_input: this library has no vision tower; inputs with images are refused"); return EINVAL_; }
+  PassFlags f;
+  return g->g.extend(in->ids, in->n, f, logits, hidden);
 }
 int32_t b200_graph_extend_rows(b200_graph* g, const int32_t* ids, int32_t n, const float** logits, const float** residual) {
   if (!g || !ids) { set_error("extend_rows: null argument"); return EINVAL_; }
@@ -132,9 +154,27 @@ int32_t b200_graph_speculate(b200_graph* g, int32_t on) {
   g->g.speculating = on != 0;
   return OK;
 }
+int32_t b200_graph_speculating(const b200_graph* g) { return g && g->g.speculating ? 1 : 0; }
+int32_t b200_graph_speculate_first(b200_graph* g, int32_t on) {
+  if (!g) return EINVAL_;
+  if (g->g.spec_n > 0) { set_error("speculate_first: a speculative pass is in flight; commit or rewind it first"); return ESTATE; }
+  g->g.spec_first = on != 0;
+  return OK;
+}
 int32_t b200_graph_keep(b200_graph* g, int32_t k) { if (!g) return EINVAL_; return g->g.keep(k); }
+int32_t b200_graph_keep_first(b200_graph* g) { if (!g) return EINVAL_; return g->g.keep(1); }
 int32_t b200_graph_commit(b200_graph* g) { if (!g) return EINVAL_; return g->g.keep(g->g.spec_n); }
-int32_t b200_graph_rewind(b200_graph* g) { if (!g) return EINVAL_; return g->g.keep(0); }
+int32_t b200_graph_rewind(b200_graph* g) {
+  if (!g) return EINVAL_;
+  // with SpeculateFirst on, row 0 of a pass is a token already emitted: the pass ends by Commit or KeepFirst (llm/graph.go:1166-1178)
+  if (g->g.spec_first && g->g.spec_n > 0) { set_error("rewind: with speculate_first on a pass is ended by commit or keep_first"); return ESTATE; }
+  return g->g.keep(0);
+}
+int32_t b200_graph_residual_row(b200_graph* g, int32_t r, float* dst) { if (!g || !dst) { set_error("residual_row: null argument"); return EINVAL_; } return g->g.residual_row(r, dst); }
+int32_t b200_graph_pass_experts(b200_graph* g, int32_t* out) { if (!g || !out) { set_error("pass_experts: null argument"); return EINVAL_; } return g->g.pass_experts(out); }
+int32_t b200_graph_stats_get(const b200_graph* g, b200_graph_stats* out) { if (!g || !out) return EINVAL_; *out = g->g.stats; return OK; }
+int32_t b200_graph_stats_reset(b200_graph* g) { if (!g) return EINVAL_; g->g.stats = b200_graph_stats{}; return OK; }
+int32_t b200_graph_inject_wait_timeout(b200_graph* g) { if (!g) return EINVAL_; return g->g.inject_wait_timeout(); }
 
 int32_t b200_graph_generate_greedy(b200_graph* g, const int32_t* slots, const int32_t* first_ids, int32_t n, int32_t steps, int32_t* out_ids) {
   if (!g || !slots || !first_ids || !out_ids) { set_error("generate_greedy: null argument"); return EINVAL_; }
@@ -157,20 +197,39 @@ int32_t b200_draft_rows(b200_graph* g, const float* hs, const int32_t* ids, int3
   if (!g || !hs || !ids) { set_error("draft_rows: null argument"); return EINVAL_; }
   return g->g.draft_rows(hs, ids, n, vocab_k, residual, logits);
 }
-int32_t b200_draft_past(const b200_graph* g) { return g ? g->g.draft_past[g->g.cur] : 0; }
+int32_t b200_draft_past(const b200_graph* g) { return g ? g->g.draft_past[g->g.dcur] : 0; }
 int32_t b200_draft_rewind(b200_graph* g, int32_t past) {
   if (!g) return EINVAL_;
-  if (past < 0 || past > g->g.draft_past[g->g.cur]) { set_error("draft_rewind: position outside the draft cache"); return EINVAL_; }
-  g->g.draft_past[g->g.cur] = past;
+  if (past < 0 || past > g->g.draft_past[g->g.dcur]) { set_error("draft_rewind: position outside the draft cache"); return EINVAL_; }
+  g->g.draft_past[g->g.dcur] = past;
   return OK;
 }
+int32_t b200_draft_set_vocab(b200_graph* g, int32_t k) {
+  if (!g) return EINVAL_;
+  if (k < 0 || k % 16 || k > g->g.m->c.vocab) { set_error("draft_set_vocab: a multiple of 16 up to the vocabulary size, or 0 for all of it"); return EINVAL_; }
+  g->g.draft_vocab_default = k == g->g.m->c.vocab ? 0 : k;
+  return OK;
+}
+int32_t b200_draft_use_slot(b200_graph* g, int32_t slot) {
+  if (!g) return EINVAL_;
+  if (slot < 0 || slot >= g->g.o.slots) { set_error("draft_use_slot: draft cache slot " + std::to_string(slot) + " of " + std::to_string(g->g.o.slots)); return EINVAL_; }
+  g->g.dcur = slot;
+  return OK;
+}
+int32_t b200_draft_slots(const b200_graph* g) { return g && g->g.m->c.has_draft ? g->g.o.slots : 0; }
+int32_t b200_draft_reset(b200_graph* g) { if (!g) return EINVAL_; g->g.draft_past[g->g.dcur] = 0; return OK; }
+int32_t b200_draft_max_rows(const b200_graph* g) { return g ? g->g.LR : 0; }
+int32_t b200_draft_wide(const b200_graph* g) { return g ? g->g.m->c.n_embd : 0; }
 
 // ---- unit entry points --------------------------------------------------------------------
+// They run on the device that is current in the calling thread and free what they allocate on
+// every path out.
 static int need_device() {
   int n = 0;
   if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) { set_error("no CUDA device: this library has no CPU path"); return ECUDA; }
   return OK;
 }
+
 
 int32_t b200_dequantize(uint32_t type, const void* host_data, int64_t n, float* host_out) {
   B200_TRY(need_device());
@@ -178,77 +237,65 @@ int32_t b200_dequantize(uint32_t type, const void* host_data, int64_t n, float* 
   if (!host_data || !host_out || !block_geometry(type, &e, &nb) || n % e || n <= 0) { set_error("dequantize: bad type or element count"); return EINVAL_; }
   const int64_t bytes = gguf_row_bytes(type, n);
   DTensor t; t.type = type; t.k = n; t.rows = 1; t.stride = device_row_stride(type, n);
-  uint8_t *src = nullptr; float* out = nullptr;
-  B200_CUDA(cudaMalloc((void**)&src, (size_t)bytes));
-  B200_CUDA(cudaMalloc((void**)&t.data, (size_t)t.stride + 256));
-  B200_CUDA(cudaMalloc((void**)&out, (size_t)n * sizeof(float)));
-  int s = cudaMemcpy(src, host_data, (size_t)bytes, cudaMemcpyHostToDevice) == cudaSuccess ? OK : ECUDA;
-  if (s == OK) s = repack_rows(type, n, 1, src, t.data, 0);
-  if (s == OK) s = dequant_rows(t, 0, 1, out, 0);
-  if (s == OK && cudaMemcpy(host_out, out, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) { set_error("dequantize: copy back failed"); s = ECUDA; }
-  cudaFree(src); cudaFree(t.data); cudaFree(out);
-  return s;
+  Scratch sc;
+  uint8_t* src = nullptr; float* out = nullptr;
+  B200_TRY(sc.get(&src, (size_t)bytes)); B200_TRY(sc.get(&t.data, (size_t)t.stride + 256)); B200_TRY(sc.get(&out, (size_t)n * sizeof(float)));
+  B200_CUDA(cudaMemcpy(src, host_data, (size_t)bytes, cudaMemcpyHostToDevice));
+  B200_TRY(repack_rows(type, n, 1, src, t.data, 0));
+  B200_TRY(dequant_rows(t, 0, 1, out, 0));
+  B200_CUDA(cudaMemcpy(host_out, out, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost));
+  return OK;
+}
+
+// weights in device layout, activations as fp16 rows, an error word: what both projection entry points stage
+static int stage_projection(Scratch& sc, uint32_t type, const void* host_w, int64_t rows, int64_t k, const float* host_x, int32_t mrows,
+                            DTensor* t, __half** x16, float** y, int** err) {
+  const int64_t rb = gguf_row_bytes(type, k);
+  if (rb < 0) { set_error("projection: bad type or row length"); return EINVAL_; }
+  t->type = type; t->k = k; t->rows = rows; t->stride = device_row_stride(type, k);
+  uint8_t* src = nullptr; float* xf = nullptr;
+  B200_TRY(sc.get(&src, (size_t)(rb * rows))); B200_TRY(sc.get(&t->data, (size_t)(t->stride * rows) + 256));
+  B200_TRY(sc.get(&xf, (size_t)mrows * k * sizeof(float))); B200_TRY(sc.get(x16, (size_t)mrows * k * sizeof(__half)));
+  B200_TRY(sc.get(y, (size_t)mrows * rows * sizeof(float))); B200_TRY(sc.get(err, sizeof(int)));
+  B200_CUDA(cudaMemset(*err, 0, sizeof(int)));
+  B200_CUDA(cudaMemcpy(src, host_w, (size_t)(rb * rows), cudaMemcpyHostToDevice));
+  B200_CUDA(cudaMemcpy(xf, host_x, (size_t)mrows * k * sizeof(float), cudaMemcpyHostToDevice));
+  B200_TRY(repack_rows(type, k, rows, src, t->data, 0));
+  B200_TRY(quantize_rows_device(T_F16, xf, mrows, k, (uint8_t*)*x16, 0));
+  return OK;
+}
+static int finish_projection(const char* who, const float* y, const int* err, int64_t n, float* host_y) {
+  int herr = 0;
+  B200_CUDA(cudaMemcpy(&herr, err, sizeof(int), cudaMemcpyDeviceToHost));
+  if (herr != 0) { set_error(std::string(who) + ": a bounded wait gave up"); return ETIMEOUT; }
+  B200_CUDA(cudaMemcpy(host_y, y, (size_t)n * sizeof(float), cudaMemcpyDeviceToHost));
+  return OK;
 }
 
 int32_t b200_qgemv(uint32_t type, const void* host_w, int64_t rows, int64_t k, const float* host_x, int32_t mrows, float* host_y) {
   B200_TRY(need_device());
   if (!host_w || !host_x || !host_y || rows <= 0 || mrows <= 0) { set_error("qgemv: bad argument"); return EINVAL_; }
-  const int64_t rb = gguf_row_bytes(type, k);
-  if (rb < 0) { set_error("qgemv: bad type or row length"); return EINVAL_; }
-  DTensor t; t.type = type; t.k = k; t.rows = rows; t.stride = device_row_stride(type, k);
-  uint8_t* src = nullptr; float *xf = nullptr, *y = nullptr; __half* x16 = nullptr;
-  B200_CUDA(cudaMalloc((void**)&src, (size_t)(rb * rows)));
-  B200_CUDA(cudaMalloc((void**)&t.data, (size_t)(t.stride * rows) + 256));
-  B200_CUDA(cudaMalloc((void**)&xf, (size_t)mrows * k * sizeof(float)));
-  B200_CUDA(cudaMalloc((void**)&x16, (size_t)mrows * k * sizeof(__half)));
-  B200_CUDA(cudaMalloc((void**)&y, (size_t)mrows * rows * sizeof(float)));
-  int s = OK;
-  if (cudaMemcpy(src, host_w, (size_t)(rb * rows), cudaMemcpyHostToDevice) != cudaSuccess || cudaMemcpy(xf, host_x, (size_t)mrows * k * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess) s = ECUDA;
-  if (s == OK) s = repack_rows(type, k, rows, src, t.data, 0);
-  if (s == OK) s = quantize_rows_device(T_F16, xf, mrows, k, (uint8_t*)x16, 0);
-  if (s == OK) {
-    QGemvParams p{};
-    p.w[0] = t.data; p.seg_end[0] = (int)rows; p.nseg = 1; p.stride = t.stride; p.K = (int)k; p.N = (int)rows; p.M = mrows; p.xcols = mrows < QG_MAXCOLS ? mrows : QG_MAXCOLS;
-    p.x = x16; p.ldx = k; p.y = y; p.ldy = rows; p.x_div = 1;
-    s = launch_qgemv(type, PRO_F16, EPI_STORE, false, false, p, 0, false, 0);
-  }
-  if (s == OK && cudaMemcpy(host_y, y, (size_t)mrows * rows * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) { set_error(std::string("qgemv: ") + cudaGetErrorString(cudaGetLastError())); s = ECUDA; }
-  cudaFree(src); cudaFree(t.data); cudaFree(xf); cudaFree(x16); cudaFree(y);
-  return s;
+  Scratch sc; DTensor t; __half* x16 = nullptr; float* y = nullptr; int* err = nullptr;
+  B200_TRY(stage_projection(sc, type, host_w, rows, k, host_x, mrows, &t, &x16, &y, &err));
+  QGemvParams p{};
+  p.w[0] = t.data; p.seg_end[0] = (int)rows; p.nseg = 1; p.stride = t.stride; p.K = (int)k; p.N = (int)rows; p.M = mrows; p.xcols = mrows < QG_MAXCOLS ? mrows : QG_MAXCOLS;
+  p.x = x16; p.ldx = k; p.y = y; p.ldy = rows; p.x_div = 1; p.err = err;
+  B200_TRY(launch_qgemv(type, PRO_F16, EPI_STORE, false, false, p, 0, false, 0));
+  return finish_projection("qgemv", y, err, (int64_t)mrows * rows, host_y);
 }
 
 int32_t b200_qgemm(uint32_t type, const void* host_w, int64_t rows, int64_t k, const float* host_x, int32_t mrows, int32_t tile_rows, float* host_y) {
   B200_TRY(need_device());
   if (!host_w || !host_x || !host_y || rows <= 0 || mrows <= 0) { set_error("qgemm: bad argument"); return EINVAL_; }
-  const int64_t rb = gguf_row_bytes(type, k);
-  if (rb < 0) { set_error("qgemm: bad type or row length"); return EINVAL_; }
-  DTensor t; t.type = type; t.k = k; t.rows = rows; t.stride = device_row_stride(type, k);
-  uint8_t* src = nullptr; float *xf = nullptr, *y = nullptr; __half* x16 = nullptr;
-  B200_CUDA(cudaMalloc((void**)&src, (size_t)(rb * rows)));
-  B200_CUDA(cudaMalloc((void**)&t.data, (size_t)(t.stride * rows) + 256));
-  B200_CUDA(cudaMalloc((void**)&xf, (size_t)mrows * k * sizeof(float)));
-  B200_CUDA(cudaMalloc((void**)&x16, (size_t)mrows * k * sizeof(__half)));
-  B200_CUDA(cudaMalloc((void**)&y, (size_t)mrows * rows * sizeof(float)));
-  int s = OK;
-  if (cudaMemcpy(src, host_w, (size_t)(rb * rows), cudaMemcpyHostToDevice) != cudaSuccess || cudaMemcpy(xf, host_x, (size_t)mrows * k * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess) s = ECUDA;
-  if (s == OK) s = repack_rows(type, k, rows, src, t.data, 0);
-  if (s == OK) s = quantize_rows_device(T_F16, xf, mrows, k, (uint8_t*)x16, 0);
+  Scratch sc; DTensor t; __half* x16 = nullptr; float* y = nullptr; int* err = nullptr;
+  B200_TRY(stage_projection(sc, type, host_w, rows, k, host_x, mrows, &t, &x16, &y, &err));
   alignas(64) unsigned char tmap[128];
-  if (s == OK) s = make_x_tensor_map(x16, mrows, (int)k, tile_rows, tmap);
-  int* err = nullptr;
-  if (s == OK && (cudaMalloc((void**)&err, sizeof(int)) != cudaSuccess || cudaMemset(err, 0, sizeof(int)) != cudaSuccess)) s = ECUDA;
-  if (s == OK) {
-    QGemmParams p{};
-    p.w = t.data; p.one.expert = 0; p.one.x_row0 = 0; p.one.count = mrows; p.one.y_row0 = 0; p.max_problems = 1; p.max_count = mrows;
-    p.stride = t.stride; p.K = (int)k; p.N = (int)rows; p.y = y; p.ldy = rows; p.err = err;
-    s = launch_qgemm(type, GEMM_STORE, tile_rows, p, tmap, false, 0);
-  }
-  int herr = 0;
-  if (s == OK && cudaMemcpy(&herr, err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) { set_error(std::string("qgemm: ") + cudaGetErrorString(cudaGetLastError())); s = ECUDA; }
-  if (s == OK && herr != 0) { set_error("qgemm: a bounded barrier wait gave up"); s = ETIMEOUT; }
-  if (s == OK && cudaMemcpy(host_y, y, (size_t)mrows * rows * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) { set_error(std::string("qgemm: ") + cudaGetErrorString(cudaGetLastError())); s = ECUDA; }
-  cudaFree(src); cudaFree(t.data); cudaFree(xf); cudaFree(x16); cudaFree(y); cudaFree(err);
-  return s;
+  B200_TRY(make_x_tensor_map(x16, mrows, (int)k, tile_rows, tmap));
+  QGemmParams p{};
+  p.w = t.data; p.one.expert = 0; p.one.x_row0 = 0; p.one.count = mrows; p.one.y_row0 = 0; p.max_problems = 1; p.max_count = mrows;
+  p.stride = t.stride; p.K = (int)k; p.N = (int)rows; p.y = y; p.ldy = rows; p.err = err;
+  B200_TRY(launch_qgemm(type, GEMM_STORE, tile_rows, p, tmap, false, 0));
+  return finish_projection("qgemm", y, err, (int64_t)mrows * rows, host_y);
 }
 
 int32_t b200_qgemv_static(uint32_t type, const void* dev_w, int64_t rows, int64_t k, const float* dev_x, int32_t m, float* dev_y) {
@@ -260,14 +307,12 @@ int32_t b200_quantize(uint32_t type, const float* host_src, int64_t rows, int64_
   B200_TRY(need_device());
   const int64_t rb = gguf_row_bytes(type, k);
   if (!host_src || !host_dst || rb < 0 || rows <= 0) { set_error("quantize: bad argument"); return EINVAL_; }
-  float* f = nullptr; uint8_t* q = nullptr;
-  B200_CUDA(cudaMalloc((void**)&f, (size_t)rows * k * sizeof(float)));
-  B200_CUDA(cudaMalloc((void**)&q, (size_t)(rb * rows)));
-  int s = cudaMemcpy(f, host_src, (size_t)rows * k * sizeof(float), cudaMemcpyHostToDevice) == cudaSuccess ? OK : ECUDA;
-  if (s == OK) s = quantize_rows_device(type, f, rows, k, q, 0);
-  if (s == OK && cudaMemcpy(host_dst, q, (size_t)(rb * rows), cudaMemcpyDeviceToHost) != cudaSuccess) { set_error("quantize: copy back failed"); s = ECUDA; }
-  cudaFree(f); cudaFree(q);
-  return s;
+  Scratch sc; float* f = nullptr; uint8_t* q = nullptr;
+  B200_TRY(sc.get(&f, (size_t)rows * k * sizeof(float))); B200_TRY(sc.get(&q, (size_t)(rb * rows)));
+  B200_CUDA(cudaMemcpy(f, host_src, (size_t)rows * k * sizeof(float), cudaMemcpyHostToDevice));
+  B200_TRY(quantize_rows_device(type, f, rows, k, q, 0));
+  B200_CUDA(cudaMemcpy(host_dst, q, (size_t)(rb * rows), cudaMemcpyDeviceToHost));
+  return OK;
 }
 
 }  // extern "C"

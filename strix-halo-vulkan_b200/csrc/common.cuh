@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <string>
 
 namespace b200 {
@@ -42,6 +43,32 @@ const char* last_error();
       b200::set_error(std::string(#expr) + ": " + cudaGetErrorString(_e));                       \
       return b200::ECUDA;                                                                        \
     }                                                                                            \
+  } while (0)
+
+// Settings made with cudaFuncSetAttribute, and the SM count, belong to the device that is current when
+// they are made or read, and one process may hold graphs on several devices (the ABI takes a device
+// index per model): "done once" is therefore kept per device. Handles may be driven from different
+// threads, so the marks are atomic; two threads that both find a mark unset both make the (idempotent) setting.
+constexpr int MAX_DEVICES = 64;
+struct OncePerDevice {
+  std::atomic<int> done[MAX_DEVICES];
+};
+inline int current_device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) dev = 0;
+  return dev % MAX_DEVICES;
+}
+// SM count of the current device (cached per device); 0 on failure with the error set
+int sm_count_current();
+
+#define B200_ONCE_PER_DEVICE(expr)                                   \
+  do {                                                               \
+    static b200::OncePerDevice _once;                                \
+    const int _slot = b200::current_device_slot();                   \
+    if (_once.done[_slot].load(std::memory_order_acquire) == 0) {    \
+      B200_CUDA(expr);                                               \
+      _once.done[_slot].store(1, std::memory_order_release);         \
+    }                                                                \
   } while (0)
 
 #define B200_TRY(expr)                   \
@@ -113,9 +140,9 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src, u
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 // Bounded wait: returns false if the phase did not complete within the limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 22)) {
   const uint32_t a = (uint32_t)__cvta_generic_to_shared(bar);
-  for (uint32_t i = 0; i < (1u << 22); i++) {
+  for (uint32_t i = 0; i < limit; i++) {
     uint32_t ok;
     asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(ok) : "r"(a), "r"(parity) : "memory");
     if (ok) return true;

@@ -4,7 +4,9 @@
 #include "graph.h"
 
 #include <algorithm>
+#include <chrono>
 #include <cmath>
+#include <set>
 #include <cstdlib>
 #include <cstring>
 
@@ -468,12 +470,14 @@ int Graph::run_rows(const int32_t* ids, const int* slots, const int* pos, int M,
     if (ids[i] < 0 || ids[i] >= c.vocab) { set_error("token id " + std::to_string(ids[i]) + " is outside the vocabulary"); return EINVAL_; }
   }
   B200_CUDA(cudaSetDevice(m->device));
+  const auto host_t0 = std::chrono::steady_clock::now();
   fill_stage(stage, MR, ids, slots, pos, M, sq, lrows);
   pass_max_n = 1;
   for (const SeqDesc& s : sq) pass_max_n = std::max(pass_max_n, s.n);
   const int n_lr = (int)lrows.size(), n_seq = (int)sq.size();
   const int NV = f.draft && draft_vocab > 0 ? draft_vocab : c.vocab;
   bool single = !f.spec && !f.draft && !o.trace && o.use_cuda_graph && n_seq == M && n_lr == M && !f.want_residual;
+  B200_CUDA(cudaEventRecord(ev0, st));
   if (single) {
     auto it = decode_graphs.find(M);
     if (it == decode_graphs.end()) {
@@ -502,10 +506,30 @@ int Graph::run_rows(const int32_t* ids, const int* slots, const int* pos, int M,
   }
   if (f.want_residual) B200_CUDA(cudaMemcpyAsync(resid_host + (size_t)resid_off * c.n_embd, h, (size_t)M * c.n_embd * sizeof(float), cudaMemcpyDeviceToHost, st));
   B200_CUDA(cudaMemcpyAsync(hidden_host, h + (size_t)(M - 1) * c.n_embd, (size_t)c.n_embd * sizeof(float), cudaMemcpyDeviceToHost, st));
+  B200_CUDA(cudaEventRecord(ev1, st));
+  B200_TRY(finish_pass());
+  last_rows = M;
+  float ms = 0.f;
+  B200_CUDA(cudaEventElapsedTime(&ms, ev0, ev1));
+  stats.passes++; stats.rows += M; stats.launches += last_launches; stats.device_ms += ms;
+  stats.host_ms += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - host_t0).count();
+  stats.last_rows = M; stats.last_launches = last_launches; stats.last_device_ms = ms;
+  return OK;
+}
+
+// Reads the error word back with the pass's results. A bounded wait that gave up is reported once:
+// the word is cleared so that the graph stays usable (what the slot held is the caller's to forget,
+// as the reference's scheduler does after a failed unit, backend/llm_sched.go:713-717).
+int Graph::finish_pass() {
   B200_CUDA(cudaMemcpyAsync(err_host, err_flag, sizeof(int), cudaMemcpyDeviceToHost, st));
   B200_CUDA(cudaStreamSynchronize(st));
-  if (*err_host != 0) { set_error("a kernel gave up a bounded wait for its weight copies"); return ETIMEOUT; }
-  last_rows = M;
+  if (*err_host != 0) {
+    *err_host = 0;
+    B200_CUDA(cudaMemsetAsync(err_flag, 0, sizeof(int), st));
+    B200_CUDA(cudaStreamSynchronize(st));
+    set_error("a kernel gave up a bounded wait (a copy or a peer that never arrived); the pass's results are not valid");
+    return ETIMEOUT;
+  }
   return OK;
 }
 
@@ -600,10 +624,10 @@ int Graph::generate_greedy(const int32_t* slots_in, const int32_t* first, int n,
   }
   B200_CUDA(cudaEventRecord(ev1, st));
   B200_CUDA(cudaMemcpyAsync(ids_host, history, (size_t)steps * n * sizeof(int32_t), cudaMemcpyDeviceToHost, st));
-  B200_CUDA(cudaMemcpyAsync(err_host, err_flag, sizeof(int), cudaMemcpyDeviceToHost, st));
-  B200_CUDA(cudaStreamSynchronize(st));
-  if (*err_host != 0) { set_error("a kernel gave up a bounded wait for its weight copies"); return ETIMEOUT; }
+  B200_TRY(finish_pass());
   B200_CUDA(cudaEventElapsedTime(&last_ms, ev0, ev1));
+  stats.passes += steps; stats.rows += (int64_t)steps * n; stats.launches += (int64_t)steps * last_launches; stats.device_ms += last_ms;
+  stats.last_rows = n; stats.last_launches = last_launches; stats.last_device_ms = last_ms / steps;
   memcpy(out, ids_host, (size_t)steps * n * sizeof(int32_t));
   for (int i = 0; i < n; i++) past[slots[i]] += steps;
   spec_n = 0;
@@ -614,19 +638,20 @@ int Graph::draft_rows(const float* hs, const int32_t* ids, int n, int vocab_k, c
   const b200_config& c = m->c;
   if (!c.has_draft) { set_error("draft_rows: the checkpoint has no draft layer"); return ESTATE; }
   if (n <= 0 || n > LR) { set_error("draft_rows: row count out of range"); return ECAPACITY; }
+  if (vocab_k <= 0 && draft_vocab_default > 0) vocab_k = draft_vocab_default;
   if (vocab_k <= 0 || vocab_k > c.vocab) vocab_k = c.vocab;
   if (vocab_k % 16) { set_error("draft_rows: vocab_k must be a multiple of 16"); return EINVAL_; }
-  if (draft_past[cur] + n + 1 > o.n_kv) { set_error("draft_rows: the draft cache is full"); return ECAPACITY; }
+  if (draft_past[dcur] + n + 1 > o.n_kv) { set_error("draft_rows: the draft cache is full"); return ECAPACITY; }
   B200_CUDA(cudaSetDevice(m->device));
   B200_CUDA(cudaMemcpyAsync(hs_buf, hs, (size_t)n * c.n_embd * sizeof(float), cudaMemcpyHostToDevice, st));
   draft_vocab = vocab_k;
-  std::vector<int> slots(n, cur), pos(n), lrows(n);
-  for (int i = 0; i < n; i++) { pos[i] = draft_past[cur] + i; lrows[i] = i; }
-  std::vector<SeqDesc> sq{SeqDesc{cur, 0, n, draft_past[cur]}};
+  std::vector<int> slots(n, dcur), pos(n), lrows(n);
+  for (int i = 0; i < n; i++) { pos[i] = draft_past[dcur] + i; lrows[i] = i; }
+  std::vector<SeqDesc> sq{SeqDesc{dcur, 0, n, draft_past[dcur]}};
   PassFlags f; f.draft = true; f.want_all_logits = true; f.want_residual = true;
   resid_off = 0;
   B200_TRY(run_rows(ids, slots.data(), pos.data(), n, sq, lrows, f));
-  draft_past[cur] += n;
+  draft_past[dcur] += n;
   if (resid) *resid = resid_host;
   if (logits_out) *logits_out = logits_host;
   return OK;
@@ -695,6 +720,32 @@ int Graph::restore(int handle) {
   B200_CUDA(cudaStreamSynchronize(st));
   past[cur] = ck.past;
   spec_n = 0;
+  return OK;
+}
+
+int Graph::inject_wait_timeout() {
+  B200_CUDA(cudaSetDevice(m->device));
+  return launch_wait_timeout_probe(err_flag, st);
+}
+
+int Graph::residual_row(int r, float* dst) {
+  if (r < 0 || r >= last_rows) { set_error("residual_row: the last pass had " + std::to_string(last_rows) + " rows"); return EINVAL_; }
+  B200_CUDA(cudaSetDevice(m->device));
+  B200_CUDA(cudaMemcpyAsync(dst, h + (size_t)r * m->c.n_embd, (size_t)m->c.n_embd * sizeof(float), cudaMemcpyDeviceToHost, st));
+  B200_CUDA(cudaStreamSynchronize(st));
+  return OK;
+}
+
+int Graph::pass_experts(int* out) {
+  // the routing buffers are shared by all layers: what is readable after a pass is the last layer's selection
+  const int used = m->c.n_expert_used;
+  if (last_rows <= 0) { *out = 0; return OK; }
+  std::vector<int32_t> tk((size_t)last_rows * used);
+  B200_CUDA(cudaSetDevice(m->device));
+  B200_CUDA(cudaMemcpyAsync(tk.data(), topk, tk.size() * sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+  B200_CUDA(cudaStreamSynchronize(st));
+  std::set<int32_t> seen(tk.begin(), tk.end());
+  *out = (int)seen.size();
   return OK;
 }
 

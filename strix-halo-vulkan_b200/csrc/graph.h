@@ -55,8 +55,11 @@ struct Graph {
   std::vector<int> past, draft_past;
   int cur = 0;
   // speculation
-  bool speculating = false;
+  bool speculating = false, spec_first = false;
   int spec_pos0 = -1, spec_n = 0;
+  int dcur = 0;        // slot whose draft cache the draft calls read and write (MTPHead.UseSlot)
+  // running totals over the passes this graph ran (the reference's GraphStats: llm/graph.go:527-589)
+  b200_graph_stats stats{};
   // host staging (pinned)
   uint8_t* stage = nullptr; size_t stage_bytes = 0;
   float *logits_host = nullptr, *resid_host = nullptr, *hidden_host = nullptr;
@@ -70,7 +73,7 @@ struct Graph {
   std::map<int, float*> decode_h;  // residual buffer a replayed decode graph of M rows finishes in
   long long* timeline = nullptr;  // [launch][8] phase timestamps when B200_TIMELINE is set
   int timeline_cap = 0;
-  int launches = 0, last_launches = 0, draft_vocab = 0, resid_off = 0;
+  int launches = 0, last_launches = 0, draft_vocab = 0, draft_vocab_default = 0, resid_off = 0;
   float last_ms = 0.f;
   // checkpoints: DeltaNet state + rings of a slot at a token boundary
   struct Ckpt { int slot, past; std::vector<float*> state, ring; };
@@ -93,6 +96,10 @@ struct Graph {
   int checkpoint(int* handle);
   int restore(int handle);
   int64_t trace(int what, void* dst, int64_t nbytes);
+  int residual_row(int r, float* dst);
+  int pass_experts(int* out);
+  int inject_wait_timeout();
+  int finish_pass();
   template <class T> int dalloc(T** p, size_t n, bool zero = true);
 };
 

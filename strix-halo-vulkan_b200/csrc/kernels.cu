@@ -545,8 +545,7 @@ int launch_router(const RouterParams& p, bool pdl, cudaStream_t st) {
   if (p.h != nullptr) {
     if (p.M > 8) { set_error("router: the fused norm handles at most 8 rows"); return EINVAL_; }
     smem = (size_t)p.M * p.H * sizeof(__half);
-    static size_t configured = 0;
-    if (smem > configured) { B200_CUDA(cudaFuncSetAttribute(router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); configured = 200 * 1024; }
+    B200_ONCE_PER_DEVICE(cudaFuncSetAttribute(router_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     if (smem > 200 * 1024) { set_error("router: rows too long for shared memory"); return ECAPACITY; }
   }
   return launch_k(router_kernel, dim3(grid, p.h != nullptr ? 1 : (p.M + 7) / 8), dim3(256), smem, pdl, st, p);
@@ -1547,13 +1546,9 @@ int launch_attn_decode(const AttnParams& p, bool pdl, cudaStream_t st) {
   int s;
   if (p.split_cells >= 256 && ((p.hd == 256 && G == 8) || (p.hd == 128 && G == 4))) {
     // long splits: eight warps fed by bulk copies
-    static bool configured = false;
     const size_t smem = (size_t)8 * 3 * 16 * (p.hd * 2 + 64);
-    if (!configured) {
-      B200_CUDA(cudaFuncSetAttribute(attn_ring_kernel<256, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * 16 * (256 * 2 + 64)));
-      B200_CUDA(cudaFuncSetAttribute(attn_ring_kernel<128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * 16 * (128 * 2 + 64)));
-      configured = true;
-    }
+    B200_ONCE_PER_DEVICE(cudaFuncSetAttribute(attn_ring_kernel<256, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * 16 * (256 * 2 + 64)));
+    B200_ONCE_PER_DEVICE(cudaFuncSetAttribute(attn_ring_kernel<128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 3 * 16 * (128 * 2 + 64)));
     return p.hd == 256 ? launch_k(attn_ring_kernel<256, 8>, grid, dim3(256), smem, pdl, st, p)
                        : launch_k(attn_ring_kernel<128, 4>, grid, dim3(256), smem, pdl, st, p);
   }
@@ -1639,6 +1634,27 @@ __global__ void advance_kernel(int32_t* ids, const int32_t* next, int* row_pos, 
 int launch_advance(int32_t* ids, const int32_t* next, int* row_pos, SeqDesc* seqs, int M, int32_t* history, int* hist_len, cudaStream_t st) {
   if (M > 1024) { set_error("advance: too many rows"); return ECAPACITY; }
   advance_kernel<<<1, 1024, 0, st>>>(ids, next, row_pos, seqs, M, history, hist_len);
+  B200_CUDA(cudaGetLastError());
+  return OK;
+}
+
+// =========================================================================================
+// Failure-detection probe: a bounded wait that nothing can satisfy. The barrier expects 16 bytes of
+// copies and none is issued, so the wait runs out, the error word is set and the kernel returns; no
+// copy is in flight and nothing faults. The host then sees the word exactly as it would after a real
+// copy that never landed.
+// =========================================================================================
+__global__ void wait_timeout_probe_kernel(int* err, uint32_t limit) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    mbar_expect_tx(&bar, 16);
+    if (!mbar_wait(&bar, 0, limit)) atomicExch(err, 1);
+  }
+}
+int launch_wait_timeout_probe(int* err, cudaStream_t st) {
+  wait_timeout_probe_kernel<<<1, 32, 0, st>>>(err, 1u << 16);
   B200_CUDA(cudaGetLastError());
   return OK;
 }

@@ -99,6 +99,9 @@ int launch_attn_pack(const AttnParams& p, bool pdl, cudaStream_t st);
 int launch_attn_decode(const AttnParams& p, bool pdl, cudaStream_t st);
 int launch_attn_merge(const AttnParams& p, bool pdl, cudaStream_t st);
 
+// a one-thread kernel whose bounded wait must run out: sets *err (failure detection without a fault)
+int launch_wait_timeout_probe(int* err, cudaStream_t st);
+
 int launch_argmax(const float* logits, int M, int V, int32_t* out, bool pdl, cudaStream_t st);
 
 // rows of the same pass: ids[i] = next[i], pos[i] += 1 (device-resident greedy loop)

@@ -10,6 +10,19 @@ static thread_local std::string g_err;
 void set_error(const std::string& s) { g_err = s; }
 const char* last_error() { return g_err.c_str(); }
 
+int sm_count_current() {
+  static std::atomic<int> cache[MAX_DEVICES];
+  const int slot = current_device_slot();
+  int n = cache[slot].load(std::memory_order_acquire);
+  if (n > 0) return n;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess || n <= 0) { set_error(std::string("cannot read the SM count: ") + cudaGetErrorString(e)); return 0; }
+  cache[slot].store(n, std::memory_order_release);
+  return n;
+}
+
 Model::~Model() {
   cudaSetDevice(device);
   for (void* p : allocs) cudaFree(p);
@@ -19,10 +32,15 @@ int Model::alloc_tensor(const std::string& name, uint32_t type, uint32_t n_dims,
   if (finalized) { set_error("model already finalized"); return ESTATE; }
   if (n_dims < 1 || n_dims > 4) { set_error(name + ": 1..4 dims expected"); return EINVAL_; }
   if (tensors.count(name)) { set_error(name + ": tensor added twice"); return EINVAL_; }
+  // dims come from an untrusted file: every product is checked before it is used as a size
   int64_t k = d[0], rows = 1;
-  for (uint32_t i = 1; i < n_dims; i++) rows *= d[i];
-  int64_t stride = device_row_stride(type, k);
+  for (uint32_t i = 0; i < n_dims; i++) {
+    if (d[i] <= 0 || d[i] > ((int64_t)1 << 40)) { set_error(name + ": dimension out of range"); return EINVAL_; }
+    if (i > 0 && __builtin_mul_overflow(rows, d[i], &rows)) { set_error(name + ": element count overflows"); return EINVAL_; }
+  }
+  int64_t stride = device_row_stride(type, k), total = 0;
   if (stride < 0 || k <= 0 || rows <= 0) { set_error(name + ": unsupported type or row length"); return EINVAL_; }
+  if (__builtin_mul_overflow(stride, rows, &total) || total > ((int64_t)1 << 46)) { set_error(name + ": tensor size overflows"); return EINVAL_; }
   B200_CUDA(cudaSetDevice(device));
   void* p = nullptr;
   B200_CUDA(cudaMalloc(&p, (size_t)(stride * rows) + 256));
@@ -169,7 +187,8 @@ int Model::finalize() {
   }
   if (c.ffn_shared != c.ffn_expert) bad += " ffn_shared(must equal ffn_expert: the shared expert runs as one more tile of the expert kernel)";
   if (c.dn_head_dim != 128 || c.dn_conv != 4) bad += " ssm(state_size must be 128 and conv_kernel 4)";
-  if (c.n_head % c.n_head_kv) bad += " attention(head_count must be a multiple of head_count_kv)";
+  if (c.dn_heads_k <= 0 || c.dn_heads_v % c.dn_heads_k) bad += " ssm(time_step_rank must be a multiple of group_count: V head h reads K head h % group_count, llm/deltanet.go:405-418)";
+  if (c.n_head_kv <= 0 || c.n_head % c.n_head_kv) bad += " attention(head_count must be a multiple of head_count_kv)";
   if (H % 256) bad += " embedding_length(must be a multiple of 256)";
   if (c.n_expert > 1024 || c.n_expert_used > 32 || c.n_expert_used > c.n_expert) bad += " experts(at most 1024 experts, 32 used)";
   if (!missing.empty()) { set_error("checkpoint is missing tensors:" + missing); return EINVAL_; }

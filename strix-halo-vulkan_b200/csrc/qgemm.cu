@@ -422,10 +422,9 @@ int launch_t(const QGemmParams& p, const CUtensorMap& tm, bool pdl, cudaStream_t
   constexpr bool DUAL = EPI == GEMM_SWIGLU;
   auto kernel = qgemm_kernel<TYPE, TN, EPI>;
   const size_t smem = (size_t)gm_stages(TN, DUAL) * gm_stage_bytes(TN, DUAL) + 1024;
-  static bool configured = false;
-  if (!configured) { B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); configured = true; }
-  static int sm_count = 0;
-  if (sm_count == 0) { int dev = 0; B200_CUDA(cudaGetDevice(&dev)); B200_CUDA(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev)); }
+  B200_ONCE_PER_DEVICE(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int sm_count = sm_count_current();
+  if (sm_count <= 0) return ECUDA;
   const int n_tiles = (p.N + GM_ROWS - 1) / GM_ROWS;
   const int64_t total = (int64_t)(p.problems != nullptr ? p.max_problems : 1) * n_tiles * ((p.max_count + TN - 1) / TN);
   const int gx = (int)std::max<int64_t>(1, std::min<int64_t>(total, sm_count)), gy = 1;

@@ -4,16 +4,11 @@
 
 namespace b200 {
 
-static int g_sm_count = 0;
-
 template <int TYPE, int PRO, int EPI, bool DUAL, bool GROUPED>
 static int launch_one(const QGemvParams& p, int max_entries, bool pdl, cudaStream_t st) {
   auto kernel = qgemv_kernel<TYPE, PRO, EPI, DUAL, GROUPED>;
-  if (g_sm_count == 0) {
-    int dev = 0;
-    B200_CUDA(cudaGetDevice(&dev));
-    B200_CUDA(cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev));
-  }
+  const int g_sm_count = sm_count_current();
+  if (g_sm_count <= 0) return ECUDA;
   const int nb = p.K / 256;
   const int wpt = nb >= 8 ? 8 : nb >= 4 ? 4 : nb >= 2 ? 2 : 1;
   const int tpc = QG_WARPS / wpt;
@@ -48,11 +43,7 @@ static int launch_one(const QGemvParams& p, int max_entries, bool pdl, cudaStrea
   if (ns > per_cta) ns = per_cta;
   if (ns < 1) ns = 1;
   const size_t smem = fixed + (size_t)ns * stage;
-  static size_t configured = 0;
-  if (smem > configured) {
-    B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(220 * 1024 + 4096)));
-    configured = 220 * 1024 + 4096;
-  }
+  B200_ONCE_PER_DEVICE(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(220 * 1024 + 4096)));
   QGemvParams pp = p;
   pp.nstage = ns;
   dim3 grid(gx, ny, nz);
@@ -101,8 +92,7 @@ static int launch_md(const MoeDown1Params& p, bool pdl, cudaStream_t st) {
   const int slots1 = p.used + 1, cl = p.split;
   const size_t smem = md_smem(p.K, (slots1 + cl - 1) / cl, p.stride);
   if (smem > 200 * 1024) { set_error("moe_down1: tiles too large for shared memory"); return ECAPACITY; }
-  static bool configured = false;
-  if (!configured) { B200_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); configured = true; }
+  B200_ONCE_PER_DEVICE(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(((p.N + 15) / 16) * cl); cfg.blockDim = dim3(QG_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute attr[1];

@@ -102,6 +102,7 @@ class Graph:
         _lib.check(L.b200_graph_create(model._h, C.byref(o), C.byref(self._h)))
         self.vocab, self.n_embd = model.cfg["vocab"], model.cfg["n_embd"]
         self.max_tokens = max_tokens
+        self._draft_vocab = 0
 
     def destroy(self):
         if self._h:
@@ -152,6 +153,37 @@ class Graph:
         lg, hd = self._call(_lib.load().b200_graph_extend, ids, 1, 1)
         return lg[0], hd[0]
 
+    def extend_input(self, ids, n_images=0):
+        """Graph.ExtendInput (llm/graph.go:1716); inputs that carry images are refused (no vision tower)."""
+        ids = _i32(ids)
+        inp = _lib.Input(ids.ctypes.data, ids.size, n_images)
+        lg, hd = C.c_void_p(), C.c_void_p()
+        _lib.check(_lib.load().b200_graph_extend_input(self._h, C.byref(inp), C.byref(lg), C.byref(hd)))
+        return (np.ctypeslib.as_array(C.cast(lg, C.POINTER(C.c_float)), (self.vocab,)).copy(),
+                np.ctypeslib.as_array(C.cast(hd, C.POINTER(C.c_float)), (self.n_embd,)).copy())
+
+    def residual_row(self, r):
+        out = np.empty(self.n_embd, dtype=np.float32)
+        _lib.check(_lib.load().b200_graph_residual_row(self._h, r, out.ctypes.data))
+        return out
+
+    def pass_experts(self):
+        n = C.c_int32()
+        _lib.check(_lib.load().b200_graph_pass_experts(self._h, C.byref(n)))
+        return n.value
+
+    def stats(self):
+        st = _lib.GraphStats()
+        _lib.check(_lib.load().b200_graph_stats_get(self._h, C.byref(st)))
+        return {n: getattr(st, n) for n, _ in _lib.GraphStats._fields_}
+
+    def stats_reset(self):
+        _lib.check(_lib.load().b200_graph_stats_reset(self._h))
+
+    def inject_wait_timeout(self):
+        """Queues a kernel whose bounded wait must run out: the next pass reports ETIMEOUT (nothing faults)."""
+        _lib.check(_lib.load().b200_graph_inject_wait_timeout(self._h))
+
     def extend_rows(self, ids):
         n = len(ids)
         return self._call(_lib.load().b200_graph_extend_rows, ids, n, n)
@@ -196,6 +228,15 @@ class Graph:
     def speculate(self, on):
         _lib.check(_lib.load().b200_graph_speculate(self._h, int(on)))
 
+    def speculating(self):
+        return bool(_lib.load().b200_graph_speculating(self._h))
+
+    def speculate_first(self, on):
+        _lib.check(_lib.load().b200_graph_speculate_first(self._h, int(on)))
+
+    def keep_first(self):
+        _lib.check(_lib.load().b200_graph_keep_first(self._h))
+
     def keep(self, k):
         _lib.check(_lib.load().b200_graph_keep(self._h, k))
 
@@ -211,9 +252,29 @@ class Graph:
         ids = _i32(ids)
         res, lg = C.c_void_p(), C.c_void_p()
         _lib.check(_lib.load().b200_draft_rows(self._h, hs.ctypes.data, ids.ctypes.data, ids.size, vocab_k, C.byref(res), C.byref(lg)))
+        vocab_k = vocab_k or self._draft_vocab
         V = vocab_k if 0 < vocab_k < self.vocab else self.vocab
         return (np.ctypeslib.as_array(C.cast(res, C.POINTER(C.c_float)), (ids.size, self.n_embd)).copy(),
                 np.ctypeslib.as_array(C.cast(lg, C.POINTER(C.c_float)), (ids.size, V)).copy())
+
+    def draft_set_vocab(self, k):
+        _lib.check(_lib.load().b200_draft_set_vocab(self._h, k))
+        self._draft_vocab = 0 if k == self.vocab else k
+
+    def draft_use_slot(self, s):
+        _lib.check(_lib.load().b200_draft_use_slot(self._h, s))
+
+    def draft_slots(self):
+        return int(_lib.load().b200_draft_slots(self._h))
+
+    def draft_reset(self):
+        _lib.check(_lib.load().b200_draft_reset(self._h))
+
+    def draft_max_rows(self):
+        return int(_lib.load().b200_draft_max_rows(self._h))
+
+    def draft_wide(self):
+        return int(_lib.load().b200_draft_wide(self._h))
 
     def draft_past(self):
         return int(_lib.load().b200_draft_past(self._h))

@@ -23,6 +23,15 @@ class GraphOpts(C.Structure):
                                          "use_cuda_graph", "trace")]
 
 
+class GraphStats(C.Structure):
+    _fields_ = [("passes", C.c_int64), ("rows", C.c_int64), ("launches", C.c_int64), ("device_ms", C.c_double), ("host_ms", C.c_double),
+                ("last_rows", C.c_int32), ("last_launches", C.c_int32), ("last_device_ms", C.c_float)]
+
+
+class Input(C.Structure):
+    _fields_ = [("ids", C.c_void_p), ("n", C.c_int32), ("n_images", C.c_int32)]
+
+
 class B200Error(RuntimeError):
     def __init__(self, status, msg):
         super().__init__(f"{STATUS_NAME[status] if 0 <= status < len(STATUS_NAME) else status}: {msg}")
@@ -55,6 +64,7 @@ SYMBOLS = {
     "b200_graph_set_past": (I32, [P, I32]),
     "b200_graph_forward": (I32, [P, P, I32, PP, PP]),
     "b200_graph_extend": (I32, [P, P, I32, PP, PP]),
+    "b200_graph_extend_input": (I32, [P, C.POINTER(Input), PP, PP]),
     "b200_graph_extend_rows": (I32, [P, P, I32, PP, PP]),
     "b200_graph_extend_residual": (I32, [P, P, I32, PP, PP]),
     "b200_graph_decode_rows": (I32, [P, P, P, I32, PP]),
@@ -62,7 +72,15 @@ SYMBOLS = {
     "b200_graph_restore": (I32, [P, I32]),
     "b200_graph_checkpoint_free": (I32, [P, I32]),
     "b200_graph_speculate": (I32, [P, I32]),
+    "b200_graph_speculating": (I32, [P]),
+    "b200_graph_speculate_first": (I32, [P, I32]),
     "b200_graph_keep": (I32, [P, I32]),
+    "b200_graph_keep_first": (I32, [P]),
+    "b200_graph_residual_row": (I32, [P, I32, P]),
+    "b200_graph_pass_experts": (I32, [P, C.POINTER(I32)]),
+    "b200_graph_stats_get": (I32, [P, C.POINTER(GraphStats)]),
+    "b200_graph_stats_reset": (I32, [P]),
+    "b200_graph_inject_wait_timeout": (I32, [P]),
     "b200_graph_commit": (I32, [P]),
     "b200_graph_rewind": (I32, [P]),
     "b200_graph_generate_greedy": (I32, [P, P, P, I32, I32, P]),
@@ -71,6 +89,12 @@ SYMBOLS = {
     "b200_graph_timeline": (I32, [P, P, I32]),
     "b200_graph_trace": (I64, [P, I32, P, I64]),
     "b200_draft_rows": (I32, [P, P, P, I32, I32, PP, PP]),
+    "b200_draft_set_vocab": (I32, [P, I32]),
+    "b200_draft_use_slot": (I32, [P, I32]),
+    "b200_draft_slots": (I32, [P]),
+    "b200_draft_reset": (I32, [P]),
+    "b200_draft_max_rows": (I32, [P]),
+    "b200_draft_wide": (I32, [P]),
     "b200_draft_past": (I32, [P]),
     "b200_draft_rewind": (I32, [P, I32]),
     "b200_dequantize": (I32, [U32, P, I64, P]),

@@ -47,4 +47,6 @@ def main(ref):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_fixtures.py <path of a checkout of the reference repository>")
+    main(sys.argv[1])
