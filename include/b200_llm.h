@@ -56,6 +56,13 @@ typedef struct {
   int32_t trace;            /* 1: keep per-layer hidden states and routing for b200_graph_trace */
 } b200_graph_opts;
 
+/* Weight matrices a pass multiplies as fp16-rounded values (b200_graph_fp16_weight_mask). */
+enum {
+  B200_W16_DN_QKV = 1 << 8, B200_W16_DN_GATE = 1 << 9, B200_W16_DN_OUT = 1 << 10,
+  B200_W16_ATTN_Q = 1 << 11, B200_W16_ATTN_K = 1 << 12, B200_W16_ATTN_V = 1 << 13, B200_W16_ATTN_OUT = 1 << 14,
+  B200_W16_ROUTER = 1 << 15, B200_W16_EXPERTS = 1 << 16, B200_W16_SHARED = 1 << 17, B200_W16_HEAD = 1 << 18
+};
+
 /* Running totals of a graph (llm.GraphStats, llm/graph.go:527-589, reduced to what one CUDA stream can tell). */
 typedef struct {
   int64_t passes;        /* passes run (Runs) */
@@ -148,6 +155,11 @@ int32_t b200_graph_rewind(b200_graph* g);
 int32_t b200_graph_residual_row(b200_graph* g, int32_t r, float* dst);
 /* Distinct experts the last pass's last layer routed to, over all its rows (PassExperts :1677). */
 int32_t b200_graph_pass_experts(b200_graph* g, int32_t* out);
+/* Which weight matrices a pass of `rows` rows that returns `logit_rows` rows of logits sends through the
+ * tensor-core kernels, i.e. multiplies rounded to fp16 after dequantisation as the reference's many-row
+ * GEMMs do (shaders/llm_gemm.comp MODE 2, shaders/llm_moe_gemm.comp:260-261); the others stay exact as in
+ * its decode GEMVs. A B200_W16_* bit set. A checker that wants the pass's arithmetic mirrors this set. */
+uint32_t b200_graph_fp16_weight_mask(const b200_graph* g, int32_t rows, int32_t logit_rows);
 int32_t b200_graph_stats_get(const b200_graph* g, b200_graph_stats* out);                  /* Stats :527-589 */
 int32_t b200_graph_stats_reset(b200_graph* g);
 

@@ -42,6 +42,8 @@ struct Layer {
   Tensor enorm, hnorm, eh_proj, head_norm;
 };
 
+inline bool dev_like(int numerics) { return (numerics & 0xff) == ORC_DEVICE_LIKE; }
+inline bool w16(int numerics, int bit) { return (numerics & bit) != 0; }
 inline float sigmoidf_(float x) { return (float)(1.0 / (1.0 + std::exp(-(double)x))); }  // llm/hc.go:266
 inline float siluf_(float x) { return x * sigmoidf_(x); }                                // llm/hc.go:268
 
@@ -61,7 +63,10 @@ std::vector<float> to_f32(const Tensor& t) {
 }
 
 // y = W x over rows [0, rows) of t starting at row0; serial f32 sum (llm/hc.go:255-264).
-void matvec(const Tensor& t, int64_t row0, int64_t rows, const float* x, float* y) {
+// w16: every dequantised weight is rounded to fp16 first, as the reference's many-row tensor-core
+// GEMMs do when they unpack a weight slab into LDS (shaders/llm_gemm.comp MODE 2,
+// shaders/llm_moe_gemm.comp:260-261, 428-430); its decode GEMVs keep the f32 value.
+void matvec(const Tensor& t, int64_t row0, int64_t rows, const float* x, float* y, bool w16 = false) {
   const int64_t k = t.ne[0];
 #pragma omp parallel
   {
@@ -73,6 +78,7 @@ void matvec(const Tensor& t, int64_t row0, int64_t rows, const float* x, float* 
         w = (const float*)t.row(row0 + r);
       } else {
         dequantize(t.type, t.row(row0 + r), k, buf.data());
+        if (w16) for (int64_t i = 0; i < k; i++) buf[(size_t)i] = f16_round(buf[(size_t)i]);
         w = buf.data();
       }
       float s = 0;
@@ -205,8 +211,8 @@ void deltanet_token(const orc_model& m, int li, orc_seq::L& st, const float* xn,
     float sc = (float)(1.0 / std::sqrt(ss / (double)d + (double)c.eps));
     for (int j = 0; j < d; j++) w.fin[h * d + j] = x[j] * sc * sm.ssm_norm[j] * sigmoidf_(w.z[h * d + j]);
   }
-  if (numerics == ORC_DEVICE_LIKE) round_f16(w.fin.data(), vw);
-  matvec(L.ssm_out, 0, c.n_embd, w.fin.data(), out);
+  if (dev_like(numerics)) round_f16(w.fin.data(), vw);
+  matvec(L.ssm_out, 0, c.n_embd, w.fin.data(), out, w16(numerics, ORC_W16_DN_OUT));
 }
 
 // NeoX partial rotary on the first rope_dims of each head, angle walked in f64
@@ -237,9 +243,9 @@ void attn_token(const orc_model& m, int li, orc_seq::L& st, const float* xn, int
   const int hd = c.head_dim, H = c.n_head, Hkv = c.n_head_kv, kvw = Hkv * hd;
   std::vector<float> qfull((size_t)H * 2 * hd);
   w.q.resize((size_t)H * hd); w.gate.resize((size_t)H * hd); w.kk.resize(kvw); w.vv.resize(kvw);
-  matvec(L.q, 0, (int64_t)H * 2 * hd, xn, qfull.data());
-  matvec(L.k, 0, kvw, xn, w.kk.data());
-  matvec(L.v, 0, kvw, xn, w.vv.data());
+  matvec(L.q, 0, (int64_t)H * 2 * hd, xn, qfull.data(), w16(numerics, ORC_W16_ATTN_Q));
+  matvec(L.k, 0, kvw, xn, w.kk.data(), w16(numerics, ORC_W16_ATTN_K));
+  matvec(L.v, 0, kvw, xn, w.vv.data(), w16(numerics, ORC_W16_ATTN_V));
   for (int h = 0; h < H; h++) {  // per head: hd query rows then hd gate rows (llm/attn.go:162-166)
     memcpy(&w.q[(size_t)h * hd], &qfull[(size_t)h * 2 * hd], sizeof(float) * hd);
     memcpy(&w.gate[(size_t)h * hd], &qfull[(size_t)h * 2 * hd + hd], sizeof(float) * hd);
@@ -248,7 +254,7 @@ void attn_token(const orc_model& m, int li, orc_seq::L& st, const float* xn, int
   for (int h = 0; h < Hkv; h++) rmsnorm(&w.kk[(size_t)h * hd], sm.k_norm.data(), hd, c.eps, &w.kk[(size_t)h * hd]);
   rope(c, w.q.data(), H, pos);
   rope(c, w.kk.data(), Hkv, pos);
-  if (numerics == ORC_DEVICE_LIKE) {  // fp16 cache and fp16 query (llm/attn.go:176-184, 196-199)
+  if (dev_like(numerics)) {  // fp16 cache and fp16 query (llm/attn.go:176-184, 196-199)
     round_f16(w.kk.data(), kvw); round_f16(w.vv.data(), kvw); round_f16(w.q.data(), (int64_t)H * hd);
   }
   if ((int64_t)st.K.size() < (int64_t)(cell + 1) * kvw) { st.K.resize((size_t)(cell + 1) * kvw); st.V.resize((size_t)(cell + 1) * kvw); }
@@ -275,7 +281,7 @@ void attn_token(const orc_model& m, int li, orc_seq::L& st, const float* xn, int
       float sum = 0;
       for (int j = 0; j < n; j++) { scores[j] = (float)std::exp((double)(scores[j] - mx)); sum += scores[j]; }
       float* dst = &w.ctx[(size_t)h * hd];
-      if (numerics == ORC_DEVICE_LIKE) {
+      if (dev_like(numerics)) {
         // Device-like: probabilities meet the fp16 values as fp16 and the division by
         // the f32 row sum comes last (shaders/llm_attn_wmma.comp:860, llm_attn_combine.comp:70-102).
         for (int j = 0; j < n; j++) {
@@ -294,8 +300,8 @@ void attn_token(const orc_model& m, int li, orc_seq::L& st, const float* xn, int
     }
   }
   for (int i = 0; i < H * hd; i++) w.ctx[i] = w.ctx[i] * sigmoidf_(w.gate[i]);  // gate on the output (llm/attn.go:203-208)
-  if (numerics == ORC_DEVICE_LIKE) round_f16(w.ctx.data(), (int64_t)H * hd);
-  matvec(L.o, 0, c.n_embd, w.ctx.data(), out);
+  if (dev_like(numerics)) round_f16(w.ctx.data(), (int64_t)H * hd);
+  matvec(L.o, 0, c.n_embd, w.ctx.data(), out, w16(numerics, ORC_W16_ATTN_OUT));
 }
 
 // Routed + shared MoE block for one token (llm/moe.go:219-409). x is the f32 norm
@@ -307,7 +313,7 @@ void moe_token(const orc_model& m, int li, const float* x, const float* xr, int 
   const auto& sm = m.small[li];
   const int nE = c.n_expert, used = c.n_expert_used, ff = c.ffn_expert, ffs = c.ffn_shared, H = c.n_embd;
   w.logits.resize(nE); w.probs.resize(nE); w.idx.resize(nE);
-  matvec(L.router, 0, nE, xr, w.logits.data());
+  matvec(L.router, 0, nE, xr, w.logits.data(), w16(numerics, ORC_W16_ROUTER));
   {  // softmaxInto (llm/moe.go:426-443)
     float mx = -INFINITY;
     for (int e = 0; e < nE; e++) if (w.logits[e] > mx) mx = w.logits[e];
@@ -335,22 +341,24 @@ void moe_token(const orc_model& m, int li, const float* x, const float* xr, int 
   for (int j = 0; j < H; j++) out[j] = 0;
   for (int k = 0; k < used; k++) {
     int e = w.idx[k];
-    matvec(L.gate_exps, (int64_t)e * ff, ff, xr, w.g.data());
-    matvec(L.up_exps, (int64_t)e * ff, ff, xr, w.u.data());
+    const bool ew = w16(numerics, ORC_W16_EXPERTS);
+    matvec(L.gate_exps, (int64_t)e * ff, ff, xr, w.g.data(), ew);
+    matvec(L.up_exps, (int64_t)e * ff, ff, xr, w.u.data(), ew);
     for (int j = 0; j < ff; j++) w.sw[j] = siluf_(w.g[j]) * w.u[j];
-    if (numerics == ORC_DEVICE_LIKE) round_f16(w.sw.data(), ff);  // shaders/llm_moe_gemv.comp:777-781
-    matvec(L.down_exps, (int64_t)e * H, H, w.sw.data(), w.down.data());
+    if (dev_like(numerics)) round_f16(w.sw.data(), ff);  // shaders/llm_moe_gemv.comp:777-781
+    matvec(L.down_exps, (int64_t)e * H, H, w.sw.data(), w.down.data(), ew);
     for (int j = 0; j < H; j++) out[j] += w.down[j] * wt[k];
   }
   // shared expert and its one-column sigmoid gate (llm/moe.go:363-409). Device-like: the
   // gate column sees the same fp16 vector as the router (llm/gpu_moe.go:27-33).
-  matvec(L.gate_sh, 0, ffs, xr, w.g.data());
-  matvec(L.up_sh, 0, ffs, xr, w.u.data());
+  const bool sw16 = w16(numerics, ORC_W16_SHARED);
+  matvec(L.gate_sh, 0, ffs, xr, w.g.data(), sw16);
+  matvec(L.up_sh, 0, ffs, xr, w.u.data(), sw16);
   for (int j = 0; j < ffs; j++) w.sw[j] = siluf_(w.g[j]) * w.u[j];
-  if (numerics == ORC_DEVICE_LIKE) round_f16(w.sw.data(), ffs);
+  if (dev_like(numerics)) round_f16(w.sw.data(), ffs);
   w.sh.resize(H);
-  matvec(L.down_sh, 0, H, w.sw.data(), w.sh.data());
-  const float* gx = numerics == ORC_DEVICE_LIKE ? xr : x;
+  matvec(L.down_sh, 0, H, w.sw.data(), w.sh.data(), sw16);
+  const float* gx = dev_like(numerics) ? xr : x;
   float gl = 0;
   for (int j = 0; j < H; j++) gl += sm.sh_gate_inp[j] * gx[j];
   float s = sigmoidf_(gl);
@@ -369,7 +377,7 @@ void layer_token(const orc_model& m, int li, orc_seq::L& st, float* h, int cell,
   const auto& sm = m.small[li];
   w.xn.resize(H); w.mix.resize(H); w.ffn.resize(H);
   rmsnorm(h, sm.attn_norm.data(), H, c.eps, w.xn.data());
-  if (numerics == ORC_DEVICE_LIKE) round_f16(w.xn.data(), H);
+  if (dev_like(numerics)) round_f16(w.xn.data(), H);
   if (m.layers[li].is_attn) attn_token(m, li, st, w.xn.data(), cell, pos, numerics, w.mix.data(), w);
   else deltanet_token(m, li, st, w.xn.data(), numerics, w.mix.data(), w);
   if (mix_out) memcpy(mix_out, w.mix.data(), sizeof(float) * H);
@@ -377,7 +385,7 @@ void layer_token(const orc_model& m, int li, orc_seq::L& st, float* h, int cell,
   std::vector<float> x(H), xr(H);
   rmsnorm(h, sm.ffn_norm.data(), H, c.eps, x.data());
   xr = x;
-  if (numerics == ORC_DEVICE_LIKE) round_f16(xr.data(), H);
+  if (dev_like(numerics)) round_f16(xr.data(), H);
   moe_token(m, li, x.data(), xr.data(), numerics, w.ffn.data(), topk, topkw, margin, w);
   if (ffn_out) memcpy(ffn_out, w.ffn.data(), sizeof(float) * H);
   for (int j = 0; j < H; j++) h[j] += w.ffn[j];
@@ -513,10 +521,10 @@ int orc_extend(const orc_model* m, orc_seq* s, const int32_t* ids, int n, int nu
     if (!want) continue;
     rmsnorm(h.data(), m->out_norm.data(), H, c.eps, xn.data());
     if (tr && tr->normed) memcpy(tr->normed + (size_t)t * H, xn.data(), sizeof(float) * H);
-    if (numerics == ORC_DEVICE_LIKE) round_f16(xn.data(), H);
+    if (dev_like(numerics)) round_f16(xn.data(), H);
     if ((tr && tr->logits) || (logits_last && t == n - 1)) {
       logits.resize(c.vocab);
-      matvec(m->output, 0, c.vocab, xn.data(), logits.data());
+      matvec(m->output, 0, c.vocab, xn.data(), logits.data(), w16(numerics, ORC_W16_HEAD));
       if (tr && tr->logits) memcpy(tr->logits + (size_t)t * c.vocab, logits.data(), sizeof(float) * c.vocab);
       if (logits_last && t == n - 1) memcpy(logits_last, logits.data(), sizeof(float) * c.vocab);
     }
@@ -536,7 +544,7 @@ int orc_draft_step(const orc_model* m, orc_seq* ds, const float* h_prev, int32_t
   embed_row(*m, id, e.data());
   rmsnorm(e.data(), sm.enorm.data(), H, c.eps, x.data());
   rmsnorm(h_prev, sm.hnorm.data(), H, c.eps, x.data() + H);
-  if (numerics == ORC_DEVICE_LIKE) round_f16(x.data(), 2 * H);
+  if (dev_like(numerics)) round_f16(x.data(), 2 * H);
   matvec(m->layers[li].eh_proj, 0, H, x.data(), h.data());
   Work w;
   int cell = ds->past, pos = ds->past + 1;  // the cell holds the token one position ahead of the trunk row that seeded it
@@ -545,7 +553,7 @@ int orc_draft_step(const orc_model* m, orc_seq* ds, const float* h_prev, int32_t
   if (h_out) memcpy(h_out, h.data(), sizeof(float) * H);
   if (logits) {
     rmsnorm(h.data(), sm.head_norm.data(), H, c.eps, xn.data());
-    if (numerics == ORC_DEVICE_LIKE) round_f16(xn.data(), H);
+    if (dev_like(numerics)) round_f16(xn.data(), H);
     int64_t nv = draft_vocab > 0 && draft_vocab < c.vocab ? draft_vocab : c.vocab;
     matvec(m->output, 0, nv, xn.data(), logits);
   }

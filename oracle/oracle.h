@@ -54,6 +54,15 @@ typedef struct orc_seq orc_seq;
  * matmul input, the SwiGLU output, K, V and the attention probabilities are rounded to
  * fp16 where the reference's device path stores them as fp16. */
 enum { ORC_EXACT = 0, ORC_DEVICE_LIKE = 1 };
+/* OR-ed into `numerics`: the named weight matrices are rounded to fp16 after dequantisation, as the
+ * reference's many-row tensor-core GEMMs do when they unpack weights into LDS (shaders/llm_gemm.comp
+ * MODE 2, shaders/llm_moe_gemm.comp:260-261, 428-430), while its decode GEMVs keep the f32 value
+ * (shaders/llm_gemv.comp:133-186). Which matrices a pass rounds depends on its row count. */
+enum {
+  ORC_W16_DN_QKV = 1 << 8, ORC_W16_DN_GATE = 1 << 9, ORC_W16_DN_OUT = 1 << 10,
+  ORC_W16_ATTN_Q = 1 << 11, ORC_W16_ATTN_K = 1 << 12, ORC_W16_ATTN_V = 1 << 13, ORC_W16_ATTN_OUT = 1 << 14,
+  ORC_W16_ROUTER = 1 << 15, ORC_W16_EXPERTS = 1 << 16, ORC_W16_SHARED = 1 << 17, ORC_W16_HEAD = 1 << 18
+};
 
 uint16_t orc_f32_to_f16(float f);
 float orc_f16_to_f32(uint16_t h);

@@ -13,6 +13,10 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB = None
 
 EXACT, DEVICE_LIKE = 0, 1
+# OR-ed into `numerics`: weight matrices rounded to fp16 after dequantisation (oracle.h ORC_W16_*)
+W16_DN_QKV, W16_DN_GATE, W16_DN_OUT, W16_ATTN_Q, W16_ATTN_K, W16_ATTN_V, W16_ATTN_OUT, W16_ROUTER, W16_EXPERTS, W16_SHARED, W16_HEAD = \
+    (1 << b for b in range(8, 19))
+W16_ALL = sum(1 << b for b in range(8, 19))
 
 
 class Tensor(C.Structure):

@@ -172,6 +172,7 @@ int32_t b200_graph_rewind(b200_graph* g) {
 }
 int32_t b200_graph_residual_row(b200_graph* g, int32_t r, float* dst) { if (!g || !dst) { set_error("residual_row: null argument"); return EINVAL_; } return g->g.residual_row(r, dst); }
 int32_t b200_graph_pass_experts(b200_graph* g, int32_t* out) { if (!g || !out) { set_error("pass_experts: null argument"); return EINVAL_; } return g->g.pass_experts(out); }
+uint32_t b200_graph_fp16_weight_mask(const b200_graph* g, int32_t rows, int32_t logit_rows) { return g ? g->g.fp16_weight_mask(rows, logit_rows) : 0; }
 int32_t b200_graph_stats_get(const b200_graph* g, b200_graph_stats* out) { if (!g || !out) return EINVAL_; *out = g->g.stats; return OK; }
 int32_t b200_graph_stats_reset(b200_graph* g) { if (!g) return EINVAL_; g->g.stats = b200_graph_stats{}; return OK; }
 int32_t b200_graph_inject_wait_timeout(b200_graph* g) { if (!g) return EINVAL_; return g->g.inject_wait_timeout(); }

@@ -156,6 +156,42 @@ int Graph::max_entries_for(int M) const {
   return std::min(M * used, m->c.n_expert + (M * used + ec - 1) / ec) + (M + ec - 1) / ec;
 }
 
+// Tile height of a many-row projection of N weight rows over M activation rows: as tall as the pass allows,
+// shrunk while the launch would leave SMs idle. 0: its tiles would cover under a third of the SMs and the
+// projection stays on the column-tiled kernel (exact weights).
+static int gemm_tile_rows(int M, int N) {
+  int tn = M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  while (tn > 64 && ((N + 127) / 128) * ((M + tn - 1) / tn) < 120) tn /= 2;
+  if (((N + 127) / 128) * ((M + tn - 1) / tn) < 48) return 0;
+  return tn;
+}
+static bool pass_uses_gemm(int M, int H) { return !(M <= QG_FUSED_ROWS && H <= QG_COMBINE_MAX_K) && M >= 16; }
+static bool pass_moe_gemm(const b200_config& c, const LayerW& L, int M, int H) {
+  return pass_uses_gemm(M, H) && (int64_t)M * c.n_expert_used >= 32 * (int64_t)c.n_expert && L.gate_exps.type == L.gate_sh.type && L.down_exps.type == L.down_sh.type;
+}
+
+// Which weight matrices a pass of M rows multiplies as fp16-rounded values (the tensor-core kernels, the
+// reference's prefill arithmetic: shaders/llm_gemm.comp MODE 2, shaders/llm_moe_gemm.comp:260-261) and
+// which as exact dequantised values (the column-tiled kernels). The same predicates drive enqueue_pass.
+uint32_t Graph::fp16_weight_mask(int M, int n_logit_rows) const {
+  const b200_config& c = m->c;
+  const int H = c.n_embd, D = c.dn_head_dim, qk = c.dn_heads_k * D, vw = c.dn_heads_v * D, cw = 2 * qk + vw;
+  const int hd = c.head_dim, qw = c.n_head * hd, kvw = c.n_head_kv * hd;
+  if (!pass_uses_gemm(M, H)) return 0;
+  uint32_t mask = 0;
+  if (gemm_tile_rows(M, cw)) mask |= B200_W16_DN_QKV;
+  if (gemm_tile_rows(M, vw)) mask |= B200_W16_DN_GATE;
+  if (gemm_tile_rows(M, H)) mask |= B200_W16_DN_OUT | B200_W16_ATTN_OUT;
+  if (gemm_tile_rows(M, 2 * qw)) mask |= B200_W16_ATTN_Q;
+  if (gemm_tile_rows(M, kvw)) mask |= B200_W16_ATTN_K | B200_W16_ATTN_V;
+  for (const LayerW& L : m->layers) {
+    if (M >= 64 && L.router.type == T_Q8_0) mask |= B200_W16_ROUTER;
+    if (pass_moe_gemm(c, L, M, H)) mask |= B200_W16_EXPERTS | B200_W16_SHARED;
+  }
+  if (n_logit_rows == M && gemm_tile_rows(M, c.vocab)) mask |= B200_W16_HEAD;
+  return mask;
+}
+
 // ---- one pass over M rows --------------------------------------------------------------
 // Per layer: [in-proj] [DeltaNet step | attention pre-pass + split-KV attention] [out-proj + residual]
 // [router + top-k + work list] [experts gate/up + SwiGLU] [experts down + weighted combine + residual].
@@ -214,14 +250,12 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     return t;
   };
   // passes of 16 rows and more run their dense projections on the tensor cores
-  const bool use_gemm = !fused && M >= 16;
-  const int tn = M <= 64 ? 64 : M <= 128 ? 128 : 256, ti = tn == 64 ? 0 : tn == 128 ? 1 : 2;
+  const bool use_gemm = pass_uses_gemm(M, H);
   // tile height per projection: as tall as the pass allows, shrunk while the launch would leave SMs idle
   // a projection whose tiles would cover under a third of the SMs stays on the column-tiled kernel
   auto gemm = [&](const DTensor& w, int K, int N, const __half* x, const unsigned char (*tmaps)[128], float* y, int64_t ldy, int epi) {
-    int tn = M <= 64 ? 64 : M <= 128 ? 128 : 256;
-    while (tn > 64 && ((N + 127) / 128) * ((M + tn - 1) / tn) < 120) tn /= 2;
-    if (((N + 127) / 128) * ((M + tn - 1) / tn) < 48) {
+    const int tn = gemm_tile_rows(M, N);
+    if (tn == 0) {
       QGemvParams q = base(w, K, N, x, K);
       q.y = y; q.ldy = ldy;
       return launch_qgemv(w.type, PRO_F16, epi == GEMM_RESID ? EPI_RESID : EPI_STORE, false, false, q, 0, pdl(), st);
@@ -338,7 +372,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     r.defer = fused && M == 1; r.ecols = entry_cols(M);
     // 32 rows per expert on average and more: the experts run as grouped tensor-core GEMMs over expert-sorted
     // rows (below that the column-tiled kernel, which streams each expert's weights in whole tiles, is faster)
-    const bool moe_gemm = use_gemm && (int64_t)M * used >= 32 * (int64_t)c.n_expert && L.gate_exps.type == L.gate_sh.type && L.down_exps.type == L.down_sh.type;
+    const bool moe_gemm = pass_moe_gemm(c, L, M, H);
     r.gprob = moe_gemm ? gprob : nullptr;
     if (use_gemm && M >= 64 && L.router.type == T_Q8_0) {
       // many rows: the router logits are one more tensor-core GEMM (the reference's prefill router is an fp16

@@ -86,6 +86,7 @@ struct Graph {
   int enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f);
   static int entry_cols(int M);
   int max_entries_for(int M) const;
+  uint32_t fp16_weight_mask(int M, int n_logit_rows) const;
   int run_rows(const int32_t* ids, const int* slots, const int* pos, int M, const std::vector<SeqDesc>& sq, const std::vector<int>& lrows, const PassFlags& f);
   int extend(const int32_t* ids, int n, const PassFlags& f, const float** logits_out, const float** hidden_out);
   int decode_rows(const int32_t* slots, const int32_t* ids, int n, const float** logits_out);

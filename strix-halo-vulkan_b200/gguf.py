@@ -96,6 +96,29 @@ class Writer:
                 f.write(b"\0" * ((-data.size) % self.alignment))
 
 
+def write_split(path_stem, arch, metadata, tensors, n_shards, alignment=32):
+    """Writes a checkpoint as `n_shards` files `<stem>-0000i-of-0000n.gguf` in llama.cpp's split convention
+    (gguf/gguf.go:726-733): every shard a whole GGUF with its own tensor table, the first carrying the model's
+    metadata, each carrying split.no / split.count / split.tensors.count. Returns the paths."""
+    names = list(tensors)
+    per = (len(names) + n_shards - 1) // n_shards
+    paths = []
+    for i in range(n_shards):
+        w = Writer(arch, alignment)
+        if i == 0:
+            for row in metadata:
+                w.add(*row)
+        w.add("split.no", U16, i)
+        w.add("split.count", U16, n_shards)
+        w.add("split.tensors.count", I32, len(names))
+        for name in names[i * per:(i + 1) * per]:
+            typ, dims, data = tensors[name]
+            w.add_tensor(name, typ, dims, data)
+        paths.append(f"{path_stem}-{i + 1:05d}-of-{n_shards:05d}.gguf")
+        w.write(paths[-1])
+    return paths
+
+
 class Reader:
     """mmap view of one GGUF file: `.kv` dict and `.tensors` {name: (type, dims, uint8 view)}."""
 

@@ -172,6 +172,10 @@ class Graph:
         _lib.check(_lib.load().b200_graph_pass_experts(self._h, C.byref(n)))
         return n.value
 
+    def fp16_weight_mask(self, rows, logit_rows=1):
+        """B200_W16_* bits: the weight matrices a pass of `rows` rows multiplies rounded to fp16 (tensor-core kernels)."""
+        return int(_lib.load().b200_graph_fp16_weight_mask(self._h, rows, logit_rows))
+
     def stats(self):
         st = _lib.GraphStats()
         _lib.check(_lib.load().b200_graph_stats_get(self._h, C.byref(st)))

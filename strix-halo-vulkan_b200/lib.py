@@ -11,6 +11,11 @@ OK, EINVAL, ECAPACITY, ECUDA, ENCCL, ETIMEOUT, ESTATE, ENOMEM, EIO = range(9)
 STATUS_NAME = ["OK", "EINVAL", "ECAPACITY", "ECUDA", "ENCCL", "ETIMEOUT", "ESTATE", "ENOMEM", "EIO"]
 
 
+# B200_W16_*: weight matrices a pass multiplies rounded to fp16 (b200_graph_fp16_weight_mask)
+W16_DN_QKV, W16_DN_GATE, W16_DN_OUT, W16_ATTN_Q, W16_ATTN_K, W16_ATTN_V, W16_ATTN_OUT, W16_ROUTER, W16_EXPERTS, W16_SHARED, W16_HEAD = \
+    (1 << b for b in range(8, 19))
+
+
 class Config(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("n_layer", "n_embd", "vocab", "n_head", "n_head_kv", "head_dim", "rope_dims")] + \
                [("rope_base", C.c_float), ("eps", C.c_float)] + \
@@ -78,6 +83,7 @@ SYMBOLS = {
     "b200_graph_keep_first": (I32, [P]),
     "b200_graph_residual_row": (I32, [P, I32, P]),
     "b200_graph_pass_experts": (I32, [P, C.POINTER(I32)]),
+    "b200_graph_fp16_weight_mask": (U32, [P, I32, I32]),
     "b200_graph_stats_get": (I32, [P, C.POINTER(GraphStats)]),
     "b200_graph_stats_reset": (I32, [P]),
     "b200_graph_inject_wait_timeout": (I32, [P]),

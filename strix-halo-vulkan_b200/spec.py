@@ -20,20 +20,31 @@ def argmax(logits):
 
 
 class Speculator:
-    def __init__(self, graph, depth=SPEC_DEPTH_DEFAULT, draft_vocab=0):
+    """One sequence's speculative loop. Several of them share a slotted graph, one per slot
+    (NewSlotSpeculator, llm/spec.go; llm/spec_slots_test.go:199): each call first makes its slot the
+    graph's and the draft cache's current one (Graph.UseSlot + MTPHead.UseSlot, llm/mtp.go:500-529), so
+    rounds of different slots may be interleaved in any order."""
+
+    def __init__(self, graph, depth=SPEC_DEPTH_DEFAULT, draft_vocab=0, slot=None):
         if depth < 1 or depth > 4:
             raise ValueError("depth is 1..4")
-        self.g, self.depth, self.draft_vocab = graph, depth, draft_vocab
+        self.g, self.depth, self.draft_vocab, self.slot = graph, depth, draft_vocab, slot
         self.h = None          # trunk residual of the last fed position
         self.pend = None       # the token emitted but not yet fed to the trunk
         self.owe_h, self.owe_x = [], []
         self.stats = dict(rounds=0, drafted=0, accepted=0, tokens=0)
+
+    def _select(self):
+        if self.slot is not None:
+            self.g.use_slot(self.slot)        # moves the draft cache's slot along
+            self.g.draft_use_slot(self.slot)
 
     def prime(self, ids, pick=argmax):
         """Prefill the trunk, prime the draft's cache with every (residual, next token) pair of
         the prompt (llm/spec.go:285-328) and return the first emitted token."""
         ids = np.asarray(ids, dtype=np.int32)
         g = self.g
+        self._select()
         g.reset()
         res_rows, logits = [], None
         mt = g.max_tokens
@@ -54,6 +65,7 @@ class Speculator:
         names draft k's token (default: the draft head's argmax); `pick(logits)` names the
         trunk's token of a row."""
         g = self.g
+        self._select()
         at = g.past()
         depth = self.depth if room is None else max(1, min(self.depth, room - 1))
         if g.draft_past() != at - 1 - len(self.owe_x):

@@ -4,20 +4,21 @@ import numpy as np
 # Tolerances of the contract: hidden states and logits within max relative error 1e-2;
 # routing indices and greedy ids exact unless the top-k margin / logit gap is below 1e-3.
 #
-# "Relative" is taken against the tensor's own scale: max|got - want| / max|want|. The
-# reference's compare() (llm/hc_test.go:52-83) reports this pair (maxAbs, refMax) next to an
-# element-wise ratio floored at |want| > 1e-3; the element-wise ratio is reported here too
-# (`max_rel`) but cannot be the gate: with fp16 staging of every matmul input, two correct
-# implementations that add in different orders flip fp16 roundings, which moves elements that
-# sit near zero by far more than 1% of their own value (the CPU oracle's exact and
-# device-like modes differ from each other by more than the CUDA path differs from either).
+# Three bounds are asserted on every compared tensor:
+#   1. max|got - want| <= REL_TOL * max|want|                  (the contract's bound on the tensor's own scale)
+#   2. rms(got - want) <= RMS_TOL * rms(want)                   (no systematic drift hiding under bound 1)
+#   3. |got - want| / |want| <= REL_TOL for every element with |want| >= BIG_FRAC * max|want|
+#      (the element-wise ratio where it is meaningful)
+# The reference's compare() (llm/hc_test.go:52-83) reports an element-wise ratio with the denominator
+# floored at 1e-3 (`max_rel` below). It is computed, returned and printed with every failure, but the
+# floor is an absolute number made for that checkpoint's activations: with fp16 staging of every matmul
+# input two correct implementations that add in different orders flip fp16 roundings, which moves an
+# element whose own value is 2e-3 by its whole size (the CPU oracle's exact and device-like modes differ
+# from each other by more than that), so bound 3 takes the ratio over the elements that carry the tensor.
 REL_TOL = 1e-2
+RMS_TOL = 3e-3
+BIG_FRAC = 0.25
 NEAR_TIE = 1e-3
-# Passes of 16 rows and more run on the tensor cores with the reference's prefill arithmetic: every
-# dequantised weight is rounded to fp16 (shaders/llm_gemm.comp MODE 2). That moves hidden states by about
-# 1e-3 of their scale against the exact-weight oracle, and with them the router's probabilities, so a
-# top-k boundary is only safe from flipping when it is wider than a few times that.
-NEAR_TIE_MANY_ROWS = 5e-3
 
 
 def compare(got, want):
@@ -27,8 +28,11 @@ def compare(got, want):
     assert np.isfinite(got).all(), "non-finite values"
     d = np.abs(got - want)
     big = np.abs(want) > 1e-3
+    ref_max = float(np.abs(want).max())
+    carry = np.abs(want) >= BIG_FRAC * ref_max
     return dict(max_abs=float(d.max()), max_rel=float((d[big] / np.abs(want[big])).max()) if big.any() else 0.0,
-                rms=float(np.sqrt((d ** 2).mean())), ref_max=float(np.abs(want).max()))
+                rms=float(np.sqrt((d ** 2).mean())), ref_max=ref_max, ref_rms=float(np.sqrt((want ** 2).mean())),
+                rel_big=float((d[carry] / np.abs(want[carry])).max()) if carry.any() and ref_max > 0 else 0.0)
 
 
 def logit_gap(logits):
@@ -39,4 +43,31 @@ def logit_gap(logits):
 def assert_close(got, want, what, tol=REL_TOL):
     r = compare(got, want)
     assert r["max_abs"] <= tol * r["ref_max"], f"{what}: {r}"
+    if tol >= REL_TOL:   # comparisons at the contract's tolerance (against the oracle); tighter ones are already inside it
+        assert r["rms"] <= (RMS_TOL * tol / REL_TOL) * r["ref_rms"] + 1e-12, f"{what} (rms): {r}"
+        assert r["rel_big"] <= tol, f"{what} (element-wise on the large elements): {r}"
     return r
+
+
+def routing_flips(gpu_topk, orc_topk, margin, what=""):
+    """Routed sets must be the oracle's, bit for bit, except where the oracle's own top-k boundary is a
+    documented near-tie (margin below NEAR_TIE): there either neighbour is a valid pick. gpu_topk is
+    [n_layer][T][used], orc_topk [T][n_layer][used], margin [T][n_layer]. Returns (clean, flips): clean[l] is
+    the number of leading rows of layer l that no flip at this or an earlier layer can have reached (a flip
+    at token t changes that token from that layer on, and later tokens through the sequence state), flips the
+    list of (layer, token, margin)."""
+    nl, T = gpu_topk.shape[0], gpu_topk.shape[1]
+    clean = np.full(nl, T)
+    flips = []
+    for l in range(nl):
+        upto = int(clean[l - 1]) if l else T
+        first = upto
+        for t in range(upto):
+            if set(gpu_topk[l, t].tolist()) != set(orc_topk[t, l].tolist()):
+                assert margin[t, l] < NEAR_TIE, f"{what}: layer {l} token {t} routes to {sorted(gpu_topk[l, t].tolist())}, the oracle to " \
+                                                f"{sorted(orc_topk[t, l].tolist())}, with a clear margin {margin[t, l]:.3e}"
+                flips.append((l, t, float(margin[t, l])))
+                first = min(first, t)
+                break   # rows after a flip in this layer are no longer comparable
+        clean[l] = first
+    return clean, flips

@@ -30,6 +30,32 @@ def test_cxx_gguf_reader_agrees_with_python_reader(pkg, tiny):
         all(abs(tiny["model"].cfg[k] - tiny["cfg"][k]) < 1e-6 * max(1, abs(tiny["cfg"][k])) for k in tiny["model"].cfg)
 
 
+def test_split_checkpoint_opens_from_any_shard(pkg, tiny, tmp_path):
+    # gguf/gguf.go:748-818 OpenSet: any member names the set; an incomplete or inconsistent set is refused
+    import shutil
+    r = tiny["reader"]
+    meta = modelgen.config.metadata(tiny["cfg"] | {"full_attention_interval": 4, "types": {}})
+    paths = pkg.gguf.write_split(str(tmp_path / "tiny"), "qwen3next", meta, r.tensors, 3)
+    m = pkg.Model.open(paths[1])
+    for name in ("token_embd.weight", "blk.0.attn_qkv.weight", "blk.3.attn_v.weight", "output.weight"):
+        assert np.array_equal(m.read_tensor(name), r.tensors[name][2]), name
+    g = pkg.Graph(m, n_kv=32, use_cuda_graph=False)
+    whole = pkg.Graph(tiny["model"], n_kv=32, use_cuda_graph=False)
+    ids = prompt(tiny["cfg"], 5, seed=15)
+    assert np.array_equal(g.forward(ids)[0].view(np.uint32), whole.forward(ids)[0].view(np.uint32))
+    # a shard is missing
+    d2 = tmp_path / "partial"; d2.mkdir()
+    for p in paths[:2]:
+        shutil.copy(p, d2)
+    with pytest.raises(pkg.lib.B200Error, match="shard 3 of 3 is missing"):
+        pkg.Model.open(str(d2 / "tiny-00001-of-00003.gguf"))
+    # shards in the wrong places
+    d3 = tmp_path / "swapped"; d3.mkdir()
+    shutil.copy(paths[0], d3 / "tiny-00002-of-00003.gguf"); shutil.copy(paths[1], d3 / "tiny-00001-of-00003.gguf"); shutil.copy(paths[2], d3)
+    with pytest.raises(pkg.lib.B200Error, match="split.no"):
+        pkg.Model.open(str(d3 / "tiny-00001-of-00003.gguf"))
+
+
 def test_prefill_matches_oracle_layer_by_layer(pkg, tiny):
     cfg = tiny["cfg"]
     ids = prompt(cfg, 24)
@@ -259,6 +285,35 @@ def test_device_greedy_loop_and_cuda_graph_replay(pkg, tiny):
     assert [int(np.argmax(l0))] + out[:, 0].tolist()[:-1] == host_ids[:23] or out[:, 0].tolist() == host_ids[1:24]
     assert dev.past() == len(ids) + 23
     assert dev.last_launches() > 0 and dev.last_device_ms() > 0
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_graph_survives(pkg, tiny):
+    """Failure detection without a fault: a kernel whose bounded wait nothing can satisfy gives up, sets the
+    graph's error word and returns; the pass after it reports ETIMEOUT, and the graph then works again."""
+    cfg = tiny["cfg"]
+    ids = prompt(cfg, 10, seed=12)
+    g = pkg.Graph(tiny["model"], n_kv=64, use_cuda_graph=False)
+    want, _ = g.forward(ids)
+    g.inject_wait_timeout()
+    with pytest.raises(pkg.lib.B200Error) as e:
+        g.forward(ids)
+    assert e.value.status == pkg.lib.ETIMEOUT
+    again, _ = g.forward(ids)               # the error word was cleared with the report
+    assert np.array_equal(again.view(np.uint32), want.view(np.uint32))
+
+
+def test_extend_input_and_pass_experts(pkg, tiny):
+    cfg = tiny["cfg"]
+    ids = prompt(cfg, 6, seed=14)
+    g = pkg.Graph(tiny["model"], n_kv=32, use_cuda_graph=False)
+    a, _ = g.forward(ids)
+    g.reset()
+    b, hb = g.extend_input(ids)             # ExtendInput with no images is Extend (llm/graph.go:1709-1716)
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+    with pytest.raises(pkg.lib.B200Error):
+        g.extend_input(ids, n_images=1)     # no vision tower
+    assert cfg["n_expert_used"] <= g.pass_experts() <= min(cfg["n_expert"], cfg["n_expert_used"] * len(ids))
+    assert np.array_equal(g.residual_row(len(ids) - 1), hb)
 
 
 def test_capacity_and_id_refusals(pkg, tiny):

@@ -86,6 +86,60 @@ def test_speculative_output_is_plain_greedy(pkg, drafted, depth):
     assert got3[:n_out] == want
 
 
+def test_slotted_speculation_is_plain_greedy_per_slot(pkg, drafted):
+    """Config 5's batch shape on the tiny model: several sequences speculate over ONE slotted graph and one
+    slotted draft cache, their rounds interleaved; every slot emits its own plain greedy sequence
+    (llm/spec_slots_test.go:199 TestServedSpeculationIsPlain)."""
+    cfg = drafted["cfg"]
+    S, n_out, depth = 4, 12, 2
+    rng = np.random.default_rng(17)
+    prompts = [rng.integers(0, cfg["vocab"], 9 + 3 * s).astype(np.int32) for s in range(S)]
+    want = [plain_greedy(pkg, drafted["model"], p, n_out) for p in prompts]
+    g = pkg.Graph(drafted["model"], n_kv=96, max_tokens=32, slots=S, speculative=True, spec_rows=depth + 1, use_cuda_graph=False)
+    assert g.draft_slots() == S and g.draft_max_rows() >= depth + 1 and g.draft_wide() == cfg["n_embd"]
+    sps = [pkg.spec.Speculator(g, depth=depth, slot=s) for s in range(S)]
+    got = [[sp.prime(p)] for sp, p in zip(sps, prompts)]
+    rnd = 0
+    while any(len(o) < n_out for o in got):
+        for s in ((0, 2, 1, 3) if rnd % 2 else (3, 1, 0, 2)):     # interleave in changing orders
+            if len(got[s]) < n_out:
+                base = len(got[s])
+                # slot 1 gets a proposer that knows the future, the others the real (random) draft head
+                prop = (lambda lg, k, b=base, w=want[s]: w[b + k] if b + k < len(w) else 0) if s == 1 else None
+                got[s] += sps[s].round(propose=prop)
+        rnd += 1
+    for s in range(S):
+        assert got[s][:n_out] == want[s], s
+    assert sps[1].stats["accepted"] > 0
+
+
+def test_speculate_first_and_draft_vocabulary(pkg, drafted):
+    cfg = drafted["cfg"]
+    g = pkg.Graph(drafted["model"], n_kv=32, speculative=True, spec_rows=3, use_cuda_graph=False)
+    plain = pkg.Graph(drafted["model"], n_kv=32, use_cuda_graph=False)
+    g.forward([1, 2, 3]); plain.forward([1, 2, 3])
+    assert not g.speculating()
+    g.speculate(True); g.speculate_first(True)
+    assert g.speculating()
+    g.extend_rows([7, 8, 9])
+    with pytest.raises(pkg.lib.B200Error):
+        g.rewind()                          # with SpeculateFirst a pass ends by Commit or KeepFirst (llm/graph.go:1166)
+    g.keep_first()
+    assert g.past() == 4
+    g.speculate(False)
+    a, _ = g.extend([5]); plain.extend([7]); b, _ = plain.extend([5])
+    assert_close(a, b, "after keep_first", tol=1e-3)
+    # SetVocab: draft logits over the first k ids only (llm/mtp.go:675)
+    with pytest.raises(pkg.lib.B200Error):
+        g.draft_set_vocab(1000)             # not a multiple of 16
+    g.draft_set_vocab(4096)
+    _, res = plain.extend_residual([11, 12])
+    _, lg = g.draft_rows(res[:1], [12])
+    assert lg.shape == (1, 4096)
+    g.draft_reset()
+    assert g.draft_past() == 0
+
+
 def test_speculation_refusals(pkg, drafted):
     g = pkg.Graph(drafted["model"], n_kv=32, speculative=True, spec_rows=3, use_cuda_graph=False)
     g.forward([1, 2, 3])

@@ -100,3 +100,20 @@ def test_argmax_ties_to_lowest_id(orc):
     # llm/sample.go:359-367
     assert orc.argmax(np.array([1, 3, 3, 2], dtype=np.float32)) == 1
     assert orc.argmax(np.array([-np.inf, -np.inf], dtype=np.float32)) == 0
+
+
+def test_fp16_weight_mode_rounds_only_the_named_matrices(orc, tiny_path):
+    """The oracle's many-row arithmetic: dequantised weights rounded to fp16 (shaders/llm_gemm.comp MODE 2).
+    With no bit set the result is the device-like one; the head bit alone changes only what the head does."""
+    import modelgen
+    om, cfg, _ = modelgen.oracle_model(tiny_path)
+    ids = np.random.default_rng(2).integers(0, cfg["vocab"], 3).astype(np.int32)
+    base, tb = om.seq().extend(ids, trace=("hidden",))
+    same, _ = om.seq().extend(ids, numerics=orc.DEVICE_LIKE)
+    assert np.array_equal(base, same)
+    head, th = om.seq().extend(ids, numerics=orc.DEVICE_LIKE | orc.W16_HEAD, trace=("hidden",))
+    assert np.array_equal(tb["hidden"], th["hidden"]) and not np.array_equal(base, head)
+    allw, ta = om.seq().extend(ids, numerics=orc.DEVICE_LIKE | orc.W16_ALL, trace=("hidden",))
+    assert not np.array_equal(tb["hidden"], ta["hidden"])
+    scale = np.abs(base).max()
+    assert np.abs(head - base).max() < 2e-3 * scale and np.abs(allw - base).max() < 1e-2 * scale
