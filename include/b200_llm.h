@@ -72,6 +72,8 @@ typedef struct {
   double host_ms;        /* host wall clock around enqueue + wait of every pass (Submit) */
   int32_t last_rows, last_launches;
   float last_device_ms;
+  int64_t expert_streams; /* routed experts whose weights the passes streamed, summed over layers and passes (what
+                             a step's byte count needs: a many-slot pass touches far fewer than rows x used) */
 } b200_graph_stats;
 
 /* Graph.ExtendInput's argument (llm/graph.go:1716): token ids plus, in the reference, image spans.
@@ -182,6 +184,31 @@ int32_t b200_graph_timeline(b200_graph* g, int64_t* dst, int32_t max_launches);
  * [n_layer][rows][used] (int32), 3 routing weights [n_layer][rows][used+1], 4 top-k margin
  * [n_layer][rows]. Returns bytes written or a negative status. */
 int64_t b200_graph_trace(b200_graph* g, int32_t what, void* dst, int64_t nbytes);
+
+/* ---- expert parallelism over NVLink peer memory (no counterpart in the reference, which keeps every expert on
+ * one device: llm/gpu_moe.go:693-705) -----------------------------------------------------------------------------
+ * `world` ranks, one GPU each, every rank holding the checkpoint and its own slots. With the switch on, a
+ * batched decode pass (b200_graph_decode_rows / _generate_greedy with the SAME row count on every rank, called at
+ * the same time) runs each MoE layer expert-parallel: rank r computes the routed experts
+ * [r * n_expert / world, (r + 1) * n_expert / world) for the rows of ALL ranks; rows and routing travel as peer
+ * stores into buffers every rank exposes, outputs travel back the same way, and the row's owner adds them in slot
+ * order, so the logits are those of the same pass with all experts local. world * rows must fit max_tokens.
+ * Waits on a peer are bounded (2 s): a rank that never arrives turns the pass into B200_ETIMEOUT.
+ *
+ * One process per GPU: every rank calls _ep_export, the hosts exchange the 64-byte handles (any transport), every
+ * rank calls _ep_attach with all of them in rank order. Ranks that share a process (one graph per device) call
+ * _ep_prepare and then _ep_attach_local with the graphs in rank order instead. */
+typedef struct { unsigned char bytes[64]; } b200_ep_handle;
+int32_t b200_graph_ep_export(b200_graph* g, int32_t rank, int32_t world, b200_ep_handle* out);
+int32_t b200_graph_ep_attach(b200_graph* g, const b200_ep_handle* handles /* [world] */);
+int32_t b200_graph_ep_prepare(b200_graph* g, int32_t rank, int32_t world);
+int32_t b200_graph_ep_attach_local(b200_graph* g, b200_graph* const* graphs /* [world] */, int32_t world);
+int32_t b200_graph_ep_enable(b200_graph* g, int32_t on);
+
+/* Fills `cells` cells of the current slot's KV caches (fp16, per layer: keys normal(0,1), values normal(0,0.5))
+ * and its DeltaNet state (normal(0,0.05)) with seeded values and declares them prefilled. For throughput
+ * measurements of long contexts that are "already there": the timed decode then reads real, non-zero caches. */
+int32_t b200_graph_synth_context(b200_graph* g, int32_t cells, uint64_t seed);
 
 /* ---- MTP draft head (llm.MTPHead, llm/mtp.go:441-760) ---------------------------------- */
 /* One draft step per row: seeds from residual rows hs [n][n_embd] and token ids (the tokens

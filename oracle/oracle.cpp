@@ -63,9 +63,10 @@ std::vector<float> to_f32(const Tensor& t) {
 }
 
 // y = W x over rows [0, rows) of t starting at row0; serial f32 sum (llm/hc.go:255-264).
-// w16: every dequantised weight is rounded to fp16 first, as the reference's many-row tensor-core
-// GEMMs do when they unpack a weight slab into LDS (shaders/llm_gemm.comp MODE 2,
-// shaders/llm_moe_gemm.comp:260-261, 428-430); its decode GEMVs keep the f32 value.
+// w16: every weight is an fp16 value, as in the reference's many-row tensor-core GEMMs, which round the
+// dequantised weight when they unpack a slab into LDS (shaders/llm_gemm.comp MODE 2,
+// shaders/llm_moe_gemm.comp:260-261, 428-430; formed as dequantize_w16 describes); its decode GEMVs keep
+// the f32 value.
 void matvec(const Tensor& t, int64_t row0, int64_t rows, const float* x, float* y, bool w16 = false) {
   const int64_t k = t.ne[0];
 #pragma omp parallel
@@ -77,8 +78,8 @@ void matvec(const Tensor& t, int64_t row0, int64_t rows, const float* x, float* 
       if (t.type == T_F32) {
         w = (const float*)t.row(row0 + r);
       } else {
-        dequantize(t.type, t.row(row0 + r), k, buf.data());
-        if (w16) for (int64_t i = 0; i < k; i++) buf[(size_t)i] = f16_round(buf[(size_t)i]);
+        if (w16) dequantize_w16(t.type, t.row(row0 + r), k, buf.data());
+        else dequantize(t.type, t.row(row0 + r), k, buf.data());
         w = buf.data();
       }
       float s = 0;
@@ -406,6 +407,7 @@ uint16_t orc_f32_to_f16(float f) { return f32_to_f16(f); }
 float orc_f16_to_f32(uint16_t h) { return f16_to_f32(h); }
 int64_t orc_row_bytes(uint32_t type, int64_t n) { return row_bytes(type, n); }
 int orc_dequantize(uint32_t type, const void* data, int64_t n, float* dst) { return dequantize(type, data, n, dst); }
+int orc_dequantize_w16(uint32_t type, const void* data, int64_t n, float* dst) { return dequantize_w16(type, data, n, dst); }
 int orc_quantize(uint32_t type, const float* src, int64_t rows, int64_t k, void* dst) { return quantize(type, src, rows, k, dst); }
 
 int orc_matvec(uint32_t type, const void* wd, int64_t rows, int64_t k, const float* x, float* y) {

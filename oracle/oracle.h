@@ -68,6 +68,9 @@ uint16_t orc_f32_to_f16(float f);
 float orc_f16_to_f32(uint16_t h);
 int64_t orc_row_bytes(uint32_t type, int64_t n);
 int orc_dequantize(uint32_t type, const void* data, int64_t n, float* dst);
+/* The same elements as the many-row tensor-core kernels multiply them: fp16 values formed with the f32
+ * factors carried as fp16 hi + lo pairs (the correctly rounded fp16 of orc_dequantize's value, or a neighbour). */
+int orc_dequantize_w16(uint32_t type, const void* data, int64_t n, float* dst);
 int orc_quantize(uint32_t type, const float* src, int64_t rows, int64_t k, void* dst);
 
 /* y[rows] = W[rows][k] . x, serial f32 accumulation (llm/hc.go:255-264). */

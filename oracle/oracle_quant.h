@@ -196,6 +196,70 @@ inline void dequant_iq4_nl(const uint8_t* blk, float* out) {
 
 // n elements of `type` at `data` -> dst. Returns 0, or -1 for an unknown type or a
 // count that is not a whole number of blocks (gguf/dequant.go:54-100).
+// ---- weights as the many-row tensor-core kernels see them -------------------------------
+// The reference's many-row GEMMs unpack a weight slab into LDS as `float16_t(ds * nib - dm)`: the f32 value
+// rounded to fp16 once (shaders/llm_moe_gemm.comp:260-261, 428-430). The CUDA kernels form the same value in
+// fp16 arithmetic, with the two f32 factors d*sc and dmin*m carried as fp16 hi + lo pairs:
+//   w = fp16( fp16(q*hi(ds) + hi(-dm)) + fp16(q*lo(ds) + lo(-dm)) )
+// (each fp16(...) one fused multiply-add rounded once). That lands on the correctly rounded value or on a
+// neighbour of it (checked against the plain rounding over the reference's golden blocks by the oracle's
+// own tests), and it is what this function restates, so that a many-row pass is compared with an oracle that
+// multiplies bit-identical weights.
+inline float f16_round_d(double x) {
+  if (x == 0.0 || !std::isfinite(x)) return (float)x;
+  int e;
+  std::frexp(x, &e);                      // |x| = f * 2^e, f in [0.5, 1)
+  int q = e - 11;                         // quantum 2^q keeps 11 significant bits
+  if (q < -24) q = -24;                   // subnormal range of fp16
+  const double r = std::nearbyint(std::ldexp(x, -q));   // ties to even
+  return (float)std::ldexp(r, q);
+}
+inline void h16_split(float v, float* hi, float* lo) { *hi = f16_round(v); *lo = f16_round(v - *hi); }
+inline float w16_k(int q, float dh, float dl, float nh, float nl) {
+  const float t1 = f16_round_d((double)q * dh + nh), t2 = f16_round_d((double)q * dl + nl);
+  return f16_round_d((double)t1 + (double)t2);
+}
+inline float w16_s(int a, float dh, float dl) { return f16_round_d((double)a * dh + (double)f16_round_d((double)a * dl)); }
+
+inline void dequant_w16_q45_k(const uint8_t* blk, float* out, bool q5) {
+  float d = rd_f16(blk), dmin = rd_f16(blk + 2);
+  const uint8_t* scales = blk + 4; const uint8_t* qh = blk + 16; const uint8_t* ql = blk + (q5 ? 48 : 16);
+  for (int j = 0; j < 4; j++) {
+    for (int half = 0; half < 2; half++) {
+      uint8_t sc, m;
+      scale_min_k4(2 * j + half, scales, &sc, &m);
+      float dh, dl, nh, nl;
+      h16_split(d * (float)sc, &dh, &dl);
+      h16_split(-(dmin * (float)m), &nh, &nl);
+      for (int l = 0; l < 32; l++) {
+        int q = half ? (ql[32 * j + l] >> 4) : (ql[32 * j + l] & 0xF);
+        if (q5 && ((qh[l] >> (2 * j + half)) & 1)) q += 16;
+        out[64 * j + 32 * half + l] = w16_k(q, dh, dl, nh, nl);
+      }
+    }
+  }
+}
+inline void dequant_w16_q6_k(const uint8_t* blk, float* out) {
+  const uint8_t* ql = blk; const uint8_t* qh = blk + 128; const int8_t* sc = (const int8_t*)(blk + 192);
+  float d = rd_f16(blk + 208);
+  for (int n = 0; n < 256; n += 128) {
+    for (int l = 0; l < 32; l++) {
+      int is = l / 16;
+      uint8_t h = qh[n / 4 + l];
+      const int q[4] = {(int)((ql[n / 2 + l] & 0xF) | (((h >> 0) & 3) << 4)) - 32, (int)((ql[n / 2 + l + 32] & 0xF) | (((h >> 2) & 3) << 4)) - 32,
+                        (int)((ql[n / 2 + l] >> 4) | (((h >> 4) & 3) << 4)) - 32, (int)((ql[n / 2 + l + 32] >> 4) | (((h >> 6) & 3) << 4)) - 32};
+      const int8_t* g = sc + n / 16 + is;
+      for (int k = 0; k < 4; k++) {
+        float dh, dl;
+        h16_split(d * (float)g[2 * k], &dh, &dl);
+        out[n + l + 32 * k] = w16_s(q[k], dh, dl);
+      }
+    }
+  }
+}
+// n elements of `type` as fp16-representable weights; types the tensor-core kernels do not take are rounded once.
+inline int dequantize_w16(uint32_t type, const void* data, int64_t n, float* dst);
+
 inline int dequantize(uint32_t type, const void* data, int64_t n, float* dst) {
   int e, nb;
   if (!block_geometry(type, &e, &nb) || n % e) return -1;
@@ -224,6 +288,24 @@ inline int dequantize(uint32_t type, const void* data, int64_t n, float* dst) {
 // llm/quantk.go:211-226 (packScaleMinK4). float32 accumulators on purpose
 // (llm/sim.go:803-808). Compile with -ffp-contract=off: the reference's host language
 // does not fuse multiply-adds on x86-64.
+
+inline int dequantize_w16(uint32_t type, const void* data, int64_t n, float* dst) {
+  const uint8_t* p = (const uint8_t*)data;
+  if (type == T_Q4_K || type == T_Q5_K) {
+    if (n % 256) return -1;
+    const int bb = type == T_Q4_K ? 144 : 176;
+    for (int64_t b = 0; b < n / 256; b++) dequant_w16_q45_k(p + b * bb, dst + b * 256, type == T_Q5_K);
+    return 0;
+  }
+  if (type == T_Q6_K) {
+    if (n % 256) return -1;
+    for (int64_t b = 0; b < n / 256; b++) dequant_w16_q6_k(p + b * 210, dst + b * 256);
+    return 0;
+  }
+  int rc = dequantize(type, data, n, dst);   // Q8_0: fp16(d * q) is the single rounding; F16/F32: rounded once
+  if (rc == 0) for (int64_t i = 0; i < n; i++) dst[i] = f16_round(dst[i]);
+  return rc;
+}
 
 inline float nearest_int(float v) { return (float)nearbyint((double)v); }  // round-half-even
 

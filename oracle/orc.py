@@ -55,6 +55,7 @@ def lib():
         L.orc_f16_to_f32.restype = C.c_float; L.orc_f16_to_f32.argtypes = [C.c_uint16]
         L.orc_row_bytes.restype = C.c_int64; L.orc_row_bytes.argtypes = [C.c_uint32, C.c_int64]
         L.orc_dequantize.argtypes = [C.c_uint32, C.c_void_p, C.c_int64, C.c_void_p]
+        L.orc_dequantize_w16.argtypes = [C.c_uint32, C.c_void_p, C.c_int64, C.c_void_p]
         L.orc_quantize.argtypes = [C.c_uint32, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
         L.orc_matvec.argtypes = [C.c_uint32, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
         L.orc_rmsnorm.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_float, C.c_void_p]
@@ -81,6 +82,15 @@ def dequantize(typ, data, n):
     buf = np.ascontiguousarray(np.frombuffer(data, dtype=np.uint8))
     out = np.empty(n, dtype=np.float32)
     if lib().orc_dequantize(typ, buf.ctypes.data, n, out.ctypes.data) != 0:
+        raise ValueError(f"cannot dequantize type {typ} x {n}")
+    return out
+
+
+def dequantize_w16(typ, data, n):
+    """The elements as the tensor-core kernels multiply them (fp16 values)."""
+    buf = np.ascontiguousarray(np.frombuffer(data, dtype=np.uint8))
+    out = np.empty(n, dtype=np.float32)
+    if lib().orc_dequantize_w16(typ, buf.ctypes.data, n, out.ctypes.data) != 0:
         raise ValueError(f"cannot dequantize type {typ} x {n}")
     return out
 

@@ -8,7 +8,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200llm.so")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall"]
-SOURCES = {"kernels.cu": [], "qgemv.cu": [], "qgemm.cu": [], "synth.cu": ["-fmad=false"], "model.cu": [], "graph.cu": [], "api.cu": [], "static_scratch.cu": [], "gguf_reader.cpp": []}
+SOURCES = {"kernels.cu": [], "qgemv.cu": [], "qgemm.cu": [], "synth.cu": ["-fmad=false"], "model.cu": [], "graph.cu": [], "api.cu": [], "static_scratch.cu": [], "ep.cu": [], "gguf_reader.cpp": []}
 
 
 def _newer(target, deps):

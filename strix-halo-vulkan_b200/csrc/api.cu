@@ -173,8 +173,38 @@ int32_t b200_graph_rewind(b200_graph* g) {
 int32_t b200_graph_residual_row(b200_graph* g, int32_t r, float* dst) { if (!g || !dst) { set_error("residual_row: null argument"); return EINVAL_; } return g->g.residual_row(r, dst); }
 int32_t b200_graph_pass_experts(b200_graph* g, int32_t* out) { if (!g || !out) { set_error("pass_experts: null argument"); return EINVAL_; } return g->g.pass_experts(out); }
 uint32_t b200_graph_fp16_weight_mask(const b200_graph* g, int32_t rows, int32_t logit_rows) { return g ? g->g.fp16_weight_mask(rows, logit_rows) : 0; }
-int32_t b200_graph_stats_get(const b200_graph* g, b200_graph_stats* out) { if (!g || !out) return EINVAL_; *out = g->g.stats; return OK; }
-int32_t b200_graph_stats_reset(b200_graph* g) { if (!g) return EINVAL_; g->g.stats = b200_graph_stats{}; return OK; }
+int32_t b200_graph_stats_get(const b200_graph* g, b200_graph_stats* out) {
+  if (!g || !out) return EINVAL_;
+  *out = g->g.stats;
+  int64_t dev = 0;
+  cudaSetDevice(g->g.m->device);
+  if (cudaMemcpy(&dev, g->g.distinct_dev, sizeof(dev), cudaMemcpyDeviceToHost) != cudaSuccess) { set_error("stats: cannot read the device counter"); return ECUDA; }
+  out->expert_streams = dev + g->g.single_row_layers * g->g.m->c.n_expert_used;
+  return OK;
+}
+int32_t b200_graph_stats_reset(b200_graph* g) {
+  if (!g) return EINVAL_;
+  g->g.stats = b200_graph_stats{}; g->g.single_row_layers = 0;
+  cudaSetDevice(g->g.m->device);
+  if (cudaMemset(g->g.distinct_dev, 0, sizeof(int64_t)) != cudaSuccess) { set_error("stats: cannot clear the device counter"); return ECUDA; }
+  return OK;
+}
+int32_t b200_graph_ep_export(b200_graph* g, int32_t rank, int32_t world, b200_ep_handle* out) { if (!g || !out) return EINVAL_; return g->g.ep_export(rank, world, out->bytes); }
+int32_t b200_graph_ep_attach(b200_graph* g, const b200_ep_handle* handles) { if (!g || !handles) return EINVAL_; return g->g.ep_attach(handles); }
+int32_t b200_graph_ep_prepare(b200_graph* g, int32_t rank, int32_t world) { if (!g) return EINVAL_; return g->g.ep_prepare(rank, world); }
+int32_t b200_graph_ep_attach_local(b200_graph* g, b200_graph* const* graphs, int32_t world) {
+  if (!g || !graphs || world < 1 || world > EP_MAX_RANKS) { set_error("ep_attach_local: bad argument"); return EINVAL_; }
+  Graph* peers[EP_MAX_RANKS] = {};
+  for (int i = 0; i < world; i++) peers[i] = graphs[i] ? &graphs[i]->g : nullptr;
+  return g->g.ep_attach_local(peers, world);
+}
+int32_t b200_graph_ep_enable(b200_graph* g, int32_t on) {
+  if (!g) return EINVAL_;
+  if (on && !g->g.ep_ready) { set_error("ep_enable: attach the peers first"); return ESTATE; }
+  g->g.ep_on = on != 0;
+  return OK;
+}
+int32_t b200_graph_synth_context(b200_graph* g, int32_t cells, uint64_t seed) { if (!g) return EINVAL_; return g->g.synth_context(g->g.cur, cells, seed); }
 int32_t b200_graph_inject_wait_timeout(b200_graph* g) { if (!g) return EINVAL_; return g->g.inject_wait_timeout(); }
 
 int32_t b200_graph_generate_greedy(b200_graph* g, const int32_t* slots, const int32_t* first_ids, int32_t n, int32_t steps, int32_t* out_ids) {

@@ -30,6 +30,7 @@ Graph::~Graph() {
   for (auto& kv : decode_graphs) cudaGraphExecDestroy(kv.second);
   for (auto& kv : greedy_graphs) cudaGraphExecDestroy(kv.second);
   for (auto& kv : ckpts) { for (float* p : kv.second.state) cudaFree(p); for (float* p : kv.second.ring) cudaFree(p); }
+  for (void* p : ep_mapped) cudaIpcCloseMemHandle(p);
   for (void* p : allocs) cudaFree(p);
   if (stage) cudaFreeHost(stage);
   if (logits_host) cudaFreeHost(logits_host);
@@ -94,6 +95,7 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   B200_TRY(dalloc(&ids_dev, (size_t)MR)); B200_TRY(dalloc(&next_ids, (size_t)MR)); B200_TRY(dalloc(&row_slot, (size_t)MR));
   B200_TRY(dalloc(&row_pos, (size_t)MR)); B200_TRY(dalloc(&logit_rows, (size_t)MR)); B200_TRY(dalloc(&seqs, (size_t)MR));
   B200_TRY(dalloc(&hist_len, 1));
+  B200_TRY(dalloc(&distinct_dev, 1));
   if (c.has_draft) { B200_TRY(dalloc(&e_buf, (size_t)MR * H)); B200_TRY(dalloc(&hs_buf, (size_t)MR * H)); B200_TRY(dalloc(&xcat16, (size_t)MR * 2 * H)); }
   // rotary table, angle walked in f64 like the reference (llm/attn.go:554-584, llm/gpu_attn.go:1440-1477)
   {
@@ -204,6 +206,9 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
   const int hd = c.head_dim, qw = c.n_head * hd, kvw = c.n_head_kv * hd, used = c.n_expert_used, slots1 = used + 1;
   const int xcols = std::min(M, QG_MAXCOLS);
   const bool fused = M <= QG_FUSED_ROWS && H <= QG_COMBINE_MAX_K;
+  // expert-parallel MoE block: plain decode passes only (every rank runs the same number of rows at the same time)
+  const bool epx = ep_on && ep_ready && !f.draft && !f.spec && n_seq == M;
+  const int Mg = epx ? M * ep.world : M;   // rows of all ranks
   float* hc = hbuf[0];      // residual rows of this pass
   bool pending = false;     // fused passes: the MoE output of the last layer is not in hc yet; the next
                             // projection of the residual folds it in while staging and writes the other buffer
@@ -369,10 +374,11 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     if (fused) { r.h = hc; r.gamma = (const float*)L.ffn_norm.data; r.ss_in = ss_part; r.ss_n = ss_n; r.eps = c.eps; r.xn_out = xn16; }
     r.M = M; r.H = H; r.nE = c.n_expert; r.used = used; r.logits = r_logits; r.probs = nullptr; r.topk = topk; r.topk_w = topk_w;
     r.tl = tl(); r.margin = margin; r.entries = entries; r.n_entries = n_entries; r.cols = cols; r.ticket = r_ticket; r.max_entries = max_entries;
-    r.defer = fused && M == 1; r.ecols = entry_cols(M);
+    r.defer = fused && M == 1 && !epx; r.ecols = entry_cols(M); r.distinct = distinct_dev;
+    if (epx) { r.entries = nullptr; r.gprob = nullptr; }   // routing only: the work list comes from the gathered routing
     // 32 rows per expert on average and more: the experts run as grouped tensor-core GEMMs over expert-sorted
     // rows (below that the column-tiled kernel, which streams each expert's weights in whole tiles, is faster)
-    const bool moe_gemm = pass_moe_gemm(c, L, M, H);
+    const bool moe_gemm = pass_moe_gemm(c, L, M, H) && !epx;
     r.gprob = moe_gemm ? gprob : nullptr;
     if (use_gemm && M >= 64 && L.router.type == T_Q8_0) {
       // many rows: the router logits are one more tensor-core GEMM (the reference's prefill router is an fp16
@@ -387,9 +393,33 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     } else {
       B200_TRY(launch_router(r, pdl(), st));
     }
-    const int ne = max_entries_for(M);
+    const int ne = max_entries_for(Mg);
     comb_used = used; comb_w = topk_w;
-    if (moe_gemm) {
+    float* down_rows = down;   // where the pairs of this rank's rows land
+    if (epx) {
+      // dispatch -> work list over my experts -> gate/up -> down (stores to the rows' owners) -> barrier
+      EpParams e = ep;
+      e.rows = M; e.xn = xn16; e.topk = topk;
+      B200_TRY(launch_ep_dispatch(e, pdl(), st));
+      RouterParams w = r;
+      w.M = Mg; w.topk = reinterpret_cast<int32_t*>(ep_arena + ep.off_topk); w.entries = entries; w.ecols = entry_cols(Mg);
+      w.e_lo = ep.rank * (c.n_expert / ep.world); w.e_hi = w.e_lo + c.n_expert / ep.world; w.sh_lo = ep.rank * M; w.sh_hi = w.sh_lo + M;
+      B200_TRY(launch_ep_worklist(w, pdl(), st));
+      const int ecx = std::min(std::min(Mg, QG_MAXCOLS), entry_cols(Mg));
+      QGemvParams p = base(L.gate_exps, H, c.ffn_expert, reinterpret_cast<const __half*>(ep_arena + ep.off_xg), H);
+      p.w2[0] = L.up_exps.data; p.ws = L.gate_sh.data; p.ws2 = L.up_sh.data; p.expert_stride = (int64_t)c.ffn_expert * L.gate_exps.stride;
+      p.entries = entries; p.n_entries = n_entries; p.cols = cols; p.x_div = slots1; p.xcols = ecx; p.M = Mg;
+      p.y16 = act16; p.ldy = c.ffn_expert;
+      B200_TRY(launch_qgemv(L.gate_exps.type, PRO_F16, EPI_SWIGLU, true, true, p, ne, pdl(), st));
+      QGemvParams q = base(L.down_exps, c.ffn_expert, H, act16, c.ffn_expert);
+      q.ws = L.down_sh.data; q.expert_stride = (int64_t)H * L.down_exps.stride;
+      q.entries = entries; q.n_entries = n_entries; q.cols = cols; q.x_div = 1; q.xcols = ecx; q.M = Mg;
+      q.y = nullptr; q.ldy = H; q.y_rank_rows = M * slots1;
+      for (int i = 0; i < ep.world; i++) q.y_rank[i] = reinterpret_cast<float*>(ep.base[i] + ep.off_down);
+      B200_TRY(launch_qgemv(L.down_exps.type, PRO_F16, EPI_STORE, false, true, q, ne, pdl(), st));
+      B200_TRY(launch_ep_barrier(e, pdl(), st));
+      down_rows = reinterpret_cast<float*>(ep_arena + ep.off_down);
+    } else if (moe_gemm) {
       const int avg = M * used / c.n_expert, tne = avg <= 40 ? 64 : 128, tie = tne == 64 ? 0 : 1;
       B200_TRY(launch_moe_gather(xn16, cols, M * used, slots1, H, xperm16, pdl(), st));
       QGemmParams g{};
@@ -434,10 +464,12 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       B200_TRY(launch_qgemv(L.down_exps.type, PRO_F16, EPI_STORE, false, true, q, ne, pdl(), st));
     }
     }
-    if (fused && M == 1) pending = true;
+    if (fused && M == 1 && !epx) pending = true;
     else {
       const DTensor& next_norm = f.draft ? L.head_norm : (l + 1 < c.n_layer ? m->layers[l + 1].attn_norm : m->output_norm);
-      B200_TRY(launch_row_tail(row_tail(2, next_norm), pdl(), st));
+      TailParams tp = row_tail(2, next_norm);
+      tp.down = down_rows;
+      B200_TRY(launch_row_tail(tp, pdl(), st));
       xn_valid = fused;
     }
     if (o.trace) {
@@ -513,7 +545,8 @@ int Graph::run_rows(const int32_t* ids, const int* slots, const int* pos, int M,
   bool single = !f.spec && !f.draft && !o.trace && o.use_cuda_graph && n_seq == M && n_lr == M && !f.want_residual;
   B200_CUDA(cudaEventRecord(ev0, st));
   if (single) {
-    auto it = decode_graphs.find(M);
+    const int gkey = M * 2 + (ep_on ? 1 : 0);
+    auto it = decode_graphs.find(gkey);
     if (it == decode_graphs.end()) {
       // the decode step is captured once and replayed, positions living in device memory
       // (the reference's pre-recorded command buffer: llm/graph.go:238-258)
@@ -528,11 +561,11 @@ int Graph::run_rows(const int32_t* ids, const int* slots, const int* pos, int M,
       e = cudaGraphInstantiate(&exec, graph, 0);
       cudaGraphDestroy(graph);
       if (e != cudaSuccess) { set_error(std::string("graph instantiate: ") + cudaGetErrorString(e)); return ECUDA; }
-      it = decode_graphs.emplace(M, exec).first;
-      decode_h[M] = h;
+      it = decode_graphs.emplace(gkey, exec).first;
+      decode_h[gkey] = h;
     }
     B200_CUDA(cudaGraphLaunch(it->second, st));
-    h = decode_h[M];
+    h = decode_h[gkey];
   } else {
     B200_TRY(upload_stage(this, M, n_seq, n_lr));
     B200_TRY(enqueue_pass(M, n_seq, n_lr, f));
@@ -548,6 +581,7 @@ int Graph::run_rows(const int32_t* ids, const int* slots, const int* pos, int M,
   stats.passes++; stats.rows += M; stats.launches += last_launches; stats.device_ms += ms;
   stats.host_ms += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - host_t0).count();
   stats.last_rows = M; stats.last_launches = last_launches; stats.last_device_ms = ms;
+  if (M == 1 && !f.draft) single_row_layers += m->c.n_layer;
   return OK;
 }
 
@@ -608,6 +642,7 @@ int Graph::decode_rows(const int32_t* slots_in, const int32_t* ids, int n, const
     if (past[s] + 1 > o.n_kv) { set_error("decode_rows: slot " + std::to_string(s) + " is full"); return ECAPACITY; }
     seen[s] = 1; slots[i] = s; pos[i] = past[s]; lrows[i] = i; sq[i] = SeqDesc{s, i, 1, past[s]};
   }
+  if (ep_on && (int64_t)n * ep.world > MR) { set_error("decode_rows: with expert parallelism the rows of all ranks (" + std::to_string(n) + " x " + std::to_string(ep.world) + ") must fit max_tokens"); return ECAPACITY; }
   PassFlags f; f.want_all_logits = true;
   B200_TRY(run_rows(ids, slots.data(), pos.data(), n, sq, lrows, f));
   for (int i = 0; i < n; i++) past[slots[i]] += 1;
@@ -630,6 +665,7 @@ int Graph::generate_greedy(const int32_t* slots_in, const int32_t* first, int n,
     if (past[s] + steps > o.n_kv) { set_error("generate_greedy: slot " + std::to_string(s) + " would overflow its context"); return ECAPACITY; }
     seen[s] = 1; slots[i] = s; pos[i] = past[s]; lrows[i] = i; sq[i] = SeqDesc{s, i, 1, past[s]};
   }
+  if (ep_on && (int64_t)n * ep.world > MR) { set_error("generate_greedy: with expert parallelism the rows of all ranks must fit max_tokens"); return ECAPACITY; }
   B200_CUDA(cudaSetDevice(m->device));
   fill_stage(stage, MR, first, slots.data(), pos.data(), n, sq, lrows);
   B200_TRY(upload_stage(this, n, n, n));
@@ -637,7 +673,8 @@ int Graph::generate_greedy(const int32_t* slots_in, const int32_t* first, int n,
   PassFlags f; f.want_all_logits = true; f.greedy = true;
   cudaGraphExec_t exec = nullptr;
   if (o.use_cuda_graph && !o.trace) {
-    auto it = greedy_graphs.find(n);
+    const int gkey = n * 2 + (ep_on ? 1 : 0);
+    auto it = greedy_graphs.find(gkey);
     if (it == greedy_graphs.end()) {
       cudaGraph_t graph = nullptr;
       B200_CUDA(cudaStreamSynchronize(st));
@@ -648,7 +685,7 @@ int Graph::generate_greedy(const int32_t* slots_in, const int32_t* first, int n,
       e = cudaGraphInstantiate(&exec, graph, 0);
       cudaGraphDestroy(graph);
       if (e != cudaSuccess) { set_error(std::string("graph instantiate: ") + cudaGetErrorString(e)); return ECUDA; }
-      greedy_graphs.emplace(n, exec);
+      greedy_graphs.emplace(gkey, exec);
     } else exec = it->second;
   }
   B200_CUDA(cudaEventRecord(ev0, st));
@@ -662,6 +699,7 @@ int Graph::generate_greedy(const int32_t* slots_in, const int32_t* first, int n,
   B200_CUDA(cudaEventElapsedTime(&last_ms, ev0, ev1));
   stats.passes += steps; stats.rows += (int64_t)steps * n; stats.launches += (int64_t)steps * last_launches; stats.device_ms += last_ms;
   stats.last_rows = n; stats.last_launches = last_launches; stats.last_device_ms = last_ms / steps;
+  if (n == 1) single_row_layers += (int64_t)steps * m->c.n_layer;
   memcpy(out, ids_host, (size_t)steps * n * sizeof(int32_t));
   for (int i = 0; i < n; i++) past[slots[i]] += steps;
   spec_n = 0;
@@ -754,6 +792,34 @@ int Graph::restore(int handle) {
   B200_CUDA(cudaStreamSynchronize(st));
   past[cur] = ck.past;
   spec_n = 0;
+  return OK;
+}
+
+int Graph::synth_context(int slot, int cells, uint64_t seed) {
+  const b200_config& c = m->c;
+  if (cells < 0 || cells > o.n_kv) { set_error("synth_context: more cells than the slot holds"); return ECAPACITY; }
+  B200_CUDA(cudaSetDevice(m->device));
+  const int64_t kvw = (int64_t)c.n_head_kv * c.head_dim, n = (int64_t)cells * kvw;
+  if (n > 0) {
+    float* tmp = nullptr;   // f32 staging of one layer's cells, rounded to fp16 into the cache
+    B200_CUDA(cudaMalloc((void**)&tmp, (size_t)n * sizeof(float)));
+    int s = OK;
+    for (int i = 0; i < n_attn && s == OK; i++) {
+      for (int kv = 0; kv < 2 && s == OK; kv++) {
+        __half* dst = (kv ? vcache[i] : kcache[i]) + (size_t)slot * kv_slot_stride;
+        s = synth_fill(tmp, n, seed * 7919 + (uint64_t)(i * 2 + kv) * 104729 + (uint64_t)slot * 1299709, 0, 0.f, kv ? 0.5f : 1.0f, st);
+        if (s == OK) s = quantize_rows_device(T_F16, tmp, cells, kvw, (uint8_t*)dst, st);
+      }
+    }
+    cudaStreamSynchronize(st);
+    cudaFree(tmp);
+    B200_TRY(s);
+  }
+  for (int i = 0; i < n_dn; i++)
+    B200_TRY(synth_fill(dn_state[i] + (size_t)slot * state_slot_stride, state_slot_stride, seed * 15485863 + (uint64_t)i * 32452843 + (uint64_t)slot, 0, 0.f, 0.05f, st));
+  B200_CUDA(cudaStreamSynchronize(st));
+  past[slot] = cells;
+  if (slot == cur) spec_n = 0;
   return OK;
 }
 

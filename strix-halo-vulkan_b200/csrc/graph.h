@@ -5,6 +5,7 @@
 #include <map>
 #include <vector>
 
+#include "ep.cuh"
 #include "kernels.cuh"
 #include "model.h"
 
@@ -45,6 +46,8 @@ struct Graph {
   int32_t *topk = nullptr, *ids_dev = nullptr, *next_ids = nullptr, *history = nullptr;
   int *r_ticket = nullptr, *err_flag = nullptr, *err_host = nullptr, *n_entries = nullptr, *cols = nullptr, *row_slot = nullptr, *row_pos = nullptr, *logit_rows = nullptr, *hist_len = nullptr;
   int4* entries = nullptr;
+  int64_t* distinct_dev = nullptr;     // experts streamed by the work lists built so far (device counter)
+  int64_t single_row_layers = 0;       // layers run by single-row passes, whose experts are selected inside the expert kernel
   SeqDesc* seqs = nullptr;
   float* rope = nullptr;
   int proj_ld = 0, max_entries = 0, nsplit = 0, split_cells = 0;
@@ -75,6 +78,13 @@ struct Graph {
   int timeline_cap = 0;
   int launches = 0, last_launches = 0, draft_vocab = 0, draft_vocab_default = 0, resid_off = 0;
   float last_ms = 0.f;
+  // expert parallelism (ep.cuh): exchange arena, peers' arenas as mapped here, switch
+  EpParams ep{};
+  uint8_t* ep_arena = nullptr;
+  size_t ep_arena_bytes = 0;
+  int* ep_epoch = nullptr;
+  std::vector<void*> ep_mapped;
+  bool ep_ready = false, ep_on = false;
   // checkpoints: DeltaNet state + rings of a slot at a token boundary
   struct Ckpt { int slot, past; std::vector<float*> state, ring; };
   std::map<int, Ckpt> ckpts;
@@ -101,6 +111,11 @@ struct Graph {
   int pass_experts(int* out);
   int inject_wait_timeout();
   int finish_pass();
+  int ep_prepare(int rank, int world);
+  int ep_export(int rank, int world, void* handle64);
+  int ep_attach(const void* handles64);
+  int ep_attach_local(Graph* const* peers, int world);
+  int synth_context(int slot, int cells, uint64_t seed);
   template <class T> int dalloc(T** p, size_t n, bool zero = true);
 };
 

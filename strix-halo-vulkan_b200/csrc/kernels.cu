@@ -239,10 +239,21 @@ __device__ void build_work_list(const RouterParams& p, int* counts, int* offs, i
     tl_mark(p.tl, 6, true);
     return;
   }
+  const int e_lo = p.e_hi > 0 ? p.e_lo : 0, e_hi = p.e_hi > 0 ? p.e_hi : nE;
+  const int sh_lo = p.sh_hi > 0 ? p.sh_lo : 0, sh_hi = p.sh_hi > 0 ? p.sh_hi : M;
   for (int i = tid; i <= nE; i += 256) counts[i] = 0;
   __syncthreads();
-  for (int i = tid; i < M * used; i += 256) atomicAdd(&counts[__ldcg(p.topk + i)], 1);
+  for (int i = tid; i < M * used; i += 256) {
+    const int e = __ldcg(p.topk + i);
+    if (e >= e_lo && e < e_hi) atomicAdd(&counts[e], 1);
+  }
   __syncthreads();
+  if (p.distinct != nullptr) {   // experts this pass streams (what a step's byte count needs)
+    int mine = 0;
+    for (int e = tid; e < nE; e += 256) mine += counts[e] > 0;
+    mine = __reduce_add_sync(0xffffffffu, mine);
+    if (lane == 0 && mine > 0) atomicAdd(reinterpret_cast<unsigned long long*>(p.distinct), (unsigned long long)mine);
+  }
   if (warp == 0) {  // exclusive scans of the pair counts and of the entry counts (EC columns per entry)
     const int per = (nE + 31) / 32;
     int c = 0, en = 0;
@@ -268,19 +279,33 @@ __device__ void build_work_list(const RouterParams& p, int* counts, int* offs, i
   }
   // one GEMM problem per expert for the tensor-core expert kernels: rows [offs, offs + count) of the expert-sorted order
   if (p.gprob != nullptr) for (int e = tid; e < nE; e += 256) p.gprob[e] = make_int4(e, offs[e], counts[e], offs[e]);
-  const int nsh = (M + EC - 1) / EC;
+  const int nshr = sh_hi - sh_lo, nsh = (nshr + EC - 1) / EC;
   for (int i = tid; i < nsh; i += 256)
-    if (eoff[nE] + i < p.max_entries) p.entries[eoff[nE] + i] = make_int4(-1, offs[nE] + EC * i, min(EC, M - EC * i), 0);
+    if (eoff[nE] + i < p.max_entries) p.entries[eoff[nE] + i] = make_int4(-1, offs[nE] + EC * i, min(EC, nshr - EC * i), 0);
   if (tid == 0) *p.n_entries = min(eoff[nE] + nsh, p.max_entries);
   __syncthreads();
   for (int i = tid; i <= nE; i += 256) counts[i] = 0;
   __syncthreads();
   for (int i = tid; i < M * used; i += 256) {
     const int e = __ldcg(p.topk + i), n = i / used, k = i - n * used;
+    if (e < e_lo || e >= e_hi) continue;
     const int pos = atomicAdd(&counts[e], 1);
     p.cols[offs[e] + pos] = n * (used + 1) + k;
   }
-  for (int n = tid; n < M; n += 256) p.cols[offs[nE] + n] = n * (used + 1) + used;
+  for (int n = tid; n < nshr; n += 256) p.cols[offs[nE] + n] = (sh_lo + n) * (used + 1) + used;
+}
+
+// Work list of an expert-parallel pass: the gathered routing of every rank's rows, restricted to the experts
+// this rank owns. One CTA.
+__global__ void __launch_bounds__(256) ep_worklist_kernel(RouterParams p) {
+  __shared__ int counts[1025], offs[1025], eoff[1025];
+  pdl_wait();
+  pdl_launch();
+  build_work_list(p, counts, offs, eoff);
+}
+int launch_ep_worklist(const RouterParams& p, bool pdl, cudaStream_t st) {
+  if (p.nE > 1024 || p.used > 32 || p.M < 2) { set_error("ep_worklist: shape outside kernel limits"); return ECAPACITY; }
+  return launch_k(ep_worklist_kernel, dim3(1), dim3(256), 0, pdl, st, p);
 }
 
 __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
@@ -413,6 +438,7 @@ __global__ void __launch_bounds__(256) router_kernel(RouterParams p) {
   if (!is_last) return;
   __threadfence();
   if (tid == 0) *p.ticket = 0;
+  if (p.entries == nullptr) return;   // routing only (expert-parallel passes build their list from the gathered routing)
   build_work_list(p, counts, offs, eoff);
 }
 
@@ -531,6 +557,7 @@ __global__ void __launch_bounds__(256) route_rows_kernel(RouterParams p) {
   if (!is_last) return;
   __threadfence();
   if (tid == 0) *p.ticket = 0;
+  if (p.entries == nullptr) return;   // routing only
   build_work_list(p, counts, offs, eoff);
 }
 int launch_route_rows(const RouterParams& p, bool pdl, cudaStream_t st) {

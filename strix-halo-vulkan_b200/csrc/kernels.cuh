@@ -47,6 +47,8 @@ int launch_router(const RouterParams& p, bool pdl, cudaStream_t st);
 bool router_mma_fits(const RouterParams& p);
 int launch_router_mma(const RouterParams& p, bool pdl, cudaStream_t st);
 int launch_route_rows(const RouterParams& p, bool pdl, cudaStream_t st);
+// work list only, from routing that is already in p.topk (expert-parallel passes: the gathered routing)
+int launch_ep_worklist(const RouterParams& p, bool pdl, cudaStream_t st);
 int launch_moe_gather(const __half* xn, const int* cols, int pairs, int slots1, int H, __half* xperm, bool pdl, cudaStream_t st);
 
 

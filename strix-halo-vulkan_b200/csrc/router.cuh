@@ -23,6 +23,10 @@ struct RouterParams {
   int max_entries;
   int defer;           // 1: stop after the logits; the expert kernel that follows selects the experts itself
   int ecols;           // columns per work-list entry (8, or 4 for passes of some tens of rows; 0 means 8)
+  // expert parallelism: the work list keeps the experts [e_lo, e_hi) only (e_hi == 0: all) and makes shared-expert
+  // entries for the rows [sh_lo, sh_hi) only (sh_hi == 0: all rows)
+  int e_lo, e_hi, sh_lo, sh_hi;
+  int64_t* distinct;   // optional: += the number of experts this pass's work list touches (for the byte count of a step)
   Timeline tl;
 };
 

@@ -134,6 +134,37 @@ class Graph:
     def set_past(self, past):
         _lib.check(_lib.load().b200_graph_set_past(self._h, past))
 
+    def synth_context(self, cells, seed=0):
+        """Fills the current slot's caches and state with seeded values and declares `cells` cells prefilled."""
+        _lib.check(_lib.load().b200_graph_synth_context(self._h, cells, seed))
+
+    # -- expert parallelism ----------------------------------------------------------------
+    def ep_export(self, rank, world):
+        """This rank's exchange buffers as 64 opaque bytes for the other ranks' processes."""
+        h = _lib.EpHandle()
+        _lib.check(_lib.load().b200_graph_ep_export(self._h, rank, world, C.byref(h)))
+        return bytes(h.bytes)
+
+    def ep_attach(self, handles):
+        arr = (_lib.EpHandle * len(handles))()
+        for i, b in enumerate(handles):
+            C.memmove(arr[i].bytes, bytes(b), 64)
+        _lib.check(_lib.load().b200_graph_ep_attach(self._h, arr))
+
+    @staticmethod
+    def ep_connect_local(graphs):
+        """Ranks in one process, one graph per device, in rank order."""
+        L = _lib.load()
+        n = len(graphs)
+        for r, g in enumerate(graphs):
+            _lib.check(L.b200_graph_ep_prepare(g._h, r, n))
+        arr = (C.c_void_p * n)(*[g._h.value for g in graphs])
+        for g in graphs:
+            _lib.check(L.b200_graph_ep_attach_local(g._h, arr, n))
+
+    def ep_enable(self, on=True):
+        _lib.check(_lib.load().b200_graph_ep_enable(self._h, int(on)))
+
     # -- passes --------------------------------------------------------------------------
     def _call(self, fn, ids, rows_logits, rows_hidden, vocab=None):
         ids = _i32(ids)

@@ -30,7 +30,11 @@ class GraphOpts(C.Structure):
 
 class GraphStats(C.Structure):
     _fields_ = [("passes", C.c_int64), ("rows", C.c_int64), ("launches", C.c_int64), ("device_ms", C.c_double), ("host_ms", C.c_double),
-                ("last_rows", C.c_int32), ("last_launches", C.c_int32), ("last_device_ms", C.c_float)]
+                ("last_rows", C.c_int32), ("last_launches", C.c_int32), ("last_device_ms", C.c_float), ("expert_streams", C.c_int64)]
+
+
+class EpHandle(C.Structure):
+    _fields_ = [("bytes", C.c_ubyte * 64)]
 
 
 class Input(C.Structure):
@@ -89,6 +93,12 @@ SYMBOLS = {
     "b200_graph_inject_wait_timeout": (I32, [P]),
     "b200_graph_commit": (I32, [P]),
     "b200_graph_rewind": (I32, [P]),
+    "b200_graph_ep_export": (I32, [P, I32, I32, C.POINTER(EpHandle)]),
+    "b200_graph_ep_attach": (I32, [P, C.POINTER(EpHandle)]),
+    "b200_graph_ep_prepare": (I32, [P, I32, I32]),
+    "b200_graph_ep_attach_local": (I32, [P, PP, I32]),
+    "b200_graph_ep_enable": (I32, [P, I32]),
+    "b200_graph_synth_context": (I32, [P, I32, U64]),
     "b200_graph_generate_greedy": (I32, [P, P, P, I32, I32, P]),
     "b200_graph_last_device_ms": (F32, [P]),
     "b200_graph_last_launches": (I32, [P]),

@@ -31,6 +31,20 @@ def test_qgemm_matches_fp16_weight_product(pkg, orc, typ, rows, k, m, tile):
     assert np.abs(got - want).max() <= TOL * scale, (np.abs(got - want).max(), scale)
 
 
+@pytest.mark.parametrize("typ", [12, 13, 14, 8])
+def test_qgemm_multiplies_the_weights_the_oracle_names(pkg, orc, typ):
+    """The oracle's many-row mode states the fp16 weights bit for bit (hi + lo factor pairs): against a product
+    over exactly those weights only the summation order differs."""
+    rng = np.random.default_rng(31 + typ)
+    rows, k, m = 256, 2048, 96
+    q = orc.quantize(typ, (0.02 * rng.standard_normal((rows, k))).astype(np.float32))
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    got = pkg.qgemm(typ, q, rows, k, x, 64)
+    w = orc.dequantize_w16(typ, q, rows * k).reshape(rows, k).astype(np.float64)
+    want = (x.astype(np.float16).astype(np.float64) @ w.T).astype(np.float32)
+    assert np.abs(got - want).max() <= 2e-6 * np.abs(want).max() + 1e-7, np.abs(got - want).max()
+
+
 @pytest.mark.parametrize("rows,k,m", [(512, 2048, 300), (128, 256, 5), (96, 1024, 70)])
 def test_qgemm_q8_0_router_weights(pkg, orc, rows, k, m):
     # the router's weight type, 64-row tiles only (many-row passes compute the router logits this way)

@@ -117,3 +117,21 @@ def test_fp16_weight_mode_rounds_only_the_named_matrices(orc, tiny_path):
     assert not np.array_equal(tb["hidden"], ta["hidden"])
     scale = np.abs(base).max()
     assert np.abs(head - base).max() < 2e-3 * scale and np.abs(allw - base).max() < 1e-2 * scale
+
+
+def test_tensor_core_weights_are_the_rounded_value_or_a_neighbour(orc):
+    """The fp16 weights of the many-row kernels (hi + lo factor pairs) against the reference's single rounding of
+    the f32 value (shaders/llm_moe_gemm.comp:260-261): never further than one fp16 ulp, mostly identical."""
+    rng = np.random.default_rng(9)
+    for typ in (12, 13, 14, 8):
+        q = orc.quantize(typ, (0.02 * rng.standard_normal((64, 1024))).astype(np.float32))
+        exact = orc.dequantize(typ, q, 64 * 1024)
+        once = exact.astype(np.float16)
+        got = orc.dequantize_w16(typ, q, 64 * 1024)
+        assert np.array_equal(got, got.astype(np.float16).astype(np.float32))      # fp16 values
+        steps = np.abs(got.astype(np.float16).view(np.int16).astype(np.int32) - once.view(np.int16).astype(np.int32))
+        steps[got == once.astype(np.float32)] = 0                                     # +0 against -0
+        assert steps.max() <= 2, (typ, steps.max())
+        assert (steps > 1).mean() < 1e-4 and (steps == 0).mean() > 0.8, (typ, (steps == 0).mean())
+        if typ in (14, 8):
+            assert steps.max() == 0                                                   # one factor: fp16(d * sc * q) is the single rounding
