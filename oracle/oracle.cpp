@@ -139,10 +139,9 @@ void deltanet_token(const orc_model& m, int li, orc_seq::L& st, const float* xn,
   const auto& sm = m.small[li];
   const int d = c.dn_head_dim, Hk = c.dn_heads_k, Hv = c.dn_heads_v, K = c.dn_conv;
   const int qk = Hk * d, vw = Hv * d, cw = 2 * qk + vw, hist = K - 1;
-  (void)numerics;
   w.proj.resize(cw); w.z.resize(vw); w.ab.resize(2 * Hv);
-  matvec(L.qkv, 0, cw, xn, w.proj.data());
-  matvec(L.z, 0, vw, xn, w.z.data());
+  matvec(L.qkv, 0, cw, xn, w.proj.data(), w16(numerics, ORC_W16_DN_QKV));
+  matvec(L.z, 0, vw, xn, w.z.data(), w16(numerics, ORC_W16_DN_GATE));
   matvec(L.alpha, 0, Hv, xn, w.ab.data());
   matvec(L.beta, 0, Hv, xn, w.ab.data() + Hv);
   // decay and write strength (llm/deltanet.go:266-271)

@@ -52,8 +52,14 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   if (o.n_kv <= 0) { set_error("graph: n_kv must be positive"); return EINVAL_; }
   if (o.speculative && o.spec_rows <= 0) o.spec_rows = 3;
   if (o.spec_rows > DN_RING - 3) { set_error("graph: spec_rows is limited to 5 (the conv ring keeps 8 positions)"); return ECAPACITY; }
-  MR = std::min(o.max_tokens, 2048);   // rows per pass (the attention kernel keeps per-row split partials)
+  // Rows per pass. Many-row passes of one sequence run the tiled causal attention kernel, which keeps nothing per
+  // row; where the head layout has no such kernel, every row goes through the split-KV kernel, whose per-row
+  // partial results cap the pass at 2048 rows.
+  const int grp = c.n_head_kv > 0 ? c.n_head / c.n_head_kv : 0;
+  const bool tiled_attn = (grp == 8 && c.head_dim == 256) || (grp == 4 && c.head_dim == 128);
+  MR = std::min(o.max_tokens, tiled_attn ? 4096 : 2048);
   LR = std::min(MR, 512);              // rows whose logits a pass can return
+  attn_rows = tiled_attn ? std::min(MR, std::max(std::max(o.slots, 16), o.spec_rows)) : MR;   // rows the split-KV kernel may see
   // a CTA's four warps take 16 cells each per round; longer contexts get longer splits so the merge stays short
   split_cells = o.attn_split_cells > 0 ? (o.attn_split_cells + 15) / 16 * 16 : (o.n_kv <= 4096 ? 64 : o.n_kv <= 8192 ? 128 : o.n_kv <= 16384 ? 256 : 512);
   nsplit = (o.n_kv + split_cells - 1) / split_cells;
@@ -73,7 +79,7 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   max_entries = std::max(max_entries_for(MR), max_entries_for(std::min(MR, 128)));
   B200_TRY(dalloc(&hbuf[0], (size_t)MR * H)); B200_TRY(dalloc(&hbuf[1], (size_t)MR * H)); h = hbuf[0]; B200_TRY(dalloc(&proj, (size_t)MR * proj_ld));
   B200_TRY(dalloc(&xn16, (size_t)MR * H)); B200_TRY(dalloc(&q16, (size_t)MR * qw)); B200_TRY(dalloc(&ctx16, (size_t)MR * qw));
-  B200_TRY(dalloc(&attn_partial, (size_t)MR * c.n_head * nsplit * (hd + 2)));
+  B200_TRY(dalloc(&attn_partial, (size_t)attn_rows * c.n_head * nsplit * (hd + 2)));
   B200_TRY(dalloc(&r_logits, (size_t)MR * c.n_expert));
   B200_TRY(dalloc(&topk, (size_t)MR * used)); B200_TRY(dalloc(&topk_w, (size_t)MR * slots1)); B200_TRY(dalloc(&margin, (size_t)MR));
   B200_TRY(dalloc(&entries, (size_t)max_entries)); B200_TRY(dalloc(&n_entries, 1)); B200_TRY(dalloc(&cols, (size_t)MR * slots1));
@@ -356,9 +362,15 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       a.one_row_per_seq = M == n_seq && !f.spec; a.err = err_flag; a.tl = tl();
       B200_TRY(launch_attn_pack(a, pdl(), st));
       a.tl = tl();
-      B200_TRY(launch_attn_decode(a, pdl(), st));
-      a.tl = tl();
-      B200_TRY(launch_attn_merge(a, pdl(), st));
+      if (n_seq == 1 && !f.spec && attn_prefill_fits(a)) {
+        // many rows of one sequence: query tiles x key tiles, straight to the gated context rows
+        B200_TRY(launch_attn_prefill(a, pdl(), st));
+      } else {
+        if (M > attn_rows) { set_error("pass of " + std::to_string(M) + " rows: the split attention buffers hold " + std::to_string(attn_rows)); return ECAPACITY; }
+        B200_TRY(launch_attn_decode(a, pdl(), st));
+        a.tl = tl();
+        B200_TRY(launch_attn_merge(a, pdl(), st));
+      }
       QGemvParams q = base(L.o, qw, H, ctx16, qw);
       q.y = hc; q.ldy = H;
       if (fused) { q.ss_out = ss_part; ss_n = qgemv_groups(qw, H); }

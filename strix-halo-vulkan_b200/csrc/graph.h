@@ -26,6 +26,7 @@ struct Graph {
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   int MR = 0;           // rows per pass
   int LR = 0;           // rows whose logits one pass can return
+  int attn_rows = 0;    // rows a pass may send through the split-KV attention kernel (its partial results are per row)
   int n_dn = 0, n_attn = 0;
   std::vector<int> dn_index, attn_index;  // layer -> index among its kind (draft layer = last attention)
   // activations

@@ -949,6 +949,7 @@ __global__ void __launch_bounds__(512, 2) dn_head_kernel(DnStepParams p) {
 // -----------------------------------------------------------------------------------------
 constexpr int DN_PACK = 292;   // floats per (CTA id, token): q 128 | k 128 | v 32 | decay | beta | pad 2
 constexpr int DN_PRE_TOKENS = 16;
+constexpr int DN_CHUNK_FROM = 64;   // sequences of this many tokens and more run the chunked recurrence, shorter ones the token-by-token scan
 
 __global__ void __launch_bounds__(128) dn_pre_kernel(DnStepParams p) {
   const int D = 128, RB = 4;
@@ -1096,6 +1097,210 @@ __global__ void __launch_bounds__(128) dn_scan_kernel(DnStepParams p) {
   }
 }
 
+// -----------------------------------------------------------------------------------------
+// The recurrence in chunks of 64 tokens (the chunked form of the gated delta rule). Within a chunk the per-token
+// updates  s_j <- g_t s_j + beta_t (v_t[j] - g_t s_j . k_t) k_t  are solved for all tokens at once: with
+// L_t = sum_{r<=t} log g_r and ratio(t, r) = exp(L_t - L_r),
+//   A[t][r] = beta_t ratio(t, r) (k_t . k_r)  (r < t),      W[t][r] = ratio(t, r) (q_t . k_r)  (r <= t),
+//   R[t][j] = beta_t (v_t[j] - exp(L_t) (S0 k_t)[j]),       D[t][j] = R[t][j] - sum_{r<t} A[t][r] D[r][j],
+//   o_t[j]  = (exp(L_t) (S0 q_t)[j] + sum_{r<=t} W[t][r] D[r][j]) / sqrt(128),
+//   S_C     = exp(L_C) S0 + sum_r ratio(C, r) D[r] k_r^T,
+// which is the token-by-token recurrence re-associated (llm/deltanet.go:365-418 is the sequential form; the
+// reference has no chunked one, llm/gpu_deltanet.go:48-52). Everything stays f32 (the state and the recurrence
+// are f32 throughout in the reference's device path), so the matrix products run on the FMA pipe, register-tiled,
+// from shared memory; only the 64-step forward substitution for D is sequential, and it is 32 columns wide.
+// A CTA owns 32 state rows of one head, as dn_scan_kernel does, and reads the same packed inputs.
+// grid (Hv * 4, n_seq), block 256, dynamic shared memory DN_CHUNK_SMEM.
+// -----------------------------------------------------------------------------------------
+constexpr int DN_C = 64;                       // tokens per chunk
+constexpr int DN_KP = 132;                     // pitch of the K and Q rows (floats): 16-byte reads of rows tx, tx+16, .. fall on distinct banks
+constexpr int DN_AP = 68;                      // pitch of A and W rows
+constexpr int DN_SP = 33;                      // pitch of the transposed state block ST[i][j]
+constexpr size_t DN_CHUNK_SMEM = sizeof(float) * (2 * DN_C * DN_KP + 128 * DN_SP + 2 * DN_C * 32 + 2 * DN_C * DN_AP + 4 * DN_C);
+
+__global__ void __launch_bounds__(256, 1) dn_chunk_kernel(DnStepParams p) {
+  const int D = 128, RB = 4;
+  const int h = blockIdx.x / RB, rb = blockIdx.x % RB;
+  const SeqDesc sq = p.seqs[blockIdx.y];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  extern __shared__ __align__(16) float dc_smem[];
+  float* Ks = dc_smem;                          // [64][DN_KP]
+  float* Qs = Ks + DN_C * DN_KP;                // [64][DN_KP]
+  float* ST = Qs + DN_C * DN_KP;                // [128 i][DN_SP]: the CTA's 32 state rows, transposed
+  float* Vs = ST + 128 * DN_SP;                 // [64][32] values, then R
+  float* Dm = Vs + DN_C * 32;                   // [64][32] the solved deltas
+  float* Am = Dm + DN_C * 32;                   // [64][DN_AP]
+  float* Wm = Am + DN_C * DN_AP;                // [64][DN_AP]
+  float* Lg = Wm + DN_C * DN_AP;                // [64] cumulative log decay
+  float* Bt = Lg + DN_C;                        // [64] beta
+  float* Gm = Bt + DN_C;                        // [64] exp(L_t)
+  float* Cr = Gm + DN_C;                        // [64] exp(L_C - L_r)
+  float* Sg = p.state + (size_t)sq.slot * p.state_slot_stride + (size_t)h * D * D + (size_t)(rb * 32) * D;
+  // the state block does not depend on the producer kernel
+  for (int idx = tid; idx < 32 * D; idx += 256) { const int j = idx >> 7, i = idx & 127; ST[i * DN_SP + j] = Sg[idx]; }
+  const float oscale = 1.0f / sqrtf((float)D);
+  pdl_wait();
+  pdl_launch();
+  const float* pp = p.pre + ((size_t)blockIdx.x * p.pre_rows + sq.row0) * DN_PACK;
+  const int ty = tid >> 4, tx = tid & 15;
+  for (int c0 = 0; c0 < sq.n; c0 += DN_C) {
+    const int n = min(DN_C, sq.n - c0);
+    __syncthreads();                            // the previous chunk's readers are done with every buffer
+    // ---- inputs: q, k rows (zero past the end), values, decay and beta ----
+    for (int idx = tid; idx < DN_C * 64; idx += 256) {
+      const int t = idx >> 6, c = idx & 63;     // 64 float4 per token: 32 of q, 32 of k
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (t < n) v = __ldcg(reinterpret_cast<const float4*>(pp + (size_t)(c0 + t) * DN_PACK + 4 * c));
+      float* dst = (c < 32 ? Qs : Ks) + t * DN_KP + 4 * (c & 31);
+      *reinterpret_cast<float4*>(dst) = v;
+    }
+    for (int idx = tid; idx < DN_C * 32; idx += 256) {
+      const int t = idx >> 5, j = idx & 31;
+      Vs[idx] = t < n ? __ldcg(pp + (size_t)(c0 + t) * DN_PACK + 256 + j) : 0.f;
+    }
+    if (warp == 0) {                            // cumulative log decay of the chunk: two tokens per lane
+      const int t0 = 2 * lane, t1 = t0 + 1;
+      const float g0 = t0 < n ? __ldcg(pp + (size_t)(c0 + t0) * DN_PACK + 288) : 1.f, g1 = t1 < n ? __ldcg(pp + (size_t)(c0 + t1) * DN_PACK + 288) : 1.f;
+      Bt[t0] = t0 < n ? __ldcg(pp + (size_t)(c0 + t0) * DN_PACK + 289) : 0.f;
+      Bt[t1] = t1 < n ? __ldcg(pp + (size_t)(c0 + t1) * DN_PACK + 289) : 0.f;
+      const float l0 = fmaxf(logf(g0), -87.f), l1 = fmaxf(logf(g1), -87.f);
+      float run = l0 + l1;                      // inclusive scan over the lanes' pair sums
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) { const float up = __shfl_up_sync(0xffffffffu, run, o); if (lane >= o) run += up; }
+      Lg[t0] = run - l1; Lg[t1] = run;
+      const float total = __shfl_sync(0xffffffffu, run, 31);
+      Gm[t0] = expf(run - l1); Gm[t1] = expf(run);
+      Cr[t0] = expf(total - (run - l1)); Cr[t1] = expf(total - run);
+    }
+    __syncthreads();
+    // ---- A = beta ratio (K K^T) below the diagonal, W = ratio (Q K^T) on and below it: 4 x 4 per thread ----
+    {
+      float aa[4][4], ww[4][4];
+#pragma unroll
+      for (int a = 0; a < 4; a++)
+#pragma unroll
+        for (int b = 0; b < 4; b++) { aa[a][b] = 0.f; ww[a][b] = 0.f; }
+      for (int i = 0; i < D; i += 4) {
+        float4 kt[4], qt[4], kr[4];
+#pragma unroll
+        for (int a = 0; a < 4; a++) {
+          kt[a] = *reinterpret_cast<const float4*>(Ks + (ty + 16 * a) * DN_KP + i);
+          qt[a] = *reinterpret_cast<const float4*>(Qs + (ty + 16 * a) * DN_KP + i);
+          kr[a] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * a) * DN_KP + i);
+        }
+#pragma unroll
+        for (int a = 0; a < 4; a++)
+#pragma unroll
+          for (int b = 0; b < 4; b++) {
+            aa[a][b] += kt[a].x * kr[b].x + kt[a].y * kr[b].y + kt[a].z * kr[b].z + kt[a].w * kr[b].w;
+            ww[a][b] += qt[a].x * kr[b].x + qt[a].y * kr[b].y + qt[a].z * kr[b].z + qt[a].w * kr[b].w;
+          }
+      }
+#pragma unroll
+      for (int a = 0; a < 4; a++)
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+          const int t = ty + 16 * a, r = tx + 16 * b;
+          const float ratio = r <= t ? expf(Lg[t] - Lg[r]) : 0.f;
+          Am[t * DN_AP + r] = r < t ? Bt[t] * ratio * aa[a][b] : 0.f;
+          Wm[t * DN_AP + r] = ratio * ww[a][b];
+        }
+    }
+    // ---- KS = K S0^T, QS = Q S0^T: lane = state row j, warp w takes tokens w, w + 8, ... ----
+    float qs[8];
+    {
+      float ks[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++) { ks[u] = 0.f; qs[u] = 0.f; }
+      for (int i = 0; i < D; i += 4) {
+        const float s0 = ST[i * DN_SP + lane], s1 = ST[(i + 1) * DN_SP + lane], s2 = ST[(i + 2) * DN_SP + lane], s3 = ST[(i + 3) * DN_SP + lane];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          const float4 kk = *reinterpret_cast<const float4*>(Ks + (warp + 8 * u) * DN_KP + i);
+          const float4 qq = *reinterpret_cast<const float4*>(Qs + (warp + 8 * u) * DN_KP + i);
+          ks[u] += kk.x * s0 + kk.y * s1 + kk.z * s2 + kk.w * s3;
+          qs[u] += qq.x * s0 + qq.y * s1 + qq.z * s2 + qq.w * s3;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int t = warp + 8 * u;
+        Vs[t * 32 + lane] = Bt[t] * (Vs[t * 32 + lane] - Gm[t] * ks[u]);   // R
+        qs[u] *= Gm[t];
+      }
+    }
+    __syncthreads();
+    // ---- forward substitution, one warp: D[t] = R[t] - sum_{r<t} A[t][r] D[r]; lane = column j ----
+    if (warp == 0) {
+      for (int t = 0; t < DN_C; t++) {
+        float a0 = Vs[t * 32 + lane], a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        const float* ar = Am + t * DN_AP;
+        int r = 0;
+        for (; r + 4 <= t; r += 4) {
+          const float4 a = *reinterpret_cast<const float4*>(ar + r);
+          a0 -= a.x * Dm[r * 32 + lane]; a1 -= a.y * Dm[(r + 1) * 32 + lane];
+          a2 -= a.z * Dm[(r + 2) * 32 + lane]; a3 -= a.w * Dm[(r + 3) * 32 + lane];
+        }
+        for (; r < t; r++) a0 -= ar[r] * Dm[r * 32 + lane];
+        Dm[t * 32 + lane] = (a0 + a1) + (a2 + a3);   // read back by this lane only
+      }
+    }
+    __syncthreads();
+    // ---- outputs: o_t[j] = (Gamma_t QS + W D) / sqrt(D) ----
+    {
+      float acc[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++) acc[u] = qs[u];
+      for (int r = 0; r < DN_C; r += 4) {
+        const float d0 = Dm[r * 32 + lane], d1 = Dm[(r + 1) * 32 + lane], d2 = Dm[(r + 2) * 32 + lane], d3 = Dm[(r + 3) * 32 + lane];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          const float4 w = *reinterpret_cast<const float4*>(Wm + (warp + 8 * u) * DN_AP + r);
+          acc[u] += w.x * d0 + w.y * d1 + w.z * d2 + w.w * d3;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int t = warp + 8 * u;
+        if (t < n) p.o_raw[(size_t)(sq.row0 + c0 + t) * (p.Hv * D) + h * D + rb * 32 + lane] = acc[u] * oscale;
+      }
+    }
+    // ---- state: ST[i][j] = Gamma_C ST[i][j] + sum_r Cr[r] K[r][i] D[r][j]; warp w takes i in [16w, 16w + 16) ----
+    {
+      float acc[16];
+      const float gc = Gm[DN_C - 1];
+#pragma unroll
+      for (int u = 0; u < 16; u++) acc[u] = gc * ST[(16 * warp + u) * DN_SP + lane];
+      for (int r = 0; r < DN_C; r++) {
+        const float dr = Cr[r] * Dm[r * 32 + lane];
+        const float* kr = Ks + r * DN_KP + 16 * warp;
+#pragma unroll
+        for (int v4 = 0; v4 < 4; v4++) {
+          const float4 kk = *reinterpret_cast<const float4*>(kr + 4 * v4);
+          acc[4 * v4] += kk.x * dr; acc[4 * v4 + 1] += kk.y * dr; acc[4 * v4 + 2] += kk.z * dr; acc[4 * v4 + 3] += kk.w * dr;
+        }
+      }
+      __syncthreads();                          // every warp has read the old state block (KS / QS above)
+#pragma unroll
+      for (int u = 0; u < 16; u++) ST[(16 * warp + u) * DN_SP + lane] = acc[u];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < 32 * D; idx += 256) { const int j = idx >> 7, i = idx & 127; Sg[idx] = ST[i * DN_SP + j]; }
+  // the ring keeps the last positions' conv inputs (written here, after every read of the old ring by the pre-pass)
+  if (tid < 128) {
+    const int hk = h % p.Hk, qk = p.Hk * D;
+    const int ch_q = hk * D + tid, ch_k = qk + hk * D + tid, ch_v = 2 * qk + h * D + rb * 32 + (tid & 31);
+    float* ring = p.ring + (size_t)sq.slot * p.ring_slot_stride + (size_t)blockIdx.x * (DN_RING * DN_RING_W);
+    for (int i = max(0, sq.n - DN_RING); i < sq.n; i++) {
+      const float* pr = p.proj + (size_t)(sq.row0 + i) * p.ldp;
+      float* rw = ring + (size_t)((sq.pos0 + i) & (DN_RING - 1)) * DN_RING_W;
+      rw[tid] = pr[ch_q]; rw[128 + tid] = pr[ch_k];
+      if (tid < 32) rw[256 + tid] = pr[ch_v];
+    }
+  }
+}
+
 // gated RMSNorm of one token's head: sums of squares grouped as the step kernel groups them (eight rows
 // per warp in order, four warps per row block, four row blocks)
 __global__ void __launch_bounds__(128) dn_post_kernel(DnStepParams p, int M) {
@@ -1127,7 +1332,13 @@ int launch_dn_scan(const DnStepParams& p, int M, int max_n, bool pdl, cudaStream
   if (p.D != 128 || p.conv != 4) { set_error("dn_scan: head dim must be 128 and conv kernel 4"); return EINVAL_; }
   if (p.mid != nullptr || p.pre == nullptr || p.o_raw == nullptr) { set_error("dn_scan: not available for speculative passes"); return EINVAL_; }
   B200_TRY(launch_k(dn_pre_kernel, dim3(p.Hv * 4, p.n_seq, (max_n + DN_PRE_TOKENS - 1) / DN_PRE_TOKENS), dim3(128), 0, pdl, st, p));
-  B200_TRY(launch_k(dn_scan_kernel, dim3(p.Hv * 4, p.n_seq), dim3(128), 0, true, st, p));
+  if (max_n >= DN_CHUNK_FROM) {
+    // long sequences: the recurrence in chunks of 64 tokens
+    B200_ONCE_PER_DEVICE(cudaFuncSetAttribute(dn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DN_CHUNK_SMEM));
+    B200_TRY(launch_k(dn_chunk_kernel, dim3(p.Hv * 4, p.n_seq), dim3(256), DN_CHUNK_SMEM, true, st, p));
+  } else {
+    B200_TRY(launch_k(dn_scan_kernel, dim3(p.Hv * 4, p.n_seq), dim3(128), 0, true, st, p));
+  }
   return launch_k(dn_post_kernel, dim3(M, p.Hv), dim3(128), 0, true, st, p, M);
 }
 
@@ -1519,6 +1730,162 @@ __global__ void __launch_bounds__(256, 1) attn_ring_kernel(AttnParams p) {
   tl_mark(p.tl, 4);
 }
 
+// -----------------------------------------------------------------------------------------
+// Causal attention of a many-row pass of ONE sequence (prefill): query tiles x key/value tiles with an online
+// softmax, no per-row split partials and no merge launch (the reference's flash form:
+// shaders/llm_attn_wmma.comp:102-117 QT/BM query tiles, :161-190 HROWS). A CTA of eight warps owns 8 * 16 / G
+// consecutive query rows of one KV head; a warp takes 16 / G of them with the G query heads of the group, which
+// fills the sixteen rows of the mma's M axis (G = 8: rows 2w and 2w + 1 with heads 0..7). Key and value tiles of 32 cells
+// reach shared memory by bulk copies (one per cache row, both tensors on one mbarrier, two stages) and are shared
+// by the eight warps; the query tile is staged once. Fragment layout, fp16 probabilities and the order of the
+// arithmetic are those of the split-KV kernels above; a cell past a row's own position scores -inf.
+// The result goes straight to the gated fp16 context rows. grid (ceil(M / (128 / G)), Hkv), block 256.
+// -----------------------------------------------------------------------------------------
+template <int HD, int G>
+__global__ void __launch_bounds__(256, 1) attn_prefill_kernel(AttnParams p) {
+  static_assert(G == 8 || G == 4, "the sixteen M rows are 16 / G query rows of G heads");
+  constexpr int KS = HD / 16, NB = HD / 64, TC = 32;
+  constexpr int RW = 16 / G, QT = 8 * RW;                      // query rows per warp and per CTA
+  constexpr int KP = HD * 2 + 64, VP = HD * 2 + 16;           // row pitches in bytes (bank-conflict-free 16-byte reads)
+  extern __shared__ __align__(128) uint8_t pf_smem[];          // Q [QT][G][KP] | K [2][TC][KP] | V [2][TC][VP]
+  __shared__ __align__(8) uint64_t full[2];
+  uint8_t* qs = pf_smem;
+  uint8_t* ks = qs + (size_t)QT * G * KP;
+  uint8_t* vs = ks + (size_t)2 * TC * KP;
+  const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;      // long rows first
+  const int kvh = blockIdx.y, n0 = tile * QT;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  if (tid == 0) { mbar_init(&full[0], 1); mbar_init(&full[1], 1); mbar_fence_init(); }
+  __syncthreads();
+  pdl_wait();
+  pdl_launch();
+  const int slot = p.row_slot[n0], pos0 = p.row_pos[n0];       // rows of one sequence at consecutive positions
+  const int rows = min(QT, p.M - n0);
+  const int ncell = pos0 + rows;                                // cells the tile's last row sees
+  const int ntile = (ncell + TC - 1) / TC;
+  const size_t cell_stride = (size_t)p.Hkv * HD;
+  const __half* kbase = p.kcache + (size_t)slot * p.slot_stride + (size_t)kvh * HD;
+  const __half* vbase = p.vcache + (size_t)slot * p.slot_stride + (size_t)kvh * HD;
+  auto issue = [&](int k) {   // warp 0: key and value rows of tile k into stage k & 1
+    if (k >= ntile) return;
+    const int s = k & 1;
+    if (lane == 0) mbar_expect_tx(&full[s], 2u * TC * HD * 2);
+    __syncwarp();
+    const int row = min(k * TC + lane, ncell - 1);             // rows past the end repeat the last one and are masked
+    bulk_copy_g2s(ks + ((size_t)s * TC + lane) * KP, kbase + (size_t)row * cell_stride, HD * 2, &full[s]);
+    bulk_copy_g2s(vs + ((size_t)s * TC + lane) * VP, vbase + (size_t)row * cell_stride, HD * 2, &full[s]);
+  };
+  if (warp == 0) { issue(0); issue(1); }
+  // the query tile: row r, head h at qs + (r * G + h) * KP
+  for (int i = tid; i < QT * G * (HD / 8); i += 256) {
+    const int d8 = i % (HD / 8), rh = i / (HD / 8), r = rh / G, h = rh - r * G;
+    const int n = n0 + min(r, rows - 1);
+    *reinterpret_cast<uint4*>(qs + (size_t)rh * KP + d8 * 16) = *reinterpret_cast<const uint4*>(p.q16 + ((size_t)n * p.Hq + kvh * G + h) * HD + d8 * 8);
+  }
+  __syncthreads();
+  // M row g is query row rA with head g % G, M row g + 8 is query row rB with the same head
+  const int rA = RW * warp + g / G, rB = rA + 8 / G, hh = g % G;
+  const int posA = pos0 + min(rA, rows - 1), posB = pos0 + min(rB, rows - 1);
+  const int pos_warp = pos0 + min(RW * warp + RW - 1, rows - 1);   // the warp's last row
+  const uint8_t* qa_row = qs + (size_t)(rA * G + hh) * KP + t * 16;
+  const uint8_t* qb_row = qs + (size_t)(rB * G + hh) * KP + t * 16;
+  const float scale = 1.0f / sqrtf((float)HD);
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; i++) { o[i][0] = 0.f; o[i][1] = 0.f; o[i][2] = 0.f; o[i][3] = 0.f; }
+  float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
+  bool lost = false;
+  for (int k = 0; k < ntile; k++) {
+    const int s = k & 1;
+    if (!mbar_wait(&full[s], (uint32_t)((k >> 1) & 1))) { lost = true; break; }
+#pragma unroll 1
+    for (int blk = 0; blk < TC / 16; blk++) {
+      const int cb = k * TC + blk * 16;
+      if (cb > pos_warp) break;                                // every cell of the block lies past all of the warp's rows
+      // ---- scores of 16 cells for both rows ----
+      const uint8_t* kt = ks + ((size_t)s * TC + blk * 16 + g) * KP + t * 16;
+      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < KS / 2; j++) {
+        const uint4 qa = lds128(qa_row + j * 64), qb = lds128(qb_row + j * 64);
+        const uint4 ka = lds128(kt + j * 64), kb = lds128(kt + 8 * KP + j * 64);
+        const uint32_t a0[4] = {qa.x, qb.x, qa.y, qb.y}, a1[4] = {qa.z, qb.z, qa.w, qb.w};
+        mma16816(s0, a0, ka.x, ka.y);
+        mma16816(s0, a1, ka.z, ka.w);
+        mma16816(s1, a0, kb.x, kb.y);
+        mma16816(s1, a1, kb.z, kb.w);
+      }
+      // rows g (A) and g + 8 (B); cells cb + 2t, +1 (tile 0) and cb + 8 + 2t, +1 (tile 1)
+      const int cell[4] = {cb + 2 * t, cb + 2 * t + 1, cb + 8 + 2 * t, cb + 9 + 2 * t};
+      float sa[4] = {s0[0] * scale, s0[1] * scale, s1[0] * scale, s1[1] * scale};
+      float sb[4] = {s0[2] * scale, s0[3] * scale, s1[2] * scale, s1[3] * scale};
+#pragma unroll
+      for (int u = 0; u < 4; u++) { if (cell[u] > posA) sa[u] = -INFINITY; if (cell[u] > posB) sb[u] = -INFINITY; }
+      float mxA = fmaxf(fmaxf(sa[0], sa[1]), fmaxf(sa[2], sa[3])), mxB = fmaxf(fmaxf(sb[0], sb[1]), fmaxf(sb[2], sb[3]));
+      mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1)); mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+      mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1)); mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+      // cell 0 lies at or before every row's position, so the running maxima are finite from the first block on
+      const float mnA = fmaxf(mA, mxA), mnB = fmaxf(mB, mxB);
+      const float corrA = expf(mA - mnA), corrB = expf(mB - mnB);
+      float pa_[4], pb_[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) { pa_[u] = expf(sa[u] - mnA); pb_[u] = expf(sb[u] - mnB); }
+      lA = lA * corrA + ((pa_[0] + pa_[1]) + (pa_[2] + pa_[3]));
+      lB = lB * corrB + ((pb_[0] + pb_[1]) + (pb_[2] + pb_[3]));
+      mA = mnA; mB = mnB;
+      const uint32_t pa[4] = {pack_half2(pa_[0], pa_[1]), pack_half2(pb_[0], pb_[1]), pack_half2(pa_[2], pa_[3]), pack_half2(pb_[2], pb_[3])};
+      // ---- O = O * corr + P V ----
+      const uint8_t* vt = vs + ((size_t)s * TC + blk * 16 + 2 * t) * VP + g * 16;
+#pragma unroll
+      for (int b = 0; b < NB; b++) {
+        const uint4 wa = lds128(vt + b * 128), wb = lds128(vt + VP + b * 128), wc = lds128(vt + 8 * VP + b * 128), wd = lds128(vt + 9 * VP + b * 128);
+        const uint32_t ra[4] = {wa.x, wa.y, wa.z, wa.w}, rb[4] = {wb.x, wb.y, wb.z, wb.w}, rc[4] = {wc.x, wc.y, wc.z, wc.w}, rd[4] = {wd.x, wd.y, wd.z, wd.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          float* oe = o[b * 8 + 2 * j];
+          float* oo = o[b * 8 + 2 * j + 1];
+          float acc_e[4] = {oe[0] * corrA, oe[1] * corrA, oe[2] * corrB, oe[3] * corrB};
+          float acc_o[4] = {oo[0] * corrA, oo[1] * corrA, oo[2] * corrB, oo[3] * corrB};
+          mma16816(acc_e, pa, __byte_perm(ra[j], rb[j], 0x5410), __byte_perm(rc[j], rd[j], 0x5410));
+          mma16816(acc_o, pa, __byte_perm(ra[j], rb[j], 0x7632), __byte_perm(rc[j], rd[j], 0x7632));
+          oe[0] = acc_e[0]; oe[1] = acc_e[1]; oe[2] = acc_e[2]; oe[3] = acc_e[3];
+          oo[0] = acc_o[0]; oo[1] = acc_o[1]; oo[2] = acc_o[2]; oo[3] = acc_o[3];
+        }
+      }
+    }
+    __syncthreads();                       // every warp is done with stage s
+    if (warp == 0) { fence_proxy_async(); issue(k + 2); }
+  }
+  if (lost && p.err != nullptr && lane == 0) atomicExch(p.err, 1);  // a copy never landed: report; the result is void
+  lA += __shfl_xor_sync(0xffffffffu, lA, 1); lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+  lB += __shfl_xor_sync(0xffffffffu, lB, 1); lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+  // out = O / l * sigmoid(gate) -> fp16 context rows (reference: shaders/llm_attn_combine.comp:100-102)
+#pragma unroll
+  for (int half = 0; half < 2; half++) {
+    const int r = half ? rB : rA;
+    if (r >= rows) continue;
+    const int n = n0 + r, head = kvh * G + hh;
+    const float inv = 1.0f / (half ? lB : lA);
+    const float* gate = p.proj + (size_t)n * p.ldp + (size_t)head * 2 * HD + HD;
+    __half* dst = p.ctx16 + (size_t)n * p.Hq * HD + (size_t)head * HD;
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+#pragma unroll
+      for (int par = 0; par < 2; par++) {            // o[..][0] and o[..][1] are dims 8 * (2t + par + 8b) + i
+        const int d0 = 8 * (2 * t + par + 8 * b);
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          const float v0 = o[b * 8 + 2 * i][2 * half + par] * inv * sigmoid_acc(gate[d0 + 2 * i]);
+          const float v1 = o[b * 8 + 2 * i + 1][2 * half + par] * inv * sigmoid_acc(gate[d0 + 2 * i + 1]);
+          w[i] = pack_half2(v0, v1);
+        }
+        *reinterpret_cast<uint4*>(dst + d0) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  }
+}
+
 // Merge of the splits: O = sum_s O_s * exp(m_s - m*), divide by the merged row sum, times
 // sigmoid(gate), to fp16 (reference: shaders/llm_attn_combine.comp:43-102). grid (Hq, M), block hd.
 __global__ void attn_merge_kernel(AttnParams p) {
@@ -1585,6 +1952,21 @@ int launch_attn_decode(const AttnParams& p, bool pdl, cudaStream_t st) {
   else if (p.hd == 256 && G == 4) s = launch_k(attn_mma_kernel<256, 4>, grid, block, 0, pdl, st, p);
   else { set_error("attn_decode: unsupported head_dim / group size (128 or 256 dims, 4 or 8 query heads per KV head)"); return EINVAL_; }
   return s;
+}
+// many rows of one sequence: the tiled causal kernel (rows [0, M) sit at consecutive positions of one slot)
+bool attn_prefill_fits(const AttnParams& p) {
+  const int G = p.Hkv > 0 ? p.Hq / p.Hkv : 0;
+  return ((G == 8 && p.hd == 256) || (G == 4 && p.hd == 128)) && p.M >= 16;
+}
+int launch_attn_prefill(const AttnParams& p, bool pdl, cudaStream_t st) {
+  if (!attn_prefill_fits(p)) { set_error("attn_prefill: 8 query heads per KV head of 256 dims, or 4 of 128"); return EINVAL_; }
+  const int G = p.Hq / p.Hkv, QT = 128 / G;
+  const dim3 grid((p.M + QT - 1) / QT, p.Hkv);
+  auto smem = [](int hd) { return (size_t)128 * (hd * 2 + 64) + (size_t)2 * 32 * (hd * 2 + 64) + (size_t)2 * 32 * (hd * 2 + 16); };
+  B200_ONCE_PER_DEVICE(cudaFuncSetAttribute(attn_prefill_kernel<256, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem(256)));
+  B200_ONCE_PER_DEVICE(cudaFuncSetAttribute(attn_prefill_kernel<128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem(128)));
+  return p.hd == 256 ? launch_k(attn_prefill_kernel<256, 8>, grid, dim3(256), smem(256), pdl, st, p)
+                     : launch_k(attn_prefill_kernel<128, 4>, grid, dim3(256), smem(128), pdl, st, p);
 }
 int launch_attn_merge(const AttnParams& p, bool pdl, cudaStream_t st) {
   return launch_k(attn_merge_kernel, dim3(p.Hq, p.M), dim3(p.hd), (size_t)2 * p.nsplit * sizeof(float), pdl, st, p);

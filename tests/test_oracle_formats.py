@@ -113,6 +113,10 @@ def test_fp16_weight_mode_rounds_only_the_named_matrices(orc, tiny_path):
     assert np.array_equal(base, same)
     head, th = om.seq().extend(ids, numerics=orc.DEVICE_LIKE | orc.W16_HEAD, trace=("hidden",))
     assert np.array_equal(tb["hidden"], th["hidden"]) and not np.array_equal(base, head)
+    for bit in range(8, 19):     # every named matrix is wired: its bit alone changes the result
+        one, _ = om.seq().extend(ids, numerics=orc.DEVICE_LIKE | (1 << bit))
+        assert not np.array_equal(one, base), f"bit {bit} has no effect"
+        assert np.abs(one - base).max() < 3e-3 * np.abs(base).max()
     allw, ta = om.seq().extend(ids, numerics=orc.DEVICE_LIKE | orc.W16_ALL, trace=("hidden",))
     assert not np.array_equal(tb["hidden"], ta["hidden"])
     scale = np.abs(base).max()
