@@ -47,6 +47,8 @@ def algorithmic_bytes_per_token(pkg, cfg, ctx):
     H, nE, used, ff = cfg["n_embd"], cfg["n_expert"], cfg["n_expert_used"], cfg["ffn_expert"]
     w = 0
     for name, typ, dims, _ in config.manifest(cfg):
+        if name.startswith(f"blk.{cfg['n_layer']}."):
+            continue                                          # the draft layer is not part of a plain decode step
         nbytes = gguf.tensor_bytes(typ, dims)
         if name == "token_embd.weight":
             nbytes = gguf.row_bytes(typ, dims[0])            # one row is gathered
@@ -121,6 +123,8 @@ def batched_bytes(pkg, cfg, slots, ctx, streams_per_step):
     nE = cfg["n_expert"]
     dense = expert_one = 0
     for name, typ, dims, _ in config.manifest(cfg):
+        if name.startswith(f"blk.{cfg['n_layer']}."):
+            continue                                          # the draft layer is not part of a plain decode step
         nb = gguf.tensor_bytes(typ, dims)
         if name == "token_embd.weight":
             nb = gguf.row_bytes(typ, dims[0]) * slots
@@ -197,7 +201,7 @@ def cpu_baseline(pkg, cfg, device, tokens=8):
     config = pkg.config
     times, parity = {}, None
     for nl in (4, 12):
-        sub = config.variant(cfg, n_layer=nl, name=f"{cfg['name']}-{nl}-layer")
+        sub = config.variant(cfg, n_layer=nl, has_draft=0, name=f"{cfg['name']}-{nl}-layer")
         gm = pkg.Model.synthetic(sub, seed=0, device=device)
         tensors = {name: (typ, dims, gm.read_tensor(name)) for name, typ, dims, _ in config.manifest(sub)}
         om = orc.Model(config.graph_fields(sub), tensors)
@@ -256,8 +260,87 @@ def verify_pass_times(pkg, model, cfg, prompt, torch):
         torch.cuda.synchronize()
         out[str(rows)] = round((time.perf_counter() - t0) / 12 * 1e3, 3)
         g.speculate(False)
+    g.destroy()
     return {"verify_pass_ms_by_rows": out, "context": len(prompt),
             "note": "host-timed through extend_rows (every row's logits copied to the host); rows -> time ratio only"}
+
+
+def speculative_decode(pkg, model, cfg, torch, batch, prompt_len, n_out, depths=(1, 2, 4)):
+    """BASELINE config 5: MTP speculative decoding with the 1-layer draft head (gated GQA attention + 512-expert MoE,
+    random Q4_K-mix weights), every round verified in one trunk pass. `batch` sequences share one slotted graph and
+    draft cache, their rounds interleaved. With independent random draft and trunk weights nothing is accepted, so
+    what is reported is the cost of a round against a plain greedy step, and that the emitted ids ARE the plain
+    greedy ids."""
+    rng = np.random.default_rng(11)
+    prompts = [rng.integers(0, cfg["vocab"], prompt_len).astype(np.int32) for _ in range(batch)]
+    # plain greedy ids of every sequence (the reference: llm/spec_slots_test.go:199 compares with exactly this)
+    gp = pkg.Graph(model, n_kv=prompt_len + n_out + 8, max_tokens=2048, slots=batch, use_cuda_graph=True)
+    firsts = []
+    for s in range(batch):
+        gp.use_slot(s)
+        lg, _ = gp.forward(prompts[s])
+        firsts.append(int(np.argmax(lg)))
+    torch.cuda.synchronize(); t0 = time.perf_counter()
+    plain = gp.generate_greedy(list(range(batch)), firsts, n_out - 1)
+    torch.cuda.synchronize()
+    plain_ms = (time.perf_counter() - t0) / (n_out - 1) * 1e3        # one batched greedy step
+    plain_ids = [[firsts[s]] + plain[:, s].tolist() for s in range(batch)]
+    gp.destroy()
+    out = {"batch": batch, "prompt_tokens": prompt_len, "output_tokens": n_out, "plain_batched_step_ms": round(plain_ms, 3), "depths": {}}
+    for depth in depths:
+        g = pkg.Graph(model, n_kv=prompt_len + n_out + 16, max_tokens=2048, slots=batch, speculative=True, spec_rows=depth + 1, use_cuda_graph=False)
+        sps = [pkg.spec.Speculator(g, depth=depth, draft_vocab=65536, slot=s) for s in range(batch)]
+        got = [[sp.prime(p)] for sp, p in zip(sps, prompts)]
+        torch.cuda.synchronize(); t0 = time.perf_counter()
+        rounds = 0
+        while any(len(o) < n_out for o in got):
+            for s in range(batch):
+                if len(got[s]) < n_out:
+                    got[s] += sps[s].round(room=n_out - len(got[s]) + 1)
+                    rounds += 1
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        same = all(got[s][:n_out] == plain_ids[s][:n_out] for s in range(batch))
+        acc = sum(sp.stats["accepted"] for sp in sps)
+        out["depths"][str(depth)] = {"round_ms": round(dt / rounds * 1e3, 3), "tokens_per_round": round(sum(len(o) for o in got) / rounds, 3),
+                                     "accepted_drafts": acc, "ids_equal_plain_greedy": bool(same)}
+        g.destroy()
+    out["note"] = "a round = draft steps (draft head over the first 65536 ids) + one verify pass of depth + 1 rows through the host loop " \
+                  "(llm/spec.go:703-852); rounds of the batch's sequences are interleaved one slot at a time, as the reference's scheduler speculates only " \
+                  "for a conversation that decodes alone (backend/llm_sched.go:940-954)"
+    return out
+
+
+def prefill_config4(pkg, model, cfg, torch, n=32768, chunk=4096):
+    """BASELINE config 4: one n-token uniform-random prompt in passes of `chunk` rows: K-quant tcgen05 GEMMs for the
+    projections and the experts, the chunked (64-token) gated delta rule, tiled causal attention writing the fp16 cache."""
+    g = pkg.Graph(model, n_kv=n + 16, max_tokens=chunk, slots=1, use_cuda_graph=False)
+    ids = np.random.default_rng(13).integers(0, cfg["vocab"], n).astype(np.int32)
+    g.forward(ids[:chunk])                      # first-use set-up, untimed
+    g.stats_reset()
+    torch.cuda.synchronize(); t0 = time.perf_counter()
+    g.forward(ids)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    st = g.stats()
+    g.destroy()
+    # algorithmic flops: 2 x active weights per token, plus attention 4 * ctx * head_dim * heads per layer, plus the delta rule
+    gguf, config = pkg.gguf, pkg.config
+    active = 0
+    for name, typ, dims, _ in config.manifest(cfg):
+        if name == "token_embd.weight" or name.startswith(f"blk.{cfg['n_layer']}."):
+            continue
+        k = int(np.prod(dims))
+        active += k // cfg["n_expert"] * cfg["n_expert_used"] if "_exps." in name else k
+    active -= cfg["vocab"] * cfg["n_embd"] * (1 - 1.0 / n)          # the head runs for the last row only
+    n_at = sum(1 for l in range(cfg["n_layer"]) if config.is_attention_layer(cfg, l))
+    n_dn = cfg["n_layer"] - n_at
+    attn = 4.0 * (n / 2) * cfg["head_dim"] * cfg["n_head"] * n_at
+    dn = 6.0 * cfg["dn_head_dim"] ** 2 * cfg["dn_heads_v"] * n_dn
+    flops_tok = 2.0 * active + attn + dn
+    return {"prompt_tokens": n, "chunk": chunk, "value": n / dt, "unit": "tok/s", "seconds": round(dt, 3), "passes": st["passes"],
+            "device_ms": round(st["device_ms"], 1), "gflop_per_token": round(flops_tok / 1e9, 2),
+            "achieved_tflops": round(flops_tok * n / dt / 1e12, 1), "launches_per_pass": st["last_launches"]}
 
 
 def main():
@@ -286,6 +369,8 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     pkg = importlib.import_module("strix-halo-vulkan_b200")
     cfg = pkg.config.CONFIGS[args.config]
+    if args.config == "a3b" and not args.layers:
+        cfg = pkg.config.variant(cfg, has_draft=1)       # blk.48: the MTP draft layer (config 5); the trunk is the same 48 layers
     if args.layers:
         cfg = pkg.config.variant(cfg, n_layer=args.layers, name=f"{cfg['name']}-{args.layers}-layer-prefix")
     prompt_len = args.prompt or (PROMPT if args.config == "a3b" else 128)
@@ -410,12 +495,24 @@ def main():
             batch = batched_decode(pkg, model, cfg, args.slots, min(steps, 32), rank, world, dist, barrier)
         except Exception as e:  # an extra measurement must not lose the headline line
             batch = {"error": str(e)[:300]}
-    spec = None
-    if rank == 0 and args.slots > 0 and args.config == "a3b":
+    spec = config4 = None
+    if rank == 0 and world == 1 and args.slots > 0 and args.config == "a3b":
         try:
             spec = verify_pass_times(pkg, model, cfg, prompt, torch)
+            spec["batch1"] = speculative_decode(pkg, model, cfg, torch, 1, 4096, 48)
+            spec["batch16"] = speculative_decode(pkg, model, cfg, torch, 16, 512, 16, depths=(2,))
         except Exception as e:  # an extra measurement must not lose the headline line
-            spec = {"error": str(e)[:200]}
+            spec = dict(spec or {}, error=str(e)[:300])
+    if args.slots > 0 and args.config == "a3b":
+        # config 4 on every rank: the prompt is one sequence and its attention / DeltaNet layers do not shard, so N GPUs
+        # prefill N prompts (replicas); the slowest rank's time counts
+        try:
+            config4 = prefill_config4(pkg, model, cfg, torch)
+            secs = max_over_ranks(config4["seconds"], world)
+            config4.update(seconds=round(secs, 3), value=world * config4["prompt_tokens"] / secs, n_gpus=world,
+                           parallelism="replicas: one prompt per GPU" if world > 1 else "single GPU")
+        except Exception as e:
+            config4 = {"error": str(e)[:300]}
     if rank == 0:
         ms_per_step = dev_ms / steps
         value = whole_job_rate(steps, world, dev_ms)
@@ -443,6 +540,8 @@ def main():
         }
         if spec is not None:
             line["spec"] = spec
+        if config4 is not None:
+            line["prefill_32k"] = config4
         if batch is not None:
             line["batch64"] = batch
         if not args.no_cpu_baseline and world == 1:

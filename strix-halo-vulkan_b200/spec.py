@@ -53,6 +53,7 @@ class Speculator:
             res_rows.append(res)
         res = np.concatenate(res_rows)
         g.draft_rewind(0)
+        mt = min(mt, g.draft_max_rows())
         for o in range(0, len(ids) - 1, mt):
             n = min(mt, len(ids) - 1 - o)
             g.draft_rows(res[o:o + n], ids[o + 1:o + 1 + n], 16)   # cache only; logits are not needed

@@ -106,6 +106,8 @@ def prefill_both(g, orc, seq, ids, chunk, what):
         g.extend(part)
         tr = g.trace(len(part))
         _, ot = seq.extend(part, numerics=orc.DEVICE_LIKE | g.fp16_weight_mask(len(part), 1), trace=("topk", "margin"), want_last=False)
+        if flipped:
+            continue          # the sequence states differ from here on: later decisions are no longer comparable
         _, flips = routing_flips(tr["topk"], ot["topk"], ot["margin"], f"{what}, rows {o}..{o + len(part)}")
         flipped = flipped or bool(flips)
         noisy += noise_flips(flips)
