@@ -155,6 +155,7 @@ def test_slots_with_long_contexts_batched_against_the_oracle(pkg, orc, a3b4):
                     # routed sets are the oracle's except at a documented near-tie
                     assert od["margin"][0, l] < NOISE_TIE, f"{rows}-row pass, slot {s}, layer {l}: routing differs at a clear margin {od['margin'][0, l]:.3e}"
                     near_tie.add(s); noisy += od["margin"][0, l] >= NEAR_TIE
+                    break     # later layers see a different residual row: no longer comparable
             if s in near_tie:
                 continue
             assert_close(got[s], want, f"{rows}-row pass, slot {s} ({lens[s]} cells)")
