@@ -307,7 +307,7 @@ void attn_token(const orc_model& m, int li, orc_seq::L& st, const float* xn, int
 // Routed + shared MoE block for one token (llm/moe.go:219-409). x is the f32 norm
 // output, xr the same vector as the matmuls see it (fp16-rounded when device-like).
 void moe_token(const orc_model& m, int li, const float* x, const float* xr, int numerics, float* out,
-               int32_t* topk_out, float* topkw_out, float* margin_out, Work& w) {
+               int32_t* topk_out, float* topkw_out, float* margin_out, Work& w, const int32_t* forced = nullptr) {
   const orc_config& c = m.c;
   const Layer& L = m.layers[li];
   const auto& sm = m.small[li];
@@ -325,17 +325,19 @@ void moe_token(const orc_model& m, int li, const float* x, const float* xr, int 
   for (int e = 0; e < nE; e++) w.idx[e] = e;
   // descending probability, equal probabilities keep ascending index (llm/moe.go:249-252)
   std::stable_sort(w.idx.begin(), w.idx.end(), [&](int a, int b) { return w.probs[a] > w.probs[b]; });
+  if (topk_out) for (int k = 0; k < used; k++) topk_out[k] = w.idx[k];
+  if (margin_out) {
+    float pk = w.probs[w.idx[used - 1]], pn = used < nE ? w.probs[w.idx[used]] : 0.f;
+    *margin_out = pk > 0 ? (pk - pn) / pk : 0.f;
+  }
+  // a checker may make the block follow another implementation's selection (same weights rule, its experts)
+  if (forced != nullptr && forced[0] >= 0) for (int k = 0; k < used; k++) w.idx[k] = forced[k];
   float sum = 0;
   std::vector<float> wt(used);
   for (int k = 0; k < used; k++) { wt[k] = w.probs[w.idx[k]]; sum += wt[k]; }
   if (sum < 6.103515625e-5f) sum = 6.103515625e-5f;  // llm/moe.go:256-282
   for (int k = 0; k < used; k++) wt[k] = wt[k] / sum;
-  if (topk_out) for (int k = 0; k < used; k++) topk_out[k] = w.idx[k];
   if (topkw_out) for (int k = 0; k < used; k++) topkw_out[k] = wt[k];
-  if (margin_out) {
-    float pk = w.probs[w.idx[used - 1]], pn = used < nE ? w.probs[w.idx[used]] : 0.f;
-    *margin_out = pk > 0 ? (pk - pn) / pk : 0.f;
-  }
   // routed experts, weights after the FFN, summed in slot order (llm/moe.go:289-359)
   w.g.resize(std::max(ff, ffs)); w.u.resize(std::max(ff, ffs)); w.sw.resize(std::max(ff, ffs)); w.down.resize(H);
   for (int j = 0; j < H; j++) out[j] = 0;
@@ -371,7 +373,7 @@ void embed_row(const orc_model& m, int32_t id, float* dst) {  // llm/model.go:12
 
 // One layer (mixer + MoE) on the residual h for one token.
 void layer_token(const orc_model& m, int li, orc_seq::L& st, float* h, int cell, int pos, int numerics, Work& w,
-                 float* mix_out, float* ffn_out, int32_t* topk, float* topkw, float* margin) {
+                 float* mix_out, float* ffn_out, int32_t* topk, float* topkw, float* margin, const int32_t* forced = nullptr) {
   const orc_config& c = m.c;
   const int H = c.n_embd;
   const auto& sm = m.small[li];
@@ -386,7 +388,7 @@ void layer_token(const orc_model& m, int li, orc_seq::L& st, float* h, int cell,
   rmsnorm(h, sm.ffn_norm.data(), H, c.eps, x.data());
   xr = x;
   if (dev_like(numerics)) round_f16(xr.data(), H);
-  moe_token(m, li, x.data(), xr.data(), numerics, w.ffn.data(), topk, topkw, margin, w);
+  moe_token(m, li, x.data(), xr.data(), numerics, w.ffn.data(), topk, topkw, margin, w, forced);
   if (ffn_out) memcpy(ffn_out, w.ffn.data(), sizeof(float) * H);
   for (int j = 0; j < H; j++) h[j] += w.ffn[j];
 }
@@ -514,7 +516,7 @@ int orc_extend(const orc_model* m, orc_seq* s, const int32_t* ids, int n, int nu
       layer_token(*m, l, s->l[l], h.data(), pos, pos, numerics, w,
                   tr && tr->mix_out ? tr->mix_out + o * H : nullptr, tr && tr->ffn_out ? tr->ffn_out + o * H : nullptr,
                   tr && tr->topk ? tr->topk + o * used : nullptr, tr && tr->topk_w ? tr->topk_w + o * used : nullptr,
-                  tr && tr->margin ? tr->margin + o : nullptr);
+                  tr && tr->margin ? tr->margin + o : nullptr, tr && tr->force_topk ? tr->force_topk + o * used : nullptr);
       if (tr && tr->hidden) memcpy(tr->hidden + o * H, h.data(), sizeof(float) * H);
     }
     s->past++;

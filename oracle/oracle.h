@@ -45,6 +45,11 @@ typedef struct {
   float* topk_w;   /* [n][n_layer][n_expert_used] normalised routing weights */
   float* margin;   /* [n][n_layer] (p_k - p_{k+1}) / p_k at the top-k boundary */
   float* logits;   /* [n][vocab] every row's logits */
+  /* INPUT, optional: [n][n_layer][n_expert_used] experts to route to, in slot order, instead of the oracle's own
+   * top-k (entries < 0: own choice). The oracle still reports its own selection and margin in topk / margin; the
+   * routing weights are its own probabilities of the forced experts. A checker uses this to follow the routing
+   * of the implementation under test across a documented near-tie, so that everything after it stays comparable. */
+  const int32_t* force_topk;
 } orc_trace;
 
 typedef struct orc_model orc_model;

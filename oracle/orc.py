@@ -33,7 +33,7 @@ class Config(C.Structure):
 
 class Trace(C.Structure):
     _fields_ = [("mix_out", C.c_void_p), ("ffn_out", C.c_void_p), ("hidden", C.c_void_p), ("normed", C.c_void_p),
-                ("topk", C.c_void_p), ("topk_w", C.c_void_p), ("margin", C.c_void_p), ("logits", C.c_void_p)]
+                ("topk", C.c_void_p), ("topk_w", C.c_void_p), ("margin", C.c_void_p), ("logits", C.c_void_p), ("force_topk", C.c_void_p)]
 
 
 def build(force=False):
@@ -174,8 +174,10 @@ class Seq:
     def past(self):
         return int(lib().orc_seq_past(self.h))
 
-    def extend(self, ids, numerics=DEVICE_LIKE, trace=(), want_last=True):
-        """Advance by len(ids) tokens. Returns (last-row logits or None, {trace name: array})."""
+    def extend(self, ids, numerics=DEVICE_LIKE, trace=(), want_last=True, force_topk=None):
+        """Advance by len(ids) tokens. Returns (last-row logits or None, {trace name: array}). force_topk
+        [n][n_layer][used] (int32, rows < 0: own choice) makes the MoE blocks route to the given experts in that slot
+        order; the trace's topk / margin still report the oracle's own selection."""
         c = self.model.cfg
         ids = np.ascontiguousarray(ids, dtype=np.int32)
         n = ids.size
@@ -188,6 +190,11 @@ class Seq:
             shp, dt = shapes[name]
             out[name] = np.zeros(shp, dtype=dt)
             setattr(tr, name, out[name].ctypes.data)
+        if force_topk is not None:
+            forced = np.ascontiguousarray(force_topk, dtype=np.int32)
+            if forced.shape != (n, nl, used):
+                raise ValueError(f"force_topk must be {(n, nl, used)}, got {forced.shape}")
+            tr.force_topk = forced.ctypes.data
         last = np.empty(V, dtype=np.float32) if want_last else None
         rc = lib().orc_extend(self.model.h, self.h, ids.ctypes.data, n, numerics,
                               last.ctypes.data if want_last else None, C.byref(tr))

@@ -87,7 +87,7 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   B200_TRY(dalloc(&act16, (size_t)MR * slots1 * c.ffn_expert)); B200_TRY(dalloc(&down, (size_t)MR * slots1 * H));
   B200_TRY(dalloc(&logits, (size_t)LR * c.vocab));
   { B200_TRY(dalloc(&dn_pre, (size_t)c.dn_heads_v * 4 * MR * 292)); B200_TRY(dalloc(&dn_oraw, (size_t)MR * vw)); }
-  { const float one[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f}; B200_TRY(dalloc(&ones, 8)); B200_CUDA(cudaMemcpy(ones, one, sizeof(one), cudaMemcpyHostToDevice)); }
+  { std::vector<float> one(64, 1.f); B200_TRY(dalloc(&ones, one.size())); B200_CUDA(cudaMemcpy(ones, one.data(), one.size() * sizeof(float), cudaMemcpyHostToDevice)); }
   B200_TRY(dalloc(&xperm16, (size_t)MR * used * H)); B200_TRY(dalloc(&gprob, (size_t)c.n_expert)); B200_TRY(dalloc(&n_expert_dev, 1));
   B200_CUDA(cudaMemcpy(n_expert_dev, &c.n_expert, sizeof(int), cudaMemcpyHostToDevice));
   for (int i = 0; i < 3; i++) {
@@ -386,7 +386,10 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     if (fused) { r.h = hc; r.gamma = (const float*)L.ffn_norm.data; r.ss_in = ss_part; r.ss_n = ss_n; r.eps = c.eps; r.xn_out = xn16; }
     r.M = M; r.H = H; r.nE = c.n_expert; r.used = used; r.logits = r_logits; r.probs = nullptr; r.topk = topk; r.topk_w = topk_w;
     r.tl = tl(); r.margin = margin; r.entries = entries; r.n_entries = n_entries; r.cols = cols; r.ticket = r_ticket; r.max_entries = max_entries;
-    r.defer = fused && M == 1 && !epx; r.ecols = entry_cols(M); r.distinct = distinct_dev;
+    // passes of at most 8 rows: the router stops after its logits and every row is routed, computed and combined on
+    // the single-row schedule, so each row's result is the single-row pass's, bit for bit (the reference's batched
+    // decode and verify passes equal their rows stepped alone: llm/graph_batch_test.go:36, llm/spec_slots_test.go:199)
+    r.defer = fused && !epx; r.ecols = entry_cols(M); r.distinct = r.defer ? nullptr : distinct_dev;
     if (epx) { r.entries = nullptr; r.gprob = nullptr; }   // routing only: the work list comes from the gathered routing
     // 32 rows per expert on average and more: the experts run as grouped tensor-core GEMMs over expert-sorted
     // rows (below that the column-tiled kernel, which streams each expert's weights in whole tiles, is faster)
@@ -455,28 +458,28 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     } else {
     QGemvParams p = base(L.gate_exps, H, c.ffn_expert, xn16, H);
     p.w2[0] = L.up_exps.data; p.ws = L.gate_sh.data; p.ws2 = L.up_sh.data; p.expert_stride = (int64_t)c.ffn_expert * L.gate_exps.stride;
-    p.entries = entries; p.n_entries = n_entries; p.cols = cols; p.x_div = slots1; p.xcols = std::min(xcols, entry_cols(M));
+    p.entries = entries; p.n_entries = n_entries; p.cols = cols; p.x_div = slots1; p.xcols = r.defer ? 1 : std::min(xcols, entry_cols(M));
     p.y16 = act16; p.ldy = c.ffn_expert;
     p.route_here = r.defer; p.route = r;
-    B200_TRY(launch_qgemv(L.gate_exps.type, PRO_F16, EPI_SWIGLU, true, true, p, ne, pdl(), st));
+    B200_TRY(launch_qgemv(L.gate_exps.type, PRO_F16, EPI_SWIGLU, true, true, p, r.defer ? M * slots1 : ne, pdl(), st));
     QGemvParams q = base(L.down_exps, c.ffn_expert, H, act16, c.ffn_expert);
     q.ws = L.down_sh.data; q.expert_stride = (int64_t)H * L.down_exps.stride;
     q.entries = entries; q.n_entries = n_entries; q.cols = cols; q.x_div = 1; q.xcols = std::min(xcols, entry_cols(M));
     q.y = down; q.ldy = H;
-    if (fused && M == 1 && L.down_exps.type == L.down_sh.type && slots1 <= 16) {
-      // one row: the routing weights are applied inside the down projection, which leaves a few partial rows
+    if (r.defer && L.down_exps.type == L.down_sh.type && slots1 <= 16) {
+      // per row: the routing weights are applied inside the down projection, which leaves a few partial rows
       // (one per CTA of a tile) for the next projection to add, instead of used + 1 expert rows
       MoeDown1Params d1{};
       d1.w = L.down_exps.data; d1.ws = L.down_sh.data; d1.expert_stride = (int64_t)H * L.down_exps.stride; d1.stride = L.down_exps.stride;
       d1.K = c.ffn_expert; d1.N = H; d1.used = used; d1.topk = topk; d1.topk_w = topk_w; d1.act = act16; d1.part = down;
       d1.split = moe_down1_split(used, c.ffn_expert); d1.err = err_flag; d1.tl = tl();
-      B200_TRY(launch_moe_down1(L.down_exps.type, d1, pdl(), st));
+      B200_TRY(launch_moe_down1(L.down_exps.type, d1, M, pdl(), st));
       comb_used = d1.split - 1; comb_w = ones;
     } else {
       B200_TRY(launch_qgemv(L.down_exps.type, PRO_F16, EPI_STORE, false, true, q, ne, pdl(), st));
     }
     }
-    if (fused && M == 1 && !epx) pending = true;
+    if (r.defer) pending = true;
     else {
       const DTensor& next_norm = f.draft ? L.head_norm : (l + 1 < c.n_layer ? m->layers[l + 1].attn_norm : m->output_norm);
       TailParams tp = row_tail(2, next_norm);
@@ -593,7 +596,8 @@ int Graph::run_rows(const int32_t* ids, const int* slots, const int* pos, int M,
   stats.passes++; stats.rows += M; stats.launches += last_launches; stats.device_ms += ms;
   stats.host_ms += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - host_t0).count();
   stats.last_rows = M; stats.last_launches = last_launches; stats.last_device_ms = ms;
-  if (M == 1 && !f.draft) single_row_layers += m->c.n_layer;
+  // rows of fused passes select their experts inside the expert kernel: one stream per row and slot
+  if (M <= QG_FUSED_ROWS && m->c.n_embd <= QG_COMBINE_MAX_K && !f.draft && !(ep_on && ep_ready && n_seq == M)) single_row_layers += (int64_t)M * m->c.n_layer;
   return OK;
 }
 
@@ -711,7 +715,7 @@ int Graph::generate_greedy(const int32_t* slots_in, const int32_t* first, int n,
   B200_CUDA(cudaEventElapsedTime(&last_ms, ev0, ev1));
   stats.passes += steps; stats.rows += (int64_t)steps * n; stats.launches += (int64_t)steps * last_launches; stats.device_ms += last_ms;
   stats.last_rows = n; stats.last_launches = last_launches; stats.last_device_ms = last_ms / steps;
-  if (n == 1) single_row_layers += (int64_t)steps * m->c.n_layer;
+  if (n <= QG_FUSED_ROWS && m->c.n_embd <= QG_COMBINE_MAX_K && !(ep_on && ep_ready)) single_row_layers += (int64_t)steps * n * m->c.n_layer;
   memcpy(out, ids_host, (size_t)steps * n * sizeof(int32_t));
   for (int i = 0; i < n; i++) past[slots[i]] += steps;
   spec_n = 0;

@@ -48,7 +48,7 @@ struct Graph {
   int *r_ticket = nullptr, *err_flag = nullptr, *err_host = nullptr, *n_entries = nullptr, *cols = nullptr, *row_slot = nullptr, *row_pos = nullptr, *logit_rows = nullptr, *hist_len = nullptr;
   int4* entries = nullptr;
   int64_t* distinct_dev = nullptr;     // experts streamed by the work lists built so far (device counter)
-  int64_t single_row_layers = 0;       // layers run by single-row passes, whose experts are selected inside the expert kernel
+  int64_t single_row_layers = 0;       // (row, layer) pairs of fused passes, whose experts are selected inside the expert kernel
   SeqDesc* seqs = nullptr;
   float* rope = nullptr;
   int proj_ld = 0, max_entries = 0, nsplit = 0, split_cells = 0;

@@ -35,8 +35,9 @@ int launch_embed(const EmbedParams& p, cudaStream_t st);
 
 // K-quant projections; `pdl` marks the launch as a programmatic dependent of the previous kernel.
 int launch_qgemv(uint32_t type, int pro, int epi, bool dual, bool grouped, const QGemvParams& p, int max_entries, bool pdl, cudaStream_t st);
-// single-row pass: every selected expert's down projection, the weighted sum and the residual add in one launch
-int launch_moe_down1(uint32_t type, const MoeDown1Params& p, bool pdl, cudaStream_t st);
+// passes of at most QG_FUSED_ROWS rows: per row, every selected expert's down projection with the routing weights applied,
+// left as a few partial rows for the next projection to add
+int launch_moe_down1(uint32_t type, const MoeDown1Params& p, int rows, bool pdl, cudaStream_t st);
 int moe_down1_split(int used, int K);
 int qgemv_groups(int K, int N);
 int launch_row_tail(const TailParams& tp, bool pdl, cudaStream_t st);

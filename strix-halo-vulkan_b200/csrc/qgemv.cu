@@ -87,14 +87,14 @@ int moe_down1_split(int used, int K) {
 }
 
 template <int TYPE>
-static int launch_md(const MoeDown1Params& p, bool pdl, cudaStream_t st) {
+static int launch_md(const MoeDown1Params& p, int rows, bool pdl, cudaStream_t st) {
   auto kernel = moe_down1_kernel<TYPE>;
   const int slots1 = p.used + 1, cl = p.split;
   const size_t smem = md_smem(p.K, (slots1 + cl - 1) / cl, p.stride);
   if (smem > 200 * 1024) { set_error("moe_down1: tiles too large for shared memory"); return ECAPACITY; }
   B200_ONCE_PER_DEVICE(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(((p.N + 15) / 16) * cl); cfg.blockDim = dim3(QG_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cfg.gridDim = dim3(((p.N + 15) / 16) * cl, rows); cfg.blockDim = dim3(QG_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -103,12 +103,12 @@ static int launch_md(const MoeDown1Params& p, bool pdl, cudaStream_t st) {
   return OK;
 }
 
-int launch_moe_down1(uint32_t type, const MoeDown1Params& p, bool pdl, cudaStream_t st) {
-  if (p.K % 256 != 0 || p.K <= 0 || p.used + 1 > MD_MAXSLOTS || p.split < 1 || p.split > 4 || p.part == nullptr) { set_error("moe_down1: shape outside kernel limits"); return EINVAL_; }
+int launch_moe_down1(uint32_t type, const MoeDown1Params& p, int rows, bool pdl, cudaStream_t st) {
+  if (p.K % 256 != 0 || p.K <= 0 || p.used + 1 > MD_MAXSLOTS || p.split < 1 || p.split > 4 || p.part == nullptr || rows < 1 || rows > QG_FUSED_ROWS) { set_error("moe_down1: shape outside kernel limits"); return EINVAL_; }
   switch (type) {
-    case T_Q4_K: return launch_md<T_Q4_K>(p, pdl, st);
-    case T_Q5_K: return launch_md<T_Q5_K>(p, pdl, st);
-    case T_Q6_K: return launch_md<T_Q6_K>(p, pdl, st);
+    case T_Q4_K: return launch_md<T_Q4_K>(p, rows, pdl, st);
+    case T_Q5_K: return launch_md<T_Q5_K>(p, rows, pdl, st);
+    case T_Q6_K: return launch_md<T_Q6_K>(p, rows, pdl, st);
   }
   set_error("moe_down1: weight type has no fused projection kernel (Q4_K, Q5_K, Q6_K only)");
   return EINVAL_;

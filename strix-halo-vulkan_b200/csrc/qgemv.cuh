@@ -53,9 +53,9 @@ struct QGemvParams {
   const uint8_t* ws;         // shared expert weights (grouped mode)
   const uint8_t* ws2;
   int x_div;                 // grouped: x row = cols[c] / x_div
-  // grouped, single-row passes: the router kernel stopped after the logits (route.defer); every CTA
-  // selects the experts itself (one warp, a few hundred instructions) instead of waiting for a last
-  // router CTA to do it, and CTA (0,0) leaves the selection and the work list for the kernels after it
+  // grouped, passes of at most QG_FUSED_ROWS rows: the router kernel stopped after the logits (route.defer); every
+  // CTA selects the experts of its row itself (one warp, a few hundred instructions) instead of waiting for a last
+  // router CTA to do it, and the first CTA of a row leaves the row's selection for the kernels after it
   int route_here;
   RouterParams route;
   // plain mode columns: rows [ztile*8, ztile*8+8) of M
@@ -533,8 +533,13 @@ __device__ __forceinline__ void stage_x_norm(const QGemvParams& p, uint8_t* xs, 
 __device__ __forceinline__ void stage_x_combine(const QGemvParams& p, uint8_t* xs, __half* sxs, float* scratch, int ncols, const int* xrows,
                                                 int xstride, bool writer, const float4* pre_gam = nullptr, const float4* pre_h = nullptr) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, K = p.K, slots1 = p.used + 1;
-  // element index of this thread, rotated by whole 128-byte lines per CTA (every CTA reads the same rows)
-  const int et = (tid + 8 * (int)((blockIdx.x + blockIdx.y) & 31)) & (QG_THREADS - 1);
+  // Element index of this thread, rotated per CTA (every CTA reads the same rows: they should not all ask for the
+  // same line at the same moment). The rotation moves whole warps, and the warps' sums of squares are added in the
+  // order of the elements, not of the warps: every CTA, whatever its index and whatever the launch's grid, forms the
+  // same sums in the same order, so a row's normalised values do not depend on which CTA computes them.
+  const int rot = (int)((blockIdx.x + blockIdx.y) & 7);
+  const int et = (tid + 32 * rot) & (QG_THREADS - 1);
+  const int ewarp = (warp + rot) & (QG_WARPS - 1);   // the warp-sized group of elements this warp holds
   // the norm weights are fetched with the first loads, not after the reduction
   float4 gam[2];
 #pragma unroll
@@ -578,7 +583,7 @@ __device__ __forceinline__ void stage_x_combine(const QGemvParams& p, uint8_t* x
 #pragma unroll
     for (int cc = 0; cc < 4; cc++) {
       sq[cc] = warp_sum(sq[cc]);
-      if (lane == 0) scratch[warp * 4 + cc] = sq[cc];
+      if (lane == 0) scratch[ewarp * 4 + cc] = sq[cc];
     }
     __syncthreads();
 #pragma unroll
@@ -657,24 +662,29 @@ __global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 
     pdl_wait();  // the entries (or the logits) are written by the router kernel
     int4 e;
     if (p.route_here) {
-      const int used = p.route.used, y = blockIdx.y;
-      const bool writer = blockIdx.x == 0 && y == 0;
-      active = y <= used;
+      // blockIdx.y = row * (used + 1) + slot: every row of the pass is routed and computed on its own, exactly as a
+      // single-row pass would do it, so a pass of several rows gives each row the single-row result bit for bit
+      const int used = p.route.used, slots1 = used + 1, y = blockIdx.y, row = y / slots1, slot = y - row * slots1;
+      const bool writer = blockIdx.x == 0 && slot == 0;
+      active = row < p.route.M;
       if (warp == 0) {
-        if (active || writer) {
-          const int ex = p.route.nE <= 512 ? route_token<16>(p.route, 0, lane, writer, y, route_topk) : route_token<32>(p.route, 0, lane, writer, y, route_topk);
-          if (lane == 0) route_expert = y < used ? ex : -1;
+        if (active) {
+          const int ex = p.route.nE <= 512 ? route_token<16>(p.route, row, lane, writer, slot, route_topk) : route_token<32>(p.route, row, lane, writer, slot, route_topk);
+          if (lane == 0) route_expert = slot < used ? ex : -1;
         }
       } else if constexpr (PRO == PRO_F16) {
-        // meanwhile the other warps stage the pass's single activation row (it does not depend on the routing)
-        copy_x_row(p.x, K, xs, tid - 32, QG_THREADS - 32);
+        // meanwhile the other warps stage the row's activations (they do not depend on the routing)
+        if (active) copy_x_row(p.x + (int64_t)row * p.ldx, K, xs, tid - 32, QG_THREADS - 32);
       }
       x_copied = PRO == PRO_F16;  // for every thread alike: the barrier below covers the copy
       __syncthreads();
       e = make_int4(route_expert, y, 1, 0);
-      if (writer) {  // the work list of a single row: one entry per slot, the shared expert last
-        if (tid < used) { p.route.entries[tid] = make_int4(route_topk[tid], tid, 1, 0); p.route.cols[tid] = tid; }
-        if (tid == used) { p.route.entries[used] = make_int4(-1, used, 1, 0); p.route.cols[used] = used; *p.route.n_entries = used + 1; }
+      if (writer && p.route.entries != nullptr) {  // the row's part of the work list: one entry per slot, the shared expert last
+        if (tid < used) { p.route.entries[row * slots1 + tid] = make_int4(route_topk[tid], row * slots1 + tid, 1, 0); p.route.cols[row * slots1 + tid] = row * slots1 + tid; }
+        if (tid == used) {
+          p.route.entries[row * slots1 + used] = make_int4(-1, row * slots1 + used, 1, 0); p.route.cols[row * slots1 + used] = row * slots1 + used;
+          if (row == 0) *p.route.n_entries = p.route.M * slots1;
+        }
       }
     } else {
       active = (int)blockIdx.y < *p.n_entries;
@@ -727,7 +737,7 @@ __global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 
   if constexpr (PRO == PRO_COMBINE) {
     if (p.M == 1) {
       pre = true;
-      const int et = (tid + 8 * (int)((blockIdx.x + blockIdx.y) & 31)) & (QG_THREADS - 1);
+      const int et = (tid + 32 * (int)((blockIdx.x + blockIdx.y) & 7)) & (QG_THREADS - 1);   // as in stage_x_combine
 #pragma unroll
       for (int i = 0; i < 2; i++) {
         const int k = et * 4 + i * QG_THREADS * 4;
@@ -861,10 +871,10 @@ struct MoeDown1Params {
   const uint8_t* ws;        // shared expert
   int64_t expert_stride, stride;
   int K, N, used;
-  const int32_t* topk;      // [used]
-  const float* topk_w;      // [used + 1]
-  const __half* act;        // [used + 1][K]
-  float* part;              // [split][N] weighted partial sums, one row per CTA of a tile
+  const int32_t* topk;      // [rows][used]
+  const float* topk_w;      // [rows][used + 1]
+  const __half* act;        // [rows][used + 1][K]
+  float* part;              // [rows][split][N] weighted partial sums, one row per CTA of a tile; blockIdx.y is the row
   int split;                // CTAs per tile (1..4)
   int* err;
   Timeline tl;
@@ -900,10 +910,14 @@ __global__ void __launch_bounds__(QG_THREADS) moe_down1_kernel(const MoeDown1Par
   pdl_wait();   // the selection and the activations come from the kernel before
   pdl_launch();
   tl_mark(p.tl, 1);
+  const int prow = blockIdx.y;   // row of the pass: each row is finished exactly as a single-row pass finishes its own
+  const int32_t* topk = p.topk + (size_t)prow * p.used;
+  const float* topk_w = p.topk_w + (size_t)prow * slots1;
+  const __half* act = p.act + (size_t)prow * slots1 * K;
   if (tid < nloc) {
     const int s = rank + tid * CL;
-    expert[tid] = s < p.used ? __ldcg(p.topk + s) : -1;
-    wgt[tid] = __ldcg(p.topk_w + s);
+    expert[tid] = s < p.used ? __ldcg(topk + s) : -1;
+    wgt[tid] = __ldcg(topk_w + s);
   }
   __syncthreads();
   const int tile = blockIdx.x / CL, nrows = min(16, p.N - tile * 16);
@@ -914,7 +928,7 @@ __global__ void __launch_bounds__(QG_THREADS) moe_down1_kernel(const MoeDown1Par
       bulk_copy_g2s(tiles + (size_t)i * tile_bytes, base + (size_t)tile * 16 * p.stride, (uint32_t)(nrows * p.stride), &bar);
     }
   }
-  for (int i = 0; i < nloc; i++) copy_x_row(p.act + (size_t)(rank + i * CL) * K, K, xs + (size_t)i * xstride, tid, QG_THREADS);
+  for (int i = 0; i < nloc; i++) copy_x_row(act + (size_t)(rank + i * CL) * K, K, xs + (size_t)i * xstride, tid, QG_THREADS);
   __syncthreads();
   stage_sx(K, maxloc, xs, sxs, nloc, xstride);
   tl_mark(p.tl, 2);
@@ -946,7 +960,7 @@ __global__ void __launch_bounds__(QG_THREADS) moe_down1_kernel(const MoeDown1Par
     float v = 0.f;
 #pragma unroll
     for (int w = 0; w < QG_WARPS; w++) v += red[w][tid];
-    p.part[(size_t)rank * p.N + (size_t)tile * 16 + tid] = v;
+    p.part[((size_t)prow * CL + rank) * p.N + (size_t)tile * 16 + tid] = v;
   }
   tl_mark(p.tl, 4);
 }

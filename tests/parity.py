@@ -60,30 +60,42 @@ def assert_close(got, want, what, tol=REL_TOL):
 
 
 def routing_flips(gpu_topk, orc_topk, margin, what=""):
-    """Routed sets must be the oracle's, bit for bit, except where the oracle's own top-k boundary is a
-    documented near-tie (margin below NEAR_TIE) or, from the second layer on, inside the fp16 staging noise (below
-    NOISE_TIE, see above): there either neighbour is a valid pick. gpu_topk is
-    [n_layer][T][used], orc_topk [T][n_layer][used], margin [T][n_layer]. Returns (clean, flips): clean[l] is
-    the number of leading rows of layer l that no flip at this or an earlier layer can have reached (a flip
-    at token t changes that token from that layer on, and later tokens through the sequence state), flips the
-    list of (layer, token, margin)."""
+    """Routed sets must be the oracle's, bit for bit, except where the oracle's own top-k boundary is a documented
+    near-tie (margin below NEAR_TIE) or inside the fp16 staging noise (below NOISE_TIE, see above): there either
+    neighbour is a valid pick. gpu_topk is [n_layer][T][used], orc_topk [T][n_layer][used] (the oracle's OWN
+    selection), margin [T][n_layer]. The oracle is expected to have FOLLOWED the implementation's routing
+    (Seq.extend(force_topk=...)), so a flip does not disturb what comes after it and every decision is judged on
+    its own. Returns the flips as (layer, token, margin); a difference at a clear margin fails."""
     nl, T = gpu_topk.shape[0], gpu_topk.shape[1]
-    clean = np.full(nl, T)
     flips = []
     for l in range(nl):
-        upto = int(clean[l - 1]) if l else T
-        first = upto
-        for t in range(upto):
+        for t in range(T):
             if set(gpu_topk[l, t].tolist()) != set(orc_topk[t, l].tolist()):
                 assert margin[t, l] < NOISE_TIE, f"{what}: layer {l} token {t} routes to {sorted(gpu_topk[l, t].tolist())}, the oracle to " \
                                                  f"{sorted(orc_topk[t, l].tolist())}, with a clear margin {margin[t, l]:.3e}"
                 flips.append((l, t, float(margin[t, l])))
-                first = min(first, t)
-                break   # rows after a flip in this layer are no longer comparable
-        clean[l] = first
-    return clean, flips
+    return flips
 
 
 def noise_flips(flips):
     """The flips that are not the contract's near-ties but staging noise (NEAR_TIE <= margin < NOISE_TIE)."""
     return [f for f in flips if f[2] >= NEAR_TIE]
+
+
+def follow_pass(g, orc, seq, ids, what, logit_rows=1):
+    """Runs `ids` as ONE pass of the current slot of a traced graph and through the oracle in the pass's own
+    arithmetic (the weight matrices the pass rounds to fp16 rounded there too), the oracle following the pass's
+    routing. Every routing decision is judged (routing_flips), every row's residual after every layer and the
+    last row's logits are held to the contract's bounds. Returns (logits, oracle logits, flips)."""
+    T = len(ids)
+    logits, _ = g.extend(ids)
+    tr = g.trace(T)
+    forced = np.ascontiguousarray(tr["topk"].transpose(1, 0, 2))
+    want, ot = seq.extend(ids, numerics=orc.DEVICE_LIKE | g.fp16_weight_mask(T, logit_rows), trace=("hidden", "topk", "margin"), force_topk=forced)
+    flips = routing_flips(tr["topk"], ot["topk"], ot["margin"], what)
+    for l in range(tr["hidden"].shape[0]):
+        assert_close(tr["hidden"][l], ot["hidden"][:, l], f"{what}: layer {l} residual, {T} rows")
+    assert_close(logits, want, f"{what}: logits of the last row")
+    noisy = noise_flips(flips)
+    assert len(noisy) <= max(1, T * tr["hidden"].shape[0] // 100), f"{what}: too many flips above the near-tie margin: {noisy}"
+    return logits, want, flips

@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 
 import modelgen
-from parity import NEAR_TIE, NOISE_TIE, assert_close, compare, logit_gap, noise_flips, routing_flips
+from parity import NEAR_TIE, assert_close, follow_pass, logit_gap, noise_flips, routing_flips
 
 pytestmark = pytest.mark.gpu
 
@@ -37,51 +37,19 @@ def test_device_generated_checkpoint_dequantises_like_the_oracle(pkg, orc, a3b4)
         assert 0.005 < np.std(want) < 0.04     # N(0, 0.02) survived the quantiser
 
 
-def check_pass(g, orc, seq, ids, what, min_clean=1):
-    """One pass of len(ids) rows on a traced graph against the oracle in the same arithmetic."""
-    T = len(ids)
-    cfg = g.model.cfg
-    logits, _ = g.extend(ids)
-    tr = g.trace(T)
-    want, ot = seq.extend(ids, numerics=orc.DEVICE_LIKE | g.fp16_weight_mask(T, 1), trace=("hidden", "topk", "margin"))
-    clean, flips = routing_flips(tr["topk"], ot["topk"], ot["margin"], what)
-    for l in range(cfg["n_layer"]):
-        if clean[l] > 0:
-            assert_close(tr["hidden"][l][:clean[l]], ot["hidden"][:clean[l], l], f"{what}: layer {l} residual, {clean[l]} of {T} rows")
-        if clean[l] < T:
-            # Rows after a documented near-tie: the flipped row itself differs by an expert, and later rows see it
-            # through the sequence state, which can tip further boundaries. No element-wise claim there, but the
-            # rows must still be the same computation: most of them route alike, and the error stays small in rms.
-            rest = slice(int(clean[l]), T)
-            same = np.mean([set(tr["topk"][l, t].tolist()) == set(ot["topk"][t, l].tolist()) for t in range(int(clean[l]), T)])
-            r = compare(tr["hidden"][l][rest], ot["hidden"][rest, l])
-            assert same >= 0.9 and r["rms"] <= 5e-2 * r["ref_rms"], f"{what}: layer {l} after the first near-tie: {same:.3f} of the rows route alike, {r}"
-    assert clean[-1] >= min_clean, f"{what}: routing flips {flips} leave only {clean[-1]} comparable rows"
-    assert len(noise_flips(flips)) <= 1, f"{what}: flips above the near-tie margin {noise_flips(flips)}"
-    if clean[-1] == T:
-        assert_close(logits, want, f"{what}: logits of the last row")
-    return logits, want, flips
-
-
 def test_full_shape_prefill_and_greedy_decode_match_oracle(pkg, orc, a3b4):
     cfg = a3b4["cfg"]
     ids = np.random.default_rng(1).integers(0, cfg["vocab"], 24).astype(np.int32)
     g = pkg.Graph(a3b4["model"], n_kv=64, max_tokens=32, trace=True, use_cuda_graph=False)
     seq = a3b4["oracle"].seq()
     g.reset()
-    logits, want, flips = check_pass(g, orc, seq, ids, "24-row prefill", min_clean=4)
-    tainted = bool(flips)
+    logits, want, flips = follow_pass(g, orc, seq, ids, "24-row prefill")
     for step in range(8):
-        if not tainted:
-            assert_close(logits, want, f"logits at step {step}")
-            tg, to = int(np.argmax(logits)), int(np.argmax(want))
-            assert tg == to or logit_gap(want) < NEAR_TIE, (step, tg, to, logit_gap(want))
-        to = int(np.argmax(want))
-        logits, _ = g.extend([to])
-        tr = g.trace(1)
-        want, od = seq.extend([to], trace=("topk", "margin"))
-        _, f2 = routing_flips(tr["topk"], od["topk"], od["margin"], f"decode step {step}")
-        tainted = tainted or bool(f2)
+        tg, to = int(np.argmax(logits)), int(np.argmax(want))
+        assert tg == to or logit_gap(want) < NEAR_TIE, (step, tg, to, logit_gap(want))
+        logits, want, f2 = follow_pass(g, orc, seq, [to], f"decode step {step}")
+        flips += f2
+    assert len(noise_flips(flips)) <= 2, flips
 
 
 def test_eighty_row_pass_routes_like_the_oracle(pkg, orc, a3b4):
@@ -93,26 +61,7 @@ def test_eighty_row_pass_routes_like_the_oracle(pkg, orc, a3b4):
     g = pkg.Graph(a3b4["model"], n_kv=96, max_tokens=128, trace=True, use_cuda_graph=False)
     assert g.fp16_weight_mask(T, 1) & pkg.lib.W16_ROUTER
     g.reset()
-    check_pass(g, orc, a3b4["oracle"].seq(), ids, "80-row pass", min_clean=8)
-
-
-def prefill_both(g, orc, seq, ids, chunk, what):
-    """Feeds the same tokens to a slot of the traced graph (in passes of `chunk` rows) and to the oracle and compares
-    the routed sets of every row and layer. Returns True when a routing decision differed at a documented near-tie
-    (the sequence state then legitimately differs from the oracle's); a difference at a clear margin fails."""
-    flipped, noisy = False, []
-    for o in range(0, len(ids), chunk):
-        part = ids[o:o + chunk]
-        g.extend(part)
-        tr = g.trace(len(part))
-        _, ot = seq.extend(part, numerics=orc.DEVICE_LIKE | g.fp16_weight_mask(len(part), 1), trace=("topk", "margin"), want_last=False)
-        if flipped:
-            continue          # the sequence states differ from here on: later decisions are no longer comparable
-        _, flips = routing_flips(tr["topk"], ot["topk"], ot["margin"], f"{what}, rows {o}..{o + len(part)}")
-        flipped = flipped or bool(flips)
-        noisy += noise_flips(flips)
-    assert len(noisy) <= max(1, len(ids) * g.model.cfg["n_layer"] // 100), f"{what}: too many flips above the near-tie margin: {noisy}"
-    return flipped
+    follow_pass(g, orc, a3b4["oracle"].seq(), ids, "80-row pass")
 
 
 def test_slots_with_long_contexts_batched_against_the_oracle(pkg, orc, a3b4):
@@ -121,49 +70,69 @@ def test_slots_with_long_contexts_batched_against_the_oracle(pkg, orc, a3b4):
     64-slot benchmark runs (two splits, a ragged second one). A 16-row pass (one 16-warp DeltaNet CTA per head
     and sequence, dense projections on the tensor cores) and a 64-row pass (router logits on the mma kernel,
     work-list entries of four columns) are compared slot by slot with the oracle. Every routing decision of
-    every pass, prefill included, is compared: a slot drops out of the comparison only after a documented
-    near-tie flipped one of its decisions."""
+    every pass, prefill included, is judged, and the oracle follows the passes' routing, so every slot stays
+    comparable to the end."""
     cfg = a3b4["cfg"]
     S = 64
     rng = np.random.default_rng(33)
     lens = [int(rng.integers(2, 7)) for _ in range(S)]
     lens[0], lens[5], lens[11] = 300, 262, 391           # cells already in the cache when the batched passes run
     g = pkg.Graph(a3b4["model"], n_kv=448, max_tokens=64, slots=S, attn_split_cells=256, trace=True, use_cuda_graph=False)
-    seqs, near_tie = [], set()
+    seqs, flips = [], []
     for s in range(S):
         p = rng.integers(0, cfg["vocab"], lens[s]).astype(np.int32)
         g.use_slot(s); g.reset()
         sq = a3b4["oracle"].seq()
-        if prefill_both(g, orc, sq, p, 8, f"prefill of slot {s}"):   # passes of at most 8 rows: exact weights on both sides
-            near_tie.add(s)
+        for o in range(0, len(p), 8):                    # passes of at most 8 rows: exact weights on both sides
+            flips += follow_pass(g, orc, sq, p[o:o + 8], f"prefill of slot {s}, rows {o}..")[2]
         seqs.append(sq)
     toks = rng.integers(0, cfg["vocab"], S).astype(np.int32)
-    noisy = 0
     for rows in (16, 64):
         mode = orc.DEVICE_LIKE | g.fp16_weight_mask(rows, rows)
         got = g.decode_rows(list(range(rows)), toks[:rows])
         assert g.pass_experts() > 10
         tr = g.trace(rows)
-        compared = 0
         for s in range(rows):
-            want, od = seqs[s].extend([int(toks[s])], numerics=mode, trace=("topk", "margin"))
+            forced = np.ascontiguousarray(tr["topk"][:, s:s + 1].transpose(1, 0, 2))
+            want, od = seqs[s].extend([int(toks[s])], numerics=mode, trace=("hidden", "topk", "margin"), force_topk=forced)
+            flips += routing_flips(tr["topk"][:, s:s + 1], od["topk"], od["margin"], f"{rows}-row pass, slot {s}")
             toks[s] = int(np.argmax(want))
-            if s in near_tie:
-                continue
-            for l in range(cfg["n_layer"]):
-                if set(tr["topk"][l, s].tolist()) != set(od["topk"][0, l].tolist()):
-                    # routed sets are the oracle's except at a documented near-tie
-                    assert od["margin"][0, l] < NOISE_TIE, f"{rows}-row pass, slot {s}, layer {l}: routing differs at a clear margin {od['margin'][0, l]:.3e}"
-                    near_tie.add(s); noisy += od["margin"][0, l] >= NEAR_TIE
-                    break     # later layers see a different residual row: no longer comparable
-            if s in near_tie:
-                continue
+            assert_close(tr["hidden"][-1][s], od["hidden"][0, -1], f"{rows}-row pass, slot {s} ({lens[s]} cells): last residual")
             assert_close(got[s], want, f"{rows}-row pass, slot {s} ({lens[s]} cells)")
             assert int(np.argmax(got[s])) == int(np.argmax(want)) or logit_gap(want) < NEAR_TIE
-            compared += 1
-        assert compared >= rows * 3 // 4, (compared, sorted(near_tie))
-    assert not {0, 5, 11} <= near_tie, "every long-context slot dropped out"
-    assert noisy <= 3, f"{noisy} of {80 * cfg['n_layer']} batched routing decisions flipped above the near-tie margin"
+    decisions = (sum(lens) + 80) * cfg["n_layer"]
+    assert len(noise_flips(flips)) <= decisions // 100, f"{len(noise_flips(flips))} of {decisions} routing decisions flipped above the near-tie margin: {noise_flips(flips)}"
+
+
+def test_eight_slots_batched_are_each_slot_bit_for_bit(pkg, a3b4):
+    """Passes of up to 8 rows run every row on the single-row schedule (routing inside the expert kernel, routing
+    weights applied inside the down projection, partial rows added by the next projection): a batched step and a
+    verify pass give each row exactly the logits of that row stepped alone (llm/graph_batch_test.go:36 asserts bit
+    equality the same way)."""
+    cfg = a3b4["cfg"]
+    g = pkg.Graph(a3b4["model"], n_kv=48, max_tokens=32, slots=8, speculative=True, spec_rows=5, use_cuda_graph=False)
+    rng = np.random.default_rng(19)
+    toks = rng.integers(0, cfg["vocab"], 8).astype(np.int32)
+    solo = []
+    for s in range(8):
+        g.use_slot(s); g.reset(); g.extend(rng.integers(0, cfg["vocab"], 3 + s % 4).astype(np.int32))
+        ck = g.checkpoint()
+        lg, _ = g.extend([int(toks[s])]); solo.append(lg)
+        g.restore(ck); g.checkpoint_free(ck)
+    batched = g.decode_rows(list(range(8)), toks)
+    for s in range(8):
+        assert np.array_equal(batched[s].view(np.uint32), solo[s].view(np.uint32)), f"slot {s}"
+    # a verify pass of 5 rows against the same 5 tokens stepped one by one
+    g.use_slot(0)
+    rows = rng.integers(0, cfg["vocab"], 5).astype(np.int32)
+    ck = g.checkpoint()
+    one_by_one = [g.extend([int(t)])[0] for t in rows]
+    g.restore(ck); g.checkpoint_free(ck)
+    g.speculate(True)
+    all_logits, _ = g.extend_rows(rows)
+    g.keep(5); g.speculate(False)
+    for i in range(5):
+        assert np.array_equal(all_logits[i].view(np.uint32), one_by_one[i].view(np.uint32)), f"verify row {i}"
 
 
 def test_sixteen_slots_batched_match_solo(pkg, a3b4):
@@ -225,4 +194,4 @@ def test_grouped_expert_gemm_at_512_experts_against_the_oracle(pkg, orc, a3b2):
     mask = g.fp16_weight_mask(T, 1)
     assert mask & pkg.lib.W16_EXPERTS and mask & pkg.lib.W16_SHARED and mask & pkg.lib.W16_ROUTER
     g.reset()
-    check_pass(g, orc, a3b2["oracle"].seq(), ids, "1664-row pass", min_clean=16)
+    follow_pass(g, orc, a3b2["oracle"].seq(), ids, "1664-row pass")

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 import modelgen
-from parity import NEAR_TIE, assert_close, logit_gap
+from parity import NEAR_TIE, assert_close, follow_pass, logit_gap, routing_flips
 
 pytestmark = pytest.mark.gpu
 
@@ -23,25 +23,31 @@ def fill(g, cfg, slots, seed0):
 
 
 @pytest.mark.parametrize("rows", [3, 8, 16])
-def test_one_rank_exchanging_with_itself_is_the_plain_pass(pkg, tiny_path, rows):
+def test_one_rank_exchanging_with_itself_is_the_plain_pass(pkg, orc, tiny_path, rows):
     model = pkg.Model.open(tiny_path)
-    cfg = model.cfg
+    om, cfg, _ = modelgen.oracle_model(tiny_path)
     toks = prompt(cfg, rows, 77)
-    plain = pkg.Graph(model, n_kv=48, max_tokens=32, slots=rows, use_cuda_graph=False)
-    fill(plain, cfg, rows, 100)
-    want = plain.decode_rows(list(range(rows)), toks)
-    g = pkg.Graph(model, n_kv=48, max_tokens=32, slots=rows, use_cuda_graph=False)
-    fill(g, cfg, rows, 100)
+    g = pkg.Graph(model, n_kv=48, max_tokens=32, slots=rows, trace=True, use_cuda_graph=False)
+    seqs = []
+    for s in range(rows):
+        g.use_slot(s); g.reset()
+        seqs.append(om.seq())
+        follow_pass(g, orc, seqs[-1], prompt(cfg, 4 + s % 5, 100 + s), f"prefill of slot {s}")
     pkg.Graph.ep_connect_local([g])
     g.ep_enable(True)
     got = g.decode_rows(list(range(rows)), toks)
+    tr = g.trace(rows)
+    for s in range(rows):       # against the oracle, which follows the pass's routing
+        forced = np.ascontiguousarray(tr["topk"][:, s:s + 1].transpose(1, 0, 2))
+        want, od = seqs[s].extend([int(toks[s])], numerics=orc.DEVICE_LIKE | g.fp16_weight_mask(rows, rows), trace=("topk", "margin"), force_topk=forced)
+        routing_flips(tr["topk"][:, s:s + 1], od["topk"], od["margin"], f"slot {s}")
+        assert_close(got[s], want, f"exchanged pass, slot {s}")
     if rows > 8:
-        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))     # same kernels, same work per pair
-    else:
-        # passes of at most 8 rows add the expert rows while staging the next projection when the experts are local,
-        # and in a row kernel when they are exchanged: the same sums to rounding
-        for s in range(rows):
-            assert_close(got[s], want[s], f"row {s}", tol=1e-3)
+        # from 9 rows the exchanged pass runs the kernels of the plain pass on the same work per pair: bit for bit
+        plain = pkg.Graph(model, n_kv=48, max_tokens=32, slots=rows, use_cuda_graph=False)
+        fill(plain, cfg, rows, 100)
+        want = plain.decode_rows(list(range(rows)), toks)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
     # the replayed (captured) step exchanges too
     g2 = pkg.Graph(model, n_kv=48, max_tokens=32, slots=rows, use_cuda_graph=True)
     fill(g2, cfg, rows, 100)
