@@ -280,11 +280,17 @@ def speculative_decode(pkg, model, cfg, torch, batch, prompt_len, n_out, depths=
         gp.use_slot(s)
         lg, _ = gp.forward(prompts[s])
         firsts.append(int(np.argmax(lg)))
+    # every sequence's plain greedy ids, stepped alone (the arithmetic of a verify pass's rows)
+    cks = []
+    for s in range(batch):
+        gp.use_slot(s); cks.append(gp.checkpoint())
+    plain_ids = [[firsts[s]] + gp.generate_greedy([s], [firsts[s]], n_out - 1)[:, 0].tolist() for s in range(batch)]
+    for s in range(batch):
+        gp.use_slot(s); gp.restore(cks[s]); gp.checkpoint_free(cks[s])
     torch.cuda.synchronize(); t0 = time.perf_counter()
-    plain = gp.generate_greedy(list(range(batch)), firsts, n_out - 1)
+    gp.generate_greedy(list(range(batch)), firsts, n_out - 1)
     torch.cuda.synchronize()
     plain_ms = (time.perf_counter() - t0) / (n_out - 1) * 1e3        # one batched greedy step
-    plain_ids = [[firsts[s]] + plain[:, s].tolist() for s in range(batch)]
     gp.destroy()
     out = {"batch": batch, "prompt_tokens": prompt_len, "output_tokens": n_out, "plain_batched_step_ms": round(plain_ms, 3), "depths": {}}
     for depth in depths:
@@ -423,7 +429,7 @@ def main():
         rng_b = np.random.default_rng(7)   # the contexts and first tokens of batched_decode (rank 0)
         ctx = rng_b.integers(8192, 32769, args.slots)
         for s_ in range(args.slots):
-            gb.use_slot(s_); gb.set_past(int(ctx[s_]))
+            gb.use_slot(s_); gb.synth_context(int(ctx[s_]), seed=1000 + s_)
         sl = list(range(args.slots))
         # distinct random first tokens: identical rows would all select the same ten experts
         out = gb.generate_greedy(sl, rng_b.integers(0, cfg["vocab"], args.slots).astype(np.int32), 2)

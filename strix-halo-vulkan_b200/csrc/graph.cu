@@ -173,6 +173,12 @@ static int gemm_tile_rows(int M, int N) {
   if (((N + 127) / 128) * ((M + tn - 1) / tn) < 48) return 0;
   return tn;
 }
+// Router logits of passes of this many rows and more come from the column-tiled mma kernel (Q8_0 weights as
+// fp16(d * q), the reference's many-row router arithmetic: llm_gemm MODE 2), below it from per-row dot products
+constexpr int ROUTER_MMA_FROM = 16;
+// Fused passes (at most 8 rows) of this many rows and more finish the MoE block's rows in one row kernel; with fewer
+// rows every CTA of the next projection forms them while it stages (each staged row costs every CTA a trip to L2)
+constexpr int COMBINE_ROWS_FROM = 4;
 static bool pass_uses_gemm(int M, int H) { return !(M <= QG_FUSED_ROWS && H <= QG_COMBINE_MAX_K) && M >= 16; }
 static bool pass_moe_gemm(const b200_config& c, const LayerW& L, int M, int H) {
   return pass_uses_gemm(M, H) && (int64_t)M * c.n_expert_used >= 32 * (int64_t)c.n_expert && L.gate_exps.type == L.gate_sh.type && L.down_exps.type == L.down_sh.type;
@@ -193,7 +199,7 @@ uint32_t Graph::fp16_weight_mask(int M, int n_logit_rows) const {
   if (gemm_tile_rows(M, 2 * qw)) mask |= B200_W16_ATTN_Q;
   if (gemm_tile_rows(M, kvw)) mask |= B200_W16_ATTN_K | B200_W16_ATTN_V;
   for (const LayerW& L : m->layers) {
-    if (M >= 64 && L.router.type == T_Q8_0) mask |= B200_W16_ROUTER;
+    if (M >= ROUTER_MMA_FROM && L.router.type == T_Q8_0) mask |= B200_W16_ROUTER;
     if (pass_moe_gemm(c, L, M, H)) mask |= B200_W16_EXPERTS | B200_W16_SHARED;
   }
   if (n_logit_rows == M && gemm_tile_rows(M, c.vocab)) mask |= B200_W16_HEAD;
@@ -395,7 +401,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
     // rows (below that the column-tiled kernel, which streams each expert's weights in whole tiles, is faster)
     const bool moe_gemm = pass_moe_gemm(c, L, M, H) && !epx;
     r.gprob = moe_gemm ? gprob : nullptr;
-    if (use_gemm && M >= 64 && L.router.type == T_Q8_0) {
+    if (use_gemm && M >= ROUTER_MMA_FROM && L.router.type == T_Q8_0) {
       // many rows: the router logits are one more tensor-core GEMM (the reference's prefill router is an fp16
       // GEMM too: llm_gemm MODE 2 + llm_moe_route), selection and work list in a kernel of their own
       QGemmParams g{};
@@ -479,7 +485,17 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       B200_TRY(launch_qgemv(L.down_exps.type, PRO_F16, EPI_STORE, false, true, q, ne, pdl(), st));
     }
     }
-    if (r.defer) pending = true;
+    if (r.defer && M >= COMBINE_ROWS_FROM) {
+      // the rows are finished once, by the arithmetic the next projection's staging would use (same sums in the
+      // same order, so the rows are the single-row pass's bit for bit), and the consumers read fp16 rows
+      const DTensor& next_norm = f.draft ? L.head_norm : (l + 1 < c.n_layer ? m->layers[l + 1].attn_norm : m->output_norm);
+      QGemvParams cp{};
+      cp.K = H; cp.M = M; cp.xcols = 1; cp.hsrc = hc; cp.gamma = (const float*)next_norm.data; cp.xn_out = xn16; cp.eps = c.eps;
+      cp.down = down; cp.topk_w = comb_w; cp.used = comb_used; cp.h_out = hc == hbuf[0] ? hbuf[1] : hbuf[0];
+      B200_TRY(launch_combine_rows(cp, pdl(), st));
+      hc = cp.h_out;
+      xn_valid = true;
+    } else if (r.defer) pending = true;
     else {
       const DTensor& next_norm = f.draft ? L.head_norm : (l + 1 < c.n_layer ? m->layers[l + 1].attn_norm : m->output_norm);
       TailParams tp = row_tail(2, next_norm);
@@ -488,7 +504,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       xn_valid = fused;
     }
     if (o.trace) {
-      if (fused && pending) trace_layer = l;
+      if (pending) trace_layer = l;
       else B200_CUDA(cudaMemcpyAsync(tr_out + (size_t)l * MR * H, hc, (size_t)M * H * sizeof(float), cudaMemcpyDeviceToDevice, st));
       B200_CUDA(cudaMemcpyAsync(tr_topk + (size_t)l * MR * used, topk, (size_t)M * used * sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
       B200_CUDA(cudaMemcpyAsync(tr_w + (size_t)l * MR * slots1, topk_w, (size_t)M * slots1 * sizeof(float), cudaMemcpyDeviceToDevice, st));

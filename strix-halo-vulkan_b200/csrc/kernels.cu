@@ -609,6 +609,25 @@ int launch_row_tail(const TailParams& tp, bool pdl, cudaStream_t st) {
   return launch_k(row_tail_kernel, dim3(tp.M), dim3(QG_THREADS), 0, pdl, st, tp);
 }
 
+// The MoE block's rows of a fused pass finished once instead of in every consumer CTA's staging: row n = residual +
+// the expert partial rows, then the next RMSNorm, by the very function the projection kernels stage with (so the
+// values are the ones a single-row pass forms in its next projection, bit for bit). grid M, block QG_THREADS.
+__global__ void __launch_bounds__(QG_THREADS) combine_rows_kernel(QGemvParams p) {
+  __shared__ __align__(16) uint8_t xs[2 * QG_COMBINE_MAX_K + 16 * (QG_COMBINE_MAX_K / 64) + 128];
+  __shared__ __align__(16) __half sxs[2 * (QG_COMBINE_MAX_K / 32)];
+  __shared__ float scratch[4 * QG_WARPS];
+  __shared__ int xrows[1];
+  pdl_wait();
+  pdl_launch();
+  if (threadIdx.x == 0) xrows[0] = blockIdx.x;
+  __syncthreads();
+  stage_x_combine(p, xs, sxs, scratch, 1, xrows, qg_xstride(p.K), true);
+}
+int launch_combine_rows(const QGemvParams& p, bool pdl, cudaStream_t st) {
+  if (p.K > QG_COMBINE_MAX_K || p.K % 256 || p.used < 0 || p.used > 32 || p.h_out == nullptr || p.h_out == p.hsrc || p.xn_out == nullptr) { set_error("combine_rows: outside its limits"); return EINVAL_; }
+  return launch_k(combine_rows_kernel, dim3(p.M), dim3(QG_THREADS), 0, pdl, st, p);
+}
+
 // Draft seed input: xcat[n] = fp16(rms(embd[n], enorm)) | fp16(rms(h_prev[n], hnorm))  (llm/mtp.go:352-384)
 __global__ void __launch_bounds__(QG_THREADS) concat_norm_kernel(const float* e, const float* hs, const float* enorm, const float* hnorm, float eps, int H, __half* xcat) {
   __shared__ float scratch[2 * QG_WARPS];
@@ -1344,6 +1363,7 @@ int launch_dn_scan(const DnStepParams& p, int M, int max_n, bool pdl, cudaStream
 
 int launch_dn_step(const DnStepParams& p, bool pdl, cudaStream_t st) {
   if (p.D != 128 || p.conv != 4) { set_error("dn_step: head dim must be 128 and conv kernel 4"); return EINVAL_; }
+  // (passes of at most 8 sequences stay on dn_step_kernel: they give every row the single-row pass's bits)
   if (p.n_seq >= 16) return launch_k(dn_head_kernel, dim3(p.Hv, p.n_seq), dim3(512), 0, pdl, st, p);
   return launch_k(dn_step_kernel, dim3(p.Hv * 4, p.n_seq), dim3(128), 0, pdl, st, p);
 }

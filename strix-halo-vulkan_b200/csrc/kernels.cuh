@@ -41,6 +41,8 @@ int launch_moe_down1(uint32_t type, const MoeDown1Params& p, int rows, bool pdl,
 int moe_down1_split(int used, int K);
 int qgemv_groups(int K, int N);
 int launch_row_tail(const TailParams& tp, bool pdl, cudaStream_t st);
+// rows of a fused pass: residual + expert partial rows + next RMSNorm, once per row (hsrc, down, topk_w, used, gamma, h_out, xn_out)
+int launch_combine_rows(const QGemvParams& p, bool pdl, cudaStream_t st);
 int launch_concat_norm(const float* e, const float* hs, const float* enorm, const float* hnorm, float eps, int H, int M, __half* xcat, bool pdl, cudaStream_t st);
 
 int launch_router(const RouterParams& p, bool pdl, cudaStream_t st);
