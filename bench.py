@@ -26,8 +26,8 @@ sys.path.insert(0, ROOT)
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode step, from an ncu capture of the 4-layer prefix
 # (`--profile 1 --layers 4` under ncu's dram byte counters) scaled to 36 DeltaNet + 12 attention layers + head. The
 # figure belongs to the kernels it was captured on: profiles/decode_step_a3b_dram_traffic.md names them, and it is
-# reported only while TRAFFIC_KERNELS still names the step's kernels (None: not re-captured since they changed).
-A3B_DRAM_BYTES_PER_STEP = None
+# re-captured whenever the kernels of the single-row step change (set it to None until then).
+A3B_DRAM_BYTES_PER_STEP = 2500.6e6
 PROMPT = 2048
 METRIC = "decode tok/s at batch 1 (Q4_K hybrid MoE, 80B-A3B shape)"
 

@@ -61,22 +61,35 @@ __global__ void __launch_bounds__(512) ep_dispatch_kernel(EpParams p) {
   }
 }
 
-// Combine barrier: the down projections of every rank have stored the pairs of this rank's rows into its
-// `down` buffer before their kernel ended; lane q raises this rank's flag at rank q and waits for rank q's
-// flag here. grid 1, block 32.
-__global__ void __launch_bounds__(32) ep_barrier_kernel(EpParams p) {
-  pdl_wait();
+// Combine: CTA i copies the output row of the i-th pair this rank computed into the `down` buffer of the rank
+// that owns the pair's row (16-byte stores: a row crosses NVLink as whole sectors). The last CTA to finish raises
+// this rank's flag at every rank and waits for theirs: when it returns, all pairs of this rank's rows have landed.
+// grid: an upper bound of the pair count, block 256.
+__global__ void __launch_bounds__(256) ep_combine_kernel(EpParams p) {
+  __shared__ int last;
+  pdl_wait();   // the down projections
   pdl_launch();
-  const int q = threadIdx.x;
-  const int e = *reinterpret_cast<volatile int*>(p.epoch) + 1;
-  __syncwarp();
-  __threadfence_system();
-  if (q < p.world) {
-    st_release_sys(reinterpret_cast<int*>(p.base[q] + p.off_flags) + p.rank, e);
-    wait_flag(reinterpret_cast<const int*>(p.base[p.rank] + p.off_flags) + q, e, p.limit_ns, p.err);
+  const int i = blockIdx.x, tid = threadIdx.x;
+  const int e = *reinterpret_cast<volatile int*>(p.epoch) + 1;   // read before this CTA takes its ticket
+  if (i < __ldcg(p.n_pairs)) {
+    const int pair = __ldcg(p.cols + i);
+    const int owner = pair / p.pairs_per_rank, local = pair - owner * p.pairs_per_rank;
+    const uint4* src = reinterpret_cast<const uint4*>(p.y_local + (size_t)pair * p.H);
+    uint4* dst = reinterpret_cast<uint4*>(p.base[owner] + p.off_down) + (size_t)local * (p.H / 4);
+    for (int k = tid; k < p.H / 4; k += 256) dst[k] = __ldcg(src + k);
   }
-  __syncwarp();
-  if (q == 0) { *p.epoch = e; __threadfence(); }
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) last = atomicAdd(p.done, 1) == (int)gridDim.x - 1;
+  __syncthreads();
+  if (!last) return;
+  __threadfence_system();
+  if (tid < p.world) {
+    st_release_sys(reinterpret_cast<int*>(p.base[tid] + p.off_flags) + p.rank, e);
+    wait_flag(reinterpret_cast<const int*>(p.base[p.rank] + p.off_flags) + tid, e, p.limit_ns, p.err);
+  }
+  __syncthreads();
+  if (tid == 0) { *p.done = 0; *p.epoch = e; __threadfence(); }
 }
 
 static int launch_ep(void (*kernel)(EpParams), int grid, int block, const EpParams& p, bool pdl, cudaStream_t st) {
@@ -90,7 +103,7 @@ static int launch_ep(void (*kernel)(EpParams), int grid, int block, const EpPara
   return OK;
 }
 int launch_ep_dispatch(const EpParams& p, bool pdl, cudaStream_t st) { return launch_ep(ep_dispatch_kernel, p.world, 512, p, pdl, st); }
-int launch_ep_barrier(const EpParams& p, bool pdl, cudaStream_t st) { return launch_ep(ep_barrier_kernel, 1, 32, p, pdl, st); }
+int launch_ep_combine(const EpParams& p, int max_pairs, bool pdl, cudaStream_t st) { return launch_ep(ep_combine_kernel, max_pairs, 256, p, pdl, st); }
 
 // ---- the graph's side -----------------------------------------------------------------------
 // One device allocation per rank holds everything peers write: flags, the gathered rows and routing, and
@@ -115,7 +128,7 @@ int Graph::ep_prepare(int rank, int world) {
   B200_CUDA(cudaMemset(p, 0, ep_arena_bytes));
   allocs.push_back(p);
   ep_arena = (uint8_t*)p;
-  B200_TRY(dalloc(&ep_epoch, 2));
+  B200_TRY(dalloc(&ep_epoch, 4));   // epoch, ticket, pair count
   ep.rank = rank; ep.world = world; ep.epoch = ep_epoch; ep.done = ep_epoch + 1; ep.err = err_flag;
   ep.H = c.n_embd; ep.used = c.n_expert_used; ep.limit_ns = 2000000000ll;
   for (int q = 0; q < EP_MAX_RANKS; q++) ep.base[q] = nullptr;

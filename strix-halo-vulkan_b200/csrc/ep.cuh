@@ -12,9 +12,10 @@
 //                gathered buffers (xg, topk_g) and raises its flag there; it then waits for all peers' flags;
 //   2. work list built from the gathered routing, restricted to the experts [r*E/world, (r+1)*E/world) that
 //                this rank owns (plus the shared expert for its own rows);
-//   3. experts   gate/up + SwiGLU, then down: the down projection writes each pair's output row straight
-//                into the `down` buffer of the rank that owns the pair's row;
-//   4. combine   flags again (all pairs of my rows have landed), then the ordinary slot-order sum.
+//   3. experts   gate/up + SwiGLU, then down into local memory;
+//   4. combine   every pair's output row is copied, as whole 16-byte stores, into the `down` buffer of the rank
+//                that owns the pair's row; flags again (all pairs of my rows have landed), then the ordinary
+//                slot-order sum.
 // No load ever reads another GPU's memory: remote data always lands in local HBM first.
 #pragma once
 #include "common.cuh"
@@ -34,9 +35,15 @@ struct EpParams {
   const __half* xn;                  // [rows][H] local normalised rows
   const int32_t* topk;               // [rows][used] local routing
   long long limit_ns;                // how long a wait may last
+  // combine: the down projections' outputs of the pairs this rank computed, [pair id][H] f32 in local memory, the
+  // pair ids in work-list order and their count (written by the work-list kernel)
+  const float* y_local;
+  const int* cols;
+  const int* n_pairs;
+  int pairs_per_rank;                // rows * (used + 1): pair id / pairs_per_rank owns the pair's row
 };
 
 int launch_ep_dispatch(const EpParams& p, bool pdl, cudaStream_t st);
-int launch_ep_barrier(const EpParams& p, bool pdl, cudaStream_t st);
+int launch_ep_combine(const EpParams& p, int max_pairs, bool pdl, cudaStream_t st);
 
 }  // namespace b200

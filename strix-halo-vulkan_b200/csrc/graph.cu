@@ -425,6 +425,7 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       RouterParams w = r;
       w.M = Mg; w.topk = reinterpret_cast<int32_t*>(ep_arena + ep.off_topk); w.entries = entries; w.ecols = entry_cols(Mg);
       w.e_lo = ep.rank * (c.n_expert / ep.world); w.e_hi = w.e_lo + c.n_expert / ep.world; w.sh_lo = ep.rank * M; w.sh_hi = w.sh_lo + M;
+      w.n_pairs = ep_epoch + 2;
       B200_TRY(launch_ep_worklist(w, pdl(), st));
       const int ecx = std::min(std::min(Mg, QG_MAXCOLS), entry_cols(Mg));
       QGemvParams p = base(L.gate_exps, H, c.ffn_expert, reinterpret_cast<const __half*>(ep_arena + ep.off_xg), H);
@@ -435,10 +436,10 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       QGemvParams q = base(L.down_exps, c.ffn_expert, H, act16, c.ffn_expert);
       q.ws = L.down_sh.data; q.expert_stride = (int64_t)H * L.down_exps.stride;
       q.entries = entries; q.n_entries = n_entries; q.cols = cols; q.x_div = 1; q.xcols = ecx; q.M = Mg;
-      q.y = nullptr; q.ldy = H; q.y_rank_rows = M * slots1;
-      for (int i = 0; i < ep.world; i++) q.y_rank[i] = reinterpret_cast<float*>(ep.base[i] + ep.off_down);
+      q.y = down; q.ldy = H;     // local: rows by pair id; the combine kernel carries them to the rows' owners
       B200_TRY(launch_qgemv(L.down_exps.type, PRO_F16, EPI_STORE, false, true, q, ne, pdl(), st));
-      B200_TRY(launch_ep_barrier(e, pdl(), st));
+      e.y_local = down; e.cols = cols; e.n_pairs = ep_epoch + 2; e.pairs_per_rank = M * slots1;
+      B200_TRY(launch_ep_combine(e, M * slots1 + (Mg - M) * used, pdl(), st));
       down_rows = reinterpret_cast<float*>(ep_arena + ep.off_down);
     } else if (moe_gemm) {
       const int avg = M * used / c.n_expert, tne = avg <= 40 ? 64 : 128, tie = tne == 64 ? 0 : 1;

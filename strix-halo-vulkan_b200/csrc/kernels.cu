@@ -282,7 +282,7 @@ __device__ void build_work_list(const RouterParams& p, int* counts, int* offs, i
   const int nshr = sh_hi - sh_lo, nsh = (nshr + EC - 1) / EC;
   for (int i = tid; i < nsh; i += 256)
     if (eoff[nE] + i < p.max_entries) p.entries[eoff[nE] + i] = make_int4(-1, offs[nE] + EC * i, min(EC, nshr - EC * i), 0);
-  if (tid == 0) *p.n_entries = min(eoff[nE] + nsh, p.max_entries);
+  if (tid == 0) { *p.n_entries = min(eoff[nE] + nsh, p.max_entries); if (p.n_pairs != nullptr) *p.n_pairs = offs[nE] + nshr; }
   __syncthreads();
   for (int i = tid; i <= nE; i += 256) counts[i] = 0;
   __syncthreads();

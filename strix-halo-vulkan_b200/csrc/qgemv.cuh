@@ -90,10 +90,6 @@ struct QGemvParams {
   float* y;                  // STORE / RESID: float [.][ldy]
   int64_t ldy;
   __half* y16;               // SWIGLU: half [.][ldy]
-  // expert parallelism, STORE epilogue of the grouped kernel: output row r belongs to rank r / y_rank_rows and
-  // is written as row r % y_rank_rows of that rank's buffer (a peer store over NVLink); null entries: local y
-  float* y_rank[8];
-  int y_rank_rows;
 };
 
 __host__ __device__ inline int qg_xstride(int K) {
@@ -823,15 +819,7 @@ __global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 
           if constexpr (DUAL) v2 += rb[(size_t)(QG_WARPS + l2 * wpt + w) * 128 + rc];
         }
         const int64_t orow = (!GROUPED && p.row_ids != nullptr) ? col_off + c : col_rows[c];
-        if constexpr (EPI == EPI_STORE) {
-          if (GROUPED && p.y_rank_rows > 0) {
-            const int owner = (int)(orow / p.y_rank_rows);
-            p.y_rank[owner][(orow - (int64_t)owner * p.y_rank_rows) * p.ldy + grow] = v;
-          } else {
-            p.y[orow * p.ldy + grow] = v;
-          }
-          sq += v * v;
-        }
+        if constexpr (EPI == EPI_STORE) { p.y[orow * p.ldy + grow] = v; sq += v * v; }
         else if constexpr (EPI == EPI_RESID) { const float nv = p.y[orow * p.ldy + grow] + v; p.y[orow * p.ldy + grow] = nv; sq += nv * nv; }
         else {  // SwiGLU of (gate, up) rounded to fp16 (reference: shaders/llm_moe_gemv.comp:777-781)
           float sw = v * sigmoid_acc(v) * v2;

@@ -26,6 +26,7 @@ struct RouterParams {
   // expert parallelism: the work list keeps the experts [e_lo, e_hi) only (e_hi == 0: all) and makes shared-expert
   // entries for the rows [sh_lo, sh_hi) only (sh_hi == 0: all rows)
   int e_lo, e_hi, sh_lo, sh_hi;
+  int* n_pairs;        // optional: the number of (row, slot) pairs in cols (routed pairs of the kept experts + shared rows)
   int64_t* distinct;   // optional: += the number of experts this pass's work list touches (for the byte count of a step)
   Timeline tl;
 };
