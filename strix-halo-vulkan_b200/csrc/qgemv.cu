@@ -4,6 +4,9 @@
 
 namespace b200 {
 
+// max_entries: the work-list length the grid is sized for. The kernel's CTAs walk a longer list with stride, so a
+// caller that knows its list to be short against the bound (expert-parallel passes: a rank computes only its own
+// experts' pairs) passes the length it expects and keeps the device full.
 template <int TYPE, int PRO, int EPI, bool DUAL, bool GROUPED>
 static int launch_one(const QGemvParams& p, int max_entries, bool pdl, cudaStream_t st) {
   auto kernel = qgemv_kernel<TYPE, PRO, EPI, DUAL, GROUPED>;

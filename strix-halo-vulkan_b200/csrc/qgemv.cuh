@@ -651,8 +651,14 @@ __global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 
   }
   __syncthreads();
 
+  // Grouped launches over a work list walk its entries with stride gridDim.y (the host sizes the grid for the number
+  // of entries it expects, not for the largest possible list); everything else runs the body once. The weight ring's
+  // stage counter and the reduction buffer's parity carry over from one entry to the next.
+  int ey = blockIdx.y, it = 0, buf = 0;
+  for (bool more = true; more;) {
+  more = false;
   const uint8_t *wa = nullptr, *wb = nullptr;
-  int ncols = 0, col_off = 0;
+  int ncols = 0, col_off = 0, n_ent = 0;
   bool active = true, x_copied = false;
   if constexpr (GROUPED) {
     pdl_wait();  // the entries (or the logits) are written by the router kernel
@@ -683,8 +689,9 @@ __global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 
         }
       }
     } else {
-      active = (int)blockIdx.y < *p.n_entries;
-      if (active) e = p.entries[blockIdx.y];
+      n_ent = *p.n_entries;
+      active = ey < n_ent;
+      if (active) e = p.entries[ey];
     }
     if (active) {
       col_off = e.y; ncols = e.z;
@@ -724,7 +731,7 @@ __global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 
   };
   if (active && tid == 0) {
     int grp = blockIdx.x;
-    for (int s = 0; s < NS && grp < ngroups; s++, grp += gridDim.x) issue_group(grp, s);
+    for (int k = 0; k < NS && grp < ngroups; k++, grp += gridDim.x) issue_group(grp, (it + k) % NS);
   }
   // Single-row combine: the norm weights and the residual row (final four kernels back) are fetched before the
   // wait, so that only the partial rows of the down projection are asked of L2 once it is over.
@@ -764,7 +771,6 @@ __global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 
     const bool live = g < ncols;
     const uint8_t* xrow = xs + (size_t)(live ? g : 0) * xstride;
     const __half* sxrow = sxs + (size_t)((t & 1) * p.xcols + (live ? g : 0)) * (K / 32);
-    int buf = 0, it = 0;
     for (int grp = blockIdx.x; grp < ngroups; grp += gridDim.x, it++) {
       const int s = it % NS;
       if (!mbar_wait(&full_bar[s], (uint32_t)((it / NS) & 1))) {
@@ -843,6 +849,14 @@ __global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 
       }
       buf ^= 1;
     }
+  }
+  if constexpr (GROUPED) {
+    if (!p.route_here) {
+      ey += (int)gridDim.y;
+      more = ey < n_ent;
+      if (more) __syncthreads();   // every warp is done with the staged activations of this entry
+    }
+  }
   }
   tl_mark(p.tl, 4);
 }
