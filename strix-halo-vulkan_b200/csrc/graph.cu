@@ -157,7 +157,7 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
 
 // Columns per work-list entry. A pass of some tens of rows leaves one or two rows per touched expert: entries of
 // four columns halve the activation staging of the expert kernels, which then fit three to an SM.
-int Graph::entry_cols(int M) { return M >= 32 && M <= 128 ? 4 : 8; }
+int Graph::entry_cols(int M) { return M >= 16 && M <= 128 ? 4 : 8; }
 
 int Graph::max_entries_for(int M) const {
   const int used = m->c.n_expert_used, ec = entry_cols(M);
@@ -428,19 +428,16 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       w.n_pairs = ep_epoch + 2;
       B200_TRY(launch_ep_worklist(w, pdl(), st));
       const int ecx = std::min(std::min(Mg, QG_MAXCOLS), entry_cols(Mg));
-      // this rank's share of the pairs, a quarter more for uneven routing, and its shared-expert entries: what the
-      // grid is sized for (longer lists are walked with stride)
-      const int ne_ep = std::min(ne, (Mg * used / ep.world) * 5 / 4 / std::max(1, entry_cols(Mg) / 2) + (M + entry_cols(Mg) - 1) / entry_cols(Mg) + 8);
       QGemvParams p = base(L.gate_exps, H, c.ffn_expert, reinterpret_cast<const __half*>(ep_arena + ep.off_xg), H);
       p.w2[0] = L.up_exps.data; p.ws = L.gate_sh.data; p.ws2 = L.up_sh.data; p.expert_stride = (int64_t)c.ffn_expert * L.gate_exps.stride;
       p.entries = entries; p.n_entries = n_entries; p.cols = cols; p.x_div = slots1; p.xcols = ecx; p.M = Mg;
       p.y16 = act16; p.ldy = c.ffn_expert;
-      B200_TRY(launch_qgemv(L.gate_exps.type, PRO_F16, EPI_SWIGLU, true, true, p, ne_ep, pdl(), st));
+      B200_TRY(launch_qgemv(L.gate_exps.type, PRO_F16, EPI_SWIGLU, true, true, p, ne, pdl(), st));
       QGemvParams q = base(L.down_exps, c.ffn_expert, H, act16, c.ffn_expert);
       q.ws = L.down_sh.data; q.expert_stride = (int64_t)H * L.down_exps.stride;
       q.entries = entries; q.n_entries = n_entries; q.cols = cols; q.x_div = 1; q.xcols = ecx; q.M = Mg;
       q.y = down; q.ldy = H;     // local: rows by pair id; the combine kernel carries them to the rows' owners
-      B200_TRY(launch_qgemv(L.down_exps.type, PRO_F16, EPI_STORE, false, true, q, ne_ep, pdl(), st));
+      B200_TRY(launch_qgemv(L.down_exps.type, PRO_F16, EPI_STORE, false, true, q, ne, pdl(), st));
       e.y_local = down; e.cols = cols; e.n_pairs = ep_epoch + 2; e.pairs_per_rank = M * slots1;
       B200_TRY(launch_ep_combine(e, M * slots1 + (Mg - M) * used, pdl(), st));
       down_rows = reinterpret_cast<float*>(ep_arena + ep.off_down);

@@ -4,9 +4,8 @@
 
 namespace b200 {
 
-// max_entries: the work-list length the grid is sized for. The kernel's CTAs walk a longer list with stride, so a
-// caller that knows its list to be short against the bound (expert-parallel passes: a rank computes only its own
-// experts' pairs) passes the length it expects and keeps the device full.
+// max_entries: grid.y of a launch whose CTAs route for themselves (one per row and slot). Launches over a work list
+// ignore it: their grid is the device's resident CTAs, which share the list evenly whatever its length.
 template <int TYPE, int PRO, int EPI, bool DUAL, bool GROUPED>
 static int launch_one(const QGemvParams& p, int max_entries, bool pdl, cudaStream_t st) {
   auto kernel = qgemv_kernel<TYPE, PRO, EPI, DUAL, GROUPED>;
@@ -26,30 +25,37 @@ static int launch_one(const QGemvParams& p, int max_entries, bool pdl, cudaStrea
   const size_t fixed = qg_fixed_smem(p.K, p.xcols, DUAL), stage = qg_stage_bytes(p.K, p.stride, DUAL);
   const size_t budgets[4] = {0, 220 * 1024, 110 * 1024, 72 * 1024};
   if (fixed + stage > budgets[1]) { set_error("qgemv: row length too large for shared memory"); return ECAPACITY; }
-  int occ = 1, rounds = 1, gx = 1;
-  for (int o = 3; o >= 1; o--) {
-    if (o == 3 && !GROUPED && TYPE != T_Q6_K) continue;  // the other plain kernels are compiled for two CTAs per SM
-    int cap = g_sm_count * o / (ny * nz);
-    if (cap < 1) cap = 1;
-    // every CTA walks the same number of groups (a ragged last round leaves most SMs idle)
-    rounds = (groups + cap - 1) / cap;
-    gx = (groups + rounds - 1) / rounds;
-    occ = o;
-    // more work-list entries than SMs (a many-row pass over the experts): two CTAs per SM with one stage each
-    // beat one CTA with a deep ring - the walk is bound by the latencies inside a CTA, not by the copies
-    const int need = (GROUPED && ny > g_sm_count) ? 1 : std::min(rounds, 2);
-    if (fixed + (size_t)need * stage <= budgets[o]) break;
+  int occ = 1, rounds = 1, gx = 1, ns = 1;
+  dim3 grid;
+  if (GROUPED && !p.route_here) {
+    // A work list: persistent CTAs, each with an equal contiguous share of the list's (entry, group) units. The
+    // walk is bound by the instructions that turn quants into fragments, so the resident warps count for more than
+    // the ring's depth: three CTAs per SM with a single stage beat two with two stages when three fit.
+    occ = fixed + stage <= budgets[3] ? 3 : fixed + stage <= budgets[2] ? 2 : 1;
+    ns = (int)((budgets[occ] - fixed) / stage);
+    if (ns > QG_MAX_STAGES) ns = QG_MAX_STAGES;
+    grid = dim3(g_sm_count * occ, 1, 1);
+  } else {
+    for (int o = 3; o >= 1; o--) {
+      if (o == 3 && !GROUPED && TYPE != T_Q6_K) continue;  // the other plain kernels are compiled for two CTAs per SM
+      int cap = g_sm_count * o / (ny * nz);
+      if (cap < 1) cap = 1;
+      // every CTA walks the same number of groups (a ragged last round leaves most SMs idle)
+      rounds = (groups + cap - 1) / cap;
+      gx = (groups + rounds - 1) / rounds;
+      occ = o;
+      if (fixed + (size_t)std::min(rounds, 2) * stage <= budgets[o]) break;
+    }
+    ns = (int)((budgets[occ] - fixed) / stage);
+    if (ns > QG_MAX_STAGES) ns = QG_MAX_STAGES;
+    if (ns > rounds) ns = rounds;
+    if (ns < 1) ns = 1;
+    grid = dim3(gx, ny, nz);
   }
-  const int per_cta = rounds;
-  int ns = (int)((budgets[occ] - fixed) / stage);
-  if (ns > QG_MAX_STAGES) ns = QG_MAX_STAGES;
-  if (ns > per_cta) ns = per_cta;
-  if (ns < 1) ns = 1;
   const size_t smem = fixed + (size_t)ns * stage;
   B200_ONCE_PER_DEVICE(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(220 * 1024 + 4096)));
   QGemvParams pp = p;
   pp.nstage = ns;
-  dim3 grid(gx, ny, nz);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid; cfg.blockDim = dim3(QG_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute attr[1];

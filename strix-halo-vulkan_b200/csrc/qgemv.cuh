@@ -612,8 +612,9 @@ __device__ __forceinline__ void stage_x_combine(const QGemvParams& p, uint8_t* x
 }
 
 // ---- the kernel ----------------------------------------------------------------------------
-// grid.x: persistent CTAs walking the row-tile groups; grid.y: expert entry (grouped) or 0;
-// grid.z: column tile of 8 activation rows (plain mode).
+// grid.x: persistent CTAs walking the row-tile groups; grid.y: (row, slot) of a grouped launch that
+// routes for itself, else 0; grid.z: column tile of 8 activation rows (plain mode). A grouped launch over
+// a work list is one row of CTAs that share the list's (entry, group) units evenly.
 //
 // Weights reach the SM as whole tiles (16 consecutive rows are one contiguous run of the
 // checkpoint's own blocks) through cp.async.bulk into a ring of shared-memory stages, each
@@ -651,18 +652,19 @@ __global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 
   }
   __syncthreads();
 
-  // Grouped launches over a work list walk its entries with stride gridDim.y (the host sizes the grid for the number
-  // of entries it expects, not for the largest possible list); everything else runs the body once. The weight ring's
-  // stage counter and the reduction buffer's parity carry over from one entry to the next.
-  int ey = blockIdx.y, it = 0, buf = 0;
-  for (bool more = true; more;) {
-  more = false;
+  // What this CTA walks is a sequence of units, each one row-tile group of one weight matrix. Plain launches and
+  // launches that route for themselves take the groups blockIdx.x, blockIdx.x + gridDim.x, ... of the one matrix they
+  // are given. Launches over a work list cut the whole list, entries * groups units, into one contiguous run per CTA:
+  // every CTA gets the same share whatever the list's length (known only on the device), a run stages the activation
+  // rows of an entry once, and the weight ring runs ahead across the entries' boundaries.
   const uint8_t *wa = nullptr, *wb = nullptr;
-  int ncols = 0, col_off = 0, n_ent = 0;
+  int ncols = 0, col_off = 0, n_units = 0;
+  long long u0 = 0;
   bool active = true, x_copied = false;
+  bool flat = false;
+  auto own_units = [&]() { return (int)blockIdx.x < ngroups ? (ngroups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0; };
   if constexpr (GROUPED) {
     pdl_wait();  // the entries (or the logits) are written by the router kernel
-    int4 e;
     if (p.route_here) {
       // blockIdx.y = row * (used + 1) + slot: every row of the pass is routed and computed on its own, exactly as a
       // single-row pass would do it, so a pass of several rows gives each row the single-row result bit for bit
@@ -680,7 +682,6 @@ __global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 
       }
       x_copied = PRO == PRO_F16;  // for every thread alike: the barrier below covers the copy
       __syncthreads();
-      e = make_int4(route_expert, y, 1, 0);
       if (writer && p.route.entries != nullptr) {  // the row's part of the work list: one entry per slot, the shared expert last
         if (tid < used) { p.route.entries[row * slots1 + tid] = make_int4(route_topk[tid], row * slots1 + tid, 1, 0); p.route.cols[row * slots1 + tid] = row * slots1 + tid; }
         if (tid == used) {
@@ -688,23 +689,27 @@ __global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 
           if (row == 0) *p.route.n_entries = p.route.M * slots1;
         }
       }
+      if (active) {
+        const int ex = route_expert;
+        col_off = y; ncols = 1;
+        wa = ex >= 0 ? p.w[0] + (size_t)ex * p.expert_stride : p.ws;
+        if constexpr (DUAL) wb = ex >= 0 ? p.w2[0] + (size_t)ex * p.expert_stride : p.ws2;
+        n_units = own_units();
+      }
     } else {
-      n_ent = *p.n_entries;
-      active = ey < n_ent;
-      if (active) e = p.entries[ey];
-    }
-    if (active) {
-      col_off = e.y; ncols = e.z;
-      wa = e.x >= 0 ? p.w[0] + (size_t)e.x * p.expert_stride : p.ws;
-      if constexpr (DUAL) wb = e.x >= 0 ? p.w2[0] + (size_t)e.x * p.expert_stride : p.ws2;
+      flat = true;
+      const long long U = (long long)*p.n_entries * ngroups, C = (long long)gridDim.x * gridDim.y, c = (long long)blockIdx.y * gridDim.x + blockIdx.x;
+      u0 = c * U / C;
+      n_units = (int)((c + 1) * U / C - u0);
     }
   } else {
     ncols = p.M - (int)blockIdx.z * QG_MAXCOLS;
     if (ncols > QG_MAXCOLS) ncols = QG_MAXCOLS;
     col_off = (int)blockIdx.z * QG_MAXCOLS;
+    n_units = own_units();
   }
   // thread 0 is the producer: one bulk copy per tile (and per tensor when DUAL)
-  auto issue_group = [&](int grp, int s) {
+  auto issue_group = [&](int grp, int s, const uint8_t* ga, const uint8_t* gb) {
     uint32_t total = 0;
     for (int l = 0; l < tpc; l++) {
       const int tile = grp * tpc + l;
@@ -715,7 +720,7 @@ __global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 
       const int tile = grp * tpc + l;
       if (tile >= tiles) continue;
       const uint32_t bytes = (uint32_t)(min(16, p.N - tile * 16) * p.stride);
-      const uint8_t *base = wa, *base2 = wb;
+      const uint8_t *base = ga, *base2 = gb;
       int seg_r0 = 0;
       if constexpr (!GROUPED) {
         int sg = 0;
@@ -729,10 +734,22 @@ __global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 
       if constexpr (DUAL) bulk_copy_g2s(dst + tile_bytes, base2 + (size_t)(tile * 16 - seg_r0) * p.stride, bytes, &full_bar[s]);
     }
   };
-  if (active && tid == 0) {
-    int grp = blockIdx.x;
-    for (int k = 0; k < NS && grp < ngroups; k++, grp += gridDim.x) issue_group(grp, (it + k) % NS);
-  }
+  // unit j of this CTA goes to ring stage j % NS
+  auto issue_unit = [&](int j) {
+    if (flat) {
+      const long long u = u0 + j;
+      const int en = (int)(u / ngroups), grp = (int)(u - (long long)en * ngroups);
+      const int ex = p.entries[en].x;
+      const uint8_t* ga = ex >= 0 ? p.w[0] + (size_t)ex * p.expert_stride : p.ws;
+      const uint8_t* gb = nullptr;
+      if constexpr (DUAL) gb = ex >= 0 ? p.w2[0] + (size_t)ex * p.expert_stride : p.ws2;
+      issue_group(grp, j % NS, ga, gb);
+    } else {
+      issue_group((int)blockIdx.x + j * (int)gridDim.x, j % NS, wa, wb);
+    }
+  };
+  if (tid == 0)
+    for (int k = 0; k < NS && k < n_units; k++) issue_unit(k);
   // Single-row combine: the norm weights and the residual row (final four kernels back) are fetched before the
   // wait, so that only the partial rows of the down projection are asked of L2 once it is over.
   float4 pre_g[2], pre_h[2];
@@ -753,7 +770,11 @@ __global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 
   pdl_launch();
   tl_mark(p.tl, 1);
 
-  if (active) {
+  bool live = false;
+  const uint8_t* xrow = xs;
+  const __half* sxrow = sxs;
+  // the activation rows of the current entry (or of this launch's column tile) into shared memory
+  auto stage_rows = [&]() {
     if (tid < QG_MAXCOLS) {
       const int c = tid < ncols ? tid : 0;
       int id;
@@ -766,97 +787,101 @@ __global__ void __launch_bounds__(QG_THREADS, (GROUPED || TYPE == T_Q6_K) ? 3 : 
     if constexpr (PRO == PRO_COMBINE) stage_x_combine(p, xs, sxs, scratch, ncols, xrows, xstride, blockIdx.x == 0 && blockIdx.y == 0, pre ? pre_g : nullptr, pre ? pre_h : nullptr);
     else if constexpr (PRO == PRO_NORM) stage_x_norm(p, xs, sxs, scratch, ncols, xrows, xstride, p.xn_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0);
     else stage_x_f16(p.x, p.ldx, K, p.xcols, xs, sxs, ncols, xrows, xstride, x_copied);
-    tl_mark(p.tl, 2);
+    live = g < ncols;
+    xrow = xs + (size_t)(live ? g : 0) * xstride;
+    sxrow = sxs + (size_t)((t & 1) * p.xcols + (live ? g : 0)) * (K / 32);
+  };
+  if (active && !flat) { stage_rows(); tl_mark(p.tl, 2); }
 
-    const bool live = g < ncols;
-    const uint8_t* xrow = xs + (size_t)(live ? g : 0) * xstride;
-    const __half* sxrow = sxs + (size_t)((t & 1) * p.xcols + (live ? g : 0)) * (K / 32);
-    for (int grp = blockIdx.x; grp < ngroups; grp += gridDim.x, it++) {
-      const int s = it % NS;
-      if (!mbar_wait(&full_bar[s], (uint32_t)((it / NS) & 1))) {
-        if (p.err != nullptr && tid == 0) atomicExch(p.err, 1);  // a copy never landed: report and leave
-        return;
+  int cur = -1, buf = 0;
+  for (int it = 0; it < n_units; it++) {
+    int grp;
+    if (flat) {
+      const long long u = u0 + it;
+      const int en = (int)(u / ngroups);
+      grp = (int)(u - (long long)en * ngroups);
+      if (en != cur) {
+        if (cur >= 0) __syncthreads();   // every warp is done with the rows and the row ids of the entry before
+        const int4 e = p.entries[en];
+        col_off = e.y; ncols = e.z; cur = en;
+        stage_rows();
       }
-      if (it == 0) tl_mark(p.tl, 3);
-      float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
-      const int tile = grp * tpc + lt;
-      if (tile < tiles) {
-        int r0 = g, r1 = g + 8;
-        const int nrows = min(16, p.N - tile * 16);
-        if (r0 >= nrows) r0 = nrows - 1;
-        if (r1 >= nrows) r1 = nrows - 1;
-        const uint8_t* tb = stages + (size_t)s * stage_bytes + (size_t)lt * tile_bytes * (DUAL ? 2 : 1);
-        for (int blk = kslice; blk < nb; blk += wpt) {
-          typename RowRegs<TYPE>::type a0, a1;
-          issue_row<TYPE>(a0, tb + (size_t)r0 * p.stride, nb, blk, t);
-          issue_row<TYPE>(a1, tb + (size_t)r1 * p.stride, nb, blk, t);
-          block_accumulate<TYPE>(acc, a0, a1, xrow, sxrow, live, blk, t);
-          if constexpr (DUAL) {
-            issue_row<TYPE>(a0, tb + tile_bytes + (size_t)r0 * p.stride, nb, blk, t);
-            issue_row<TYPE>(a1, tb + tile_bytes + (size_t)r1 * p.stride, nb, blk, t);
-            block_accumulate<TYPE>(acc2, a0, a1, xrow, sxrow, live, blk, t);
-          }
+    } else {
+      grp = (int)blockIdx.x + it * (int)gridDim.x;
+    }
+    const int s = it % NS;
+    if (!mbar_wait(&full_bar[s], (uint32_t)((it / NS) & 1))) {
+      if (p.err != nullptr && tid == 0) atomicExch(p.err, 1);  // a copy never landed: report and leave
+      return;
+    }
+    if (it == 0) tl_mark(p.tl, 3);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
+    const int tile = grp * tpc + lt;
+    if (tile < tiles) {
+      int r0 = g, r1 = g + 8;
+      const int nrows = min(16, p.N - tile * 16);
+      if (r0 >= nrows) r0 = nrows - 1;
+      if (r1 >= nrows) r1 = nrows - 1;
+      const uint8_t* tb = stages + (size_t)s * stage_bytes + (size_t)lt * tile_bytes * (DUAL ? 2 : 1);
+      for (int blk = kslice; blk < nb; blk += wpt) {
+        typename RowRegs<TYPE>::type a0, a1;
+        issue_row<TYPE>(a0, tb + (size_t)r0 * p.stride, nb, blk, t);
+        issue_row<TYPE>(a1, tb + (size_t)r1 * p.stride, nb, blk, t);
+        block_accumulate<TYPE>(acc, a0, a1, xrow, sxrow, live, blk, t);
+        if constexpr (DUAL) {
+          issue_row<TYPE>(a0, tb + tile_bytes + (size_t)r0 * p.stride, nb, blk, t);
+          issue_row<TYPE>(a1, tb + tile_bytes + (size_t)r1 * p.stride, nb, blk, t);
+          block_accumulate<TYPE>(acc2, a0, a1, xrow, sxrow, live, blk, t);
         }
       }
-      // cross-warp reduction in warp order, double-buffered so one barrier per group suffices
-      float* myred = red + (size_t)buf * RED + (size_t)warp * 128;
-      myred[g * 8 + 2 * t] = acc[0]; myred[g * 8 + 2 * t + 1] = acc[1];
-      myred[(g + 8) * 8 + 2 * t] = acc[2]; myred[(g + 8) * 8 + 2 * t + 1] = acc[3];
-      if constexpr (DUAL) {
-        float* r2 = myred + QG_WARPS * 128;
-        r2[g * 8 + 2 * t] = acc2[0]; r2[g * 8 + 2 * t + 1] = acc2[1];
-        r2[(g + 8) * 8 + 2 * t] = acc2[2]; r2[(g + 8) * 8 + 2 * t + 1] = acc2[3];
+    }
+    // cross-warp reduction in warp order, double-buffered so one barrier per group suffices
+    float* myred = red + (size_t)buf * RED + (size_t)warp * 128;
+    myred[g * 8 + 2 * t] = acc[0]; myred[g * 8 + 2 * t + 1] = acc[1];
+    myred[(g + 8) * 8 + 2 * t] = acc[2]; myred[(g + 8) * 8 + 2 * t + 1] = acc[3];
+    if constexpr (DUAL) {
+      float* r2 = myred + QG_WARPS * 128;
+      r2[g * 8 + 2 * t] = acc2[0]; r2[g * 8 + 2 * t + 1] = acc2[1];
+      r2[(g + 8) * 8 + 2 * t] = acc2[2]; r2[(g + 8) * 8 + 2 * t + 1] = acc2[3];
+    }
+    __syncthreads();
+    // every warp is done with stage s: refill it with the unit NS iterations ahead
+    if (tid == 0 && it + NS < n_units) { fence_proxy_async(); issue_unit(it + NS); }
+    const float* rb = red + (size_t)buf * RED;
+    float sq = 0.f;  // this thread's column is tid & 7 in every iteration
+    for (int i = tid; i < tpc * 128; i += QG_THREADS) {
+      const int l2 = i >> 7, rc = i & 127, r = rc >> 3, c = rc & 7;
+      const int grow = (grp * tpc + l2) * 16 + r;
+      if (grow >= p.N || c >= ncols) continue;
+      float v = 0.f, v2 = 0.f;
+      for (int w = 0; w < wpt; w++) {
+        v += rb[(size_t)(l2 * wpt + w) * 128 + rc];
+        if constexpr (DUAL) v2 += rb[(size_t)(QG_WARPS + l2 * wpt + w) * 128 + rc];
       }
-      __syncthreads();
-      // every warp is done with stage s: refill it with the group NS iterations ahead
-      if (tid == 0) {
-        const int next = grp + NS * (int)gridDim.x;
-        if (next < ngroups) { fence_proxy_async(); issue_group(next, s); }
+      const int64_t orow = (!GROUPED && p.row_ids != nullptr) ? col_off + c : col_rows[c];
+      if constexpr (EPI == EPI_STORE) { p.y[orow * p.ldy + grow] = v; sq += v * v; }
+      else if constexpr (EPI == EPI_RESID) { const float nv = p.y[orow * p.ldy + grow] + v; p.y[orow * p.ldy + grow] = nv; sq += nv * nv; }
+      else {  // SwiGLU of (gate, up) rounded to fp16 (reference: shaders/llm_moe_gemv.comp:777-781)
+        float sw = v * sigmoid_acc(v) * v2;
+        p.y16[orow * p.ldy + grow] = __float2half_rn(sw);
       }
-      const float* rb = red + (size_t)buf * RED;
-      float sq = 0.f;  // this thread's column is tid & 7 in every iteration
-      for (int i = tid; i < tpc * 128; i += QG_THREADS) {
-        const int l2 = i >> 7, rc = i & 127, r = rc >> 3, c = rc & 7;
-        const int grow = (grp * tpc + l2) * 16 + r;
-        if (grow >= p.N || c >= ncols) continue;
-        float v = 0.f, v2 = 0.f;
-        for (int w = 0; w < wpt; w++) {
-          v += rb[(size_t)(l2 * wpt + w) * 128 + rc];
-          if constexpr (DUAL) v2 += rb[(size_t)(QG_WARPS + l2 * wpt + w) * 128 + rc];
-        }
-        const int64_t orow = (!GROUPED && p.row_ids != nullptr) ? col_off + c : col_rows[c];
-        if constexpr (EPI == EPI_STORE) { p.y[orow * p.ldy + grow] = v; sq += v * v; }
-        else if constexpr (EPI == EPI_RESID) { const float nv = p.y[orow * p.ldy + grow] + v; p.y[orow * p.ldy + grow] = nv; sq += nv * nv; }
-        else {  // SwiGLU of (gate, up) rounded to fp16 (reference: shaders/llm_moe_gemv.comp:777-781)
-          float sw = v * sigmoid_acc(v) * v2;
-          p.y16[orow * p.ldy + grow] = __float2half_rn(sw);
-        }
-      }
-      if constexpr (EPI != EPI_SWIGLU && !GROUPED) {
-        if (p.ss_out != nullptr) {  // sum of squares of this group's rows per column, in a fixed order
-          sq += __shfl_xor_sync(0xffffffffu, sq, 8);
-          sq += __shfl_xor_sync(0xffffffffu, sq, 16);
-          if (lane < 8) ssq[buf][warp][lane] = sq;
-          __syncthreads();
-          if (tid < ncols) {
-            float t2 = 0.f;
+    }
+    if constexpr (EPI != EPI_SWIGLU && !GROUPED) {
+      if (p.ss_out != nullptr) {  // sum of squares of this group's rows per column, in a fixed order
+        sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+        sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+        if (lane < 8) ssq[buf][warp][lane] = sq;
+        __syncthreads();
+        if (tid < ncols) {
+          float t2 = 0.f;
 #pragma unroll
-            for (int w = 0; w < QG_WARPS; w++) t2 += ssq[buf][w][tid];
-            const int64_t orow = p.row_ids != nullptr ? col_off + tid : col_rows[tid];
-            p.ss_out[orow * SS_LD + grp] = t2;
-          }
+          for (int w = 0; w < QG_WARPS; w++) t2 += ssq[buf][w][tid];
+          const int64_t orow = p.row_ids != nullptr ? col_off + tid : col_rows[tid];
+          p.ss_out[orow * SS_LD + grp] = t2;
         }
       }
-      buf ^= 1;
     }
-  }
-  if constexpr (GROUPED) {
-    if (!p.route_here) {
-      ey += (int)gridDim.y;
-      more = ey < n_ent;
-      if (more) __syncthreads();   // every warp is done with the staged activations of this entry
-    }
-  }
+    buf ^= 1;
   }
   tl_mark(p.tl, 4);
 }
