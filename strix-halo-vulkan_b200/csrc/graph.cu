@@ -86,7 +86,7 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   B200_TRY(dalloc(&r_ticket, (size_t)2 + MR / 8)); B200_TRY(dalloc(&err_flag, 1)); B200_TRY(dalloc(&ss_part, (size_t)MR * SS_LD)); B200_TRY(dalloc(&y16, (size_t)MR * vw));
   B200_TRY(dalloc(&act16, (size_t)MR * slots1 * c.ffn_expert)); B200_TRY(dalloc(&down, (size_t)MR * slots1 * H));
   B200_TRY(dalloc(&logits, (size_t)LR * c.vocab));
-  { B200_TRY(dalloc(&dn_pre, (size_t)c.dn_heads_v * 4 * MR * 292)); B200_TRY(dalloc(&dn_oraw, (size_t)MR * vw)); }
+  { B200_TRY(dalloc(&dn_pre, (size_t)c.dn_heads_v * 4 * MR * 292)); B200_TRY(dalloc(&dn_oraw, (size_t)MR * vw)); B200_TRY(dalloc(&dn_ab, (size_t)MR * 2 * c.dn_heads_v)); }
   { std::vector<float> one(64, 1.f); B200_TRY(dalloc(&ones, one.size())); B200_CUDA(cudaMemcpy(ones, one.data(), one.size() * sizeof(float), cudaMemcpyHostToDevice)); }
   B200_TRY(dalloc(&xperm16, (size_t)MR * used * H)); B200_TRY(dalloc(&gprob, (size_t)c.n_expert)); B200_TRY(dalloc(&n_expert_dev, 1));
   B200_CUDA(cudaMemcpy(n_expert_dev, &c.n_expert, sizeof(int), cudaMemcpyHostToDevice));
@@ -323,8 +323,8 @@ int Graph::enqueue_pass(int M, int n_seq, int n_logit_rows, const PassFlags& f) 
       d.mid = f.spec ? dn_mid[di] : nullptr; d.mid_stride = state_slot_stride; d.mid_seq_stride = mid_seq_stride;
       d.H = H; d.Hk = c.dn_heads_k; d.Hv = c.dn_heads_v; d.D = D; d.conv = c.dn_conv; d.eps = c.eps; d.tl = tl();
       if (!fused && !f.spec && M > n_seq) {  // some sequence is long: state-independent part in parallel, then the scan
-        d.pre = dn_pre; d.pre_rows = MR; d.o_raw = dn_oraw;
-        B200_TRY(launch_dn_scan(d, M, pass_max_n, pdl(), st)); launches += 2;
+        d.pre = dn_pre; d.pre_rows = MR; d.o_raw = dn_oraw; d.ab = dn_ab;
+        B200_TRY(launch_dn_scan(d, M, pass_max_n, pdl(), st)); launches += 3;
       } else {
         B200_TRY(launch_dn_step(d, pdl(), st));
       }

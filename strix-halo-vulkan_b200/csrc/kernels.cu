@@ -970,13 +970,52 @@ constexpr int DN_PACK = 292;   // floats per (CTA id, token): q 128 | k 128 | v 
 constexpr int DN_PRE_TOKENS = 16;
 constexpr int DN_CHUNK_FROM = 64;   // sequences of this many tokens and more run the chunked recurrence, shorter ones the token-by-token scan
 
+// alpha / beta projections of all rows of a pass (llm/deltanet.go:305-318): out[row][o], o = head for alpha, Hv + head
+// for beta. A CTA keeps 16 rows of the normalised input in shared memory and walks the 2*Hv weight rows once for all
+// of them (a warp per weight row, lanes along K), so the weights are read once per 16 tokens instead of once per
+// token and row block. grid ceil(M / 16), block 256, dynamic shared memory 16 * H halves.
+constexpr int DN_AB_ROWS = 16;
+__global__ void __launch_bounds__(256) dn_ab_kernel(DnStepParams p, int M) {
+  extern __shared__ __align__(16) uint8_t dn_ab_smem[];
+  __half* xs = reinterpret_cast<__half*>(dn_ab_smem);
+  const int H = p.H, r0 = blockIdx.x * DN_AB_ROWS, nr = min(DN_AB_ROWS, M - r0);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  pdl_wait();
+  pdl_launch();
+  for (int i = tid; i < DN_AB_ROWS * H / 8; i += 256) {
+    const int r = i / (H / 8), c = i - r * (H / 8);
+    reinterpret_cast<uint4*>(xs)[i] = r < nr ? __ldcg(reinterpret_cast<const uint4*>(p.xn + (size_t)(r0 + r) * H) + c) : make_uint4(0, 0, 0, 0);
+  }
+  __syncthreads();
+  for (int o = warp; o < 2 * p.Hv; o += 8) {
+    const float* w = o < p.Hv ? p.alpha_w + (size_t)o * H : p.beta_w + (size_t)(o - p.Hv) * H;
+    float acc[DN_AB_ROWS];
+#pragma unroll
+    for (int r = 0; r < DN_AB_ROWS; r++) acc[r] = 0.f;
+    for (int k = lane * 4; k < H; k += 128) {
+      const float4 wv = *reinterpret_cast<const float4*>(w + k);
+#pragma unroll
+      for (int r = 0; r < DN_AB_ROWS; r++) {
+        const uint2 xv = *reinterpret_cast<const uint2*>(xs + (size_t)r * H + k);
+        const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&xv.x)), f23 = __half22float2(*reinterpret_cast<const __half2*>(&xv.y));
+        acc[r] = fmaf(wv.w, f23.y, fmaf(wv.z, f23.x, fmaf(wv.y, f01.y, fmaf(wv.x, f01.x, acc[r]))));
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < DN_AB_ROWS; r++) {
+      const float v = warp_sum(acc[r]);
+      if (lane == 0 && r < nr) p.ab[(size_t)(r0 + r) * 2 * p.Hv + o] = v;
+    }
+  }
+}
+
 __global__ void __launch_bounds__(128) dn_pre_kernel(DnStepParams p) {
   const int D = 128, RB = 4;
   const int h = blockIdx.x / RB, rb = blockIdx.x % RB, hk = h % p.Hk;
   const SeqDesc sq = p.seqs[blockIdx.y];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qk = p.Hk * D, H = p.H;
-  __shared__ float red[16];
+  __shared__ float red[8];
   const int i0 = blockIdx.z * DN_PRE_TOKENS, i1 = min(sq.n, i0 + DN_PRE_TOKENS);
   if (i0 >= sq.n) return;
   const int ch_q = hk * D + tid, ch_k = qk + hk * D + tid, ch_v = 2 * qk + h * D + rb * 32 + (tid & 31);
@@ -1003,15 +1042,8 @@ __global__ void __launch_bounds__(128) dn_pre_kernel(DnStepParams p) {
   for (int i = i0; i < i1; i++) {
     const int row = sq.row0 + i;
     const float* pr = p.proj + (size_t)row * p.ldp;
-    const __half* xn = p.xn + (size_t)row * H;
-    float pa = 0.f, pb = 0.f;
-    for (int k = tid * 4; k < H; k += 512) {
-      const float4 wa = *reinterpret_cast<const float4*>(p.alpha_w + (size_t)h * H + k), wb = *reinterpret_cast<const float4*>(p.beta_w + (size_t)h * H + k);
-      const __half2 x01 = *reinterpret_cast<const __half2*>(xn + k), x23 = *reinterpret_cast<const __half2*>(xn + k + 2);
-      const float2 f01 = __half22float2(x01), f23 = __half22float2(x23);
-      pa += wa.x * f01.x + wa.y * f01.y + wa.z * f23.x + wa.w * f23.y;
-      pb += wb.x * f01.x + wb.y * f01.y + wb.z * f23.x + wb.w * f23.y;
-    }
+    float alpha = 0.f, betar = 0.f;
+    if (tid == 0) { alpha = __ldcg(p.ab + (size_t)row * 2 * p.Hv + h); betar = __ldcg(p.ab + (size_t)row * 2 * p.Hv + p.Hv + h); }
     const float cq = pr[ch_q], ck = pr[ch_k], cv = pr[ch_v];
     const float q = silu_acc(hq[0] * cwq.x + hq[1] * cwq.y + hq[2] * cwq.z + cq * cwq.w);
     const float k = silu_acc(hkk[0] * cwk.x + hkk[1] * cwk.y + hkk[2] * cwk.z + ck * cwk.w);
@@ -1020,13 +1052,11 @@ __global__ void __launch_bounds__(128) dn_pre_kernel(DnStepParams p) {
     hkk[0] = hkk[1]; hkk[1] = hkk[2]; hkk[2] = ck;
     hv[0] = hv[1]; hv[1] = hv[2]; hv[2] = cv;
     const float sq2 = warp_sum(q * q), sk2 = warp_sum(k * k);
-    pa = warp_sum(pa); pb = warp_sum(pb);
     __syncthreads();
-    if (lane == 0) { red[warp] = sq2; red[4 + warp] = sk2; red[8 + warp] = pa; red[12 + warp] = pb; }
+    if (lane == 0) { red[warp] = sq2; red[4 + warp] = sk2; }
     __syncthreads();
     const float qn = 1.0f / sqrtf(red[0] + red[1] + red[2] + red[3] + p.eps);
     const float kn = 1.0f / sqrtf(red[4] + red[5] + red[6] + red[7] + p.eps);
-    const float alpha = red[8] + red[9] + red[10] + red[11], betar = red[12] + red[13] + red[14] + red[15];
     float* out = p.pre + ((size_t)blockIdx.x * p.pre_rows + row) * DN_PACK;
     out[tid] = q * qn;
     out[128 + tid] = k * kn;
@@ -1350,7 +1380,11 @@ __global__ void __launch_bounds__(128) dn_post_kernel(DnStepParams p, int M) {
 int launch_dn_scan(const DnStepParams& p, int M, int max_n, bool pdl, cudaStream_t st) {
   if (p.D != 128 || p.conv != 4) { set_error("dn_scan: head dim must be 128 and conv kernel 4"); return EINVAL_; }
   if (p.mid != nullptr || p.pre == nullptr || p.o_raw == nullptr) { set_error("dn_scan: not available for speculative passes"); return EINVAL_; }
-  B200_TRY(launch_k(dn_pre_kernel, dim3(p.Hv * 4, p.n_seq, (max_n + DN_PRE_TOKENS - 1) / DN_PRE_TOKENS), dim3(128), 0, pdl, st, p));
+  if (p.ab == nullptr || p.H % 128 != 0 || (size_t)DN_AB_ROWS * p.H * 2 > 200 * 1024) { set_error("dn_scan: row length must be a multiple of 128 (at most 6400)"); return EINVAL_; }
+  const int ab_smem = DN_AB_ROWS * p.H * 2;
+  B200_ONCE_PER_DEVICE(cudaFuncSetAttribute(dn_ab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+  B200_TRY(launch_k(dn_ab_kernel, dim3((M + DN_AB_ROWS - 1) / DN_AB_ROWS), dim3(256), ab_smem, pdl, st, p, M));
+  B200_TRY(launch_k(dn_pre_kernel, dim3(p.Hv * 4, p.n_seq, (max_n + DN_PRE_TOKENS - 1) / DN_PRE_TOKENS), dim3(128), 0, true, st, p));
   if (max_n >= DN_CHUNK_FROM) {
     // long sequences: the recurrence in chunks of 64 tokens
     B200_ONCE_PER_DEVICE(cudaFuncSetAttribute(dn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DN_CHUNK_SMEM));

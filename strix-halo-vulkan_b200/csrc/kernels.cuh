@@ -73,6 +73,7 @@ struct DnStepParams {
   float* pre;                                // [Hv*4][pre_rows][292]
   int64_t pre_rows;
   float* o_raw;                              // [M][Hv*D]
+  float* ab;                                 // [M][2*Hv] alpha | beta projections of every row
   int H, Hk, Hv, D, conv;
   float eps;
   Timeline tl;
@@ -80,7 +81,8 @@ struct DnStepParams {
 constexpr int DN_RING = 8;      // positions kept per ring
 constexpr int DN_RING_W = 288;  // conv inputs per CTA: q 128 | k 128 | v 32
 int launch_dn_step(const DnStepParams& p, bool pdl, cudaStream_t st);
-// three launches: state-independent part for all tokens, the scan, the gated norm (max_n = longest sequence)
+// four launches: alpha / beta projections of all rows, the rest of the state-independent part, the scan, the gated
+// norm (max_n = longest sequence)
 int launch_dn_scan(const DnStepParams& p, int M, int max_n, bool pdl, cudaStream_t st);
 
 struct AttnParams {
