@@ -69,7 +69,13 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
 // kind::f16 instruction descriptor: f32 accumulate, fp16 A and B, both K-major, M 128, N tn
 __host__ __device__ constexpr uint32_t idesc_f16(int tn) { return (1u << 4) | ((uint32_t)(tn >> 3) << 17) | ((uint32_t)(GM_ROWS >> 4) << 24); }
 
-__device__ __forceinline__ uint4 ldg128(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+// Weight loads keep their place in the instruction stream (volatile): a block is asked for one whole block of work
+// before its first use, and a compiler free to sink the loads next to their uses would undo that.
+__device__ __forceinline__ uint4 ldg128(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
   __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -89,11 +95,19 @@ struct RawBlock {
   uint32_t d;
 };
 
-__device__ __forceinline__ void k4_scale_min_dev(int j, const uint4& hdr, int& sc, int& m) {  // gguf/dequant.go:238-243
-  const uint32_t w[3] = {hdr.y, hdr.z, hdr.w};
-  auto byte_at = [&](int i) { return (int)((w[i >> 2] >> (8 * (i & 3))) & 0xFF); };
-  if (j < 4) { sc = byte_at(j) & 63; m = byte_at(j + 4) & 63; }
-  else { sc = (byte_at(j + 4) & 0xF) | ((byte_at(j - 4) >> 6) << 4); m = (byte_at(j + 4) >> 4) | ((byte_at(j) >> 6) << 4); }
+// (scale, min) of sub-block 2 * pair + half (gguf/dequant.go:238-243). The twelve packed bytes are the words y, z, w
+// of the header quad; `pair` is a compile-time constant at every call, `half` may be a run-time value, so the byte
+// inside a word is picked by a shift and no array is indexed.
+__device__ __forceinline__ void k4_scale_min_dev(int pair, int half, const uint4& hdr, int& sc, int& m) {
+  const int sh = 8 * (2 * (pair & 1) + half);
+  if (pair < 2) {
+    sc = (int)((hdr.y >> sh) & 63);
+    m = (int)((hdr.z >> sh) & 63);
+  } else {
+    const uint32_t hi = (hdr.w >> sh) & 0xFF;
+    sc = (int)((hi & 0xF) | ((((hdr.y >> sh) & 0xFF) >> 6) << 4));
+    m = (int)((hi >> 4) | ((((hdr.z >> sh) & 0xFF) >> 6) << 4));
+  }
 }
 
 template <int TYPE>
@@ -141,16 +155,17 @@ __device__ __forceinline__ void bytes_to_h2(uint32_t w, uint32_t off, uint32_t& 
   p23 = hadd2_u(__byte_perm(w, 0x64646464u, 0x4342), off);
 }
 
-// HALF selects which 32 of the K step's 64 elements a thread forms: chunks 4*HALF .. 4*HALF+3.
-template <int TYPE, int HALF>
-__device__ __forceinline__ void dequant32(const RawBlock<TYPE>& r, int j, uint4 (&out)[4]) {
+// `half` selects which 32 of the K step's 64 elements a thread forms: chunks 4*half .. 4*half+3. It may be a run-time
+// value (the two halves of a row then share one instruction stream); j is a compile-time constant at every call.
+template <int TYPE>
+__device__ __forceinline__ void dequant32(const RawBlock<TYPE>& r, int j, int half, uint4 (&out)[4]) {
   if constexpr (TYPE == T_Q4_K || TYPE == T_Q5_K) {
-    // low nibbles are sub-block 2j (HALF 0), high nibbles sub-block 2j+1 (HALF 1); word w holds bytes 4w..4w+3
+    // low nibbles are sub-block 2j (half 0), high nibbles sub-block 2j+1 (half 1); word w holds bytes 4w..4w+3
     constexpr int QS = TYPE == T_Q4_K ? 1 : 3;  // first nibble quad
     const uint32_t m1024 = h2_bcast(-1024.f);
     const float d = h2f_lo(r.q[0].x), dmin = h2f_hi(r.q[0].x);
     int sc, m;
-    k4_scale_min_dev(2 * j + HALF, r.q[0], sc, m);
+    k4_scale_min_dev(j, half, r.q[0], sc, m);
     uint32_t dh, dl, nh, nl;
     h2_split(__fmul_rn(d, (float)sc), dh, dl);
     h2_split(-__fmul_rn(dmin, (float)m), nh, nl);
@@ -165,8 +180,8 @@ __device__ __forceinline__ void dequant32(const RawBlock<TYPE>& r, int j, uint4 
       uint32_t o[4];
 #pragma unroll
       for (int h = 0; h < 2; h++) {
-        uint32_t w = (qw[2 * c + h] >> (4 * HALF)) & 0x0F0F0F0Fu;
-        if constexpr (TYPE == T_Q5_K) w |= ((hb[2 * c + h] >> (2 * j + HALF)) & 0x01010101u) << 4;  // fifth bit -> bit 4
+        uint32_t w = (qw[2 * c + h] >> (4 * half)) & 0x0F0F0F0Fu;
+        if constexpr (TYPE == T_Q5_K) w |= ((hb[2 * c + h] >> (2 * j + half)) & 0x01010101u) << 4;  // fifth bit -> bit 4
         uint32_t a, b;
         bytes_to_h2(w, m1024, a, b);
         o[2 * h] = hadd2_u(hfma2_u(a, dh, nh), hfma2_u(a, dl, nl));
@@ -178,13 +193,13 @@ __device__ __forceinline__ void dequant32(const RawBlock<TYPE>& r, int j, uint4 
     // bytes are int8: flip the sign bit (b + 128 as unsigned), ride the exponent trick, take 1152 off
     const uint32_t m1152 = h2_bcast(-1152.f);
     const uint32_t dw[4] = {r.q[16].x, r.q[16].y, r.q[16].z, r.q[16].w};
-    const int bi = 2 * j + HALF;  // 32-element block of the super-block
-    const float dv = (bi & 1) ? h2f_hi(dw[bi >> 1]) : h2f_lo(dw[bi >> 1]);
+    const float dv = half ? h2f_hi(dw[j]) : h2f_lo(dw[j]);  // 32-element block 2j + half of the super-block
     uint32_t ds, dsl;
     h2_split(dv, ds, dsl);
 #pragma unroll
     for (int c = 0; c < 4; c++) {
-      const uint4 qv = r.q[4 * j + 2 * HALF + (c >> 1)];
+      const uint4 qlo = r.q[4 * j + (c >> 1)], qhi = r.q[4 * j + 2 + (c >> 1)];
+      const uint4 qv = half ? qhi : qlo;
       const uint32_t w0 = ((c & 1) ? qv.z : qv.x) ^ 0x80808080u, w1 = ((c & 1) ? qv.w : qv.y) ^ 0x80808080u;
       uint32_t a, b, e, f;
       bytes_to_h2(w0, m1152, a, b);
@@ -192,18 +207,19 @@ __device__ __forceinline__ void dequant32(const RawBlock<TYPE>& r, int j, uint4 
       out[c] = make_uint4(hfma2_u(a, ds, hmul2_u(a, dsl)), hfma2_u(b, ds, hmul2_u(b, dsl)), hfma2_u(e, ds, hmul2_u(e, dsl)), hfma2_u(f, ds, hmul2_u(f, dsl)));
     }
   } else {
-    const int hf = j >> 1, up = j & 1, quarter = 2 * up + HALF;  // half hf, quarter: elements l = 0..31
+    const int hf = j >> 1, up = j & 1, quarter = 2 * up + half;  // half hf, quarter: elements l = 0..31
     const float dd = __half2float(__ushort_as_half((unsigned short)r.d));
-    const uint4 l0 = r.q[4 * hf + 2 * HALF], l1 = r.q[4 * hf + 2 * HALF + 1], g0 = r.q[8 + 2 * hf], g1 = r.q[9 + 2 * hf];
+    const uint4 l0 = half ? r.q[4 * hf + 2] : r.q[4 * hf], l1 = half ? r.q[4 * hf + 3] : r.q[4 * hf + 1], g0 = r.q[8 + 2 * hf], g1 = r.q[9 + 2 * hf];
     const uint32_t lw[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
     const uint32_t hw[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
     const uint32_t scw[4] = {r.q[12].x, r.q[12].y, r.q[12].z, r.q[12].w};
     const uint32_t m1056 = h2_bcast(-1056.f);  // the 1024 of the exponent trick and the format's centre 32
 #pragma unroll
     for (int c = 0; c < 4; c++) {         // l = 8c .. 8c+7: words 2c, 2c+1; scale index 8*hf + l/16 + 2*quarter
-      const int si = 8 * hf + (c >> 1) + 2 * quarter;
+      // = 4 * (2*hf + up) + (c >> 1) + 2 * half: the word is fixed at compile time, the byte inside it is not
+      const uint32_t scword = scw[2 * hf + up];
       uint32_t ds, dsl;
-      h2_split(__fmul_rn(dd, (float)(int)(int8_t)((scw[si >> 2] >> (8 * (si & 3))) & 0xFF)), ds, dsl);
+      h2_split(__fmul_rn(dd, (float)(int)(int8_t)((scword >> (8 * ((c >> 1) + 2 * half))) & 0xFF)), ds, dsl);
       uint32_t o[4];
 #pragma unroll
       for (int h = 0; h < 2; h++) {
@@ -219,11 +235,10 @@ __device__ __forceinline__ void dequant32(const RawBlock<TYPE>& r, int j, uint4 
   }
 }
 
-// chunks 4*HALF .. 4*HALF+3 of row r of a [rows][128-byte] tile under the 128-byte swizzle
-template <int HALF>
-__device__ __forceinline__ void store_swizzled(uint8_t* tile, int r, const uint4 (&v)[4]) {
+// chunks 4*half .. 4*half+3 of row r of a [rows][128-byte] tile under the 128-byte swizzle
+__device__ __forceinline__ void store_swizzled(uint8_t* tile, int r, int half, const uint4 (&v)[4]) {
 #pragma unroll
-  for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(tile + r * 128 + (((4 * HALF + c) ^ (r & 7)) << 4)) = v[c];
+  for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(tile + r * 128 + (((4 * half + c) ^ (r & 7)) << 4)) = v[c];
 }
 
 template <int TYPE, int TN, int EPI>
@@ -320,9 +335,10 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
   } else {
     // ---- dequantisation, then the epilogue ------------------------------------------------------
     // warps 2..5 form the first 32 elements of every row's K step and drain the first half of the
-    // accumulator's columns, warps 6..9 the second halves: two warps per scheduler hide each other's latencies
-    auto role = [&](auto half_c) {
-    constexpr int HALF = decltype(half_c)::value;
+    // accumulator's columns, warps 6..9 the second halves: two warps per scheduler hide each other's latencies.
+    // Both halves run the same instructions (`half` is data), and the loop over a row's super-blocks is not
+    // unrolled, so the loop body stays small enough for the instruction caches.
+    const int half = warp >= 6 ? 1 : 0;
     const int r = ((warp - 2) & 3) * 32 + lane;    // weight row of the tile this thread dequantises
     const int q = warp & 3;                        // TMEM lane quarter this warp may read
     uint32_t it = 0, tcount = 0;
@@ -330,40 +346,33 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
       GemmProblem pr; int nt, tt;
       if (!item(idx, pr, nt, tt)) continue;
       const int wrow = min(nt * GM_ROWS + r, p.N - 1);
-      const uint8_t* row = p.w + (size_t)pr.expert * p.expert_stride + (size_t)wrow * p.stride;
-      const uint8_t* row2 = DUAL ? p.w2 + (size_t)pr.expert * p.expert_stride + (size_t)wrow * p.stride : nullptr;
-      bool ok = true;
-      // one K step: dequantise, wait for the stage to be free, store the swizzled tile, signal the MMA warp.
       // Gated pair: warps 2..5 form the whole K step of the gate tensor, warps 6..9 that of the up tensor
       // (a thread then holds super-blocks of one tensor only).
-      const uint8_t* myrow = DUAL && HALF ? row2 : row;
+      const uint8_t* myrow = (DUAL && half ? p.w2 : p.w) + (size_t)pr.expert * p.expert_stride + (size_t)wrow * p.stride;
+      bool ok = true;
+      // one K step: dequantise, wait for the stage to be free, store the swizzled tile, signal the MMA warp
       auto step = [&](const RawBlock<TYPE>& ra, int j) {
         const int s = it % NS;
         uint4 v[4], v2[4];
-        if constexpr (DUAL) { dequant32<TYPE, 0>(ra, j, v); dequant32<TYPE, 1>(ra, j, v2); }
-        else dequant32<TYPE, HALF>(ra, j, v);
+        if constexpr (DUAL) { dequant32<TYPE>(ra, j, 0, v); dequant32<TYPE>(ra, j, 1, v2); }
+        else dequant32<TYPE>(ra, j, half, v);
         if (!mbar_wait(&empty[s], ((it / NS) & 1) ^ 1)) { give_up(); ok = false; return; }
         uint8_t* a = smem + (size_t)s * STAGE;
-        if constexpr (DUAL) { store_swizzled<0>(a + HALF * A_BYTES, r, v); store_swizzled<1>(a + HALF * A_BYTES, r, v2); }
-        else store_swizzled<HALF>(a, r, v);
+        if constexpr (DUAL) { store_swizzled(a + half * A_BYTES, r, 0, v); store_swizzled(a + half * A_BYTES, r, 1, v2); }
+        else store_swizzled(a, r, half, v);
         fence_proxy_async();                       // make the generic-proxy stores visible to the tensor core
         __syncwarp();
         if (lane == 0) mbar_arrive(&full_a[s]);
         it++;
       };
-      auto fetch = [&](RawBlock<TYPE>& ra, int blk) {
-        if (blk < nb) load_raw<TYPE>(myrow, nb, blk, ra);
-      };
-      auto block = [&](const RawBlock<TYPE>& ra) {
+      RawBlock<TYPE> cur, nxt;
+      load_raw<TYPE>(myrow, nb, 0, cur);
+#pragma unroll 1
+      for (int blk = 0; blk < nb && ok; blk++) {
+        if (blk + 1 < nb) load_raw<TYPE>(myrow, nb, blk + 1, nxt);
 #pragma unroll
-        for (int j = 0; j < 4; j++) if (ok) step(ra, j);
-      };
-      RawBlock<TYPE> a0, a1;
-      fetch(a0, 0);
-      for (int blk = 0; blk < nb && ok; blk += 2) {
-        fetch(a1, blk + 1);
-        block(a0);
-        if (blk + 1 < nb && ok) { fetch(a0, blk + 2); block(a1); }
+        for (int j = 0; j < 4; j++) if (ok) step(cur, j);
+        cur = nxt;
       }
       if (!ok) break;
       if (!mbar_wait(&acc_full, tcount & 1)) { give_up(); break; }
@@ -371,7 +380,7 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
       const int orow = nt * GM_ROWS + q * 32 + lane;  // TMEM lane = weight row
       const int t0 = tt * TN;
 #pragma unroll 1
-      for (int c0 = HALF * (TN / 2); c0 < (HALF + 1) * (TN / 2); c0 += 32) {
+      for (int c0 = half * (TN / 2); c0 < (half + 1) * (TN / 2); c0 += 32) {
         uint32_t acc[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, acc);
         if constexpr (DUAL) {
@@ -404,9 +413,6 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
       if (lane == 0) mbar_arrive(&acc_empty);
       tcount++;
     }
-    };
-    if (warp < 6) role(std::integral_constant<int, 0>{});
-    else role(std::integral_constant<int, 1>{});
   }
   // ---- teardown: every thread arrives; tensor memory is released by the warp that took it -------
   tc_fence_before();
