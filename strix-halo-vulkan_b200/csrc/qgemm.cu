@@ -381,6 +381,10 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
       const int t0 = tt * TN;
 #pragma unroll 1
       for (int c0 = half * (TN / 2); c0 < (half + 1) * (TN / 2); c0 += 32) {
+        // output row of column c0 + lane (-1: past the problem's rows), fetched by the lanes side by side and handed
+        // round by shuffles: no store below waits for a load of its own
+        int my_row = -1;
+        if (t0 + c0 + lane < pr.count) my_row = p.y_rows != nullptr ? __ldg(p.y_rows + pr.y_row0 + t0 + c0 + lane) : pr.y_row0 + t0 + c0 + lane;
         uint32_t acc[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c0, acc);
         if constexpr (DUAL) {
@@ -388,23 +392,31 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
           tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + TN + c0, up);
 #pragma unroll
           for (int i = 0; i < 32; i++) {
-            const int t = t0 + c0 + i;
-            if (t < pr.count && orow < p.N) {
+            const int yr = __shfl_sync(0xffffffffu, my_row, i);
+            if (yr >= 0 && orow < p.N) {
               const float g = __uint_as_float(acc[i]), u = __uint_as_float(up[i]);
-              const int64_t yr = p.y_rows != nullptr ? p.y_rows[pr.y_row0 + t] : pr.y_row0 + t;
-              p.y16[yr * p.ldy + orow] = __float2half_rn(g * sigmoid_acc(g) * u);  // shaders/llm_moe_gemv.comp:777-781
+              p.y16[(int64_t)yr * p.ldy + orow] = __float2half_rn(g * sigmoid_acc(g) * u);  // shaders/llm_moe_gemv.comp:777-781
             }
+          }
+        } else if constexpr (EPI == GEMM_RESID) {
+          // the old values first, all of them in flight together, then the sums
+          float old[32];
+#pragma unroll
+          for (int i = 0; i < 32; i++) {
+            const int yr = __shfl_sync(0xffffffffu, my_row, i);
+            old[i] = 0.f;
+            if (yr >= 0 && orow < p.N) asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(old[i]) : "l"(p.y + (int64_t)yr * p.ldy + orow));
+          }
+#pragma unroll
+          for (int i = 0; i < 32; i++) {
+            const int yr = __shfl_sync(0xffffffffu, my_row, i);
+            if (yr >= 0 && orow < p.N) p.y[(int64_t)yr * p.ldy + orow] = old[i] + __uint_as_float(acc[i]);
           }
         } else {
 #pragma unroll
           for (int i = 0; i < 32; i++) {
-            const int t = t0 + c0 + i;
-            if (t < pr.count && orow < p.N) {
-              const int64_t yr = p.y_rows != nullptr ? p.y_rows[pr.y_row0 + t] : pr.y_row0 + t;
-              float* dst = p.y + yr * p.ldy + orow;
-              if constexpr (EPI == GEMM_RESID) *dst = *dst + __uint_as_float(acc[i]);
-              else *dst = __uint_as_float(acc[i]);
-            }
+            const int yr = __shfl_sync(0xffffffffu, my_row, i);
+            if (yr >= 0 && orow < p.N) p.y[(int64_t)yr * p.ldy + orow] = __uint_as_float(acc[i]);
           }
         }
       }
