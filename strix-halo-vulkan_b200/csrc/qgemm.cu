@@ -16,7 +16,7 @@ constexpr int GM_THREADS = 320;   // warp 0: TMA, warp 1: MMA + TMEM owner, warp
 constexpr int GM_ROWS = 128;      // weight rows per tile = UMMA M = TMEM lanes
 constexpr int GM_KSTEP = 64;      // fp16 elements per K step = one 128-byte swizzle row
 constexpr int A_BYTES = GM_ROWS * 128;
-constexpr int GM_SPROB = 512;     // problems cached in shared memory
+constexpr int GM_SPROB = 1024;    // most problems (experts) of a grouped launch: the list lives in shared memory
 
 __host__ __device__ constexpr int gm_stages(int tn, bool dual) { return tn >= 256 ? (dual ? 3 : 4) : tn >= 128 ? (dual ? 4 : 6) : (dual ? 5 : 8); }
 __host__ __device__ constexpr int gm_stage_bytes(int tn, bool dual) { return A_BYTES * (dual ? 2 : 1) + tn * 128; }
@@ -252,6 +252,7 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
   __shared__ uint32_t tmem_base_sm;
   __shared__ volatile int failed;
   __shared__ GemmProblem sprob[GM_SPROB];
+  __shared__ int stile[GM_SPROB + 1];   // activation tiles before each problem (exclusive scan)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   if (tid == 0) {
@@ -270,21 +271,38 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
 
   const int n_prob = p.n_problems != nullptr ? min(*p.n_problems, p.max_problems) : 1;
   const int K = p.K, nb = K / 256, ksteps = K / GM_KSTEP;
-  // work items: (activation-row tile, problem, weight-row tile), the weight tile fastest; items past a
-  // problem's rows are skipped, and since every problem has a first activation tile the live items of a
-  // grouped launch sit together at the front, spread evenly over the CTAs
-  const int n_tiles = (p.N + GM_ROWS - 1) / GM_ROWS, t_max = (p.max_count + TN - 1) / TN, per_tt = n_prob * n_tiles, total = t_max * per_tt;
-  auto item = [&](int idx, GemmProblem& pr, int& nt, int& tt) {
-    tt = idx / per_tt;
-    const int rem = idx - tt * per_tt, e = rem / n_tiles;
-    nt = rem - e * n_tiles;
-    pr = p.problems == nullptr ? p.one : e < GM_SPROB ? sprob[e] : p.problems[e];
-    return tt * TN < pr.count;
-  };
-  if (p.problems != nullptr) {  // the problem list is scanned by three roles: keep it in shared memory
-    for (int e = tid; e < n_prob && e < GM_SPROB; e += GM_THREADS) sprob[e] = p.problems[e];
-    __syncthreads();
+  // Work items: (problem, activation-row tile, weight-row tile), the weight tile fastest, over the tiles the problems
+  // really have: a scan of ceil(count / TN) per problem, made once per CTA, turns an item index into its problem by
+  // bisection. CTAs next to each other work on the same activation tile (read through L2 once).
+  const int n_tiles = (p.N + GM_ROWS - 1) / GM_ROWS;
+  if (p.problems != nullptr) {
+    for (int e = tid; e < n_prob; e += GM_THREADS) sprob[e] = p.problems[e];
+  } else if (tid == 0) {
+    sprob[0] = p.one;
   }
+  __syncthreads();
+  if (warp == 0) {
+    const int per = (n_prob + 31) / 32;
+    int c = 0;
+    for (int i = 0; i < per; i++) { const int e = lane * per + i; if (e < n_prob) c += (sprob[e].count + TN - 1) / TN; }
+    int cs = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const int up = __shfl_up_sync(0xffffffffu, cs, o); if (lane >= o) cs += up; }
+    int run = cs - c;
+    for (int i = 0; i < per; i++) { const int e = lane * per + i; if (e < n_prob) { stile[e] = run; run += (sprob[e].count + TN - 1) / TN; } }
+    if (lane == 31) stile[n_prob] = cs;
+  }
+  __syncthreads();
+  const int total = stile[n_prob] * n_tiles;
+  auto item = [&](int idx, GemmProblem& pr, int& nt, int& tt) {
+    const int tile = idx / n_tiles;
+    nt = idx - tile * n_tiles;
+    int lo = 0, hi = n_prob - 1;          // the last problem whose first tile is not after `tile`
+    while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (stile[mid] <= tile) lo = mid; else hi = mid - 1; }
+    pr = sprob[lo];
+    tt = tile - stile[lo];
+    return true;
+  };
   auto give_up = [&]() { if (p.err != nullptr) atomicExch(p.err, 1); failed = 1; };
 
   if (warp == 0) {
@@ -342,6 +360,8 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
     const int r = ((warp - 2) & 3) * 32 + lane;    // weight row of the tile this thread dequantises
     const int q = warp & 3;                        // TMEM lane quarter this warp may read
     uint32_t it = 0, tcount = 0;
+    RawBlock<TYPE> cur, nxt;
+    bool primed = false;                           // cur already holds the first block of the item about to start
     for (int idx = blockIdx.x; idx < total && !failed; idx += gridDim.x) {
       GemmProblem pr; int nt, tt;
       if (!item(idx, pr, nt, tt)) continue;
@@ -365,8 +385,7 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
         if (lane == 0) mbar_arrive(&full_a[s]);
         it++;
       };
-      RawBlock<TYPE> cur, nxt;
-      load_raw<TYPE>(myrow, nb, 0, cur);
+      if (!primed) load_raw<TYPE>(myrow, nb, 0, cur);
 #pragma unroll 1
       for (int blk = 0; blk < nb && ok; blk++) {
         if (blk + 1 < nb) load_raw<TYPE>(myrow, nb, blk + 1, nxt);
@@ -375,6 +394,15 @@ __global__ void __launch_bounds__(GM_THREADS) qgemm_kernel(const __grid_constant
         cur = nxt;
       }
       if (!ok) break;
+      // the first block of this thread's row in the CTA's next item is asked for now and arrives under the epilogue
+      primed = false;
+      if (idx + (int)gridDim.x < total) {
+        GemmProblem npr; int nnt, ntt;
+        item(idx + gridDim.x, npr, nnt, ntt);
+        const uint8_t* nrow = (DUAL && half ? p.w2 : p.w) + (size_t)npr.expert * p.expert_stride + (size_t)min(nnt * GM_ROWS + r, p.N - 1) * p.stride;
+        load_raw<TYPE>(nrow, nb, 0, cur);
+        primed = true;
+      }
       if (!mbar_wait(&acc_full, tcount & 1)) { give_up(); break; }
       tc_fence_after();
       const int orow = nt * GM_ROWS + q * 32 + lane;  // TMEM lane = weight row
@@ -444,7 +472,9 @@ int launch_t(const QGemmParams& p, const CUtensorMap& tm, bool pdl, cudaStream_t
   const int sm_count = sm_count_current();
   if (sm_count <= 0) return ECUDA;
   const int n_tiles = (p.N + GM_ROWS - 1) / GM_ROWS;
-  const int64_t total = (int64_t)(p.problems != nullptr ? p.max_problems : 1) * n_tiles * ((p.max_count + TN - 1) / TN);
+  if (p.problems != nullptr && p.max_problems > GM_SPROB) { set_error("qgemm: more problems than the kernel's shared-memory list holds (1024)"); return ECAPACITY; }
+  // upper bound of the items: every problem's tiles, each problem rounding up at most once
+  const int64_t total = ((int64_t)(p.max_count + TN - 1) / TN + (p.problems != nullptr ? p.max_problems : 0)) * n_tiles;
   const int gx = (int)std::max<int64_t>(1, std::min<int64_t>(total, sm_count)), gy = 1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(gx, gy); cfg.blockDim = dim3(GM_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
