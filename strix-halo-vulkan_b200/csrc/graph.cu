@@ -86,7 +86,7 @@ int Graph::init(Model* model, const b200_graph_opts& opts) {
   B200_TRY(dalloc(&r_ticket, (size_t)2 + MR / 8)); B200_TRY(dalloc(&err_flag, 1)); B200_TRY(dalloc(&ss_part, (size_t)MR * SS_LD)); B200_TRY(dalloc(&y16, (size_t)MR * vw));
   B200_TRY(dalloc(&act16, (size_t)MR * slots1 * c.ffn_expert)); B200_TRY(dalloc(&down, (size_t)MR * slots1 * H));
   B200_TRY(dalloc(&logits, (size_t)LR * c.vocab));
-  { B200_TRY(dalloc(&dn_pre, (size_t)c.dn_heads_v * 4 * MR * 292)); B200_TRY(dalloc(&dn_oraw, (size_t)MR * vw)); B200_TRY(dalloc(&dn_ab, (size_t)MR * 2 * c.dn_heads_v)); }
+  { B200_TRY(dalloc(&dn_pre, (size_t)MR * ((size_t)c.dn_heads_k * 256 + (size_t)c.dn_heads_v * 130))); B200_TRY(dalloc(&dn_oraw, (size_t)MR * vw)); B200_TRY(dalloc(&dn_ab, (size_t)MR * 2 * c.dn_heads_v)); }
   { std::vector<float> one(64, 1.f); B200_TRY(dalloc(&ones, one.size())); B200_CUDA(cudaMemcpy(ones, one.data(), one.size() * sizeof(float), cudaMemcpyHostToDevice)); }
   B200_TRY(dalloc(&xperm16, (size_t)MR * used * H)); B200_TRY(dalloc(&gprob, (size_t)c.n_expert)); B200_TRY(dalloc(&n_expert_dev, 1));
   B200_CUDA(cudaMemcpy(n_expert_dev, &c.n_expert, sizeof(int), cudaMemcpyHostToDevice));

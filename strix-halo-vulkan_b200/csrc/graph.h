@@ -36,7 +36,7 @@ struct Graph {
   __half *xn16 = nullptr, *q16 = nullptr, *ctx16 = nullptr, *act16 = nullptr, *y16 = nullptr, *xcat16 = nullptr;
   // TMA tensor maps of the fp16 activation buffers for the many-row GEMM, per tile height 64 / 128 / 256
   alignas(64) unsigned char tm_xn[3][128], tm_y16[3][128], tm_ctx[3][128], tm_xperm[3][128], tm_act[3][128];
-  float *dn_pre = nullptr, *dn_oraw = nullptr, *dn_ab = nullptr;   // many-token DeltaNet: packed scan inputs [Hv*4][rows][292], raw outputs [rows][Hv*D]
+  float *dn_pre = nullptr, *dn_oraw = nullptr, *dn_ab = nullptr;   // many-token DeltaNet: scan inputs (q | k per key head, v and decay | beta per value head), raw outputs [rows][Hv*D]
   int pass_max_n = 1;                            // longest sequence of the pass being enqueued
   float* ones = nullptr;       // [8] weights 1.0 (the combine of pre-weighted partial rows)
   __half* xperm16 = nullptr;   // [rows * used][H]: activation rows in expert-sorted order

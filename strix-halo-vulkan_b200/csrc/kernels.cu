@@ -966,7 +966,14 @@ __global__ void __launch_bounds__(512, 2) dn_head_kernel(DnStepParams p) {
 // in parallel and packed per (head, row block) and token; the scan then walks the tokens with no
 // block-wide synchronisation at all; the gated norm runs per token afterwards.
 // -----------------------------------------------------------------------------------------
-constexpr int DN_PACK = 292;   // floats per (CTA id, token): q 128 | k 128 | v 32 | decay | beta | pad 2
+// State-independent inputs of the many-token recurrence, written once per pass by dn_pre_kernel and read by every
+// CTA that needs them (the four row blocks of a head share its v, decay and beta; the value heads of a key head
+// share its q and k): [Hk][rows][256] normalised q | k, then [Hv][rows][128] v, then [Hv][rows][2] decay | beta.
+__device__ __forceinline__ float* dn_pre_qk(const DnStepParams& p, int hk, int64_t row) { return p.pre + ((size_t)hk * p.pre_rows + row) * 256; }
+__device__ __forceinline__ float* dn_pre_v(const DnStepParams& p, int h, int64_t row) { return p.pre + (size_t)p.Hk * p.pre_rows * 256 + ((size_t)h * p.pre_rows + row) * 128; }
+__device__ __forceinline__ float* dn_pre_gb(const DnStepParams& p, int h, int64_t row) {
+  return p.pre + (size_t)p.pre_rows * ((size_t)p.Hk * 256 + (size_t)p.Hv * 128) + ((size_t)h * p.pre_rows + row) * 2;
+}
 constexpr int DN_PRE_TOKENS = 16;
 constexpr int DN_CHUNK_FROM = 64;   // sequences of this many tokens and more run the chunked recurrence, shorter ones the token-by-token scan
 
@@ -1009,59 +1016,69 @@ __global__ void __launch_bounds__(256) dn_ab_kernel(DnStepParams p, int M) {
   }
 }
 
+// grid (Hk + Hv, n_seq, 16-token groups), block 128. CTAs [0, Hk): q and k of one key head (conv + SiLU + L2 norm);
+// CTAs [Hk, Hk + Hv): v of one value head (conv + SiLU) and the head's decay and beta from the projected alpha / beta.
+// Conv inputs of the positions before this pass come from the rings the decode kernels keep per (head, row block).
 __global__ void __launch_bounds__(128) dn_pre_kernel(DnStepParams p) {
   const int D = 128, RB = 4;
-  const int h = blockIdx.x / RB, rb = blockIdx.x % RB, hk = h % p.Hk;
+  const bool is_qk = (int)blockIdx.x < p.Hk;
+  const int hd = is_qk ? blockIdx.x : blockIdx.x - p.Hk;     // key head or value head
   const SeqDesc sq = p.seqs[blockIdx.y];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qk = p.Hk * D, H = p.H;
+  const int qk = p.Hk * D;
   __shared__ float red[8];
   const int i0 = blockIdx.z * DN_PRE_TOKENS, i1 = min(sq.n, i0 + DN_PRE_TOKENS);
   if (i0 >= sq.n) return;
-  const int ch_q = hk * D + tid, ch_k = qk + hk * D + tid, ch_v = 2 * qk + h * D + rb * 32 + (tid & 31);
-  const float4 cwq = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch_q * 4);
-  const float4 cwk = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch_k * 4);
-  const float4 cwv = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch_v * 4);
-  const float a_h = p.ssm_a[h], dtb = p.dt_bias[h];
-  float* ring = p.ring + (size_t)sq.slot * p.ring_slot_stride + (size_t)blockIdx.x * (DN_RING * DN_RING_W);
+  // channels of the projection row: two (q, k) for a key head, one (v) for a value head
+  const int ch_a = is_qk ? hd * D + tid : 2 * qk + hd * D + tid, ch_b = qk + hd * D + tid;
+  const float4 cwa = *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch_a * 4);
+  const float4 cwb = is_qk ? *reinterpret_cast<const float4*>(p.conv_w + (size_t)ch_b * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+  const float a_h = is_qk ? 0.f : p.ssm_a[hd], dtb = is_qk ? 0.f : p.dt_bias[hd];
+  // ring of the decode kernels' CTA (head, row block): q at 0..127 and k at 128..255 of any CTA of a head whose key head
+  // this is (head hd, block 0 is one), v at 256..287 of the block that owns the channel
+  const float* ring_a = p.ring + (size_t)sq.slot * p.ring_slot_stride + (size_t)(is_qk ? hd * RB : hd * RB + (tid >> 5)) * (DN_RING * DN_RING_W) + (is_qk ? tid : 256 + (tid & 31));
+  const float* ring_b = p.ring + (size_t)sq.slot * p.ring_slot_stride + (size_t)(hd * RB) * (DN_RING * DN_RING_W) + 128 + tid;
   pdl_wait();
   pdl_launch();
   // conv input of token index ii (may be negative: before this pass): the projection row, else the ring
-  auto input = [&](int ii, int ch, int ring_off) {
+  auto input = [&](int ii, int ch, const float* ring) {
     if (ii >= 0) return p.proj[(size_t)(sq.row0 + ii) * p.ldp + ch];
     const int pos = sq.pos0 + ii;
-    return pos >= 0 ? ring[(size_t)(pos & (DN_RING - 1)) * DN_RING_W + ring_off] : 0.f;
+    return pos >= 0 ? ring[(size_t)(pos & (DN_RING - 1)) * DN_RING_W] : 0.f;
   };
-  float hq[3], hkk[3], hv[3];
+  float ha[3], hb[3] = {0.f, 0.f, 0.f};
 #pragma unroll
   for (int j = 0; j < 3; j++) {
-    hq[j] = input(i0 - 3 + j, ch_q, tid);
-    hkk[j] = input(i0 - 3 + j, ch_k, 128 + tid);
-    hv[j] = input(i0 - 3 + j, ch_v, 256 + (tid & 31));
+    ha[j] = input(i0 - 3 + j, ch_a, ring_a);
+    if (is_qk) hb[j] = input(i0 - 3 + j, ch_b, ring_b);
   }
   for (int i = i0; i < i1; i++) {
     const int row = sq.row0 + i;
     const float* pr = p.proj + (size_t)row * p.ldp;
-    float alpha = 0.f, betar = 0.f;
-    if (tid == 0) { alpha = __ldcg(p.ab + (size_t)row * 2 * p.Hv + h); betar = __ldcg(p.ab + (size_t)row * 2 * p.Hv + p.Hv + h); }
-    const float cq = pr[ch_q], ck = pr[ch_k], cv = pr[ch_v];
-    const float q = silu_acc(hq[0] * cwq.x + hq[1] * cwq.y + hq[2] * cwq.z + cq * cwq.w);
-    const float k = silu_acc(hkk[0] * cwk.x + hkk[1] * cwk.y + hkk[2] * cwk.z + ck * cwk.w);
-    const float v = silu_acc(hv[0] * cwv.x + hv[1] * cwv.y + hv[2] * cwv.z + cv * cwv.w);
-    hq[0] = hq[1]; hq[1] = hq[2]; hq[2] = cq;
-    hkk[0] = hkk[1]; hkk[1] = hkk[2]; hkk[2] = ck;
-    hv[0] = hv[1]; hv[1] = hv[2]; hv[2] = cv;
-    const float sq2 = warp_sum(q * q), sk2 = warp_sum(k * k);
-    __syncthreads();
-    if (lane == 0) { red[warp] = sq2; red[4 + warp] = sk2; }
-    __syncthreads();
-    const float qn = 1.0f / sqrtf(red[0] + red[1] + red[2] + red[3] + p.eps);
-    const float kn = 1.0f / sqrtf(red[4] + red[5] + red[6] + red[7] + p.eps);
-    float* out = p.pre + ((size_t)blockIdx.x * p.pre_rows + row) * DN_PACK;
-    out[tid] = q * qn;
-    out[128 + tid] = k * kn;
-    if (tid < 32) out[256 + tid] = v;
-    if (tid == 0) { out[288] = expf(softplus_ref(alpha + dtb) * a_h); out[289] = sigmoid_acc(betar); }
+    const float ca = pr[ch_a];
+    const float va = silu_acc(ha[0] * cwa.x + ha[1] * cwa.y + ha[2] * cwa.z + ca * cwa.w);
+    ha[0] = ha[1]; ha[1] = ha[2]; ha[2] = ca;
+    if (is_qk) {
+      const float cb = pr[ch_b];
+      const float vb = silu_acc(hb[0] * cwb.x + hb[1] * cwb.y + hb[2] * cwb.z + cb * cwb.w);
+      hb[0] = hb[1]; hb[1] = hb[2]; hb[2] = cb;
+      const float sq2 = warp_sum(va * va), sk2 = warp_sum(vb * vb);
+      __syncthreads();
+      if (lane == 0) { red[warp] = sq2; red[4 + warp] = sk2; }
+      __syncthreads();
+      const float qn = 1.0f / sqrtf(red[0] + red[1] + red[2] + red[3] + p.eps);
+      const float kn = 1.0f / sqrtf(red[4] + red[5] + red[6] + red[7] + p.eps);
+      float* out = dn_pre_qk(p, hd, row);
+      out[tid] = va * qn;
+      out[128 + tid] = vb * kn;
+    } else {
+      dn_pre_v(p, hd, row)[tid] = va;
+      if (tid == 0) {
+        const float alpha = __ldcg(p.ab + (size_t)row * 2 * p.Hv + hd), betar = __ldcg(p.ab + (size_t)row * 2 * p.Hv + p.Hv + hd);
+        float* gb = dn_pre_gb(p, hd, row);
+        gb[0] = expf(softplus_ref(alpha + dtb) * a_h); gb[1] = sigmoid_acc(betar);
+      }
+    }
   }
 }
 
@@ -1086,18 +1103,20 @@ __global__ void __launch_bounds__(128) dn_scan_kernel(DnStepParams p) {
   const float oscale = 1.0f / sqrtf((float)D);
   pdl_wait();
   pdl_launch();
-  const float* pp = p.pre + ((size_t)blockIdx.x * p.pre_rows + sq.row0) * DN_PACK;
+  const float* pqk = dn_pre_qk(p, h % p.Hk, sq.row0);
+  const float* pv = dn_pre_v(p, h, sq.row0) + rb * 32;
+  const float* pgb = dn_pre_gb(p, h, sq.row0);
   float4 kq[16], nkq[16];  // k quarter (8 float4) then q quarter
   float vv, nvv = 0.f; float2 gb, ngb = make_float2(0.f, 0.f);
   auto fetch = [&](int i, float4 (&dst)[16], float& v, float2& g) {
-    const float* t = pp + (size_t)i * DN_PACK;
+    const float* t = pqk + (size_t)i * 256;
 #pragma unroll
     for (int u = 0; u < 8; u++) {
       dst[u] = __ldcg(reinterpret_cast<const float4*>(t + 128 + 32 * part + 4 * u));
       dst[8 + u] = __ldcg(reinterpret_cast<const float4*>(t + 32 * part + 4 * u));
     }
-    v = __ldcg(t + 256 + jl);
-    g = __ldcg(reinterpret_cast<const float2*>(t + 288));
+    v = __ldcg(pv + (size_t)i * 128 + jl);
+    g = __ldcg(reinterpret_cast<const float2*>(pgb + (size_t)i * 2));
   };
   fetch(0, kq, vv, gb);
   for (int i = 0; i < sq.n; i++) {
@@ -1190,7 +1209,9 @@ __global__ void __launch_bounds__(256, 1) dn_chunk_kernel(DnStepParams p) {
   const float oscale = 1.0f / sqrtf((float)D);
   pdl_wait();
   pdl_launch();
-  const float* pp = p.pre + ((size_t)blockIdx.x * p.pre_rows + sq.row0) * DN_PACK;
+  const float* pqk = dn_pre_qk(p, h % p.Hk, sq.row0);
+  const float* pv = dn_pre_v(p, h, sq.row0) + rb * 32;
+  const float* pgb = dn_pre_gb(p, h, sq.row0);
   const int ty = tid >> 4, tx = tid & 15;
   for (int c0 = 0; c0 < sq.n; c0 += DN_C) {
     const int n = min(DN_C, sq.n - c0);
@@ -1199,19 +1220,19 @@ __global__ void __launch_bounds__(256, 1) dn_chunk_kernel(DnStepParams p) {
     for (int idx = tid; idx < DN_C * 64; idx += 256) {
       const int t = idx >> 6, c = idx & 63;     // 64 float4 per token: 32 of q, 32 of k
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (t < n) v = __ldcg(reinterpret_cast<const float4*>(pp + (size_t)(c0 + t) * DN_PACK + 4 * c));
+      if (t < n) v = __ldcg(reinterpret_cast<const float4*>(pqk + (size_t)(c0 + t) * 256 + 4 * c));
       float* dst = (c < 32 ? Qs : Ks) + t * DN_KP + 4 * (c & 31);
       *reinterpret_cast<float4*>(dst) = v;
     }
     for (int idx = tid; idx < DN_C * 32; idx += 256) {
       const int t = idx >> 5, j = idx & 31;
-      Vs[idx] = t < n ? __ldcg(pp + (size_t)(c0 + t) * DN_PACK + 256 + j) : 0.f;
+      Vs[idx] = t < n ? __ldcg(pv + (size_t)(c0 + t) * 128 + j) : 0.f;
     }
     if (warp == 0) {                            // cumulative log decay of the chunk: two tokens per lane
       const int t0 = 2 * lane, t1 = t0 + 1;
-      const float g0 = t0 < n ? __ldcg(pp + (size_t)(c0 + t0) * DN_PACK + 288) : 1.f, g1 = t1 < n ? __ldcg(pp + (size_t)(c0 + t1) * DN_PACK + 288) : 1.f;
-      Bt[t0] = t0 < n ? __ldcg(pp + (size_t)(c0 + t0) * DN_PACK + 289) : 0.f;
-      Bt[t1] = t1 < n ? __ldcg(pp + (size_t)(c0 + t1) * DN_PACK + 289) : 0.f;
+      const float g0 = t0 < n ? __ldcg(pgb + (size_t)(c0 + t0) * 2) : 1.f, g1 = t1 < n ? __ldcg(pgb + (size_t)(c0 + t1) * 2) : 1.f;
+      Bt[t0] = t0 < n ? __ldcg(pgb + (size_t)(c0 + t0) * 2 + 1) : 0.f;
+      Bt[t1] = t1 < n ? __ldcg(pgb + (size_t)(c0 + t1) * 2 + 1) : 0.f;
       const float l0 = fmaxf(logf(g0), -87.f), l1 = fmaxf(logf(g1), -87.f);
       float run = l0 + l1;                      // inclusive scan over the lanes' pair sums
 #pragma unroll
@@ -1384,7 +1405,7 @@ int launch_dn_scan(const DnStepParams& p, int M, int max_n, bool pdl, cudaStream
   const int ab_smem = DN_AB_ROWS * p.H * 2;
   B200_ONCE_PER_DEVICE(cudaFuncSetAttribute(dn_ab_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
   B200_TRY(launch_k(dn_ab_kernel, dim3((M + DN_AB_ROWS - 1) / DN_AB_ROWS), dim3(256), ab_smem, pdl, st, p, M));
-  B200_TRY(launch_k(dn_pre_kernel, dim3(p.Hv * 4, p.n_seq, (max_n + DN_PRE_TOKENS - 1) / DN_PRE_TOKENS), dim3(128), 0, true, st, p));
+  B200_TRY(launch_k(dn_pre_kernel, dim3(p.Hk + p.Hv, p.n_seq, (max_n + DN_PRE_TOKENS - 1) / DN_PRE_TOKENS), dim3(128), 0, true, st, p));
   if (max_n >= DN_CHUNK_FROM) {
     // long sequences: the recurrence in chunks of 64 tokens
     B200_ONCE_PER_DEVICE(cudaFuncSetAttribute(dn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DN_CHUNK_SMEM));

@@ -69,8 +69,8 @@ struct DnStepParams {
   __half* y16;                               // [M][Hv*D] gated-norm output: fp16(rms(o) * norm_w * sigmoid(z))
   float* mid;                                // speculation: [n_seq][rows][Hv][D][D] state after each token; the slot's own state is then left untouched
   int64_t mid_stride, mid_seq_stride;        // floats between consecutive rows / sequences of mid
-  // many-token form (launch_dn_scan): packed per (CTA id, row) inputs of the scan, and its raw outputs
-  float* pre;                                // [Hv*4][pre_rows][292]
+  // many-token form (launch_dn_scan): state-independent inputs of the scan for every row, and its raw outputs
+  float* pre;                                // [Hk][pre_rows][256] q | k, [Hv][pre_rows][128] v, [Hv][pre_rows][2] decay | beta
   int64_t pre_rows;
   float* o_raw;                              // [M][Hv*D]
   float* ab;                                 // [M][2*Hv] alpha | beta projections of every row
