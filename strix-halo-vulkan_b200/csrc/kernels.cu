@@ -1178,26 +1178,35 @@ __global__ void __launch_bounds__(128) dn_scan_kernel(DnStepParams p) {
 // are f32 throughout in the reference's device path), so the matrix products run on the FMA pipe, register-tiled,
 // from shared memory; only the 64-step forward substitution for D is sequential, and it is 32 columns wide.
 // A CTA owns 32 state rows of one head, as dn_scan_kernel does, and reads the same packed inputs.
-// grid (Hv * 4, n_seq), block 256, dynamic shared memory DN_CHUNK_SMEM.
+// grid (Hv * 4, n_seq), block 512, dynamic shared memory DN_CHUNK_SMEM.
 // -----------------------------------------------------------------------------------------
 constexpr int DN_C = 64;                       // tokens per chunk
 constexpr int DN_KP = 132;                     // pitch of the K and Q rows (floats): 16-byte reads of rows tx, tx+16, .. fall on distinct banks
 constexpr int DN_AP = 68;                      // pitch of A and W rows
-constexpr int DN_SP = 33;                      // pitch of the transposed state block ST[i][j]
-constexpr size_t DN_CHUNK_SMEM = sizeof(float) * (2 * DN_C * DN_KP + 128 * DN_SP + 2 * DN_C * 32 + 2 * DN_C * DN_AP + 4 * DN_C);
+constexpr int DN_DP = 68;                      // pitch of the solved deltas, kept transposed: DT[j][r]
+constexpr size_t DN_CHUNK_SMEM = sizeof(float) * (2 * DN_C * DN_KP + 32 * DN_KP + DN_C * 32 + 32 * DN_DP + 2 * DN_C * DN_AP + 4 * DN_C);
 
-__global__ void __launch_bounds__(256, 1) dn_chunk_kernel(DnStepParams p) {
+__global__ void __launch_bounds__(512, 1) dn_chunk_kernel(DnStepParams p) {
   const int D = 128, RB = 4;
   const int h = blockIdx.x / RB, rb = blockIdx.x % RB;
   const SeqDesc sq = p.seqs[blockIdx.y];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // Two halves of eight warps work side by side: the first on what the forward substitution needs (A, then K S0^T
+  // and the right-hand sides) and later on the state, the second on what only the outputs need (Q S0^T, W, then the
+  // outputs). w8 / t2 are a thread's warp and thread index inside its half.
+  const bool second = warp >= 8;
+  const int w8 = warp & 7, t2 = tid & 255;
+  // products of token rows with the state block or the deltas: a lane takes four of the 32 columns j (j8 + 8m) and a
+  // quarter of the contraction range (cq), eight tokens (w8 + 8u) - 128 multiply-adds per twelve 16-byte reads -
+  // and the four lanes of a column add their quarters with two shuffles
+  const int j8 = lane & 7, cq = lane >> 3;
   extern __shared__ __align__(16) float dc_smem[];
   float* Ks = dc_smem;                          // [64][DN_KP]
   float* Qs = Ks + DN_C * DN_KP;                // [64][DN_KP]
-  float* ST = Qs + DN_C * DN_KP;                // [128 i][DN_SP]: the CTA's 32 state rows, transposed
-  float* Vs = ST + 128 * DN_SP;                 // [64][32] values, then R
-  float* Dm = Vs + DN_C * 32;                   // [64][32] the solved deltas
-  float* Am = Dm + DN_C * 32;                   // [64][DN_AP]
+  float* ST = Qs + DN_C * DN_KP;                // [32 j][DN_KP]: the CTA's 32 state rows
+  float* Vs = ST + 32 * DN_KP;                  // [64][32] values, then R
+  float* DT = Vs + DN_C * 32;                   // [32 j][DN_DP] the solved deltas, transposed
+  float* Am = DT + 32 * DN_DP;                  // [64][DN_AP]
   float* Wm = Am + DN_C * DN_AP;                // [64][DN_AP]
   float* Lg = Wm + DN_C * DN_AP;                // [64] cumulative log decay
   float* Bt = Lg + DN_C;                        // [64] beta
@@ -1205,26 +1214,26 @@ __global__ void __launch_bounds__(256, 1) dn_chunk_kernel(DnStepParams p) {
   float* Cr = Gm + DN_C;                        // [64] exp(L_C - L_r)
   float* Sg = p.state + (size_t)sq.slot * p.state_slot_stride + (size_t)h * D * D + (size_t)(rb * 32) * D;
   // the state block does not depend on the producer kernel
-  for (int idx = tid; idx < 32 * D; idx += 256) { const int j = idx >> 7, i = idx & 127; ST[i * DN_SP + j] = Sg[idx]; }
+  for (int idx = tid; idx < 32 * D; idx += 512) { const int j = idx >> 7, i = idx & 127; ST[j * DN_KP + i] = Sg[idx]; }
   const float oscale = 1.0f / sqrtf((float)D);
   pdl_wait();
   pdl_launch();
   const float* pqk = dn_pre_qk(p, h % p.Hk, sq.row0);
   const float* pv = dn_pre_v(p, h, sq.row0) + rb * 32;
   const float* pgb = dn_pre_gb(p, h, sq.row0);
-  const int ty = tid >> 4, tx = tid & 15;
+  const int ty = t2 >> 4, tx = t2 & 15;
   for (int c0 = 0; c0 < sq.n; c0 += DN_C) {
     const int n = min(DN_C, sq.n - c0);
     __syncthreads();                            // the previous chunk's readers are done with every buffer
     // ---- inputs: q, k rows (zero past the end), values, decay and beta ----
-    for (int idx = tid; idx < DN_C * 64; idx += 256) {
+    for (int idx = tid; idx < DN_C * 64; idx += 512) {
       const int t = idx >> 6, c = idx & 63;     // 64 float4 per token: 32 of q, 32 of k
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
       if (t < n) v = __ldcg(reinterpret_cast<const float4*>(pqk + (size_t)(c0 + t) * 256 + 4 * c));
       float* dst = (c < 32 ? Qs : Ks) + t * DN_KP + 4 * (c & 31);
       *reinterpret_cast<float4*>(dst) = v;
     }
-    for (int idx = tid; idx < DN_C * 32; idx += 256) {
+    for (int idx = tid; idx < DN_C * 32; idx += 512) {
       const int t = idx >> 5, j = idx & 31;
       Vs[idx] = t < n ? __ldcg(pv + (size_t)(c0 + t) * 128 + j) : 0.f;
     }
@@ -1243,28 +1252,25 @@ __global__ void __launch_bounds__(256, 1) dn_chunk_kernel(DnStepParams p) {
       Cr[t0] = expf(total - (run - l1)); Cr[t1] = expf(total - run);
     }
     __syncthreads();
-    // ---- A = beta ratio (K K^T) below the diagonal, W = ratio (Q K^T) on and below it: 4 x 4 per thread ----
-    {
-      float aa[4][4], ww[4][4];
+    // ---- a 64 x 64 product of token rows against the key rows, 4 x 4 per thread: the first half forms
+    //      A = beta ratio (K K^T) below the diagonal, the second W = ratio (Q K^T) on and below it ----
+    auto gram = [&](const float* Xs, float* Out, bool is_a) {
+      float aa[4][4];
 #pragma unroll
       for (int a = 0; a < 4; a++)
 #pragma unroll
-        for (int b = 0; b < 4; b++) { aa[a][b] = 0.f; ww[a][b] = 0.f; }
+        for (int b = 0; b < 4; b++) aa[a][b] = 0.f;
       for (int i = 0; i < D; i += 4) {
-        float4 kt[4], qt[4], kr[4];
+        float4 xt[4], kr[4];
 #pragma unroll
         for (int a = 0; a < 4; a++) {
-          kt[a] = *reinterpret_cast<const float4*>(Ks + (ty + 16 * a) * DN_KP + i);
-          qt[a] = *reinterpret_cast<const float4*>(Qs + (ty + 16 * a) * DN_KP + i);
+          xt[a] = *reinterpret_cast<const float4*>(Xs + (ty + 16 * a) * DN_KP + i);
           kr[a] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * a) * DN_KP + i);
         }
 #pragma unroll
         for (int a = 0; a < 4; a++)
 #pragma unroll
-          for (int b = 0; b < 4; b++) {
-            aa[a][b] += kt[a].x * kr[b].x + kt[a].y * kr[b].y + kt[a].z * kr[b].z + kt[a].w * kr[b].w;
-            ww[a][b] += qt[a].x * kr[b].x + qt[a].y * kr[b].y + qt[a].z * kr[b].z + qt[a].w * kr[b].w;
-          }
+          for (int b = 0; b < 4; b++) aa[a][b] += xt[a].x * kr[b].x + xt[a].y * kr[b].y + xt[a].z * kr[b].z + xt[a].w * kr[b].w;
       }
 #pragma unroll
       for (int a = 0; a < 4; a++)
@@ -1272,91 +1278,149 @@ __global__ void __launch_bounds__(256, 1) dn_chunk_kernel(DnStepParams p) {
         for (int b = 0; b < 4; b++) {
           const int t = ty + 16 * a, r = tx + 16 * b;
           const float ratio = r <= t ? expf(Lg[t] - Lg[r]) : 0.f;
-          Am[t * DN_AP + r] = r < t ? Bt[t] * ratio * aa[a][b] : 0.f;
-          Wm[t * DN_AP + r] = ratio * ww[a][b];
+          Out[t * DN_AP + r] = is_a ? (r < t ? Bt[t] * ratio * aa[a][b] : 0.f) : ratio * aa[a][b];
         }
-    }
-    // ---- KS = K S0^T, QS = Q S0^T: lane = state row j, warp w takes tokens w, w + 8, ... ----
-    float qs[8];
-    {
-      float ks[8];
+    };
+    // ---- out[m][u] = sum_c X[w8 + 8u][c] * Y[j8 + 8m][c] over `len` values of c: X rows of pitch xp (token rows
+    //      or W rows), Y rows of pitch yp (the state block or the transposed deltas) ----
+    auto rows_times = [&](const float* X, int xp, const float* Y, int yp, int len, float (&out)[4][8]) {
 #pragma unroll
-      for (int u = 0; u < 8; u++) { ks[u] = 0.f; qs[u] = 0.f; }
-      for (int i = 0; i < D; i += 4) {
-        const float s0 = ST[i * DN_SP + lane], s1 = ST[(i + 1) * DN_SP + lane], s2 = ST[(i + 2) * DN_SP + lane], s3 = ST[(i + 3) * DN_SP + lane];
+      for (int m = 0; m < 4; m++)
+#pragma unroll
+        for (int u = 0; u < 8; u++) out[m][u] = 0.f;
+      const int cbeg = cq * (len / 4);
+      for (int c = cbeg; c < cbeg + len / 4; c += 4) {
+        float4 yv[4];
+#pragma unroll
+        for (int m = 0; m < 4; m++) yv[m] = *reinterpret_cast<const float4*>(Y + (j8 + 8 * m) * yp + c);
 #pragma unroll
         for (int u = 0; u < 8; u++) {
-          const float4 kk = *reinterpret_cast<const float4*>(Ks + (warp + 8 * u) * DN_KP + i);
-          const float4 qq = *reinterpret_cast<const float4*>(Qs + (warp + 8 * u) * DN_KP + i);
-          ks[u] += kk.x * s0 + kk.y * s1 + kk.z * s2 + kk.w * s3;
-          qs[u] += qq.x * s0 + qq.y * s1 + qq.z * s2 + qq.w * s3;
+          const float4 xx = *reinterpret_cast<const float4*>(X + (w8 + 8 * u) * xp + c);
+#pragma unroll
+          for (int m = 0; m < 4; m++) out[m][u] += xx.x * yv[m].x + xx.y * yv[m].y + xx.z * yv[m].z + xx.w * yv[m].w;
         }
       }
 #pragma unroll
-      for (int u = 0; u < 8; u++) {
-        const int t = warp + 8 * u;
-        Vs[t * 32 + lane] = Bt[t] * (Vs[t * 32 + lane] - Gm[t] * ks[u]);   // R
-        qs[u] *= Gm[t];
-      }
-    }
-    __syncthreads();
-    // ---- forward substitution, one warp: D[t] = R[t] - sum_{r<t} A[t][r] D[r]; lane = column j ----
-    if (warp == 0) {
-      for (int t = 0; t < DN_C; t++) {
-        float a0 = Vs[t * 32 + lane], a1 = 0.f, a2 = 0.f, a3 = 0.f;
-        const float* ar = Am + t * DN_AP;
-        int r = 0;
-        for (; r + 4 <= t; r += 4) {
-          const float4 a = *reinterpret_cast<const float4*>(ar + r);
-          a0 -= a.x * Dm[r * 32 + lane]; a1 -= a.y * Dm[(r + 1) * 32 + lane];
-          a2 -= a.z * Dm[(r + 2) * 32 + lane]; a3 -= a.w * Dm[(r + 3) * 32 + lane];
-        }
-        for (; r < t; r++) a0 -= ar[r] * Dm[r * 32 + lane];
-        Dm[t * 32 + lane] = (a0 + a1) + (a2 + a3);   // read back by this lane only
-      }
-    }
-    __syncthreads();
-    // ---- outputs: o_t[j] = (Gamma_t QS + W D) / sqrt(D) ----
-    {
-      float acc[8];
-#pragma unroll
-      for (int u = 0; u < 8; u++) acc[u] = qs[u];
-      for (int r = 0; r < DN_C; r += 4) {
-        const float d0 = Dm[r * 32 + lane], d1 = Dm[(r + 1) * 32 + lane], d2 = Dm[(r + 2) * 32 + lane], d3 = Dm[(r + 3) * 32 + lane];
+      for (int m = 0; m < 4; m++)
 #pragma unroll
         for (int u = 0; u < 8; u++) {
-          const float4 w = *reinterpret_cast<const float4*>(Wm + (warp + 8 * u) * DN_AP + r);
-          acc[u] += w.x * d0 + w.y * d1 + w.z * d2 + w.w * d3;
+          out[m][u] += __shfl_xor_sync(0xffffffffu, out[m][u], 8);
+          out[m][u] += __shfl_xor_sync(0xffffffffu, out[m][u], 16);
         }
-      }
+    };
+    float qs[4][8];
+    if (!second) {
+      gram(Ks, Am, true);
+      float ks[4][8];
+      rows_times(Ks, DN_KP, ST, DN_KP, D, ks);
+      // right-hand sides R; of a column's four lanes, lane cq writes the tokens u = cq and cq + 4
 #pragma unroll
-      for (int u = 0; u < 8; u++) {
-        const int t = warp + 8 * u;
-        if (t < n) p.o_raw[(size_t)(sq.row0 + c0 + t) * (p.Hv * D) + h * D + rb * 32 + lane] = acc[u] * oscale;
+      for (int m = 0; m < 4; m++)
+#pragma unroll
+        for (int u = 0; u < 8; u++)
+          if ((u & 3) == cq) {
+            const int t = w8 + 8 * u, j = j8 + 8 * m;
+            Vs[t * 32 + j] = Bt[t] * (Vs[t * 32 + j] - Gm[t] * ks[m][u]);
+          }
+      asm volatile("bar.sync 1, 256;" ::: "memory");   // A and R are complete (the first half wrote them)
+      // ---- forward substitution D[t] = R[t] - sum_{r<t} A[t][r] D[r] in four blocks of 16 tokens: the part of the sum
+      //      that comes from the blocks already solved is taken off the block's right-hand sides by the whole half
+      //      (thread -> token t, columns j0 and j0 + 16), then one warp solves the 16 x 16 triangle with the block's
+      //      deltas in registers (lane = column j; every index is a compile-time constant, so the loads run ahead of
+      //      the chain of dependent multiply-adds) ----
+      for (int b = 0; b < DN_C / 16; b++) {
+        if (b > 0) {
+          const int t = 16 * b + (t2 >> 4), j0 = t2 & 15;
+          float s0 = 0.f, s1 = 0.f;
+          for (int r = 0; r < 16 * b; r += 4) {
+            const float4 a = *reinterpret_cast<const float4*>(Am + t * DN_AP + r);
+            const float4 d0 = *reinterpret_cast<const float4*>(DT + j0 * DN_DP + r), d1 = *reinterpret_cast<const float4*>(DT + (j0 + 16) * DN_DP + r);
+            s0 += a.x * d0.x + a.y * d0.y + a.z * d0.z + a.w * d0.w;
+            s1 += a.x * d1.x + a.y * d1.y + a.z * d1.z + a.w * d1.w;
+          }
+          Vs[t * 32 + j0] -= s0; Vs[t * 32 + j0 + 16] -= s1;
+          asm volatile("bar.sync 1, 256;" ::: "memory");
+        }
+        if (warp == 0) {
+          float d[16];
+#pragma unroll
+          for (int tl = 0; tl < 16; tl++) {
+            const int t = 16 * b + tl;
+            float acc = Vs[t * 32 + lane];
+            float av[16];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++)
+              if (4 * q4 < tl) {
+                const float4 a = *reinterpret_cast<const float4*>(Am + t * DN_AP + 16 * b + 4 * q4);
+                av[4 * q4] = a.x; av[4 * q4 + 1] = a.y; av[4 * q4 + 2] = a.z; av[4 * q4 + 3] = a.w;
+              }
+#pragma unroll
+            for (int r = 0; r < 16; r++)
+              if (r < tl) acc -= av[r] * d[r];
+            d[tl] = acc;
+          }
+          float* dl = DT + lane * DN_DP + 16 * b;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; q4++) *reinterpret_cast<float4*>(dl + 4 * q4) = make_float4(d[4 * q4], d[4 * q4 + 1], d[4 * q4 + 2], d[4 * q4 + 3]);
+        }
+        if (b + 1 < DN_C / 16) asm volatile("bar.sync 1, 256;" ::: "memory");   // the block's deltas are there for the next update
       }
+    } else {
+      rows_times(Qs, DN_KP, ST, DN_KP, D, qs);
+#pragma unroll
+      for (int m = 0; m < 4; m++)
+#pragma unroll
+        for (int u = 0; u < 8; u++) qs[m][u] *= Gm[w8 + 8 * u];
+      gram(Qs, Wm, false);
     }
-    // ---- state: ST[i][j] = Gamma_C ST[i][j] + sum_r Cr[r] K[r][i] D[r][j]; warp w takes i in [16w, 16w + 16) ----
-    {
-      float acc[16];
+    __syncthreads();
+    if (second) {
+      // ---- outputs: o_t[j] = (Gamma_t QS + W D) / sqrt(D) ----
+      float wd[4][8];
+      rows_times(Wm, DN_AP, DT, DN_DP, DN_C, wd);
+#pragma unroll
+      for (int m = 0; m < 4; m++)
+#pragma unroll
+        for (int u = 0; u < 8; u++)
+          if ((u & 3) == cq) {
+            const int t = w8 + 8 * u;
+            if (t < n) p.o_raw[(size_t)(sq.row0 + c0 + t) * (p.Hv * D) + h * D + rb * 32 + j8 + 8 * m] = (qs[m][u] + wd[m][u]) * oscale;
+          }
+    } else {
+      // ---- state: S[j][i] = Gamma_C S[j][i] + sum_r Cr[r] D[r][j] K[r][i]: a thread owns columns j = jp, jp + 16 and
+      //      the i in [i0, i0 + 4) and [i0 + 64, i0 + 68), and nobody else reads or writes them now (the products with the
+      //      old state are done) ----
+      const int jp = t2 >> 4, i0 = 4 * (t2 & 15);
+      float acc[2][8];
       const float gc = Gm[DN_C - 1];
 #pragma unroll
-      for (int u = 0; u < 16; u++) acc[u] = gc * ST[(16 * warp + u) * DN_SP + lane];
-      for (int r = 0; r < DN_C; r++) {
-        const float dr = Cr[r] * Dm[r * 32 + lane];
-        const float* kr = Ks + r * DN_KP + 16 * warp;
+      for (int jj = 0; jj < 2; jj++) {
+        const float4 s0 = *reinterpret_cast<const float4*>(ST + (jp + 16 * jj) * DN_KP + i0), s1 = *reinterpret_cast<const float4*>(ST + (jp + 16 * jj) * DN_KP + i0 + 64);
+        acc[jj][0] = gc * s0.x; acc[jj][1] = gc * s0.y; acc[jj][2] = gc * s0.z; acc[jj][3] = gc * s0.w;
+        acc[jj][4] = gc * s1.x; acc[jj][5] = gc * s1.y; acc[jj][6] = gc * s1.z; acc[jj][7] = gc * s1.w;
+      }
+      for (int r = 0; r < DN_C; r += 4) {
+        const float4 cr = *reinterpret_cast<const float4*>(Cr + r);
+        const float4 d0 = *reinterpret_cast<const float4*>(DT + jp * DN_DP + r), d1 = *reinterpret_cast<const float4*>(DT + (jp + 16) * DN_DP + r);
+        const float c0v[4] = {cr.x * d0.x, cr.y * d0.y, cr.z * d0.z, cr.w * d0.w}, c1v[4] = {cr.x * d1.x, cr.y * d1.y, cr.z * d1.z, cr.w * d1.w};
 #pragma unroll
-        for (int v4 = 0; v4 < 4; v4++) {
-          const float4 kk = *reinterpret_cast<const float4*>(kr + 4 * v4);
-          acc[4 * v4] += kk.x * dr; acc[4 * v4 + 1] += kk.y * dr; acc[4 * v4 + 2] += kk.z * dr; acc[4 * v4 + 3] += kk.w * dr;
+        for (int e = 0; e < 4; e++) {
+          const float4 k0 = *reinterpret_cast<const float4*>(Ks + (r + e) * DN_KP + i0), k1 = *reinterpret_cast<const float4*>(Ks + (r + e) * DN_KP + i0 + 64);
+          acc[0][0] += k0.x * c0v[e]; acc[0][1] += k0.y * c0v[e]; acc[0][2] += k0.z * c0v[e]; acc[0][3] += k0.w * c0v[e];
+          acc[0][4] += k1.x * c0v[e]; acc[0][5] += k1.y * c0v[e]; acc[0][6] += k1.z * c0v[e]; acc[0][7] += k1.w * c0v[e];
+          acc[1][0] += k0.x * c1v[e]; acc[1][1] += k0.y * c1v[e]; acc[1][2] += k0.z * c1v[e]; acc[1][3] += k0.w * c1v[e];
+          acc[1][4] += k1.x * c1v[e]; acc[1][5] += k1.y * c1v[e]; acc[1][6] += k1.z * c1v[e]; acc[1][7] += k1.w * c1v[e];
         }
       }
-      __syncthreads();                          // every warp has read the old state block (KS / QS above)
 #pragma unroll
-      for (int u = 0; u < 16; u++) ST[(16 * warp + u) * DN_SP + lane] = acc[u];
+      for (int jj = 0; jj < 2; jj++) {
+        *reinterpret_cast<float4*>(ST + (jp + 16 * jj) * DN_KP + i0) = make_float4(acc[jj][0], acc[jj][1], acc[jj][2], acc[jj][3]);
+        *reinterpret_cast<float4*>(ST + (jp + 16 * jj) * DN_KP + i0 + 64) = make_float4(acc[jj][4], acc[jj][5], acc[jj][6], acc[jj][7]);
+      }
     }
   }
   __syncthreads();
-  for (int idx = tid; idx < 32 * D; idx += 256) { const int j = idx >> 7, i = idx & 127; Sg[idx] = ST[i * DN_SP + j]; }
+  for (int idx = tid; idx < 32 * D; idx += 512) { const int j = idx >> 7, i = idx & 127; Sg[idx] = ST[j * DN_KP + i]; }
   // the ring keeps the last positions' conv inputs (written here, after every read of the old ring by the pre-pass)
   if (tid < 128) {
     const int hk = h % p.Hk, qk = p.Hk * D;
@@ -1409,7 +1473,7 @@ int launch_dn_scan(const DnStepParams& p, int M, int max_n, bool pdl, cudaStream
   if (max_n >= DN_CHUNK_FROM) {
     // long sequences: the recurrence in chunks of 64 tokens
     B200_ONCE_PER_DEVICE(cudaFuncSetAttribute(dn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DN_CHUNK_SMEM));
-    B200_TRY(launch_k(dn_chunk_kernel, dim3(p.Hv * 4, p.n_seq), dim3(256), DN_CHUNK_SMEM, true, st, p));
+    B200_TRY(launch_k(dn_chunk_kernel, dim3(p.Hv * 4, p.n_seq), dim3(512), DN_CHUNK_SMEM, true, st, p));
   } else {
     B200_TRY(launch_k(dn_scan_kernel, dim3(p.Hv * 4, p.n_seq), dim3(128), 0, true, st, p));
   }
