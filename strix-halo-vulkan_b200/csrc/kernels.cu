@@ -1176,8 +1176,8 @@ __global__ void __launch_bounds__(128) dn_scan_kernel(DnStepParams p) {
 // which is the token-by-token recurrence re-associated (llm/deltanet.go:365-418 is the sequential form; the
 // reference has no chunked one, llm/gpu_deltanet.go:48-52). Everything stays f32 (the state and the recurrence
 // are f32 throughout in the reference's device path), so the matrix products run on the FMA pipe, register-tiled,
-// from shared memory; only the 64-step forward substitution for D is sequential, and it is 32 columns wide.
-// A CTA owns 32 state rows of one head, as dn_scan_kernel does, and reads the same packed inputs.
+// from shared memory; only the forward substitution for D is sequential (32 columns wide, solved in four blocks of
+// 16 tokens). A CTA owns 32 state rows of one head, as dn_scan_kernel does, and reads the same inputs.
 // grid (Hv * 4, n_seq), block 512, dynamic shared memory DN_CHUNK_SMEM.
 // -----------------------------------------------------------------------------------------
 constexpr int DN_C = 64;                       // tokens per chunk
